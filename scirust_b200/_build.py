@@ -1,0 +1,114 @@
+"""In-tree native build: nvcc for the sm_100a CUDA library, g++ for the CPU runtime.
+
+Outputs land in ``scirust_b200/lib/`` next to the sources so that a snapshot of the
+repository carries the binaries with it:
+
+* ``libscirust_b200_cuda.so``  - every ``csrc/*.cu`` (tcgen05 GEMM, attention, decode, comm ...)
+* ``libscirust_b200_rt.so``    - every ``csrc/*.cpp`` (CPU runtime: fixed-order fp32 math,
+  arena / paged-KV block allocators, TCP tree all-reduce, samplers); no CUDA dependency.
+
+A source is recompiled when its object is older than it or than any header.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+CSRC = ROOT / "csrc"
+LIB = ROOT / "lib"
+OBJ = LIB / "obj"
+
+CUDA_LIB = LIB / "libscirust_b200_cuda.so"
+RT_LIB = LIB / "libscirust_b200_rt.so"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "--expt-relaxed-constexpr",
+    "-Xcompiler", "-fPIC",
+    "-Xcompiler", "-fvisibility=default",
+]
+# Deterministic fp32 paths are compiled without contraction or fast division so the
+# arithmetic is IEEE and reproducible (the reference's NVRTC build pins the same four
+# options: scirust-cuda/src/raw_runtime.rs:308-323).
+STRICT_FLAGS = ["-fmad=false", "-prec-div=true", "-prec-sqrt=true", "-ftz=false"]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-ffp-contract=off", "-pthread"]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    raise RuntimeError("nvcc not found")
+
+
+def _stale(src: Path, obj: Path, headers: list[Path]) -> bool:
+    if not obj.exists():
+        return True
+    t = obj.stat().st_mtime
+    return src.stat().st_mtime > t or any(h.stat().st_mtime > t for h in headers)
+
+
+def _run(cmd: list[str]) -> None:
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("build failed: " + " ".join(cmd) + "\n" + r.stdout + r.stderr)
+
+
+def build_cuda(force: bool = False, verbose: bool = False) -> Path:
+    OBJ.mkdir(parents=True, exist_ok=True)
+    headers = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
+    sources = sorted(CSRC.glob("*.cu"))
+    nvcc = _nvcc()
+    jobs = []
+    objs = []
+    for src in sources:
+        obj = OBJ / (src.stem + ".o")
+        objs.append(obj)
+        if force or _stale(src, obj, headers):
+            flags = list(NVCC_FLAGS)
+            if src.stem.endswith("_strict"):
+                flags += STRICT_FLAGS
+            if verbose:
+                flags += ["-Xptxas", "-v"]
+            jobs.append([nvcc, *flags, "-I", str(CSRC), "-c", str(src), "-o", str(obj)])
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            list(ex.map(_run, jobs))
+    if jobs or not CUDA_LIB.exists():
+        _run([nvcc, "-shared", "-o", str(CUDA_LIB), *map(str, objs), "-lcudart"])
+    return CUDA_LIB
+
+
+def build_rt(force: bool = False) -> Path:
+    OBJ.mkdir(parents=True, exist_ok=True)
+    headers = sorted(CSRC.glob("*.h")) + sorted(CSRC.glob("*.hpp"))
+    sources = sorted(CSRC.glob("*.cpp"))
+    cxx = os.environ.get("CXX", "g++")
+    objs, jobs = [], []
+    for src in sources:
+        obj = OBJ / (src.stem + ".cpp.o")
+        objs.append(obj)
+        if force or _stale(src, obj, headers):
+            jobs.append([cxx, *CXX_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)])
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            list(ex.map(_run, jobs))
+    if sources and (jobs or not RT_LIB.exists()):
+        _run([cxx, "-shared", "-pthread", "-o", str(RT_LIB), *map(str, objs)])
+    return RT_LIB
+
+
+def build_all(force: bool = False, verbose: bool = False) -> None:
+    build_cuda(force=force, verbose=verbose)
+    build_rt(force=force)
+
+
+if __name__ == "__main__":
+    build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    print("built:", CUDA_LIB, RT_LIB)

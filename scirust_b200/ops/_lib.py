@@ -1,0 +1,128 @@
+"""ctypes bindings for the two native libraries.
+
+``cuda()`` returns the handle of ``libscirust_b200_cuda.so`` (sm_100a kernels) and
+``rt()`` the handle of ``libscirust_b200_rt.so`` (CPU runtime). Both are built in-tree by
+``scirust_b200._build``; if a library is missing it is built on first use when a compiler
+is present, otherwise a clear error is raised - on a GPU machine the ops never fall back
+to another implementation silently.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import torch
+
+from .. import _build
+
+_cuda = None
+_rt = None
+
+vp, i32, i64, f32, sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
+
+ERRORS = {1: "bad argument", 2: "misaligned pointer or pitch", 3: "driver entry point unavailable",
+          4: "kernel launch failed", 5: "size beyond supported maximum", 6: "runtime error"}
+
+STATUS = {0: "ok", 1: "timeout: TMA stage never filled", 2: "timeout: stage never freed",
+          3: "timeout: accumulator never completed", 4: "timeout: accumulator never drained",
+          5: "timeout: peer flag never arrived", 6: "timeout", 7: "bad argument on device"}
+
+_CUDA_SIGS = {
+    "sb_gemm_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, i32, vp, vp],
+    "sb_rmsnorm_fwd": [vp, vp, vp, vp, i32, i32, i32, i32, f32, vp],
+    "sb_rmsnorm_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp],
+    "sb_rope": [vp, i32, i32, i32, i32, i32, i32, vp, vp, vp, i32, vp],
+    "sb_swiglu_fwd": [vp, vp, i32, i32, vp],
+    "sb_swiglu_bwd": [vp, vp, vp, i32, i32, vp],
+    "sb_add_bf16": [vp, vp, vp, sz, vp],
+    "sb_embed_fwd": [vp, vp, vp, i32, i32, i32, vp],
+    "sb_embed_bwd": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
+    "sb_ce_fwd_bwd": [vp, vp, vp, vp, i32, i32, i32, f32, vp],
+    "sb_sumsq": [vp, sz, i32, vp, vp, i32, vp],
+    "sb_optim_step": [vp, vp, vp, vp, i32, vp, sz, sz, f32, f32, f32, f32, f32, f32, f32, vp, f32, f32, i32, vp],
+    "sb_cast": [vp, vp, sz, i32, f32, vp],
+}
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def _load(path: Path, builder) -> C.CDLL:
+    if not path.exists():
+        builder()
+    if not path.exists():
+        raise NativeError(f"native library {path.name} is missing and could not be built")
+    return C.CDLL(str(path))
+
+
+def cuda() -> C.CDLL:
+    global _cuda
+    if _cuda is None:
+        lib = _load(_build.CUDA_LIB, _build.build_cuda)
+        for name, sig in _CUDA_SIGS.items():
+            if hasattr(lib, name):
+                fn = getattr(lib, name)
+                fn.argtypes = sig
+                fn.restype = i32
+        _cuda = lib
+    return _cuda
+
+
+def register(name: str, sig: list) -> None:
+    """Declare the signature of an entry point defined in another ops module."""
+    _CUDA_SIGS[name] = sig
+    if _cuda is not None and hasattr(_cuda, name):
+        fn = getattr(_cuda, name)
+        fn.argtypes = sig
+        fn.restype = i32
+
+
+def rt() -> C.CDLL:
+    global _rt
+    if _rt is None:
+        _rt = _load(_build.RT_LIB, _build.build_rt)
+    return _rt
+
+
+def ptr(t) -> int | None:
+    if t is None:
+        return None
+    return t.data_ptr()
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise NativeError(f"{what}: {ERRORS.get(rc, rc)}")
+
+
+def call(name: str, *args) -> None:
+    fn = getattr(cuda(), name)
+    check(fn(*args), name)
+
+
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def status_word(device=None) -> torch.Tensor:
+    """Per-device int32 word that kernels with bounded waits write an error code into."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    w = _status_words.get(key)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=dev)
+        _status_words[key] = w
+    return w
+
+
+def check_status(device=None) -> None:
+    """Synchronising read of the status word; raises if any kernel recorded a timeout."""
+    w = status_word(device)
+    code = int(w.item())
+    if code != 0:
+        w.zero_()
+        raise NativeError(f"device kernel reported: {STATUS.get(code, code)}")

@@ -1,0 +1,130 @@
+"""bf16 GEMM on the hand-written tcgen05/TMEM/TMA kernel (csrc/gemm_tcgen05.cu).
+
+Three storage forms cover forward, input-gradient and weight-gradient products without
+any transpose copy (the reference calls cuBLASLt for the same three forms,
+scirust-cuda/src/chain.rs:1037,1177,1228):
+
+* ``matmul_nn(x[M,K], w[K,N])``       forward with ``[in, out]`` weights (x·W layout)
+* ``matmul_nt(a[M,K], b[N,K])``       a · bᵀ (input gradient, tied LM head)
+* ``matmul_tn(a[K,M], b[K,N])``       aᵀ · b (weight gradient), split-K in fixed order
+
+CPU tensors take the plain PyTorch path (fp32 accumulate, bf16 result) so model logic can
+be tested without a GPU; CUDA tensors always run the native kernel.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+_NUM_SMS = 148
+_workspaces: dict[int, torch.Tensor] = {}
+
+# Count of native kernel launches, for benchmark reporting.
+launch_count = 0
+
+
+def _workspace(nfloats: int, device) -> torch.Tensor:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nfloats:
+        ws = torch.empty(max(nfloats, 1 << 22), dtype=torch.float32, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _pick_splits(M: int, N: int, K: int, bn: int) -> int:
+    tiles = ((M + 127) // 128) * ((N + bn - 1) // bn)
+    num_kb = (K + 63) // 64
+    if tiles >= _NUM_SMS // 2 or num_kb < 16:
+        return 1
+    s = min((_NUM_SMS + tiles - 1) // tiles, num_kb // 8, 16)
+    return max(1, s)
+
+
+def _check2d(t: torch.Tensor, name: str) -> None:
+    if t.dim() != 2 or t.dtype != torch.bfloat16 or t.stride(1) != 1:
+        raise ValueError(f"{name}: expected a 2-D bf16 matrix with unit inner stride, got "
+                         f"{tuple(t.shape)} {t.dtype} strides {t.stride()}")
+
+
+def _gemm(a, b, M, N, K, a_mn, b_mn, out, residual, splits, bn):
+    global launch_count
+    _check2d(a, "a")
+    _check2d(b, "b")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    else:
+        _check2d(out, "out")
+        if tuple(out.shape) != (M, N):
+            raise ValueError(f"out has shape {tuple(out.shape)}, expected {(M, N)}")
+    if residual is not None:
+        _check2d(residual, "residual")
+        if tuple(residual.shape) != (M, N):
+            raise ValueError("residual shape mismatch")
+    if bn is None:
+        bn = 128 if N <= 128 else 256
+    if splits is None:
+        splits = _pick_splits(M, N, K, bn)
+    ws = _workspace(splits * M * N, a.device) if splits > 1 else None
+    st = _lib.status_word(a.device)
+    _lib.call("sb_gemm_bf16", a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(residual), M, N, K,
+              a.stride(0), b.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
+              int(a_mn), int(b_mn), splits, _lib.ptr(ws), bn, st.data_ptr(), _lib.stream())
+    launch_count += 2 if splits > 1 else 1
+    return out
+
+
+def _ref(a, b, residual, out):
+    y = a.float() @ b.float()
+    if residual is not None:
+        y = y + residual.float()
+    y = y.to(torch.bfloat16)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def matmul_nn(x, w, residual=None, out=None, splits=None, bn=None):
+    """x[M,K] @ w[K,N] (+ residual) -> bf16 [M,N]."""
+    M, K = x.shape
+    K2, N = w.shape
+    if K != K2:
+        raise ValueError(f"matmul_nn: inner dims differ ({K} vs {K2})")
+    if not x.is_cuda:
+        return _ref(x, w, residual, out)
+    return _gemm(x, w, M, N, K, False, True, out, residual, splits, bn)
+
+
+def matmul_nt(a, b, residual=None, out=None, splits=None, bn=None):
+    """a[M,K] @ b[N,K]ᵀ (+ residual) -> bf16 [M,N]."""
+    M, K = a.shape
+    N, K2 = b.shape
+    if K != K2:
+        raise ValueError(f"matmul_nt: inner dims differ ({K} vs {K2})")
+    if not a.is_cuda:
+        return _ref(a, b.t(), residual, out)
+    return _gemm(a, b, M, N, K, False, False, out, residual, splits, bn)
+
+
+def matmul_tn(a, b, residual=None, out=None, splits=None, bn=None):
+    """a[K,M]ᵀ @ b[K,N] (+ residual) -> bf16 [M,N]; the weight-gradient form."""
+    K, M = a.shape
+    K2, N = b.shape
+    if K != K2:
+        raise ValueError(f"matmul_tn: inner dims differ ({K} vs {K2})")
+    if not a.is_cuda:
+        return _ref(a.t(), b, residual, out)
+    return _gemm(a, b, M, N, K, True, True, out, residual, splits, bn)
+
+
+def matmul_tt_a(a, b, residual=None, out=None, splits=None, bn=None):
+    """a[K,M]ᵀ @ b[N,K]ᵀ -> bf16 [M,N] (A MN-major, B K-major); completes the set."""
+    K, M = a.shape
+    N, K2 = b.shape
+    if K != K2:
+        raise ValueError("matmul_tt_a: inner dims differ")
+    if not a.is_cuda:
+        return _ref(a.t(), b.t(), residual, out)
+    return _gemm(a, b, M, N, K, True, False, out, residual, splits, bn)

@@ -1,0 +1,77 @@
+"""tcgen05 GEMM against a plain fp32 PyTorch reference, all operand forms."""
+import pytest
+import torch
+
+from scirust_b200 import ops
+from scirust_b200.ops import _lib
+
+pytestmark = pytest.mark.gpu
+
+
+def _mk(shape, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+
+
+def _check(y, ref, K):
+    _lib.check_status()
+    err = (y.float() - ref).abs().max().item()
+    tol = 2e-2 * max(1.0, ref.abs().max().item())
+    assert err <= tol, f"max err {err} > {tol}"
+
+
+SHAPES = [(128, 128, 64), (256, 256, 256), (384, 512, 1024), (200, 264, 136), (2048, 1536, 1024), (1000, 5632, 1024)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_nn(M, N, K):
+    x, w = _mk((M, K), 1), _mk((K, N), 2)
+    _check(ops.matmul_nn(x, w), x.float() @ w.float(), K)
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_nt(M, N, K):
+    a, b = _mk((M, K), 3), _mk((N, K), 4)
+    _check(ops.matmul_nt(a, b), a.float() @ b.float().t(), K)
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_tn(M, N, K):
+    a, b = _mk((K, M), 5), _mk((K, N), 6)
+    _check(ops.matmul_tn(a, b, splits=1), a.float().t() @ b.float(), K)
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES[:4])
+def test_tt_a(M, N, K):
+    a, b = _mk((K, M), 7), _mk((N, K), 8)
+    _check(ops.matmul_tt_a(a, b), a.float().t() @ b.float().t(), K)
+
+
+def test_residual_and_bn128():
+    x, w, r = _mk((512, 1024), 1), _mk((1024, 1024), 2), _mk((512, 1024), 9)
+    ref = x.float() @ w.float() + r.float()
+    _check(ops.matmul_nn(x, w, residual=r), ref, 1024)
+    _check(ops.matmul_nn(x, w, residual=r, bn=128), ref, 1024)
+
+
+def test_splitk_fixed_order_is_repeatable():
+    a, b, r = _mk((8192, 1024), 5), _mk((8192, 1536), 6), _mk((1024, 1536), 3)
+    ref = a.float().t() @ b.float() + r.float()
+    y1 = ops.matmul_tn(a, b, residual=r, splits=8)
+    y2 = ops.matmul_tn(a, b, residual=r, splits=8)
+    _check(y1, ref, 8192)
+    assert torch.equal(y1, y2)
+    y3 = ops.matmul_tn(a, b, residual=r)  # heuristic split
+    _check(y3, ref, 8192)
+
+
+def test_strided_views():
+    big = _mk((512, 3072), 11)
+    x = big[:, 1024:2048]  # pitch 3072, offset 2048 bytes
+    w = _mk((1024, 256), 12)
+    out = torch.zeros((512, 1024), dtype=torch.bfloat16, device="cuda")
+    ops.matmul_nn(x, w, out=out[:, 512:768])
+    _lib.check_status()
+    ref = x.float() @ w.float()
+    assert (out[:, 512:768].float() - ref).abs().max().item() < 0.3
+    assert out[:, :512].abs().max().item() == 0 and out[:, 768:].abs().max().item() == 0
