@@ -1,0 +1,551 @@
+// GQA flash-attention backward for sm_100a on tcgen05 tensor cores, without atomics.
+//
+// Three launches:
+//   1. delta[b,h,s] = sum_d dO * O                                   (bandwidth-bound)
+//   2. dK/dV: one CTA per (128-row kv tile, kv head, batch); loops over the query heads of
+//      the group and over query tiles in ascending order, accumulating dK and dV in tensor
+//      memory:  S^T = K Q^T,  dP^T = V dO^T,  dV += P^T dO,  dK += dS^T Q
+//   3. dQ: one CTA per (128-row query tile, head, batch); loops over kv tiles in ascending
+//      order:   S = Q K^T,  dP = dO V^T,  dQ += dS K
+// Every sum has a fixed order, so gradients are bitwise repeatable (the reference gets the
+// same property from per-(sequence, head) serial launches: cuda_model.rs:948-999, and
+// softmax_bwd / scale_mask_bwd in scirust-cuda/src/chain.rs:479,337).
+//
+// P is recomputed from the saved log-sum-exp; dS = P * (dP - delta) * scale.
+#include "sm100_ptx.cuh"
+#include "api.h"
+
+namespace sb {
+
+int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_outer);
+
+constexpr int BT = 128;          // tile edge (query rows and kv rows)
+constexpr int BWD_THREADS = 192;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct BwdParams {
+  int B, S, H, Hkv;
+  int ld_dqkv;
+  float scale, scale_log2;
+  int causal;
+  const float* lse;    // [B,H,S]
+  const float* delta;  // [B,H,S]
+  __nv_bfloat16* dqkv; // [B*S, ld_dqkv]
+  int* status;
+};
+
+// Store 32 bf16 (packed in 16 words) of row r, columns [c*32, c*32+32) into a [128 x 128] bf16 tile
+// laid out as two 128-byte-swizzled K-major chunks of 64 columns.
+__device__ __forceinline__ void store_row32_sw128(uint8_t* tile, int r, int c, const uint32_t* pk) {
+  uint8_t* prow = tile + (c >> 1) * (BT * 128) + r * 128;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int unit = ((c & 1) * 4 + u) ^ (r & 7);
+    *reinterpret_cast<uint4*>(prow + unit * 16) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
+  }
+}
+
+// --------------------------------------------------------------------------- delta
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                  float* __restrict__ delta, int B, int S, int H, int dh, int ld_o, int ld_do) {
+  const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (w >= B * S * H) return;
+  const int row = w / H, h = w - row * H;
+  const __nv_bfloat16* po = o + static_cast<size_t>(row) * ld_o + h * dh;
+  const __nv_bfloat16* pd = d_o + static_cast<size_t>(row) * ld_do + h * dh;
+  float acc = 0.f;
+  for (int c = lane * 2; c < dh; c += 64) {
+    const uint32_t a = *reinterpret_cast<const uint32_t*>(po + c);
+    const uint32_t g = *reinterpret_cast<const uint32_t*>(pd + c);
+    acc += bf16_lo(a) * bf16_lo(g) + bf16_hi(a) * bf16_hi(g);
+  }
+#pragma unroll
+  for (int o2 = 16; o2 > 0; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
+  if (lane == 0) {
+    const int b = row / S, s = row - b * S;
+    delta[(static_cast<size_t>(b) * H + h) * S + s] = acc;
+  }
+}
+
+// --------------------------------------------------------------------------- dK / dV
+template <int DH>
+struct DkvCfg {
+  static constexpr int QS = (DH == 64) ? 2 : 1;       // (Q, dO) ring stages
+  static constexpr int T_BYTES = BT * DH * 2;         // one [128 x DH] tile
+  static constexpr int PT_BYTES = BT * BT * 2;
+  static constexpr int TILE_BYTES = 2 * T_BYTES + QS * 2 * T_BYTES + 2 * PT_BYTES;
+  static constexpr int SMEM_BYTES = TILE_BYTES + 2 * 4 * BT * 4 + 1024 + 128;
+  static constexpr int TMEM_COLS = 512;  // S^T 128 | dP^T 128 | dK DH | dV DH
+};
+
+template <int DH>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
+                         const BwdParams p) {
+  using Cfg = DkvCfg<DH>;
+  constexpr int NCH = DH / 64;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + Cfg::T_BYTES;
+  uint8_t* sQ = sV + Cfg::T_BYTES;                 // QS stages
+  uint8_t* sdO = sQ + Cfg::QS * Cfg::T_BYTES;      // QS stages
+  uint8_t* sPT = sdO + Cfg::QS * Cfg::T_BYTES;
+  uint8_t* sdST = sPT + Cfg::PT_BYTES;
+  // Per-warp private copies of the query tile's LSE and delta (no cross-warp barrier is needed,
+  // so a warp that gives up on a wait can never strand another warp at a barrier).
+  float* s_lse = reinterpret_cast<float*>(sdST + Cfg::PT_BYTES);  // [4 warps][128]
+  float* s_delta = s_lse + 4 * BT;                                // [4 warps][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 4 * BT);
+  uint64_t* kv_full = bars;
+  uint64_t* q_full = bars + 1;            // QS
+  uint64_t* q_empty = q_full + Cfg::QS;   // QS
+  uint64_t* st_full = q_empty + Cfg::QS;
+  uint64_t* p_full = st_full + 1;
+  uint64_t* done = p_full + 1;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(done + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_t = (p.S + BT - 1) / BT;
+  const int kt = blockIdx.x;  // kv tile
+  const int kvh = blockIdx.y, b = blockIdx.z;
+  const int group = p.H / p.Hkv;
+  const int kv0 = kt * BT;
+  const int row_base = b * p.S;
+  const int qt_first = p.causal ? kt : 0;
+  const int n_qt = n_t - qt_first;
+  const int n_iter = group * n_qt;  // iteration t -> head kvh*group + t / n_qt, q tile qt_first + t % n_qt
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < Cfg::QS; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
+    mbar_init(st_full, 1);
+    mbar_init(p_full, 4);
+    mbar_init(done, 1);
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 0 && lane == 0) { prefetch_tmap(&tm_qkv); prefetch_tmap(&tm_do); }
+  if (warp == 1) { tmem_alloc(tmem_holder, Cfg::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+  const uint32_t tm_ST = tmem_base, tm_dPT = tmem_base + 128, tm_dK = tmem_base + 256, tm_dV = tmem_base + 256 + DH;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(kv_full, 2 * Cfg::T_BYTES);
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        tma_load_2d(sK + c * (BT * 128), &tm_qkv, kv_full, (p.H + kvh) * DH + c * 64, row_base + kv0);
+        tma_load_2d(sV + c * (BT * 128), &tm_qkv, kv_full, (p.H + p.Hkv + kvh) * DH + c * 64, row_base + kv0);
+      }
+      int st = 0;
+      uint32_t ph = 0;
+      for (int t = 0; t < n_iter; ++t) {
+        const int head = kvh * group + t / n_qt;
+        const int qt = qt_first + t % n_qt;
+        if (!mbar_wait(&q_empty[st], ph ^ 1, p.status, ST_TIMEOUT_EMPTY)) break;
+        mbar_arrive_expect_tx(&q_full[st], 2 * Cfg::T_BYTES);
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          tma_load_2d(sQ + st * Cfg::T_BYTES + c * (BT * 128), &tm_qkv, &q_full[st], head * DH + c * 64,
+                      row_base + qt * BT);
+          tma_load_2d(sdO + st * Cfg::T_BYTES + c * (BT * 128), &tm_do, &q_full[st], head * DH + c * 64,
+                      row_base + qt * BT);
+        }
+        if (++st == Cfg::QS) { st = 0; ph ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(BT, BT, false, false);   // [kv x q], both K-major
+      constexpr uint32_t idesc_g = make_idesc_bf16(BT, DH, false, true);    // [kv x dh], B MN-major
+      bool ok = mbar_wait(kv_full, 0, p.status, ST_TIMEOUT_FULL);
+      int st = 0;
+      uint32_t ph = 0;
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
+      auto issue_scores = [&](int stage, uint32_t phase) -> bool {
+        if (!mbar_wait(&q_full[stage], phase, p.status, ST_TIMEOUT_FULL)) return false;
+        tc_fence_after();
+        const uint32_t bQ = smem_u32(sQ + stage * Cfg::T_BYTES), bdO = smem_u32(sdO + stage * Cfg::T_BYTES);
+#pragma unroll
+        for (int k = 0; k < DH / 16; ++k) {
+          const uint32_t off = (k >> 2) * (BT * 128) + (k & 3) * 32;
+          umma_bf16_ss(tm_ST, make_smem_desc(aK + off, 16, 1024), make_smem_desc(bQ + off, 16, 1024), idesc_s,
+                       k > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < DH / 16; ++k) {
+          const uint32_t off = (k >> 2) * (BT * 128) + (k & 3) * 32;
+          umma_bf16_ss(tm_dPT, make_smem_desc(aV + off, 16, 1024), make_smem_desc(bdO + off, 16, 1024), idesc_s,
+                       k > 0 ? 1u : 0u);
+        }
+        umma_commit(st_full);
+        return true;
+      };
+      if (ok && n_iter > 0) ok = issue_scores(0, 0);
+      for (int t = 0; t < n_iter && ok; ++t) {
+        if (!mbar_wait(p_full, t & 1, p.status, ST_TIMEOUT_MISC)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t aPT = smem_u32(sPT), adST = smem_u32(sdST);
+        const uint32_t bQ = smem_u32(sQ + st * Cfg::T_BYTES), bdO = smem_u32(sdO + st * Cfg::T_BYTES);
+#pragma unroll
+        for (int k = 0; k < BT / 16; ++k) {
+          const uint32_t aoff = (k >> 2) * (BT * 128) + (k & 3) * 32;
+          umma_bf16_ss(tm_dV, make_smem_desc(aPT + aoff, 16, 1024),
+                       make_smem_desc(bdO + k * (16 * 128), BT * 128, 1024), idesc_g, (t > 0 || k > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < BT / 16; ++k) {
+          const uint32_t aoff = (k >> 2) * (BT * 128) + (k & 3) * 32;
+          umma_bf16_ss(tm_dK, make_smem_desc(adST + aoff, 16, 1024),
+                       make_smem_desc(bQ + k * (16 * 128), BT * 128, 1024), idesc_g, (t > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&q_empty[st]);
+        if (++st == Cfg::QS) { st = 0; ph ^= 1; }
+        if (t + 1 < n_iter) ok = issue_scores(st, ph);
+      }
+      if (ok) umma_commit(done);
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;  // kv row inside the tile == TMEM lane
+    const int kv_idx = kv0 + r;
+    const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
+    bool ok = true;
+    for (int t = 0; t < n_iter; ++t) {
+      const int head = kvh * group + t / n_qt;
+      const int qt = qt_first + t % n_qt;
+      const int q0 = qt * BT;
+      float* lse_b = s_lse + q * BT;
+      float* del_b = s_delta + q * BT;
+      __syncwarp();  // previous iteration's reads are complete
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int col = e * 32 + lane;
+        const int qi = q0 + col;
+        const size_t idx = (static_cast<size_t>(b) * p.H + head) * p.S + qi;
+        lse_b[col] = qi < p.S ? p.lse[idx] * LOG2E : 0.f;
+        del_b[col] = qi < p.S ? p.delta[idx] : 0.f;
+      }
+      __syncwarp();
+      if (!mbar_wait(st_full, t & 1, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const bool diag = p.causal && qt == kt;
+      const bool tail = q0 + BT > p.S;
+#pragma unroll 1
+      for (int c = 0; c < BT / 32; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32(tm_ST + lane_off + c * 32, sv);
+        tmem_ld_32x32(tm_dPT + lane_off + c * 32, dv);
+        tmem_ld_wait();
+        uint32_t pk[16], dk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float pr[2], ds[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = c * 32 + i + e;  // query row inside the tile
+            float pv = exp2f(__uint_as_float(sv[i + e]) * p.scale_log2 - lse_b[col]);
+            if ((diag && r > col) || (tail && q0 + col >= p.S)) pv = 0.f;
+            pr[e] = pv;
+            ds[e] = pv * (__uint_as_float(dv[i + e]) - del_b[col]) * p.scale;
+          }
+          pk[i >> 1] = pack_bf16x2(pr[0], pr[1]);
+          dk[i >> 1] = pack_bf16x2(ds[0], ds[1]);
+        }
+        store_row32_sw128(sPT, r, c, pk);
+        store_row32_sw128(sdST, r, c, dk);
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    if (ok && mbar_wait(done, 0, p.status, ST_TIMEOUT_TMEM_FULL)) {
+      tc_fence_after();
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t src = which == 0 ? tm_dK : tm_dV;
+        const int col0 = (which == 0 ? (p.H + kvh) : (p.H + p.Hkv + kvh)) * DH;
+#pragma unroll 1
+        for (int c = 0; c < DH / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(src + lane_off + c * 32, v);
+          tmem_ld_wait();
+          if (kv_idx < p.S) {
+            __nv_bfloat16* dst = p.dqkv + static_cast<size_t>(row_base + kv_idx) * p.ld_dqkv + col0 + c * 32;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(v[u * 8 + 0]), __uint_as_float(v[u * 8 + 1]));
+              w.y = pack_bf16x2(__uint_as_float(v[u * 8 + 2]), __uint_as_float(v[u * 8 + 3]));
+              w.z = pack_bf16x2(__uint_as_float(v[u * 8 + 4]), __uint_as_float(v[u * 8 + 5]));
+              w.w = pack_bf16x2(__uint_as_float(v[u * 8 + 6]), __uint_as_float(v[u * 8 + 7]));
+              *reinterpret_cast<uint4*>(dst + u * 8) = w;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+// --------------------------------------------------------------------------- dQ
+template <int DH>
+struct DqCfg {
+  static constexpr int KS = (DH == 64) ? 2 : 1;  // (K, V) ring stages
+  static constexpr int T_BYTES = BT * DH * 2;
+  static constexpr int DS_BYTES = BT * BT * 2;
+  static constexpr int TILE_BYTES = 2 * T_BYTES + KS * 2 * T_BYTES + DS_BYTES;
+  static constexpr int SMEM_BYTES = TILE_BYTES + 1024 + 128;
+  static constexpr int TMEM_COLS = 512;  // S 128 | dP 128 | dQ DH
+};
+
+template <int DH>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
+                        const BwdParams p) {
+  using Cfg = DqCfg<DH>;
+  constexpr int NCH = DH / 64;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sdO = sQ + Cfg::T_BYTES;
+  uint8_t* sK = sdO + Cfg::T_BYTES;               // KS stages
+  uint8_t* sV = sK + Cfg::KS * Cfg::T_BYTES;      // KS stages
+  uint8_t* sdS = sV + Cfg::KS * Cfg::T_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + Cfg::DS_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;            // KS
+  uint64_t* kv_empty = kv_full + Cfg::KS;  // KS
+  uint64_t* s_full = kv_empty + Cfg::KS;
+  uint64_t* p_full = s_full + 1;
+  uint64_t* done = p_full + 1;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(done + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_t = (p.S + BT - 1) / BT;
+  const int qt = n_t - 1 - blockIdx.x;
+  const int head = blockIdx.y, b = blockIdx.z;
+  const int kvh = head / (p.H / p.Hkv);
+  const int q0 = qt * BT;
+  const int row_base = b * p.S;
+  const int n_blocks = p.causal ? (qt + 1) : n_t;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < Cfg::KS; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 4);
+    mbar_init(done, 1);
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 0 && lane == 0) { prefetch_tmap(&tm_qkv); prefetch_tmap(&tm_do); }
+  if (warp == 1) { tmem_alloc(tmem_holder, Cfg::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+  const uint32_t tm_S = tmem_base, tm_dP = tmem_base + 128, tm_dQ = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, 2 * Cfg::T_BYTES);
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        tma_load_2d(sQ + c * (BT * 128), &tm_qkv, q_full, head * DH + c * 64, row_base + q0);
+        tma_load_2d(sdO + c * (BT * 128), &tm_do, q_full, head * DH + c * 64, row_base + q0);
+      }
+      int st = 0;
+      uint32_t ph = 0;
+      for (int j = 0; j < n_blocks; ++j) {
+        if (!mbar_wait(&kv_empty[st], ph ^ 1, p.status, ST_TIMEOUT_EMPTY)) break;
+        mbar_arrive_expect_tx(&kv_full[st], 2 * Cfg::T_BYTES);
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          tma_load_2d(sK + st * Cfg::T_BYTES + c * (BT * 128), &tm_qkv, &kv_full[st], (p.H + kvh) * DH + c * 64,
+                      row_base + j * BT);
+          tma_load_2d(sV + st * Cfg::T_BYTES + c * (BT * 128), &tm_qkv, &kv_full[st],
+                      (p.H + p.Hkv + kvh) * DH + c * 64, row_base + j * BT);
+        }
+        if (++st == Cfg::KS) { st = 0; ph ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(BT, BT, false, false);
+      constexpr uint32_t idesc_g = make_idesc_bf16(BT, DH, false, true);
+      bool ok = mbar_wait(q_full, 0, p.status, ST_TIMEOUT_FULL);
+      int st = 0;
+      uint32_t ph = 0;
+      const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO);
+      auto issue_scores = [&](int stage, uint32_t phase) -> bool {
+        if (!mbar_wait(&kv_full[stage], phase, p.status, ST_TIMEOUT_FULL)) return false;
+        tc_fence_after();
+        const uint32_t bK = smem_u32(sK + stage * Cfg::T_BYTES), bV = smem_u32(sV + stage * Cfg::T_BYTES);
+#pragma unroll
+        for (int k = 0; k < DH / 16; ++k) {
+          const uint32_t off = (k >> 2) * (BT * 128) + (k & 3) * 32;
+          umma_bf16_ss(tm_S, make_smem_desc(aQ + off, 16, 1024), make_smem_desc(bK + off, 16, 1024), idesc_s,
+                       k > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < DH / 16; ++k) {
+          const uint32_t off = (k >> 2) * (BT * 128) + (k & 3) * 32;
+          umma_bf16_ss(tm_dP, make_smem_desc(adO + off, 16, 1024), make_smem_desc(bV + off, 16, 1024), idesc_s,
+                       k > 0 ? 1u : 0u);
+        }
+        umma_commit(s_full);
+        return true;
+      };
+      if (ok) ok = issue_scores(0, 0);
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        if (!mbar_wait(p_full, j & 1, p.status, ST_TIMEOUT_MISC)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t adS = smem_u32(sdS), bK = smem_u32(sK + st * Cfg::T_BYTES);
+#pragma unroll
+        for (int k = 0; k < BT / 16; ++k) {
+          const uint32_t aoff = (k >> 2) * (BT * 128) + (k & 3) * 32;
+          umma_bf16_ss(tm_dQ, make_smem_desc(adS + aoff, 16, 1024),
+                       make_smem_desc(bK + k * (16 * 128), BT * 128, 1024), idesc_g, (j > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[st]);
+        if (++st == Cfg::KS) { st = 0; ph ^= 1; }
+        if (j + 1 < n_blocks) ok = issue_scores(st, ph);
+      }
+      if (ok) umma_commit(done);
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const int q_idx = q0 + r;
+    const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
+    float lse2 = 0.f, del = 0.f;
+    if (q_idx < p.S) {
+      const size_t idx = (static_cast<size_t>(b) * p.H + head) * p.S + q_idx;
+      lse2 = p.lse[idx] * LOG2E;
+      del = p.delta[idx];
+    }
+    bool ok = true;
+    for (int j = 0; j < n_blocks; ++j) {
+      if (!mbar_wait(s_full, j & 1, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int kv0 = j * BT;
+      const bool need_mask = (p.causal && j == n_blocks - 1) || (kv0 + BT > p.S);
+      const int limit = p.causal ? min(q_idx, p.S - 1) : (p.S - 1);
+#pragma unroll 1
+      for (int c = 0; c < BT / 32; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32(tm_S + lane_off + c * 32, sv);
+        tmem_ld_32x32(tm_dP + lane_off + c * 32, dv);
+        tmem_ld_wait();
+        uint32_t dk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float ds[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            float pv = exp2f(__uint_as_float(sv[i + e]) * p.scale_log2 - lse2);
+            if (need_mask && kv0 + c * 32 + i + e > limit) pv = 0.f;
+            ds[e] = pv * (__uint_as_float(dv[i + e]) - del) * p.scale;
+          }
+          dk[i >> 1] = pack_bf16x2(ds[0], ds[1]);
+        }
+        store_row32_sw128(sdS, r, c, dk);
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    if (ok && mbar_wait(done, 0, p.status, ST_TIMEOUT_TMEM_FULL)) {
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tm_dQ + lane_off + c * 32, v);
+        tmem_ld_wait();
+        if (q_idx < p.S) {
+          __nv_bfloat16* dst = p.dqkv + static_cast<size_t>(row_base + q_idx) * p.ld_dqkv + head * DH + c * 32;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(v[u * 8 + 0]), __uint_as_float(v[u * 8 + 1]));
+            w.y = pack_bf16x2(__uint_as_float(v[u * 8 + 2]), __uint_as_float(v[u * 8 + 3]));
+            w.z = pack_bf16x2(__uint_as_float(v[u * 8 + 4]), __uint_as_float(v[u * 8 + 5]));
+            w.w = pack_bf16x2(__uint_as_float(v[u * 8 + 6]), __uint_as_float(v[u * 8 + 7]));
+            *reinterpret_cast<uint4*>(dst + u * 8) = w;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+template <int DH>
+static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& td, const BwdParams& p, cudaStream_t stream) {
+  auto k1 = attention_bwd_dkv_kernel<DH>;
+  auto k2 = attention_bwd_dq_kernel<DH>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<DH>::SMEM_BYTES) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, DqCfg<DH>::SMEM_BYTES) != cudaSuccess)
+      return SB_ERR_LAUNCH;
+    attr_set = true;
+  }
+  const int n_t = (p.S + BT - 1) / BT;
+  k1<<<dim3(n_t, p.Hkv, p.B), BWD_THREADS, DkvCfg<DH>::SMEM_BYTES, stream>>>(tq, td, p);
+  if (cudaGetLastError() != cudaSuccess) return SB_ERR_LAUNCH;
+  k2<<<dim3(n_t, p.H, p.B), BWD_THREADS, DqCfg<DH>::SMEM_BYTES, stream>>>(tq, td, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+// qkv, dqkv: bf16 [B*S, ld]; O, dO: bf16 [B*S, ld_o / ld_do] (H*dh columns); lse: fp32 [B,H,S];
+// delta: fp32 [B,H,S] scratch written here. dqkv receives dQ | dK | dV in the qkv layout.
+extern "C" int sb_attention_bwd(const void* qkv, const void* O, const float* lse, const void* dO, void* dqkv,
+                                float* delta, int B, int S, int H, int Hkv, int dh, int ld, int ld_o, int ld_do,
+                                float scale, int causal, int* status, void* stream_) {
+  if (B <= 0 || S <= 0 || H <= 0 || Hkv <= 0 || (H % Hkv) || (dh != 64 && dh != 128)) return SB_ERR_ARG;
+  if ((ld & 7) || (reinterpret_cast<uintptr_t>(dqkv) & 15)) return SB_ERR_ALIGN;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  CUtensorMap tq, td;
+  int rc = make_tmap_2d_bf16(&tq, qkv, static_cast<uint64_t>(ld), static_cast<uint64_t>(B) * S, ld, 64, 128);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&td, dO, static_cast<uint64_t>(H) * dh, static_cast<uint64_t>(B) * S, ld_do, 64, 128);
+  if (rc) return rc;
+  const int warps = B * S * H;
+  attn_delta_kernel<<<(warps + 7) / 8, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(O),
+                                                         static_cast<const __nv_bfloat16*>(dO), delta, B, S, H, dh,
+                                                         ld_o, ld_do);
+  if (cudaGetLastError() != cudaSuccess) return SB_ERR_LAUNCH;
+  BwdParams p;
+  p.B = B; p.S = S; p.H = H; p.Hkv = Hkv;
+  p.ld_dqkv = ld;
+  p.scale = scale;
+  p.scale_log2 = scale * LOG2E;
+  p.causal = causal;
+  p.lse = lse;
+  p.delta = delta;
+  p.dqkv = static_cast<__nv_bfloat16*>(dqkv);
+  p.status = status;
+  return dh == 64 ? launch_bwd<64>(tq, td, p, stream) : launch_bwd<128>(tq, td, p, stream);
+}

@@ -1,0 +1,72 @@
+"""GQA flash attention (prefill / training) on the tcgen05 kernels in csrc/attention_*_tcgen05.cu.
+
+The activation layout is the fused projection output ``qkv [B*S, (H + 2*Hkv) * dh]`` (q heads, k heads,
+v heads; RoPE already applied to q and k), so no per-head slicing copies exist (the reference slices and
+re-concatenates per head: scirust-sciagent/src/cuda_model.rs:796-869).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+from . import gemm as _g
+
+_lib.register("sb_attention_fwd", [_lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32,
+                                   _lib.i32, _lib.i32, _lib.f32, _lib.i32, _lib.vp, _lib.vp])
+_lib.register("sb_attention_bwd", [_lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32,
+                                   _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.f32,
+                                   _lib.i32, _lib.vp, _lib.vp])
+
+
+def attention_ref(qkv, B, S, H, Hkv, dh, causal=True, scale=None):
+    """fp32 dense reference: returns (O [B*S, H*dh] fp32, LSE [B,H,S] fp32)."""
+    scale = 1.0 / math.sqrt(dh) if scale is None else scale
+    x = qkv.float().reshape(B, S, H + 2 * Hkv, dh)
+    q = x[:, :, :H].permute(0, 2, 1, 3)
+    k = x[:, :, H:H + Hkv].permute(0, 2, 1, 3).repeat_interleave(H // Hkv, 1)
+    v = x[:, :, H + Hkv:].permute(0, 2, 1, 3).repeat_interleave(H // Hkv, 1)
+    s = torch.matmul(q, k.transpose(-1, -2)) * scale
+    if causal:
+        mask = torch.triu(torch.ones(S, S, dtype=torch.bool, device=qkv.device), 1)
+        s = s.masked_fill(mask, float("-inf"))
+    lse = torch.logsumexp(s, -1)
+    o = torch.matmul(torch.softmax(s, -1), v)
+    return o.permute(0, 2, 1, 3).reshape(B * S, H * dh), lse
+
+
+def attention_fwd(qkv, B, S, H, Hkv, dh, causal=True, scale=None, want_lse=True):
+    scale = 1.0 / math.sqrt(dh) if scale is None else scale
+    if not qkv.is_cuda:
+        o, lse = attention_ref(qkv, B, S, H, Hkv, dh, causal, scale)
+        return o.to(qkv.dtype), lse
+    if qkv.dim() != 2 or qkv.stride(1) != 1 or qkv.dtype != torch.bfloat16:
+        raise ValueError("qkv must be a 2-D bf16 matrix with unit inner stride")
+    out = torch.empty((B * S, H * dh), dtype=torch.bfloat16, device=qkv.device)
+    lse = torch.empty((B, H, S), dtype=torch.float32, device=qkv.device) if want_lse else None
+    _lib.call("sb_attention_fwd", qkv.data_ptr(), out.data_ptr(), _lib.ptr(lse), B, S, H, Hkv, dh, qkv.stride(0),
+              out.stride(0), float(scale), int(causal), _lib.status_word(qkv.device).data_ptr(), _lib.stream())
+    _g.launch_count += 1
+    return out, lse
+
+
+def attention_bwd_ref(qkv, do, B, S, H, Hkv, dh, causal=True, scale=None):
+    x = qkv.detach().float().requires_grad_(True)
+    o, _ = attention_ref(x, B, S, H, Hkv, dh, causal, scale)
+    o.backward(do.float())
+    return x.grad
+
+
+def attention_bwd(qkv, o, lse, do, B, S, H, Hkv, dh, causal=True, scale=None):
+    """Gradient w.r.t. the fused qkv matrix (same layout), deterministic (no atomics)."""
+    scale = 1.0 / math.sqrt(dh) if scale is None else scale
+    if not qkv.is_cuda:
+        return attention_bwd_ref(qkv, do, B, S, H, Hkv, dh, causal, scale).to(qkv.dtype)
+    dqkv = torch.empty_like(qkv)
+    delta = torch.empty((B, H, S), dtype=torch.float32, device=qkv.device)
+    _lib.call("sb_attention_bwd", qkv.data_ptr(), o.data_ptr(), lse.data_ptr(), do.data_ptr(), dqkv.data_ptr(),
+              delta.data_ptr(), B, S, H, Hkv, dh, qkv.stride(0), o.stride(0), do.stride(0), float(scale),
+              int(causal), _lib.status_word(qkv.device).data_ptr(), _lib.stream())
+    _g.launch_count += 3
+    return dqkv

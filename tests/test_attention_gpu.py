@@ -1,0 +1,45 @@
+"""tcgen05 flash attention against the dense fp32 PyTorch reference."""
+import pytest
+import torch
+
+from scirust_b200.ops import _lib, attention as A
+
+pytestmark = pytest.mark.gpu
+
+
+def _qkv(B, S, H, Hkv, dh, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return torch.randn(B * S, (H + 2 * Hkv) * dh, generator=g, device="cuda").to(torch.bfloat16)
+
+
+CASES = [(1, 128, 1, 1, 64), (2, 256, 4, 2, 64), (1, 1000, 4, 1, 64), (2, 2048, 16, 4, 64), (1, 384, 4, 2, 128),
+         (1, 200, 2, 2, 128)]
+
+
+@pytest.mark.parametrize("B,S,H,Hkv,dh", CASES)
+@pytest.mark.parametrize("causal", [True, False])
+def test_forward(B, S, H, Hkv, dh, causal):
+    qkv = _qkv(B, S, H, Hkv, dh)
+    o, lse = A.attention_fwd(qkv, B, S, H, Hkv, dh, causal=causal)
+    _lib.check_status()
+    o_ref, lse_ref = A.attention_ref(qkv, B, S, H, Hkv, dh, causal=causal)
+    assert (o.float() - o_ref).abs().max().item() < 3e-2
+    assert (lse - lse_ref).abs().max().item() < 2e-2
+    o2, _ = A.attention_fwd(qkv, B, S, H, Hkv, dh, causal=causal)
+    assert torch.equal(o, o2)
+
+
+@pytest.mark.parametrize("B,S,H,Hkv,dh", CASES)
+@pytest.mark.parametrize("causal", [True, False])
+def test_backward(B, S, H, Hkv, dh, causal):
+    qkv = _qkv(B, S, H, Hkv, dh, seed=1)
+    g = torch.Generator(device="cuda").manual_seed(2)
+    do = torch.randn(B * S, H * dh, generator=g, device="cuda").to(torch.bfloat16)
+    o, lse = A.attention_fwd(qkv, B, S, H, Hkv, dh, causal=causal)
+    d = A.attention_bwd(qkv, o, lse, do, B, S, H, Hkv, dh, causal=causal)
+    _lib.check_status()
+    ref = A.attention_bwd_ref(qkv, do, B, S, H, Hkv, dh, causal=causal)
+    err = (d.float() - ref).abs().max().item()
+    assert err < 3e-2 * max(1.0, ref.abs().max().item()), err
+    d2 = A.attention_bwd(qkv, o, lse, do, B, S, H, Hkv, dh, causal=causal)
+    assert torch.equal(d, d2)
