@@ -11,6 +11,7 @@ A source is recompiled when its object is older than it or than any header.
 """
 from __future__ import annotations
 
+import hashlib
 import os
 import shutil
 import subprocess
@@ -47,11 +48,26 @@ def _nvcc() -> str:
     raise RuntimeError("nvcc not found")
 
 
-def _stale(src: Path, obj: Path, headers: list[Path]) -> bool:
-    if not obj.exists():
+def _digest(src: Path, headers: list[Path], flags: list[str]) -> str:
+    h = hashlib.sha256()
+    for f in [src, *headers]:
+        h.update(f.name.encode())
+        h.update(f.read_bytes())
+    h.update(" ".join(flags).encode())
+    return h.hexdigest()
+
+
+def _stale(src: Path, obj: Path, headers: list[Path], flags: list[str]) -> bool:
+    """Content-addressed staleness (file times do not survive a copy of the tree): the object is
+    current when the digest recorded beside it matches source + headers + flags."""
+    tag = obj.with_suffix(obj.suffix + ".sha")
+    if not obj.exists() or not tag.exists():
         return True
-    t = obj.stat().st_mtime
-    return src.stat().st_mtime > t or any(h.stat().st_mtime > t for h in headers)
+    return tag.read_text().strip() != _digest(src, headers, flags)
+
+
+def _stamp(src: Path, obj: Path, headers: list[Path], flags: list[str]) -> None:
+    obj.with_suffix(obj.suffix + ".sha").write_text(_digest(src, headers, flags))
 
 
 def _run(cmd: list[str]) -> None:
@@ -67,19 +83,22 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
     nvcc = _nvcc()
     jobs = []
     objs = []
+    stamps = []
     for src in sources:
         obj = OBJ / (src.stem + ".o")
         objs.append(obj)
-        if force or _stale(src, obj, headers):
-            flags = list(NVCC_FLAGS)
-            if src.stem.endswith("_strict"):
-                flags += STRICT_FLAGS
-            if verbose:
-                flags += ["-Xptxas", "-v"]
-            jobs.append([nvcc, *flags, "-I", str(CSRC), "-c", str(src), "-o", str(obj)])
+        flags = list(NVCC_FLAGS)
+        if src.stem.endswith("_strict"):
+            flags += STRICT_FLAGS
+        if force or _stale(src, obj, headers, flags):
+            extra = ["-Xptxas", "-v"] if verbose else []
+            jobs.append([nvcc, *flags, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)])
+            stamps.append((src, obj, flags))
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(_run, jobs))
+        for src, obj, flags in stamps:
+            _stamp(src, obj, headers, flags)
     if jobs or not CUDA_LIB.exists():
         _run([nvcc, "-shared", "-o", str(CUDA_LIB), *map(str, objs), "-lcudart"])
     return CUDA_LIB
@@ -90,15 +109,18 @@ def build_rt(force: bool = False) -> Path:
     headers = sorted(CSRC.glob("*.h")) + sorted(CSRC.glob("*.hpp"))
     sources = sorted(CSRC.glob("*.cpp"))
     cxx = os.environ.get("CXX", "g++")
-    objs, jobs = [], []
+    objs, jobs, stamps = [], [], []
     for src in sources:
         obj = OBJ / (src.stem + ".cpp.o")
         objs.append(obj)
-        if force or _stale(src, obj, headers):
+        if force or _stale(src, obj, headers, CXX_FLAGS):
             jobs.append([cxx, *CXX_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)])
+            stamps.append((src, obj))
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(_run, jobs))
+        for src, obj in stamps:
+            _stamp(src, obj, headers, CXX_FLAGS)
     if sources and (jobs or not RT_LIB.exists()):
         _run([cxx, "-shared", "-pthread", "-o", str(RT_LIB), *map(str, objs)])
     return RT_LIB

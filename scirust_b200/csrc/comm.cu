@@ -1,0 +1,227 @@
+// Peer-memory substrate and the fused data-parallel gradient all-reduce.
+//
+// Symmetric memory: every rank cudaMalloc's a region of the same size, exports it with
+// cudaIpcGetMemHandle, and maps every peer's region (cudaIpcOpenMemHandle). Kernels then receive
+// a table of W base pointers and address a peer's copy of a buffer directly over NVLink.
+//
+// Flag protocol (all waits bounded; a wait that runs out stores ST_TIMEOUT_PEER in the status
+// word and the kernel leaves without touching peer memory again):
+//   flags live in each rank's own region: flags[slot][phase][src_rank] (uint32 epochs).
+//   A rank announces phase p of call `epoch` by storing `epoch` into flags[slot][p][my_rank] of
+//   EVERY peer (st.release.sys) and waits for its own flags[slot][p][*] to reach `epoch`
+//   (ld.acquire.sys).
+//
+// sb_allreduce_bf16 (the data-parallel gradient reduction; reference semantics: rank-ordered sum
+// then one multiply by 1/world, scirust-core/src/distributed.rs:96-167):
+//   phase 0  "my bucket is final"            -> wait for all peers
+//   reduce   rank r owns shard r of the bucket: pulls that shard from every rank's bucket with
+//            peer loads, adds in rank order 0..W-1 in fp32 (bf16 -> fp32 cast fused), scales by
+//            1/W (or any factor), rounds once, and pushes the result to every rank's output
+//            buffer (bf16 or fp32) with peer stores
+//   phase 1  "my pushes are done and I no longer read your bucket" -> last CTA waits for all
+//            peers before the kernel ends, so the next kernel in the stream may read the output
+//            and overwrite the bucket.
+// Because each element is reduced by exactly one rank and broadcast, all replicas receive
+// identical bits, and the sum order is fixed: the result is bitwise repeatable at a fixed world.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+#include "api.h"
+#include "sm100_ptx.cuh"
+
+namespace sb {
+
+constexpr int MAX_WORLD = 16;
+constexpr uint64_t kPeerWaitNsDefault = 10000000000ull;  // 10 s: a peer may start its kernel late
+
+struct PeerTable {
+  void* in[MAX_WORLD];        // peers' input buffers (bucket base)
+  void* out[MAX_WORLD];       // peers' output buffers
+  uint32_t* flags[MAX_WORLD]; // peers' flag arrays
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_peer_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+// Wait until flags[0..W-1] >= epoch (epochs only grow). One thread calls this.
+__device__ bool wait_flags(const uint32_t* flags, int W, uint32_t epoch, uint64_t limit_ns, int* status) {
+  const uint64_t t0 = globaltimer_ns();
+  for (int r = 0; r < W; ++r) {
+    uint32_t spins = 0;
+    while (static_cast<int32_t>(ld_acquire_sys(flags + r) - epoch) < 0) {
+      if ((++spins & 0xff) == 0) {
+        if (globaltimer_ns() - t0 > limit_ns) {
+          atomicCAS(status, 0, ST_TIMEOUT_PEER);
+          return false;
+        }
+        if (*reinterpret_cast<volatile int*>(status) != 0) return false;
+      }
+    }
+  }
+  return true;
+}
+
+struct AllReduceParams {
+  PeerTable t;
+  int rank, W;
+  size_t n;            // elements in the bucket (multiple of 8)
+  float scale;
+  uint32_t epoch;
+  int slot;            // flag slot (bucket index)
+  int out_fp32;
+  uint64_t wait_ns;
+  unsigned int* cta_counter;  // local, zero before the call; reset by the kernel
+  int* status;
+};
+
+__global__ void __launch_bounds__(512)
+allreduce_bf16_kernel(const __grid_constant__ AllReduceParams p) {
+  __shared__ int s_ok;
+  const int W = p.W;
+  uint32_t* my_flags = p.t.flags[p.rank] + static_cast<size_t>(p.slot) * 2 * MAX_WORLD;
+  if (threadIdx.x == 0) {
+    if (blockIdx.x == 0) {
+      __threadfence_system();
+      for (int r = 0; r < W; ++r)
+        st_release_sys(p.t.flags[r] + static_cast<size_t>(p.slot) * 2 * MAX_WORLD + p.rank, p.epoch);
+    }
+    s_ok = wait_flags(my_flags, W, p.epoch, p.wait_ns, p.status) ? 1 : 0;
+  }
+  __syncthreads();
+  const bool ok = s_ok != 0;
+
+  if (ok) {
+    // shard r = [r*per, min(n, (r+1)*per)), per a multiple of 8 elements
+    const size_t per = ((p.n + W - 1) / W + 7) / 8 * 8;
+    const size_t lo = min(p.n, per * p.rank);
+    const size_t hi = min(p.n, lo + per);
+    const size_t n8 = (hi - lo) / 8;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+      const size_t e = lo + i * 8;
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int r = 0; r < W; ++r) {  // fixed rank order
+        const uint4 v = ld_peer_v4(static_cast<const __nv_bfloat16*>(p.t.in[r]) + e);
+        acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x);
+        acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
+        acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z);
+        acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] *= p.scale;
+      if (p.out_fp32) {
+        const uint4 a = make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]),
+                                   __float_as_uint(acc[3]));
+        const uint4 b = make_uint4(__float_as_uint(acc[4]), __float_as_uint(acc[5]), __float_as_uint(acc[6]),
+                                   __float_as_uint(acc[7]));
+        for (int r = 0; r < W; ++r) {
+          const int dst = (p.rank + r) % W;  // spread the pushes over the peers
+          float* o = static_cast<float*>(p.t.out[dst]) + e;
+          *reinterpret_cast<uint4*>(o) = a;
+          *reinterpret_cast<uint4*>(o + 4) = b;
+        }
+      } else {
+        const uint4 o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                                   pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+        for (int r = 0; r < W; ++r) {
+          const int dst = (p.rank + r) % W;
+          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.t.out[dst]) + e) = o;
+        }
+      }
+    }
+  }
+  // completion: the last CTA to finish announces phase 1 and waits for every peer's phase 1.
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(p.cta_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *p.cta_counter = 0;  // ready for the next call on this stream
+      if (ok) {
+        __threadfence_system();
+        for (int r = 0; r < W; ++r)
+          st_release_sys(p.t.flags[r] + static_cast<size_t>(p.slot) * 2 * MAX_WORLD + MAX_WORLD + p.rank, p.epoch);
+        wait_flags(my_flags + MAX_WORLD, W, p.epoch, p.wait_ns, p.status);
+      }
+    }
+  }
+}
+
+// A wait that nothing satisfies: used by tests to check that a bounded wait returns a status
+// instead of hanging. Waits `limit_ns` at most on flags that stay below `epoch`.
+__global__ void wait_probe_kernel(const uint32_t* flags, int W, uint32_t epoch, uint64_t limit_ns, int* status) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) wait_flags(flags, W, epoch, limit_ns, status);
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" int sb_malloc(size_t bytes, void** out) {
+  return cudaMalloc(out, bytes) == cudaSuccess ? 0 : SB_ERR_RUNTIME;
+}
+extern "C" int sb_free(void* p) { return cudaFree(p) == cudaSuccess ? 0 : SB_ERR_RUNTIME; }
+extern "C" int sb_memset(void* p, int v, size_t bytes, void* stream) {
+  return cudaMemsetAsync(p, v, bytes, static_cast<cudaStream_t>(stream)) == cudaSuccess ? 0 : SB_ERR_RUNTIME;
+}
+// handle_out: 64 bytes
+extern "C" int sb_ipc_get_handle(void* p, void* handle_out) {
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, p) != cudaSuccess) return SB_ERR_RUNTIME;
+  memcpy(handle_out, &h, sizeof(h));
+  return 0;
+}
+extern "C" int sb_ipc_open(const void* handle, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  return cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess ? 0 : SB_ERR_RUNTIME;
+}
+extern "C" int sb_ipc_close(void* p) { return cudaIpcCloseMemHandle(p) == cudaSuccess ? 0 : SB_ERR_RUNTIME; }
+extern "C" int sb_ipc_handle_size() { return static_cast<int>(sizeof(cudaIpcMemHandle_t)); }
+extern "C" int sb_flag_words_per_slot() { return 2 * MAX_WORLD; }
+
+// in_ptrs/out_ptrs/flag_ptrs: host arrays of W device pointers (peer-mapped; entry `rank` is local).
+// n_elems must be a multiple of 8; buffers 16-byte aligned. wait_ms <= 0 selects the default.
+extern "C" int sb_allreduce_bf16(void* const* in_ptrs, void* const* out_ptrs, void* const* flag_ptrs, int rank,
+                                 int W, size_t n_elems, float scale, uint32_t epoch, int slot, int out_fp32,
+                                 unsigned int* cta_counter, int n_ctas, int wait_ms, int* status, void* stream) {
+  if (W < 1 || W > MAX_WORLD || rank < 0 || rank >= W || (n_elems & 7) || n_ctas < 1) return SB_ERR_ARG;
+  AllReduceParams p;
+  for (int r = 0; r < W; ++r) {
+    if ((reinterpret_cast<uintptr_t>(in_ptrs[r]) & 15) || (reinterpret_cast<uintptr_t>(out_ptrs[r]) & 15))
+      return SB_ERR_ALIGN;
+    p.t.in[r] = in_ptrs[r];
+    p.t.out[r] = out_ptrs[r];
+    p.t.flags[r] = static_cast<uint32_t*>(flag_ptrs[r]);
+  }
+  p.rank = rank; p.W = W; p.n = n_elems; p.scale = scale; p.epoch = epoch; p.slot = slot;
+  p.out_fp32 = out_fp32;
+  p.wait_ns = wait_ms > 0 ? static_cast<uint64_t>(wait_ms) * 1000000ull : kPeerWaitNsDefault;
+  p.cta_counter = cta_counter;
+  p.status = status;
+  allreduce_bf16_kernel<<<n_ctas, 512, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+}
+
+extern "C" int sb_wait_probe(const void* flags, int W, uint32_t epoch, int wait_ms, int* status, void* stream) {
+  wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint32_t*>(flags), W, epoch, static_cast<uint64_t>(wait_ms) * 1000000ull, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+}

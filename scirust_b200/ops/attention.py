@@ -52,10 +52,11 @@ def attention_fwd(qkv, B, S, H, Hkv, dh, causal=True, scale=None, want_lse=True)
 
 
 def attention_bwd_ref(qkv, do, B, S, H, Hkv, dh, causal=True, scale=None):
-    x = qkv.detach().float().requires_grad_(True)
-    o, _ = attention_ref(x, B, S, H, Hkv, dh, causal, scale)
-    o.backward(do.float())
-    return x.grad
+    with torch.enable_grad():
+        x = qkv.detach().float().requires_grad_(True)
+        o, _ = attention_ref(x, B, S, H, Hkv, dh, causal, scale)
+        (g,) = torch.autograd.grad(o, x, do.float())
+    return g
 
 
 def attention_bwd(qkv, o, lse, do, B, S, H, Hkv, dh, causal=True, scale=None):

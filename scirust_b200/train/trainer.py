@@ -1,0 +1,106 @@
+"""Mixed-precision trainer for the SciAgent decoder: bf16 compute weights, fp32 master weights and
+AdamW moments, device-side global-norm clipping, deferred telemetry.
+
+Counterpart of the reference's ``CudaTrainer`` (scirust-sciagent/src/cuda_model.rs:1239-2225:
+``train_step_batch_deferred`` :1393-1523, ``global_grad_sumsq`` + ``adamw_step_with_norm``
+:1440-1518, deferred diagnostics :1525-1529). Differences by design: the whole model is one flat
+buffer, so the gradient norm is two launches and the optimizer one launch (the reference issues
+2 + 1 launches per tensor); the step never synchronises with the host unless the caller reads the
+loss; data-parallel gradient reduction is a pluggable ``grad_reducer``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from .. import ops
+from .schedule import ConstantSchedule, WarmupCosineSchedule
+
+
+@dataclass
+class TrainerConfig:
+    lr: float = 3e-4
+    min_lr: float = 3e-5
+    warmup_steps: int = 0
+    total_steps: int = 0          # 0 = constant learning rate
+    beta1: float = 0.9
+    beta2: float = 0.95
+    eps: float = 1e-8
+    weight_decay: float = 0.1
+    max_grad_norm: float = 1.0
+    telemetry_interval: int = 0   # 0 = never read the loss back unless asked
+    optimizer: str = "adamw"
+
+
+class Trainer:
+    """``train_step(tokens)`` takes ``[B, S+1]`` int64 token ids (host, ideally pinned, or device) and
+    returns the loss as a device scalar. ``grad_reducer(flat_grad) -> scale`` may reduce the flat
+    gradient across data-parallel ranks and returns the factor still to be applied (1/world)."""
+
+    def __init__(self, model, cfg: TrainerConfig | None = None, grad_reducer=None):
+        self.model = model
+        self.cfg = cfg or TrainerConfig()
+        c = self.cfg
+        self.schedule = (WarmupCosineSchedule(c.lr, c.min_lr, c.warmup_steps, c.total_steps)
+                         if c.total_steps > 0 else ConstantSchedule(c.lr))
+        flat = model.flat
+        self.master = flat.float()
+        self.m = torch.zeros_like(self.master)
+        self.v = torch.zeros_like(self.master)
+        self.grad_sumsq = torch.zeros(1, dtype=torch.float32, device=flat.device)
+        self.step = 0
+        self.grad_reducer = grad_reducer
+        self.last_loss = None
+        self._dev_tokens = None
+
+    # -- data ------------------------------------------------------------------------------
+    def _to_device(self, tokens):
+        dev = self.model.flat.device
+        if tokens.device == dev:
+            return tokens
+        if self._dev_tokens is None or self._dev_tokens.shape != tokens.shape:
+            self._dev_tokens = torch.empty(tokens.shape, dtype=tokens.dtype, device=dev)
+        self._dev_tokens.copy_(tokens, non_blocking=True)
+        return self._dev_tokens
+
+    # -- one optimisation step ---------------------------------------------------------------
+    def train_step(self, tokens):
+        model, c = self.model, self.cfg
+        tok = self._to_device(tokens)
+        inp = tok[:, :-1].contiguous()
+        tgt = tok[:, 1:].contiguous()
+        model.zero_grad_flags()
+        loss = model(inp, tgt)
+        loss.backward()
+        grad = model.flat_grad
+        grad_scale = 1.0
+        if self.grad_reducer is not None:
+            out = self.grad_reducer(grad)
+            if isinstance(out, tuple):
+                grad, grad_scale = out
+            else:
+                grad_scale = out
+        ops.sumsq(grad, out=self.grad_sumsq)
+        self.step += 1
+        lr = self.schedule.lr_at(self.step - 1)
+        ops.optim_step(self.master, self.m, self.v, grad, model.flat, lr=lr, beta1=c.beta1, beta2=c.beta2,
+                       eps=c.eps, weight_decay=c.weight_decay, step=self.step, decay_end=model.decay_end,
+                       grad_sumsq=self.grad_sumsq, max_grad_norm=c.max_grad_norm, grad_scale=grad_scale,
+                       mode=c.optimizer)
+        self.last_loss = loss.detach()
+        return self.last_loss
+
+    def grad_norm(self) -> float:
+        return float(self.grad_sumsq.sqrt().item())
+
+    # -- state -------------------------------------------------------------------------------
+    def state_dict(self) -> dict:
+        return {"step": self.step, "master": self.master, "m": self.m, "v": self.v}
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.step = int(sd["step"])
+        self.master.copy_(sd["master"])
+        self.m.copy_(sd["m"])
+        self.v.copy_(sd["v"])
+        self.model.flat.copy_(self.master.to(torch.bfloat16))

@@ -1,0 +1,45 @@
+"""Multi-GPU tests (2 ranks as child processes, one GPU each). Skipped with fewer than 2 GPUs.
+
+The fused kernels run on plain peer loads/stores; NVLS is switched off for NCCL in these
+children so that a rank leaving between steps cannot disturb a multicast binding."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(script: str, nproc: int, port: int, timeout: int = 300):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "mp", script)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    return r.stdout
+
+
+def _need(n):
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
+def test_fused_allreduce_matches_rank_ordered_sum():
+    _need(2)
+    out = _run("mp_allreduce.py", 2, 29611)
+    assert "ALLREDUCE_OK" in out
+
+
+def test_dp_training_fused_equals_nccl_baseline():
+    _need(2)
+    out = _run("mp_dp_train.py", 2, 29612)
+    assert "DP_TRAIN_OK" in out
+
+
+def test_tp_fused_layers_match_nccl_baseline():
+    _need(2)
+    out = _run("mp_tp_layers.py", 2, 29613)
+    assert "TP_OK" in out
