@@ -623,3 +623,41 @@ extern "C" int sb_cast(const void* in, void* out, size_t n, int to_bf16, float s
                                                         static_cast<float*>(out), n, scale);
   CHECK_LAUNCH();
 }
+
+// ---------------------------------------------------------------------------
+// sb_sumsq_no_alloc: the sum of squares for callers that cannot allocate (see
+// sumsq_no_alloc.h). Same kernels and launch shape as sb_sumsq; the per-block partials go to
+// an array that is part of the library image instead of a caller-provided buffer.
+// ---------------------------------------------------------------------------
+#include "sumsq_no_alloc.h"
+
+static __device__ __align__(256) float g_sumsq_no_alloc_scratch[SB_SUMSQ_NO_ALLOC_MAX_PARTIALS];
+
+// Device address of the scratch array, resolved once per device. In host code the array's name
+// is only a handle for the runtime, not something a kernel can dereference.
+static float* g_sumsq_no_alloc_ptr[64] = {nullptr};
+
+extern "C" int sb_sumsq_no_alloc(const void* g, size_t n, int is_bf16, float* out, int accumulate, void* stream) {
+  if (n == 0 || g == nullptr || out == nullptr) return SB_ERR_ARG;
+  if (n > SB_SUMSQ_NO_ALLOC_MAX_ELEMS) return SB_ERR_TOO_LARGE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return SB_ERR_RUNTIME;
+  float* scratch = g_sumsq_no_alloc_ptr[dev];
+  if (scratch == nullptr) {
+    // first call on this device (which is current): ask the runtime where the array lives here
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_sumsq_no_alloc_scratch) != cudaSuccess || p == nullptr) return SB_ERR_RUNTIME;
+    scratch = static_cast<float*>(p);
+    g_sumsq_no_alloc_ptr[dev] = scratch;
+  }
+  const size_t nb = (n + SB_SUMSQ_NO_ALLOC_ELEMS_PER_PARTIAL - 1) / SB_SUMSQ_NO_ALLOC_ELEMS_PER_PARTIAL;
+  if (is_bf16)
+    sumsq_partial_kernel<__nv_bfloat16><<<static_cast<unsigned>(nb), 256, 0, STREAM>>>(
+        static_cast<const __nv_bfloat16*>(g), n, scratch);
+  else
+    sumsq_partial_kernel<float><<<static_cast<unsigned>(nb), 256, 0, STREAM>>>(static_cast<const float*>(g), n,
+                                                                               scratch);
+  if (cudaGetLastError() != cudaSuccess) return SB_ERR_LAUNCH;
+  sumsq_finish_kernel<<<1, 256, 0, STREAM>>>(scratch, static_cast<int>(nb), out, accumulate);
+  CHECK_LAUNCH();
+}
