@@ -21,7 +21,7 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64
                       uint32_t box_inner, uint32_t box_outer);
 
 constexpr int BT = 128;          // tile edge (query rows and kv rows)
-constexpr int BWD_THREADS = 192;
+constexpr int BWD_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 softmax (two per TMEM lane quarter)
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct BwdParams {
@@ -30,7 +30,7 @@ struct BwdParams {
   float scale, scale_log2;
   int causal;
   const float* lse;    // [B,H,S]
-  const float* delta;  // [B,H,S]
+  const float2* stats; // [B,H,S] (lse * log2(e), delta), written by attn_delta_kernel
   __nv_bfloat16* dqkv; // [B*S, ld_dqkv]
   int* status;
 };
@@ -48,7 +48,8 @@ __device__ __forceinline__ void store_row32_sw128(uint8_t* tile, int r, int c, c
 
 // --------------------------------------------------------------------------- delta
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
-                                  float* __restrict__ delta, int B, int S, int H, int dh, int ld_o, int ld_do) {
+                                  const float* __restrict__ lse, float2* __restrict__ stats, int B, int S, int H,
+                                  int dh, int ld_o, int ld_do) {
   const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (w >= B * S * H) return;
@@ -65,18 +66,25 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
   for (int o2 = 16; o2 > 0; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
   if (lane == 0) {
     const int b = row / S, s = row - b * S;
-    delta[(static_cast<size_t>(b) * H + h) * S + s] = acc;
+    const size_t idx = (static_cast<size_t>(b) * H + h) * S + s;
+    stats[idx] = make_float2(lse[idx] * LOG2E, acc);
   }
 }
 
 // --------------------------------------------------------------------------- dK / dV
+// Pipeline (DH == 64): the bf16 P^T / dS^T tiles are double-buffered in shared memory, so the MMA
+// warp issues the score products of iteration t+1 *before* the gradient products of iteration t;
+// the softmax warps then work on t+1 while the tensor cores finish t. With DH == 128 shared
+// memory only fits single buffers and the two groups are issued in program order.
 template <int DH>
 struct DkvCfg {
+  static constexpr bool PDB = (DH == 64);             // double-buffer P^T / dS^T
+  static constexpr int NPB = PDB ? 2 : 1;
   static constexpr int QS = (DH == 64) ? 2 : 1;       // (Q, dO) ring stages
   static constexpr int T_BYTES = BT * DH * 2;         // one [128 x DH] tile
   static constexpr int PT_BYTES = BT * BT * 2;
-  static constexpr int TILE_BYTES = 2 * T_BYTES + QS * 2 * T_BYTES + 2 * PT_BYTES;
-  static constexpr int SMEM_BYTES = TILE_BYTES + 2 * 4 * BT * 4 + 1024 + 128;
+  static constexpr int TILE_BYTES = 2 * T_BYTES + QS * 2 * T_BYTES + NPB * 2 * PT_BYTES;
+  static constexpr int SMEM_BYTES = TILE_BYTES + 1024 + 128;
   static constexpr int TMEM_COLS = 512;  // S^T 128 | dP^T 128 | dK DH | dV DH
 };
 
@@ -92,13 +100,9 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __gri
   uint8_t* sV = sK + Cfg::T_BYTES;
   uint8_t* sQ = sV + Cfg::T_BYTES;                 // QS stages
   uint8_t* sdO = sQ + Cfg::QS * Cfg::T_BYTES;      // QS stages
-  uint8_t* sPT = sdO + Cfg::QS * Cfg::T_BYTES;
-  uint8_t* sdST = sPT + Cfg::PT_BYTES;
-  // Per-warp private copies of the query tile's LSE and delta (no cross-warp barrier is needed,
-  // so a warp that gives up on a wait can never strand another warp at a barrier).
-  float* s_lse = reinterpret_cast<float*>(sdST + Cfg::PT_BYTES);  // [4 warps][128]
-  float* s_delta = s_lse + 4 * BT;                                // [4 warps][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 4 * BT);
+  uint8_t* sPT = sdO + Cfg::QS * Cfg::T_BYTES;     // NPB buffers
+  uint8_t* sdST = sPT + Cfg::NPB * Cfg::PT_BYTES;  // NPB buffers
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdST + Cfg::NPB * Cfg::PT_BYTES);
   uint64_t* kv_full = bars;
   uint64_t* q_full = bars + 1;            // QS
   uint64_t* q_empty = q_full + Cfg::QS;   // QS
@@ -122,7 +126,7 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __gri
     mbar_init(kv_full, 1);
     for (int s = 0; s < Cfg::QS; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
     mbar_init(st_full, 1);
-    mbar_init(p_full, 4);
+    mbar_init(p_full, 8);  // one arrival per softmax warp
     mbar_init(done, 1);
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -165,13 +169,14 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __gri
       constexpr uint32_t idesc_s = make_idesc_bf16(BT, BT, false, false);   // [kv x q], both K-major
       constexpr uint32_t idesc_g = make_idesc_bf16(BT, DH, false, true);    // [kv x dh], B MN-major
       bool ok = mbar_wait(kv_full, 0, p.status, ST_TIMEOUT_FULL);
-      int st = 0;
-      uint32_t ph = 0;
+      int st_s = 0;          // stage / phase of the next score issue
+      uint32_t ph_s = 0;
+      int st_g = 0;          // stage of the next gradient issue
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
-      auto issue_scores = [&](int stage, uint32_t phase) -> bool {
-        if (!mbar_wait(&q_full[stage], phase, p.status, ST_TIMEOUT_FULL)) return false;
+      auto issue_scores = [&]() -> bool {
+        if (!mbar_wait(&q_full[st_s], ph_s, p.status, ST_TIMEOUT_FULL)) return false;
         tc_fence_after();
-        const uint32_t bQ = smem_u32(sQ + stage * Cfg::T_BYTES), bdO = smem_u32(sdO + stage * Cfg::T_BYTES);
+        const uint32_t bQ = smem_u32(sQ + st_s * Cfg::T_BYTES), bdO = smem_u32(sdO + st_s * Cfg::T_BYTES);
 #pragma unroll
         for (int k = 0; k < DH / 16; ++k) {
           const uint32_t off = (k >> 2) * (BT * 128) + (k & 3) * 32;
@@ -185,14 +190,13 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __gri
                        k > 0 ? 1u : 0u);
         }
         umma_commit(st_full);
+        if (++st_s == Cfg::QS) { st_s = 0; ph_s ^= 1; }
         return true;
       };
-      if (ok && n_iter > 0) ok = issue_scores(0, 0);
-      for (int t = 0; t < n_iter && ok; ++t) {
-        if (!mbar_wait(p_full, t & 1, p.status, ST_TIMEOUT_MISC)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t aPT = smem_u32(sPT), adST = smem_u32(sdST);
-        const uint32_t bQ = smem_u32(sQ + st * Cfg::T_BYTES), bdO = smem_u32(sdO + st * Cfg::T_BYTES);
+      auto issue_grads = [&](int t) {
+        const int pb = Cfg::PDB ? (t & 1) : 0;
+        const uint32_t aPT = smem_u32(sPT + pb * Cfg::PT_BYTES), adST = smem_u32(sdST + pb * Cfg::PT_BYTES);
+        const uint32_t bQ = smem_u32(sQ + st_g * Cfg::T_BYTES), bdO = smem_u32(sdO + st_g * Cfg::T_BYTES);
 #pragma unroll
         for (int k = 0; k < BT / 16; ++k) {
           const uint32_t aoff = (k >> 2) * (BT * 128) + (k & 3) * 32;
@@ -205,15 +209,30 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __gri
           umma_bf16_ss(tm_dK, make_smem_desc(adST + aoff, 16, 1024),
                        make_smem_desc(bQ + k * (16 * 128), BT * 128, 1024), idesc_g, (t > 0 || k > 0) ? 1u : 0u);
         }
-        umma_commit(&q_empty[st]);
-        if (++st == Cfg::QS) { st = 0; ph ^= 1; }
-        if (t + 1 < n_iter) ok = issue_scores(st, ph);
+        umma_commit(&q_empty[st_g]);
+        if (++st_g == Cfg::QS) st_g = 0;
+      };
+      if (ok && n_iter > 0) ok = issue_scores();
+      for (int t = 0; t < n_iter && ok; ++t) {
+        if (!mbar_wait(p_full, t & 1, p.status, ST_TIMEOUT_MISC)) { ok = false; break; }
+        tc_fence_after();
+        if (Cfg::PDB) {
+          // scores of t+1 first: their commit also covers the gradient MMAs of t-1, which is what
+          // lets the softmax warps reuse the P^T/dS^T buffer of parity (t+1)&1.
+          if (t + 1 < n_iter) ok = issue_scores();
+          issue_grads(t);
+        } else {
+          issue_grads(t);
+          if (t + 1 < n_iter) ok = issue_scores();
+        }
       }
       if (ok) umma_commit(done);
     }
   } else {
-    const int q = warp & 3;
-    const int r = q * 32 + lane;  // kv row inside the tile == TMEM lane
+    const int sw = warp - 2;        // 0..7
+    const int q = warp & 3;         // TMEM lane quarter
+    const int half = sw >> 2;       // which 64 query columns of the tile this warp handles
+    const int r = q * 32 + lane;    // kv row inside the tile == TMEM lane
     const int kv_idx = kv0 + r;
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
     bool ok = true;
@@ -221,24 +240,17 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __gri
       const int head = kvh * group + t / n_qt;
       const int qt = qt_first + t % n_qt;
       const int q0 = qt * BT;
-      float* lse_b = s_lse + q * BT;
-      float* del_b = s_delta + q * BT;
-      __syncwarp();  // previous iteration's reads are complete
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int col = e * 32 + lane;
-        const int qi = q0 + col;
-        const size_t idx = (static_cast<size_t>(b) * p.H + head) * p.S + qi;
-        lse_b[col] = qi < p.S ? p.lse[idx] * LOG2E : 0.f;
-        del_b[col] = qi < p.S ? p.delta[idx] : 0.f;
-      }
-      __syncwarp();
+      const float2* stats = p.stats + (static_cast<size_t>(b) * p.H + head) * p.S;
+      const int pb = Cfg::PDB ? (t & 1) : 0;
+      uint8_t* pt_buf = sPT + pb * Cfg::PT_BYTES;
+      uint8_t* dst_buf = sdST + pb * Cfg::PT_BYTES;
       if (!mbar_wait(st_full, t & 1, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       const bool diag = p.causal && qt == kt;
       const bool tail = q0 + BT > p.S;
 #pragma unroll 1
-      for (int c = 0; c < BT / 32; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;  // 32-column chunk of the tile
         uint32_t sv[32], dv[32];
         tmem_ld_32x32(tm_ST + lane_off + c * 32, sv);
         tmem_ld_32x32(tm_dPT + lane_off + c * 32, dv);
@@ -250,16 +262,18 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __gri
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int col = c * 32 + i + e;  // query row inside the tile
-            float pv = exp2f(__uint_as_float(sv[i + e]) * p.scale_log2 - lse_b[col]);
+            const int qi = min(q0 + col, p.S - 1);
+            const float2 sd = __ldg(stats + qi);  // same address in every lane: one broadcast load
+            float pv = exp2f(__uint_as_float(sv[i + e]) * p.scale_log2 - sd.x);
             if ((diag && r > col) || (tail && q0 + col >= p.S)) pv = 0.f;
             pr[e] = pv;
-            ds[e] = pv * (__uint_as_float(dv[i + e]) - del_b[col]) * p.scale;
+            ds[e] = pv * (__uint_as_float(dv[i + e]) - sd.y) * p.scale;
           }
           pk[i >> 1] = pack_bf16x2(pr[0], pr[1]);
           dk[i >> 1] = pack_bf16x2(ds[0], ds[1]);
         }
-        store_row32_sw128(sPT, r, c, pk);
-        store_row32_sw128(sdST, r, c, dk);
+        store_row32_sw128(pt_buf, r, c, pk);
+        store_row32_sw128(dst_buf, r, c, dk);
       }
       tc_fence_before();
       fence_proxy_async_smem();
@@ -268,12 +282,14 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __gri
     }
     if (ok && mbar_wait(done, 0, p.status, ST_TIMEOUT_TMEM_FULL)) {
       tc_fence_after();
+      constexpr int CPW = DH / 64;  // 32-column chunks per warp and matrix
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         const uint32_t src = which == 0 ? tm_dK : tm_dV;
         const int col0 = (which == 0 ? (p.H + kvh) : (p.H + p.Hkv + kvh)) * DH;
 #pragma unroll 1
-        for (int c = 0; c < DH / 32; ++c) {
+        for (int cc = 0; cc < CPW; ++cc) {
+          const int c = half * CPW + cc;
           uint32_t v[32];
           tmem_ld_32x32(src + lane_off + c * 32, v);
           tmem_ld_wait();
@@ -302,10 +318,12 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __gri
 // --------------------------------------------------------------------------- dQ
 template <int DH>
 struct DqCfg {
+  static constexpr bool PDB = (DH == 64);        // double-buffer dS
+  static constexpr int NPB = PDB ? 2 : 1;
   static constexpr int KS = (DH == 64) ? 2 : 1;  // (K, V) ring stages
   static constexpr int T_BYTES = BT * DH * 2;
   static constexpr int DS_BYTES = BT * BT * 2;
-  static constexpr int TILE_BYTES = 2 * T_BYTES + KS * 2 * T_BYTES + DS_BYTES;
+  static constexpr int TILE_BYTES = 2 * T_BYTES + KS * 2 * T_BYTES + NPB * DS_BYTES;
   static constexpr int SMEM_BYTES = TILE_BYTES + 1024 + 128;
   static constexpr int TMEM_COLS = 512;  // S 128 | dP 128 | dQ DH
 };
@@ -322,8 +340,8 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid
   uint8_t* sdO = sQ + Cfg::T_BYTES;
   uint8_t* sK = sdO + Cfg::T_BYTES;               // KS stages
   uint8_t* sV = sK + Cfg::KS * Cfg::T_BYTES;      // KS stages
-  uint8_t* sdS = sV + Cfg::KS * Cfg::T_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + Cfg::DS_BYTES);
+  uint8_t* sdS = sV + Cfg::KS * Cfg::T_BYTES;     // NPB buffers
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + Cfg::NPB * Cfg::DS_BYTES);
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;            // KS
   uint64_t* kv_empty = kv_full + Cfg::KS;  // KS
@@ -345,7 +363,7 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid
     mbar_init(q_full, 1);
     for (int s = 0; s < Cfg::KS; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     mbar_init(s_full, 1);
-    mbar_init(p_full, 4);
+    mbar_init(p_full, 8);
     mbar_init(done, 1);
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -386,13 +404,13 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid
       constexpr uint32_t idesc_s = make_idesc_bf16(BT, BT, false, false);
       constexpr uint32_t idesc_g = make_idesc_bf16(BT, DH, false, true);
       bool ok = mbar_wait(q_full, 0, p.status, ST_TIMEOUT_FULL);
-      int st = 0;
-      uint32_t ph = 0;
+      int st_s = 0, st_g = 0;
+      uint32_t ph_s = 0;
       const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO);
-      auto issue_scores = [&](int stage, uint32_t phase) -> bool {
-        if (!mbar_wait(&kv_full[stage], phase, p.status, ST_TIMEOUT_FULL)) return false;
+      auto issue_scores = [&]() -> bool {
+        if (!mbar_wait(&kv_full[st_s], ph_s, p.status, ST_TIMEOUT_FULL)) return false;
         tc_fence_after();
-        const uint32_t bK = smem_u32(sK + stage * Cfg::T_BYTES), bV = smem_u32(sV + stage * Cfg::T_BYTES);
+        const uint32_t bK = smem_u32(sK + st_s * Cfg::T_BYTES), bV = smem_u32(sV + st_s * Cfg::T_BYTES);
 #pragma unroll
         for (int k = 0; k < DH / 16; ++k) {
           const uint32_t off = (k >> 2) * (BT * 128) + (k & 3) * 32;
@@ -406,35 +424,47 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid
                        k > 0 ? 1u : 0u);
         }
         umma_commit(s_full);
+        if (++st_s == Cfg::KS) { st_s = 0; ph_s ^= 1; }
         return true;
       };
-      if (ok) ok = issue_scores(0, 0);
-      for (int j = 0; j < n_blocks && ok; ++j) {
-        if (!mbar_wait(p_full, j & 1, p.status, ST_TIMEOUT_MISC)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t adS = smem_u32(sdS), bK = smem_u32(sK + st * Cfg::T_BYTES);
+      auto issue_grad = [&](int j) {
+        const int pb = Cfg::PDB ? (j & 1) : 0;
+        const uint32_t adS = smem_u32(sdS + pb * Cfg::DS_BYTES), bK = smem_u32(sK + st_g * Cfg::T_BYTES);
 #pragma unroll
         for (int k = 0; k < BT / 16; ++k) {
           const uint32_t aoff = (k >> 2) * (BT * 128) + (k & 3) * 32;
           umma_bf16_ss(tm_dQ, make_smem_desc(adS + aoff, 16, 1024),
                        make_smem_desc(bK + k * (16 * 128), BT * 128, 1024), idesc_g, (j > 0 || k > 0) ? 1u : 0u);
         }
-        umma_commit(&kv_empty[st]);
-        if (++st == Cfg::KS) { st = 0; ph ^= 1; }
-        if (j + 1 < n_blocks) ok = issue_scores(st, ph);
+        umma_commit(&kv_empty[st_g]);
+        if (++st_g == Cfg::KS) st_g = 0;
+      };
+      if (ok) ok = issue_scores();
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        if (!mbar_wait(p_full, j & 1, p.status, ST_TIMEOUT_MISC)) { ok = false; break; }
+        tc_fence_after();
+        if (Cfg::PDB) {
+          if (j + 1 < n_blocks) ok = issue_scores();
+          issue_grad(j);
+        } else {
+          issue_grad(j);
+          if (j + 1 < n_blocks) ok = issue_scores();
+        }
       }
       if (ok) umma_commit(done);
     }
   } else {
+    const int sw = warp - 2;
     const int q = warp & 3;
+    const int half = sw >> 2;
     const int r = q * 32 + lane;
     const int q_idx = q0 + r;
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
     float lse2 = 0.f, del = 0.f;
     if (q_idx < p.S) {
-      const size_t idx = (static_cast<size_t>(b) * p.H + head) * p.S + q_idx;
-      lse2 = p.lse[idx] * LOG2E;
-      del = p.delta[idx];
+      const float2 sd = p.stats[(static_cast<size_t>(b) * p.H + head) * p.S + q_idx];
+      lse2 = sd.x;
+      del = sd.y;
     }
     bool ok = true;
     for (int j = 0; j < n_blocks; ++j) {
@@ -443,8 +473,10 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid
       const int kv0 = j * BT;
       const bool need_mask = (p.causal && j == n_blocks - 1) || (kv0 + BT > p.S);
       const int limit = p.causal ? min(q_idx, p.S - 1) : (p.S - 1);
+      uint8_t* ds_buf = sdS + (Cfg::PDB ? (j & 1) : 0) * Cfg::DS_BYTES;
 #pragma unroll 1
-      for (int c = 0; c < BT / 32; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
         uint32_t sv[32], dv[32];
         tmem_ld_32x32(tm_S + lane_off + c * 32, sv);
         tmem_ld_32x32(tm_dP + lane_off + c * 32, dv);
@@ -461,7 +493,7 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid
           }
           dk[i >> 1] = pack_bf16x2(ds[0], ds[1]);
         }
-        store_row32_sw128(sdS, r, c, dk);
+        store_row32_sw128(ds_buf, r, c, dk);
       }
       tc_fence_before();
       fence_proxy_async_smem();
@@ -470,8 +502,10 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid
     }
     if (ok && mbar_wait(done, 0, p.status, ST_TIMEOUT_TMEM_FULL)) {
       tc_fence_after();
+      constexpr int CPW = DH / 64;
 #pragma unroll 1
-      for (int c = 0; c < DH / 32; ++c) {
+      for (int cc = 0; cc < CPW; ++cc) {
+        const int c = half * CPW + cc;
         uint32_t v[32];
         tmem_ld_32x32(tm_dQ + lane_off + c * 32, v);
         tmem_ld_wait();
@@ -520,7 +554,8 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& td, const BwdPar
 using namespace sb;
 
 // qkv, dqkv: bf16 [B*S, ld]; O, dO: bf16 [B*S, ld_o / ld_do] (H*dh columns); lse: fp32 [B,H,S];
-// delta: fp32 [B,H,S] scratch written here. dqkv receives dQ | dK | dV in the qkv layout.
+// delta: scratch of 2*B*H*S floats written here ((lse*log2e, delta) pairs). dqkv receives dQ | dK | dV in
+// the qkv layout.
 extern "C" int sb_attention_bwd(const void* qkv, const void* O, const float* lse, const void* dO, void* dqkv,
                                 float* delta, int B, int S, int H, int Hkv, int dh, int ld, int ld_o, int ld_do,
                                 float scale, int causal, int* status, void* stream_) {
@@ -534,8 +569,9 @@ extern "C" int sb_attention_bwd(const void* qkv, const void* O, const float* lse
   if (rc) return rc;
   const int warps = B * S * H;
   attn_delta_kernel<<<(warps + 7) / 8, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(O),
-                                                         static_cast<const __nv_bfloat16*>(dO), delta, B, S, H, dh,
-                                                         ld_o, ld_do);
+                                                         static_cast<const __nv_bfloat16*>(dO), lse,
+                                                         reinterpret_cast<float2*>(delta), B, S, H, dh, ld_o,
+                                                         ld_do);
   if (cudaGetLastError() != cudaSuccess) return SB_ERR_LAUNCH;
   BwdParams p;
   p.B = B; p.S = S; p.H = H; p.Hkv = Hkv;
@@ -544,7 +580,7 @@ extern "C" int sb_attention_bwd(const void* qkv, const void* O, const float* lse
   p.scale_log2 = scale * LOG2E;
   p.causal = causal;
   p.lse = lse;
-  p.delta = delta;
+  p.stats = reinterpret_cast<const float2*>(delta);
   p.dqkv = static_cast<__nv_bfloat16*>(dqkv);
   p.status = status;
   return dh == 64 ? launch_bwd<64>(tq, td, p, stream) : launch_bwd<128>(tq, td, p, stream);

@@ -33,6 +33,7 @@
 namespace sb {
 
 constexpr int MAX_WORLD = 16;
+constexpr int SLOT_WORDS = 4 * MAX_WORLD;  // flag words per slot (phases 0..3 x MAX_WORLD ranks)
 constexpr uint64_t kPeerWaitNsDefault = 10000000000ull;  // 10 s: a peer may start its kernel late
 
 struct PeerTable {
@@ -93,12 +94,12 @@ __global__ void __launch_bounds__(512)
 allreduce_bf16_kernel(const __grid_constant__ AllReduceParams p) {
   __shared__ int s_ok;
   const int W = p.W;
-  uint32_t* my_flags = p.t.flags[p.rank] + static_cast<size_t>(p.slot) * 2 * MAX_WORLD;
+  uint32_t* my_flags = p.t.flags[p.rank] + static_cast<size_t>(p.slot) * SLOT_WORDS;
   if (threadIdx.x == 0) {
     if (blockIdx.x == 0) {
       __threadfence_system();
       for (int r = 0; r < W; ++r)
-        st_release_sys(p.t.flags[r] + static_cast<size_t>(p.slot) * 2 * MAX_WORLD + p.rank, p.epoch);
+        st_release_sys(p.t.flags[r] + static_cast<size_t>(p.slot) * SLOT_WORDS + p.rank, p.epoch);
     }
     s_ok = wait_flags(my_flags, W, p.epoch, p.wait_ns, p.status) ? 1 : 0;
   }
@@ -157,7 +158,7 @@ allreduce_bf16_kernel(const __grid_constant__ AllReduceParams p) {
       if (ok) {
         __threadfence_system();
         for (int r = 0; r < W; ++r)
-          st_release_sys(p.t.flags[r] + static_cast<size_t>(p.slot) * 2 * MAX_WORLD + MAX_WORLD + p.rank, p.epoch);
+          st_release_sys(p.t.flags[r] + static_cast<size_t>(p.slot) * SLOT_WORDS + MAX_WORLD + p.rank, p.epoch);
         wait_flags(my_flags + MAX_WORLD, W, p.epoch, p.wait_ns, p.status);
       }
     }
@@ -195,7 +196,7 @@ extern "C" int sb_ipc_open(const void* handle, void** out) {
 }
 extern "C" int sb_ipc_close(void* p) { return cudaIpcCloseMemHandle(p) == cudaSuccess ? 0 : SB_ERR_RUNTIME; }
 extern "C" int sb_ipc_handle_size() { return static_cast<int>(sizeof(cudaIpcMemHandle_t)); }
-extern "C" int sb_flag_words_per_slot() { return 2 * MAX_WORLD; }
+extern "C" int sb_flag_words_per_slot() { return SLOT_WORDS; }
 
 // in_ptrs/out_ptrs/flag_ptrs: host arrays of W device pointers (peer-mapped; entry `rank` is local).
 // n_elems must be a multiple of 8; buffers 16-byte aligned. wait_ms <= 0 selects the default.

@@ -18,7 +18,8 @@
 // Kernel shape: persistent, one CTA per SM, 6 warps:
 //   warp 0   TMA producer (one elected lane)
 //   warp 1   MMA issuer (one elected lane); owns the TMEM allocation
-//   warp 2-5 epilogue: each warp drains the 32 TMEM lanes its (warp_id % 4) may touch
+//   warp 2-9 epilogue: a warp may touch the 32 TMEM lanes of quarter (warp_id % 4); the two
+//            warps of a quarter split the tile's columns
 // Two fp32 accumulators (2 x BN columns of TMEM) let the epilogue of tile i overlap the
 // main loop of tile i+1. K is walked in a fixed order, so results are bitwise
 // repeatable; split-K writes fp32 partials that a second kernel adds in split order.
@@ -30,7 +31,7 @@ namespace sb {
 constexpr int BM = 128;
 constexpr int BK = 64;       // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
 
 template <int BN>
 struct GemmCfg {
@@ -83,7 +84,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 4);  // one arrival per epilogue warp
+      mbar_init(&tmem_empty[a], 8);  // one arrival per epilogue warp
     }
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -175,7 +176,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else {
     // -------------------------------- epilogue --------------------------------
-    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    const int q = warp & 3;            // TMEM lane quarter this warp may access
+    const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp drains
     bool ok = true;
     int it = 0;
     for (int t = blockIdx.x; t < tiles_total && ok; t += gridDim.x, ++it) {
@@ -190,7 +192,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int row = m_idx * BM + q * 32 + lane;
       const uint32_t taddr_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
         uint32_t r[32];
         tmem_ld_32x32(taddr_row + c * 32, r);
         tmem_ld_wait();

@@ -65,7 +65,7 @@ def attention_bwd(qkv, o, lse, do, B, S, H, Hkv, dh, causal=True, scale=None):
     if not qkv.is_cuda:
         return attention_bwd_ref(qkv, do, B, S, H, Hkv, dh, causal, scale).to(qkv.dtype)
     dqkv = torch.empty_like(qkv)
-    delta = torch.empty((B, H, S), dtype=torch.float32, device=qkv.device)
+    delta = torch.empty((B, H, S, 2), dtype=torch.float32, device=qkv.device)
     _lib.call("sb_attention_bwd", qkv.data_ptr(), o.data_ptr(), lse.data_ptr(), do.data_ptr(), dqkv.data_ptr(),
               delta.data_ptr(), B, S, H, Hkv, dh, qkv.stride(0), o.stride(0), do.stride(0), float(scale),
               int(causal), _lib.status_word(qkv.device).data_ptr(), _lib.stream())

@@ -1,0 +1,110 @@
+"""Micro-benchmarks of single native kernels (CUDA-event timing, warm-up, L2 flush between
+iterations). Also the small fixed workloads that the committed profiler summaries were taken on.
+
+    python -m scirust_b200.ops.bench_kernels gemm --form nt --m 8192 --n 8192 --k 8192
+    python -m scirust_b200.ops.bench_kernels attention --batch 8 --seq 2048 --heads 16 --kv-heads 4 --dh 64
+    python -m scirust_b200.ops.bench_kernels attention_bwd --batch 1 --seq 2048
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import _lib, attention as att, basic, gemm
+
+BF = torch.bfloat16
+
+
+def _time(fn, iters: int, warmup: int, flush: bool = True) -> float:
+    """Mean milliseconds per call; a 256 MiB buffer is rewritten between calls to evict L2."""
+    scratch = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush:
+            scratch.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    _lib.check_status()
+    return total / iters
+
+
+def _rand(shape, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, generator=g, device="cuda") * 0.5).to(BF)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["gemm", "attention", "attention_bwd", "rmsnorm", "ce", "adamw"])
+    ap.add_argument("--form", default="nt", choices=["nn", "nt", "tn"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--kv-heads", type=int, default=4)
+    ap.add_argument("--dh", type=int, default=64)
+    ap.add_argument("--rows", type=int, default=16384)
+    ap.add_argument("--cols", type=int, default=1024)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-flush", action="store_true")
+    a = ap.parse_args(argv)
+    out = {"kernel": a.kernel}
+    flush = not a.no_flush
+    if a.kernel == "gemm":
+        M, N, K = a.m, a.n, a.k
+        if a.form == "nn":
+            x, w = _rand((M, K), 1), _rand((K, N), 2)
+            fn = lambda: gemm.matmul_nn(x, w)  # noqa: E731
+        elif a.form == "nt":
+            x, w = _rand((M, K), 1), _rand((N, K), 2)
+            fn = lambda: gemm.matmul_nt(x, w)  # noqa: E731
+        else:
+            x, w = _rand((K, M), 1), _rand((K, N), 2)
+            fn = lambda: gemm.matmul_tn(x, w)  # noqa: E731
+        ms = _time(fn, a.iters, a.warmup, flush)
+        out.update(form=a.form, m=M, n=N, k=K, ms=ms, tflops=2.0 * M * N * K / ms / 1e9)
+    elif a.kernel in ("attention", "attention_bwd"):
+        B, S, H, Hkv, dh = a.batch, a.seq, a.heads, a.kv_heads, a.dh
+        qkv = _rand((B * S, (H + 2 * Hkv) * dh), 3)
+        flops = 4.0 * B * H * S * S * dh / 2
+        if a.kernel == "attention":
+            ms = _time(lambda: att.attention_fwd(qkv, B, S, H, Hkv, dh), a.iters, a.warmup, flush)
+        else:
+            o, lse = att.attention_fwd(qkv, B, S, H, Hkv, dh)
+            do = _rand((B * S, H * dh), 4)
+            ms = _time(lambda: att.attention_bwd(qkv, o, lse, do, B, S, H, Hkv, dh), a.iters, a.warmup, flush)
+            flops *= 2.5
+        out.update(batch=B, seq=S, heads=H, kv_heads=Hkv, dh=dh, causal=True, ms=ms, tflops=flops / ms / 1e9)
+    elif a.kernel == "rmsnorm":
+        x, w = _rand((a.rows, a.cols), 5), _rand((a.cols,), 6)
+        ms = _time(lambda: basic.rmsnorm_fwd(x, w), a.iters, a.warmup, flush)
+        out.update(rows=a.rows, cols=a.cols, ms=ms, gbs=2 * x.numel() * 2 / ms / 1e6)
+    elif a.kernel == "ce":
+        x = _rand((a.rows, a.cols), 7)
+        t = torch.randint(0, a.cols, (a.rows,), device="cuda")
+        ms = _time(lambda: basic.ce_fwd_bwd(x, t, 1.0 / a.rows), a.iters, a.warmup, flush)
+        out.update(rows=a.rows, cols=a.cols, ms=ms, gbs=3 * x.numel() * 2 / ms / 1e6)
+    elif a.kernel == "adamw":
+        n = a.rows * a.cols
+        p = torch.randn(n, device="cuda")
+        m, v = torch.zeros_like(p), torch.zeros_like(p)
+        g, pb = _rand((n,), 8), torch.empty(n, dtype=BF, device="cuda")
+        ms = _time(lambda: basic.optim_step(p, m, v, g, pb, lr=1e-3, step=1), a.iters, a.warmup, flush)
+        out.update(n=n, ms=ms, gbs=n * (12 + 12 + 2 + 2) / ms / 1e6)
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

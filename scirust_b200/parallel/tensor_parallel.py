@@ -1,0 +1,190 @@
+"""Tensor parallelism with sequence-parallel activations (Megatron-style column/row sharding).
+
+Activations between blocks are sharded over the token dimension (rank r holds rows
+``[r*T/W, (r+1)*T/W)``); inside a block the QKV and gate/up projections are column-parallel and the
+o_proj / down projections row-parallel. Each boundary is one fused kernel
+(csrc/gemm_dist_tcgen05.cu):
+
+* ``ag_matmul``   all-gather -> GEMM: the sharded operand is read tile by tile from the owning
+  rank's memory by TMA while the tensor cores run; nothing is gathered into a buffer.
+* ``matmul_rs``   GEMM -> reduce-scatter: partial tiles go straight from the epilogue to the owning
+  rank, which adds the W partials in rank order (+ residual).
+
+``backend="nccl"`` runs the same math as NCCL all-gather / reduce-scatter around library GEMMs
+(`torch.matmul`): the baseline configuration the fused path is measured against. The reference has
+no tensor parallelism at all (src/lib.rs:133); what is kept from it is the fixed rank-order
+reduction contract (scirust-core/src/distributed.rs:96-167).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from ..ops import gemm as _g
+from .symm import SymmetricRegion
+
+BF = torch.bfloat16
+
+_lib.register("sb_gemm_dist_bf16", [_lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32,
+                                    _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32,
+                                    _lib.i32, _lib.i32, _lib.i32, _lib.i32, C.c_uint32, _lib.vp, _lib.i32, _lib.i32,
+                                    _lib.vp, _lib.vp])
+
+
+class TPContext:
+    """Process-group state for the fused tensor-parallel kernels: a symmetric region holding the
+    peer-visible activation buffers, the double-buffered reduce-scatter staging area and the flag
+    slots."""
+
+    def __init__(self, group, max_rows: int, max_cols: int, sym_bytes: int = 0, backend: str = "fused",
+                 wait_ms: int = 0):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.backend = backend
+        self.wait_ms = wait_ms
+        self.dev = torch.device("cuda", torch.cuda.current_device())
+        self.epoch = 0
+        self.rs_calls = 0
+        self._named = {}
+        if backend == "fused":
+            stage_bytes = max_rows * max_cols * 2          # W * (rows/W) * cols bf16
+            total = 2 * stage_bytes + sym_bytes + (1 << 20)
+            self.region = SymmetricRegion(group, total, device=self.dev)
+            self.stage = [self.region.tensor((max_rows * max_cols,), BF) for _ in range(2)]
+            self.stage_ptrs = [self.region.peer_ptrs(s) for s in self.stage]
+            self.slot = self.region.new_slot()
+            wps = self.region.words_per_slot
+            self.flag_ptrs = (C.c_void_p * self.world)(
+                *[b + self.region.data_bytes + self.slot * wps * 4 for b in self.region.peer_base])
+            self.counters = torch.zeros(32, dtype=torch.int32, device=self.dev)
+        else:
+            self.region = None
+
+    # peer-visible persistent buffers, keyed by name (activations that another rank's kernel reads)
+    def buffer(self, name: str, shape, dtype=BF) -> torch.Tensor:
+        key = (name, tuple(shape), dtype)
+        t = self._named.get(key)
+        if t is None:
+            if self.region is not None:
+                t = self.region.tensor(tuple(shape), dtype)
+            else:
+                t = torch.empty(tuple(shape), dtype=dtype, device=self.dev)
+            self._named[key] = t
+        return t
+
+    def _ptrs(self, t: torch.Tensor, gathered: bool):
+        if gathered:
+            return self.region.peer_ptrs(t)
+        return (C.c_void_p * self.world)(*([t.data_ptr()] * self.world))
+
+    def _call(self, a, b, out, residual, M, N, K, a_mn, b_mn, a_gather, b_gather, scatter, bn=0):
+        self.epoch += 1
+        stage = None
+        if scatter:
+            stage = self.stage_ptrs[self.rs_calls & 1]
+            self.rs_calls += 1
+            if M * N > self.stage[0].numel():
+                raise ValueError("reduce-scatter staging area too small for this product")
+        _lib.call("sb_gemm_dist_bf16", self._ptrs(a, a_gather), self._ptrs(b, b_gather), out.data_ptr(),
+                  _lib.ptr(residual), stage, self.flag_ptrs, M, N, K, a.stride(0), b.stride(0), out.stride(0),
+                  residual.stride(0) if residual is not None else 0, int(a_mn), int(b_mn), int(a_gather),
+                  int(b_gather), int(scatter), self.rank, self.world, self.epoch, self.counters.data_ptr(), bn,
+                  self.wait_ms, _lib.status_word(self.dev).data_ptr(), _lib.stream())
+        _g.launch_count += 1
+        return out
+
+    # ---------------------------------------------------------------- fused products
+    def ag_matmul_nn(self, x_shard, w):
+        """all-gather(x_shard over rows) @ w   -> [T, N]; x_shard must come from ``buffer()``."""
+        Tl, K = x_shard.shape
+        T, N = Tl * self.world, w.shape[1]
+        if self.backend != "fused":
+            x = torch.empty((T, K), dtype=BF, device=self.dev)
+            dist.all_gather_into_tensor(x, x_shard.contiguous(), group=self.group)
+            return torch.matmul(x, w)
+        out = torch.empty((T, N), dtype=BF, device=self.dev)
+        return self._call(x_shard, w, out, None, T, N, K, False, True, True, False, False)
+
+    def ag_matmul_nt(self, x_shard, w):
+        """all-gather(x_shard) @ wᵀ  (w [N, K]) -> [T, N]."""
+        Tl, K = x_shard.shape
+        T, N = Tl * self.world, w.shape[0]
+        if self.backend != "fused":
+            x = torch.empty((T, K), dtype=BF, device=self.dev)
+            dist.all_gather_into_tensor(x, x_shard.contiguous(), group=self.group)
+            return torch.matmul(x, w.t())
+        out = torch.empty((T, N), dtype=BF, device=self.dev)
+        return self._call(x_shard, w, out, None, T, N, K, False, False, True, False, False)
+
+    def matmul_nn_rs(self, a, w, residual_shard=None):
+        """reduce-scatter over rows of (a @ w) (+ residual_shard) -> [T/W, N]."""
+        T, K = a.shape
+        N = w.shape[1]
+        Tl = T // self.world
+        if self.backend != "fused":
+            full = torch.matmul(a, w)
+            out = torch.empty((Tl, N), dtype=BF, device=self.dev)
+            dist.reduce_scatter_tensor(out, full, group=self.group)
+            return out + residual_shard if residual_shard is not None else out
+        out = torch.empty((Tl, N), dtype=BF, device=self.dev)
+        return self._call(a, w, out, residual_shard, T, N, K, False, True, False, False, True)
+
+    def matmul_nt_rs(self, a, w, residual_shard=None):
+        """reduce-scatter over rows of (a @ wᵀ) (w [N, K]) (+ residual_shard) -> [T/W, N]."""
+        T, K = a.shape
+        N = w.shape[0]
+        Tl = T // self.world
+        if self.backend != "fused":
+            full = torch.matmul(a, w.t())
+            out = torch.empty((Tl, N), dtype=BF, device=self.dev)
+            dist.reduce_scatter_tensor(out, full, group=self.group)
+            return out + residual_shard if residual_shard is not None else out
+        out = torch.empty((Tl, N), dtype=BF, device=self.dev)
+        return self._call(a, w, out, residual_shard, T, N, K, False, False, False, False, True)
+
+    def ag_matmul_tn(self, x_shard, dy, out=None, residual=None):
+        """all-gather(x_shard)ᵀ @ dy -> [K_x, N]: weight gradient of a column-parallel layer
+        (x sharded over tokens, dy local with all tokens)."""
+        Tl, M = x_shard.shape
+        T, N = dy.shape
+        if self.backend != "fused":
+            x = torch.empty((T, M), dtype=BF, device=self.dev)
+            dist.all_gather_into_tensor(x, x_shard.contiguous(), group=self.group)
+            r = torch.matmul(x.t(), dy)
+            if residual is not None:
+                r = r + residual
+            if out is not None:
+                out.copy_(r)
+                return out
+            return r
+        if out is None:
+            out = torch.empty((M, N), dtype=BF, device=self.dev)
+        return self._call(x_shard, dy, out, residual, M, N, T, True, True, True, False, False)
+
+    def matmul_tn_ag(self, a, dy_shard, out=None, residual=None):
+        """aᵀ @ all-gather(dy_shard) -> [K_a, N]: weight gradient of a row-parallel layer
+        (a local with all tokens, dy sharded over tokens)."""
+        T, M = a.shape
+        Tl, N = dy_shard.shape
+        if self.backend != "fused":
+            dy = torch.empty((T, N), dtype=BF, device=self.dev)
+            dist.all_gather_into_tensor(dy, dy_shard.contiguous(), group=self.group)
+            r = torch.matmul(a.t(), dy)
+            if residual is not None:
+                r = r + residual
+            if out is not None:
+                out.copy_(r)
+                return out
+            return r
+        if out is None:
+            out = torch.empty((M, N), dtype=BF, device=self.dev)
+        return self._call(a, dy_shard, out, residual, M, N, T, True, True, False, True, False)
+
+    def close(self):
+        if self.region is not None:
+            self.region.close()
+            self.region = None

@@ -75,13 +75,20 @@ class Trainer:
         loss.backward()
         grad = model.flat_grad
         grad_scale = 1.0
+        if hasattr(model, "finish_grads"):
+            # tensor-parallel shard: sum replicated parameters' gradients, learn the remaining scale
+            grad_scale = model.finish_grads()
         if self.grad_reducer is not None:
             out = self.grad_reducer(grad)
             if isinstance(out, tuple):
-                grad, grad_scale = out
+                grad, g2 = out
             else:
-                grad_scale = out
-        ops.sumsq(grad, out=self.grad_sumsq)
+                g2 = out
+            grad_scale *= g2
+        if hasattr(model, "global_grad_sumsq"):
+            model.global_grad_sumsq(self.grad_sumsq, grad_scale)
+        else:
+            ops.sumsq(grad, out=self.grad_sumsq)
         self.step += 1
         lr = self.schedule.lr_at(self.step - 1)
         ops.optim_step(self.master, self.m, self.v, grad, model.flat, lr=lr, beta1=c.beta1, beta2=c.beta2,

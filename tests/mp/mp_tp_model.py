@@ -1,0 +1,56 @@
+"""Child of tests/test_multigpu.py: the tensor-parallel decoder (fused kernels) trains like the
+single-GPU model and like its own NCCL baseline."""
+import os
+
+import torch
+import torch.distributed as dist
+
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+dist.init_process_group("nccl", device_id=dev)
+
+from scirust_b200.models import GQADecoder, SciAgentConfig  # noqa: E402
+from scirust_b200.models.sciagent_tp import TPDecoder  # noqa: E402
+from scirust_b200.ops import _lib  # noqa: E402
+from scirust_b200.parallel.tensor_parallel import TPContext  # noqa: E402
+from scirust_b200.train import Trainer, TrainerConfig  # noqa: E402
+
+cfg = SciAgentConfig(vocab_size=1024, d_model=256, n_layers=2, n_heads=4, n_kv_heads=2, d_ff=512, max_seq_len=256,
+                     rope_theta=10000.0)
+B, S = 2, 256
+g = torch.Generator().manual_seed(7)
+batches = [torch.randint(0, cfg.vocab_size, (B, S + 1), generator=g) for _ in range(3)]
+
+
+def run_tp(backend):
+    tp = TPContext(dist.group.WORLD, B * S, cfg.d_model, sym_bytes=32 << 20, backend=backend)
+    model = TPDecoder(cfg, tp, seed=3)
+    tr = Trainer(model, TrainerConfig(lr=1e-3))
+    losses = []
+    for tok in batches:
+        l = tr.train_step(tok).detach().clone()
+        dist.all_reduce(l)
+        losses.append(float(l.item()) / world)
+    torch.cuda.synchronize()
+    _lib.check_status(dev)
+    flat = model.flat.clone()
+    tp.close()
+    return losses, flat
+
+
+lf, wf = run_tp("fused")
+lf2, wf2 = run_tp("fused")
+ln, wn = run_tp("nccl")
+assert torch.equal(wf, wf2), "fused tensor-parallel training is not bitwise repeatable"
+full = GQADecoder(cfg, device=dev, seed=3)
+tr = Trainer(full, TrainerConfig(lr=1e-3))
+l1 = [float(tr.train_step(t).item()) for t in batches]
+for a, b, c in zip(lf, ln, l1):
+    assert abs(a - c) < 3e-2 and abs(b - c) < 3e-2, (lf, ln, l1)
+rel = (wf.float() - wn.float()).norm() / wn.float().norm()
+assert rel < 5e-3, rel
+dist.barrier()
+if rank == 0:
+    print("TP_MODEL_OK", lf, ln, l1, float(rel))
+dist.destroy_process_group()

@@ -43,3 +43,9 @@ def test_tp_fused_layers_match_nccl_baseline():
     _need(2)
     out = _run("mp_tp_layers.py", 2, 29613)
     assert "TP_OK" in out
+
+
+def test_tp_decoder_trains_like_single_gpu():
+    _need(2)
+    out = _run("mp_tp_model.py", 2, 29614)
+    assert "TP_MODEL_OK" in out
