@@ -1,0 +1,279 @@
+"""Inference engine for the SciAgent / Llama-shaped GQA decoder: batched flash prefill, paged bf16
+KV cache, split-KV flash-decode, bf16 or int8 per-output-channel weights, device-side greedy
+feedback (no per-token device->host copy) and CUDA-graph replay of the decode step.
+
+Counterparts in the reference: ``CudaModel::prefill_cached`` / ``decode_step_cached`` /
+``generate_cached`` (scirust-sciagent/src/cuda_model.rs:450-581), the batch-1 latency decoder with
+fused QKV and gate/up, fixed-capacity KV and device feedback (scirust-sciagent/src/cuda_decode.rs:
+17-470), ``PagedKvCache`` (scirust-core/src/nn/paged_attention.rs:21-147) and per-channel int8
+weights (scirust-core/src/quantization.rs:95-190). Differences by design: prefill is one batched
+causal pass (the reference's latency decoder feeds the prompt token by token), the cache is paged
+and pre-sized (the reference's general path re-allocates the cache every token), any batch size
+decodes in one step, and sampling other than greedy uses the shared ``sample_row`` policy on a
+logits row copied to the host.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from .. import ops
+from ..generate import SamplerRng, SamplingParams, sample_row
+from ..ops import _lib, attention as att, decode as D
+from .sciagent import BF, GQADecoder, SciAgentConfig
+
+
+class BlockAllocator:
+    """Host-side page allocator (native: csrc/rt_alloc.cpp)."""
+
+    def __init__(self, n_blocks: int):
+        lib = _lib.rt()
+        lib.sbrt_balloc_new.restype = C.c_void_p
+        lib.sbrt_balloc_new.argtypes = [C.c_int32]
+        lib.sbrt_balloc_delete.argtypes = [C.c_void_p]
+        lib.sbrt_balloc_num_free.argtypes = [C.c_void_p]
+        lib.sbrt_balloc_num_free.restype = C.c_int32
+        lib.sbrt_balloc_alloc.argtypes = [C.c_void_p, C.c_int32, C.c_void_p]
+        lib.sbrt_balloc_alloc.restype = C.c_int32
+        lib.sbrt_balloc_free.argtypes = [C.c_void_p, C.c_void_p, C.c_int32]
+        lib.sbrt_balloc_free.restype = C.c_int32
+        self._lib = lib
+        self._h = lib.sbrt_balloc_new(n_blocks)
+        if not self._h:
+            raise ValueError("n_blocks must be positive")
+        self.n_blocks = n_blocks
+
+    def num_free(self) -> int:
+        return int(self._lib.sbrt_balloc_num_free(self._h))
+
+    def alloc(self, n: int) -> list:
+        buf = (C.c_int32 * max(n, 1))()
+        if self._lib.sbrt_balloc_alloc(self._h, n, buf) != 0:
+            raise MemoryError(f"KV cache exhausted: {n} pages requested, {self.num_free()} free")
+        return list(buf[:n])
+
+    def free(self, ids) -> None:
+        ids = list(ids)
+        buf = (C.c_int32 * max(len(ids), 1))(*ids)
+        if self._lib.sbrt_balloc_free(self._h, buf, len(ids)) != 0:
+            raise ValueError("invalid page ids returned to the allocator")
+
+    def __del__(self):
+        try:
+            if self._h:
+                self._lib.sbrt_balloc_delete(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+
+class PagedKVCache:
+    """Pools ``[n_layers][n_blocks, 2, Hkv, page, dh]`` (bf16) + block table + lengths."""
+
+    def __init__(self, n_layers, n_blocks, Hkv, dh, page, max_batch, max_seq, device):
+        self.page, self.max_batch = page, max_batch
+        self.max_blocks = (max_seq + page - 1) // page
+        self.pools = [torch.zeros((n_blocks, 2, Hkv, page, dh), dtype=BF, device=device) for _ in range(n_layers)]
+        self.alloc = BlockAllocator(n_blocks)
+        self.table_host = torch.zeros((max_batch, self.max_blocks), dtype=torch.int32)
+        self.block_table = torch.zeros((max_batch, self.max_blocks), dtype=torch.int32, device=device)
+        self.seq_len = torch.zeros(max_batch, dtype=torch.int32, device=device)
+        self.owned = [[] for _ in range(max_batch)]
+
+    def reserve(self, seq: int, n_tokens: int) -> None:
+        """Make sure sequence ``seq`` owns pages for positions < n_tokens."""
+        need = (n_tokens + self.page - 1) // self.page
+        if need > self.max_blocks:
+            raise ValueError("sequence longer than the cache was sized for")
+        have = len(self.owned[seq])
+        if need > have:
+            new = self.alloc.alloc(need - have)
+            self.table_host[seq, have:need] = torch.tensor(new, dtype=torch.int32)
+            self.owned[seq] += new
+
+    def commit(self) -> None:
+        self.block_table.copy_(self.table_host, non_blocking=True)
+
+    def release(self, seq: int) -> None:
+        self.alloc.free(self.owned[seq])
+        self.owned[seq] = []
+        self.table_host[seq].zero_()
+
+
+class InferenceEngine:
+    def __init__(self, model: GQADecoder, quant: str | None = None, max_batch: int = 1, max_seq: int = 4096,
+                 page: int = 64, use_graph: bool = True):
+        cfg = model.cfg
+        self.cfg, self.quant = cfg, quant
+        dev = model.flat.device
+        self.dev = dev
+        self.max_batch, self.max_seq = max_batch, max_seq
+        self.use_graph = use_graph and dev.type == "cuda"
+
+        def prep(w):
+            return D.quantize_per_channel(w.detach()) if quant == "int8" else w.detach()
+        self.embed = model.embed.detach()
+        self.layers = []
+        for l in model.layers:
+            self.layers.append({"rms1": l.rms_attn.detach(), "wqkv": prep(l.wqkv), "wo": prep(l.wo),
+                                "rms2": l.rms_ffn.detach(), "wgu": prep(l.wgu), "wd": prep(l.wd)})
+        self.rms_final = model.rms_final.detach()
+        # LM head as [d, V] so the weight-streaming kernels read it row by row
+        self.head_t = prep(model.head_weight().detach().t().contiguous())
+        n_blocks = max_batch * ((max_seq + page - 1) // page)
+        self.cache = PagedKVCache(cfg.n_layers, n_blocks, cfg.n_kv_heads, cfg.head_dim, page, max_batch, max_seq, dev)
+        self.cos, self.sin = ops.rope_table(max(cfg.max_seq_len, max_seq), cfg.head_dim, cfg.rope_theta, dev)
+        self.tokens = torch.zeros(max_batch, dtype=torch.int64, device=dev)     # device feedback buffer
+        self.logits = torch.zeros((max_batch, cfg.vocab_size), dtype=torch.float32, device=dev)
+        self._graph = None
+        self._graph_batch = None
+
+    # ------------------------------------------------------------------ linear dispatch
+    def _linear(self, x, w, residual=None):
+        M = x.shape[0]
+        if M <= 8:
+            return D.gemv(x, w, residual=residual)
+        if isinstance(w, D.QuantWeight):
+            w = w.dequantize()
+        return ops.matmul_nn(x, w, residual=residual)
+
+    # ------------------------------------------------------------------ prefill
+    def prefill(self, tokens: torch.Tensor):
+        """tokens [B, P] (all prompts the same length). Fills the cache, leaves the greedy next
+        token of every sequence in ``self.tokens`` and returns the last-position logits [B, V]."""
+        cfg, cache = self.cfg, self.cache
+        B, P = tokens.shape
+        H, Hkv, dh = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        tok = tokens.to(self.dev)
+        for b in range(B):
+            if cache.owned[b]:
+                cache.release(b)
+            cache.reserve(b, min(self.max_seq, P + 1))
+        cache.commit()
+        seq_of = torch.arange(B, dtype=torch.int32, device=self.dev).repeat_interleave(P)
+        pos = torch.arange(P, dtype=torch.int32, device=self.dev).repeat(B)
+        x = ops.embed_fwd(self.embed, tok.reshape(-1))
+        for li, l in enumerate(self.layers):
+            h, _ = ops.rmsnorm_fwd(x, l["rms1"], cfg.eps, want_inv=False)
+            qkv = self._linear(h, l["wqkv"])
+            ops.rope_(qkv, H + Hkv, dh, P, self.cos, self.sin)
+            D.kv_append(qkv, H, Hkv, dh, cache.pools[li], cache.block_table, cache.page, seq_of, pos)
+            a, _ = att.attention_fwd(qkv, B, P, H, Hkv, dh, causal=True, want_lse=False)
+            x = self._linear(a, l["wo"], residual=x)
+            h, _ = ops.rmsnorm_fwd(x, l["rms2"], cfg.eps, want_inv=False)
+            gu = self._linear(h, l["wgu"])
+            x = self._linear(ops.swiglu_fwd(gu), l["wd"], residual=x)
+        last = x.view(B, P, -1)[:, -1, :].contiguous()
+        hn, _ = ops.rmsnorm_fwd(last, self.rms_final, cfg.eps, want_inv=False)
+        logits = self.logits[:B]
+        self._head(hn, logits)
+        D.argmax_rows(logits, out_tokens=self.tokens[:B])
+        cache.seq_len[:B] = P
+        return logits
+
+    def _head(self, hn, logits):
+        M = hn.shape[0]
+        if M <= 8:
+            D.gemv(hn, self.head_t, out_f32=logits)
+        else:
+            w = self.head_t.dequantize() if isinstance(self.head_t, D.QuantWeight) else self.head_t
+            logits.copy_(ops.matmul_nn(hn, w).float())
+
+    # ------------------------------------------------------------------ decode
+    def _decode_body(self, B: int, max_len: int):
+        cfg, cache = self.cfg, self.cache
+        H, Hkv, dh = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        seq_of = self._seq_of[:B]
+        pos = cache.seq_len[:B]
+        x = ops.embed_fwd(self.embed, self.tokens[:B])
+        for li, l in enumerate(self.layers):
+            h, _ = ops.rmsnorm_fwd(x, l["rms1"], cfg.eps, want_inv=False)
+            qkv = self._linear(h, l["wqkv"])
+            ops.rope_(qkv, H + Hkv, dh, 1, self.cos, self.sin, positions=pos)
+            D.kv_append(qkv, H, Hkv, dh, cache.pools[li], cache.block_table, cache.page, seq_of, pos)
+            a = D.decode_attention(qkv, cache.pools[li], cache.block_table, cache.page, self._len_plus1[:B], H, Hkv,
+                                   dh, max_len=max_len)
+            x = self._linear(a, l["wo"], residual=x)
+            h, _ = ops.rmsnorm_fwd(x, l["rms2"], cfg.eps, want_inv=False)
+            gu = self._linear(h, l["wgu"])
+            x = self._linear(ops.swiglu_fwd(gu), l["wd"], residual=x)
+        hn, _ = ops.rmsnorm_fwd(x, self.rms_final, cfg.eps, want_inv=False)
+        self._head(hn, self.logits[:B])
+
+    def _step_eager(self, B, max_len, greedy=True):
+        torch.add(self.cache.seq_len[:B], 1, out=self._len_plus1[:B])
+        self._decode_body(B, max_len)
+        if greedy:
+            D.argmax_rows(self.logits[:B], out_tokens=self.tokens[:B], generated=self._generated, step=0)
+        self.cache.seq_len[:B] += 1
+
+    def generate(self, prompts: torch.Tensor, max_new: int, params: SamplingParams | None = None, seed: int = 0,
+                 stop_on_zero: bool = False):
+        """Greedy (device feedback, graph replay) or sampled generation. Returns int64 [B, max_new]."""
+        params = params or SamplingParams()
+        B, P = prompts.shape
+        if B > self.max_batch or P + max_new > self.max_seq:
+            raise ValueError("request exceeds the engine's max_batch / max_seq")
+        greedy = params.temperature <= 0.0 and params.repetition_penalty <= 1.0
+        for b in range(B):
+            if self.cache.owned[b]:
+                self.cache.release(b)
+        logits = self.prefill(prompts)
+        for b in range(B):
+            self.cache.reserve(b, P + max_new)
+        self.cache.commit()
+        out = torch.zeros((B, max_new), dtype=torch.int64, device=self.dev)
+        self._seq_of = torch.arange(self.max_batch, dtype=torch.int32, device=self.dev)
+        self._len_plus1 = torch.zeros(self.max_batch, dtype=torch.int32, device=self.dev)
+        self._generated = None
+        rngs = [SamplerRng(seed + b) for b in range(B)]
+        history = [list(map(int, prompts[b].tolist())) for b in range(B)]
+        if not greedy:
+            first = [sample_row(logits[b], params, history[b], rngs[b]) for b in range(B)]
+            self.tokens[:B] = torch.tensor(first, dtype=torch.int64, device=self.dev)
+        out[:, 0] = self.tokens[:B]
+        max_len = P + max_new
+        if greedy and self.use_graph and max_new > 2:
+            self._generated = None
+            # one eager step warms every workspace, then the step is captured once and replayed
+            self._step_eager(B, max_len)
+            out[:, 1] = self.tokens[:B]
+            g = torch.cuda.CUDAGraph()
+            s = torch.cuda.Stream(device=self.dev)
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                with torch.cuda.graph(g, stream=s):
+                    self._step_eager(B, max_len)
+            torch.cuda.current_stream().wait_stream(s)
+            # capture only records; run the recorded step for positions 2 .. max_new-1
+            for i in range(2, max_new):
+                g.replay()
+                out[:, i] = self.tokens[:B]
+        else:
+            for i in range(1, max_new):
+                self._step_eager(B, max_len, greedy=greedy)
+                if not greedy:
+                    lg = self.logits[:B].cpu()
+                    for b in range(B):
+                        history[b].append(int(out[b, i - 1]))
+                    nxt = [sample_row(lg[b], params, history[b], rngs[b]) for b in range(B)]
+                    self.tokens[:B] = torch.tensor(nxt, dtype=torch.int64, device=self.dev)
+                out[:, i] = self.tokens[:B]
+        _lib.check_status(self.dev) if self.dev.type == "cuda" else None
+        return out
+
+
+def reference_generate(model: GQADecoder, prompts: torch.Tensor, max_new: int) -> torch.Tensor:
+    """Full-recompute greedy decoding through the training forward (the naive path the cached
+    decoder must agree with token for token: scirust-sciagent/tests/cuda_parity.rs:184)."""
+    toks = prompts.clone()
+    out = []
+    with torch.no_grad():
+        for _ in range(max_new):
+            logits = model(toks)
+            nxt = torch.stack([torch.tensor(D._nan_safe_argmax(r.float().cpu())) for r in logits]).to(toks.device)
+            out.append(nxt)
+            toks = torch.cat([toks, nxt[:, None]], 1)
+    return torch.stack(out, 1)

@@ -1,0 +1,202 @@
+"""Decode-time ops (csrc/decode.cu): weight-streaming GEMV for bf16 / int8 per-channel weights,
+paged-KV append, split-KV GQA flash-decode, arg-max with device feedback, per-channel
+quantisation. CPU tensors take the fp32 PyTorch statement of the same arithmetic."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+from . import gemm as _g
+
+BF = torch.bfloat16
+vp, i32, f32 = _lib.vp, _lib.i32, _lib.f32
+_lib.register("sb_gemv", [vp, i32, vp, i32, vp, vp, i32, vp, i32, vp, i32, i32, i32, i32, i32, vp, vp])
+_lib.register("sb_kv_append", [vp, i32, i32, i32, i32, vp, vp, i32, i32, vp, vp, i32, vp])
+_lib.register("sb_decode_attention", [vp, i32, vp, vp, i32, i32, vp, i32, i32, i32, i32, i32, f32, vp, vp, vp, i32,
+                                      vp])
+_lib.register("sb_argmax", [vp, i32, i32, vp, vp, vp, vp, i32, i32, vp])
+_lib.register("sb_quantize_per_channel", [vp, i32, i32, i32, vp, vp, vp])
+_lib.register("sb_dequantize", [vp, vp, i32, i32, vp, vp])
+
+_ws: dict = {}
+
+
+def _workspace(n, device):
+    key = str(device)
+    w = _ws.get(key)
+    if w is None or w.numel() < n:
+        w = torch.empty(max(n, 1 << 22), dtype=torch.float32, device=device)
+        _ws[key] = w
+    return w
+
+
+class QuantWeight:
+    """int8 weight ``q [K, N]`` with one fp32 scale per output column (x.W layout):
+    ``W ~= q * scale[None, :]`` (scirust-core/src/quantization.rs:95-125)."""
+
+    def __init__(self, q: torch.Tensor, scale: torch.Tensor):
+        self.q, self.scale = q, scale
+
+    @property
+    def shape(self):
+        return self.q.shape
+
+    def dequantize(self) -> torch.Tensor:
+        if not self.q.is_cuda:
+            return (self.q.float() * self.scale[None, :]).to(BF)
+        K, N = self.q.shape
+        w = torch.empty((K, N), dtype=BF, device=self.q.device)
+        _lib.call("sb_dequantize", self.q.data_ptr(), self.scale.data_ptr(), K, N, w.data_ptr(), _lib.stream())
+        _g.launch_count += 1
+        return w
+
+
+def quantize_per_channel(w: torch.Tensor) -> QuantWeight:
+    K, N = w.shape
+    if not w.is_cuda:
+        wf = w.float()
+        mx = wf.abs().amax(0)
+        scale = torch.where(mx == 0, torch.ones_like(mx), mx / 127.0)
+        v = wf / scale[None, :]
+        q = torch.where(v >= 0, torch.floor(v + 0.5), torch.ceil(v - 0.5)).clamp(-128, 127).to(torch.int8)
+        return QuantWeight(q, scale)
+    w = w.contiguous()
+    scale = torch.empty(N, dtype=torch.float32, device=w.device)
+    q = torch.empty((K, N), dtype=torch.int8, device=w.device)
+    _lib.call("sb_quantize_per_channel", w.data_ptr(), K, N, w.stride(0), scale.data_ptr(), q.data_ptr(),
+              _lib.stream())
+    _g.launch_count += 2
+    return QuantWeight(q, scale)
+
+
+def _auto_splits(N, K, cols):
+    ctas = (N + cols - 1) // cols
+    s = max(1, min(148 * 2 // max(ctas, 1), K // 256))
+    return s
+
+
+def gemv(x, w, residual=None, out=None, out_f32=None, splits=None):
+    """y[M,N] = x[M,K] @ W (+ residual) for small M, streaming W once. ``w`` is a bf16 ``[K, N]``
+    matrix or a ``QuantWeight``. Rows are processed in groups of 8."""
+    M, K = x.shape
+    quant = isinstance(w, QuantWeight)
+    wm = w.q if quant else w
+    N = wm.shape[1]
+    if not x.is_cuda:
+        wf = (w.q.float() if quant else w.float())
+        y = x.float() @ wf
+        if quant:
+            y = y * w.scale[None, :]
+        if residual is not None:
+            y = y + residual.float()
+        if out_f32 is not None:
+            out_f32.copy_(y)
+        if out is not None:
+            out.copy_(y.to(BF))
+            return out
+        return y.to(BF) if out_f32 is None else out_f32
+    if out is None and out_f32 is None:
+        out = torch.empty((M, N), dtype=BF, device=x.device)
+    if splits is None:
+        splits = _auto_splits(N, K, 512 if quant else 256)
+    ws = _workspace(splits * min(M, 8) * N, x.device)
+    for m0 in range(0, M, 8):
+        mb = min(8, M - m0)
+        xs = x[m0:m0 + mb]
+        _lib.call("sb_gemv", xs.data_ptr(), xs.stride(0), wm.data_ptr(), wm.stride(0),
+                  w.scale.data_ptr() if quant else None,
+                  residual[m0:m0 + mb].data_ptr() if residual is not None else None,
+                  residual.stride(0) if residual is not None else 0,
+                  out[m0:m0 + mb].data_ptr() if out is not None else None, out.stride(0) if out is not None else 0,
+                  out_f32[m0:m0 + mb].data_ptr() if out_f32 is not None else None, mb, N, K, int(quant), splits,
+                  ws.data_ptr(), _lib.stream())
+        _g.launch_count += 2
+    return out if out is not None else out_f32
+
+
+def kv_append(qkv, H, Hkv, dh, pool, block_table, page, seq_of, pos):
+    """Copy k/v heads of each row of ``qkv`` into the paged pool ``[n_blocks, 2, Hkv, page, dh]``."""
+    n = qkv.shape[0]
+    if not qkv.is_cuda:
+        for t in range(n):
+            b, p = int(seq_of[t]), int(pos[t])
+            blk = int(block_table[b, p // page])
+            kv = qkv[t, H * dh:].reshape(2, Hkv, dh)
+            pool[blk, :, :, p % page, :] = kv
+        return
+    _lib.call("sb_kv_append", qkv.data_ptr(), qkv.stride(0), H, Hkv, dh, pool.data_ptr(), block_table.data_ptr(),
+              block_table.shape[1], page, seq_of.data_ptr(), pos.data_ptr(), n, _lib.stream())
+    _g.launch_count += 1
+
+
+def decode_attention_ref(q, pool, block_table, page, seq_len, H, Hkv, dh, scale=None):
+    scale = 1.0 / math.sqrt(dh) if scale is None else scale
+    B = q.shape[0]
+    out = torch.zeros((B, H * dh), dtype=torch.float32, device=q.device)
+    G = H // Hkv
+    for b in range(B):
+        L = int(seq_len[b])
+        nb = (L + page - 1) // page
+        blocks = block_table[b, :nb].long()
+        kv = pool[blocks].float()                     # [nb, 2, Hkv, page, dh]
+        k = kv[:, 0].permute(1, 0, 2, 3).reshape(Hkv, nb * page, dh)[:, :L]
+        v = kv[:, 1].permute(1, 0, 2, 3).reshape(Hkv, nb * page, dh)[:, :L]
+        qb = q[b, :H * dh].float().reshape(Hkv, G, dh)
+        s = torch.einsum("hgd,hld->hgl", qb, k) * scale
+        o = torch.einsum("hgl,hld->hgd", torch.softmax(s, -1), v)
+        out[b] = o.reshape(-1)
+    return out
+
+
+def decode_attention(q, pool, block_table, page, seq_len, H, Hkv, dh, scale=None, n_splits=None, max_len=None):
+    """Single-query GQA attention of each sequence over its paged KV. q: [B, >= H*dh] (RoPE'd)."""
+    scale = 1.0 / math.sqrt(dh) if scale is None else scale
+    B = q.shape[0]
+    if not q.is_cuda:
+        return decode_attention_ref(q, pool, block_table, page, seq_len, H, Hkv, dh, scale).to(BF)
+    if n_splits is None:
+        L = max_len if max_len is not None else block_table.shape[1] * page
+        n_splits = max(1, min(32, (148 * 2) // max(1, B * Hkv), (L + 255) // 256))
+    ws = _workspace(B * H * n_splits * (dh + 2), q.device)
+    part_o = ws[:B * H * n_splits * dh]
+    part_ml = ws[B * H * n_splits * dh:B * H * n_splits * (dh + 2)]
+    out = torch.empty((B, H * dh), dtype=BF, device=q.device)
+    _lib.call("sb_decode_attention", q.data_ptr(), q.stride(0), pool.data_ptr(), block_table.data_ptr(),
+              block_table.shape[1], page, seq_len.data_ptr(), B, H, Hkv, dh, n_splits, float(scale),
+              part_o.data_ptr(), part_ml.data_ptr(), out.data_ptr(), out.stride(0), _lib.stream())
+    _g.launch_count += 2
+    return out
+
+
+def argmax_rows(logits_f32, out_tokens=None, generated=None, step=0):
+    """Greedy token per row (first maximum wins). Writes int64 tokens on the device."""
+    rows, V = logits_f32.shape
+    if not logits_f32.is_cuda:
+        tok = torch.tensor([int(torch.argmax(r)) if not torch.isnan(r).any() else _nan_safe_argmax(r)
+                            for r in logits_f32], dtype=torch.int64)
+        if out_tokens is not None:
+            out_tokens.copy_(tok)
+            tok = out_tokens
+        if generated is not None:
+            generated[:, step] = tok
+        return tok
+    slabs = (V + 4095) // 4096
+    pval = torch.empty(rows * slabs, dtype=torch.float32, device=logits_f32.device)
+    pidx = torch.empty(rows * slabs, dtype=torch.int32, device=logits_f32.device)
+    if out_tokens is None:
+        out_tokens = torch.empty(rows, dtype=torch.int64, device=logits_f32.device)
+    _lib.call("sb_argmax", logits_f32.data_ptr(), rows, V, pval.data_ptr(), pidx.data_ptr(), out_tokens.data_ptr(),
+              _lib.ptr(generated), generated.stride(0) if generated is not None else 0, step, _lib.stream())
+    _g.launch_count += 2
+    return out_tokens
+
+
+def _nan_safe_argmax(r):
+    best, bv = 0, float(r[0])
+    for j in range(1, r.numel()):
+        v = float(r[j])
+        if v > bv:
+            bv, best = v, j
+    return best

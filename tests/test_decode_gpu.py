@@ -1,0 +1,95 @@
+"""Decode-time kernels and the inference engine against fp32 PyTorch references."""
+import pytest
+import torch
+
+from scirust_b200.models import GQADecoder, SciAgentConfig
+from scirust_b200.models.infer import InferenceEngine, reference_generate
+from scirust_b200.ops import _lib, decode as D
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def _r(shape, seed, scale=0.5):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, generator=g, device="cuda") * scale).to(BF)
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 1024, 1536), (3, 4096, 512), (8, 2816, 1024), (13, 1024, 264)])
+def test_gemv_bf16(M, K, N):
+    x, w, r = _r((M, K), 1), _r((K, N), 2), _r((M, N), 3)
+    y = D.gemv(x, w, residual=r)
+    ref = x.float() @ w.float() + r.float()
+    assert (y.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+    assert torch.equal(y, D.gemv(x, w, residual=r))
+    f = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    D.gemv(x, w, out_f32=f)
+    assert (f - x.float() @ w.float()).abs().max().item() <= 2e-3 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 1024, 1536), (5, 4096, 512), (8, 1024, 2048)])
+def test_gemv_int8_and_quantize(M, K, N):
+    x, w = _r((M, K), 4), _r((K, N), 5)
+    qw = D.quantize_per_channel(w)
+    qc = D.quantize_per_channel(w.cpu())
+    assert torch.allclose(qw.scale.cpu(), qc.scale, rtol=1e-6)
+    assert (qw.q.cpu().int() - qc.q.int()).abs().max().item() <= 1   # bf16 half-way cases may round either way
+    y = D.gemv(x, qw)
+    ref = x.float() @ (qw.q.float() * qw.scale[None, :])
+    assert (y.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+    assert (qw.dequantize().float() - qw.q.float() * qw.scale[None, :]).abs().max().item() <= 1e-2
+
+
+@pytest.mark.parametrize("dh,H,Hkv", [(64, 16, 4), (128, 32, 8), (128, 4, 4)])
+def test_paged_decode_attention(dh, H, Hkv):
+    B, page, max_seq = 3, 16, 700
+    max_blocks = (max_seq + page - 1) // page
+    n_blocks = B * max_blocks
+    pool = torch.zeros((n_blocks, 2, Hkv, page, dh), dtype=BF, device="cuda")
+    perm = torch.randperm(n_blocks, generator=torch.Generator().manual_seed(0)).int()
+    table = perm.reshape(B, max_blocks).cuda()          # scattered physical pages
+    lens = torch.tensor([1, 257, 700], dtype=torch.int32, device="cuda")
+    ld = (H + 2 * Hkv) * dh
+    for b in range(B):
+        L = int(lens[b])
+        rows = _r((L, ld), 10 + b)
+        D.kv_append(rows, H, Hkv, dh, pool, table, page, torch.full((L,), b, dtype=torch.int32, device="cuda"),
+                    torch.arange(L, dtype=torch.int32, device="cuda"))
+    q = _r((B, ld), 20)
+    out = D.decode_attention(q, pool, table, page, lens, H, Hkv, dh, n_splits=5)
+    ref = D.decode_attention_ref(q, pool, table, page, lens, H, Hkv, dh)
+    assert (out.float() - ref).abs().max().item() < 2e-2
+    one = D.decode_attention(q, pool, table, page, lens, H, Hkv, dh, n_splits=1)
+    assert (one.float() - ref).abs().max().item() < 2e-2
+    assert torch.equal(out, D.decode_attention(q, pool, table, page, lens, H, Hkv, dh, n_splits=5))
+
+
+def test_argmax_tie_and_nan_rules():
+    V = 10000
+    lg = torch.randn(4, V, device="cuda")
+    lg[0, 77] = 50.0
+    lg[0, 9000] = 50.0          # tie -> lower id
+    lg[1, 5] = float("nan")     # NaN never beats a number
+    lg[1, 4100] = 60.0
+    lg[2] = -5.0
+    lg[2, 8191] = -4.0
+    tok = D.argmax_rows(lg)
+    assert tok.tolist()[:3] == [77, 4100, 8191]
+    assert int(tok[3]) == int(torch.argmax(lg[3]))
+
+
+@pytest.mark.parametrize("quant", [None, "int8"])
+def test_engine_cached_equals_naive_and_graph(quant):
+    cfg = SciAgentConfig(vocab_size=1024, d_model=256, n_layers=2, n_heads=4, n_kv_heads=2, d_ff=512,
+                         max_seq_len=512, rope_theta=10000.0)
+    model = GQADecoder(cfg, device="cuda", seed=5, init_std=0.08)
+    prompts = torch.randint(1, 1024, (2, 128), generator=torch.Generator().manual_seed(1)).cuda()
+    eager = InferenceEngine(model, quant=quant, max_batch=2, max_seq=256, page=16, use_graph=False)
+    graph = InferenceEngine(model, quant=quant, max_batch=2, max_seq=256, page=16, use_graph=True)
+    a = eager.generate(prompts, 8)
+    b = graph.generate(prompts, 8)
+    _lib.check_status()
+    assert torch.equal(a, b)
+    if quant is None:
+        naive = reference_generate(model, prompts, 8)
+        assert torch.equal(a, naive), (a.tolist(), naive.tolist())
