@@ -1,0 +1,4 @@
+from .tape import Tape, Var, TapeError  # noqa: F401
+from .optim import Sgd, Adam, AdamW, Optimizer  # noqa: F401
+from .scheduler import (LrSchedule, Constant, StepDecay, Exponential, CosineAnnealing, WarmupCosine,  # noqa: F401
+                        ReduceOnPlateau)

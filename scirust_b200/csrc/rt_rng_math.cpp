@@ -241,3 +241,14 @@ void sbrt_adam_step_f32(float* p, float* m, float* v, const float* g, int64_t n,
 }
 
 }  // extern "C"
+
+// Bit-portable GEMM: every product and sum in fp64 (an fp32 x fp32 product is exact in fp64),
+// k ascending, one rounding to fp32 at the end (scirust-core/src/portable_f32.rs:1033-1075).
+extern "C" void sbrt_gemm_f32_portable(const float* A, const float* B, float* C, int64_t M, int64_t K, int64_t N) {
+  for (int64_t i = 0; i < M; ++i)
+    for (int64_t j = 0; j < N; ++j) {
+      double acc = 0.0;
+      for (int64_t l = 0; l < K; ++l) acc += static_cast<double>(A[i * K + l]) * static_cast<double>(B[l * N + j]);
+      C[i * N + j] = static_cast<float>(acc);
+    }
+}

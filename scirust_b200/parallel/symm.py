@@ -66,6 +66,7 @@ class SymmetricRegion:
                 self.peer_base.append(q.value)
         self._bytes = torch.as_tensor(_Raw(self.base, total), device=self.device)
         self._cursor = 0
+        self._carved = []
         self._next_slot = 0
         dist.barrier(group=group)
 
@@ -79,7 +80,11 @@ class SymmetricRegion:
         if start + nbytes > self.data_bytes:
             raise MemoryError("symmetric region exhausted")
         self._cursor = start + nbytes
-        return self._bytes[start:start + nbytes].view(dtype).view(shape)
+        # a separate storage object per carve-out: views of one base tensor would share a version
+        # counter, and autograd would then see every in-place write to one buffer as a change of all
+        raw = torch.as_tensor(_Raw(self.base + start, nbytes), device=self.device)
+        self._carved.append(raw)
+        return raw.view(dtype).view(shape)
 
     def offset_of(self, t: torch.Tensor) -> int:
         off = t.data_ptr() - self.base
@@ -109,13 +114,18 @@ class SymmetricRegion:
         return s
 
     def close(self):
+        """Collective: every rank must call it. Peers are unmapped only after all ranks have
+        drained their streams, and the local region is freed only after all peers unmapped it."""
         lib = _lib.cuda()
         torch.cuda.synchronize()
+        dist.barrier(group=self.group)
         for r, b in enumerate(self.peer_base):
             if r != self.rank and b:
                 lib.sb_ipc_close(b)
         self.peer_base = []
+        dist.barrier(group=self.group)
         if self.base:
             self._bytes = None
+            self._carved = []
             lib.sb_free(self.base)
             self.base = 0

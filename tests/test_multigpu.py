@@ -18,6 +18,10 @@ def _run(script: str, nproc: int, port: int, timeout: int = 300):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "mp", script)]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    log_dir = os.environ.get("SB_TEST_LOG_DIR")
+    if log_dir:
+        with open(os.path.join(log_dir, script + ".log"), "w") as f:
+            f.write(r.stdout + "\n---- stderr ----\n" + r.stderr)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     return r.stdout
 
