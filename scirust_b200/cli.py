@@ -1,0 +1,333 @@
+"""``scirust``-style command line (scirust-cli/src/lib.rs:631-760; exit-code contract
+docs/CLI_CONTRACT.md:20-34: 0 ok, 1 domain failure, 2 usage / IO, 3 validation, 5 numerical,
+6 cancelled, 7 internal). Standard output is byte-deterministic for a given command line; timing
+goes to stderr and only when stderr is a terminal (lib.rs:626-651).
+
+    python -m scirust_b200.cli quickstart
+    python -m scirust_b200.cli train --model debug --steps 20 --data shards/*.bin --checkpoint-dir ckpt
+    python -m scirust_b200.cli infer --checkpoint ckpt/step_20 --prompt "fn main" --max-new 32
+    python -m scirust_b200.cli sciagent info|generate|quantize|attest ...
+    python -m scirust_b200.cli bpe train|encode|decode ...
+    python -m scirust_b200.cli verify emit|verify ...
+"""
+from __future__ import annotations
+
+import argparse
+import glob
+import hashlib
+import json
+import sys
+import time
+
+EXIT_OK, EXIT_FAIL, EXIT_USAGE, EXIT_VALIDATION, EXIT_NUMERICAL, EXIT_CANCELLED, EXIT_INTERNAL = 0, 1, 2, 3, 5, 6, 7
+
+
+class _Parser(argparse.ArgumentParser):
+    def error(self, message):
+        raise SystemExit(self._usage_exit(message))
+
+    def _usage_exit(self, message):
+        sys.stderr.write(f"error: {message}\n")
+        return EXIT_USAGE
+
+
+def _device(name):
+    import torch
+    if name == "auto":
+        return "cuda" if torch.cuda.is_available() else "cpu"
+    return name
+
+
+def cmd_version(a):
+    from . import __version__
+    print(f"scirust_b200 {__version__}")
+    return EXIT_OK
+
+
+def cmd_info(a):
+    import torch
+    from . import __version__
+    from ._build import CUDA_LIB, RT_LIB
+    print(f"scirust_b200 {__version__}")
+    print(f"torch {torch.__version__}")
+    print(f"cuda_available {torch.cuda.is_available()}")
+    if torch.cuda.is_available():
+        p = torch.cuda.get_device_properties(0)
+        print(f"device {p.name} sm_{p.major}{p.minor} {p.total_memory // (1 << 20)} MiB x{torch.cuda.device_count()}")
+    print(f"native_cuda_lib {'present' if CUDA_LIB.exists() else 'missing'}")
+    print(f"native_rt_lib {'present' if RT_LIB.exists() else 'missing'}")
+    return EXIT_OK
+
+
+def cmd_quickstart(a):
+    from .models.mlp_cpu import train_gaussian_mlp
+    model, hist = train_gaussian_mlp(epochs=a.epochs, seed=a.seed, fma=a.fma, log=print)
+    loss, acc = hist[-1]
+    print(f"final loss {loss:.6f} accuracy {acc:.4f} fingerprint {model.fingerprint():016x}")
+    if loss != loss:
+        return EXIT_NUMERICAL
+    return EXIT_OK if acc >= 0.9 else EXIT_FAIL
+
+
+def _load_tokenizer(path):
+    from .tokenizer import BpeTokenizer
+    return BpeTokenizer.load_json(path)
+
+
+def cmd_bpe(a):
+    from .tokenizer import BpeTrainer
+    if a.action == "train":
+        texts = [open(p, encoding="utf-8").read() for p in a.inputs]
+        tok = BpeTrainer(a.vocab_size, a.min_frequency).train(texts)
+        tok.save_json(a.out)
+        print(f"vocab {tok.vocab_size()} merges {len(tok.merges)} -> {a.out}")
+    elif a.action == "encode":
+        print(" ".join(str(i) for i in _load_tokenizer(a.tokenizer).encode(a.text)))
+    else:
+        print(_load_tokenizer(a.tokenizer).decode([int(t) for t in a.text.split()]))
+    return EXIT_OK
+
+
+def cmd_train(a):
+    import torch
+    from .data.datasets import TokenShardDataset
+    from .io import checkpoint as CK
+    from .models import GQADecoder, SciAgentConfig
+    from .train import Trainer, TrainerConfig
+    dev = _device(a.device)
+    cfg = SciAgentConfig.preset(a.model)
+    paths = sorted(p for pat in a.data for p in glob.glob(pat))
+    start = 0
+    if a.resume:
+        last = CK.latest_checkpoint(a.checkpoint_dir)
+        if last is None:
+            sys.stderr.write("error: --resume given but no checkpoint found\n")
+            return EXIT_USAGE
+        model, meta = CK.load_sciagent_checkpoint(last, device=dev)
+        cfg, start = model.cfg, meta["step"]
+    else:
+        model = GQADecoder(cfg, device=dev, seed=a.seed)
+    tc = TrainerConfig(lr=a.lr, min_lr=a.min_lr, warmup_steps=a.warmup_steps, total_steps=a.total_steps,
+                       max_grad_norm=a.max_grad_norm, weight_decay=a.weight_decay)
+    tr = Trainer(model, tc)
+    if a.resume:
+        CK.load_optimizer_state(model, tr, last)
+    if paths:
+        ds = TokenShardDataset(paths, a.seq_len, cfg.vocab_size, val_frac=a.val_frac, seed=a.seed)
+        get = lambda s: ds.batch(s, a.batch_size)  # noqa: E731
+    else:
+        def get(s):
+            g = torch.Generator().manual_seed(a.seed * 1000003 + s)
+            return torch.randint(0, cfg.vocab_size, (a.batch_size, a.seq_len + 1), generator=g)
+    t0 = time.time()
+    loss = float("nan")
+    for step in range(start, a.steps):
+        loss = float(tr.train_step(get(step)).item())
+        if loss != loss:
+            sys.stderr.write(f"error: loss is NaN at step {step}\n")
+            return EXIT_NUMERICAL
+        if (step + 1) % a.log_interval == 0 or step + 1 == a.steps:
+            print(f"[step {step + 1}] {a.batch_size}x{a.seq_len} loss {loss:.4f} | lr {tr.schedule.lr_at(step):.3e} | "
+                  f"gnorm {tr.grad_norm():.3f}")
+        if a.checkpoint_dir and a.save_interval and (step + 1) % a.save_interval == 0:
+            CK.save_sciagent_checkpoint(model, f"{a.checkpoint_dir}/step_{step + 1}", step + 1, loss,
+                                        tr.schedule.lr_at(step), trainer=tr)
+            if a.keep_last:
+                CK.prune_checkpoints(a.checkpoint_dir, a.keep_last)
+    if a.checkpoint_dir:
+        CK.save_sciagent_checkpoint(model, f"{a.checkpoint_dir}/step_{a.steps}", a.steps, loss,
+                                    tr.schedule.lr_at(max(a.steps - 1, 0)), trainer=tr)
+    if sys.stderr.isatty():
+        dt = time.time() - t0
+        sys.stderr.write(f"{(a.steps - start) * a.batch_size * a.seq_len / max(dt, 1e-9):.0f} tok/s\n")
+    return EXIT_OK
+
+
+def cmd_infer(a):
+    import torch
+    from .generate import SamplingParams
+    from .io import checkpoint as CK
+    from .models.infer import InferenceEngine
+    dev = _device(a.device)
+    model, meta = CK.load_sciagent_checkpoint(a.checkpoint, device=dev)
+    if a.tokenizer:
+        tok = _load_tokenizer(a.tokenizer)
+        ids = tok.encode(a.prompt)
+    else:
+        tok, ids = None, [int(t) for t in a.prompt.split()]
+    if not ids:
+        sys.stderr.write("error: empty prompt\n")
+        return EXIT_VALIDATION
+    eng = InferenceEngine(model, quant=a.quant, max_batch=1, max_seq=len(ids) + a.max_new + 1)
+    params = SamplingParams(a.temperature, a.top_k, a.top_p, a.repetition_penalty)
+    out = eng.generate(torch.tensor([ids]), a.max_new, params, seed=a.seed)[0].tolist()
+    if 0 in out:
+        out = out[:out.index(0)]      # token 0 stops generation
+    print(tok.decode(out) if tok else " ".join(str(t) for t in out))
+    return EXIT_OK
+
+
+def cmd_sciagent(a):
+    from .io import checkpoint as CK
+    if a.action == "info":
+        meta = CK.read_meta(a.checkpoint)
+        print(json.dumps({"step": meta["step"], "loss": meta["loss"], "lr": meta["lr"], "config": meta["config"].to_dict()},
+                         indent=2, sort_keys=True))
+        return EXIT_OK
+    if a.action == "generate":
+        return cmd_infer(a)
+    if a.action == "quantize":
+        import torch
+        from . import quantization as Q
+        model, _ = CK.load_sciagent_checkpoint(a.checkpoint)
+        sd = model.reference_state_dict()
+        blob, index, off = [], {}, 0
+        for k in sorted(sd):
+            packed, scale, shape, pad = Q.int4_group_quantize(sd[k], a.group)
+            raw = packed.numpy().tobytes() + scale.numpy().astype("<f4").tobytes()
+            index[k] = {"shape": list(shape), "pad": pad, "offset": off, "codes": packed.numel(), "groups": scale.numel()}
+            blob.append(raw)
+            off += len(raw)
+        hdr = json.dumps({"format": "SCIAGENT-INT4-1", "group": a.group, "tensors": index}).encode()
+        with open(a.out, "wb") as f:
+            f.write(len(hdr).to_bytes(8, "little") + hdr + b"".join(blob))
+        print(f"wrote {a.out}: {off + len(hdr) + 8} bytes ({sum(v.numel() for v in sd.values()) * 4} fp32 bytes)")
+        return EXIT_OK
+    if a.action == "attest":
+        from pathlib import Path
+        mb = (Path(a.checkpoint) / "model.safetensors").read_bytes()
+        rec = {"model_sha256": hashlib.sha256(mb).hexdigest(), "model_bytes": len(mb),
+               "kernel_semantics_version": CK.MODEL_SEMANTICS_VERSION}
+        if a.tokenizer:
+            rec["tokenizer_sha256"] = hashlib.sha256(Path(a.tokenizer).read_bytes()).hexdigest()
+        print(json.dumps(rec, indent=2, sort_keys=True))
+        return EXIT_OK
+    return EXIT_USAGE
+
+
+def cmd_verify(a):
+    from pathlib import Path
+    from .io import proof
+    art = Path(a.artifact).read_bytes()
+    if a.action == "emit":
+        try:
+            text = proof.build_bundle(art, a.batch, a.seeds)
+        except ValueError as e:
+            sys.stderr.write(f"error: {e}\n")
+            return EXIT_VALIDATION
+        if a.out:
+            Path(a.out).write_text(text)
+        else:
+            sys.stdout.write(text)
+        return EXIT_OK
+    errs = proof.verify_bundle(Path(a.bundle).read_text(), art)
+    for e in errs:
+        print(f"MISMATCH {e}")
+    print("VERIFIED" if not errs else f"FAILED ({len(errs)} mismatches)")
+    return EXIT_OK if not errs else EXIT_FAIL
+
+
+def build_parser():
+    p = _Parser(prog="scirust", description="scirust_b200 command line")
+    sub = p.add_subparsers(dest="cmd")
+    sub.add_parser("version").set_defaults(fn=cmd_version)
+    sub.add_parser("info").set_defaults(fn=cmd_info)
+    q = sub.add_parser("quickstart")
+    q.add_argument("--epochs", type=int, default=100)
+    q.add_argument("--seed", type=int, default=42)
+    q.add_argument("--fma", action="store_true")
+    q.set_defaults(fn=cmd_quickstart)
+    b = sub.add_parser("bpe")
+    b.add_argument("action", choices=["train", "encode", "decode"])
+    b.add_argument("--inputs", nargs="*", default=[])
+    b.add_argument("--vocab-size", type=int, default=8192)
+    b.add_argument("--min-frequency", type=int, default=2)
+    b.add_argument("--out", default="bpe.json")
+    b.add_argument("--tokenizer", default="bpe.json")
+    b.add_argument("--text", default="")
+    b.set_defaults(fn=cmd_bpe)
+    t = sub.add_parser("train")
+    t.add_argument("--model", default="debug")
+    t.add_argument("--data", nargs="*", default=[])
+    t.add_argument("--steps", type=int, default=10)
+    t.add_argument("--batch-size", type=int, default=2)
+    t.add_argument("--seq-len", type=int, default=128)
+    t.add_argument("--lr", type=float, default=3e-4)
+    t.add_argument("--min-lr", type=float, default=3e-5)
+    t.add_argument("--warmup-steps", type=int, default=0)
+    t.add_argument("--total-steps", type=int, default=0)
+    t.add_argument("--max-grad-norm", type=float, default=1.0)
+    t.add_argument("--weight-decay", type=float, default=0.1)
+    t.add_argument("--val-frac", type=float, default=0.0)
+    t.add_argument("--seed", type=int, default=0)
+    t.add_argument("--checkpoint-dir", default="")
+    t.add_argument("--save-interval", type=int, default=0)
+    t.add_argument("--keep-last", type=int, default=0)
+    t.add_argument("--log-interval", type=int, default=10)
+    t.add_argument("--resume", action="store_true")
+    t.add_argument("--device", default="auto")
+    t.set_defaults(fn=cmd_train)
+
+    def gen_args(sp):
+        sp.add_argument("--checkpoint", required=True)
+        sp.add_argument("--tokenizer", default="")
+        sp.add_argument("--prompt", default="")
+        sp.add_argument("--max-new", type=int, default=32)
+        sp.add_argument("--temperature", type=float, default=0.0)
+        sp.add_argument("--top-k", type=int, default=0)
+        sp.add_argument("--top-p", type=float, default=1.0)
+        sp.add_argument("--repetition-penalty", type=float, default=1.0)
+        sp.add_argument("--seed", type=int, default=0)
+        sp.add_argument("--quant", default=None, choices=[None, "int8"])
+        sp.add_argument("--device", default="auto")
+    i = sub.add_parser("infer")
+    gen_args(i)
+    i.set_defaults(fn=cmd_infer)
+    s = sub.add_parser("sciagent")
+    s.add_argument("action", choices=["info", "generate", "quantize", "attest"])
+    gen_args(s)
+    s.add_argument("--out", default="model.int4.bin")
+    s.add_argument("--group", type=int, default=32)
+    s.set_defaults(fn=cmd_sciagent)
+    v = sub.add_parser("verify")
+    v.add_argument("action", choices=["emit", "verify"])
+    v.add_argument("--artifact", required=True)
+    v.add_argument("--bundle", default="")
+    v.add_argument("--batch", type=int, default=1)
+    v.add_argument("--seeds", type=int, nargs="*", default=[1, 2, 3])
+    v.add_argument("--out", default="")
+    v.set_defaults(fn=cmd_verify)
+    return p
+
+
+def run(argv) -> int:
+    """Entry point returning the exit code (never raises for user errors)."""
+    p = build_parser()
+    try:
+        a = p.parse_args(list(argv))
+    except SystemExit as e:
+        return int(e.code) if isinstance(e.code, int) else EXIT_USAGE
+    if not getattr(a, "fn", None):
+        p.print_help()
+        return EXIT_OK
+    try:
+        return int(a.fn(a))
+    except KeyboardInterrupt:
+        return EXIT_CANCELLED
+    except (FileNotFoundError, PermissionError, IsADirectoryError) as e:
+        sys.stderr.write(f"error: {e}\n")
+        return EXIT_USAGE
+    except (ValueError, KeyError) as e:
+        sys.stderr.write(f"error: {e}\n")
+        return EXIT_VALIDATION
+    except Exception as e:  # noqa: BLE001
+        sys.stderr.write(f"internal error: {type(e).__name__}: {e}\n")
+        return EXIT_INTERNAL
+
+
+def main():
+    sys.exit(run(sys.argv[1:]))
+
+
+if __name__ == "__main__":
+    main()

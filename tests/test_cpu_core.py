@@ -1,0 +1,313 @@
+"""CPU tests: RNG streams, formats, tape/optimizers, numerics, quantisation, tokenizer, caches,
+data, deterministic MLP, CLI exit codes."""
+import json
+import math
+import os
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+from scirust_b200 import nn, quantization as Q
+from scirust_b200.autodiff import Adam, AdamW, Sgd, Tape, WarmupCosine
+from scirust_b200.io import artifacts as A
+from scirust_b200.io import checkpoint as CK
+from scirust_b200.io import proof, safetensors as ST
+from scirust_b200.nn.rng import PcgEngine, Philox4x32
+from scirust_b200.numerics import lowprec as L
+from scirust_b200.numerics import portable as P
+from scirust_b200.numerics import reproducible as R
+
+REF = "/root/reference"
+need_ref = pytest.mark.skipif(not os.path.isdir(REF), reason="reference tree not mounted")
+
+
+# ------------------------------------------------------------------ RNG
+def test_pcg_is_deterministic_and_in_range():
+    a, b = PcgEngine(42), PcgEngine(42)
+    assert [a.next_u32() for _ in range(100)] == [b.next_u32() for _ in range(100)]
+    assert PcgEngine(1).next_u32() != PcgEngine(2).next_u32()
+    f = PcgEngine(7).fill_float((1000,))
+    assert 0.0 <= float(f.min()) and float(f.max()) < 1.0
+    n = PcgEngine(3).fill_normal((20000,), 1.0, 2.0)
+    assert abs(float(n.mean()) - 1.0) < 0.05 and abs(float(n.std()) - 2.0) < 0.05
+
+
+def test_philox_known_answers_and_fingerprint():
+    z = Philox4x32(0)
+    assert z.block([0, 0, 0, 0]).tolist() == [0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8]
+    f = Philox4x32(0xFFFFFFFFFFFFFFFF)
+    assert f.block([0xFFFFFFFF] * 4).tolist() == [0x408F276D, 0x41C83B0E, 0xA20BC7C6, 0x6D5451FD]
+    p = Philox4x32((0x299F31D0 << 32) | 0xA4093822)
+    assert p.block([0x243F6A88, 0x85A308D3, 0x13198A2E, 0x03707344]).tolist() == [0xD16CFE09, 0x94FDCCEB, 0x5001E420,
+                                                                                  0x24126EA1]
+    rng = Philox4x32(20260710)
+    fp = 0xCBF29CE484222325
+    for i in range(4096):
+        fp = ((fp ^ rng.u32_at(0, i)) * 0x100000001B3) & 0xFFFFFFFFFFFFFFFF
+    assert fp == 0xF96C6B6AECA699F5
+
+
+# ------------------------------------------------------------------ formats
+def test_safetensors_layout_and_errors():
+    t = {"b": torch.arange(6.0).reshape(2, 3), "a": torch.ones(1, 2)}
+    raw = ST.serialize([("b", t["b"]), ("a", t["a"])])
+    (hlen,) = struct.unpack("<Q", raw[:8])
+    assert raw[8:8 + hlen].decode() == ('{"b":{"dtype":"F32","shape":[2,3],"data_offsets":[0,24]},'
+                                        '"a":{"dtype":"F32","shape":[1,2],"data_offsets":[24,32]}}')
+    back = ST.deserialize(raw)
+    assert torch.equal(back["b"], t["b"]) and torch.equal(back["a"], t["a"])
+    for bad in (b"", raw[:20], struct.pack("<Q", 1 << 40) + b"{}", struct.pack("<Q", 2) + b"[]"):
+        with pytest.raises(ValueError):
+            ST.deserialize(bad)
+
+
+@need_ref
+def test_safetensors_roundtrip_of_shipped_checkpoint_is_byte_identical():
+    raw = open(f"{REF}/scirust-sciagent/checkpoints/small-20M/final/model.safetensors", "rb").read()
+    sd = ST.deserialize(raw)
+    assert len(sd) == 38 and tuple(sd["sciagent.embed.weight"].shape) == (8192, 128)
+    assert ST.serialize([(k, sd[k]) for k in ST.header_order(raw)]) == raw
+
+
+def test_srt1_manifest_qsr1_proof():
+    sd = {"1.weight": torch.randn(3, 2), "0.bias": torch.randn(1, 3)}
+    raw = A.srt1_to_bytes(sd)
+    assert raw[:4] == b"SRT1" and raw[8:12] == struct.pack("<I", 6)  # keys sorted: "0.bias" first
+    back = A.srt1_from_bytes(raw)
+    assert all(torch.equal(back[k], sd[k]) for k in sd)
+    with pytest.raises(ValueError):
+        A.srt1_from_bytes(raw[:-3])
+    specs = [A.LayerSpec("conv2d", (1, 8, 3, 1, True, 28, 28)), A.LayerSpec("relu"), A.LayerSpec("maxpool2d", (2, 2, 8, 28, 28)),
+             A.LayerSpec("linear", (1568, 10)), A.LayerSpec("layernorm", (10, 1e-5))]
+    text = A.write_manifest(specs)
+    assert text.splitlines()[0] == "conv2d 1 8 3 1 same 28 28" and text.splitlines()[-1] == "layernorm 10 0.00001"
+    assert A.parse_manifest("# c\n\n" + text) == specs
+    with pytest.raises(ValueError):
+        A.parse_manifest("linear 3")
+    m = A.QModel([A.QLinear(3, 2, 0.01, True, np.array([0.002, 0.003], np.float32), np.array([1, -2, 3, 4, -5, 6], np.int8),
+                            np.array([10, -20], np.int32)),
+                  A.QLinear(2, 2, 0.05, False, np.array([0.01, 0.02], np.float32), np.array([1, 2, -3, 4], np.int8),
+                            np.array([0, 5], np.int32))])
+    b = m.to_bytes()
+    m2 = A.QModel.from_bytes(b)
+    assert m2.to_bytes() == b
+    x = [0.5, -0.25, 0.125]
+    assert np.array_equal(m.infer(x, 1), m2.infer(x, 1))
+    for cut in (3, 9, 20, len(b) - 1):
+        with pytest.raises(ValueError):
+            A.QModel.from_bytes(b[:cut])
+    bundle = proof.build_bundle(b, 2, [1, 2])
+    assert proof.verify_bundle(bundle, b) == []
+    tampered = bytearray(b)
+    tampered[-1] ^= 1
+    assert proof.verify_bundle(bundle, bytes(tampered))
+    cert = proof.resource_certificate(m, 2)
+    assert cert["mac_count"] == 2 * (3 * 2 + 2 * 2)
+
+
+def test_quantize_multiplier_and_requant():
+    m, s = A.quantize_multiplier(0.3)
+    assert 2 ** 30 <= m < 2 ** 31 and abs(m / 2 ** 31 / 2 ** s - 0.3) < 1e-9
+    assert A.quantize_multiplier(0.0) == (0, 0)
+    assert int(A.requant_i32(np.array([1000], dtype=np.int64), m, s)[0]) == 300
+    assert A.quantize_tensor(np.array([0.5, -0.5, 1.5, 2.5, 500.0], np.float32), 1.0).tolist() == [1, -1, 2, 3, 127]
+
+
+def test_core_checkpoint_json(tmp_path):
+    CK.save_checkpoint(tmp_path / "e3", {"w": torch.ones(2, 2)}, {"learning_rate": 0.1, "m": {"w": torch.zeros(4)}}, 3, 30)
+    CK.save_checkpoint(tmp_path / "e1", {"w": torch.ones(2, 2)}, {}, 1, 10)
+    ck = CK.load_checkpoint(tmp_path / "e3")
+    assert ck["weights"]["w"] == [1.0] * 4 and ck["optimizer_state"]["learning_rate"] == pytest.approx(0.1)
+    assert [e for e, _ in CK.list_checkpoints(tmp_path)] == [1, 3]
+
+
+# ------------------------------------------------------------------ tape and optimizers
+def test_tape_gradients_match_finite_differences():
+    torch.manual_seed(0)
+    x0, w0 = torch.randn(5, 4), torch.randn(4, 3)
+
+    def f(w):
+        t = Tape()
+        x, wv = t.constant(x0), t.input(w)
+        y = x.matmul(wv).tanh().softmax().log().sum_axis(1).mean()
+        return t, wv, y
+    t, wv, y = f(w0)
+    t.backward(y)
+    g = t.grad(wv.idx).t
+    num = torch.zeros_like(w0)
+    for i in range(4):
+        for j in range(3):
+            d = torch.zeros_like(w0)
+            d[i, j] = 1e-3
+            num[i, j] = (f(w0 + d)[2].item() - f(w0 - d)[2].item()) / 2e-3
+    assert torch.allclose(g, num, atol=2e-3)
+    with pytest.raises(Exception):
+        Tape().input(torch.ones(1, 1)).add(wv)
+
+
+def test_optimizer_formulas():
+    for opt, expect in ((Sgd(0.1).with_momentum(0.9), None), (Adam(0.01), None), (AdamW(0.01, weight_decay=0.1), None)):
+        t = Tape()
+        w = t.input(torch.tensor([[1.0, -2.0]]))
+        t.backward(w.mul(w).sum())
+        p0 = w.t.detach().clone()
+        opt.step([w.idx], t)
+        g = 2 * p0
+        if isinstance(opt, Sgd):
+            ref = p0 - 0.1 * g
+        else:
+            m, v = 0.1 * g, 0.001 * g * g
+            upd = 0.01 * (m / 0.1) / (torch.sqrt(v / 0.001) + 1e-8)
+            ref = p0 - upd - (0.01 * 0.1 * p0 if isinstance(opt, AdamW) else 0)
+        assert torch.allclose(w.t.detach(), ref, atol=1e-6)
+    s = WarmupCosine(1.0, 0.1, 10, 110)
+    assert s.lr_at(0) == 0 and s.lr_at(10) == pytest.approx(1.0) and s.lr_at(110) == 0.1 and s.lr_at(60) == pytest.approx(0.55)
+
+
+# ------------------------------------------------------------------ numerics
+def test_reproducible_sum_is_order_independent_and_correctly_rounded():
+    xs = (np.random.RandomState(0).randn(500) * 10.0 ** np.random.RandomState(1).randint(-6, 7, 500)).astype(np.float32)
+    a = R.reproducible_sum(xs)
+    assert a == R.reproducible_sum(xs[::-1]) == R.reproducible_sum(np.random.RandomState(2).permutation(xs))
+    assert a == float(np.float32(math.fsum(float(v) for v in xs)))
+    acc1, acc2 = R.ExactAccumulator().add_all(xs[:200]), R.ExactAccumulator().add_all(xs[200:])
+    acc1.merge(R.ExactAccumulator.from_bytes(acc2.to_bytes()))
+    assert acc1.round_f32() == a
+
+
+def test_portable_functions():
+    import decimal
+    for x in (0.0, 1.0, -3.5, 10.25, 88.0, -100.0):
+        want = float(np.float32(float(decimal.Context(prec=50).exp(decimal.Decimal(x)))))
+        assert float(P.exp_f32(x)) == want
+    assert float(P.ln_f32(1.0)) == 0.0 and np.isnan(P.ln_f32(-1.0)) and P.exp_f32(200.0) == np.inf
+    sm = P.softmax_f32([1.0, 2.0, 3.0])
+    assert abs(float(sm.sum()) - 1.0) < 1e-6
+    a, b = torch.randn(6, 9), torch.randn(9, 4)
+    assert torch.equal(P.gemm_f32(a, b), (a.double() @ b.double()).float()) or torch.allclose(P.gemm_f32(a, b), a @ b, atol=1e-5)
+
+
+def test_lowprec():
+    assert L.to_bf16([1.00390625])[0] == 1.0 and L.to_bf16([1.01171875])[0] == np.float32(1.015625)
+    sr = L.stochastic_round_bf16(np.full(2000, 1.00390625, np.float32), seed=5)
+    frac = float((sr > 1.0).mean())
+    assert 0.4 < frac < 0.6
+    assert np.array_equal(sr[:100], L.stochastic_round_bf16(np.full(100, 1.00390625, np.float32), seed=5))
+    sc = L.DynamicLossScaler(init_scale=8.0, growth_interval=2)
+    assert not sc.update(True) and sc.scale == 4.0
+    assert sc.update(False) and sc.update(False) and sc.scale == 8.0
+
+
+# ------------------------------------------------------------------ quantisation
+def test_quantization_core_vectors():
+    q, s = Q.quantize_per_channel([1.0, -2.0, 0.5, 4.0, 1.0, -0.25], 2, 3)
+    assert np.allclose(s, [4 / 127, 2 / 127, 0.5 / 127]) and q.tolist() == [32, -127, 127, 127, 64, -64]
+    assert Q.matmul_int8([1, 2, 3, 4, 5, 6], [7, 8, 9, 10, 11, 12], 2, 3, 2).tolist() == [58, 64, 139, 154]
+    assert Q.quantize_tensor([500.0, -500.0, 0.0], Q.compute_scale([500.0, -500.0, 0.0])).tolist() == [127, -127, 0]
+    x = np.random.RandomState(0).randn(4, 8).astype(np.float32)
+    w = np.random.RandomState(1).randn(8, 5).astype(np.float32)
+    wq, ws = Q.quantize_per_channel(w, 8, 5)
+    y = Q.quantized_linear_forward(x, 4, 8, wq, ws, np.zeros(5, np.float32), 5).reshape(4, 5)
+    assert np.abs(y - x @ w).max() < 0.15
+    with pytest.raises(ValueError):
+        Q.quantized_linear_forward(x, 4, 8, wq[:-1], ws, np.zeros(5), 5)
+
+
+def test_quantization_methods():
+    torch.manual_seed(0)
+    W, X = torch.randn(32, 16), torch.randn(128, 32)
+    rtn = Q._rtn(W, 4, W.abs().amax(0) / 7)
+    assert ((X @ Q.gptq_quantize(W, X)) - X @ W).pow(2).mean() < ((X @ rtn) - X @ W).pow(2).mean()
+    wq, s = Q.awq_quantize(W, X)
+    assert ((X @ wq) - X @ W).pow(2).mean() <= ((X @ rtn) - X @ W).pow(2).mean() * 1.05
+    codes, scale = Q.ternary_quantize(W)
+    assert set(codes.unique().tolist()) <= {-1, 0, 1}
+    assert (Q.nf4_dequantize(*Q.nf4_quantize(W)) - W).abs().max() < 0.6
+    assert (Q.int4_group_dequantize(*Q.int4_group_quantize(W)) - W).abs().max() < 0.35
+    xs, wsm, sm = Q.smoothquant_apply(X, W)
+    assert torch.allclose(xs @ wsm, X @ W, atol=1e-4)
+
+
+# ------------------------------------------------------------------ tokenizer, caches, data
+def test_bpe_train_encode_decode(tmp_path):
+    from scirust_b200.tokenizer import BpeTokenizer, BpeTrainer
+    text = "fn alpha<T>() { alpha::<T>(); } // café — ✅\n" * 40
+    tok = BpeTrainer(400).train([text])
+    tok2 = BpeTrainer(400).train([text])
+    assert tok.merges == tok2.merges
+    for src in ["Vec<T>", "fn main() {}", "a < b && b << 2", "", "rms → √(mean(x²)+eps) · wᵀ ✅ é"]:
+        assert tok.decode(tok.encode(src)) == src
+    tok.save_json(tmp_path / "t.json")
+    back = BpeTokenizer.load_json(tmp_path / "t.json")
+    assert back.encode("fn alpha") == tok.encode("fn alpha")
+    assert tok.encode_with_special("x", True, True)[0] == 1 and tok.encode_with_special("x", True, True)[-1] == 2
+    with pytest.raises(ValueError):
+        BpeTokenizer.from_json_str("{}")
+
+
+def test_kv_caches_against_plain():
+    from scirust_b200.nn.kv_cache import (ElasticKvCache, LatentKvCache, PagedKvCache, PlainKvCache, QuantKvCache,
+                                          TieredKvCache)
+    torch.manual_seed(0)
+    d = 16
+    caches = {"plain": PlainKvCache(d), "paged": PagedKvCache(d, 4, 16), "q8": QuantKvCache(d, 8),
+              "elastic": ElasticKvCache(d, window=8), "latent": LatentKvCache(d, d, residual_bits=0),
+              "tiered": TieredKvCache(d, d, hot=4, warm=8)}
+    for _ in range(37):
+        k, v = torch.randn(d), torch.randn(d)
+        for c in caches.values():
+            c.append(k, v)
+    q = torch.randn(d)
+    ref = caches["plain"].decode_step(q)
+    assert torch.equal(caches["paged"].decode_step(q), ref)      # paged == contiguous, bit for bit
+    assert (caches["q8"].decode_step(q) - ref).abs().max() < 0.05
+    assert (caches["elastic"].decode_step(q) - ref).abs().max() < 0.5
+    assert (caches["latent"].decode_step(q) - ref).abs().max() < 1e-4   # full-rank basis is lossless
+    assert (caches["tiered"].decode_step(q) - ref).abs().max() < 0.05
+    small = ElasticKvCache(d, window=4, budget_bytes=4 * d * 8 + 10 * (d // 2 + 4) * 2)
+    for _ in range(64):
+        small.append(torch.randn(d), torch.randn(d))
+        small.decode_step(q)
+    assert small.evicted > 0 and small.nbytes() <= small.budget
+    caches["paged"].release()
+    assert len(caches["paged"].free) == 16
+
+
+def test_data_loading_is_a_function_of_seed_and_epoch(tmp_path):
+    from scirust_b200.data import DataLoader, TokenShardDataset, gaussian_clusters, write_token_shard
+    ds = gaussian_clusters()
+    a, b = DataLoader(ds, 16, seed=3), DataLoader(ds, 16, seed=3)
+    assert torch.equal(a.order(5), b.order(5)) and not torch.equal(a.order(5), a.order(6))
+    assert sum(x.shape[0] for x, _ in a) == 150 and a.epoch == 1
+    write_token_shard(tmp_path / "s.bin", np.arange(5000) % 300)
+    ts = TokenShardDataset([tmp_path / "s.bin"], 32, vocab_size=256, val_frac=0.1, seed=1)
+    assert int(ts.tokens.max()) < 256 and (ts.tokens == 3).any()      # ids >= vocab map to <unk>
+    assert len(ts.val_windows) > 0 and len(ts.train_windows) + len(ts.val_windows) == (5000 - 1) // 32
+    b1 = ts.batch(7, 4)
+    assert b1.shape == (4, 33) and torch.equal(b1, TokenShardDataset([tmp_path / "s.bin"], 32, 256, 0.1, 1).batch(7, 4))
+
+
+def test_deterministic_mlp_is_bit_reproducible():
+    from scirust_b200.models.mlp_cpu import train_gaussian_mlp
+    m1, h1 = train_gaussian_mlp(epochs=30)
+    m2, h2 = train_gaussian_mlp(epochs=30)
+    assert m1.fingerprint() == m2.fingerprint() and h1 == h2
+    assert h1[-1][1] >= 0.95 and h1[-1][0] < h1[0][0]
+    m3, _ = train_gaussian_mlp(epochs=30, fma=True)
+    assert m3.fingerprint() != m1.fingerprint()       # fused multiply-add is a different rounding order
+
+
+def test_cli_exit_codes(tmp_path, capsys):
+    from scirust_b200 import cli
+    assert cli.run(["version"]) == 0
+    assert cli.run(["nonsense"]) == 2
+    assert cli.run(["sciagent", "info", "--checkpoint", str(tmp_path / "missing")]) == 3
+    assert cli.run(["train", "--model", "debug", "--steps", "2", "--checkpoint-dir", str(tmp_path / "ck")]) == 0
+    assert (tmp_path / "ck" / "step_2" / "meta.json").exists()
+    assert not list((tmp_path / "ck").glob(".*partial"))
+    assert cli.run(["infer", "--checkpoint", str(tmp_path / "ck" / "step_2"), "--prompt", "5 6 7", "--max-new", "4"]) == 0
+    out1 = capsys.readouterr().out
+    assert cli.run(["infer", "--checkpoint", str(tmp_path / "ck" / "step_2"), "--prompt", "5 6 7", "--max-new", "4"]) == 0
+    assert capsys.readouterr().out.splitlines()[-1] == out1.splitlines()[-1]
