@@ -1,0 +1,176 @@
+"""Host-side collectives (threads and TCP as ranks), data-parallel determinism, logical sharding,
+gloo process groups; failures are injected on the host."""
+import os
+import socket
+import subprocess
+import sys
+import threading
+
+import numpy as np
+import pytest
+import torch
+
+from scirust_b200.nn.rng import Philox4x32
+from scirust_b200.parallel import host_collectives as HC
+from scirust_b200.parallel.mesh import DeviceMesh, PartitionSpec, ShardingError, plan_sharding, shard_map
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _inputs(world, n, seed=7):
+    return [Philox4x32(seed).fill_f32(r, 0, n) * np.float32(10 ** (r % 5 - 2)) for r in range(world)]
+
+
+def test_thread_allreduce_is_rank_ordered_mean():
+    xs = _inputs(4, 257)
+
+    def fn(ctx):
+        out = ctx.all_reduce("g", xs[ctx.rank])
+        b = ctx.broadcast("w", xs[0] if ctx.rank == 0 else None)
+        ctx.barrier()
+        return out, b
+    res = HC.run_ranks(4, fn)
+    acc = np.zeros(257, np.float32)
+    for x in xs:
+        acc = (acc + x).astype(np.float32)
+    want = (acc * np.float32(0.25)).astype(np.float32)
+    for out, b in res:
+        assert np.array_equal(out, want) and np.array_equal(b, xs[0])
+
+
+def test_thread_allreduce_mismatch_is_an_error_on_every_rank():
+    def fn(ctx):
+        return ctx.all_reduce("g", np.zeros(3 if ctx.rank else 4, np.float32))
+    with pytest.raises(HC.CollectiveError):
+        HC.run_ranks(3, fn)
+
+    def fn2(ctx):
+        return ctx.all_reduce_dict({"a": np.zeros(2), ("b" if ctx.rank else "c"): np.zeros(2)})
+    with pytest.raises(HC.CollectiveError):
+        HC.run_ranks(2, fn2)
+
+
+@pytest.mark.parametrize("world", [1, 2, 5, 8])
+def test_tree_allreduce_jitter_never_changes_bits(world):
+    xs = _inputs(world, 129)
+    base = HC.tree_all_reduce(xs)
+    for seed in (1, 2, 3):
+        again = HC.tree_all_reduce(xs, jitter_seed=seed)
+        assert all(np.array_equal(a, base[0]) for a in again)
+    exact = HC.tree_all_reduce(xs, combine=HC.ExactSum, jitter_seed=4)
+    import math
+    want = np.array([np.float32(math.fsum(float(x[i]) for x in xs)) for i in range(129)], np.float32)
+    assert np.array_equal(exact[0], want)        # topology-independent, correctly rounded
+
+
+def _free_ports(n):
+    socks = [socket.socket() for _ in range(n)]
+    for s in socks:
+        s.bind(("127.0.0.1", 0))
+    ports = [s.getsockname()[1] for s in socks]
+    for s in socks:
+        s.close()
+    return ports
+
+
+def test_tcp_tree_allreduce_matches_in_process_engine():
+    world = 5
+    xs = _inputs(world, 64)
+    addrs = [("127.0.0.1", p) for p in _free_ports(world)]
+    out, errs = [None] * world, []
+
+    def work(r):
+        try:
+            out[r] = HC.tcp_tree_all_reduce_rank(r, world, addrs, xs[r], timeout=20)
+        except Exception as e:  # noqa: BLE001
+            errs.append(e)
+    ts = [threading.Thread(target=work, args=(r,)) for r in range(world)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    assert not errs, errs
+    ref = HC.tree_all_reduce(xs)[0]
+    assert all(np.array_equal(o, ref) for o in out)
+
+
+def test_tcp_frames_reject_unexpected_rank_and_oversize():
+    a, b = socket.socketpair()
+    HC.send_frame(a, 9, b"abc")
+    with pytest.raises(HC.CollectiveError):
+        HC.recv_frame(b, {1, 2})
+    a.sendall((1).to_bytes(4, "little") + (HC.MAX_FRAME + 1).to_bytes(8, "little"))
+    with pytest.raises(HC.CollectiveError):
+        HC.recv_frame(b, {1})
+    a.close()
+    with pytest.raises(HC.CollectiveError):
+        HC.recv_frame(b, {1})                      # peer went away mid-frame
+    b.close()
+
+
+def test_tcp_rank_that_never_joins_times_out_cleanly():
+    addrs = [("127.0.0.1", p) for p in _free_ports(3)]
+    with pytest.raises((HC.CollectiveError, OSError)):
+        HC.tcp_tree_all_reduce_rank(0, 3, addrs, np.ones(4, np.float32), timeout=0.5)   # children never connect
+
+
+def test_data_parallel_update_is_identical_for_any_worker_count_and_threading():
+    rs = np.random.RandomState(0)
+    x, y = rs.randn(64, 6).astype(np.float32), rs.randn(64, 1).astype(np.float32)
+
+    def grad_fn(params, xb, yb):
+        w = params[0]
+        err = xb @ w - yb
+        return float((err ** 2).mean()), [(2.0 / len(xb)) * (xb.T @ err)]
+
+    def upd(params, grads):
+        params[0] -= np.float32(0.05) * grads[0]
+    finals = {}
+    for threaded in (False, True):
+        p = [np.zeros((6, 1), np.float32)]
+        t = HC.DataParallelTrainer(4, grad_fn, upd)
+        for _ in range(5):
+            (t.train_batch_threaded if threaded else t.train_batch)(p, x, y)
+        finals[threaded] = p[0].copy()
+    assert np.array_equal(finals[False], finals[True])
+
+
+def test_mesh_and_shard_map():
+    mesh = DeviceMesh(("dp", "tp"), (2, 2))
+    assert mesh.coords(3) == {"dp": 1, "tp": 1} and mesh.group_ranks("tp", 2) == [2, 3]
+    x, w = torch.randn(8, 6), torch.randn(6, 4)
+    y = shard_map(lambda a, b: a @ b, mesh, (PartitionSpec("dp", None), PartitionSpec(None, "tp")),
+                  PartitionSpec("dp", "tp"), x, w)
+    assert torch.allclose(y, x @ w, atol=1e-6)
+    z = shard_map(lambda a: a.sum(0, keepdim=True) * 0 + 1, mesh, (PartitionSpec(None, None),), PartitionSpec(None, None), x)
+    assert z.shape == (1, 6)
+    with pytest.raises(ShardingError):
+        plan_sharding((7, 4), PartitionSpec("dp", None), mesh)
+    with pytest.raises(ShardingError):
+        shard_map(lambda a: a[:1] , mesh, (PartitionSpec("dp", None),), PartitionSpec(None, None), x)
+
+
+def test_gloo_ranks_rank_that_raises_fails_the_job():
+    code = (
+        "import os, sys, datetime, torch, torch.distributed as dist\n"
+        "dist.init_process_group('gloo', timeout=datetime.timedelta(seconds=5))\n"
+        "r = dist.get_rank()\n"
+        "t = torch.ones(4) * (r + 1)\n"
+        "dist.all_reduce(t)\n"
+        "assert t[0] == 3\n"
+        "if os.environ.get('FAIL_RANK') == str(r):\n"
+        "    raise SystemExit(3)          # leaves between steps, nothing in flight\n"
+        "try:\n"
+        "    dist.all_reduce(t)\n"
+        "    print('SECOND_OK')\n"
+        "except Exception as e:\n"
+        "    print('PEER_LOST', type(e).__name__)\n"
+        "    sys.exit(0)\n")
+    base = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+            "127.0.0.1", "--master-port", "29631", "-c" if False else "--no-python", sys.executable, "-c", code]
+    ok = subprocess.run(base, capture_output=True, text=True, timeout=120, env=dict(os.environ, PYTHONPATH=ROOT))
+    assert ok.returncode == 0 and ok.stdout.count("SECOND_OK") == 2, ok.stdout + ok.stderr
+    bad = subprocess.run(base, capture_output=True, text=True, timeout=120,
+                         env=dict(os.environ, PYTHONPATH=ROOT, FAIL_RANK="1"))
+    assert bad.returncode != 0
+    assert "PEER_LOST" in bad.stdout or "SECOND_OK" not in bad.stdout
