@@ -53,3 +53,9 @@ def test_tp_decoder_trains_like_single_gpu():
     _need(2)
     out = _run("mp_tp_model.py", 2, 29614)
     assert "TP_MODEL_OK" in out
+
+
+def test_dp_cnn_fused_allreduce_with_overlap():
+    _need(2)
+    out = _run("mp_dp_cnn.py", 2, 29615)
+    assert "DP_CNN_OK" in out
