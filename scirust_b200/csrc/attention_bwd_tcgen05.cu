@@ -46,6 +46,41 @@ __device__ __forceinline__ void store_row32_sw128(uint8_t* tile, int r, int c, c
   }
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Element-wise core of both backward kernels for 32 score columns of one query row (thread = query
+// row r, TMEM lane r): p = 2^(s*sl2 - lse2), dS = p * (dP*scale - delta*scale); columns beyond
+// `lim` are masked. Writes dS (and P when WRITE_P) as bf16 into the swizzled [q x kv] tiles.
+template <bool MASK, bool WRITE_P>
+__device__ __forceinline__ void bwd_chunk(uint32_t tm_S, uint32_t tm_dP, uint32_t lane_off, int c, int r, int lim,
+                                          float sl2, float lse2, float delta_s, float scale, uint8_t* p_buf,
+                                          uint8_t* ds_buf) {
+  uint32_t sv[32], dv[32];
+  tmem_ld_32x32(tm_S + lane_off + c * 32, sv);
+  tmem_ld_32x32(tm_dP + lane_off + c * 32, dv);
+  tmem_ld_wait();
+  uint32_t pk[16], dk[16];
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    float p0 = fast_exp2(fmaf(__uint_as_float(sv[i]), sl2, -lse2));
+    float p1 = fast_exp2(fmaf(__uint_as_float(sv[i + 1]), sl2, -lse2));
+    if (MASK) {
+      if (c * 32 + i > lim) p0 = 0.f;
+      if (c * 32 + i + 1 > lim) p1 = 0.f;
+    }
+    const float d0 = p0 * fmaf(__uint_as_float(dv[i]), scale, -delta_s);
+    const float d1 = p1 * fmaf(__uint_as_float(dv[i + 1]), scale, -delta_s);
+    if (WRITE_P) pk[i >> 1] = pack_bf16x2(p0, p1);
+    dk[i >> 1] = pack_bf16x2(d0, d1);
+  }
+  if (WRITE_P) store_row32_sw128(p_buf, r, c, pk);
+  store_row32_sw128(ds_buf, r, c, dk);
+}
+
 // --------------------------------------------------------------------------- delta
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                   const float* __restrict__ lse, float2* __restrict__ stats, int B, int S, int H,
@@ -137,6 +172,8 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __gri
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+  // S and dP are [query x kv] (TMEM lane = query row, as in the dQ kernel); their bf16 images P and dS
+  // are stored [q rows][kv] and consumed as MN-major A operands (A^T) by the dV / dK products.
   const uint32_t tm_ST = tmem_base, tm_dPT = tmem_base + 128, tm_dK = tmem_base + 256, tm_dV = tmem_base + 256 + DH;
 
   if (warp == 0) {
@@ -166,8 +203,8 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __gri
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(BT, BT, false, false);   // [kv x q], both K-major
-      constexpr uint32_t idesc_g = make_idesc_bf16(BT, DH, false, true);    // [kv x dh], B MN-major
+      constexpr uint32_t idesc_s = make_idesc_bf16(BT, BT, false, false);   // [q x kv], both K-major
+      constexpr uint32_t idesc_g = make_idesc_bf16(BT, DH, true, true);     // [kv x dh] = A^T B, both MN-major
       bool ok = mbar_wait(kv_full, 0, p.status, ST_TIMEOUT_FULL);
       int st_s = 0;          // stage / phase of the next score issue
       uint32_t ph_s = 0;
@@ -180,13 +217,13 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __gri
 #pragma unroll
         for (int k = 0; k < DH / 16; ++k) {
           const uint32_t off = (k >> 2) * (BT * 128) + (k & 3) * 32;
-          umma_bf16_ss(tm_ST, make_smem_desc(aK + off, 16, 1024), make_smem_desc(bQ + off, 16, 1024), idesc_s,
+          umma_bf16_ss(tm_ST, make_smem_desc(bQ + off, 16, 1024), make_smem_desc(aK + off, 16, 1024), idesc_s,
                        k > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int k = 0; k < DH / 16; ++k) {
           const uint32_t off = (k >> 2) * (BT * 128) + (k & 3) * 32;
-          umma_bf16_ss(tm_dPT, make_smem_desc(aV + off, 16, 1024), make_smem_desc(bdO + off, 16, 1024), idesc_s,
+          umma_bf16_ss(tm_dPT, make_smem_desc(bdO + off, 16, 1024), make_smem_desc(aV + off, 16, 1024), idesc_s,
                        k > 0 ? 1u : 0u);
         }
         umma_commit(st_full);
@@ -198,15 +235,13 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __gri
         const uint32_t aPT = smem_u32(sPT + pb * Cfg::PT_BYTES), adST = smem_u32(sdST + pb * Cfg::PT_BYTES);
         const uint32_t bQ = smem_u32(sQ + st_g * Cfg::T_BYTES), bdO = smem_u32(sdO + st_g * Cfg::T_BYTES);
 #pragma unroll
-        for (int k = 0; k < BT / 16; ++k) {
-          const uint32_t aoff = (k >> 2) * (BT * 128) + (k & 3) * 32;
-          umma_bf16_ss(tm_dV, make_smem_desc(aPT + aoff, 16, 1024),
+        for (int k = 0; k < BT / 16; ++k) {   // k walks 16 query rows at a time in both operands
+          umma_bf16_ss(tm_dV, make_smem_desc(aPT + k * (16 * 128), BT * 128, 1024),
                        make_smem_desc(bdO + k * (16 * 128), BT * 128, 1024), idesc_g, (t > 0 || k > 0) ? 1u : 0u);
         }
 #pragma unroll
         for (int k = 0; k < BT / 16; ++k) {
-          const uint32_t aoff = (k >> 2) * (BT * 128) + (k & 3) * 32;
-          umma_bf16_ss(tm_dK, make_smem_desc(adST + aoff, 16, 1024),
+          umma_bf16_ss(tm_dK, make_smem_desc(adST + k * (16 * 128), BT * 128, 1024),
                        make_smem_desc(bQ + k * (16 * 128), BT * 128, 1024), idesc_g, (t > 0 || k > 0) ? 1u : 0u);
         }
         umma_commit(&q_empty[st_g]);
@@ -231,49 +266,38 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __gri
   } else {
     const int sw = warp - 2;        // 0..7
     const int q = warp & 3;         // TMEM lane quarter
-    const int half = sw >> 2;       // which 64 query columns of the tile this warp handles
-    const int r = q * 32 + lane;    // kv row inside the tile == TMEM lane
+    const int half = sw >> 2;       // which 64 kv columns of the tile this warp handles
+    const int r = q * 32 + lane;    // row inside the tile == TMEM lane (query row in the loop, kv row at the end)
     const int kv_idx = kv0 + r;
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
+    const float delta_scale = p.scale;
     bool ok = true;
     for (int t = 0; t < n_iter; ++t) {
       const int head = kvh * group + t / n_qt;
       const int qt = qt_first + t % n_qt;
       const int q0 = qt * BT;
-      const float2* stats = p.stats + (static_cast<size_t>(b) * p.H + head) * p.S;
+      const int q_idx = q0 + r;
+      const float2 sd = __ldg(p.stats + (static_cast<size_t>(b) * p.H + head) * p.S + min(q_idx, p.S - 1));
       const int pb = Cfg::PDB ? (t & 1) : 0;
       uint8_t* pt_buf = sPT + pb * Cfg::PT_BYTES;
       uint8_t* dst_buf = sdST + pb * Cfg::PT_BYTES;
+      // last visible kv column of this query row inside the tile (-1: row is past the sequence end)
+      const bool diag = p.causal && qt == kt;
+      int lim = min(diag ? r : BT - 1, p.S - 1 - kv0);
+      if (q_idx >= p.S) lim = -1;
+      const bool need_mask = diag || (q0 + BT > p.S) || (kv0 + BT > p.S);
       if (!mbar_wait(st_full, t & 1, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      const bool diag = p.causal && qt == kt;
-      const bool tail = q0 + BT > p.S;
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = half * 2 + cc;  // 32-column chunk of the tile
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32(tm_ST + lane_off + c * 32, sv);
-        tmem_ld_32x32(tm_dPT + lane_off + c * 32, dv);
-        tmem_ld_wait();
-        uint32_t pk[16], dk[16];
+      if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float pr[2], ds[2];
+        for (int cc = 0; cc < 2; ++cc)
+          bwd_chunk<true, true>(tm_ST, tm_dPT, lane_off, half * 2 + cc, r, lim, p.scale_log2, sd.x,
+                                sd.y * delta_scale, p.scale, pt_buf, dst_buf);
+      } else {
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int col = c * 32 + i + e;  // query row inside the tile
-            const int qi = min(q0 + col, p.S - 1);
-            const float2 sd = __ldg(stats + qi);  // same address in every lane: one broadcast load
-            float pv = exp2f(__uint_as_float(sv[i + e]) * p.scale_log2 - sd.x);
-            if ((diag && r > col) || (tail && q0 + col >= p.S)) pv = 0.f;
-            pr[e] = pv;
-            ds[e] = pv * (__uint_as_float(dv[i + e]) - sd.y) * p.scale;
-          }
-          pk[i >> 1] = pack_bf16x2(pr[0], pr[1]);
-          dk[i >> 1] = pack_bf16x2(ds[0], ds[1]);
-        }
-        store_row32_sw128(pt_buf, r, c, pk);
-        store_row32_sw128(dst_buf, r, c, dk);
+        for (int cc = 0; cc < 2; ++cc)
+          bwd_chunk<false, true>(tm_ST, tm_dPT, lane_off, half * 2 + cc, r, lim, p.scale_log2, sd.x,
+                                 sd.y * delta_scale, p.scale, pt_buf, dst_buf);
       }
       tc_fence_before();
       fence_proxy_async_smem();
@@ -471,29 +495,21 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid
       if (!mbar_wait(s_full, j & 1, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       const int kv0 = j * BT;
-      const bool need_mask = (p.causal && j == n_blocks - 1) || (kv0 + BT > p.S);
-      const int limit = p.causal ? min(q_idx, p.S - 1) : (p.S - 1);
+      const bool diag = p.causal && j == n_blocks - 1;
+      const bool need_mask = diag || (kv0 + BT > p.S) || (q0 + BT > p.S);
+      int lim = min(diag ? r : BT - 1, p.S - 1 - kv0);
+      if (q_idx >= p.S) lim = -1;
       uint8_t* ds_buf = sdS + (Cfg::PDB ? (j & 1) : 0) * Cfg::DS_BYTES;
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = half * 2 + cc;
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32(tm_S + lane_off + c * 32, sv);
-        tmem_ld_32x32(tm_dP + lane_off + c * 32, dv);
-        tmem_ld_wait();
-        uint32_t dk[16];
+      if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float ds[2];
+        for (int cc = 0; cc < 2; ++cc)
+          bwd_chunk<true, false>(tm_S, tm_dP, lane_off, half * 2 + cc, r, lim, p.scale_log2, lse2, del * p.scale,
+                                 p.scale, nullptr, ds_buf);
+      } else {
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            float pv = exp2f(__uint_as_float(sv[i + e]) * p.scale_log2 - lse2);
-            if (need_mask && kv0 + c * 32 + i + e > limit) pv = 0.f;
-            ds[e] = pv * (__uint_as_float(dv[i + e]) - del) * p.scale;
-          }
-          dk[i >> 1] = pack_bf16x2(ds[0], ds[1]);
-        }
-        store_row32_sw128(ds_buf, r, c, dk);
+        for (int cc = 0; cc < 2; ++cc)
+          bwd_chunk<false, false>(tm_S, tm_dP, lane_off, half * 2 + cc, r, lim, p.scale_log2, lse2, del * p.scale,
+                                  p.scale, nullptr, ds_buf);
       }
       tc_fence_before();
       fence_proxy_async_smem();

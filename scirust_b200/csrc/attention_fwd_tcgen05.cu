@@ -47,6 +47,65 @@ struct AttParams {
   int* status;
 };
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Online-softmax update for one 128-column score block of one query row (thread = row r = TMEM
+// lane): pass 1 finds the row maximum, pass 2 writes P = 2^(s*sl2 - m_new) as bf16 into the
+// 128B-swizzled K-major tile and sums it. `m` is updated; alpha = 2^(m_old - m_new).
+template <bool MASK>
+__device__ __forceinline__ void softmax_block(uint32_t taddr, uint8_t* sP, int r, int lim, float sl2, float& m,
+                                              float& alpha, float& rowsum) {
+  constexpr float NEG = -1.0e30f;
+  float mx = NEG;
+#pragma unroll 1
+  for (int c = 0; c < ATT_BN / 32; ++c) {
+    uint32_t v[32];
+    tmem_ld_32x32(taddr + c * 32, v);
+    tmem_ld_wait();
+    float m4[4] = {NEG, NEG, NEG, NEG};   // four chains shorten the dependency chain of the max
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      float s = __uint_as_float(v[i]);
+      if (MASK && c * 32 + i > lim) s = NEG;
+      m4[i & 3] = fmaxf(m4[i & 3], s);
+    }
+    mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
+  }
+  const float m_new = fmaxf(m, mx * sl2);
+  alpha = fast_exp2(m - m_new);
+  float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+  for (int c = 0; c < ATT_BN / 32; ++c) {
+    uint32_t v[32];
+    tmem_ld_32x32(taddr + c * 32, v);
+    tmem_ld_wait();
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), sl2, -m_new));
+      float p1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), sl2, -m_new));
+      if (MASK) {
+        if (c * 32 + i > lim) p0 = 0.f;
+        if (c * 32 + i + 1 > lim) p1 = 0.f;
+      }
+      sum4[(i >> 1) & 3] += p0 + p1;
+      pk[i >> 1] = pack_bf16x2(p0, p1);
+    }
+    uint8_t* prow = sP + (c >> 1) * (ATT_BM * 128) + r * 128;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int unit = ((c & 1) * 4 + u) ^ (r & 7);
+      *reinterpret_cast<uint4*>(prow + unit * 16) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
+    }
+  }
+  rowsum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+  m = m_new;
+}
+
 template <int DH>
 __global__ void __launch_bounds__(ATT_THREADS)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap, const AttParams p) {
@@ -183,50 +242,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap, const AttParams p
       tc_fence_after();
       const int kv0 = j * ATT_BN;
       const bool need_mask = (p.causal && j == n_blocks - 1) || (kv0 + ATT_BN > p.S);
-      const int limit = p.causal ? min(q_idx, p.S - 1) : (p.S - 1);  // last visible kv index
-      float mx = NEG;
-#pragma unroll 1
-      for (int c = 0; c < ATT_BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_S + lane_off + c * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]);
-          if (need_mask && kv0 + c * 32 + i > limit) s = NEG;
-          mx = fmaxf(mx, s);
-        }
-      }
-      const float m_new = fmaxf(m, mx * p.scale_log2);
-      const float alpha = exp2f(m - m_new);
-      float rowsum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < ATT_BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_S + lane_off + c * 32, v);
-        tmem_ld_wait();
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
-          float p0 = exp2f(s0 * p.scale_log2 - m_new), p1 = exp2f(s1 * p.scale_log2 - m_new);
-          if (need_mask) {
-            if (kv0 + c * 32 + i > limit) p0 = 0.f;
-            if (kv0 + c * 32 + i + 1 > limit) p1 = 0.f;
-          }
-          rowsum += p0 + p1;
-          pk[i >> 1] = pack_bf16x2(p0, p1);
-        }
-        // P[r, c*32 .. c*32+32) -> 128B-swizzled K-major tile: chunk (c>>1), 16-byte units (c&1)*4 .. +4
-        uint8_t* prow = sP + (c >> 1) * (ATT_BM * 128) + r * 128;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int unit = ((c & 1) * 4 + u) ^ (r & 7);
-          *reinterpret_cast<uint4*>(prow + unit * 16) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
-        }
-      }
+      // last visible kv column of this row inside the block
+      const int lim = (p.causal ? min(q_idx, p.S - 1) : (p.S - 1)) - kv0;
+      float alpha, rowsum;
+      if (need_mask) softmax_block<true>(tmem_S + lane_off, sP, r, lim, p.scale_log2, m, alpha, rowsum);
+      else softmax_block<false>(tmem_S + lane_off, sP, r, lim, p.scale_log2, m, alpha, rowsum);
       l = l * alpha + rowsum;
-      m = m_new;
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();

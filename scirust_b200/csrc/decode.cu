@@ -33,15 +33,40 @@ __device__ __forceinline__ uint32_t dpack(float lo, float hi) {
 // ---------------------------------------------------------------------------
 constexpr int GEMV_KCHUNK = 256;  // rows of X staged in shared memory at a time
 
+// Optional prologue applied to X while it is staged (so the producing kernel disappears):
+//   PRO_RMSNORM: x <- bf16(x * rsqrt(mean(x^2) + eps) * norm_w[k]); the row statistic is computed by
+//                one warp per row in exactly the order of rmsnorm_fwd_kernel, so fused and unfused
+//                paths agree bit for bit.
+//   PRO_SWIGLU:  X is a fused [gate | up] row of width 2K: x <- bf16(silu(gate[k]) * up[k]).
+enum { PRO_NONE = 0, PRO_RMSNORM = 1, PRO_SWIGLU = 2 };
+
 template <int MB, bool INT8>
 __global__ void __launch_bounds__(256)
 gemv_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const void* __restrict__ Wv, int ldw, float* __restrict__ part,
-            int M, int N, int K, int k_per_split) {
+            int M, int N, int K, int k_per_split, int prologue, const __nv_bfloat16* __restrict__ norm_w, float eps) {
   constexpr int VEC = INT8 ? 16 : 8;
   constexpr int COLS = 32 * VEC;
   __shared__ float xs[MB][GEMV_KCHUNK];
   __shared__ float buf[256 * VEC];  // cross-warp reduction: [warp][lane][VEC]
+  __shared__ float s_inv[8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (prologue == PRO_RMSNORM) {
+    if (warp < M) {
+      const __nv_bfloat16* xr = X + static_cast<size_t>(warp) * ldx;
+      float ss = 0.f;
+      for (int c = lane * 8; c < K; c += 256) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
+        const float f[8] = {dbflo(raw.x), dbfhi(raw.x), dbflo(raw.y), dbfhi(raw.y),
+                            dbflo(raw.z), dbfhi(raw.z), dbflo(raw.w), dbfhi(raw.w)};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane == 0) s_inv[warp] = rsqrtf(ss / static_cast<float>(K) + eps);
+    }
+    __syncthreads();
+  }
   const int col = blockIdx.x * COLS + lane * VEC;
   const int k0 = blockIdx.y * k_per_split;
   const int k1 = min(K, k0 + k_per_split);
@@ -56,7 +81,18 @@ gemv_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const void* __restrict
     __syncthreads();
     for (int i = threadIdx.x; i < MB * GEMV_KCHUNK; i += 256) {
       const int m = i / GEMV_KCHUNK, kk = i - m * GEMV_KCHUNK;
-      xs[m][kk] = (m < M && kk < kn) ? __bfloat162float(X[static_cast<size_t>(m) * ldx + kc + kk]) : 0.f;
+      float xv = 0.f;
+      if (m < M && kk < kn) {
+        const int k = kc + kk;
+        xv = __bfloat162float(X[static_cast<size_t>(m) * ldx + k]);
+        if (prologue == PRO_RMSNORM) {
+          xv = __bfloat162float(__float2bfloat16_rn(xv * s_inv[m] * __bfloat162float(norm_w[k])));
+        } else if (prologue == PRO_SWIGLU) {
+          const float u = __bfloat162float(X[static_cast<size_t>(m) * ldx + K + k]);
+          xv = __bfloat162float(__float2bfloat16_rn(xv / (1.f + __expf(-xv)) * u));
+        }
+      }
+      xs[m][kk] = xv;
     }
     __syncthreads();
     if (col < N) {
@@ -143,6 +179,41 @@ __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, 
     const uint4 v = *reinterpret_cast<const uint4*>(src + kv * Hkv * dh + r * 8);
     __nv_bfloat16* dst = pool + ((((static_cast<size_t>(blk) * 2 + kv) * Hkv + h) * page + slot) * dh + d);
     *reinterpret_cast<uint4*>(dst) = v;
+  }
+}
+
+// Decode-step fusion of RoPE and the cache append: rotates the q and k heads of each new token in
+// place (interleaved pairs, head-local frequency, position pos[t]) and writes the rotated k and the
+// v heads into the paged pool. One block per token.
+__global__ void rope_kv_append_kernel(__nv_bfloat16* __restrict__ qkv, int ld, int H, int Hkv, int dh,
+                                      const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                      __nv_bfloat16* __restrict__ pool, const int* __restrict__ block_table,
+                                      int max_blocks, int page, const int* __restrict__ seq_of,
+                                      const int* __restrict__ pos, int n_tok) {
+  const int t = blockIdx.x;
+  if (t >= n_tok) return;
+  const int b = seq_of[t], p = pos[t];
+  const int half = dh >> 1;
+  __nv_bfloat16* row = qkv + static_cast<size_t>(t) * ld;
+  const int n_pairs = (H + Hkv) * half;
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int head = i / half, pr = i - head * half;
+    const float c = cos_t[static_cast<size_t>(p) * half + pr], s = sin_t[static_cast<size_t>(p) * half + pr];
+    __nv_bfloat16* e = row + head * dh + 2 * pr;
+    const float x0 = __bfloat162float(e[0]), x1 = __bfloat162float(e[1]);
+    e[0] = __float2bfloat16_rn(x0 * c - x1 * s);
+    e[1] = __float2bfloat16_rn(x0 * s + x1 * c);
+  }
+  __syncthreads();
+  const int blk = block_table[b * max_blocks + p / page];
+  const int slot = p % page;
+  const int per = Hkv * dh / 8;
+  const __nv_bfloat16* src = row + H * dh;
+  for (int i = threadIdx.x; i < 2 * per; i += blockDim.x) {
+    const int kv = i / per, r = i - kv * per;
+    const int h = (r * 8) / dh, d = (r * 8) - h * dh;
+    const uint4 v = *reinterpret_cast<const uint4*>(src + kv * Hkv * dh + r * 8);
+    *reinterpret_cast<uint4*>(pool + ((((static_cast<size_t>(blk) * 2 + kv) * Hkv + h) * page + slot) * dh + d)) = v;
   }
 }
 
@@ -352,14 +423,14 @@ using namespace sb;
 
 template <bool INT8>
 static int launch_gemv(const void* X, int ldx, const void* W, int ldw, float* part, int M, int N, int K, int splits,
-                       int kps, cudaStream_t s) {
+                       int kps, int pro, const void* nw, float eps, cudaStream_t s) {
   constexpr int COLS = INT8 ? 512 : 256;
   dim3 grid((N + COLS - 1) / COLS, splits);
   const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(X);
-  if (M <= 1) gemv_kernel<1, INT8><<<grid, 256, 0, s>>>(x, ldx, W, ldw, part, M, N, K, kps);
-  else if (M <= 2) gemv_kernel<2, INT8><<<grid, 256, 0, s>>>(x, ldx, W, ldw, part, M, N, K, kps);
-  else if (M <= 4) gemv_kernel<4, INT8><<<grid, 256, 0, s>>>(x, ldx, W, ldw, part, M, N, K, kps);
-  else if (M <= 8) gemv_kernel<8, INT8><<<grid, 256, 0, s>>>(x, ldx, W, ldw, part, M, N, K, kps);
+  if (M <= 1) gemv_kernel<1, INT8><<<grid, 256, 0, s>>>(x, ldx, W, ldw, part, M, N, K, kps, pro, static_cast<const __nv_bfloat16*>(nw), eps);
+  else if (M <= 2) gemv_kernel<2, INT8><<<grid, 256, 0, s>>>(x, ldx, W, ldw, part, M, N, K, kps, pro, static_cast<const __nv_bfloat16*>(nw), eps);
+  else if (M <= 4) gemv_kernel<4, INT8><<<grid, 256, 0, s>>>(x, ldx, W, ldw, part, M, N, K, kps, pro, static_cast<const __nv_bfloat16*>(nw), eps);
+  else if (M <= 8) gemv_kernel<8, INT8><<<grid, 256, 0, s>>>(x, ldx, W, ldw, part, M, N, K, kps, pro, static_cast<const __nv_bfloat16*>(nw), eps);
   else return SB_ERR_ARG;
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
@@ -367,15 +438,18 @@ static int launch_gemv(const void* X, int ldx, const void* W, int ldw, float* pa
 // Y[M,N] = X[M,K] * W[K,N] (* scale[n]) (+ R). M <= 8 per call (callers loop over row groups).
 // W bf16 (is_int8 == 0) or int8 with fp32 column scales. workspace: splits*M*N floats.
 // Returns the number of k-splits used through *splits_out when splits == 0 (auto).
+// prologue: 0 none, 1 RMSNorm of X with gain norm_w (K must be a multiple of 8), 2 SwiGLU over a
+// fused [gate | up] X of row width 2K.
 extern "C" int sb_gemv(const void* X, int ldx, const void* W, int ldw, const float* scale, const void* R, int ldr,
                        void* out_bf16, int ldo, float* out_f32, int M, int N, int K, int is_int8, int splits,
-                       float* workspace, void* stream) {
+                       float* workspace, int prologue, const void* norm_w, float eps, void* stream) {
   if (M <= 0 || M > 8 || N <= 0 || K <= 0 || (N & 7) || (is_int8 && (N & 15))) return SB_ERR_ARG;
+  if (prologue < 0 || prologue > 2 || (prologue == 1 && (!norm_w || (K & 7) || (ldx & 7)))) return SB_ERR_ARG;
   if (splits < 1) splits = 1;
   int kps = ((K + splits - 1) / splits + 7) / 8 * 8;
   splits = (K + kps - 1) / kps;
-  int rc = is_int8 ? launch_gemv<true>(X, ldx, W, ldw, workspace, M, N, K, splits, kps, STREAM)
-                   : launch_gemv<false>(X, ldx, W, ldw, workspace, M, N, K, splits, kps, STREAM);
+  int rc = is_int8 ? launch_gemv<true>(X, ldx, W, ldw, workspace, M, N, K, splits, kps, prologue, norm_w, eps, STREAM)
+                   : launch_gemv<false>(X, ldx, W, ldw, workspace, M, N, K, splits, kps, prologue, norm_w, eps, STREAM);
   if (rc) return rc;
   gemv_finish_kernel<<<(M * N + 255) / 256, 256, 0, STREAM>>>(workspace, splits, M, N, scale,
                                                              static_cast<const __nv_bfloat16*>(R), ldr,
@@ -389,6 +463,16 @@ extern "C" int sb_kv_append(const void* qkv, int ld, int H, int Hkv, int dh, voi
   kv_append_kernel<<<n_tok, 128, 0, STREAM>>>(static_cast<const __nv_bfloat16*>(qkv), ld, H, Hkv, dh,
                                               static_cast<__nv_bfloat16*>(pool), block_table, max_blocks, page,
                                               seq_of, pos, n_tok);
+  CHECK_LAUNCH();
+}
+
+extern "C" int sb_rope_kv_append(void* qkv, int ld, int H, int Hkv, int dh, const float* cos_t, const float* sin_t,
+                                 void* pool, const int* block_table, int max_blocks, int page, const int* seq_of,
+                                 const int* pos, int n_tok, void* stream) {
+  if (n_tok <= 0 || (dh & 7)) return SB_ERR_ARG;
+  rope_kv_append_kernel<<<n_tok, 256, 0, STREAM>>>(static_cast<__nv_bfloat16*>(qkv), ld, H, Hkv, dh, cos_t, sin_t,
+                                                   static_cast<__nv_bfloat16*>(pool), block_table, max_blocks, page,
+                                                   seq_of, pos, n_tok);
   CHECK_LAUNCH();
 }
 

@@ -136,6 +136,8 @@ class InferenceEngine:
         if M <= 8:
             return D.gemv(x, w, residual=residual)
         if isinstance(w, D.QuantWeight):
+            if w.q.shape[1] % 16 == 0:
+                return D.matmul_w8(x, w, residual=residual)
             w = w.dequantize()
         return ops.matmul_nn(x, w, residual=residual)
 
@@ -178,8 +180,10 @@ class InferenceEngine:
         if M <= 8:
             D.gemv(hn, self.head_t, out_f32=logits)
         else:
-            w = self.head_t.dequantize() if isinstance(self.head_t, D.QuantWeight) else self.head_t
-            logits.copy_(ops.matmul_nn(hn, w).float())
+            if isinstance(self.head_t, D.QuantWeight):
+                logits.copy_(D.matmul_w8(hn, self.head_t).float())
+            else:
+                logits.copy_(ops.matmul_nn(hn, self.head_t).float())
 
     # ------------------------------------------------------------------ decode
     def _decode_body(self, B: int, max_len: int):
@@ -188,17 +192,28 @@ class InferenceEngine:
         seq_of = self._seq_of[:B]
         pos = cache.seq_len[:B]
         x = ops.embed_fwd(self.embed, self.tokens[:B])
+        small = B <= 8      # weight-streaming path: norms and SwiGLU are fused into the GEMV loads
         for li, l in enumerate(self.layers):
-            h, _ = ops.rmsnorm_fwd(x, l["rms1"], cfg.eps, want_inv=False)
-            qkv = self._linear(h, l["wqkv"])
-            ops.rope_(qkv, H + Hkv, dh, 1, self.cos, self.sin, positions=pos)
-            D.kv_append(qkv, H, Hkv, dh, cache.pools[li], cache.block_table, cache.page, seq_of, pos)
+            if small:
+                qkv = D.gemv(x, l["wqkv"], rms_weight=l["rms1"], eps=cfg.eps)
+            else:
+                h, _ = ops.rmsnorm_fwd(x, l["rms1"], cfg.eps, want_inv=False)
+                qkv = self._linear(h, l["wqkv"])
+            D.rope_kv_append(qkv, H, Hkv, dh, self.cos, self.sin, cache.pools[li], cache.block_table, cache.page,
+                             seq_of, pos)
             a = D.decode_attention(qkv, cache.pools[li], cache.block_table, cache.page, self._len_plus1[:B], H, Hkv,
                                    dh, max_len=max_len)
             x = self._linear(a, l["wo"], residual=x)
-            h, _ = ops.rmsnorm_fwd(x, l["rms2"], cfg.eps, want_inv=False)
-            gu = self._linear(h, l["wgu"])
-            x = self._linear(ops.swiglu_fwd(gu), l["wd"], residual=x)
+            if small:
+                gu = D.gemv(x, l["wgu"], rms_weight=l["rms2"], eps=cfg.eps)
+                x = D.gemv(gu, l["wd"], residual=x, swiglu=True)
+            else:
+                h, _ = ops.rmsnorm_fwd(x, l["rms2"], cfg.eps, want_inv=False)
+                gu = self._linear(h, l["wgu"])
+                x = self._linear(ops.swiglu_fwd(gu), l["wd"], residual=x)
+        if small:
+            D.gemv(x, self.head_t, out_f32=self.logits[:B], rms_weight=self.rms_final, eps=cfg.eps)
+            return
         hn, _ = ops.rmsnorm_fwd(x, self.rms_final, cfg.eps, want_inv=False)
         self._head(hn, self.logits[:B])
 

@@ -12,13 +12,16 @@ from . import gemm as _g
 
 BF = torch.bfloat16
 vp, i32, f32 = _lib.vp, _lib.i32, _lib.f32
-_lib.register("sb_gemv", [vp, i32, vp, i32, vp, vp, i32, vp, i32, vp, i32, i32, i32, i32, i32, vp, vp])
+_lib.register("sb_gemv", [vp, i32, vp, i32, vp, vp, i32, vp, i32, vp, i32, i32, i32, i32, i32, vp, i32, vp, f32, vp])
+_lib.register("sb_rope_kv_append", [vp, i32, i32, i32, i32, vp, vp, vp, vp, i32, i32, vp, vp, i32, vp])
 _lib.register("sb_kv_append", [vp, i32, i32, i32, i32, vp, vp, i32, i32, vp, vp, i32, vp])
 _lib.register("sb_decode_attention", [vp, i32, vp, vp, i32, i32, vp, i32, i32, i32, i32, i32, f32, vp, vp, vp, i32,
                                       vp])
 _lib.register("sb_argmax", [vp, i32, i32, vp, vp, vp, vp, i32, i32, vp])
 _lib.register("sb_quantize_per_channel", [vp, i32, i32, i32, vp, vp, vp])
 _lib.register("sb_dequantize", [vp, vp, i32, i32, vp, vp])
+
+_lib.register("sb_gemm_w8", [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp])
 
 _ws: dict = {}
 
@@ -77,14 +80,21 @@ def _auto_splits(N, K, cols):
     return s
 
 
-def gemv(x, w, residual=None, out=None, out_f32=None, splits=None):
-    """y[M,N] = x[M,K] @ W (+ residual) for small M, streaming W once. ``w`` is a bf16 ``[K, N]``
-    matrix or a ``QuantWeight``. Rows are processed in groups of 8."""
-    M, K = x.shape
+def gemv(x, w, residual=None, out=None, out_f32=None, splits=None, rms_weight=None, eps=1e-5, swiglu=False):
+    """y[M,N] = f(x)[M,K] @ W (+ residual) for small M, streaming W once. ``w`` is a bf16 ``[K, N]``
+    matrix or a ``QuantWeight``. Rows are processed in groups of 8. ``rms_weight`` fuses the RMSNorm of
+    ``x`` into the load; ``swiglu`` treats ``x`` as a fused ``[gate | up]`` row of width 2K."""
     quant = isinstance(w, QuantWeight)
     wm = w.q if quant else w
-    N = wm.shape[1]
+    K, N = wm.shape
+    M = x.shape[0]
     if not x.is_cuda:
+        if rms_weight is not None:
+            xf = x.float()
+            x = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * rms_weight.float()).to(BF)
+        elif swiglu:
+            g, u = x[:, :K].float(), x[:, K:].float()
+            x = (g * torch.sigmoid(g) * u).to(BF)
         wf = (w.q.float() if quant else w.float())
         y = x.float() @ wf
         if quant:
@@ -111,9 +121,35 @@ def gemv(x, w, residual=None, out=None, out_f32=None, splits=None):
                   residual.stride(0) if residual is not None else 0,
                   out[m0:m0 + mb].data_ptr() if out is not None else None, out.stride(0) if out is not None else 0,
                   out_f32[m0:m0 + mb].data_ptr() if out_f32 is not None else None, mb, N, K, int(quant), splits,
-                  ws.data_ptr(), _lib.stream())
+                  ws.data_ptr(), 1 if rms_weight is not None else (2 if swiglu else 0), _lib.ptr(rms_weight),
+                  float(eps), _lib.stream())
         _g.launch_count += 2
     return out if out is not None else out_f32
+
+
+def matmul_w8(x, w: QuantWeight, residual=None, out=None, splits=None):
+    """y[M,N] = (x[M,K] @ int8 W) * scale (+ residual) on the dequant-fused tcgen05 GEMM
+    (csrc/gemm_w8_tcgen05.cu): the int8 codes are widened to bf16 in shared memory, so the weights
+    cross HBM once as int8. For M <= 8 prefer ``gemv``."""
+    M, K = x.shape
+    N = w.q.shape[1]
+    if not x.is_cuda:
+        y = (x.float() @ w.q.float()) * w.scale[None, :]
+        if residual is not None:
+            y = y + residual.float()
+        return y.to(BF)
+    if out is None:
+        out = torch.empty((M, N), dtype=BF, device=x.device)
+    if splits is None:
+        tiles = ((M + 127) // 128) * ((N + 255) // 256)
+        nkb = (K + 63) // 64
+        splits = 1 if tiles >= 74 or nkb < 16 else max(1, min((148 + tiles - 1) // tiles, nkb // 8, 16))
+    ws = _workspace(splits * M * N, x.device) if splits > 1 else None
+    _lib.call("sb_gemm_w8", x.data_ptr(), w.q.data_ptr(), w.scale.data_ptr(), out.data_ptr(), _lib.ptr(residual), M, N,
+              K, x.stride(0), w.q.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0, splits,
+              _lib.ptr(ws), _lib.status_word(x.device).data_ptr(), _lib.stream())
+    _g.launch_count += 2 if splits > 1 else 1
+    return out
 
 
 def kv_append(qkv, H, Hkv, dh, pool, block_table, page, seq_of, pos):
@@ -128,6 +164,18 @@ def kv_append(qkv, H, Hkv, dh, pool, block_table, page, seq_of, pos):
         return
     _lib.call("sb_kv_append", qkv.data_ptr(), qkv.stride(0), H, Hkv, dh, pool.data_ptr(), block_table.data_ptr(),
               block_table.shape[1], page, seq_of.data_ptr(), pos.data_ptr(), n, _lib.stream())
+    _g.launch_count += 1
+
+
+def rope_kv_append(qkv, H, Hkv, dh, cos_t, sin_t, pool, block_table, page, seq_of, pos):
+    """Decode step: rotate q/k of each new token in place at ``pos`` and append k, v to the pool."""
+    if not qkv.is_cuda:
+        from . import basic
+        basic.rope_(qkv, H + Hkv, dh, 1, cos_t, sin_t, positions=pos)
+        return kv_append(qkv, H, Hkv, dh, pool, block_table, page, seq_of, pos)
+    _lib.call("sb_rope_kv_append", qkv.data_ptr(), qkv.stride(0), H, Hkv, dh, cos_t.data_ptr(), sin_t.data_ptr(),
+              pool.data_ptr(), block_table.data_ptr(), block_table.shape[1], page, seq_of.data_ptr(), pos.data_ptr(),
+              qkv.shape[0], _lib.stream())
     _g.launch_count += 1
 
 

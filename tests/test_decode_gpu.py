@@ -93,3 +93,17 @@ def test_engine_cached_equals_naive_and_graph(quant):
     if quant is None:
         naive = reference_generate(model, prompts, 8)
         assert torch.equal(a, naive), (a.tolist(), naive.tolist())
+
+
+@pytest.mark.parametrize("M,K,N", [(16, 1024, 512), (64, 4096, 1536), (200, 1000, 272), (2048, 1024, 2816)])
+def test_dequant_fused_gemm(M, K, N):
+    x, w, r = _r((M, K), 6), _r((K, N), 7), _r((M, N), 8)
+    qw = D.quantize_per_channel(w)
+    ref = x.float() @ (qw.q.float() * qw.scale[None, :]) + r.float()
+    y = D.matmul_w8(x, qw, residual=r)
+    _lib.check_status()
+    assert (y.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+    y2 = D.matmul_w8(x, qw, residual=r, splits=4)
+    _lib.check_status()
+    assert (y2.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+    assert torch.equal(y2, D.matmul_w8(x, qw, residual=r, splits=4))
