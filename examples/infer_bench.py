@@ -33,6 +33,7 @@ def main():
     ap.add_argument("--quant", default="none", choices=["none", "int8"])
     ap.add_argument("--ttft-iters", type=int, default=5)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (smoke runs)")
+    ap.add_argument("--graph", type=int, default=1, help="0: launch every decode step eagerly (for launch lists)")
     a = ap.parse_args()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -41,7 +42,7 @@ def main():
         cfg.n_layers = a.layers
     model = GQADecoder(cfg, device=dev, seed=7)
     eng = InferenceEngine(model, quant=None if a.quant == "none" else "int8", max_batch=a.batch,
-                          max_seq=a.prompt + a.new + 1, page=64)
+                          max_seq=a.prompt + a.new + 1, page=64, use_graph=bool(a.graph))
     g = torch.Generator().manual_seed(0)
     prompts = torch.randint(0, cfg.vocab_size, (a.batch, a.prompt), generator=g).pin_memory()
     # time to first token

@@ -165,6 +165,108 @@ allreduce_bf16_kernel(const __grid_constant__ AllReduceParams p) {
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Latency-oriented collectives for tensor-parallel decoding (messages of a few KB to a few hundred
+// KB). One wait per call instead of two, output in plain local memory, and the epoch lives in a
+// device word that the kernel itself advances, so a captured CUDA graph can replay the call.
+//
+//   every rank: source buffer (its partial result, symmetric memory) is final when the kernel starts
+//   announce  flags[slot][0][my_rank] = epoch on every peer; wait for all peers' announcements
+//   mode 0    out[i] = residual[i] + sum over ranks r = 0..W-1 of in[r][i]   (fp32, fixed order, so
+//             every rank computes identical bits; inputs bf16 or fp32, output bf16)
+//   mode 1    out[row][r][i] = in[r][row][i]   (all-gather of 16-byte words, e.g. vocabulary-
+//             sharded logits rows)
+// There is no closing wait: a source buffer may be rewritten only after the same rank has completed
+// a LATER collective on this channel (every peer entered that later call, hence finished reading).
+// Callers alternate at least two source buffers per channel.
+struct SmallCollParams {
+  const void* in[MAX_WORLD];
+  uint32_t* flags[MAX_WORLD];
+  int rank, W, mode, in_fp32;
+  size_t n;          // mode 0: elements (multiple of 8); mode 1: 16-byte words per row per rank
+  int rows;          // mode 1
+  const __nv_bfloat16* residual;  // mode 0, may be null
+  void* out;
+  uint32_t* epoch_word;       // local device word: number of completed calls on this channel
+  int slot;
+  uint64_t wait_ns;
+  unsigned int* cta_counter;
+  int* status;
+};
+
+__global__ void __launch_bounds__(256)
+small_collective_kernel(const __grid_constant__ SmallCollParams p) {
+  __shared__ int s_ok;
+  __shared__ uint32_t s_epoch;
+  const int W = p.W;
+  if (threadIdx.x == 0) {
+    const uint32_t e = *reinterpret_cast<volatile uint32_t*>(p.epoch_word) + 1u;
+    if (blockIdx.x == 0) {
+      __threadfence_system();
+      for (int r = 0; r < W; ++r)
+        st_release_sys(p.flags[r] + static_cast<size_t>(p.slot) * SLOT_WORDS + p.rank, e);
+    }
+    s_ok = wait_flags(p.flags[p.rank] + static_cast<size_t>(p.slot) * SLOT_WORDS, W, e, p.wait_ns, p.status) ? 1 : 0;
+    s_epoch = e;
+  }
+  __syncthreads();
+  const size_t tid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const size_t nthreads = static_cast<size_t>(gridDim.x) * blockDim.x;
+  if (s_ok) {
+    if (p.mode == 0) {
+      const size_t n8 = p.n / 8;
+      for (size_t i = tid; i < n8; i += nthreads) {
+        float acc[8];
+        if (p.residual) {
+          const uint4 v = *reinterpret_cast<const uint4*>(p.residual + i * 8);
+          acc[0] = bf16_lo(v.x); acc[1] = bf16_hi(v.x); acc[2] = bf16_lo(v.y); acc[3] = bf16_hi(v.y);
+          acc[4] = bf16_lo(v.z); acc[5] = bf16_hi(v.z); acc[6] = bf16_lo(v.w); acc[7] = bf16_hi(v.w);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        }
+        for (int r = 0; r < W; ++r) {
+          if (p.in_fp32) {
+            const float* src = static_cast<const float*>(p.in[r]) + i * 8;
+            const uint4 a = ld_peer_v4(src), b = ld_peer_v4(src + 4);
+            acc[0] += __uint_as_float(a.x); acc[1] += __uint_as_float(a.y);
+            acc[2] += __uint_as_float(a.z); acc[3] += __uint_as_float(a.w);
+            acc[4] += __uint_as_float(b.x); acc[5] += __uint_as_float(b.y);
+            acc[6] += __uint_as_float(b.z); acc[7] += __uint_as_float(b.w);
+          } else {
+            const uint4 v = ld_peer_v4(static_cast<const __nv_bfloat16*>(p.in[r]) + i * 8);
+            acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x); acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
+            acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z); acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+          }
+        }
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + i * 8) =
+            make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                       pack_bf16x2(acc[6], acc[7]));
+      }
+    } else {
+      const size_t per_rank = static_cast<size_t>(p.rows) * p.n;
+      const size_t total = per_rank * W;
+      uint4* out = static_cast<uint4*>(p.out);
+      for (size_t i = tid; i < total; i += nthreads) {
+        const int r = static_cast<int>(i / per_rank);
+        const size_t w = i - static_cast<size_t>(r) * per_rank;
+        const size_t row = w / p.n, col = w - row * p.n;
+        out[(row * W + r) * p.n + col] = ld_peer_v4(static_cast<const uint4*>(p.in[r]) + w);
+      }
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(p.cta_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *p.cta_counter = 0;
+      *reinterpret_cast<volatile uint32_t*>(p.epoch_word) = s_epoch;
+    }
+  }
+}
+
 // A wait that nothing satisfies: used by tests to check that a bounded wait returns a status
 // instead of hanging. Waits `limit_ns` at most on flags that stay below `epoch`.
 __global__ void wait_probe_kernel(const uint32_t* flags, int W, uint32_t epoch, uint64_t limit_ns, int* status) {
@@ -218,6 +320,33 @@ extern "C" int sb_allreduce_bf16(void* const* in_ptrs, void* const* out_ptrs, vo
   p.cta_counter = cta_counter;
   p.status = status;
   allreduce_bf16_kernel<<<n_ctas, 512, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+}
+
+
+// mode 0: all-reduce sum (+ residual) of n elements -> bf16 `out` (local memory);
+// mode 1: all-gather of `rows` rows of n 16-byte words per rank -> out[row][rank][n].
+// epoch_word and cta_counter are local device words, zero when the channel is created.
+extern "C" int sb_small_collective(void* const* in_ptrs, void* const* flag_ptrs, int rank, int W, int mode,
+                                   int in_fp32, size_t n, int rows, const void* residual, void* out,
+                                   uint32_t* epoch_word, int slot, unsigned int* cta_counter, int n_ctas, int wait_ms,
+                                   int* status, void* stream) {
+  if (W < 1 || W > MAX_WORLD || rank < 0 || rank >= W || n_ctas < 1 || mode < 0 || mode > 1) return SB_ERR_ARG;
+  if (mode == 0 && (n & 7)) return SB_ERR_ARG;
+  if (mode == 1 && rows < 1) return SB_ERR_ARG;
+  SmallCollParams p;
+  for (int r = 0; r < W; ++r) {
+    if (reinterpret_cast<uintptr_t>(in_ptrs[r]) & 15) return SB_ERR_ALIGN;
+    p.in[r] = in_ptrs[r];
+    p.flags[r] = static_cast<uint32_t*>(flag_ptrs[r]);
+  }
+  if ((reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(residual) & 15)) return SB_ERR_ALIGN;
+  p.rank = rank; p.W = W; p.mode = mode; p.in_fp32 = in_fp32; p.n = n; p.rows = rows;
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.out = out; p.epoch_word = epoch_word; p.slot = slot;
+  p.wait_ns = wait_ms > 0 ? static_cast<uint64_t>(wait_ms) * 1000000ull : kPeerWaitNsDefault;
+  p.cta_counter = cta_counter; p.status = status;
+  small_collective_kernel<<<n_ctas, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
 

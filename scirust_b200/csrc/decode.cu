@@ -13,6 +13,7 @@
 #include <math.h>
 #include <stdint.h>
 #include "api.h"
+#include "sm100_ptx.cuh"
 
 namespace sb {
 
@@ -24,14 +25,27 @@ __device__ __forceinline__ uint32_t dpack(float lo, float hi) {
 }
 
 // ---------------------------------------------------------------------------
-// GEMV / skinny GEMM: Y[M,N] (+)= X[M,K] * W[K,N], M <= MB, W streamed once.
-// grid = (ceil(N / COLS), splits). A CTA owns COLS output columns and the k range of its split;
-// warp w walks rows k0+w, k0+w+8, ...; a lane holds VEC consecutive columns. Partials of the 8
-// warps are added in warp order in shared memory, split partials in split order by
-// gemv_finish_kernel: the summation tree depends only on (K, splits).
+// GEMV / skinny GEMM: Y[M,N] = f(X)[M,K] * W[K,N] (* scale[n]) (+ R), M <= MB <= 8, W streamed once.
+// grid = (ceil(N / COLS), splits). A CTA owns COLS output columns (512 bytes of every weight row)
+// and the k range of its split.
+//   warp 8      producer: streams the CTA's weight slab through a ring of STAGES tiles of 32 rows
+//               with bulk asynchronous copies (one 512-byte copy per row, one mbarrier per tile);
+//               it starts at once, because the weights do not depend on the previous kernel's output
+//   warps 0-7   stage f(X) for the CTA's k range in shared memory (optionally fused RMSNorm or
+//               SwiGLU), then consume tiles: warp w takes rows w, w+8, w+16, w+24 of every tile, a
+//               lane holds VEC consecutive columns
+// Partials of the 8 warps are added in warp order in shared memory; split partials go to a
+// workspace and the LAST CTA of a column block (a counter, no data atomics) adds them in split
+// order and applies scale / residual: the summation tree depends only on (K, splits), and the
+// finishing pass needs no second launch.
 // INT8: W is int8 with one fp32 scale per output column, applied after the sum.
 // ---------------------------------------------------------------------------
-constexpr int GEMV_KCHUNK = 256;  // rows of X staged in shared memory at a time
+constexpr int GEMV_KT = 32;          // rows per tile
+constexpr int GEMV_ROW_BYTES = 512;  // bytes of one weight row owned by a CTA
+constexpr int GEMV_STAGES = 6;
+constexpr int GEMV_TILE_BYTES = GEMV_KT * GEMV_ROW_BYTES;
+constexpr int GEMV_THREADS = 288;
+constexpr int GEMV_MAX_XS_BYTES = 64 * 1024;
 
 // Optional prologue applied to X while it is staged (so the producing kernel disappears):
 //   PRO_RMSNORM: x <- bf16(x * rsqrt(mean(x^2) + eps) * norm_w[k]); the row statistic is computed by
@@ -40,120 +54,205 @@ constexpr int GEMV_KCHUNK = 256;  // rows of X staged in shared memory at a time
 //   PRO_SWIGLU:  X is a fused [gate | up] row of width 2K: x <- bf16(silu(gate[k]) * up[k]).
 enum { PRO_NONE = 0, PRO_RMSNORM = 1, PRO_SWIGLU = 2 };
 
+struct GemvParams {
+  const __nv_bfloat16* X; int ldx;
+  const void* W; int ldw;            // elements
+  const float* scale;                // int8 only
+  const __nv_bfloat16* R; int ldr;
+  __nv_bfloat16* out; int ldo;
+  float* out_f32;                    // [M, N] dense, optional
+  float* part;                       // [splits, M, N] when splits > 1
+  unsigned int* counters;            // [gridDim.x], zero between calls
+  int M, N, K, k_per_split, prologue;
+  const __nv_bfloat16* norm_w; float eps;
+  int* status;
+};
+
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
 template <int MB, bool INT8>
-__global__ void __launch_bounds__(256)
-gemv_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const void* __restrict__ Wv, int ldw, float* __restrict__ part,
-            int M, int N, int K, int k_per_split, int prologue, const __nv_bfloat16* __restrict__ norm_w, float eps) {
+__global__ void __launch_bounds__(GEMV_THREADS)
+gemv_kernel(const __grid_constant__ GemvParams p) {
   constexpr int VEC = INT8 ? 16 : 8;
   constexpr int COLS = 32 * VEC;
-  __shared__ float xs[MB][GEMV_KCHUNK];
-  __shared__ float buf[256 * VEC];  // cross-warp reduction: [warp][lane][VEC]
+  constexpr int ESZ = INT8 ? 1 : 2;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* tiles = smem;                                                  // STAGES x 16 KB
+  float* xs = reinterpret_cast<float*>(smem + GEMV_STAGES * GEMV_TILE_BYTES);  // [k][MB]
+  __shared__ uint64_t full[GEMV_STAGES], empty[GEMV_STAGES];
   __shared__ float s_inv[8];
+  __shared__ int s_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (prologue == PRO_RMSNORM) {
-    if (warp < M) {
-      const __nv_bfloat16* xr = X + static_cast<size_t>(warp) * ldx;
-      float ss = 0.f;
-      for (int c = lane * 8; c < K; c += 256) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
-        const float f[8] = {dbflo(raw.x), dbfhi(raw.x), dbflo(raw.y), dbfhi(raw.y),
-                            dbflo(raw.z), dbfhi(raw.z), dbflo(raw.w), dbfhi(raw.w)};
-#pragma unroll
-        for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      if (lane == 0) s_inv[warp] = rsqrtf(ss / static_cast<float>(K) + eps);
-    }
-    __syncthreads();
+  const int M = p.M, N = p.N, K = p.K;
+  const int col0 = blockIdx.x * COLS;
+  const int k0 = blockIdx.y * p.k_per_split;
+  const int k1 = min(K, k0 + p.k_per_split);
+  const int ntiles = (k1 - k0 + GEMV_KT - 1) / GEMV_KT;
+  const uint32_t row_bytes = static_cast<uint32_t>(min(COLS, N - col0)) * ESZ;  // multiple of 16
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < GEMV_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 8); }
+    fence_barrier_init();
   }
-  const int col = blockIdx.x * COLS + lane * VEC;
-  const int k0 = blockIdx.y * k_per_split;
-  const int k1 = min(K, k0 + k_per_split);
+  __syncthreads();
+
   float acc[MB][VEC];
 #pragma unroll
   for (int m = 0; m < MB; ++m)
 #pragma unroll
     for (int j = 0; j < VEC; ++j) acc[m][j] = 0.f;
 
-  for (int kc = k0; kc < k1; kc += GEMV_KCHUNK) {
-    const int kn = min(GEMV_KCHUNK, k1 - kc);
-    __syncthreads();
-    for (int i = threadIdx.x; i < MB * GEMV_KCHUNK; i += 256) {
-      const int m = i / GEMV_KCHUNK, kk = i - m * GEMV_KCHUNK;
+  if (warp == 8) {
+    // ------------------------------ producer ------------------------------
+    const uint8_t* wbase = static_cast<const uint8_t*>(p.W) + static_cast<size_t>(col0) * ESZ;
+    const size_t pitch = static_cast<size_t>(p.ldw) * ESZ;
+    for (int t = 0; t < ntiles; ++t) {
+      const int s = t % GEMV_STAGES;
+      if (t >= GEMV_STAGES && !mbar_wait(&empty[s], ((t / GEMV_STAGES) - 1) & 1, p.status, ST_TIMEOUT_EMPTY)) break;
+      const int r0 = k0 + t * GEMV_KT;
+      const int rows = min(GEMV_KT, k1 - r0);
+      if (lane == 0) mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(rows) * row_bytes);
+      __syncwarp();
+      if (lane < rows)
+        bulk_load_1d(tiles + s * GEMV_TILE_BYTES + lane * GEMV_ROW_BYTES, wbase + static_cast<size_t>(r0 + lane) * pitch,
+                     row_bytes, &full[s]);
+    }
+  } else {
+    // ------------------------------ consumers -----------------------------
+    if (p.prologue == PRO_RMSNORM) {
+      if (warp < M) {
+        const __nv_bfloat16* xr = p.X + static_cast<size_t>(warp) * p.ldx;
+        float ss = 0.f;
+        for (int c = lane * 8; c < K; c += 256) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
+          const float f[8] = {dbflo(raw.x), dbfhi(raw.x), dbflo(raw.y), dbfhi(raw.y),
+                              dbflo(raw.z), dbfhi(raw.z), dbflo(raw.w), dbfhi(raw.w)};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) s_inv[warp] = rsqrtf(ss / static_cast<float>(K) + p.eps);
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+    }
+    const int kn_all = k1 - k0;
+    for (int i = threadIdx.x; i < kn_all * MB; i += 256) {
+      const int kk = i / MB, m = i - kk * MB;
       float xv = 0.f;
-      if (m < M && kk < kn) {
-        const int k = kc + kk;
-        xv = __bfloat162float(X[static_cast<size_t>(m) * ldx + k]);
-        if (prologue == PRO_RMSNORM) {
-          xv = __bfloat162float(__float2bfloat16_rn(xv * s_inv[m] * __bfloat162float(norm_w[k])));
-        } else if (prologue == PRO_SWIGLU) {
-          const float u = __bfloat162float(X[static_cast<size_t>(m) * ldx + K + k]);
+      if (m < M) {
+        const int k = k0 + kk;
+        xv = __bfloat162float(p.X[static_cast<size_t>(m) * p.ldx + k]);
+        if (p.prologue == PRO_RMSNORM) {
+          xv = __bfloat162float(__float2bfloat16_rn(xv * s_inv[m] * __bfloat162float(p.norm_w[k])));
+        } else if (p.prologue == PRO_SWIGLU) {
+          const float u = __bfloat162float(p.X[static_cast<size_t>(m) * p.ldx + K + k]);
           xv = __bfloat162float(__float2bfloat16_rn(xv / (1.f + __expf(-xv)) * u));
         }
       }
-      xs[m][kk] = xv;
+      xs[i] = xv;
     }
-    __syncthreads();
-    if (col < N) {
-#pragma unroll 4
-      for (int kk = warp; kk < kn; kk += 8) {
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+
+    const bool active = lane * VEC < min(COLS, N - col0);
+    for (int t = 0; t < ntiles; ++t) {
+      const int s = t % GEMV_STAGES;
+      if (!mbar_wait(&full[s], (t / GEMV_STAGES) & 1, p.status, ST_TIMEOUT_FULL)) break;
+      const int rows = min(GEMV_KT, k1 - (k0 + t * GEMV_KT));
+      const uint8_t* tile = tiles + s * GEMV_TILE_BYTES;
+      uint4 raw[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = warp + i * 8;
+        raw[i] = (active && r < rows) ? *reinterpret_cast<const uint4*>(tile + r * GEMV_ROW_BYTES + lane * 16)
+                                      : make_uint4(0u, 0u, 0u, 0u);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = warp + i * 8;
+        if (r >= rows) continue;
         float w[VEC];
         if constexpr (INT8) {
-          const int4 raw = *reinterpret_cast<const int4*>(static_cast<const int8_t*>(Wv) +
-                                                          static_cast<size_t>(kc + kk) * ldw + col);
-          const int32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+          const uint32_t words[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
 #pragma unroll
           for (int q = 0; q < 4; ++q)
 #pragma unroll
-            for (int b = 0; b < 4; ++b) w[q * 4 + b] = static_cast<float>(static_cast<int8_t>(words[q] >> (8 * b)));
+            for (int b = 0; b < 4; ++b)
+              w[q * 4 + b] = static_cast<float>(static_cast<int8_t>(static_cast<int32_t>(words[q]) >> (8 * b)));
         } else {
-          const uint4 raw = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(Wv) +
-                                                            static_cast<size_t>(kc + kk) * ldw + col);
-          w[0] = dbflo(raw.x); w[1] = dbfhi(raw.x); w[2] = dbflo(raw.y); w[3] = dbfhi(raw.y);
-          w[4] = dbflo(raw.z); w[5] = dbfhi(raw.z); w[6] = dbflo(raw.w); w[7] = dbfhi(raw.w);
+          w[0] = dbflo(raw[i].x); w[1] = dbfhi(raw[i].x); w[2] = dbflo(raw[i].y); w[3] = dbfhi(raw[i].y);
+          w[4] = dbflo(raw[i].z); w[5] = dbfhi(raw[i].z); w[6] = dbflo(raw[i].w); w[7] = dbfhi(raw[i].w);
         }
+        const float* xr = xs + (t * GEMV_KT + r) * MB;
 #pragma unroll
         for (int m = 0; m < MB; ++m) {
-          const float xv = xs[m][kk];
+          const float xv = xr[m];
 #pragma unroll
           for (int j = 0; j < VEC; ++j) acc[m][j] += xv * w[j];
         }
       }
     }
   }
-  // cross-warp reduction in warp order through shared memory, one output row at a time
+  // every tile has been consumed (or a wait gave up and no copy is read any more): reuse the ring
+  // for the cross-warp reduction, one output row at a time, warps added in warp order
   __syncthreads();
+  float* buf = reinterpret_cast<float*>(tiles);  // [8 warps][32 lanes][VEC]
+  const bool direct = gridDim.y == 1;
+#pragma unroll
   for (int m = 0; m < MB; ++m) {
+    if (warp < 8) {
 #pragma unroll
-    for (int j = 0; j < VEC; ++j) buf[(warp * 32 + lane) * VEC + j] = acc[m][j];
+      for (int j = 0; j < VEC; ++j) buf[(warp * 32 + lane) * VEC + j] = acc[m][j];
+    }
     __syncthreads();
-    // thread t sums column t (and t+256 when VEC == 16) over the 8 warps
-    for (int c = threadIdx.x; c < COLS; c += 256) {
+    for (int c = threadIdx.x; c < COLS; c += GEMV_THREADS) {
       const int l = c / VEC, j = c - l * VEC;
-      float s = 0.f;
+      float sum = 0.f;
 #pragma unroll
-      for (int w8 = 0; w8 < 8; ++w8) s += buf[(w8 * 32 + l) * VEC + j];
-      const int gc = blockIdx.x * COLS + c;
-      if (m < M && gc < N) part[(static_cast<size_t>(blockIdx.y) * M + m) * N + gc] = s;
+      for (int w8 = 0; w8 < 8; ++w8) sum += buf[(w8 * 32 + l) * VEC + j];
+      const int gc = col0 + c;
+      if (m < M && gc < N) {
+        if (direct) {
+          if (p.scale) sum *= p.scale[gc];
+          if (p.R) sum += __bfloat162float(p.R[static_cast<size_t>(m) * p.ldr + gc]);
+          if (p.out) p.out[static_cast<size_t>(m) * p.ldo + gc] = __float2bfloat16_rn(sum);
+          if (p.out_f32) p.out_f32[static_cast<size_t>(m) * N + gc] = sum;
+        } else {
+          p.part[(static_cast<size_t>(blockIdx.y) * M + m) * N + gc] = sum;
+        }
+      }
     }
     __syncthreads();
   }
-}
-
-// out[m,n] = (sum_s part[s,m,n]) * scale[n] (+ residual) -> bf16 and/or fp32
-__global__ void gemv_finish_kernel(const float* __restrict__ part, int splits, int M, int N,
-                                   const float* __restrict__ scale, const __nv_bfloat16* __restrict__ R, int ldr,
-                                   __nv_bfloat16* __restrict__ out, int ldo, float* __restrict__ out_f32) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= M * N) return;
-  const int m = i / N, n = i - m * N;
-  float s = 0.f;
-  for (int k = 0; k < splits; ++k) s += part[(static_cast<size_t>(k) * M + m) * N + n];
-  if (scale) s *= scale[n];
-  if (R) s += __bfloat162float(R[static_cast<size_t>(m) * ldr + n]);
-  if (out) out[static_cast<size_t>(m) * ldo + n] = __float2bfloat16_rn(s);
-  if (out_f32) out_f32[static_cast<size_t>(m) * N + n] = s;
+  if (direct) return;
+  // split-K finish by the last CTA of this column block
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(p.counters + blockIdx.x, 1u);
+    s_last = (prev == gridDim.y - 1) ? 1 : 0;
+    if (s_last) p.counters[blockIdx.x] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const int ncols = min(COLS, N - col0);
+  for (int i = threadIdx.x; i < M * ncols; i += GEMV_THREADS) {
+    const int m = i / ncols, gc = col0 + (i - m * ncols);
+    float sum = 0.f;
+    for (int k = 0; k < static_cast<int>(gridDim.y); ++k)
+      sum += __ldcg(p.part + (static_cast<size_t>(k) * M + m) * N + gc);
+    if (p.scale) sum *= p.scale[gc];
+    if (p.R) sum += __bfloat162float(p.R[static_cast<size_t>(m) * p.ldr + gc]);
+    if (p.out) p.out[static_cast<size_t>(m) * p.ldo + gc] = __float2bfloat16_rn(sum);
+    if (p.out_f32) p.out_f32[static_cast<size_t>(m) * N + gc] = sum;
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -219,114 +318,269 @@ __global__ void rope_kv_append_kernel(__nv_bfloat16* __restrict__ qkv, int ld, i
 
 // ---------------------------------------------------------------------------
 // Split-KV GQA flash-decode. grid = (Hkv, B, n_splits); 128 threads = 4 warps.
-// A CTA serves the G = H/Hkv query heads of one kv head for one sequence over the kv positions of
-// its split; warp w owns query head w (G <= 4) ... for G > 4 heads are looped. Each warp keeps an
-// online softmax (m, l) and a dh-wide accumulator distributed over lanes (dh/32 values per lane).
-// K/V rows are read once per CTA into shared memory in tiles of TK positions.
-// Partials (m, l, o[dh]) per (b, h, split) are combined in split order by decode_combine_kernel.
+// A CTA serves the G = H/Hkv (<= 16) query heads of one kv head for one sequence over the kv
+// positions of its split. K/V rows stream through a two-stage ring of 64-position tiles
+// (cp.async, 16-byte padded rows so ldmatrix is conflict-free); warp w owns positions
+// [16w, 16w+16) of every tile and runs them as m16n8k16 tensor-core products: the G query heads are
+// the 16 rows of the A operand (unused rows zero), S = Q K^T in two 16x8 blocks, online softmax on
+// the accumulator fragments, P re-used in registers as the A operand of O += P V.
+// At the end the four warps' (m, l, O) are merged in warp order through shared memory; the split
+// partials are merged in split order by the LAST CTA of each (sequence, kv head) (a counter, no
+// data atomics), so there is one launch and the summation tree depends only on (L, n_splits).
 // ---------------------------------------------------------------------------
 constexpr int DEC_TK = 64;
 
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
+  const uint32_t n = valid ? 16u : 0u;  // src-size 0: the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+struct DecodeAttnParams {
+  const __nv_bfloat16* q; int ldq;
+  const __nv_bfloat16* pool;
+  const int* block_table; int max_blocks, page;
+  const int* seq_len;
+  int H, Hkv, n_splits;
+  float scale_log2;
+  float* part_o;    // [B, H, n_splits, dh]
+  float* part_ml;   // [B, H, n_splits, 2]
+  __nv_bfloat16* out; int ldo;
+  unsigned int* counters;  // [B * Hkv], zero between calls
+};
+
 template <int DH>
 __global__ void __launch_bounds__(128)
-decode_attn_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ pool,
-                   const int* __restrict__ block_table, int max_blocks, int page, const int* __restrict__ seq_len,
-                   int H, int Hkv, int n_splits, float scale_log2, float* __restrict__ part_o,
-                   float* __restrict__ part_ml) {
-  constexpr int VPL = DH / 32;  // accumulator values per lane
-  __shared__ __align__(16) __nv_bfloat16 sK[DEC_TK][DH];
-  __shared__ __align__(16) __nv_bfloat16 sV[DEC_TK][DH];
-  __shared__ float sP[4][DEC_TK];
+decode_attn_kernel(const __grid_constant__ DecodeAttnParams p) {
+  constexpr int ROWB = DH * 2 + 16;            // padded row pitch in bytes
+  constexpr int TILE_B = DEC_TK * ROWB;        // one K (or V) tile
+  constexpr int KS = DH / 16;                  // k-steps of Q K^T
+  constexpr int NB = DH / 8;                   // 8-wide output blocks of P V
+  constexpr int CH = DH / 8;                   // 16-byte chunks per row
+  extern __shared__ __align__(128) uint8_t smem[];   // [2 stages][K tile | V tile]
+  __shared__ int s_last;
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
-  const int G = H / Hkv;
+  const int H = p.H, Hkv = p.Hkv, G = H / Hkv, n_splits = p.n_splits;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int L = seq_len[b];
+  const int quad = lane >> 2, tq = lane & 3;
+  const int L = p.seq_len[b];
   const int per_split = ((L + n_splits - 1) / n_splits + DEC_TK - 1) / DEC_TK * DEC_TK;
   const int p0 = split * per_split;
   const int p1 = min(L, p0 + per_split);
-  for (int g0 = 0; g0 < G; g0 += 4) {
-    const int g = g0 + warp;
-    const int h = kvh * G + g;
-    float qv[VPL];
-    if (g < G) {
-#pragma unroll
-      for (int j = 0; j < VPL; ++j)
-        qv[j] = __bfloat162float(q[static_cast<size_t>(b) * ldq + h * DH + lane * VPL + j]) ;
-    }
-    float m = -1.0e30f, l = 0.f, o[VPL];
-#pragma unroll
-    for (int j = 0; j < VPL; ++j) o[j] = 0.f;
-    for (int t0 = p0; t0 < p1; t0 += DEC_TK) {
-      const int tn = min(DEC_TK, p1 - t0);
-      __syncthreads();
-      for (int i = threadIdx.x; i < tn * (DH / 8); i += 128) {
-        const int r = i / (DH / 8), c = (i - r * (DH / 8)) * 8;
-        const int pos = t0 + r;
-        const int blk = block_table[b * max_blocks + pos / page];
-        const size_t base = (((static_cast<size_t>(blk) * 2) * Hkv + kvh) * page + pos % page) * DH + c;
-        const size_t vofs = static_cast<size_t>(Hkv) * page * DH;
-        *reinterpret_cast<uint4*>(&sK[r][c]) = *reinterpret_cast<const uint4*>(pool + base);
-        *reinterpret_cast<uint4*>(&sV[r][c]) = *reinterpret_cast<const uint4*>(pool + base + vofs);
-      }
-      __syncthreads();
-      if (g < G) {
-        // scores: each lane takes positions lane, lane+32 ...; dot over dh needs all of q: use shuffles
-        float mx = -1.0e30f;
-        for (int r = 0; r < tn; ++r) {
-          float partial = 0.f;
-#pragma unroll
-          for (int j = 0; j < VPL; ++j) partial += qv[j] * __bfloat162float(sK[r][lane * VPL + j]);
-#pragma unroll
-          for (int off = 16; off > 0; off >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, off);
-          if (lane == 0) sP[warp][r] = partial * scale_log2;
-          mx = fmaxf(mx, partial * scale_log2);
-        }
-        __syncwarp();
-        const float m_new = fmaxf(m, mx);
-        const float alpha = exp2f(m - m_new);
-        float rowsum = 0.f;
-#pragma unroll
-        for (int j = 0; j < VPL; ++j) o[j] *= alpha;
-        for (int r = 0; r < tn; ++r) {
-          const float pr = exp2f(sP[warp][r] - m_new);
-          rowsum += pr;
-#pragma unroll
-          for (int j = 0; j < VPL; ++j) o[j] += pr * __bfloat162float(sV[r][lane * VPL + j]);
-        }
-        l = l * alpha + rowsum;
-        m = m_new;
-        __syncwarp();
-      }
-    }
-    if (g < G) {
-      const size_t idx = (static_cast<size_t>(b) * H + h) * n_splits + split;
-#pragma unroll
-      for (int j = 0; j < VPL; ++j) part_o[idx * DH + lane * VPL + j] = o[j];
-      if (lane == 0) {
-        part_ml[idx * 2] = m;
-        part_ml[idx * 2 + 1] = l;
-      }
-    }
-  }
-}
+  const int ntiles = p1 > p0 ? (p1 - p0 + DEC_TK - 1) / DEC_TK : 0;
+  const size_t vofs = static_cast<size_t>(Hkv) * p.page * DH;
 
-// Combine split partials in split order 0..S-1 and write bf16 output [B, H*dh].
-__global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                      int n_splits, int dh, __nv_bfloat16* __restrict__ out, int ldo, int H) {
-  const int bh = blockIdx.x;  // b*H + h
-  const int b = bh / H, h = bh - b * H;
-  const int d = threadIdx.x;
-  if (d >= dh) return;
-  float m = -1.0e30f;
-  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(static_cast<size_t>(bh) * n_splits + s) * 2]);
-  float l = 0.f, o = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const size_t idx = static_cast<size_t>(bh) * n_splits + s;
-    const float w = exp2f(part_ml[idx * 2] - m);
-    l += part_ml[idx * 2 + 1] * w;
-    o += part_o[idx * dh + d] * w;
+  auto load_tile = [&](int t, int stage) {
+    uint8_t* kt = smem + stage * 2 * TILE_B;
+    uint8_t* vt = kt + TILE_B;
+    const int t0 = p0 + t * DEC_TK;
+    for (int i = threadIdx.x; i < DEC_TK * CH; i += 128) {
+      const int r = i / CH, c = i - r * CH;
+      const int pos = t0 + r;
+      const bool valid = pos < p1;
+      const int pp = valid ? pos : p0;
+      const int blk = p.block_table[b * p.max_blocks + pp / p.page];
+      const __nv_bfloat16* src =
+          p.pool + (((static_cast<size_t>(blk) * 2) * Hkv + kvh) * p.page + pp % p.page) * DH + c * 8;
+      cp_async16(kt + r * ROWB + c * 16, src, valid);
+      cp_async16(vt + r * ROWB + c * 16, src + vofs, valid);
+    }
+  };
+
+  if (ntiles > 0) load_tile(0, 0);
+  cp_async_commit();
+
+  // Q as A fragments: row `quad` (and quad + 8) of the 16-row operand is query head kvh*G + row
+  uint32_t qa[KS][4];
+  {
+    const __nv_bfloat16* q_lo = p.q + static_cast<size_t>(b) * p.ldq + static_cast<size_t>(kvh * G + quad) * DH;
+    const __nv_bfloat16* q_hi = q_lo + 8 * DH;
+    const bool lo = quad < G, hi = quad + 8 < G;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const int c = ks * 16 + tq * 2;
+      qa[ks][0] = lo ? *reinterpret_cast<const uint32_t*>(q_lo + c) : 0u;
+      qa[ks][1] = hi ? *reinterpret_cast<const uint32_t*>(q_hi + c) : 0u;
+      qa[ks][2] = lo ? *reinterpret_cast<const uint32_t*>(q_lo + c + 8) : 0u;
+      qa[ks][3] = hi ? *reinterpret_cast<const uint32_t*>(q_hi + c + 8) : 0u;
+    }
   }
-  out[static_cast<size_t>(b) * ldo + h * dh + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+  float m_lo = -1.0e30f, m_hi = -1.0e30f, l_lo = 0.f, l_hi = 0.f;
+  float o[NB][4];
+#pragma unroll
+  for (int j = 0; j < NB; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+
+  for (int t = 0; t < ntiles; ++t) {
+    const int stage = t & 1;
+    if (t + 1 < ntiles) load_tile(t + 1, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const uint32_t kt = smem_u32(smem + stage * 2 * TILE_B);
+    const uint32_t vt = kt + TILE_B;
+    const int t0 = p0 + t * DEC_TK;
+    // ---- S = Q K^T for this warp's 16 positions (two 16x8 blocks) ----
+    float sacc[2][4];
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) { sacc[nb][0] = sacc[nb][1] = sacc[nb][2] = sacc[nb][3] = 0.f; }
+    {
+      const int mi = lane >> 3;  // matrix index of the x4 load: block = mi / 2, k half = mi % 2
+      const uint32_t base = kt + (warp * 16 + (mi >> 1) * 8 + (lane & 7)) * ROWB + (mi & 1) * 16;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        uint32_t r0, r1, r2, r3;
+        ldsm_x4(base + ks * 32, r0, r1, r2, r3);
+        mma_16816(sacc[0], qa[ks], r0, r1);
+        mma_16816(sacc[1], qa[ks], r2, r3);
+      }
+    }
+    // ---- online softmax on the fragments ----
+    float mx_lo = -1.0e30f, mx_hi = -1.0e30f;
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+      const int pos = t0 + warp * 16 + nb * 8 + tq * 2;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const bool ok = pos + e < p1;
+        sacc[nb][e] = ok ? sacc[nb][e] * p.scale_log2 : -1.0e30f;
+        sacc[nb][2 + e] = ok ? sacc[nb][2 + e] * p.scale_log2 : -1.0e30f;
+        mx_lo = fmaxf(mx_lo, sacc[nb][e]);
+        mx_hi = fmaxf(mx_hi, sacc[nb][2 + e]);
+      }
+    }
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+    const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+    const float al_lo = exp2f(m_lo - mn_lo), al_hi = exp2f(m_hi - mn_hi);
+    m_lo = mn_lo; m_hi = mn_hi;
+    uint32_t pa[4];
+    {
+      float pr[2][4];
+      float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          // a masked score stays at -1e30: exp2 of (-1e30 - m) is 0 unless the row is empty so far,
+          // in which case m is -1e30 too and the position must still contribute nothing
+          pr[nb][e] = sacc[nb][e] > -1.0e29f ? exp2f(sacc[nb][e] - mn_lo) : 0.f;
+          pr[nb][2 + e] = sacc[nb][2 + e] > -1.0e29f ? exp2f(sacc[nb][2 + e] - mn_hi) : 0.f;
+          sum_lo += pr[nb][e];
+          sum_hi += pr[nb][2 + e];
+        }
+      }
+      l_lo = l_lo * al_lo + sum_lo;
+      l_hi = l_hi * al_hi + sum_hi;
+      pa[0] = dpack(pr[0][0], pr[0][1]);
+      pa[1] = dpack(pr[0][2], pr[0][3]);
+      pa[2] = dpack(pr[1][0], pr[1][1]);
+      pa[3] = dpack(pr[1][2], pr[1][3]);
+    }
+#pragma unroll
+    for (int j = 0; j < NB; ++j) { o[j][0] *= al_lo; o[j][1] *= al_lo; o[j][2] *= al_hi; o[j][3] *= al_hi; }
+    // ---- O += P V over this warp's 16 positions ----
+    {
+      const int mi = lane >> 3;  // k half = mi % 2, output block offset = mi / 2
+      const uint32_t base = vt + (warp * 16 + (mi & 1) * 8 + (lane & 7)) * ROWB + (mi >> 1) * 16;
+#pragma unroll
+      for (int j = 0; j < NB; j += 2) {
+        uint32_t r0, r1, r2, r3;
+        ldsm_x4_t(base + j * 16, r0, r1, r2, r3);
+        mma_16816(o[j], pa, r0, r1);
+        mma_16816(o[j + 1], pa, r2, r3);
+      }
+    }
+    __syncthreads();   // the stage is refilled by the next iteration's load
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- merge the four warps in warp order ----
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  float* sm_o = reinterpret_cast<float*>(smem);           // [4 warps][16 rows][DH]
+  float* sm_ml = sm_o + 4 * 16 * DH;                      // [4 warps][16 rows][2]
+#pragma unroll
+  for (int j = 0; j < NB; ++j) {
+    float* r_lo = sm_o + (warp * 16 + quad) * DH + j * 8 + tq * 2;
+    float* r_hi = r_lo + 8 * DH;
+    r_lo[0] = o[j][0]; r_lo[1] = o[j][1];
+    r_hi[0] = o[j][2]; r_hi[1] = o[j][3];
+  }
+  if (tq == 0) {
+    sm_ml[(warp * 16 + quad) * 2] = m_lo;      sm_ml[(warp * 16 + quad) * 2 + 1] = l_lo;
+    sm_ml[(warp * 16 + quad + 8) * 2] = m_hi;  sm_ml[(warp * 16 + quad + 8) * 2 + 1] = l_hi;
+  }
+  __syncthreads();
+  const bool direct = n_splits == 1;
+  for (int i = threadIdx.x; i < G * DH; i += 128) {
+    const int g = i / DH, d = i - g * DH;
+    float mt = -1.0e30f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mt = fmaxf(mt, sm_ml[(w * 16 + g) * 2]);
+    float lt = 0.f, ot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float wgt = exp2f(sm_ml[(w * 16 + g) * 2] - mt);
+      lt += sm_ml[(w * 16 + g) * 2 + 1] * wgt;
+      ot += sm_o[(w * 16 + g) * DH + d] * wgt;
+    }
+    const int h = kvh * G + g;
+    if (direct) {
+      p.out[static_cast<size_t>(b) * p.ldo + h * DH + d] = __float2bfloat16_rn(lt > 0.f ? ot / lt : 0.f);
+    } else {
+      const size_t idx = (static_cast<size_t>(b) * H + h) * n_splits + split;
+      p.part_o[idx * DH + d] = ot;
+      if (d == 0) { p.part_ml[idx * 2] = mt; p.part_ml[idx * 2 + 1] = lt; }
+    }
+  }
+  if (direct) return;
+  // ---- the last CTA of this (sequence, kv head) merges the splits in split order ----
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned int* ctr = p.counters + b * Hkv + kvh;
+    const unsigned int prev = atomicAdd(ctr, 1u);
+    s_last = (prev == static_cast<unsigned int>(n_splits) - 1) ? 1 : 0;
+    if (s_last) *ctr = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int i = threadIdx.x; i < G * DH; i += 128) {
+    const int g = i / DH, d = i - g * DH;
+    const int h = kvh * G + g;
+    const size_t bh = static_cast<size_t>(b) * H + h;
+    float mt = -1.0e30f;
+    for (int sidx = 0; sidx < n_splits; ++sidx) mt = fmaxf(mt, __ldcg(p.part_ml + (bh * n_splits + sidx) * 2));
+    float lt = 0.f, ot = 0.f;
+    for (int sidx = 0; sidx < n_splits; ++sidx) {
+      const size_t idx = bh * n_splits + sidx;
+      const float wgt = exp2f(__ldcg(p.part_ml + idx * 2) - mt);
+      lt += __ldcg(p.part_ml + idx * 2 + 1) * wgt;
+      ot += __ldcg(p.part_o + idx * DH + d) * wgt;
+    }
+    p.out[static_cast<size_t>(b) * p.ldo + h * DH + d] = __float2bfloat16_rn(lt > 0.f ? ot / lt : 0.f);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -421,40 +675,63 @@ using namespace sb;
 #define STREAM static_cast<cudaStream_t>(stream)
 #define CHECK_LAUNCH() return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH
 
-template <bool INT8>
-static int launch_gemv(const void* X, int ldx, const void* W, int ldw, float* part, int M, int N, int K, int splits,
-                       int kps, int pro, const void* nw, float eps, cudaStream_t s) {
-  constexpr int COLS = INT8 ? 512 : 256;
-  dim3 grid((N + COLS - 1) / COLS, splits);
-  const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(X);
-  if (M <= 1) gemv_kernel<1, INT8><<<grid, 256, 0, s>>>(x, ldx, W, ldw, part, M, N, K, kps, pro, static_cast<const __nv_bfloat16*>(nw), eps);
-  else if (M <= 2) gemv_kernel<2, INT8><<<grid, 256, 0, s>>>(x, ldx, W, ldw, part, M, N, K, kps, pro, static_cast<const __nv_bfloat16*>(nw), eps);
-  else if (M <= 4) gemv_kernel<4, INT8><<<grid, 256, 0, s>>>(x, ldx, W, ldw, part, M, N, K, kps, pro, static_cast<const __nv_bfloat16*>(nw), eps);
-  else if (M <= 8) gemv_kernel<8, INT8><<<grid, 256, 0, s>>>(x, ldx, W, ldw, part, M, N, K, kps, pro, static_cast<const __nv_bfloat16*>(nw), eps);
-  else return SB_ERR_ARG;
+template <int MB, bool INT8>
+static int launch_gemv_mb(const GemvParams& p, dim3 grid, size_t smem, cudaStream_t s) {
+  auto kern = gemv_kernel<MB, INT8>;
+  static size_t attr = 0;
+  if (smem > attr) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+      return SB_ERR_LAUNCH;
+    attr = smem;
+  }
+  kern<<<grid, GEMV_THREADS, smem, s>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
 
-// Y[M,N] = X[M,K] * W[K,N] (* scale[n]) (+ R). M <= 8 per call (callers loop over row groups).
-// W bf16 (is_int8 == 0) or int8 with fp32 column scales. workspace: splits*M*N floats.
-// Returns the number of k-splits used through *splits_out when splits == 0 (auto).
+template <bool INT8>
+static int launch_gemv(const GemvParams& p, int splits, cudaStream_t s) {
+  constexpr int COLS = INT8 ? 512 : 256;
+  dim3 grid((p.N + COLS - 1) / COLS, splits);
+  const int mb = p.M <= 1 ? 1 : p.M <= 2 ? 2 : p.M <= 4 ? 4 : 8;
+  const size_t xs_bytes = static_cast<size_t>(p.k_per_split) * mb * sizeof(float);
+  if (xs_bytes > static_cast<size_t>(GEMV_MAX_XS_BYTES)) return SB_ERR_ARG;
+  const size_t smem = static_cast<size_t>(GEMV_STAGES) * GEMV_TILE_BYTES + xs_bytes;
+  switch (mb) {
+    case 1: return launch_gemv_mb<1, INT8>(p, grid, smem, s);
+    case 2: return launch_gemv_mb<2, INT8>(p, grid, smem, s);
+    case 4: return launch_gemv_mb<4, INT8>(p, grid, smem, s);
+    default: return launch_gemv_mb<8, INT8>(p, grid, smem, s);
+  }
+}
+
+// Y[M,N] = f(X)[M,K] * W[K,N] (* scale[n]) (+ R). M <= 8 per call (callers loop over row groups).
+// W bf16 (is_int8 == 0) or int8 with fp32 column scales; the weight row pitch and base must be
+// multiples of 16 bytes. workspace: 4096 counter words (zero before the first call, left zero by
+// every call) followed by splits*M*N floats. The staged slice of X, (K / splits) * {1,2,4,8} floats,
+// must fit in 64 KB: callers raise `splits` accordingly.
 // prologue: 0 none, 1 RMSNorm of X with gain norm_w (K must be a multiple of 8), 2 SwiGLU over a
 // fused [gate | up] X of row width 2K.
 extern "C" int sb_gemv(const void* X, int ldx, const void* W, int ldw, const float* scale, const void* R, int ldr,
                        void* out_bf16, int ldo, float* out_f32, int M, int N, int K, int is_int8, int splits,
-                       float* workspace, int prologue, const void* norm_w, float eps, void* stream) {
+                       float* workspace, int prologue, const void* norm_w, float eps, int* status, void* stream) {
   if (M <= 0 || M > 8 || N <= 0 || K <= 0 || (N & 7) || (is_int8 && (N & 15))) return SB_ERR_ARG;
   if (prologue < 0 || prologue > 2 || (prologue == 1 && (!norm_w || (K & 7) || (ldx & 7)))) return SB_ERR_ARG;
+  const int esz = is_int8 ? 1 : 2;
+  if ((reinterpret_cast<uintptr_t>(W) & 15) || ((static_cast<size_t>(ldw) * esz) & 15)) return SB_ERR_ALIGN;
   if (splits < 1) splits = 1;
   int kps = ((K + splits - 1) / splits + 7) / 8 * 8;
   splits = (K + kps - 1) / kps;
-  int rc = is_int8 ? launch_gemv<true>(X, ldx, W, ldw, workspace, M, N, K, splits, kps, prologue, norm_w, eps, STREAM)
-                   : launch_gemv<false>(X, ldx, W, ldw, workspace, M, N, K, splits, kps, prologue, norm_w, eps, STREAM);
-  if (rc) return rc;
-  gemv_finish_kernel<<<(M * N + 255) / 256, 256, 0, STREAM>>>(workspace, splits, M, N, scale,
-                                                             static_cast<const __nv_bfloat16*>(R), ldr,
-                                                             static_cast<__nv_bfloat16*>(out_bf16), ldo, out_f32);
-  CHECK_LAUNCH();
+  const int cols = is_int8 ? 512 : 256;
+  if ((N + cols - 1) / cols > 4096) return SB_ERR_ARG;
+  GemvParams p;
+  p.X = static_cast<const __nv_bfloat16*>(X); p.ldx = ldx; p.W = W; p.ldw = ldw; p.scale = is_int8 ? scale : nullptr;
+  p.R = static_cast<const __nv_bfloat16*>(R); p.ldr = ldr;
+  p.out = static_cast<__nv_bfloat16*>(out_bf16); p.ldo = ldo; p.out_f32 = out_f32;
+  p.counters = reinterpret_cast<unsigned int*>(workspace);
+  p.part = workspace + 4096;
+  p.M = M; p.N = N; p.K = K; p.k_per_split = kps; p.prologue = prologue;
+  p.norm_w = static_cast<const __nv_bfloat16*>(norm_w); p.eps = eps; p.status = status;
+  return is_int8 ? launch_gemv<true>(p, splits, STREAM) : launch_gemv<false>(p, splits, STREAM);
 }
 
 extern "C" int sb_kv_append(const void* qkv, int ld, int H, int Hkv, int dh, void* pool, const int* block_table,
@@ -478,26 +755,40 @@ extern "C" int sb_rope_kv_append(void* qkv, int ld, int H, int Hkv, int dh, cons
 
 // q: bf16 [B, ldq] (H*dh used, RoPE'd); out: bf16 [B, ldo]. part_o: B*H*n_splits*dh floats,
 // part_ml: B*H*n_splits*2 floats (scratch).
+template <int DH>
+static int launch_decode_attn(const DecodeAttnParams& p, dim3 grid, cudaStream_t s) {
+  constexpr int SMEM = 2 * 2 * DEC_TK * (DH * 2 + 16);   // also covers the merge buffers (4*16*(DH+2) floats)
+  static_assert(SMEM >= 4 * 16 * (DH + 2) * 4, "merge buffers must fit in the tile ring");
+  auto kern = decode_attn_kernel<DH>;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return SB_ERR_LAUNCH;
+    attr = true;
+  }
+  kern<<<grid, 128, SMEM, s>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+}
+
+// q: [B, >= H*dh] bf16 (RoPE'd), out: [B, H*dh] bf16. part_o: B*H*n_splits*dh floats, part_ml:
+// B*H*n_splits*2 floats, counters: B*Hkv words that are zero before the first call (every call leaves
+// them zero). H / Hkv <= 16, dh in {64, 128}.
 extern "C" int sb_decode_attention(const void* q, int ldq, const void* pool, const int* block_table, int max_blocks,
                                    int page, const int* seq_len, int B, int H, int Hkv, int dh, int n_splits,
-                                   float scale, float* part_o, float* part_ml, void* out, int ldo, void* stream) {
-  if (B <= 0 || H <= 0 || Hkv <= 0 || (H % Hkv) || (dh != 64 && dh != 128) || n_splits < 1) return SB_ERR_ARG;
+                                   float scale, float* part_o, float* part_ml, unsigned int* counters, void* out,
+                                   int ldo, void* stream) {
+  if (B <= 0 || H <= 0 || Hkv <= 0 || (H % Hkv) || H / Hkv > 16 || (dh != 64 && dh != 128) || n_splits < 1 ||
+      page < 1 || (ldq & 1))
+    return SB_ERR_ARG;
+  DecodeAttnParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q); p.ldq = ldq;
+  p.pool = static_cast<const __nv_bfloat16*>(pool);
+  p.block_table = block_table; p.max_blocks = max_blocks; p.page = page; p.seq_len = seq_len;
+  p.H = H; p.Hkv = Hkv; p.n_splits = n_splits;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.part_o = part_o; p.part_ml = part_ml;
+  p.out = static_cast<__nv_bfloat16*>(out); p.ldo = ldo; p.counters = counters;
   dim3 grid(Hkv, B, n_splits);
-  const float sl2 = scale * 1.4426950408889634f;
-  if (dh == 64)
-    decode_attn_kernel<64><<<grid, 128, 0, STREAM>>>(static_cast<const __nv_bfloat16*>(q), ldq,
-                                                     static_cast<const __nv_bfloat16*>(pool), block_table,
-                                                     max_blocks, page, seq_len, H, Hkv, n_splits, sl2, part_o,
-                                                     part_ml);
-  else
-    decode_attn_kernel<128><<<grid, 128, 0, STREAM>>>(static_cast<const __nv_bfloat16*>(q), ldq,
-                                                      static_cast<const __nv_bfloat16*>(pool), block_table,
-                                                      max_blocks, page, seq_len, H, Hkv, n_splits, sl2, part_o,
-                                                      part_ml);
-  if (cudaGetLastError() != cudaSuccess) return SB_ERR_LAUNCH;
-  decode_combine_kernel<<<B * H, dh, 0, STREAM>>>(part_o, part_ml, n_splits, dh, static_cast<__nv_bfloat16*>(out),
-                                                  ldo, H);
-  CHECK_LAUNCH();
+  return dh == 64 ? launch_decode_attn<64>(p, grid, STREAM) : launch_decode_attn<128>(p, grid, STREAM);
 }
 
 // logits: fp32 [rows, V]. pval/pidx: rows * ceil(V/4096) scratch. out_tokens: int64 [rows].

@@ -112,8 +112,22 @@ class InferenceEngine:
         self.max_batch, self.max_seq = max_batch, max_seq
         self.use_graph = use_graph and dev.type == "cuda"
 
-        def prep(w):
-            return D.quantize_per_channel(w.detach()) if quant == "int8" else w.detach()
+        self.H, self.Hkv = cfg.n_heads, cfg.n_kv_heads      # heads held by this rank
+        self._load_weights(model)
+        n_blocks = max_batch * ((max_seq + page - 1) // page)
+        self.cache = PagedKVCache(cfg.n_layers, n_blocks, self.Hkv, cfg.head_dim, page, max_batch, max_seq, dev)
+        self.cos, self.sin = ops.rope_table(max(cfg.max_seq_len, max_seq), cfg.head_dim, cfg.rope_theta, dev)
+        self.tokens = torch.zeros(max_batch, dtype=torch.int64, device=dev)     # device feedback buffer
+        self.logits = torch.zeros((max_batch, cfg.vocab_size), dtype=torch.float32, device=dev)
+        self._graph = None
+        self._graph_batch = None
+
+    def _prep(self, w):
+        w = w.detach()
+        return D.quantize_per_channel(w) if self.quant == "int8" else w
+
+    def _load_weights(self, model: GQADecoder):
+        prep = self._prep
         self.embed = model.embed.detach()
         self.layers = []
         for l in model.layers:
@@ -122,15 +136,17 @@ class InferenceEngine:
         self.rms_final = model.rms_final.detach()
         # LM head as [d, V] so the weight-streaming kernels read it row by row
         self.head_t = prep(model.head_weight().detach().t().contiguous())
-        n_blocks = max_batch * ((max_seq + page - 1) // page)
-        self.cache = PagedKVCache(cfg.n_layers, n_blocks, cfg.n_kv_heads, cfg.head_dim, page, max_batch, max_seq, dev)
-        self.cos, self.sin = ops.rope_table(max(cfg.max_seq_len, max_seq), cfg.head_dim, cfg.rope_theta, dev)
-        self.tokens = torch.zeros(max_batch, dtype=torch.int64, device=dev)     # device feedback buffer
-        self.logits = torch.zeros((max_batch, cfg.vocab_size), dtype=torch.float32, device=dev)
-        self._graph = None
-        self._graph_batch = None
 
     # ------------------------------------------------------------------ linear dispatch
+    def _proj_out(self, a, w, x, swiglu=False, site="attn"):
+        """x + f(a) @ w: the attention-output and MLP-down products (row-parallel under tensor
+        parallelism, where a subclass adds the all-reduce). ``swiglu``: a is a fused [gate | up]."""
+        if a.shape[0] <= 8:
+            return D.gemv(a, w, residual=x, swiglu=swiglu)
+        if swiglu:
+            a = ops.swiglu_fwd(a)
+        return self._linear(a, w, residual=x)
+
     def _linear(self, x, w, residual=None):
         M = x.shape[0]
         if M <= 8:
@@ -147,7 +163,7 @@ class InferenceEngine:
         token of every sequence in ``self.tokens`` and returns the last-position logits [B, V]."""
         cfg, cache = self.cfg, self.cache
         B, P = tokens.shape
-        H, Hkv, dh = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        H, Hkv, dh = self.H, self.Hkv, cfg.head_dim
         tok = tokens.to(self.dev)
         for b in range(B):
             if cache.owned[b]:
@@ -163,32 +179,38 @@ class InferenceEngine:
             ops.rope_(qkv, H + Hkv, dh, P, self.cos, self.sin)
             D.kv_append(qkv, H, Hkv, dh, cache.pools[li], cache.block_table, cache.page, seq_of, pos)
             a, _ = att.attention_fwd(qkv, B, P, H, Hkv, dh, causal=True, want_lse=False)
-            x = self._linear(a, l["wo"], residual=x)
+            x = self._proj_out(a, l["wo"], x, site="attn")
             h, _ = ops.rmsnorm_fwd(x, l["rms2"], cfg.eps, want_inv=False)
             gu = self._linear(h, l["wgu"])
-            x = self._linear(ops.swiglu_fwd(gu), l["wd"], residual=x)
+            x = self._proj_out(gu, l["wd"], x, swiglu=True, site="mlp")
         last = x.view(B, P, -1)[:, -1, :].contiguous()
-        hn, _ = ops.rmsnorm_fwd(last, self.rms_final, cfg.eps, want_inv=False)
         logits = self.logits[:B]
-        self._head(hn, logits)
+        self._head(last, logits, rms_weight=self.rms_final)
         D.argmax_rows(logits, out_tokens=self.tokens[:B])
         cache.seq_len[:B] = P
         return logits
 
-    def _head(self, hn, logits):
+    def _head(self, hn, logits, rms_weight=None):
+        """logits[M, V] (fp32) = norm(hn) @ head; ``rms_weight`` asks for the final RMSNorm to be
+        applied here (fused into the weight-streaming kernel when M <= 8)."""
+        self._head_local(hn, logits, rms_weight)
+
+    def _head_local(self, hn, logits, rms_weight=None):
         M = hn.shape[0]
         if M <= 8:
-            D.gemv(hn, self.head_t, out_f32=logits)
+            D.gemv(hn, self.head_t, out_f32=logits, rms_weight=rms_weight, eps=self.cfg.eps)
+            return
+        if rms_weight is not None:
+            hn, _ = ops.rmsnorm_fwd(hn, rms_weight, self.cfg.eps, want_inv=False)
+        if isinstance(self.head_t, D.QuantWeight):
+            logits.copy_(D.matmul_w8(hn, self.head_t).float())
         else:
-            if isinstance(self.head_t, D.QuantWeight):
-                logits.copy_(D.matmul_w8(hn, self.head_t).float())
-            else:
-                logits.copy_(ops.matmul_nn(hn, self.head_t).float())
+            logits.copy_(ops.matmul_nn(hn, self.head_t).float())
 
     # ------------------------------------------------------------------ decode
     def _decode_body(self, B: int, max_len: int):
         cfg, cache = self.cfg, self.cache
-        H, Hkv, dh = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        H, Hkv, dh = self.H, self.Hkv, cfg.head_dim
         seq_of = self._seq_of[:B]
         pos = cache.seq_len[:B]
         x = ops.embed_fwd(self.embed, self.tokens[:B])
@@ -203,19 +225,14 @@ class InferenceEngine:
                              seq_of, pos)
             a = D.decode_attention(qkv, cache.pools[li], cache.block_table, cache.page, self._len_plus1[:B], H, Hkv,
                                    dh, max_len=max_len)
-            x = self._linear(a, l["wo"], residual=x)
+            x = self._proj_out(a, l["wo"], x, site="attn")
             if small:
                 gu = D.gemv(x, l["wgu"], rms_weight=l["rms2"], eps=cfg.eps)
-                x = D.gemv(gu, l["wd"], residual=x, swiglu=True)
             else:
                 h, _ = ops.rmsnorm_fwd(x, l["rms2"], cfg.eps, want_inv=False)
                 gu = self._linear(h, l["wgu"])
-                x = self._linear(ops.swiglu_fwd(gu), l["wd"], residual=x)
-        if small:
-            D.gemv(x, self.head_t, out_f32=self.logits[:B], rms_weight=self.rms_final, eps=cfg.eps)
-            return
-        hn, _ = ops.rmsnorm_fwd(x, self.rms_final, cfg.eps, want_inv=False)
-        self._head(hn, self.logits[:B])
+            x = self._proj_out(gu, l["wd"], x, swiglu=True, site="mlp")
+        self._head(x, self.logits[:B], rms_weight=self.rms_final)
 
     def _step_eager(self, B, max_len, greedy=True):
         torch.add(self.cache.seq_len[:B], 1, out=self._len_plus1[:B])

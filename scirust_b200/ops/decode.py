@@ -12,10 +12,10 @@ from . import gemm as _g
 
 BF = torch.bfloat16
 vp, i32, f32 = _lib.vp, _lib.i32, _lib.f32
-_lib.register("sb_gemv", [vp, i32, vp, i32, vp, vp, i32, vp, i32, vp, i32, i32, i32, i32, i32, vp, i32, vp, f32, vp])
+_lib.register("sb_gemv", [vp, i32, vp, i32, vp, vp, i32, vp, i32, vp, i32, i32, i32, i32, i32, vp, i32, vp, f32, vp, vp])
 _lib.register("sb_rope_kv_append", [vp, i32, i32, i32, i32, vp, vp, vp, vp, i32, i32, vp, vp, i32, vp])
 _lib.register("sb_kv_append", [vp, i32, i32, i32, i32, vp, vp, i32, i32, vp, vp, i32, vp])
-_lib.register("sb_decode_attention", [vp, i32, vp, vp, i32, i32, vp, i32, i32, i32, i32, i32, f32, vp, vp, vp, i32,
+_lib.register("sb_decode_attention", [vp, i32, vp, vp, i32, i32, vp, i32, i32, i32, i32, i32, f32, vp, vp, vp, vp, i32,
                                       vp])
 _lib.register("sb_argmax", [vp, i32, i32, vp, vp, vp, vp, i32, i32, vp])
 _lib.register("sb_quantize_per_channel", [vp, i32, i32, i32, vp, vp, vp])
@@ -32,6 +32,19 @@ def _workspace(n, device):
     if w is None or w.numel() < n:
         w = torch.empty(max(n, 1 << 22), dtype=torch.float32, device=device)
         _ws[key] = w
+    return w
+
+
+_gemv_ws: dict = {}
+
+
+def _gemv_workspace(n, device):
+    """Workspace of the GEMV: 4096 counter words (kept zero by the kernel) + split partials."""
+    key = str(device)
+    w = _gemv_ws.get(key)
+    if w is None or w.numel() < n:
+        w = torch.zeros(max(n, 1 << 22), dtype=torch.float32, device=device)
+        _gemv_ws[key] = w
     return w
 
 
@@ -74,10 +87,14 @@ def quantize_per_channel(w: torch.Tensor) -> QuantWeight:
     return QuantWeight(q, scale)
 
 
-def _auto_splits(N, K, cols):
+def _auto_splits(N, K, cols, M=1):
+    """k-splits of the weight-streaming GEMV: about two CTAs per SM, and a staged slice of X
+    ((K / splits) rows x {1,2,4,8} floats) that fits the kernel's 64 KB."""
     ctas = (N + cols - 1) // cols
-    s = max(1, min(148 * 2 // max(ctas, 1), K // 256))
-    return s
+    s = max(1, min(148 * 2 // max(ctas, 1), K // 64))
+    mb = 1 if M <= 1 else 2 if M <= 2 else 4 if M <= 4 else 8
+    lim = 65536 // (4 * mb) // 8 * 8          # rows of X per split
+    return max(s, (K + lim - 1) // lim)
 
 
 def gemv(x, w, residual=None, out=None, out_f32=None, splits=None, rms_weight=None, eps=1e-5, swiglu=False):
@@ -110,8 +127,9 @@ def gemv(x, w, residual=None, out=None, out_f32=None, splits=None, rms_weight=No
     if out is None and out_f32 is None:
         out = torch.empty((M, N), dtype=BF, device=x.device)
     if splits is None:
-        splits = _auto_splits(N, K, 512 if quant else 256)
-    ws = _workspace(splits * min(M, 8) * N, x.device)
+        splits = _auto_splits(N, K, 512 if quant else 256, min(M, 8))
+    ws = _gemv_workspace(4096 + splits * min(M, 8) * N, x.device)
+    st = _lib.status_word(x.device)
     for m0 in range(0, M, 8):
         mb = min(8, M - m0)
         xs = x[m0:m0 + mb]
@@ -122,8 +140,8 @@ def gemv(x, w, residual=None, out=None, out_f32=None, splits=None, rms_weight=No
                   out[m0:m0 + mb].data_ptr() if out is not None else None, out.stride(0) if out is not None else 0,
                   out_f32[m0:m0 + mb].data_ptr() if out_f32 is not None else None, mb, N, K, int(quant), splits,
                   ws.data_ptr(), 1 if rms_weight is not None else (2 if swiglu else 0), _lib.ptr(rms_weight),
-                  float(eps), _lib.stream())
-        _g.launch_count += 2
+                  float(eps), st.data_ptr(), _lib.stream())
+        _g.launch_count += 1
     return out if out is not None else out_f32
 
 
@@ -206,15 +224,20 @@ def decode_attention(q, pool, block_table, page, seq_len, H, Hkv, dh, scale=None
         return decode_attention_ref(q, pool, block_table, page, seq_len, H, Hkv, dh, scale).to(BF)
     if n_splits is None:
         L = max_len if max_len is not None else block_table.shape[1] * page
-        n_splits = max(1, min(32, (148 * 2) // max(1, B * Hkv), (L + 255) // 256))
+        # about four 128-thread CTAs per SM, at least two 64-position tiles per split
+        n_splits = max(1, min(64, (148 * 4 + B * Hkv - 1) // max(1, B * Hkv), (L + 127) // 128))
     ws = _workspace(B * H * n_splits * (dh + 2), q.device)
+    ctr = _gemv_workspace(4096, q.device) if B * Hkv <= 2048 else None
+    if ctr is None:
+        raise ValueError("decode_attention: batch * kv_heads above 2048 is not supported")
     part_o = ws[:B * H * n_splits * dh]
     part_ml = ws[B * H * n_splits * dh:B * H * n_splits * (dh + 2)]
     out = torch.empty((B, H * dh), dtype=BF, device=q.device)
     _lib.call("sb_decode_attention", q.data_ptr(), q.stride(0), pool.data_ptr(), block_table.data_ptr(),
               block_table.shape[1], page, seq_len.data_ptr(), B, H, Hkv, dh, n_splits, float(scale),
-              part_o.data_ptr(), part_ml.data_ptr(), out.data_ptr(), out.stride(0), _lib.stream())
-    _g.launch_count += 2
+              part_o.data_ptr(), part_ml.data_ptr(), ctr[2048:].data_ptr(), out.data_ptr(), out.stride(0),
+              _lib.stream())
+    _g.launch_count += 1
     return out
 
 

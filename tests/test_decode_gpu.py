@@ -15,7 +15,8 @@ def _r(shape, seed, scale=0.5):
     return (torch.randn(shape, generator=g, device="cuda") * scale).to(BF)
 
 
-@pytest.mark.parametrize("M,K,N", [(1, 1024, 1536), (3, 4096, 512), (8, 2816, 1024), (13, 1024, 264)])
+@pytest.mark.parametrize("M,K,N", [(1, 1024, 1536), (3, 4096, 512), (8, 2816, 1024), (13, 1024, 264),
+                                   (8, 14336, 520), (2, 40, 8), (1, 4096, 6144)])
 def test_gemv_bf16(M, K, N):
     x, w, r = _r((M, K), 1), _r((K, N), 2), _r((M, N), 3)
     y = D.gemv(x, w, residual=r)
@@ -27,7 +28,7 @@ def test_gemv_bf16(M, K, N):
     assert (f - x.float() @ w.float()).abs().max().item() <= 2e-3 * max(1.0, ref.abs().max().item())
 
 
-@pytest.mark.parametrize("M,K,N", [(1, 1024, 1536), (5, 4096, 512), (8, 1024, 2048)])
+@pytest.mark.parametrize("M,K,N", [(1, 1024, 1536), (5, 4096, 512), (8, 1024, 2048), (7, 14336, 528)])
 def test_gemv_int8_and_quantize(M, K, N):
     x, w = _r((M, K), 4), _r((K, N), 5)
     qw = D.quantize_per_channel(w)
@@ -40,7 +41,7 @@ def test_gemv_int8_and_quantize(M, K, N):
     assert (qw.dequantize().float() - qw.q.float() * qw.scale[None, :]).abs().max().item() <= 1e-2
 
 
-@pytest.mark.parametrize("dh,H,Hkv", [(64, 16, 4), (128, 32, 8), (128, 4, 4)])
+@pytest.mark.parametrize("dh,H,Hkv", [(64, 16, 4), (128, 32, 8), (128, 4, 4), (64, 16, 2), (128, 16, 1)])
 def test_paged_decode_attention(dh, H, Hkv):
     B, page, max_seq = 3, 16, 700
     max_blocks = (max_seq + page - 1) // page
