@@ -24,13 +24,23 @@ __device__ __forceinline__ uint32_t dpack(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may start
+// while its predecessor in the stream is still draining. Work that does not depend on the
+// predecessor (weight prefetch, barrier set-up) runs at once; pdl_wait() returns when the predecessor
+// has completed and its writes are visible, and must precede every read of its results and every
+// global write. pdl_trigger() tells the scheduler that this CTA no longer minds dependents being
+// co-scheduled. Both are no-ops in a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------------------
 // GEMV / skinny GEMM: Y[M,N] = f(X)[M,K] * W[K,N] (* scale[n]) (+ R), M <= MB <= 8, W streamed once.
 // grid = (ceil(N / COLS), splits). A CTA owns COLS output columns (512 bytes of every weight row)
 // and the k range of its split.
-//   warp 8      producer: streams the CTA's weight slab through a ring of STAGES tiles of 32 rows
-//               with bulk asynchronous copies (one 512-byte copy per row, one mbarrier per tile);
-//               it starts at once, because the weights do not depend on the previous kernel's output
+//   warp 8      producer: streams the CTA's weight slab through a ring of STAGES tiles of 32 rows,
+//               one 16 KB TMA tile copy and one mbarrier per stage (copies of single 512-byte rows
+//               reached less than half of the memory bandwidth); it starts at once, because the
+//               weights do not depend on the previous kernel's output
 //   warps 0-7   stage f(X) for the CTA's k range in shared memory (optionally fused RMSNorm or
 //               SwiGLU), then consume tiles: warp w takes rows w, w+8, w+16, w+24 of every tile, a
 //               lane holds VEC consecutive columns
@@ -68,15 +78,9 @@ struct GemvParams {
   int* status;
 };
 
-__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
-
 template <int MB, bool INT8>
 __global__ void __launch_bounds__(GEMV_THREADS)
-gemv_kernel(const __grid_constant__ GemvParams p) {
+gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ GemvParams p) {
   constexpr int VEC = INT8 ? 16 : 8;
   constexpr int COLS = 32 * VEC;
   constexpr int ESZ = INT8 ? 1 : 2;
@@ -92,9 +96,9 @@ gemv_kernel(const __grid_constant__ GemvParams p) {
   const int k0 = blockIdx.y * p.k_per_split;
   const int k1 = min(K, k0 + p.k_per_split);
   const int ntiles = (k1 - k0 + GEMV_KT - 1) / GEMV_KT;
-  const uint32_t row_bytes = static_cast<uint32_t>(min(COLS, N - col0)) * ESZ;  // multiple of 16
 
   if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap_w);
     for (int s = 0; s < GEMV_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 8); }
     fence_barrier_init();
   }
@@ -108,32 +112,43 @@ gemv_kernel(const __grid_constant__ GemvParams p) {
 
   if (warp == 8) {
     // ------------------------------ producer ------------------------------
-    const uint8_t* wbase = static_cast<const uint8_t*>(p.W) + static_cast<size_t>(col0) * ESZ;
-    const size_t pitch = static_cast<size_t>(p.ldw) * ESZ;
+    // the map is over 16-bit words: x = byte offset of the CTA's columns / 2 (a multiple of 256)
+    const int x0 = col0 * ESZ / 2;
     for (int t = 0; t < ntiles; ++t) {
       const int s = t % GEMV_STAGES;
       if (t >= GEMV_STAGES && !mbar_wait(&empty[s], ((t / GEMV_STAGES) - 1) & 1, p.status, ST_TIMEOUT_EMPTY)) break;
-      const int r0 = k0 + t * GEMV_KT;
-      const int rows = min(GEMV_KT, k1 - r0);
-      if (lane == 0) mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(rows) * row_bytes);
+      if (lane == 0) {
+        // rows past K and columns past N arrive as zeros and still count towards the byte total
+        mbar_arrive_expect_tx(&full[s], GEMV_TILE_BYTES);
+        tma_load_2d(tiles + s * GEMV_TILE_BYTES, &tmap_w, &full[s], x0, k0 + t * GEMV_KT);
+      }
       __syncwarp();
-      if (lane < rows)
-        bulk_load_1d(tiles + s * GEMV_TILE_BYTES + lane * GEMV_ROW_BYTES, wbase + static_cast<size_t>(r0 + lane) * pitch,
-                     row_bytes, &full[s]);
     }
+    pdl_wait();   // this warp writes results below
   } else {
     // ------------------------------ consumers -----------------------------
+    pdl_wait();   // X, the residual and the workspace belong to the previous kernel until here
     if (p.prologue == PRO_RMSNORM) {
-      if (warp < M) {
-        const __nv_bfloat16* xr = p.X + static_cast<size_t>(warp) * p.ldx;
-        float ss = 0.f;
-        for (int c = lane * 8; c < K; c += 256) {
+      // row statistic with the association of rmsnorm_fwd_kernel: per lane, accumulator a takes the
+      // 16-byte chunks lane*8 + 256*(a + 8*j); here warp a computes accumulator a of every row
+      float* s_part = xs;   // [M][8 warps][32 lanes], overwritten by the staging below
+      for (int m = 0; m < M; ++m) {
+        const __nv_bfloat16* xr = p.X + static_cast<size_t>(m) * p.ldx;
+        float a = 0.f;
+        for (int c = lane * 8 + warp * 256; c < K; c += 8 * 256) {
           const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
           const float f[8] = {dbflo(raw.x), dbfhi(raw.x), dbflo(raw.y), dbfhi(raw.y),
                               dbflo(raw.z), dbfhi(raw.z), dbflo(raw.w), dbfhi(raw.w)};
 #pragma unroll
-          for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+          for (int j = 0; j < 8; ++j) a += f[j] * f[j];
         }
+        s_part[(m * 8 + warp) * 32 + lane] = a;
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (warp < M) {
+        float ss = s_part[(warp * 8) * 32 + lane];
+#pragma unroll
+        for (int a = 1; a < 8; ++a) ss += s_part[(warp * 8 + a) * 32 + lane];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
         if (lane == 0) s_inv[warp] = rsqrtf(ss / static_cast<float>(K) + p.eps);
@@ -202,6 +217,7 @@ gemv_kernel(const __grid_constant__ GemvParams p) {
   // every tile has been consumed (or a wait gave up and no copy is read any more): reuse the ring
   // for the cross-warp reduction, one output row at a time, warps added in warp order
   __syncthreads();
+  pdl_trigger();
   float* buf = reinterpret_cast<float*>(tiles);  // [8 warps][32 lanes][VEC]
   const bool direct = gridDim.y == 1;
 #pragma unroll
@@ -246,8 +262,16 @@ gemv_kernel(const __grid_constant__ GemvParams p) {
   for (int i = threadIdx.x; i < M * ncols; i += GEMV_THREADS) {
     const int m = i / ncols, gc = col0 + (i - m * ncols);
     float sum = 0.f;
-    for (int k = 0; k < static_cast<int>(gridDim.y); ++k)
-      sum += __ldcg(p.part + (static_cast<size_t>(k) * M + m) * N + gc);
+    const float* pp = p.part + static_cast<size_t>(m) * N + gc;
+    const size_t pstride = static_cast<size_t>(M) * N;
+    const int ns = static_cast<int>(gridDim.y);
+    for (int k = 0; k < ns; k += 8) {   // eight loads in flight, added in split order
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = (k + u < ns) ? __ldcg(pp + (k + u) * pstride) : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) if (k + u < ns) sum += v[u];
+    }
     if (p.scale) sum *= p.scale[gc];
     if (p.R) sum += __bfloat162float(p.R[static_cast<size_t>(m) * p.ldr + gc]);
     if (p.out) p.out[static_cast<size_t>(m) * p.ldo + gc] = __float2bfloat16_rn(sum);
@@ -289,30 +313,30 @@ __global__ void rope_kv_append_kernel(__nv_bfloat16* __restrict__ qkv, int ld, i
                                       __nv_bfloat16* __restrict__ pool, const int* __restrict__ block_table,
                                       int max_blocks, int page, const int* __restrict__ seq_of,
                                       const int* __restrict__ pos, int n_tok) {
-  const int t = blockIdx.x;
+  // grid = (n_tok, H + 2*Hkv): one CTA per head of one token, one thread per (even, odd) pair
+  const int t = blockIdx.x, head = blockIdx.y;
   if (t >= n_tok) return;
+  pdl_wait();
   const int b = seq_of[t], p = pos[t];
   const int half = dh >> 1;
-  __nv_bfloat16* row = qkv + static_cast<size_t>(t) * ld;
-  const int n_pairs = (H + Hkv) * half;
-  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
-    const int head = i / half, pr = i - head * half;
+  const int pr = threadIdx.x;
+  if (pr >= half) return;
+  uint32_t* e = reinterpret_cast<uint32_t*>(qkv + static_cast<size_t>(t) * ld + head * dh) + pr;
+  uint32_t v = *e;
+  if (head < H + Hkv) {   // query and key heads rotate
     const float c = cos_t[static_cast<size_t>(p) * half + pr], s = sin_t[static_cast<size_t>(p) * half + pr];
-    __nv_bfloat16* e = row + head * dh + 2 * pr;
-    const float x0 = __bfloat162float(e[0]), x1 = __bfloat162float(e[1]);
-    e[0] = __float2bfloat16_rn(x0 * c - x1 * s);
-    e[1] = __float2bfloat16_rn(x0 * s + x1 * c);
+    const float x0 = dbflo(v), x1 = dbfhi(v);
+    v = dpack(x0 * c - x1 * s, x0 * s + x1 * c);
+    *e = v;
   }
-  __syncthreads();
-  const int blk = block_table[b * max_blocks + p / page];
-  const int slot = p % page;
-  const int per = Hkv * dh / 8;
-  const __nv_bfloat16* src = row + H * dh;
-  for (int i = threadIdx.x; i < 2 * per; i += blockDim.x) {
-    const int kv = i / per, r = i - kv * per;
-    const int h = (r * 8) / dh, d = (r * 8) - h * dh;
-    const uint4 v = *reinterpret_cast<const uint4*>(src + kv * Hkv * dh + r * 8);
-    *reinterpret_cast<uint4*>(pool + ((((static_cast<size_t>(blk) * 2 + kv) * Hkv + h) * page + slot) * dh + d)) = v;
+  if (head >= H) {        // key and value heads go to the cache
+    const int kv = head >= H + Hkv ? 1 : 0;
+    const int h = head - H - kv * Hkv;
+    const int blk = block_table[b * max_blocks + p / page];
+    const int slot = p % page;
+    uint32_t* dst = reinterpret_cast<uint32_t*>(
+        pool + ((((static_cast<size_t>(blk) * 2 + kv) * Hkv + h) * page + slot) * dh)) + pr;
+    *dst = v;
   }
 }
 
@@ -378,6 +402,7 @@ decode_attn_kernel(const __grid_constant__ DecodeAttnParams p) {
   const int H = p.H, Hkv = p.Hkv, G = H / Hkv, n_splits = p.n_splits;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int quad = lane >> 2, tq = lane & 3;
+  pdl_wait();
   const int L = p.seq_len[b];
   const int per_split = ((L + n_splits - 1) / n_splits + DEC_TK - 1) / DEC_TK * DEC_TK;
   const int p0 = split * per_split;
@@ -511,6 +536,7 @@ decode_attn_kernel(const __grid_constant__ DecodeAttnParams p) {
   }
   cp_async_wait<0>();
   __syncthreads();
+  pdl_trigger();
 
   // ---- merge the four warps in warp order ----
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
@@ -570,14 +596,34 @@ decode_attn_kernel(const __grid_constant__ DecodeAttnParams p) {
     const int g = i / DH, d = i - g * DH;
     const int h = kvh * G + g;
     const size_t bh = static_cast<size_t>(b) * H + h;
+    const float* ml = p.part_ml + bh * n_splits * 2;
+    const float* po = p.part_o + bh * n_splits * DH + d;
     float mt = -1.0e30f;
-    for (int sidx = 0; sidx < n_splits; ++sidx) mt = fmaxf(mt, __ldcg(p.part_ml + (bh * n_splits + sidx) * 2));
+    for (int s0 = 0; s0 < n_splits; s0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = (s0 + u < n_splits) ? __ldcg(ml + (s0 + u) * 2) : -1.0e30f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) mt = fmaxf(mt, v[u]);
+    }
     float lt = 0.f, ot = 0.f;
-    for (int sidx = 0; sidx < n_splits; ++sidx) {
-      const size_t idx = bh * n_splits + sidx;
-      const float wgt = exp2f(__ldcg(p.part_ml + idx * 2) - mt);
-      lt += __ldcg(p.part_ml + idx * 2 + 1) * wgt;
-      ot += __ldcg(p.part_o + idx * DH + d) * wgt;
+    for (int s0 = 0; s0 < n_splits; s0 += 8) {   // eight splits' loads in flight, added in split order
+      float vm[8], vl[8], vo[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const bool ok = s0 + u < n_splits;
+        vm[u] = ok ? __ldcg(ml + (s0 + u) * 2) : -1.0e30f;
+        vl[u] = ok ? __ldcg(ml + (s0 + u) * 2 + 1) : 0.f;
+        vo[u] = ok ? __ldcg(po + static_cast<size_t>(s0 + u) * DH) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (s0 + u < n_splits) {
+          const float wgt = exp2f(vm[u] - mt);
+          lt += vl[u] * wgt;
+          ot += vo[u] * wgt;
+        }
+      }
     }
     p.out[static_cast<size_t>(b) * p.ldo + h * DH + d] = __float2bfloat16_rn(lt > 0.f ? ot / lt : 0.f);
   }
@@ -675,8 +721,33 @@ using namespace sb;
 #define STREAM static_cast<cudaStream_t>(stream)
 #define CHECK_LAUNCH() return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH
 
+static bool g_pdl = false;
+
+// Launch with (or without) the programmatic-stream-serialization attribute.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_dep(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                              Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = g_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+// Switches programmatic dependent launch of the decode-path kernels (GEMV, RoPE+append,
+// flash-decode) on or off for this process; off by default.
+extern "C" int sb_set_pdl(int on) { g_pdl = on != 0; return 0; }
+
+namespace sb {
+int make_tmap_2d_u16_plain(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch_bytes,
+                           uint32_t box_inner, uint32_t box_outer);   // gemm_tcgen05.cu
+}
+
 template <int MB, bool INT8>
-static int launch_gemv_mb(const GemvParams& p, dim3 grid, size_t smem, cudaStream_t s) {
+static int launch_gemv_mb(const CUtensorMap& tm, const GemvParams& p, dim3 grid, size_t smem, cudaStream_t s) {
   auto kern = gemv_kernel<MB, INT8>;
   static size_t attr = 0;
   if (smem > attr) {
@@ -684,8 +755,7 @@ static int launch_gemv_mb(const GemvParams& p, dim3 grid, size_t smem, cudaStrea
       return SB_ERR_LAUNCH;
     attr = smem;
   }
-  kern<<<grid, GEMV_THREADS, smem, s>>>(p);
-  return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+  return launch_dep(kern, grid, dim3(GEMV_THREADS), smem, s, tm, p) == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
 
 template <bool INT8>
@@ -695,12 +765,19 @@ static int launch_gemv(const GemvParams& p, int splits, cudaStream_t s) {
   const int mb = p.M <= 1 ? 1 : p.M <= 2 ? 2 : p.M <= 4 ? 4 : 8;
   const size_t xs_bytes = static_cast<size_t>(p.k_per_split) * mb * sizeof(float);
   if (xs_bytes > static_cast<size_t>(GEMV_MAX_XS_BYTES)) return SB_ERR_ARG;
-  const size_t smem = static_cast<size_t>(GEMV_STAGES) * GEMV_TILE_BYTES + xs_bytes;
+  // the RMSNorm prologue borrows the X staging area for mb * 8 * 32 partial sums
+  const size_t smem = static_cast<size_t>(GEMV_STAGES) * GEMV_TILE_BYTES +
+                      (xs_bytes > static_cast<size_t>(mb) * 1024 ? xs_bytes : static_cast<size_t>(mb) * 1024);
+  constexpr int ESZ = INT8 ? 1 : 2;
+  CUtensorMap tm;
+  const int rc = make_tmap_2d_u16_plain(&tm, p.W, static_cast<uint64_t>(p.N) * ESZ / 2, p.K,
+                                        static_cast<uint64_t>(p.ldw) * ESZ, GEMV_ROW_BYTES / 2, GEMV_KT);
+  if (rc) return rc;
   switch (mb) {
-    case 1: return launch_gemv_mb<1, INT8>(p, grid, smem, s);
-    case 2: return launch_gemv_mb<2, INT8>(p, grid, smem, s);
-    case 4: return launch_gemv_mb<4, INT8>(p, grid, smem, s);
-    default: return launch_gemv_mb<8, INT8>(p, grid, smem, s);
+    case 1: return launch_gemv_mb<1, INT8>(tm, p, grid, smem, s);
+    case 2: return launch_gemv_mb<2, INT8>(tm, p, grid, smem, s);
+    case 4: return launch_gemv_mb<4, INT8>(tm, p, grid, smem, s);
+    default: return launch_gemv_mb<8, INT8>(tm, p, grid, smem, s);
   }
 }
 
@@ -747,10 +824,9 @@ extern "C" int sb_rope_kv_append(void* qkv, int ld, int H, int Hkv, int dh, cons
                                  void* pool, const int* block_table, int max_blocks, int page, const int* seq_of,
                                  const int* pos, int n_tok, void* stream) {
   if (n_tok <= 0 || (dh & 7)) return SB_ERR_ARG;
-  rope_kv_append_kernel<<<n_tok, 256, 0, STREAM>>>(static_cast<__nv_bfloat16*>(qkv), ld, H, Hkv, dh, cos_t, sin_t,
-                                                   static_cast<__nv_bfloat16*>(pool), block_table, max_blocks, page,
-                                                   seq_of, pos, n_tok);
-  CHECK_LAUNCH();
+  return launch_dep(rope_kv_append_kernel, dim3(n_tok, H + 2 * Hkv), dim3(dh / 2), 0, STREAM, static_cast<__nv_bfloat16*>(qkv), ld, H,
+                    Hkv, dh, cos_t, sin_t, static_cast<__nv_bfloat16*>(pool), block_table, max_blocks, page, seq_of,
+                    pos, n_tok) == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
 
 // q: bf16 [B, ldq] (H*dh used, RoPE'd); out: bf16 [B, ldo]. part_o: B*H*n_splits*dh floats,
@@ -765,8 +841,7 @@ static int launch_decode_attn(const DecodeAttnParams& p, dim3 grid, cudaStream_t
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return SB_ERR_LAUNCH;
     attr = true;
   }
-  kern<<<grid, 128, SMEM, s>>>(p);
-  return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+  return launch_dep(kern, grid, dim3(128), SMEM, s, p) == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
 
 // q: [B, >= H*dh] bf16 (RoPE'd), out: [B, H*dh] bf16. part_o: B*H*n_splits*dh floats, part_ml:

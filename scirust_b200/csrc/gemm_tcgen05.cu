@@ -310,6 +310,24 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64
   return r == CUDA_SUCCESS ? 0 : SB_ERR_DRIVER;
 }
 
+// 2-D tensor map over 16-bit words without swizzle (row-major copy of a box into shared memory).
+// Used by the weight-streaming kernels: `inner` 2-byte words are contiguous, `pitch_bytes` is the row
+// pitch. Out-of-range parts of a box are filled with zeros.
+int make_tmap_2d_u16_plain(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch_bytes,
+                           uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return SB_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (pitch_bytes & 15)) return SB_ERR_ALIGN;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : SB_ERR_DRIVER;
+}
+
 static int g_num_sms = 0;
 int num_sms() {
   if (!g_num_sms) {

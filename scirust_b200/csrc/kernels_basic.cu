@@ -51,13 +51,27 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
   const __nv_bfloat16* xr = x + static_cast<size_t>(row) * ldx;
-  float ss = 0.f;
-  for (int c = lane * 8; c < cols; c += 256) {
-    float f[8];
-    unpack8(*reinterpret_cast<const uint4*>(xr + c), f);
+  // eight interleaved accumulators (iteration i of the lane goes to accumulator i % 8), added in
+  // index order: more loads in flight, and the same association as the fused prologue of the decode
+  // GEMV, which spreads the eight accumulators over eight warps
+  float acc[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+  for (int a = 0; a < 8; ++a) acc[a] = 0.f;
+  for (int c0 = lane * 8; c0 < cols; c0 += 8 * 256) {
+#pragma unroll
+    for (int a = 0; a < 8; ++a) {
+      const int c = c0 + a * 256;
+      if (c < cols) {
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(xr + c), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[a] += f[j] * f[j];
+      }
+    }
   }
+  float ss = acc[0];
+#pragma unroll
+  for (int a = 1; a < 8; ++a) ss += acc[a];
   ss = warp_sum(ss);
   const float inv = rsqrtf(ss / static_cast<float>(cols) + eps);
   if (inv_rms && lane == 0) inv_rms[row] = inv;

@@ -20,7 +20,8 @@ import math
 import torch
 
 from .. import ops
-from ..generate import SamplerRng, SamplingParams, sample_row
+from ..generate import SamplingParams
+from ..ops.sampling import DeviceSampler
 from ..ops import _lib, attention as att, decode as D
 from .sciagent import BF, GQADecoder, SciAgentConfig
 
@@ -152,7 +153,11 @@ class InferenceEngine:
         if M <= 8:
             return D.gemv(x, w, residual=residual)
         if isinstance(w, D.QuantWeight):
-            if w.q.shape[1] % 16 == 0:
+            # few rows: the product is bound by the weight bytes, so the int8 matrix is streamed and
+            # dequantised inside the GEMM; many rows (prefill): it is bound by the tensor cores, so the
+            # layer's weights are expanded to bf16 once (a few percent of the GEMM's time) and the
+            # plain bf16 kernel runs at full rate
+            if M < 1024 and w.q.shape[1] % 16 == 0:
                 return D.matmul_w8(x, w, residual=residual)
             w = w.dequantize()
         return ops.matmul_nn(x, w, residual=residual)
@@ -234,16 +239,22 @@ class InferenceEngine:
             x = self._proj_out(gu, l["wd"], x, swiglu=True, site="mlp")
         self._head(x, self.logits[:B], rms_weight=self.rms_final)
 
-    def _step_eager(self, B, max_len, greedy=True):
+    def _step_eager(self, B, max_len, sampler=None):
         torch.add(self.cache.seq_len[:B], 1, out=self._len_plus1[:B])
-        self._decode_body(B, max_len)
-        if greedy:
+        with D.dependent_launch(self.dev.type == "cuda"):
+            self._decode_body(B, max_len)
+        if sampler is None:
             D.argmax_rows(self.logits[:B], out_tokens=self.tokens[:B], generated=self._generated, step=0)
+        else:
+            sampler.sample(self.logits[:B], out_tokens=self.tokens[:B])
+            sampler.push(self.tokens[:B])
         self.cache.seq_len[:B] += 1
 
     def generate(self, prompts: torch.Tensor, max_new: int, params: SamplingParams | None = None, seed: int = 0,
                  stop_on_zero: bool = False):
-        """Greedy (device feedback, graph replay) or sampled generation. Returns int64 [B, max_new]."""
+        """Greedy or sampled generation; the token never leaves the device between steps (arg-max or
+        the device sampler write the feedback buffer) and the step is replayed from a CUDA graph.
+        Sequence ``b`` samples from the stream seeded with ``seed + b``. Returns int64 [B, max_new]."""
         params = params or SamplingParams()
         B, P = prompts.shape
         if B > self.max_batch or P + max_new > self.max_seq:
@@ -260,24 +271,25 @@ class InferenceEngine:
         self._seq_of = torch.arange(self.max_batch, dtype=torch.int32, device=self.dev)
         self._len_plus1 = torch.zeros(self.max_batch, dtype=torch.int32, device=self.dev)
         self._generated = None
-        rngs = [SamplerRng(seed + b) for b in range(B)]
-        history = [list(map(int, prompts[b].tolist())) for b in range(B)]
+        sampler = None
         if not greedy:
-            first = [sample_row(logits[b], params, history[b], rngs[b]) for b in range(B)]
-            self.tokens[:B] = torch.tensor(first, dtype=torch.int64, device=self.dev)
+            sampler = DeviceSampler(params, B, self.cfg.vocab_size, [seed + b for b in range(B)], self.dev,
+                                    history_len=P + max_new)
+            sampler.set_history(prompts)
+            sampler.sample(logits[:B], out_tokens=self.tokens[:B])
+            sampler.push(self.tokens[:B])
         out[:, 0] = self.tokens[:B]
         max_len = P + max_new
-        if greedy and self.use_graph and max_new > 2:
-            self._generated = None
+        if self.use_graph and max_new > 2:
             # one eager step warms every workspace, then the step is captured once and replayed
-            self._step_eager(B, max_len)
+            self._step_eager(B, max_len, sampler)
             out[:, 1] = self.tokens[:B]
             g = torch.cuda.CUDAGraph()
             s = torch.cuda.Stream(device=self.dev)
             s.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(s):
                 with torch.cuda.graph(g, stream=s):
-                    self._step_eager(B, max_len)
+                    self._step_eager(B, max_len, sampler)
             torch.cuda.current_stream().wait_stream(s)
             # capture only records; run the recorded step for positions 2 .. max_new-1
             for i in range(2, max_new):
@@ -285,13 +297,7 @@ class InferenceEngine:
                 out[:, i] = self.tokens[:B]
         else:
             for i in range(1, max_new):
-                self._step_eager(B, max_len, greedy=greedy)
-                if not greedy:
-                    lg = self.logits[:B].cpu()
-                    for b in range(B):
-                        history[b].append(int(out[b, i - 1]))
-                    nxt = [sample_row(lg[b], params, history[b], rngs[b]) for b in range(B)]
-                    self.tokens[:B] = torch.tensor(nxt, dtype=torch.int64, device=self.dev)
+                self._step_eager(B, max_len, sampler)
                 out[:, i] = self.tokens[:B]
         _lib.check_status(self.dev) if self.dev.type == "cuda" else None
         return out

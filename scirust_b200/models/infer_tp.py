@@ -129,7 +129,7 @@ class TPInferenceEngine(InferenceEngine):
             out.copy_(self._linear(a, w))
             return out
         if isinstance(w, D.QuantWeight):
-            if w.q.shape[1] % 16 == 0:
+            if a.shape[0] < 1024 and w.q.shape[1] % 16 == 0:
                 return D.matmul_w8(a, w, out=out)
             w = w.dequantize()
         return ops.matmul_nn(a, w, out=out)

@@ -4,6 +4,7 @@ quantisation. CPU tensors take the fp32 PyTorch statement of the same arithmetic
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -33,6 +34,29 @@ def _workspace(n, device):
         w = torch.empty(max(n, 1 << 22), dtype=torch.float32, device=device)
         _ws[key] = w
     return w
+
+
+_lib.register("sb_set_pdl", [i32])
+
+
+class dependent_launch:
+    """Context manager: launch the decode-path kernels (GEMV, RoPE+append, flash-decode) inside the
+    block with programmatic dependent launch, so each kernel's weight prefetch overlaps the tail of
+    its predecessor. Only for call chains whose weights are not produced by the preceding kernel.
+    ``SB_PDL=0`` in the environment disables it."""
+
+    def __init__(self, enabled: bool = True):
+        self.enabled = enabled and os.environ.get("SB_PDL", "1") != "0"
+
+    def __enter__(self):
+        if self.enabled:
+            _lib.call("sb_set_pdl", 1)
+        return self
+
+    def __exit__(self, *exc):
+        if self.enabled:
+            _lib.call("sb_set_pdl", 0)
+        return False
 
 
 _gemv_ws: dict = {}

@@ -174,3 +174,13 @@ def test_gloo_ranks_rank_that_raises_fails_the_job():
                          env=dict(os.environ, PYTHONPATH=ROOT, FAIL_RANK="1"))
     assert bad.returncode != 0
     assert "PEER_LOST" in bad.stdout or "SECOND_OK" not in bad.stdout
+
+
+@pytest.mark.parametrize("world,kv", [(2, 4), (4, 1)])
+def test_tp_inference_engine_on_gloo_ranks(world, kv):
+    """Tensor-parallel sharding, row-parallel reductions and the vocabulary-parallel head, on CPU ranks."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29650 + world), os.path.join(ROOT, "tests", "mp", "mp_tp_infer.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600,
+                       env=dict(os.environ, PYTHONPATH=ROOT, SB_TP_KV=str(kv), SB_TEST_DEVICE="cpu"))
+    assert r.returncode == 0 and "TP_INFER_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]

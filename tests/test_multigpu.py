@@ -13,14 +13,15 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(script: str, nproc: int, port: int, timeout: int = 300):
+def _run(script: str, nproc: int, port: int, timeout: int = 300, extra_env=None, tag=""):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    env.update(extra_env or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "mp", script)]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
     log_dir = os.environ.get("SB_TEST_LOG_DIR")
     if log_dir:
-        with open(os.path.join(log_dir, script + ".log"), "w") as f:
+        with open(os.path.join(log_dir, script + tag + ".log"), "w") as f:
             f.write(r.stdout + "\n---- stderr ----\n" + r.stderr)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     return r.stdout
@@ -59,3 +60,18 @@ def test_dp_cnn_fused_allreduce_with_overlap():
     _need(2)
     out = _run("mp_dp_cnn.py", 2, 29615)
     assert "DP_CNN_OK" in out
+
+
+@pytest.mark.parametrize("backend,quant", [("fused", ""), ("nccl", ""), ("fused", "int8")])
+def test_tp_inference_matches_single_gpu(backend, quant):
+    _need(2)
+    out = _run("mp_tp_infer.py", 2, 29616, extra_env={"SB_TEST_DEVICE": "cuda", "SB_TP_BACKEND": backend,
+                                                      "SB_TP_QUANT": quant}, tag=f"_{backend}_{quant}")
+    assert "TP_INFER_OK" in out and f"backend={backend}" in out
+
+
+def test_tp_inference_batch16_and_replicated_kv_heads():
+    _need(2)
+    out = _run("mp_tp_infer.py", 2, 29617, extra_env={"SB_TEST_DEVICE": "cuda", "SB_TP_BATCH": "16", "SB_TP_KV": "1"},
+               tag="_b16")
+    assert "TP_INFER_OK" in out
