@@ -1,0 +1,258 @@
+"""Layers, losses, schedules, N-D optimizers, the model zoo and the telemetry helpers on CPU."""
+import math
+import os
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from scirust_b200 import nn as snn
+from scirust_b200.autodiff import nd_optim as O
+from scirust_b200.autodiff import scheduler as S
+from scirust_b200.nn import loss as L
+from scirust_b200.nn import modules as M
+from scirust_b200.nn import transformer as T
+from scirust_b200.nn import vision as V
+from scirust_b200.nn import zoo as Z
+from scirust_b200.nn.rng import PcgEngine
+from scirust_b200.utils import logging as ulog
+from scirust_b200.utils import planning
+
+
+def test_linear_conv_pool_shapes_keys_and_gradients():
+    rng = PcgEngine(3)
+    lin = M.Linear(6, 4, rng=rng).with_name("fc")
+    x = torch.randn(5, 6, requires_grad=True)
+    y = lin(x)
+    assert torch.allclose(y, x @ lin.weight + lin.bias)
+    assert set(lin.state_dict_ref()) == {"fc.weight", "fc.bias"} and lin.state_dict_ref()["fc.bias"].shape == (1, 4)
+    conv = M.Conv2d(2, 3, 3, stride=1, padding=M.Padding.SAME, in_h=8, in_w=8, rng=rng)
+    img = torch.randn(4, 2 * 8 * 8, requires_grad=True)
+    out = conv(img)
+    assert out.shape == (4, 3 * 8 * 8) and conv.weight.shape == (3, 2 * 9)
+    ref = F.conv2d(img.reshape(4, 2, 8, 8), conv.weight.reshape(3, 2, 3, 3), conv.bias.reshape(-1), padding=1)
+    assert torch.allclose(out, ref.reshape(4, -1), atol=1e-5)
+    valid = M.Conv2d(2, 3, 3, stride=2, padding=M.Padding.VALID, in_h=8, in_w=8, rng=rng)
+    assert valid.out_hw() == (3, 3) and valid(img).shape == (4, 27)
+    pool = M.MaxPool2d(2, 2, 3, 8, 8)
+    assert pool(out).shape == (4, 3 * 4 * 4)
+    out.sum().backward()
+    assert img.grad is not None and conv.weight.grad.abs().sum() > 0
+    seq = M.Sequential(M.Linear(6, 8, rng=rng), M.ReLU(), M.Linear(8, 2, rng=rng))
+    assert sorted(seq.state_dict_ref()) == ["0.bias", "0.weight", "2.bias", "2.weight"]
+    other = M.Sequential(M.Linear(6, 8, rng=PcgEngine(9)), M.ReLU(), M.Linear(8, 2, rng=PcgEngine(9)))
+    other.load_state_dict_ref(seq.state_dict_ref())
+    assert torch.equal(other(x), seq(x))
+    with pytest.raises(ValueError):
+        lin(torch.randn(2, 7))
+
+
+def test_norms_match_their_definitions():
+    x = torch.randn(16, 12)
+    ln = M.LayerNorm(12)
+    assert torch.allclose(ln(x), F.layer_norm(x, (12,)), atol=1e-5)
+    rn = M.RMSNorm(12)
+    assert torch.allclose(rn(x), x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + rn.eps), atol=1e-5)
+    bn = M.BatchNorm1d(12)
+    bn.train()
+    y = bn(x)
+    assert torch.allclose(y.mean(0), torch.zeros(12), atol=1e-5)
+    # running variance is the unbiased estimate, momentum 0.1
+    assert torch.allclose(bn.running_var, 0.9 * torch.ones(12) + 0.1 * x.var(0, unbiased=True), atol=1e-5)
+    bn.eval()
+    assert not torch.allclose(bn(x), y)
+
+
+def test_losses():
+    lg = torch.randn(6, 5, requires_grad=True)
+    idx = torch.tensor([0, 4, 2, 2, 1, 3])
+    onehot = F.one_hot(idx, 5).float()
+    ce = L.CrossEntropyLoss()
+    a = ce(lg, onehot)
+    assert a.shape == (1, 1) and torch.allclose(a.reshape(()), F.cross_entropy(lg, idx), atol=1e-6)
+    assert torch.allclose(ce.forward_with_indices(lg, idx).reshape(()), F.cross_entropy(lg, idx), atol=1e-6)
+    with pytest.raises(ValueError):
+        ce(lg, onehot[:, :4])
+    p, t = torch.randn(4, 3), torch.randn(4, 3)
+    assert torch.allclose(L.MSELoss()(p, t).reshape(()), F.mse_loss(p, t))
+    assert torch.allclose(L.NLLLoss()(F.log_softmax(lg, -1), idx).reshape(()), F.cross_entropy(lg, idx), atol=1e-6)
+    assert torch.allclose(L.PoissonNLLLoss()(p, t.abs()).reshape(()), F.poisson_nll_loss(p, t.abs(), log_input=True))
+    assert L.PINNLoss(2.0)(p, t, torch.ones(4, 1)).item() == pytest.approx(F.mse_loss(p, t).item() + 2.0)
+    lp = F.log_softmax(torch.randn(12, 2, 6), -1)
+    tg = torch.randint(1, 6, (2, 4))
+    ctc = L.CTCLoss()(lp, tg, torch.tensor([12, 12]), torch.tensor([4, 3]))
+    assert torch.isfinite(ctc)
+
+
+def test_schedules():
+    assert S.Constant(0.1).lr_at(100) == 0.1
+    assert S.StepDecay(1.0, 10, 0.5).lr_at(25) == pytest.approx(0.25)
+    assert S.Exponential(1.0, 0.9).lr_at(3) == pytest.approx(0.729)
+    cos = S.CosineAnnealing(1.0, 0.1, 100)
+    assert cos.lr_at(0) == pytest.approx(1.0) and cos.lr_at(100) == pytest.approx(0.1)
+    wc = S.WarmupCosine(1.0, 0.0, 10, 110)
+    assert wc.lr_at(5) < wc.lr_at(10) and wc.lr_at(10) == pytest.approx(1.0, abs=1e-6) and wc.lr_at(110) == pytest.approx(0.0, abs=1e-9)
+    rp = S.ReduceOnPlateau(1.0, factor=0.5, patience=2)
+    for m in [1.0, 1.0, 1.0, 1.0]:
+        lr = rp.observe(m)
+    assert lr == pytest.approx(0.5)
+
+
+@pytest.mark.parametrize("name", ["RMSprop", "Lion", "LAMB", "Adafactor", "Muon", "Adan", "AdEMAMix", "Sophia",
+                                  "ScheduleFreeSGD", "GaLore", "Prodigy"])
+def test_nd_optimizers_descend_a_quadratic(name):
+    torch.manual_seed(0)
+    target = torch.randn(8, 6)
+    w = torch.nn.Parameter(torch.zeros(8, 6))
+    b = torch.nn.Parameter(torch.zeros(6))
+    kw = {"Lion": dict(lr=3e-2), "ScheduleFreeSGD": dict(lr=0.5), "Muon": dict(lr=0.05, adam_lr=5e-2),
+          "RMSprop": dict(lr=2e-2), "LAMB": dict(lr=5e-2), "Adafactor": dict(lr=5e-2), "Adan": dict(lr=5e-2),
+          "AdEMAMix": dict(lr=5e-2), "Sophia": dict(lr=5e-2), "GaLore": dict(lr=5e-2, rank=4, update_gap=10),
+          "Prodigy": dict()}[name]
+    opt = getattr(O, name)([w, b], **kw)
+
+    def loss_fn():
+        return ((w + b - target) ** 2).mean()
+    first = loss_fn().item()
+    for _ in range(300):
+        opt.zero_grad()
+        loss_fn().backward()
+        opt.step()
+    assert loss_fn().item() < 0.5 * first, (name, first, loss_fn().item())
+
+
+def test_lookahead_sam_and_newton_schulz():
+    g = torch.randn(6, 10)
+    q = O.newton_schulz_orthogonalize(g, steps=8)
+    sv = torch.linalg.svdvals(q)
+    assert sv.max() < 1.3 and sv.min() > 0.5          # singular values pushed towards 1
+    w = torch.nn.Parameter(torch.ones(4))
+    la = O.Lookahead(torch.optim.SGD([w], lr=0.1), k=2, alpha=0.5)
+    for _ in range(4):
+        la.zero_grad()
+        (w ** 2).sum().backward()
+        la.step()
+    assert w.abs().max() < 1.0
+    w2 = torch.nn.Parameter(torch.ones(4))
+    sam = O.SAM(torch.optim.SGD([w2], lr=0.1), rho=0.05)
+    (w2 ** 2).sum().backward()
+    sam.first_step()
+    assert not torch.allclose(w2.detach(), torch.ones(4))
+    sam.base.zero_grad() if hasattr(sam, "base") else None
+    (w2 ** 2).sum().backward()
+    sam.second_step()
+    assert w2.abs().max() < 1.0
+
+
+def test_transformer_blocks_and_vision_zoo_run_and_train():
+    rng = PcgEngine(1)
+    mha = T.MultiHeadAttention(16, 4, rng=rng, causal=True)
+    x = torch.randn(2 * 6, 16)
+    y = mha(x, seq_len=6)
+    assert y.shape == x.shape
+    # causal: output at position t must not depend on later positions
+    x2 = x.clone()
+    x2[5] += 1.0
+    assert torch.allclose(mha(x2, seq_len=6)[:5], y[:5], atol=1e-6)
+    q, k, v = torch.randn(33, 8), torch.randn(33, 8), torch.randn(33, 8)
+    fa, row_max, row_sum = T.flash_attention_blockwise(q, k, v, block=16, causal=True)
+    assert torch.allclose(fa, F.scaled_dot_product_attention(q[None], k[None], v[None], is_causal=True)[0], atol=1e-5)
+    assert row_max.shape[0] == 33 and (row_sum > 0).all()
+    moe = T.MoE(16, 32, n_experts=4, top_k=2, rng=rng)
+    assert moe(torch.randn(10, 16)).shape == (10, 16)
+    lm = T.MiniLLM(vocab=50, d_model=32, n_heads=4, n_layers=2, d_ff=64, max_len=16)
+    toks = torch.randint(0, 50, (3, 12))
+    assert lm(toks).shape[-1] == 50
+    net = V.resnet18(num_classes=10, in_c=3, in_hw=16)
+    assert net(torch.randn(2, 3 * 16 * 16)).shape == (2, 10)
+    vit = V.ViT(image=16, patch=4, in_c=3, d_model=32, n_heads=4, n_layers=1, d_ff=64, num_classes=5)
+    assert vit(torch.randn(2, 3 * 16 * 16)).shape == (2, 5)
+
+
+def test_zoo_recurrent_graph_generative_operator_layers():
+    torch.manual_seed(0)
+    lstm = Z.LSTM(5, 7)
+    ref = torch.nn.LSTM(5, 7, batch_first=True)
+    with torch.no_grad():
+        ref.weight_ih_l0.copy_(lstm.w_ih.weight); ref.bias_ih_l0.copy_(lstm.w_ih.bias)
+        ref.weight_hh_l0.copy_(lstm.w_hh.weight); ref.bias_hh_l0.zero_()
+    x = torch.randn(3, 6, 5)
+    assert torch.allclose(lstm(x)[0], ref(x)[0], atol=1e-5)
+    adj = (torch.rand(9, 9) > 0.6).float()
+    adj = ((adj + adj.t()) > 0).float()
+    assert Z.GCN(4, 8, 3)(torch.randn(9, 4), adj).shape == (9, 3)
+    a = Z.GCNLayer.normalize_adjacency(adj)
+    assert torch.allclose(a, a.t(), atol=1e-6)
+    vae = Z.VAE(12, 16, 4)
+    xb = torch.randn(8, 12)
+    rec, mu, lv = vae(xb, generator=torch.Generator().manual_seed(1))
+    assert rec.shape == xb.shape and Z.VAE.loss(rec, xb, mu, lv).item() > 0
+    assert Z.KANLayer(6, 3)(torch.randn(5, 6)).shape == (5, 3)
+    fno = Z.FNO1d(in_c=1, out_c=1, width=8, modes=6, n_layers=2)
+    assert fno(torch.randn(2, 1, 64)).shape == (2, 1, 64)
+    assert Z.DeepONet(20, 1, 16, 8)(torch.randn(4, 20), torch.rand(30, 1)).shape == (4, 30)
+    ode = Z.NeuralODE(3, 16, steps=4)
+    z0 = torch.randn(5, 3, requires_grad=True)
+    ode(z0).sum().backward()
+    assert z0.grad is not None
+    tt = Z.TTLinear([4, 4], [3, 5], rank=3)
+    assert tt.full_weight().shape == (16, 15) and tt(torch.randn(2, 16)).shape == (2, 15)
+    assert sum(p.numel() for p in tt.cores) < 16 * 15
+    base = torch.nn.Linear(10, 6)
+    for dora in (False, True):
+        lora = Z.LoRALinear(base, r=2, dora=dora)
+        xx = torch.randn(3, 10)
+        assert torch.allclose(lora(xx), base(xx), atol=1e-5)        # B starts at zero: adapter is the identity
+        assert not base.weight.requires_grad and lora.A.requires_grad
+
+
+@pytest.mark.parametrize("mixer", ["llama", "retnet", "gla", "deltanet", "hgrn", "s4", "mamba", "mamba2", "rwkv",
+                                   "xlstm", "hyena"])
+def test_sequence_mixers_are_causal_and_trainable(mixer):
+    torch.manual_seed(1)
+    lm = Z.NdDecoderLM(vocab=40, d_model=32, n_layers=1, mixer=mixer, n_heads=4, n_kv_heads=2, d_ff=64)
+    toks = torch.randint(0, 40, (2, 10))
+    logits = lm(toks)
+    assert logits.shape == (2, 10, 40) and torch.isfinite(logits).all()
+    changed = toks.clone()
+    changed[:, 7] = (changed[:, 7] + 1) % 40
+    assert torch.allclose(lm(changed)[:, :7], logits[:, :7], atol=1e-4)       # no look-ahead
+    loss = F.cross_entropy(logits[:, :-1].reshape(-1, 40), toks[:, 1:].reshape(-1))
+    loss.backward()
+    assert all(p.grad is not None for p in lm.parameters() if p.requires_grad)
+
+
+def test_speculative_decoding_equals_target_greedy():
+    torch.manual_seed(2)
+    target = Z.NdDecoderLM(vocab=30, d_model=32, n_layers=2, mixer="llama", medusa_heads=2)
+    draft = Z.NdDecoderLM(vocab=30, d_model=16, n_layers=1, mixer="llama", n_heads=2, n_kv_heads=1, d_ff=32)
+    toks = torch.randint(0, 30, (1, 5))
+    out, frac = Z.speculative_generate(target, draft, toks, max_new=9, k=3)
+    ref = toks.clone()
+    with torch.no_grad():
+        for _ in range(9):
+            ref = torch.cat([ref, target(ref)[:, -1].argmax(-1, keepdim=True)], 1)
+    assert torch.equal(out, ref) and 0.0 <= frac <= 1.0
+    assert len(target.medusa_logits(toks)) == 2
+
+
+def test_training_logger_tensorboard_and_planner(tmp_path):
+    lg = ulog.TrainingLogger(tmp_path / "log.csv")
+    lg.log(1, "loss", 2.5, timestamp=10.0)
+    lg.log(2, "loss", 2.0, timestamp=11.0)
+    lg.close()
+    rows = (tmp_path / "log.csv").read_text().strip().splitlines()
+    assert len(rows) == 3 and rows[1].split(",")[0] == "1"
+    tb = ulog.TensorBoardWriter(tmp_path / "tb")
+    tb.add_scalar("loss", 1.25, 3, wall_time=5.0)
+    tb.close()
+    files = [f for f in os.listdir(tmp_path / "tb") if "tfevents" in f]
+    assert files
+    recs = list(ulog.read_tfrecords(tmp_path / "tb" / files[0]))
+    assert len(recs) >= 2                       # file-version record + the scalar
+    assert ulog.crc32c(b"123456789") == 0xE3069283
+    from scirust_b200.models import SciAgentConfig
+    cfg = SciAgentConfig.preset("gqa_12l")
+    plan = planning.plan(cfg, batch=8, seq=2048)
+    assert planning.n_params(cfg) == 168059904
+    assert plan.fits() and plan.total("flash") < plan.total("naive")

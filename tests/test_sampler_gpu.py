@@ -47,22 +47,48 @@ def test_same_seed_same_token_as_host(params):
     dev = DeviceSampler(params, rows, vocab, range(100, 100 + rows), "cuda", history_len=64)
     dev.set_history(hist)
     host_rng = [SamplerRng(100 + b) for b in range(rows)]
-    agree = total = 0
+    exact_rng = [SamplerRng(100 + b) for b in range(rows)]
+    agree_host = agree_exact = total = 0
     lgc = lg.cuda()
     for _ in range(draws):
         got = dev.sample(lgc).cpu().tolist()
         for b in range(rows):
-            want = sample_row(lg[b], params, hist[b].tolist(), host_rng[b])
-            agree += int(got[b] == want)
+            agree_host += int(got[b] == sample_row(lg[b], params, hist[b].tolist(), host_rng[b]))
+            agree_exact += int(got[b] == _exact_pick(lg[b], params, hist[b].tolist(), exact_rng[b].next_uniform()))
             total += 1
-    # identical RNG stream and ranking; a draw within float rounding of a CDF boundary may differ
-    assert agree >= 0.97 * total, f"{agree}/{total}"
+    # same RNG stream and ranking as the host policy. Against the policy evaluated in float64 only a
+    # draw within ~1e-7 of one of the 32000 CDF boundaries can differ; the host's float32 running sum
+    # is coarser than that in the low-probability tail, so agreement with it is lower there.
+    assert agree_exact >= 0.97 * total, f"exact {agree_exact}/{total}"
+    assert agree_host >= 0.7 * total, f"host {agree_host}/{total}"
     again = DeviceSampler(params, rows, vocab, range(100, 100 + rows), "cuda", history_len=64)
     again.set_history(hist)
     first = again.sample(lgc).cpu()
     ref = DeviceSampler(params, rows, vocab, range(100, 100 + rows), "cuda", history_len=64)
     ref.set_history(hist)
     assert torch.equal(first, ref.sample(lgc).cpu())
+
+
+def _exact_pick(row, params, recent, u):
+    """The sampling policy in float64 with the uniform draw ``u`` given."""
+    x = row.clone()
+    if params.repetition_penalty > 1.0:
+        for t in recent[-params.repetition_window:]:
+            x[t] = x[t] / params.repetition_penalty if x[t] > 0 else x[t] * params.repetition_penalty
+    p = torch.softmax(x.double() / params.temperature, -1)
+    order = torch.argsort(p, descending=True, stable=True)
+    ps = p[order]
+    cut = len(ps)
+    if params.top_k > 0:
+        cut = min(cut, params.top_k)
+    if params.top_p < 1.0:
+        cum = torch.cumsum(ps[:cut], 0)
+        hit = torch.nonzero(cum >= params.top_p)
+        if len(hit):
+            cut = int(hit[0]) + 1
+    cdf = torch.cumsum(ps[:cut], 0)
+    r = int(torch.searchsorted(cdf, torch.tensor(u * float(cdf[-1]), dtype=torch.float64), right=True))
+    return int(order[min(r, cut - 1)])
 
 
 def test_empirical_distribution_follows_softmax():
