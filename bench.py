@@ -133,13 +133,22 @@ def main():
 
     cfg = SciAgentConfig.preset(args.model)
     B, S = args.batch_per_gpu, args.seq_len
-    model = GQADecoder(cfg, device=dev, seed=1234)
-
-    reducer = None
-    if world > 1:
-        from scirust_b200.parallel.data_parallel import make_grad_reducer
-        reducer = make_grad_reducer(model, dist.group.WORLD, kind=args.comm if args.impl == "ours" else "nccl")
-    trainer = Trainer(model, TrainerConfig(lr=3e-4, weight_decay=0.1, max_grad_norm=1.0), grad_reducer=reducer)
+    if args.impl == "baseline":
+        # library arm: stock PyTorch operators (cuBLAS, SDPA, fused AdamW) + NCCL DDP, none of our kernels
+        from scirust_b200.models.baseline_torch import TorchLibraryDecoder, TorchLibraryTrainer
+        model = TorchLibraryDecoder(cfg, device=dev, seed=1234)
+        ddp = None
+        if world > 1:
+            ddp = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank], bucket_cap_mb=64,
+                                                            gradient_as_bucket_view=True)
+        trainer = TorchLibraryTrainer(model, ddp=ddp)
+    else:
+        model = GQADecoder(cfg, device=dev, seed=1234)
+        reducer = None
+        if world > 1:
+            from scirust_b200.parallel.data_parallel import make_grad_reducer
+            reducer = make_grad_reducer(model, dist.group.WORLD, kind=args.comm)
+        trainer = Trainer(model, TrainerConfig(lr=3e-4, weight_decay=0.1, max_grad_norm=1.0), grad_reducer=reducer)
 
     # synthetic data: a ring of pinned host batches, seeded per rank
     g = torch.Generator().manual_seed(1000 + rank)
@@ -218,7 +227,7 @@ def main():
                                 f"dh{cfg.head_dim} ff{cfg.d_ff} V{cfg.vocab_size}",
                        "global_batch": B * world, "seq_len": S, "parallelism": f"{args.parallelism}{world}",
                        "optimizer": "AdamW lr 3e-4 wd 0.1 clip 1.0, fp32 master weights",
-                       "grad_reduce": (args.comm if world > 1 else "none"),
+                       "grad_reduce": ("none" if world == 1 else "nccl-ddp" if args.impl == "baseline" else args.comm),
                        "l2": "per-step working set (activations > 5 GB) exceeds the 126 MB L2; no flush needed"},
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "ms_per_step": max(ms_e2e, wall_ms) / args.steps},

@@ -44,7 +44,8 @@ def _rand(shape, seed):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attention", "attention_bwd", "rmsnorm", "ce", "adamw"])
+    ap.add_argument("kernel", choices=["gemm", "gemm_model", "attention", "attention_bwd", "rmsnorm", "ce", "adamw"])
+    ap.add_argument("--library", action="store_true", help="gemm_model: also time torch.matmul (cuBLAS)")
     ap.add_argument("--form", default="nt", choices=["nn", "nt", "tn"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -75,6 +76,33 @@ def main(argv=None):
             fn = lambda: gemm.matmul_tn(x, w)  # noqa: E731
         ms = _time(fn, a.iters, a.warmup, flush)
         out.update(form=a.form, m=M, n=N, k=K, ms=ms, tflops=2.0 * M * N * K / ms / 1e9)
+    elif a.kernel == "gemm_model":
+        # every GEMM of one training step of the 12-layer d1024 decoder at 16384 tokens, all three forms
+        T = a.rows
+        shapes = [("qkv", 1024, 1536), ("wo", 1024, 1024), ("gate_up", 1024, 5632), ("down", 2816, 1024),
+                  ("lm_head_chunk", 1024, 32000)]
+        rows = []
+        for name, K, N in shapes:
+            Tm = 4096 if name == "lm_head_chunk" else T
+            x, w, dy = _rand((Tm, K), 1), _rand((K, N), 2), _rand((Tm, N), 3)
+            wt = w.t().contiguous()
+            forms = [("fwd x.W", lambda: gemm.matmul_nn(x, w), lambda: torch.matmul(x, w)),
+                     ("dgrad dy.W^T", lambda: gemm.matmul_nt(dy, w), lambda: torch.matmul(dy, w.t())),
+                     ("wgrad x^T.dy", lambda: gemm.matmul_tn(x, dy), lambda: torch.matmul(x.t(), dy))]
+            if name == "lm_head_chunk":   # tied head: logits = h.E^T, dh = dlogits.E, dE = dlogits^T.h
+                forms = [("fwd h.E^T", lambda: gemm.matmul_nt(x, wt), lambda: torch.matmul(x, wt.t())),
+                         ("dgrad dl.E", lambda: gemm.matmul_nn(dy, wt), lambda: torch.matmul(dy, wt)),
+                         ("wgrad dl^T.h", lambda: gemm.matmul_tn(dy, x), lambda: torch.matmul(dy.t(), x))]
+            for fname, ours, lib in forms:
+                fl = 2.0 * Tm * K * N
+                ms = _time(ours, a.iters, a.warmup, flush)
+                row = {"gemm": name, "form": fname, "tokens": Tm, "k": K, "n": N, "ms": round(ms, 4),
+                       "tflops": round(fl / ms / 1e9, 1)}
+                if a.library:
+                    ml = _time(lib, a.iters, a.warmup, flush)
+                    row.update(cublas_ms=round(ml, 4), cublas_tflops=round(fl / ml / 1e9, 1))
+                rows.append(row)
+        out["rows"] = rows
     elif a.kernel in ("attention", "attention_bwd"):
         B, S, H, Hkv, dh = a.batch, a.seq, a.heads, a.kv_heads, a.dh
         qkv = _rand((B * S, (H + 2 * Hkv) * dh), 3)

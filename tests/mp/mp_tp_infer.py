@@ -27,7 +27,7 @@ def main():
         dev = torch.device("cpu")
         dist.init_process_group("gloo")
     W = dist.get_world_size()
-    cfg = SciAgentConfig(vocab_size=512, d_model=256, n_layers=2, n_heads=8, n_kv_heads=int(os.environ.get("SB_TP_KV", "4")),
+    cfg = SciAgentConfig(vocab_size=512, d_model=512, n_layers=2, n_heads=8, n_kv_heads=int(os.environ.get("SB_TP_KV", "4")),
                          d_ff=512, max_seq_len=256)
     model = GQADecoder(cfg, device=dev, seed=3, init_std=0.08)
     B, P, NEW = (2, 24, 6) if not use_cuda else (int(os.environ.get("SB_TP_BATCH", "2")), 40, 8)

@@ -129,3 +129,22 @@ def test_shipped_reference_checkpoint_predicts_source_text():
     with torch.no_grad():
         loss = float(m(t[:, :-1], t[:, 1:]))
     assert loss < 7.0          # ln(8192) = 9.01 for a model that knows nothing
+
+
+def test_library_baseline_model_computes_the_same_loss():
+    """The stock-PyTorch arm of the benchmark is the same network: with the native model's weights its
+    loss agrees to bf16 accuracy."""
+    from scirust_b200.models.baseline_torch import TorchLibraryDecoder
+    cfg = SciAgentConfig(vocab_size=128, d_model=64, n_layers=2, n_heads=4, n_kv_heads=2, d_ff=128, max_seq_len=32)
+    ours = GQADecoder(cfg, device="cpu", seed=5, init_std=0.05)
+    lib = TorchLibraryDecoder(cfg, device="cpu", seed=0)
+    with torch.no_grad():
+        lib.embed.copy_(ours.embed)
+        lib.rms_final.copy_(ours.rms_final)
+        for a, b in zip(lib.blocks, ours.layers):
+            for n in ("rms_attn", "rms_ffn", "wqkv", "wo", "wgu", "wd"):
+                getattr(a, n).copy_(getattr(b, n))
+    toks = torch.randint(0, 128, (2, 17), generator=torch.Generator().manual_seed(3))
+    l_ours = ours(toks[:, :-1], toks[:, 1:]).float().item()
+    l_lib = lib(toks[:, :-1], toks[:, 1:]).float().item()
+    assert abs(l_ours - l_lib) < 3e-2, (l_ours, l_lib)

@@ -102,7 +102,7 @@ def test_empirical_distribution_follows_softmax():
 
 
 def test_engine_sampled_generation_graph_equals_eager():
-    cfg = SciAgentConfig(vocab_size=512, d_model=256, n_layers=2, n_heads=8, n_kv_heads=4, d_ff=512, max_seq_len=256)
+    cfg = SciAgentConfig(vocab_size=512, d_model=256, n_layers=2, n_heads=4, n_kv_heads=2, d_ff=512, max_seq_len=256)
     model = GQADecoder(cfg, device="cuda", seed=5, init_std=0.08)
     prompts = torch.randint(0, 512, (3, 20), generator=torch.Generator().manual_seed(2))
     params = SamplingParams(temperature=0.9, top_k=40, top_p=0.95, repetition_penalty=1.1)
