@@ -1,0 +1,300 @@
+// bf16 GEMM on CTA pairs (tcgen05 cta_group::2): one 256 x 256 output tile per pair of SMs.
+//
+// Same contract and operand forms as gemm_tcgen05.cu (C = op(A) * op(B), fp32 accumulation in tensor
+// memory, optional bf16 residual, K walked in a fixed order). What changes is the traffic: the two
+// CTAs of a cluster share one tcgen05.mma of M = 256, N = 256 per k-step. Each CTA stages its own
+// 128 rows of A and only HALF of the B tile (128 of the 256 columns), so a CTA moves 32 KB per
+// k-block for the same tensor work that costs 48 KB with 128 x 256 tiles per CTA, and six stages fit
+// where four did. The accumulator rows of a CTA stay in its own TMEM; the epilogue is per CTA.
+//
+//   warp 0   TMA producer (both CTAs; bytes of both are counted on the leader's "full" barrier)
+//   warp 1   MMA issuer (leader CTA only); the same warp allocates TMEM in both CTAs
+//   warp 2-9 epilogue (both CTAs; "accumulator drained" arrives on the leader's barrier)
+// Stage release and "accumulator ready" are tcgen05.commit arrivals delivered to both CTAs.
+// No TMA multicast is used.
+#include "sm100_ptx.cuh"
+#include "api.h"
+
+namespace sb {
+
+int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_outer);
+int num_sms();
+
+namespace pair {
+
+constexpr int BM = 128;        // rows of A per CTA (256 per pair)
+constexpr int BN = 256;        // columns of the pair's tile
+constexpr int BNH = BN / 2;    // columns of B staged per CTA
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 320;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BNH * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // 32 KB per CTA
+constexpr int STAGES = 6;
+constexpr int TMEM_COLS = 2 * BN;                // two accumulators
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+
+struct Params {
+  int M, N, K;
+  void* C; int ldc;
+  const void* R; int ldr;
+  int* status;
+};
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tiles = smem;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full = empty_bar + STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0 = leader, 1 = peer
+  const bool leader = rank == 0;
+  const int pair_id = blockIdx.x >> 1;
+  const int n_pairs = gridDim.x >> 1;
+
+  const int mt2 = (p.M + 2 * BM - 1) / (2 * BM);
+  const int nt = (p.N + BN - 1) / BN;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int tiles_total = mt2 * nt;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);     // leader's producer arms it; both CTAs' copies complete on it
+      mbar_init(&empty_bar[s], 1);    // one commit arrival (delivered to both CTAs)
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 16);  // 8 epilogue warps of each CTA arrive on the leader's barrier
+    }
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_holder, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                 // both CTAs' barriers exist before anyone signals across
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair_id; t < tiles_total && ok; t += n_pairs) {
+        const int n_idx = t / mt2;
+        const int m2 = t - n_idx * mt2;
+        const int row0 = (m2 * 2 + static_cast<int>(rank)) * BM;      // this CTA's rows of A
+        const int col0 = n_idx * BN + static_cast<int>(rank) * BNH;   // this CTA's columns of B
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          uint8_t* sa = tiles + stage * STAGE_BYTES;
+          uint8_t* sb_ = sa + A_BYTES;
+          if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
+          const uint32_t bar = mapa_shared(smem_u32(&full_bar[stage]), 0);
+          if constexpr (!A_MN) {
+            tma_load_2d_pair(sa, &tmap_a, bar, kb * BK, row0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_2d_pair(sa + c * (64 * BK * 2), &tmap_a, bar, row0 + c * 64, kb * BK);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d_pair(sb_, &tmap_b, bar, kb * BK, col0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BNH / 64; ++c)
+              tma_load_2d_pair(sb_ + c * (64 * BK * 2), &tmap_b, bar, col0 + c * 64, kb * BK);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer (leader only) -------------------------------
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int t = pair_id; t < tiles_total && ok; t += n_pairs, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + stage * STAGE_BYTES);
+          const uint32_t sb_ = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = A_MN ? make_smem_desc(sa + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                        : make_smem_desc(sa + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t bdesc = B_MN ? make_smem_desc(sb_ + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                        : make_smem_desc(sb_ + k * (UMMA_K * 2), 16, 1024);
+            umma_bf16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(&empty_bar[stage], 3);   // frees the stage in both CTAs
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit_pair(&tmem_full[acc], 3);
+      }
+    }
+  } else {
+    // -------------------------------- epilogue (both CTAs) --------------------------------
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const uint32_t leader_empty0 = mapa_shared(smem_u32(&tmem_empty[0]), 0);
+    const uint32_t leader_empty1 = mapa_shared(smem_u32(&tmem_empty[1]), 0);
+    bool ok = true;
+    int it = 0;
+    for (int t = pair_id; t < tiles_total && ok; t += n_pairs, ++it) {
+      const int n_idx = t / mt2;
+      const int m2 = t - n_idx * mt2;
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int row = (m2 * 2 + static_cast<int>(rank)) * BM + q * 32 + lane;
+      const uint32_t taddr_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr_row + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n_idx * BN + c * 32;
+        if (row < p.M && col0 < p.N) {
+          __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+          const __nv_bfloat16* rrow =
+              p.R ? reinterpret_cast<const __nv_bfloat16*>(p.R) + static_cast<size_t>(row) * p.ldr + col0 : nullptr;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (col0 + v * 8 < p.N) {  // N % 8 == 0 is enforced on the host
+              float f[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+              if (rrow) {
+                const uint4 rv = *reinterpret_cast<const uint4*>(rrow + v * 8);
+                f[0] += bf16_lo(rv.x); f[1] += bf16_hi(rv.x);
+                f[2] += bf16_lo(rv.y); f[3] += bf16_hi(rv.y);
+                f[4] += bf16_lo(rv.z); f[5] += bf16_hi(rv.z);
+                f[6] += bf16_lo(rv.w); f[7] += bf16_hi(rv.w);
+              }
+              uint4 o;
+              o.x = pack_bf16x2(f[0], f[1]);
+              o.y = pack_bf16x2(f[2], f[3]);
+              o.z = pack_bf16x2(f[4], f[5]);
+              o.w = pack_bf16x2(f[6], f[7]);
+              *reinterpret_cast<uint4*>(crow + v * 8) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
+    }
+  }
+
+  // Teardown: every role loop is bounded, so all threads of both CTAs arrive here. Neither CTA may
+  // leave while the other can still read its shared memory or signal its barriers.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+}
+
+template <bool A_MN, bool B_MN>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int grid, cudaStream_t stream) {
+  auto kern = gemm_pair_kernel<A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+      return SB_ERR_LAUNCH;
+    attr_set = true;
+  }
+  // size the grid to the number of CTA pairs the device can keep resident at once
+  static int max_pairs = 0;
+  if (!max_pairs) {
+    cudaLaunchConfig_t q = {};
+    q.gridDim = dim3(2 * (num_sms() / 2));
+    q.blockDim = dim3(THREADS);
+    q.dynamicSmemBytes = SMEM_BYTES;
+    cudaLaunchAttribute qa[1];
+    qa[0].id = cudaLaunchAttributeClusterDimension;
+    qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+    q.attrs = qa; q.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &q) != cudaSuccess || n < 1) n = num_sms() / 2;
+    max_pairs = n;
+  }
+  if (grid > 2 * max_pairs) grid = 2 * max_pairs;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, ta, tb, p) == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+}
+
+}  // namespace pair
+}  // namespace sb
+
+using namespace sb;
+
+// Same contract as sb_gemm_bf16 without split-K: C[M,N] (bf16) = op(A) op(B) (+ R). M, N, K > 0,
+// N % 8 == 0, leading dimensions multiples of 8 elements, 16-byte aligned bases.
+extern "C" int sb_gemm_pair_bf16(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda,
+                                 int ldb, int ldc, int ldr, int a_mn, int b_mn, int* status, void* stream_) {
+  using namespace sb::pair;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0 || (N & 7) || (ldc & 7) || (R && (ldr & 7))) return SB_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(C) & 15) || (R && (reinterpret_cast<uintptr_t>(R) & 15))) return SB_ERR_ALIGN;
+  CUtensorMap ta, tb;
+  int rc;
+  if (!a_mn) rc = make_tmap_2d_bf16(&ta, A, K, M, lda, BK, BM);
+  else rc = make_tmap_2d_bf16(&ta, A, M, K, lda, 64, BK);
+  if (rc) return rc;
+  if (!b_mn) rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, BNH);
+  else rc = make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, BK);
+  if (rc) return rc;
+  Params p;
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.R = R; p.ldr = ldr; p.status = status;
+  const int mt2 = (M + 2 * BM - 1) / (2 * BM), nt = (N + BN - 1) / BN;
+  const int pairs_avail = num_sms() / 2;
+  const int pairs = mt2 * nt < pairs_avail ? mt2 * nt : pairs_avail;
+  const int grid = 2 * pairs;
+  if (!a_mn && !b_mn) return launch<false, false>(ta, tb, p, grid, stream);
+  if (!a_mn && b_mn) return launch<false, true>(ta, tb, p, grid, stream);
+  if (a_mn && !b_mn) return launch<true, false>(ta, tb, p, grid, stream);
+  return launch<true, true>(ta, tb, p, grid, stream);
+}

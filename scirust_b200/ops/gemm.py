@@ -13,6 +13,8 @@ be tested without a GPU; CUDA tensors always run the native kernel.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib
@@ -48,6 +50,19 @@ def _check2d(t: torch.Tensor, name: str) -> None:
                          f"{tuple(t.shape)} {t.dtype} strides {t.stride()}")
 
 
+# CTA-pair kernel (csrc/gemm_pair_tcgen05.cu): 256 x 256 tiles on two SMs. "auto" uses it for
+# products with at least one full wave of such tiles and no split-K; SB_GEMM_PAIR=0/1 forces it.
+PAIR_MODE = os.environ.get("SB_GEMM_PAIR", "auto")
+
+
+def _use_pair(M, N, K, splits, bn) -> bool:
+    if PAIR_MODE == "0" or splits not in (None, 1) or bn not in (None, 256):
+        return False
+    if PAIR_MODE == "1":
+        return True
+    return ((M + 255) // 256) * ((N + 255) // 256) >= _NUM_SMS // 2 and K >= 256
+
+
 def _gemm(a, b, M, N, K, a_mn, b_mn, out, residual, splits, bn):
     global launch_count
     _check2d(a, "a")
@@ -62,6 +77,13 @@ def _gemm(a, b, M, N, K, a_mn, b_mn, out, residual, splits, bn):
         _check2d(residual, "residual")
         if tuple(residual.shape) != (M, N):
             raise ValueError("residual shape mismatch")
+    if _use_pair(M, N, K, splits, bn):
+        st = _lib.status_word(a.device)
+        _lib.call("sb_gemm_pair_bf16", a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(residual), M, N, K,
+                  a.stride(0), b.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
+                  int(a_mn), int(b_mn), st.data_ptr(), _lib.stream())
+        launch_count += 1
+        return out
     if bn is None:
         bn = 128 if N <= 128 else 256
     if splits is None:
