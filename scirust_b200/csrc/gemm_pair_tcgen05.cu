@@ -14,6 +14,7 @@
 // No TMA multicast is used.
 #include "sm100_ptx.cuh"
 #include "api.h"
+#include "gemm_sched.cuh"
 
 namespace sb {
 
@@ -41,6 +42,8 @@ struct Params {
   void* C; int ldc;
   const void* R; int ldr;
   int* status;
+  BalancedSched sched;   // workers are CTA pairs; see gemm_sched.cuh
+  float* partials;       // dense fp32 [256, 256] blocks, one per scratch slot
 };
 
 template <bool A_MN, bool B_MN>
@@ -99,12 +102,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = pair_id; t < tiles_total && ok; t += n_pairs) {
-        const int n_idx = t / mt2;
-        const int m2 = t - n_idx * mt2;
+      SegIter iter(p.sched, pair_id, n_pairs, tiles_total, num_kb, 1, num_kb);
+      Seg sg;
+      while (ok && iter.next(sg)) {
+        const int n_idx = sg.tile / mt2;
+        const int m2 = sg.tile - n_idx * mt2;
         const int row0 = (m2 * 2 + static_cast<int>(rank)) * BM;      // this CTA's rows of A
         const int col0 = n_idx * BN + static_cast<int>(rank) * BNH;   // this CTA's columns of B
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           uint8_t* sa = tiles + stage * STAGE_BYTES;
           uint8_t* sb_ = sa + A_BYTES;
@@ -136,13 +141,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
-      for (int t = pair_id; t < tiles_total && ok; t += n_pairs, ++it) {
+      SegIter iter(p.sched, pair_id, n_pairs, tiles_total, num_kb, 1, num_kb);
+      Seg sg;
+      for (; ok && iter.next(sg); ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(tiles + stage * STAGE_BYTES);
@@ -153,7 +160,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                                         : make_smem_desc(sa + k * (UMMA_K * 2), 16, 1024);
             const uint64_t bdesc = B_MN ? make_smem_desc(sb_ + k * (UMMA_K * 128), 64 * BK * 2, 1024)
                                         : make_smem_desc(sb_ + k * (UMMA_K * 2), 16, 1024);
-            umma_bf16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_bf16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > sg.kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit_pair(&empty_bar[stage], 3);   // frees the stage in both CTAs
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -169,9 +176,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t leader_empty1 = mapa_shared(smem_u32(&tmem_empty[1]), 0);
     bool ok = true;
     int it = 0;
-    for (int t = pair_id; t < tiles_total && ok; t += n_pairs, ++it) {
-      const int n_idx = t / mt2;
-      const int m2 = t - n_idx * mt2;
+    SegIter iter(p.sched, pair_id, n_pairs, tiles_total, num_kb, 1, num_kb);
+    Seg sg;
+    for (; ok && iter.next(sg); ++it) {
+      const int n_idx = sg.tile / mt2;
+      const int m2 = sg.tile - n_idx * mt2;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
@@ -184,7 +193,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tmem_ld_32x32(taddr_row + c * 32, r);
         tmem_ld_wait();
         const int col0 = n_idx * BN + c * 32;
-        if (row < p.M && col0 < p.N) {
+        if (sg.slot >= 0) {
+          // part of a tile of the balanced schedule: this CTA's 128 rows of the pair's fp32 block
+          float* prow = p.partials +
+                        (static_cast<size_t>(sg.slot) * (2 * BM) + rank * BM + (q * 32 + lane)) * BN + c * 32;
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            *reinterpret_cast<uint4*>(prow + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+        } else if (row < p.M && col0 < p.N) {
           __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
           const __nv_bfloat16* rrow =
               p.R ? reinterpret_cast<const __nv_bfloat16*>(p.R) + static_cast<size_t>(row) * p.ldr + col0 : nullptr;
@@ -226,18 +242,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
 }
 
-template <bool A_MN, bool B_MN>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int grid, cudaStream_t stream) {
-  auto kern = gemm_pair_kernel<A_MN, B_MN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
-      return SB_ERR_LAUNCH;
-    attr_set = true;
-  }
-  // size the grid to the number of CTA pairs the device can keep resident at once
-  static int max_pairs = 0;
-  if (!max_pairs) {
+// Number of CTA pairs the device keeps resident at once (the kernel runs one CTA per SM).
+static int max_pairs() {
+  static int cached = 0;
+  if (!cached) {
+    auto kern = gemm_pair_kernel<false, false>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     cudaLaunchConfig_t q = {};
     q.gridDim = dim3(2 * (num_sms() / 2));
     q.blockDim = dim3(THREADS);
@@ -248,9 +258,21 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p,
     q.attrs = qa; q.numAttrs = 1;
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, kern, &q) != cudaSuccess || n < 1) n = num_sms() / 2;
-    max_pairs = n;
+    if (n > num_sms() / 2) n = num_sms() / 2;
+    cached = n;
   }
-  if (grid > 2 * max_pairs) grid = 2 * max_pairs;
+  return cached;
+}
+
+template <bool A_MN, bool B_MN>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int grid, cudaStream_t stream) {
+  auto kern = gemm_pair_kernel<A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+      return SB_ERR_LAUNCH;
+    attr_set = true;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(THREADS);
@@ -273,8 +295,12 @@ using namespace sb;
 
 // Same contract as sb_gemm_bf16 without split-K: C[M,N] (bf16) = op(A) op(B) (+ R). M, N, K > 0,
 // N % 8 == 0, leading dimensions multiples of 8 elements, 16-byte aligned bases.
+// `workspace` (optional): sb_gemm_pair_workspace_floats() floats; with it the balanced schedule is used.
+extern "C" size_t sb_gemm_pair_workspace_floats() { return static_cast<size_t>(num_sms() / 2) * 3 * 256 * 256; }
+
 extern "C" int sb_gemm_pair_bf16(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda,
-                                 int ldb, int ldc, int ldr, int a_mn, int b_mn, int* status, void* stream_) {
+                                 int ldb, int ldc, int ldr, int a_mn, int b_mn, void* workspace, int* status,
+                                 void* stream_) {
   using namespace sb::pair;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0 || K <= 0 || (N & 7) || (ldc & 7) || (R && (ldr & 7))) return SB_ERR_ARG;
@@ -290,11 +316,30 @@ extern "C" int sb_gemm_pair_bf16(const void* A, const void* B, void* C, const vo
   Params p;
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.R = R; p.ldr = ldr; p.status = status;
   const int mt2 = (M + 2 * BM - 1) / (2 * BM), nt = (N + BN - 1) / BN;
-  const int pairs_avail = num_sms() / 2;
-  const int pairs = mt2 * nt < pairs_avail ? mt2 * nt : pairs_avail;
+  const int num_kb = (K + BK - 1) / BK;
+  const int pairs_avail = max_pairs();
+  const int tiles = mt2 * nt;
+  int pairs = tiles < pairs_avail ? tiles : pairs_avail;
+  bool fixup = false;
+  p.partials = nullptr;
+  if (workspace && plan_balanced(tiles, num_kb, pairs_avail, &p.sched, &fixup)) {
+    p.partials = static_cast<float*>(workspace);
+    pairs = p.sched.dp_tiles > 0 ? pairs_avail : p.sched.sk_workers;
+  } else {
+    p.sched.dp_tiles = p.sched.sk_tiles = p.sched.sk_workers = p.sched.sk_slots = 0;
+  }
   const int grid = 2 * pairs;
-  if (!a_mn && !b_mn) return launch<false, false>(ta, tb, p, grid, stream);
-  if (!a_mn && b_mn) return launch<false, true>(ta, tb, p, grid, stream);
-  if (a_mn && !b_mn) return launch<true, false>(ta, tb, p, grid, stream);
-  return launch<true, true>(ta, tb, p, grid, stream);
+  if (!a_mn && !b_mn) rc = launch<false, false>(ta, tb, p, grid, stream);
+  else if (!a_mn && b_mn) rc = launch<false, true>(ta, tb, p, grid, stream);
+  else if (a_mn && !b_mn) rc = launch<true, false>(ta, tb, p, grid, stream);
+  else rc = launch<true, true>(ta, tb, p, grid, stream);
+  if (rc) return rc;
+  if (fixup) {
+    dim3 fg(p.sched.sk_tiles, 2 * BM * BN / (256 * 4));
+    balanced_fixup_kernel<2 * BM, BN><<<fg, 256, 0, stream>>>(p.sched, p.partials, static_cast<__nv_bfloat16*>(C), ldc,
+                                                             static_cast<const __nv_bfloat16*>(R), ldr, M, N, mt2,
+                                                             num_kb);
+    if (cudaGetLastError() != cudaSuccess) return SB_ERR_LAUNCH;
+  }
+  return 0;
 }

@@ -25,6 +25,7 @@
 // repeatable; split-K writes fp32 partials that a second kernel adds in split order.
 #include "sm100_ptx.cuh"
 #include "api.h"
+#include "gemm_sched.cuh"
 
 namespace sb {
 
@@ -45,13 +46,15 @@ struct GemmCfg {
 
 struct GemmParams {
   int M, N, K;
-  int splits;          // split-K factor (1 = none)
+  int splits;          // explicit split-K factor (1 = none)
   int kb_per_split;    // k-blocks per split
   void* C;             // bf16 [M, ldc] when splits == 1; fp32 [splits, M, N] partials otherwise
   int ldc;
   const void* R;       // optional bf16 residual [M, ldr] added in the epilogue (splits == 1)
   int ldr;
   int* status;
+  BalancedSched sched;   // balanced schedule (splits == 1 only); see gemm_sched.cuh
+  float* partials;       // scratch slots of the balanced schedule: dense fp32 [BM, BN] blocks
 };
 
 template <int BN, bool A_MN, bool B_MN>
@@ -75,7 +78,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int mt = (p.M + BM - 1) / BM;
   const int nt = (p.N + BN - 1) / BN;
   const int num_kb = (p.K + BK - 1) / BK;
-  const int tiles_total = mt * nt * p.splits;
+  const int tiles_mn = mt * nt;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::STAGES; ++s) {
@@ -108,13 +111,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < tiles_total && ok; t += gridDim.x) {
-        const int split = t / (mt * nt);
-        const int rem = t - split * (mt * nt);
-        const int n_idx = rem / mt;
-        const int m_idx = rem - n_idx * mt;
-        const int kb0 = split * p.kb_per_split;
-        const int kb1 = min(num_kb, kb0 + p.kb_per_split);
+      SegIter iter(p.sched, blockIdx.x, gridDim.x, tiles_mn, num_kb, p.splits, p.kb_per_split);
+      Seg sg;
+      while (ok && iter.next(sg)) {
+        const int n_idx = sg.tile / mt;
+        const int m_idx = sg.tile - n_idx * mt;
+        const int kb0 = sg.kb0, kb1 = sg.kb1;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           uint8_t* sa = tiles + stage * Cfg::STAGE_BYTES;
@@ -146,10 +148,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
-      for (int t = blockIdx.x; t < tiles_total && ok; t += gridDim.x, ++it) {
-        const int split = t / (mt * nt);
-        const int kb0 = split * p.kb_per_split;
-        const int kb1 = min(num_kb, kb0 + p.kb_per_split);
+      SegIter iter(p.sched, blockIdx.x, gridDim.x, tiles_mn, num_kb, p.splits, p.kb_per_split);
+      Seg sg;
+      for (; ok && iter.next(sg); ++it) {
+        const int kb0 = sg.kb0, kb1 = sg.kb1;
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
@@ -180,11 +182,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp drains
     bool ok = true;
     int it = 0;
-    for (int t = blockIdx.x; t < tiles_total && ok; t += gridDim.x, ++it) {
-      const int split = t / (mt * nt);
-      const int rem = t - split * (mt * nt);
-      const int n_idx = rem / mt;
-      const int m_idx = rem - n_idx * mt;
+    SegIter iter(p.sched, blockIdx.x, gridDim.x, tiles_mn, num_kb, p.splits, p.kb_per_split);
+    Seg sg;
+    for (; ok && iter.next(sg); ++it) {
+      const int split = sg.split;
+      const int n_idx = sg.tile / mt;
+      const int m_idx = sg.tile - n_idx * mt;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
@@ -197,7 +200,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tmem_ld_32x32(taddr_row + c * 32, r);
         tmem_ld_wait();
         const int col0 = n_idx * BN + c * 32;
-        if (row < p.M && col0 < p.N) {
+        if (sg.slot >= 0) {
+          // part of a tile of the balanced schedule: dense fp32 block, finished by the fix-up kernel
+          float* prow = p.partials + (static_cast<size_t>(sg.slot) * BM + (q * 32 + lane)) * BN + c * 32;
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            *reinterpret_cast<uint4*>(prow + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+        } else if (row < p.M && col0 < p.N) {
           if (p.splits == 1) {
             __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
             const __nv_bfloat16* rrow =
@@ -359,8 +368,13 @@ using namespace sb;
 
 // C[M,N] (bf16, pitch ldc) = op(A) op(B) (+ R).  a_mn / b_mn select the operand
 // major-ness described at the top of this file; lda/ldb are row pitches (elements)
-// of the matrices as stored. `splits` > 1 needs `workspace` of splits*M*N floats.
+// of the matrices as stored. `splits` > 1 is explicit split-K and needs `workspace` of
+// splits*M*N floats. `splits` == 0 selects the balanced schedule (whole waves of tiles one per
+// CTA, the k-blocks of the last partial wave dealt out evenly over all SMs); it needs `workspace`
+// of sb_gemm_balanced_workspace_floats() floats and falls back to one tile per CTA without it.
 // bn: 0 = choose, else 128 or 256.
+extern "C" size_t sb_gemm_balanced_workspace_floats() { return static_cast<size_t>(num_sms()) * 3 * BM * 256; }
+
 extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda,
                             int ldb, int ldc, int ldr, int a_mn, int b_mn, int splits, void* workspace, int bn,
                             int* status, void* stream_) {
@@ -370,6 +384,7 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* R
   if (reinterpret_cast<uintptr_t>(C) & 15) return SB_ERR_ALIGN;
   if (R && (reinterpret_cast<uintptr_t>(R) & 15)) return SB_ERR_ALIGN;
   const int num_kb = (K + BK - 1) / BK;
+  const bool balanced = splits == 0 && workspace != nullptr;
   if (splits < 1) splits = 1;
   if (splits > num_kb) splits = num_kb;
   int kb_per_split = (num_kb + splits - 1) / splits;
@@ -396,9 +411,17 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* R
   p.R = splits > 1 ? nullptr : R;
   p.ldr = ldr;
   p.status = status;
+  p.partials = nullptr;
   const int mt = (M + BM - 1) / BM, nt = (N + bn - 1) / bn;
   const int tiles = mt * nt * splits;
-  const int grid = tiles < num_sms() ? tiles : num_sms();
+  int grid = tiles < num_sms() ? tiles : num_sms();
+  bool fixup = false;
+  if (balanced && plan_balanced(tiles, num_kb, num_sms(), &p.sched, &fixup)) {
+    p.partials = static_cast<float*>(workspace);
+    grid = p.sched.dp_tiles > 0 ? num_sms() : p.sched.sk_workers;
+  } else {
+    p.sched.dp_tiles = p.sched.sk_tiles = p.sched.sk_workers = p.sched.sk_slots = 0;
+  }
 
 #define SB_DISPATCH(BN_)                                                                   \
   do {                                                                                     \
@@ -411,6 +434,14 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* R
 #undef SB_DISPATCH
   if (rc) return rc;
 
+  if (fixup) {
+    dim3 fg(p.sched.sk_tiles, BM * bn / (256 * 4));
+    __nv_bfloat16* c = static_cast<__nv_bfloat16*>(C);
+    const __nv_bfloat16* r = static_cast<const __nv_bfloat16*>(R);
+    if (bn == 256) balanced_fixup_kernel<BM, 256><<<fg, 256, 0, stream>>>(p.sched, p.partials, c, ldc, r, ldr, M, N, mt, num_kb);
+    else balanced_fixup_kernel<BM, 128><<<fg, 256, 0, stream>>>(p.sched, p.partials, c, ldc, r, ldr, M, N, mt, num_kb);
+    if (cudaGetLastError() != cudaSuccess) return SB_ERR_LAUNCH;
+  }
   if (splits > 1) {
     const size_t mn = static_cast<size_t>(M) * N;
     const int threads = 256;

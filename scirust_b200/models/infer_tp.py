@@ -86,16 +86,17 @@ class TPInferenceEngine(InferenceEngine):
         v_cols = ((H + Hkv) * dh + kv0 * dh, (H + Hkv) * dh + (kv0 + hkv) * dh)
         fl = ff // W
         prep = self._prep
-        self.embed = model.embed.detach()
+        # copies, so that the caller may drop the full model (its flat parameter buffer) afterwards
+        self.embed = model.embed.detach().clone()
         self.layers = []
         for l in model.layers:
             wqkv = _cols(l.wqkv.detach(), [q_cols, k_cols, v_cols])
             wo = l.wo.detach()[r * hq * dh:(r + 1) * hq * dh].contiguous()
             wgu = _cols(l.wgu.detach(), [(r * fl, (r + 1) * fl), (ff + r * fl, ff + (r + 1) * fl)])
             wd = l.wd.detach()[r * fl:(r + 1) * fl].contiguous()
-            self.layers.append({"rms1": l.rms_attn.detach(), "wqkv": prep(wqkv), "wo": prep(wo),
-                                "rms2": l.rms_ffn.detach(), "wgu": prep(wgu), "wd": prep(wd)})
-        self.rms_final = model.rms_final.detach()
+            self.layers.append({"rms1": l.rms_attn.detach().clone(), "wqkv": prep(wqkv), "wo": prep(wo),
+                                "rms2": l.rms_ffn.detach().clone(), "wgu": prep(wgu), "wd": prep(wd)})
+        self.rms_final = model.rms_final.detach().clone()
         vl = cfg.vocab_size // W
         self.head_t = prep(model.head_weight().detach()[r * vl:(r + 1) * vl].t().contiguous())
 

@@ -53,6 +53,12 @@ def _check2d(t: torch.Tensor, name: str) -> None:
 # CTA-pair kernel (csrc/gemm_pair_tcgen05.cu): 256 x 256 tiles on two SMs. "auto" uses it for
 # products with at least one full wave of such tiles and no split-K; SB_GEMM_PAIR=0/1 forces it.
 PAIR_MODE = os.environ.get("SB_GEMM_PAIR", "auto")
+BALANCED = os.environ.get("SB_GEMM_BALANCED", "1") != "0"
+
+
+# The balanced schedule pays a fix-up pass and fp32 scratch traffic; it wins when a tile is long
+# (weight-gradient products, K = tokens) and loses on short-K products, where whole tiles per CTA stay.
+_BALANCED_MIN_K = 4096
 
 
 def _use_pair(M, N, K, splits, bn) -> bool:
@@ -60,7 +66,10 @@ def _use_pair(M, N, K, splits, bn) -> bool:
         return False
     if PAIR_MODE == "1":
         return True
-    return ((M + 255) // 256) * ((N + 255) // 256) >= _NUM_SMS // 2 and K >= 256
+    pair_tiles = ((M + 255) // 256) * ((N + 255) // 256)
+    if BALANCED and K >= _BALANCED_MIN_K:
+        return pair_tiles >= 16          # long tiles are dealt out in k-blocks, any tile count balances
+    return pair_tiles >= _NUM_SMS // 2 and K >= 256
 
 
 def _gemm(a, b, M, N, K, a_mn, b_mn, out, residual, splits, bn):
@@ -77,24 +86,32 @@ def _gemm(a, b, M, N, K, a_mn, b_mn, out, residual, splits, bn):
         _check2d(residual, "residual")
         if tuple(residual.shape) != (M, N):
             raise ValueError("residual shape mismatch")
+    long_k = K >= _BALANCED_MIN_K
     if _use_pair(M, N, K, splits, bn):
         st = _lib.status_word(a.device)
+        ws = _workspace((_NUM_SMS // 2) * 3 * 256 * 256, a.device) if (BALANCED and long_k) else None
         _lib.call("sb_gemm_pair_bf16", a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(residual), M, N, K,
                   a.stride(0), b.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
-                  int(a_mn), int(b_mn), st.data_ptr(), _lib.stream())
+                  int(a_mn), int(b_mn), _lib.ptr(ws), st.data_ptr(), _lib.stream())
         launch_count += 1
         return out
     if bn is None:
         bn = 128 if N <= 128 else 256
     if splits is None:
-        splits = _pick_splits(M, N, K, bn)
-    ws = _workspace(splits * M * N, a.device) if splits > 1 else None
+        # balanced schedule: whole waves one tile per CTA, the last partial wave's k-blocks dealt out
+        # evenly over all SMs and finished by a fix-up pass (fixed k order)
+        splits = 0 if (BALANCED and long_k) else _pick_splits(M, N, K, bn)
+    if splits == 0:
+        ws = _workspace(_NUM_SMS * 3 * 128 * 256, a.device)
+    else:
+        ws = _workspace(splits * M * N, a.device) if splits > 1 else None
     st = _lib.status_word(a.device)
     _lib.call("sb_gemm_bf16", a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(residual), M, N, K,
               a.stride(0), b.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
               int(a_mn), int(b_mn), splits, _lib.ptr(ws), bn, st.data_ptr(), _lib.stream())
     launch_count += 2 if splits > 1 else 1
     return out
+
 
 
 def _ref(a, b, residual, out):

@@ -77,7 +77,7 @@ def test_strided_views():
     assert out[:, :512].abs().max().item() == 0 and out[:, 768:].abs().max().item() == 0
 
 
-PAIR_SHAPES = [(256, 256, 64), (512, 768, 512), (300, 264, 1000), (4096, 1536, 1024), (2176, 2816, 520)]
+PAIR_SHAPES = [(256, 256, 64), (512, 768, 512), (304, 264, 1000), (4096, 1536, 1024), (2176, 2816, 520)]
 
 
 @pytest.mark.parametrize("M,N,K", PAIR_SHAPES)
@@ -106,6 +106,7 @@ def test_cta_pair_kernel_all_forms(M, N, K, form, monkeypatch):
 def test_cta_pair_kernel_is_bitwise_repeatable_and_matches_single_cta(monkeypatch):
     from scirust_b200.ops import gemm
     x, w = _mk((4096, 1024), 1), _mk((1024, 2816), 2)
+    monkeypatch.setattr(gemm, "BALANCED", False)
     monkeypatch.setattr(gemm, "PAIR_MODE", "1")
     y1 = ops.matmul_nn(x, w)
     y2 = ops.matmul_nn(x, w)
@@ -115,3 +116,40 @@ def test_cta_pair_kernel_is_bitwise_repeatable_and_matches_single_cta(monkeypatc
     assert torch.equal(y1, y2)
     # same K order and fp32 accumulation in both kernels: identical results
     assert torch.equal(y1, y0)
+
+
+@pytest.mark.parametrize("M,N,K", [(16384, 1024, 1024), (1024, 1536, 16384), (2816, 1024, 8192), (200, 264, 136),
+                                   (19072, 256, 512), (16, 6144, 4096)])
+def test_balanced_schedule_matches_plain_schedule_bitwise(M, N, K, monkeypatch):
+    """Whole waves one tile per CTA, the last partial wave dealt out in k-blocks and summed by the
+    fix-up pass in k order: fp32 partial sums are added in a fixed order, so two runs agree bit for
+    bit, and the result matches fp32 within bf16 rounding for every operand form."""
+    from scirust_b200.ops import gemm
+    monkeypatch.setattr(gemm, "PAIR_MODE", "0")
+    monkeypatch.setattr(gemm, "BALANCED", True)
+    monkeypatch.setattr(gemm, "_BALANCED_MIN_K", 0)
+    x, w, r = _mk((M, K), 1), _mk((K, N), 2), _mk((M, N), 3)
+    y1 = ops.matmul_nn(x, w, residual=r)
+    y2 = ops.matmul_nn(x, w, residual=r)
+    assert torch.equal(y1, y2)
+    _check(y1, x.float() @ w.float() + r.float(), K)
+    a, b = _mk((K, M), 5), _mk((K, N), 6)
+    _check(ops.matmul_tn(a, b), a.float().t() @ b.float(), K)
+    bt = _mk((N, K), 7)
+    _check(ops.matmul_nt(x, bt), x.float() @ bt.float().t(), K)
+
+
+@pytest.mark.parametrize("M,N,K", [(1024, 1536, 16384), (2816, 1024, 8192), (5632, 1024, 4096), (300, 520, 704)])
+def test_cta_pair_kernel_with_balanced_schedule(M, N, K, monkeypatch):
+    from scirust_b200.ops import gemm
+    monkeypatch.setattr(gemm, "PAIR_MODE", "1")
+    monkeypatch.setattr(gemm, "BALANCED", True)
+    monkeypatch.setattr(gemm, "_BALANCED_MIN_K", 0)
+    Mt = (M + 7) // 8 * 8
+    a, b, r = _mk((K, Mt), 5), _mk((K, N), 6), _mk((Mt, N), 3)
+    y1 = ops.matmul_tn(a, b, residual=r)
+    y2 = ops.matmul_tn(a, b, residual=r)
+    assert torch.equal(y1, y2)
+    _check(y1, a.float().t() @ b.float() + r.float(), K)
+    x, w = _mk((M, K), 1), _mk((K, N), 2)
+    _check(ops.matmul_nn(x, w), x.float() @ w.float(), K)
