@@ -16,6 +16,7 @@ import argparse
 import glob
 import hashlib
 import json
+import math
 import sys
 import time
 
@@ -227,6 +228,120 @@ def cmd_verify(a):
     return EXIT_OK if not errs else EXIT_FAIL
 
 
+def _matrix(a):
+    """Weight matrix for the quantiser commands: a tensor of a safetensors file, or seeded noise."""
+    import torch
+    if a.weights:
+        from .io.safetensors import load_file
+        sd = load_file(a.weights)
+        key = a.tensor or sorted(sd)[0]
+        return torch.as_tensor(sd[key]).float()
+    g = torch.Generator().manual_seed(a.seed)
+    return torch.randn(a.rows, a.cols, generator=g) * 0.05
+
+
+def cmd_quantizer(a):
+    """gptq / awq / bitnet / int4: quantise one matrix, report the reconstruction error."""
+    import torch
+    from . import quantization as Q
+    w = _matrix(a)
+    g = torch.Generator().manual_seed(a.seed + 1)
+    x = torch.randn(256, w.shape[0], generator=g)
+    if a.cmd == "gptq":
+        wq = Q.gptq_quantize(w, x, bits=a.bits)
+    elif a.cmd == "awq":
+        wq, _scales = Q.awq_quantize(w, x, bits=a.bits)
+    elif a.cmd == "bitnet":
+        t, scale = Q.ternary_quantize(w)
+        wq = t.float() * scale
+    else:
+        packed, scale, shape, pad = Q.int4_group_quantize(w, group=a.group)
+        wq = Q.int4_group_dequantize(packed, scale, shape, pad, group=a.group)
+    wq = torch.as_tensor(wq).float().reshape(w.shape)
+    werr = ((wq - w).norm() / w.norm()).item()
+    yerr = ((x @ wq - x @ w).norm() / (x @ w).norm()).item()
+    print(f"{a.cmd} shape {tuple(w.shape)} weight_rel_err {werr:.6f} output_rel_err {yerr:.6f}")
+    return EXIT_OK if math.isfinite(yerr) else EXIT_NUMERICAL
+
+
+def cmd_kvcache(a):
+    """Attention error and bytes per token of every KV-cache backend on seeded data."""
+    import torch
+    from .nn import kv_cache as KV
+    g = torch.Generator().manual_seed(a.seed)
+    d = a.head_dim
+    ks, vs, q = torch.randn(a.tokens, d, generator=g), torch.randn(a.tokens, d, generator=g), torch.randn(d, generator=g)
+    ref = KV.PlainKvCache(d)
+    caches = {"plain": KV.PlainKvCache(d), "paged": KV.PagedKvCache(d, page=16), "int8": KV.QuantKvCache(d, bits=8),
+              "int4": KV.QuantKvCache(d, bits=4), "latent": KV.LatentKvCache(d, rank=max(4, d // 2))}
+    for t in range(a.tokens):
+        ref.append(ks[t], vs[t])
+        for c in caches.values():
+            c.append(ks[t], vs[t])
+    want = ref.decode_step(q)
+    for name, c in caches.items():
+        err = ((c.decode_step(q) - want).norm() / want.norm()).item()
+        print(f"{name} rel_err {err:.6f} bytes_per_token {c.nbytes() / max(len(c), 1):.1f}")
+    return EXIT_OK
+
+
+def cmd_onnx(a):
+    from .io import onnx_json as OJ
+    from .nn import modules as M
+    from .nn.rng import PcgEngine
+    if a.action == "export":
+        rng = PcgEngine(a.seed)
+        dims = a.layers
+        layers = []
+        for i in range(len(dims) - 1):
+            layers.append(M.Linear(dims[i], dims[i + 1], rng=rng))
+            if i + 2 < len(dims):
+                layers.append(M.ReLU())
+        text = OJ.export_sequential(M.Sequential(*layers), a.name, (-1, dims[0]))
+        with open(a.file, "w") as f:
+            f.write(text)
+        print(f"wrote {a.file} ({len(text)} bytes)")
+        return EXIT_OK
+    g = OJ.import_onnx_json(open(a.file).read())
+    print(f"{g.doc['name']}: {len(g.nodes)} nodes, {len(g.weights())} initializers")
+    for n in g.nodes:
+        print(f"  {n['op_type']} {n['inputs']} -> {n['outputs']}")
+    return EXIT_OK
+
+
+def cmd_plan(a):
+    from .models import SciAgentConfig
+    from .utils import planning
+    cfg = SciAgentConfig.preset(a.model)
+    pl = planning.plan(cfg, a.batch, a.seq, tp=a.tp)
+    print(f"{a.model}: {planning.n_params(cfg)} parameters, batch {a.batch} x seq {a.seq}, tp {a.tp}")
+    for mode in ("flash", "naive"):
+        print(f"  {mode}: {pl.total(mode) / (1 << 30):.2f} GiB  fits_180GB {pl.fits(mode)}")
+    return EXIT_OK
+
+
+def cmd_calibrate(a):
+    """calibrate / conformal on a ``.pt`` file holding {"logits": [N, C], "labels": [N]}."""
+    import torch
+    from . import calibration as C
+    d = torch.load(a.data)
+    logits, labels = d["logits"].float(), d["labels"].long()
+    if logits.dim() != 2 or labels.shape[0] != logits.shape[0]:
+        raise ValueError("expected logits [N, C] and labels [N]")
+    n = logits.shape[0] // 2
+    if a.cmd == "calibrate":
+        t = C.fit_temperature(logits[:n], labels[:n])
+        before = C.expected_calibration_error(torch.softmax(logits[n:], -1), labels[n:])
+        after = C.expected_calibration_error(torch.softmax(logits[n:] / t, -1), labels[n:])
+        print(f"temperature {t:.4f} ece_before {before:.4f} ece_after {after:.4f}")
+    else:
+        thr = C.conformal_threshold(torch.softmax(logits[:n], -1), labels[:n], a.alpha)
+        sets = C.conformal_sets(torch.softmax(logits[n:], -1), thr)
+        cover = sets.gather(1, labels[n:, None]).float().mean().item()
+        print(f"threshold {thr:.4f} coverage {cover:.4f} mean_set_size {sets.float().sum(1).mean().item():.3f}")
+    return EXIT_OK
+
+
 def build_parser():
     p = _Parser(prog="scirust", description="scirust_b200 command line")
     sub = p.add_subparsers(dest="cmd")
@@ -289,6 +404,39 @@ def build_parser():
     s.add_argument("--out", default="model.int4.bin")
     s.add_argument("--group", type=int, default=32)
     s.set_defaults(fn=cmd_sciagent)
+    for name in ("gptq", "awq", "bitnet", "int4"):
+        qz = sub.add_parser(name)
+        qz.add_argument("--weights", default="")
+        qz.add_argument("--tensor", default="")
+        qz.add_argument("--rows", type=int, default=128)
+        qz.add_argument("--cols", type=int, default=64)
+        qz.add_argument("--bits", type=int, default=4)
+        qz.add_argument("--group", type=int, default=32)
+        qz.add_argument("--seed", type=int, default=0)
+        qz.set_defaults(fn=cmd_quantizer)
+    kc = sub.add_parser("kvcache")
+    kc.add_argument("--tokens", type=int, default=64)
+    kc.add_argument("--head-dim", type=int, default=32)
+    kc.add_argument("--seed", type=int, default=0)
+    kc.set_defaults(fn=cmd_kvcache)
+    ox = sub.add_parser("onnx")
+    ox.add_argument("action", choices=["export", "inspect"])
+    ox.add_argument("--file", required=True)
+    ox.add_argument("--name", default="model")
+    ox.add_argument("--layers", type=int, nargs="*", default=[4, 8, 2])
+    ox.add_argument("--seed", type=int, default=0)
+    ox.set_defaults(fn=cmd_onnx)
+    pl = sub.add_parser("plan")
+    pl.add_argument("--model", default="gqa_12l")
+    pl.add_argument("--batch", type=int, default=8)
+    pl.add_argument("--seq", type=int, default=2048)
+    pl.add_argument("--tp", type=int, default=1)
+    pl.set_defaults(fn=cmd_plan)
+    for name in ("calibrate", "conformal"):
+        cb = sub.add_parser(name)
+        cb.add_argument("--data", required=True)
+        cb.add_argument("--alpha", type=float, default=0.1)
+        cb.set_defaults(fn=cmd_calibrate)
     v = sub.add_parser("verify")
     v.add_argument("action", choices=["emit", "verify"])
     v.add_argument("--artifact", required=True)

@@ -279,3 +279,43 @@ def test_onnx_json_export_import_roundtrip():
         OJ.run_graph(OJ.import_onnx_json(broken), x) if '"param_9"' in broken else (_ for _ in ()).throw(ValueError())
     with pytest.raises(ValueError):
         OJ.import_onnx_json('{"name": "x"}')
+
+
+def test_cli_quantizer_kvcache_onnx_plan_calibrate_commands(tmp_path, capsys):
+    from scirust_b200 import cli
+    for cmd in ("gptq", "awq", "bitnet", "int4"):
+        assert cli.run([cmd, "--rows", "64", "--cols", "32"]) == 0
+        assert "output_rel_err" in capsys.readouterr().out
+    assert cli.run(["kvcache", "--tokens", "40"]) == 0
+    out = capsys.readouterr().out
+    assert "paged rel_err 0.000000" in out and "int4 rel_err" in out
+    f = str(tmp_path / "m.json")
+    assert cli.run(["onnx", "export", "--file", f, "--layers", "4", "8", "3"]) == 0
+    assert cli.run(["onnx", "inspect", "--file", f]) == 0
+    assert "Gemm" in capsys.readouterr().out
+    assert cli.run(["plan", "--model", "gqa_12l"]) == 0
+    assert "fits_180GB True" in capsys.readouterr().out
+    torch.manual_seed(0)
+    labels = torch.randint(0, 5, (400,))
+    logits = F.one_hot(labels, 5).float() * 2.0 + torch.randn(400, 5)
+    torch.save({"logits": logits * 4.0, "labels": labels}, tmp_path / "d.pt")     # over-confident by 4x
+    assert cli.run(["calibrate", "--data", str(tmp_path / "d.pt")]) == 0
+    line = capsys.readouterr().out.split()
+    t, before, after = float(line[1]), float(line[3]), float(line[5])
+    assert 2.0 < t < 8.0 and after < before
+    assert cli.run(["conformal", "--data", str(tmp_path / "d.pt"), "--alpha", "0.1"]) == 0
+    cov = float(capsys.readouterr().out.split()[3])
+    assert cov > 0.8
+    assert cli.run(["calibrate", "--data", str(tmp_path / "missing.pt")]) == 2
+
+
+def test_interval_bounds_are_sound():
+    from scirust_b200 import calibration as C
+    torch.manual_seed(1)
+    layers = [(torch.randn(4, 6), torch.randn(6)), (torch.randn(6, 3), torch.randn(3))]
+    x0 = torch.randn(4)
+    lo, hi = C.interval_bounds(layers, x0 - 0.1, x0 + 0.1)
+    for _ in range(200):
+        x = x0 + (torch.rand(4) - 0.5) * 0.2
+        y = torch.relu(x @ layers[0][0] + layers[0][1]) @ layers[1][0] + layers[1][1]
+        assert (y >= lo - 1e-5).all() and (y <= hi + 1e-5).all()
