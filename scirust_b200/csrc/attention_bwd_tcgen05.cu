@@ -17,6 +17,8 @@
 
 namespace sb {
 
+int make_tmap_3d_bf16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t pitch1,
+                      uint64_t pitch2, uint32_t box0, uint32_t box1);
 int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
                       uint32_t box_inner, uint32_t box_outer);
 
@@ -33,6 +35,7 @@ struct BwdParams {
   const float2* stats; // [B,H,S] (lse * log2(e), delta), written by attn_delta_kernel
   __nv_bfloat16* dqkv; // [B*S, ld_dqkv]
   int* status;
+  int spill_ds;        // dK/dV kernel also stores every dS tile to the [B*H, S, S] scratch (see dQ below)
 };
 
 // Store 32 bf16 (packed in 16 words) of row r, columns [c*32, c*32+32) into a [128 x 128] bf16 tile
@@ -85,21 +88,26 @@ __device__ __forceinline__ void bwd_chunk(uint32_t tm_S, uint32_t tm_dP, uint32_
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                   const float* __restrict__ lse, float2* __restrict__ stats, int B, int S, int H,
                                   int dh, int ld_o, int ld_do) {
-  const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  // a group of dh/8 lanes (8 or 16) owns one (token, head): 16-byte loads, then a butterfly inside the group
+  const int gl = dh >> 3;                       // lanes per group
+  const int gpw = 32 / gl;                      // groups per warp
   const int lane = threadIdx.x & 31;
-  if (w >= B * S * H) return;
-  const int row = w / H, h = w - row * H;
-  const __nv_bfloat16* po = o + static_cast<size_t>(row) * ld_o + h * dh;
-  const __nv_bfloat16* pd = d_o + static_cast<size_t>(row) * ld_do + h * dh;
+  const int sub = lane % gl;
+  const long long w = (static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * gpw + lane / gl;
+  const bool live = w < static_cast<long long>(B) * S * H;
   float acc = 0.f;
-  for (int c = lane * 2; c < dh; c += 64) {
-    const uint32_t a = *reinterpret_cast<const uint32_t*>(po + c);
-    const uint32_t g = *reinterpret_cast<const uint32_t*>(pd + c);
-    acc += bf16_lo(a) * bf16_lo(g) + bf16_hi(a) * bf16_hi(g);
+  int row = 0, h = 0;
+  if (live) {
+    row = static_cast<int>(w / H);
+    h = static_cast<int>(w - static_cast<long long>(row) * H);
+    const uint4 a = *reinterpret_cast<const uint4*>(o + static_cast<size_t>(row) * ld_o + h * dh + sub * 8);
+    const uint4 g = *reinterpret_cast<const uint4*>(d_o + static_cast<size_t>(row) * ld_do + h * dh + sub * 8);
+    acc = bf16_lo(a.x) * bf16_lo(g.x) + bf16_hi(a.x) * bf16_hi(g.x) + bf16_lo(a.y) * bf16_lo(g.y) +
+          bf16_hi(a.y) * bf16_hi(g.y) + bf16_lo(a.z) * bf16_lo(g.z) + bf16_hi(a.z) * bf16_hi(g.z) +
+          bf16_lo(a.w) * bf16_lo(g.w) + bf16_hi(a.w) * bf16_hi(g.w);
   }
-#pragma unroll
-  for (int o2 = 16; o2 > 0; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
-  if (lane == 0) {
+  for (int o2 = gl >> 1; o2 > 0; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
+  if (live && sub == 0) {
     const int b = row / S, s = row - b * S;
     const size_t idx = (static_cast<size_t>(b) * H + h) * S + s;
     stats[idx] = make_float2(lse[idx] * LOG2E, acc);
@@ -126,7 +134,7 @@ struct DkvCfg {
 template <int DH>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
-                         const BwdParams p) {
+                         const __grid_constant__ CUtensorMap tm_ds, const BwdParams p) {
   using Cfg = DkvCfg<DH>;
   constexpr int NCH = DH / 64;
   extern __shared__ uint8_t smem_raw[];
@@ -251,6 +259,18 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __gri
       for (int t = 0; t < n_iter && ok; ++t) {
         if (!mbar_wait(p_full, t & 1, p.status, ST_TIMEOUT_MISC)) { ok = false; break; }
         tc_fence_after();
+        if (p.spill_ds) {
+          // the finished dS tile (bf16, [q rows][kv], scale included) also goes to global memory, where
+          // the dQ kernel streams it back instead of recomputing scores; the bulk store reads shared
+          // memory asynchronously, so it must have been read out before this buffer is written again
+          const int head = kvh * group + t / n_qt;
+          const int qt = qt_first + t % n_qt;
+          const uint8_t* src = sdST + (Cfg::PDB ? (t & 1) : 0) * Cfg::PT_BYTES;
+          tma_store_wait_read<0>();
+          tma_store_3d(&tm_ds, src, kv0, qt * BT, b * p.H + head);
+          tma_store_3d(&tm_ds, src + BT * 128, kv0 + 64, qt * BT, b * p.H + head);
+          tma_store_commit();
+        }
         if (Cfg::PDB) {
           // scores of t+1 first: their commit also covers the gradient MMAs of t-1, which is what
           // lets the softmax warps reuse the P^T/dS^T buffer of parity (t+1)&1.
@@ -258,10 +278,12 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __gri
           issue_grads(t);
         } else {
           issue_grads(t);
+          if (p.spill_ds) tma_store_wait_read<0>();   // single dS buffer: read out before it is rewritten
           if (t + 1 < n_iter) ok = issue_scores();
         }
       }
       if (ok) umma_commit(done);
+      if (p.spill_ds) tma_store_wait<0>();   // the stores are complete before the CTA retires
     }
   } else {
     const int sw = warp - 2;        // 0..7
@@ -546,22 +568,152 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
 
+
+// --------------------------------------------------------------------------- dQ from stored dS
+// When the dK/dV kernel has spilled its dS tiles (bf16 [B*H, S, S], scale included), dQ = dS K is a
+// plain streamed product: no scores, no exponentials. One CTA per (query tile, head, batch) walks the
+// kv tiles in ascending order through a TMA ring of (dS tile, K tile) pairs and accumulates in TMEM.
+// It is bound by the bytes of dS (half of S x S per head under the causal mask).
 template <int DH>
-static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& td, const BwdParams& p, cudaStream_t stream) {
+struct DqsCfg {
+  static constexpr int DS_BYTES = BT * BT * 2;
+  static constexpr int K_BYTES = BT * DH * 2;
+  static constexpr int STAGE_BYTES = DS_BYTES + K_BYTES;
+  static constexpr int STAGES = (DH == 64) ? 4 : 3;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 128;
+  static constexpr int TMEM_COLS = DH;
+};
+
+template <int DH>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attention_bwd_dq_stream_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_ds,
+                               const BwdParams p) {
+  using Cfg = DqsCfg<DH>;
+  constexpr int NCH = DH / 64;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + Cfg::STAGES;
+  uint64_t* done = empty + Cfg::STAGES;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(done + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_t = (p.S + BT - 1) / BT;
+  const int qt = n_t - 1 - blockIdx.x;   // longest rows of tiles first
+  const int head = blockIdx.y, b = blockIdx.z;
+  const int kvh = head / (p.H / p.Hkv);
+  const int q0 = qt * BT;
+  const int row_base = b * p.S;
+  const int n_blocks = p.causal ? (qt + 1) : n_t;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(done, 1);
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 0 && lane == 0) { prefetch_tmap(&tm_qkv); prefetch_tmap(&tm_ds); }
+  if (warp == 1) { tmem_alloc(tmem_holder, Cfg::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm_dQ = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int st = 0;
+      uint32_t ph = 0;
+      for (int j = 0; j < n_blocks; ++j) {
+        if (!mbar_wait(&empty[st], ph ^ 1, p.status, ST_TIMEOUT_EMPTY)) break;
+        uint8_t* sdS = smem + st * Cfg::STAGE_BYTES;
+        uint8_t* sK = sdS + Cfg::DS_BYTES;
+        mbar_arrive_expect_tx(&full[st], Cfg::STAGE_BYTES);
+        tma_load_3d(sdS, &tm_ds, &full[st], j * BT, q0, b * p.H + head);
+        tma_load_3d(sdS + BT * 128, &tm_ds, &full[st], j * BT + 64, q0, b * p.H + head);
+#pragma unroll
+        for (int c = 0; c < NCH; ++c)
+          tma_load_2d(sK + c * (BT * 128), &tm_qkv, &full[st], (p.H + kvh) * DH + c * 64, row_base + j * BT);
+        if (++st == Cfg::STAGES) { st = 0; ph ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_g = make_idesc_bf16(BT, DH, false, true);
+      int st = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        if (!mbar_wait(&full[st], ph, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t adS = smem_u32(smem + st * Cfg::STAGE_BYTES), bK = adS + Cfg::DS_BYTES;
+#pragma unroll
+        for (int k = 0; k < BT / 16; ++k) {
+          const uint32_t aoff = (k >> 2) * (BT * 128) + (k & 3) * 32;
+          umma_bf16_ss(tm_dQ, make_smem_desc(adS + aoff, 16, 1024), make_smem_desc(bK + k * (16 * 128), BT * 128, 1024),
+                       idesc_g, (j > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty[st]);
+        if (++st == Cfg::STAGES) { st = 0; ph ^= 1; }
+      }
+      if (ok) umma_commit(done);
+    }
+  } else {
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int r = q * 32 + lane;
+    const int q_idx = q0 + r;
+    const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
+    if (mbar_wait(done, 0, p.status, ST_TIMEOUT_TMEM_FULL)) {
+      tc_fence_after();
+      constexpr int CPW = DH / 64;
+#pragma unroll 1
+      for (int cc = 0; cc < CPW; ++cc) {
+        const int c = half * CPW + cc;
+        uint32_t v[32];
+        tmem_ld_32x32(tm_dQ + lane_off + c * 32, v);
+        tmem_ld_wait();
+        if (q_idx < p.S) {
+          __nv_bfloat16* dst = p.dqkv + static_cast<size_t>(row_base + q_idx) * p.ld_dqkv + head * DH + c * 32;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(v[u * 8 + 0]), __uint_as_float(v[u * 8 + 1]));
+            w.y = pack_bf16x2(__uint_as_float(v[u * 8 + 2]), __uint_as_float(v[u * 8 + 3]));
+            w.z = pack_bf16x2(__uint_as_float(v[u * 8 + 4]), __uint_as_float(v[u * 8 + 5]));
+            w.w = pack_bf16x2(__uint_as_float(v[u * 8 + 6]), __uint_as_float(v[u * 8 + 7]));
+            *reinterpret_cast<uint4*>(dst + u * 8) = w;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tm_dQ, Cfg::TMEM_COLS);
+}
+
+template <int DH>
+static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& td, const CUtensorMap& tds, const BwdParams& p,
+                      cudaStream_t stream) {
   auto k1 = attention_bwd_dkv_kernel<DH>;
   auto k2 = attention_bwd_dq_kernel<DH>;
+  auto k3 = attention_bwd_dq_stream_kernel<DH>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<DH>::SMEM_BYTES) !=
             cudaSuccess ||
-        cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, DqCfg<DH>::SMEM_BYTES) != cudaSuccess)
+        cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, DqCfg<DH>::SMEM_BYTES) != cudaSuccess ||
+        cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, DqsCfg<DH>::SMEM_BYTES) != cudaSuccess)
       return SB_ERR_LAUNCH;
     attr_set = true;
   }
   const int n_t = (p.S + BT - 1) / BT;
-  k1<<<dim3(n_t, p.Hkv, p.B), BWD_THREADS, DkvCfg<DH>::SMEM_BYTES, stream>>>(tq, td, p);
+  k1<<<dim3(n_t, p.Hkv, p.B), BWD_THREADS, DkvCfg<DH>::SMEM_BYTES, stream>>>(tq, td, tds, p);
   if (cudaGetLastError() != cudaSuccess) return SB_ERR_LAUNCH;
-  k2<<<dim3(n_t, p.H, p.B), BWD_THREADS, DqCfg<DH>::SMEM_BYTES, stream>>>(tq, td, p);
+  if (p.spill_ds) k3<<<dim3(n_t, p.H, p.B), BWD_THREADS, DqsCfg<DH>::SMEM_BYTES, stream>>>(tq, tds, p);
+  else k2<<<dim3(n_t, p.H, p.B), BWD_THREADS, DqCfg<DH>::SMEM_BYTES, stream>>>(tq, td, p);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
 
@@ -571,10 +723,16 @@ using namespace sb;
 
 // qkv, dqkv: bf16 [B*S, ld]; O, dO: bf16 [B*S, ld_o / ld_do] (H*dh columns); lse: fp32 [B,H,S];
 // delta: scratch of 2*B*H*S floats written here ((lse*log2e, delta) pairs). dqkv receives dQ | dK | dV in
-// the qkv layout.
+// the qkv layout. ds_scratch (optional): B*H*S*round_up(S, 64) bf16; with it the dK/dV kernel stores its
+// dS tiles there and dQ is computed by streaming them back (faster: no second pass over the scores);
+// without it dQ recomputes scores and exponentials.
+extern "C" size_t sb_attention_bwd_ds_elems(int B, int S, int H) {
+  return static_cast<size_t>(B) * H * S * ((S + 63) / 64 * 64);
+}
+
 extern "C" int sb_attention_bwd(const void* qkv, const void* O, const float* lse, const void* dO, void* dqkv,
-                                float* delta, int B, int S, int H, int Hkv, int dh, int ld, int ld_o, int ld_do,
-                                float scale, int causal, int* status, void* stream_) {
+                                float* delta, void* ds_scratch, int B, int S, int H, int Hkv, int dh, int ld,
+                                int ld_o, int ld_do, float scale, int causal, int* status, void* stream_) {
   if (B <= 0 || S <= 0 || H <= 0 || Hkv <= 0 || (H % Hkv) || (dh != 64 && dh != 128)) return SB_ERR_ARG;
   if ((ld & 7) || (reinterpret_cast<uintptr_t>(dqkv) & 15)) return SB_ERR_ALIGN;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -583,8 +741,12 @@ extern "C" int sb_attention_bwd(const void* qkv, const void* O, const float* lse
   if (rc) return rc;
   rc = make_tmap_2d_bf16(&td, dO, static_cast<uint64_t>(H) * dh, static_cast<uint64_t>(B) * S, ld_do, 64, 128);
   if (rc) return rc;
-  const int warps = B * S * H;
-  attn_delta_kernel<<<(warps + 7) / 8, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(O),
+  if ((ld_o & 7) || (ld_do & 7) || (reinterpret_cast<uintptr_t>(O) & 15) || (reinterpret_cast<uintptr_t>(dO) & 15))
+    return SB_ERR_ALIGN;
+  const long long groups = static_cast<long long>(B) * S * H;
+  const int gpw = 32 / (dh / 8);
+  const long long warps = (groups + gpw - 1) / gpw;
+  attn_delta_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(O),
                                                          static_cast<const __nv_bfloat16*>(dO), lse,
                                                          reinterpret_cast<float2*>(delta), B, S, H, dh, ld_o,
                                                          ld_do);
@@ -599,5 +761,12 @@ extern "C" int sb_attention_bwd(const void* qkv, const void* O, const float* lse
   p.stats = reinterpret_cast<const float2*>(delta);
   p.dqkv = static_cast<__nv_bfloat16*>(dqkv);
   p.status = status;
-  return dh == 64 ? launch_bwd<64>(tq, td, p, stream) : launch_bwd<128>(tq, td, p, stream);
+  p.spill_ds = ds_scratch ? 1 : 0;
+  CUtensorMap tds = tq;   // placeholder when unused
+  if (ds_scratch) {
+    const uint64_t sp = (static_cast<uint64_t>(S) + 63) / 64 * 64;
+    rc = make_tmap_3d_bf16(&tds, ds_scratch, S, S, static_cast<uint64_t>(B) * H, sp, sp * S, 64, 128);
+    if (rc) return rc;
+  }
+  return dh == 64 ? launch_bwd<64>(tq, td, tds, p, stream) : launch_bwd<128>(tq, td, tds, p, stream);
 }

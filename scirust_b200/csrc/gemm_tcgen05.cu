@@ -319,6 +319,23 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64
   return r == CUDA_SUCCESS ? 0 : SB_ERR_DRIVER;
 }
 
+// 3-D bf16 tensor map with 128B swizzle: dims (d0 contiguous, d1, d2), pitches in elements; the box is
+// box0 x box1 x 1. Out-of-range parts of a box are zero on loads and dropped on stores.
+int make_tmap_3d_bf16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t pitch1,
+                      uint64_t pitch2, uint32_t box0, uint32_t box1) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return SB_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((pitch1 * 2) & 15) || ((pitch2 * 2) & 15)) return SB_ERR_ALIGN;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {pitch1 * 2, pitch2 * 2};
+  cuuint32_t box[3] = {box0, box1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : SB_ERR_DRIVER;
+}
+
 // 2-D tensor map over 16-bit words without swizzle (row-major copy of a box into shared memory).
 // Used by the weight-streaming kernels: `inner` 2-byte words are contiguous, `pitch_bytes` is the row
 // pitch. Out-of-range parts of a box are filled with zeros.

@@ -7,6 +7,7 @@ re-concatenates per head: scirust-sciagent/src/cuda_model.rs:796-869).
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -15,9 +16,26 @@ from . import gemm as _g
 
 _lib.register("sb_attention_fwd", [_lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32,
                                    _lib.i32, _lib.i32, _lib.f32, _lib.i32, _lib.vp, _lib.vp])
-_lib.register("sb_attention_bwd", [_lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32,
+_lib.register("sb_attention_bwd", [_lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32,
                                    _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.f32,
                                    _lib.i32, _lib.vp, _lib.vp])
+
+# The backward pass spills its dS tiles (bf16 [B*H, S, S]) to a scratch buffer so that dQ is a streamed
+# product instead of a second pass over scores and exponentials; above this size it recomputes instead.
+DS_SCRATCH_LIMIT_BYTES = int(os.environ.get("SB_ATT_DS_SCRATCH_MB", "4096")) << 20
+_ds_scratch: dict = {}
+
+
+def _scratch(B, S, H, device):
+    n = B * H * S * ((S + 63) // 64 * 64)
+    if n * 2 > DS_SCRATCH_LIMIT_BYTES:
+        return None
+    key = str(device)
+    t = _ds_scratch.get(key)
+    if t is None or t.numel() < n:
+        t = torch.empty(n, dtype=torch.bfloat16, device=device)
+        _ds_scratch[key] = t
+    return t
 
 
 def attention_ref(qkv, B, S, H, Hkv, dh, causal=True, scale=None):
@@ -66,8 +84,9 @@ def attention_bwd(qkv, o, lse, do, B, S, H, Hkv, dh, causal=True, scale=None):
         return attention_bwd_ref(qkv, do, B, S, H, Hkv, dh, causal, scale).to(qkv.dtype)
     dqkv = torch.empty_like(qkv)
     delta = torch.empty((B, H, S, 2), dtype=torch.float32, device=qkv.device)
+    ds = _scratch(B, S, H, qkv.device)
     _lib.call("sb_attention_bwd", qkv.data_ptr(), o.data_ptr(), lse.data_ptr(), do.data_ptr(), dqkv.data_ptr(),
-              delta.data_ptr(), B, S, H, Hkv, dh, qkv.stride(0), o.stride(0), do.stride(0), float(scale),
+              delta.data_ptr(), _lib.ptr(ds), B, S, H, Hkv, dh, qkv.stride(0), o.stride(0), do.stride(0), float(scale),
               int(causal), _lib.status_word(qkv.device).data_ptr(), _lib.stream())
     _g.launch_count += 3
     return dqkv

@@ -31,7 +31,10 @@ def test_forward(B, S, H, Hkv, dh, causal):
 
 @pytest.mark.parametrize("B,S,H,Hkv,dh", CASES)
 @pytest.mark.parametrize("causal", [True, False])
-def test_backward(B, S, H, Hkv, dh, causal):
+@pytest.mark.parametrize("spill", [True, False])
+def test_backward(B, S, H, Hkv, dh, causal, spill, monkeypatch):
+    # spill: dQ streams the dS tiles stored by the dK/dV kernel; otherwise it recomputes the scores
+    monkeypatch.setattr(A, "DS_SCRATCH_LIMIT_BYTES", (4 << 30) if spill else 0)
     qkv = _qkv(B, S, H, Hkv, dh, seed=1)
     g = torch.Generator(device="cuda").manual_seed(2)
     do = torch.randn(B * S, H * dh, generator=g, device="cuda").to(torch.bfloat16)
