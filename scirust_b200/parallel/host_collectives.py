@@ -357,6 +357,28 @@ def tcp_tree_all_reduce_rank(rank: int, world: int, addrs, values, combine=Fixed
             srv.close()
 
 
+def tcp_tree_all_reduce_native(rank: int, world: int, addrs, values, timeout: float = 30.0) -> np.ndarray:
+    """Same all-reduce (fp32 fixed-order sum) through the native transport (csrc/rt_collectives.cpp):
+    sockets, framing and the child-ordered sum run in C++ without the interpreter lock, so ranks living
+    in threads of one process overlap. Bitwise identical to ``tcp_tree_all_reduce_rank`` with
+    ``FixedOrderSum``; addresses must be IPv4 literals."""
+    import ctypes as C
+    from ..ops import _lib
+    lib = _lib.rt()
+    fn = lib.sbrt_tcp_tree_allreduce_f32
+    fn.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_char_p), C.POINTER(C.c_int), C.c_void_p, C.c_int64, C.c_int]
+    fn.restype = C.c_int
+    buf = np.ascontiguousarray(values, dtype=np.float32).copy()
+    hosts = (C.c_char_p * world)(*[a[0].encode() for a in addrs])
+    ports = (C.c_int * world)(*[int(a[1]) for a in addrs])
+    rc = fn(rank, world, hosts, ports, buf.ctypes.data, buf.size, int(timeout * 1000))
+    if rc != 0:
+        what = {1: "bad argument", 2: "socket error", 3: "timed out", 4: "protocol error / unexpected rank",
+                5: "out of memory", 6: "peer closed the connection"}.get(rc, str(rc))
+        raise CollectiveError(f"rank {rank}: native tree all-reduce failed: {what}")
+    return buf
+
+
 # ----------------------------------------------------------------------------- data-parallel trainer
 class DataParallelTrainer:
     """``grad_fn(params, x, y) -> (loss, grads)`` is evaluated on ``workers`` contiguous slices of the

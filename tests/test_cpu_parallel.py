@@ -184,3 +184,57 @@ def test_tp_inference_engine_on_gloo_ranks(world, kv):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600,
                        env=dict(os.environ, PYTHONPATH=ROOT, SB_TP_KV=str(kv), SB_TEST_DEVICE="cpu"))
     assert r.returncode == 0 and "TP_INFER_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_native_tcp_tree_allreduce_is_bitwise_the_python_engine_and_interoperates():
+    """The C++ transport (csrc/rt_collectives.cpp) speaks the same frames and sums in the same order:
+    all-native worlds, and worlds mixing native and Python ranks, give the in-process engine's bits."""
+    for world, native_ranks in ((7, set(range(7))), (6, {0, 2, 5}), (2, {1})):
+        xs = _inputs(world, 1000, seed=11)
+        addrs = [("127.0.0.1", p) for p in _free_ports(world)]
+        out, errs = [None] * world, []
+
+        def work(r):
+            try:
+                fn = HC.tcp_tree_all_reduce_native if r in native_ranks else HC.tcp_tree_all_reduce_rank
+                out[r] = fn(r, world, addrs, xs[r], timeout=20)
+            except Exception as e:  # noqa: BLE001
+                errs.append(e)
+        ts = [threading.Thread(target=work, args=(r,)) for r in range(world)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+        assert not errs, errs
+        ref = HC.tree_all_reduce(xs)[0]
+        assert all(np.array_equal(o, ref) for o in out)
+
+
+def test_native_tcp_failures_are_errors_not_hangs():
+    addrs = [("127.0.0.1", p) for p in _free_ports(3)]
+    with pytest.raises(HC.CollectiveError, match="timed out"):
+        HC.tcp_tree_all_reduce_native(0, 3, addrs, np.ones(4, np.float32), timeout=0.4)      # children never join
+    with pytest.raises(HC.CollectiveError, match="timed out"):
+        HC.tcp_tree_all_reduce_native(1, 3, addrs, np.ones(4, np.float32), timeout=0.4)      # parent never listens
+    # a frame from a rank that is not a child is a protocol error
+    addrs = [("127.0.0.1", p) for p in _free_ports(2)]
+    res = {}
+
+    def root():
+        try:
+            HC.tcp_tree_all_reduce_native(0, 2, addrs, np.ones(4, np.float32), timeout=5)
+        except HC.CollectiveError as e:
+            res["err"] = str(e)
+    t = threading.Thread(target=root)
+    t.start()
+    for _ in range(200):
+        try:
+            s = socket.create_connection(addrs[0], timeout=1)
+            break
+        except OSError:
+            import time
+            time.sleep(0.02)
+    HC.send_frame(s, 7, np.ones(4, np.float32).tobytes())
+    t.join()
+    s.close()
+    assert "protocol" in res.get("err", "")
