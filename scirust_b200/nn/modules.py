@@ -76,10 +76,8 @@ class _LinearFn(torch.autograd.Function):
     def forward(ctx, x, w, b):
         ctx.save_for_backward(x, w)
         ctx.has_bias = b is not None
-        y = ops.matmul_nn(x, w)
-        if b is not None:
-            y = y + b
-        return y
+        # the bias is added in the GEMM epilogue (the residual operand with a zero row pitch)
+        return ops.matmul_nn(x, w, bias=b.reshape(-1).contiguous() if b is not None else None)
 
     @staticmethod
     def backward(ctx, dy):

@@ -76,8 +76,29 @@ def _use_balanced(tiles: int, workers: int, K: int) -> bool:
     return BALANCED and K >= _BALANCED_MIN_K and (tiles >= workers or _BALANCED_MIN_K == 0)
 
 
-def _gemm(a, b, M, N, K, a_mn, b_mn, out, residual, splits, bn):
+class _Bias:
+    """A [N] (or [1, N]) bf16 row added to every output row: the residual operand of the kernels with a
+    zero row pitch, so the bias epilogue is the residual epilogue."""
+
+    def __init__(self, t: torch.Tensor, N: int):
+        t = t.reshape(-1)
+        if t.numel() != N or t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise ValueError("bias must be a contiguous bf16 vector of N elements")
+        self.t = t
+
+    def data_ptr(self):
+        return self.t.data_ptr()
+
+    def stride(self, _dim):
+        return 0
+
+
+def _gemm(a, b, M, N, K, a_mn, b_mn, out, residual, splits, bn, bias=None):
     global launch_count
+    if bias is not None:
+        if residual is not None:
+            raise ValueError("give either a residual or a bias")
+        residual = _Bias(bias, N)
     _check2d(a, "a")
     _check2d(b, "b")
     if out is None:
@@ -86,7 +107,7 @@ def _gemm(a, b, M, N, K, a_mn, b_mn, out, residual, splits, bn):
         _check2d(out, "out")
         if tuple(out.shape) != (M, N):
             raise ValueError(f"out has shape {tuple(out.shape)}, expected {(M, N)}")
-    if residual is not None:
+    if residual is not None and not isinstance(residual, _Bias):
         _check2d(residual, "residual")
         if tuple(residual.shape) != (M, N):
             raise ValueError("residual shape mismatch")
@@ -94,7 +115,7 @@ def _gemm(a, b, M, N, K, a_mn, b_mn, out, residual, splits, bn):
         st = _lib.status_word(a.device)
         pair_tiles = ((M + 255) // 256) * ((N + 255) // 256)
         ws = _workspace(_PAIRS * 3 * 256 * 256, a.device) if _use_balanced(pair_tiles, _PAIRS, K) else None
-        _lib.call("sb_gemm_pair_bf16", a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(residual), M, N, K,
+        _lib.call("sb_gemm_pair_bf16", a.data_ptr(), b.data_ptr(), out.data_ptr(), residual.data_ptr() if residual is not None else None, M, N, K,
                   a.stride(0), b.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
                   int(a_mn), int(b_mn), _lib.ptr(ws), st.data_ptr(), _lib.stream())
         launch_count += 1
@@ -111,7 +132,7 @@ def _gemm(a, b, M, N, K, a_mn, b_mn, out, residual, splits, bn):
     else:
         ws = _workspace(splits * M * N, a.device) if splits > 1 else None
     st = _lib.status_word(a.device)
-    _lib.call("sb_gemm_bf16", a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(residual), M, N, K,
+    _lib.call("sb_gemm_bf16", a.data_ptr(), b.data_ptr(), out.data_ptr(), residual.data_ptr() if residual is not None else None, M, N, K,
               a.stride(0), b.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
               int(a_mn), int(b_mn), splits, _lib.ptr(ws), bn, st.data_ptr(), _lib.stream())
     launch_count += 2 if splits > 1 else 1
@@ -130,26 +151,26 @@ def _ref(a, b, residual, out):
     return y
 
 
-def matmul_nn(x, w, residual=None, out=None, splits=None, bn=None):
-    """x[M,K] @ w[K,N] (+ residual) -> bf16 [M,N]."""
+def matmul_nn(x, w, residual=None, out=None, splits=None, bn=None, bias=None):
+    """x[M,K] @ w[K,N] (+ residual [M,N] | + bias [N]) -> bf16 [M,N]."""
     M, K = x.shape
     K2, N = w.shape
     if K != K2:
         raise ValueError(f"matmul_nn: inner dims differ ({K} vs {K2})")
     if not x.is_cuda:
-        return _ref(x, w, residual, out)
-    return _gemm(x, w, M, N, K, False, True, out, residual, splits, bn)
+        return _ref(x, w, residual if bias is None else bias.reshape(1, -1), out)
+    return _gemm(x, w, M, N, K, False, True, out, residual, splits, bn, bias)
 
 
-def matmul_nt(a, b, residual=None, out=None, splits=None, bn=None):
-    """a[M,K] @ b[N,K]ᵀ (+ residual) -> bf16 [M,N]."""
+def matmul_nt(a, b, residual=None, out=None, splits=None, bn=None, bias=None):
+    """a[M,K] @ b[N,K]ᵀ (+ residual [M,N] | + bias [N]) -> bf16 [M,N]."""
     M, K = a.shape
     N, K2 = b.shape
     if K != K2:
         raise ValueError(f"matmul_nt: inner dims differ ({K} vs {K2})")
     if not a.is_cuda:
-        return _ref(a, b.t(), residual, out)
-    return _gemm(a, b, M, N, K, False, False, out, residual, splits, bn)
+        return _ref(a, b.t(), residual if bias is None else bias.reshape(1, -1), out)
+    return _gemm(a, b, M, N, K, False, False, out, residual, splits, bn, bias)
 
 
 def matmul_tn(a, b, residual=None, out=None, splits=None, bn=None):

@@ -153,3 +153,15 @@ def test_cta_pair_kernel_with_balanced_schedule(M, N, K, monkeypatch):
     _check(y1, a.float().t() @ b.float() + r.float(), K)
     x, w = _mk((M, K), 1), _mk((K, N), 2)
     _check(ops.matmul_nn(x, w), x.float() @ w.float(), K)
+
+
+@pytest.mark.parametrize("pair", ["0", "1"])
+def test_bias_epilogue(pair, monkeypatch):
+    from scirust_b200.ops import gemm
+    monkeypatch.setattr(gemm, "PAIR_MODE", pair)
+    x, w, b = _mk((640, 512), 1), _mk((512, 768), 2), _mk((768,), 3)
+    _check(ops.matmul_nn(x, w, bias=b), x.float() @ w.float() + b.float()[None, :], 512)
+    wt = _mk((768, 512), 4)
+    _check(ops.matmul_nt(x, wt, bias=b), x.float() @ wt.float().t() + b.float()[None, :], 512)
+    with pytest.raises(ValueError):
+        ops.matmul_nn(x, w, bias=b, residual=_mk((640, 768), 5))
