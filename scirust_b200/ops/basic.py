@@ -60,7 +60,7 @@ def rmsnorm_bwd(dy, x, w, inv, dres=None, dw_out=None, want_dw=True):
     dx = torch.empty_like(x)
     part = dwf = dwb = None
     if want_dw:
-        chunks = (rows + 63) // 64
+        chunks = (rows + 255) // 256
         part = torch.empty(chunks * cols, dtype=torch.float32, device=x.device)
         if dw_out is None:
             dw_out = torch.empty(cols, dtype=torch.float32, device=x.device)
@@ -70,7 +70,7 @@ def rmsnorm_bwd(dy, x, w, inv, dres=None, dw_out=None, want_dw=True):
             dwb = dw_out
     _lib.call("sb_rmsnorm_bwd", dy.data_ptr(), x.data_ptr(), w.data_ptr(), inv.data_ptr(), _lib.ptr(dres),
               dx.data_ptr(), _lib.ptr(part), _lib.ptr(dwf), _lib.ptr(dwb), rows, cols, _lib.stream())
-    _count(2 if want_dw else 1)
+    _count(3 if want_dw else 1)
     return dx, dw_out
 
 
