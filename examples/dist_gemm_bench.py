@@ -51,7 +51,7 @@ def timed(fn, iters, warmup, scratch):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=16384)
-    ap.add_argument("--d", type=int, default=4096)
+    ap.add_argument("--d-model", dest="d", type=int, default=4096)
     ap.add_argument("--ff", type=int, default=14336)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)

@@ -44,6 +44,15 @@ struct Params {
   int* status;
   BalancedSched sched;   // workers are CTA pairs; see gemm_sched.cuh
   float* partials;       // dense fp32 [256, 256] blocks, one per scratch slot
+  // SwiGLU epilogue (ff > 0): B is a fused [gate | up] weight of 2*ff columns and N == 2*ff. A tile then
+  // holds 128 gate columns (staged by the leader CTA) and the MATCHING 128 up columns (staged by the
+  // peer), so that after writing both to C the epilogue can also write act = silu(gate) * up.
+  int ff;
+  void* act; int ld_act;
+  // SwiGLU-backward epilogue (gu != nullptr, ff == 0): the product is dh [M, N] (N = ff columns); instead
+  // of storing it, the epilogue reads the saved [gate | up] row of the forward pass and writes
+  // dgu = [dh * up * silu'(gate) | dh * silu(gate)] into C [M, 2N].
+  const void* gu; int ld_gu;
 };
 
 template <bool A_MN, bool B_MN>
@@ -66,7 +75,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int n_pairs = gridDim.x >> 1;
 
   const int mt2 = (p.M + 2 * BM - 1) / (2 * BM);
-  const int nt = (p.N + BN - 1) / BN;
+  const int nt = p.ff ? (p.ff + BNH - 1) / BNH : (p.N + BN - 1) / BN;
   const int num_kb = (p.K + BK - 1) / BK;
   const int tiles_total = mt2 * nt;
 
@@ -108,7 +117,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int n_idx = sg.tile / mt2;
         const int m2 = sg.tile - n_idx * mt2;
         const int row0 = (m2 * 2 + static_cast<int>(rank)) * BM;      // this CTA's rows of A
-        const int col0 = n_idx * BN + static_cast<int>(rank) * BNH;   // this CTA's columns of B
+        const int col0 = p.ff ? n_idx * BNH + static_cast<int>(rank) * p.ff   // gate half | matching up half
+                              : n_idx * BN + static_cast<int>(rank) * BNH;   // this CTA's columns of B
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           uint8_t* sa = tiles + stage * STAGE_BYTES;
@@ -187,11 +197,76 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tc_fence_after();
       const int row = (m2 * 2 + static_cast<int>(rank)) * BM + q * 32 + lane;
       const uint32_t taddr_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      if (p.ff) {
+        // SwiGLU tile: accumulator columns [0,128) are gate, [128,256) the matching up columns
+#pragma unroll 1
+        for (int gc = half * 2; gc < half * 2 + 2; ++gc) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32(taddr_row + gc * 32, rg);
+          tmem_ld_32x32(taddr_row + BNH + gc * 32, ru);
+          tmem_ld_wait();
+          const int gcol = n_idx * BNH + gc * 32;
+          if (row < p.M && gcol < p.ff) {
+            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc;
+            __nv_bfloat16* arow = reinterpret_cast<__nv_bfloat16*>(p.act) + static_cast<size_t>(row) * p.ld_act;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (gcol + v * 8 < p.ff) {   // ff % 8 == 0 is enforced on the host
+                uint4 og, ou, oa;
+                uint32_t* pg = &og.x; uint32_t* pu = &ou.x; uint32_t* pa = &oa.x;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  pg[j] = pack_bf16x2(__uint_as_float(rg[v * 8 + 2 * j]), __uint_as_float(rg[v * 8 + 2 * j + 1]));
+                  pu[j] = pack_bf16x2(__uint_as_float(ru[v * 8 + 2 * j]), __uint_as_float(ru[v * 8 + 2 * j + 1]));
+                  // act from the bf16-rounded gate / up, exactly what the stand-alone kernel reads back
+                  const float g0 = bf16_lo(pg[j]), g1 = bf16_hi(pg[j]);
+                  const float u0 = bf16_lo(pu[j]), u1 = bf16_hi(pu[j]);
+                  pa[j] = pack_bf16x2(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+                }
+                *reinterpret_cast<uint4*>(crow + gcol + v * 8) = og;
+                *reinterpret_cast<uint4*>(crow + p.ff + gcol + v * 8) = ou;
+                *reinterpret_cast<uint4*>(arow + gcol + v * 8) = oa;
+              }
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
         uint32_t r[32];
         tmem_ld_32x32(taddr_row + c * 32, r);
         tmem_ld_wait();
+        if (p.gu) {
+          const int col = n_idx * BN + c * 32;
+          if (row < p.M && col < p.N) {
+            const __nv_bfloat16* grow = reinterpret_cast<const __nv_bfloat16*>(p.gu) + static_cast<size_t>(row) * p.ld_gu;
+            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (col + v * 8 < p.N) {
+                const uint4 gv = *reinterpret_cast<const uint4*>(grow + col + v * 8);
+                const uint4 uv = *reinterpret_cast<const uint4*>(grow + p.N + col + v * 8);
+                const uint32_t* pg = &gv.x; const uint32_t* pu = &uv.x;
+                uint4 odg, odu;
+                uint32_t* qg = &odg.x; uint32_t* qu = &odu.x;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  // dh rounded to bf16 first: the stand-alone kernel reads it back from a bf16 tensor
+                  const uint32_t dpk = pack_bf16x2(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+                  const float d0 = bf16_lo(dpk), d1 = bf16_hi(dpk);
+                  const float g0 = bf16_lo(pg[j]), g1 = bf16_hi(pg[j]);
+                  const float u0 = bf16_lo(pu[j]), u1 = bf16_hi(pu[j]);
+                  const float s0 = 1.f / (1.f + __expf(-g0)), s1 = 1.f / (1.f + __expf(-g1));
+                  qg[j] = pack_bf16x2(d0 * u0 * s0 * (1.f + g0 * (1.f - s0)), d1 * u1 * s1 * (1.f + g1 * (1.f - s1)));
+                  qu[j] = pack_bf16x2(d0 * g0 * s0, d1 * g1 * s1);
+                }
+                *reinterpret_cast<uint4*>(crow + col + v * 8) = odg;
+                *reinterpret_cast<uint4*>(crow + p.N + col + v * 8) = odu;
+              }
+            }
+          }
+          continue;
+        }
         const int col0 = n_idx * BN + c * 32;
         if (sg.slot >= 0) {
           // part of a tile of the balanced schedule: this CTA's 128 rows of the pair's fp32 block
@@ -226,6 +301,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
         }
+      }
       }
       tc_fence_before();
       __syncwarp();
@@ -296,11 +372,16 @@ using namespace sb;
 // Same contract as sb_gemm_bf16 without split-K: C[M,N] (bf16) = op(A) op(B) (+ R). M, N, K > 0,
 // N % 8 == 0, leading dimensions multiples of 8 elements, 16-byte aligned bases.
 // `workspace` (optional): sb_gemm_pair_workspace_floats() floats; with it the balanced schedule is used.
+// `gu` (optional, with ff == 0): SwiGLU-backward epilogue. The product is dh [M, N]; C must be [M, 2N] and
+// receives dgu computed from the saved forward [gate | up] rows `gu` [M, ld_gu]; no residual.
+// `act` (optional, with ff > 0): SwiGLU epilogue. B then holds [gate | up] (N == 2*ff, ff % 8 == 0), C receives
+// the bf16 [gate | up] product as usual and `act` [M, ld_act] receives silu(gate) * up; no residual, no
+// balanced schedule on that path.
 extern "C" size_t sb_gemm_pair_workspace_floats() { return static_cast<size_t>(num_sms() / 2) * 3 * 256 * 256; }
 
 extern "C" int sb_gemm_pair_bf16(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda,
-                                 int ldb, int ldc, int ldr, int a_mn, int b_mn, void* workspace, int* status,
-                                 void* stream_) {
+                                 int ldb, int ldc, int ldr, int a_mn, int b_mn, void* workspace, void* act, int ld_act,
+                                 int ff, const void* gu, int ld_gu, int* status, void* stream_) {
   using namespace sb::pair;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0 || K <= 0 || (N & 7) || (ldc & 7) || (R && (ldr & 7))) return SB_ERR_ARG;
@@ -313,9 +394,19 @@ extern "C" int sb_gemm_pair_bf16(const void* A, const void* B, void* C, const vo
   if (!b_mn) rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, BNH);
   else rc = make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, BK);
   if (rc) return rc;
+  if (ff) {
+    if (!act || N != 2 * ff || (ff & 7) || (ld_act & 7) || R || (reinterpret_cast<uintptr_t>(act) & 15)) return SB_ERR_ARG;
+    workspace = nullptr;
+  }
   Params p;
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.R = R; p.ldr = ldr; p.status = status;
-  const int mt2 = (M + 2 * BM - 1) / (2 * BM), nt = (N + BN - 1) / BN;
+  p.ff = ff; p.act = act; p.ld_act = ld_act;
+  if (gu) {
+    if (ff || R || (ld_gu & 7) || (reinterpret_cast<uintptr_t>(gu) & 15)) return SB_ERR_ARG;
+    workspace = nullptr;
+  }
+  p.gu = gu; p.ld_gu = ld_gu;
+  const int mt2 = (M + 2 * BM - 1) / (2 * BM), nt = ff ? (ff + BNH - 1) / BNH : (N + BN - 1) / BN;
   const int num_kb = (K + BK - 1) / BK;
   const int pairs_avail = max_pairs();
   const int tiles = mt2 * nt;

@@ -139,8 +139,7 @@ class _BlockFn(torch.autograd.Function):
         a, lse = att.attention_fwd(qkv, B, S, H, Hkv, dh, causal=True)
         x2 = ops.matmul_nn(a, wo, residual=x)
         h2, inv2 = ops.rmsnorm_fwd(x2, rms2, cfg.eps)
-        gu = ops.matmul_nn(h2, wgu)
-        hm = ops.swiglu_fwd(gu)
+        gu, hm = ops.matmul_nn_swiglu(h2, wgu)      # SwiGLU in the GEMM epilogue on CUDA
         x3 = ops.matmul_nn(hm, wd, residual=x2)
         ctx.save_for_backward(x, inv1, h1, qkv, a, lse, x2, inv2, h2, gu, hm)
         ctx.blk = blk
@@ -156,9 +155,8 @@ class _BlockFn(torch.autograd.Function):
         H, Hkv, dh = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
         dx3 = dx3.contiguous()
         # FFN
-        dhm = ops.matmul_nt(dx3, wd)
         g_wd = _wgrad(wd, hm, dx3)
-        dgu = ops.swiglu_bwd(gu, dhm)
+        dgu = ops.matmul_nt_swiglu_bwd(dx3, wd, gu)     # dhm = dx3 @ wd^T never leaves the GEMM epilogue
         dh2 = ops.matmul_nt(dgu, wgu)
         g_wgu = _wgrad(wgu, h2, dgu)
         res = {}

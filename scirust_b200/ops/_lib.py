@@ -29,7 +29,7 @@ STATUS = {0: "ok", 1: "timeout: TMA stage never filled", 2: "timeout: stage neve
 
 _CUDA_SIGS = {
     "sb_gemm_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, i32, vp, vp],
-    "sb_gemm_pair_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp],
+    "sb_gemm_pair_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, i32, vp, i32, vp, vp],
     "sb_rmsnorm_fwd": [vp, vp, vp, vp, i32, i32, i32, i32, f32, vp],
     "sb_rmsnorm_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp],
     "sb_rope": [vp, i32, i32, i32, i32, i32, i32, vp, vp, vp, i32, vp],

@@ -54,6 +54,7 @@ def _check2d(t: torch.Tensor, name: str) -> None:
 # products with at least one full wave of such tiles and no split-K; SB_GEMM_PAIR=0/1 forces it.
 PAIR_MODE = os.environ.get("SB_GEMM_PAIR", "auto")
 BALANCED = os.environ.get("SB_GEMM_BALANCED", "1") != "0"
+FUSE_SWIGLU = os.environ.get("SB_FUSE_SWIGLU", "1") != "0"     # SwiGLU forward / backward in the GEMM epilogues
 
 
 # The balanced schedule pays a fix-up pass and fp32 scratch traffic (measured: about 20 us on 74 CTA
@@ -117,7 +118,7 @@ def _gemm(a, b, M, N, K, a_mn, b_mn, out, residual, splits, bn, bias=None):
         ws = _workspace(_PAIRS * 3 * 256 * 256, a.device) if _use_balanced(pair_tiles, _PAIRS, K) else None
         _lib.call("sb_gemm_pair_bf16", a.data_ptr(), b.data_ptr(), out.data_ptr(), residual.data_ptr() if residual is not None else None, M, N, K,
                   a.stride(0), b.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
-                  int(a_mn), int(b_mn), _lib.ptr(ws), st.data_ptr(), _lib.stream())
+                  int(a_mn), int(b_mn), _lib.ptr(ws), None, 0, 0, None, 0, st.data_ptr(), _lib.stream())
         launch_count += 1
         return out
     if bn is None:
@@ -160,6 +161,62 @@ def matmul_nn(x, w, residual=None, out=None, splits=None, bn=None, bias=None):
     if not x.is_cuda:
         return _ref(x, w, residual if bias is None else bias.reshape(1, -1), out)
     return _gemm(x, w, M, N, K, False, True, out, residual, splits, bn, bias)
+
+
+def matmul_nn_swiglu(x, wgu, out=None, act=None):
+    """Gate/up projection with the SwiGLU fused into the GEMM epilogue: returns ``(gu, act)`` with
+    ``gu = x @ wgu`` (bf16 ``[M, 2*ff]`` = [gate | up], kept for the backward pass) and
+    ``act = silu(gate) * up`` (bf16 ``[M, ff]``), bit-identical to ``swiglu_fwd(matmul_nn(x, wgu))``.
+    Runs on the CTA-pair kernel (each CTA of a pair stages one half: gate columns / matching up columns)."""
+    global launch_count
+    M, K = x.shape
+    K2, N = wgu.shape
+    ff = N // 2
+    if K != K2 or N % 2:
+        raise ValueError("matmul_nn_swiglu: shape mismatch")
+    fused = x.is_cuda and PAIR_MODE != "0" and FUSE_SWIGLU and ff % 8 == 0 and M >= 256
+    if not fused:
+        from . import basic
+        gu = matmul_nn(x, wgu, out=out)
+        return gu, basic.swiglu_fwd(gu, out=act)
+    _check2d(x, "x")
+    _check2d(wgu, "wgu")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    if act is None:
+        act = torch.empty((M, ff), dtype=torch.bfloat16, device=x.device)
+    st = _lib.status_word(x.device)
+    _lib.call("sb_gemm_pair_bf16", x.data_ptr(), wgu.data_ptr(), out.data_ptr(), None, M, N, K, x.stride(0),
+              wgu.stride(0), out.stride(0), 0, 0, 1, None, act.data_ptr(), act.stride(0), ff, None, 0, st.data_ptr(),
+              _lib.stream())
+    launch_count += 1
+    return out, act
+
+
+def matmul_nt_swiglu_bwd(dy, wd, gu, out=None):
+    """Backward of the SwiGLU feed-forward's middle: ``dgu = swiglu_bwd(gu, dy @ wdᵀ)`` with the
+    element-wise part in the GEMM epilogue (``dy [M, d]``, ``wd [ff, d]``, ``gu [M, 2*ff]`` saved by the
+    forward pass) -> bf16 ``[M, 2*ff]``; bit-identical to the two-step path."""
+    global launch_count
+    M, K = dy.shape
+    ff, K2 = wd.shape
+    if K != K2 or tuple(gu.shape) != (M, 2 * ff):
+        raise ValueError("matmul_nt_swiglu_bwd: shape mismatch")
+    fused = dy.is_cuda and PAIR_MODE != "0" and FUSE_SWIGLU and ff % 8 == 0 and M >= 256
+    if not fused:
+        from . import basic
+        return basic.swiglu_bwd(gu, matmul_nt(dy, wd), out=out)
+    _check2d(dy, "dy")
+    _check2d(wd, "wd")
+    _check2d(gu, "gu")
+    if out is None:
+        out = torch.empty((M, 2 * ff), dtype=torch.bfloat16, device=dy.device)
+    st = _lib.status_word(dy.device)
+    _lib.call("sb_gemm_pair_bf16", dy.data_ptr(), wd.data_ptr(), out.data_ptr(), None, M, ff, K, dy.stride(0),
+              wd.stride(0), out.stride(0), 0, 0, 0, None, None, 0, 0, gu.data_ptr(), gu.stride(0), st.data_ptr(),
+              _lib.stream())
+    launch_count += 1
+    return out
 
 
 def matmul_nt(a, b, residual=None, out=None, splits=None, bn=None, bias=None):

@@ -31,7 +31,7 @@ BF = torch.bfloat16
 _lib.register("sb_gemm_dist_bf16", [_lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32,
                                     _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32,
                                     _lib.i32, _lib.i32, _lib.i32, _lib.i32, C.c_uint32, _lib.vp, _lib.i32, _lib.i32,
-                                    _lib.vp, _lib.vp])
+                                    _lib.vp, _lib.i32, _lib.vp, _lib.vp, _lib.vp, _lib.vp])
 
 
 class TPContext:
@@ -61,6 +61,9 @@ class TPContext:
             self.flag_ptrs = (C.c_void_p * self.world)(
                 *[b + self.region.data_bytes + self.slot * wps * 4 for b in self.region.peer_base])
             self.counters = torch.zeros(32, dtype=torch.int32, device=self.dev)
+            # local landing buffer of the all-gather -> GEMM products (allocated on first use)
+            self._ag_stage = None
+            self._ag_flags = torch.zeros(2 * (max_rows // 128 + 2), dtype=torch.int32, device=self.dev)
         else:
             self.region = None
 
@@ -89,11 +92,19 @@ class TPContext:
             self.rs_calls += 1
             if M * N > self.stage[0].numel():
                 raise ValueError("reduce-scatter staging area too small for this product")
+        ag_stage, ld_stage, cflags, cctr = None, 0, None, None
+        if a_gather and not a_mn and self.world > 1 and M // 128 + 2 <= self._ag_flags.numel() // 2:
+            if self._ag_stage is None or self._ag_stage.numel() < M * K:
+                self._ag_stage = torch.empty(M * K, dtype=BF, device=self.dev)
+            ag_stage, ld_stage = self._ag_stage.data_ptr(), K
+            half = self._ag_flags.numel() // 2
+            cflags, cctr = self._ag_flags.data_ptr(), self._ag_flags[half:].data_ptr()
         _lib.call("sb_gemm_dist_bf16", self._ptrs(a, a_gather), self._ptrs(b, b_gather), out.data_ptr(),
                   _lib.ptr(residual), stage, self.flag_ptrs, M, N, K, a.stride(0), b.stride(0), out.stride(0),
                   residual.stride(0) if residual is not None else 0, int(a_mn), int(b_mn), int(a_gather),
                   int(b_gather), int(scatter), self.rank, self.world, self.epoch, self.counters.data_ptr(), bn,
-                  self.wait_ms, _lib.status_word(self.dev).data_ptr(), _lib.stream())
+                  self.wait_ms, ag_stage, ld_stage, cflags, cctr, _lib.status_word(self.dev).data_ptr(),
+                  _lib.stream())
         _g.launch_count += 1
         return out
 

@@ -165,3 +165,30 @@ def test_bias_epilogue(pair, monkeypatch):
     _check(ops.matmul_nt(x, wt, bias=b), x.float() @ wt.float().t() + b.float()[None, :], 512)
     with pytest.raises(ValueError):
         ops.matmul_nn(x, w, bias=b, residual=_mk((640, 768), 5))
+
+
+@pytest.mark.parametrize("M,K,ff", [(512, 256, 128), (4096, 1024, 2816), (1000, 512, 264)])
+def test_swiglu_epilogue_is_bitwise_the_unfused_path(M, K, ff, monkeypatch):
+    from scirust_b200.ops import basic, gemm
+    x, wgu = _mk((M, K), 1), _mk((K, 2 * ff), 2)
+    gu, act = ops.matmul_nn_swiglu(x, wgu)
+    _lib.check_status()
+    monkeypatch.setattr(gemm, "PAIR_MODE", "0")
+    monkeypatch.setattr(gemm, "BALANCED", False)
+    gu0 = ops.matmul_nn(x, wgu)
+    act0 = basic.swiglu_fwd(gu0)
+    assert torch.equal(gu, gu0)
+    assert torch.equal(act, act0)
+    _check(gu, x.float() @ wgu.float(), K)
+
+
+@pytest.mark.parametrize("M,d,ff", [(512, 256, 128), (4096, 1024, 2816), (1000, 512, 264)])
+def test_swiglu_backward_epilogue_is_bitwise_the_unfused_path(M, d, ff, monkeypatch):
+    from scirust_b200.ops import basic, gemm
+    dy, wd, gu = _mk((M, d), 1), _mk((ff, d), 2), _mk((M, 2 * ff), 3)
+    dgu = ops.matmul_nt_swiglu_bwd(dy, wd, gu)
+    _lib.check_status()
+    monkeypatch.setattr(gemm, "PAIR_MODE", "0")
+    monkeypatch.setattr(gemm, "BALANCED", False)
+    ref = basic.swiglu_bwd(gu, ops.matmul_nt(dy, wd))
+    assert torch.equal(dgu, ref)
