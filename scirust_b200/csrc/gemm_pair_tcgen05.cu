@@ -29,7 +29,11 @@ constexpr int BN = 256;        // columns of the pair's tile
 constexpr int BNH = BN / 2;    // columns of B staged per CTA
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int THREADS = 320;
+constexpr int THREADS = 448;        // warp 0 TMA, 1 MMA, 2-9 epilogue, 10-13 all-gather copiers (idle otherwise)
+constexpr int COPY_WARPS = 4;
+constexpr int GROUP_M = 8;           // row tiles (of 256 rows) per raster group
+constexpr int MAXW = 8;
+constexpr int FLAG_STRIDE = 16;     // flag words per phase in a call site's slot (as in gemm_dist_tcgen05.cu)
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int B_BYTES = BNH * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // 32 KB per CTA
@@ -53,7 +57,52 @@ struct Params {
   // of storing it, the epilogue reads the saved [gate | up] row of the forward pass and writes
   // dgu = [dh * up * silu'(gate) | dh * silu(gate)] into C [M, 2N].
   const void* gu; int ld_gu;
+  // All-gather -> GEMM (ag.W > 1): A's rows are sharded over the ranks (rank s holds rows
+  // [s*rows, (s+1)*rows) in its own buffer a_peer[s], row pitch lda). The copier warps of every CTA
+  // pull ALL shards (the local one too) into the local landing buffer that tmap_a describes,
+  // 128-row chunk by chunk, own rows first, then rank+1's, ...; a chunk's counter raises its flag and
+  // the TMA producer waits (bounded) for the flag of the chunk it is about to read. Tiles are walked in
+  // the same rotated order. flags[r]: this call site's slot on rank r ([0*16+s] "rank s's shard is
+  // final", [1*16+s] "rank s has stopped reading my shard").
+  struct {
+    int W, rank, rows;
+    const void* a_peer[MAXW]; int lda;
+    void* a_stage; int ld_stage;
+    uint32_t* flags[MAXW];
+    uint32_t* chunk_flags; unsigned int* chunk_ctr; unsigned int* cta_ctr;
+    uint32_t epoch;
+    uint64_t wait_ns;
+  } ag;
 };
+
+__device__ __forceinline__ void p_st_release_sys(uint32_t* ptr, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void p_st_release_gpu(uint32_t* ptr, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
+template <bool SYS>
+__device__ bool p_wait_flag(const uint32_t* flag, uint32_t epoch, uint64_t limit_ns, int* status) {
+  auto ld = [&]() {
+    uint32_t v;
+    if (SYS) asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    else asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    return v;
+  };
+  if (static_cast<int32_t>(ld() - epoch) >= 0) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (static_cast<int32_t>(ld() - epoch) < 0) {
+    if ((++spins & 0xff) == 0) {
+      if (globaltimer_ns() - t0 > limit_ns) {
+        atomicCAS(status, 0, ST_TIMEOUT_PEER);
+        return false;
+      }
+      if (*reinterpret_cast<volatile int*>(status) != 0) return false;
+    }
+  }
+  return true;
+}
 
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -78,8 +127,29 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int nt = p.ff ? (p.ff + BNH - 1) / BNH : (p.N + BN - 1) / BN;
   const int num_kb = (p.K + BK - 1) / BK;
   const int tiles_total = mt2 * nt;
+  // Tile order: groups of GROUP_M row tiles sweep all column tiles before the next group starts, so a
+  // wave of CTA pairs touches few distinct A and B tiles (an A larger than L2 is then read from DRAM
+  // once per group instead of once per column tile). The balanced schedule keeps plain n-major order,
+  // which is what its fix-up pass assumes.
+  const int group_m = p.sched.sk_tiles > 0 ? mt2 : (mt2 < GROUP_M ? mt2 : GROUP_M);
+  auto tile_mn = [&](int t, int& m2, int& n_idx) {
+    const int gsz = group_m * nt;
+    const int g = t / gsz;
+    const int first = g * group_m;
+    const int gm = min(group_m, mt2 - first);
+    const int within = t - g * gsz;
+    n_idx = within / gm;
+    m2 = first + (within - n_idx * gm);
+  };
+  const bool ag = p.ag.W > 1;
+  const int m_rot = ag ? p.ag.rank * (mt2 / p.ag.W) : 0;   // walk the local shard's row tiles first
 
   if (threadIdx.x == 0) {
+    if (ag && blockIdx.x == 0) {
+      // my shard is final (stream order): tell every peer
+      __threadfence_system();
+      for (int r = 0; r < p.ag.W; ++r) p_st_release_sys(p.ag.flags[r] + 0 * FLAG_STRIDE + p.ag.rank, p.ag.epoch);
+    }
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);     // leader's producer arms it; both CTAs' copies complete on it
       mbar_init(&empty_bar[s], 1);    // one commit arrival (delivered to both CTAs)
@@ -114,11 +184,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       SegIter iter(p.sched, pair_id, n_pairs, tiles_total, num_kb, 1, num_kb);
       Seg sg;
       while (ok && iter.next(sg)) {
-        const int n_idx = sg.tile / mt2;
-        const int m2 = sg.tile - n_idx * mt2;
+        int n_idx, m2;
+        tile_mn(sg.tile, m2, n_idx);
+        m2 = (m2 + m_rot) % mt2;
         const int row0 = (m2 * 2 + static_cast<int>(rank)) * BM;      // this CTA's rows of A
         const int col0 = p.ff ? n_idx * BNH + static_cast<int>(rank) * p.ff   // gate half | matching up half
                               : n_idx * BN + static_cast<int>(rank) * BNH;   // this CTA's columns of B
+        if (ag && row0 < p.M) {
+          // these 128 rows must have landed in the local buffer (copier warps of all CTAs)
+          if (!p_wait_flag<false>(p.ag.chunk_flags + row0 / BM, p.ag.epoch, p.ag.wait_ns, p.status)) { ok = false; break; }
+          asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy stores -> TMA reads
+        }
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           uint8_t* sa = tiles + stage * STAGE_BYTES;
@@ -178,6 +254,57 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (ok) umma_commit_pair(&tmem_full[acc], 3);
       }
     }
+  } else if (warp >= 10) {
+    // -------------------------------- copiers (both CTAs) ---------------------------------
+    if (ag && !A_MN) {
+      const int cw = warp - 10;
+      const int cpr = p.ag.rows / BM;                                        // chunks per rank
+      const size_t vec_per_row = static_cast<size_t>(p.K) / 8;               // 16-byte words per row
+      const size_t vec_per_chunk = vec_per_row * BM;
+      const size_t lo = vec_per_chunk * blockIdx.x / gridDim.x, hi = vec_per_chunk * (blockIdx.x + 1) / gridDim.x;
+      for (int s = 0; s < p.ag.W; ++s) {
+        const int src = (p.ag.rank + s) % p.ag.W;
+        if (s > 0) {
+          int ready = 1;
+          if (lane == 0)
+            ready = p_wait_flag<true>(p.ag.flags[p.ag.rank] + 0 * FLAG_STRIDE + src, p.ag.epoch, p.ag.wait_ns, p.status) ? 1 : 0;
+          ready = __shfl_sync(0xffffffffu, ready, 0);
+          if (!ready) break;
+        }
+        const uint4* peer = static_cast<const uint4*>(p.ag.a_peer[src]);
+        for (int ci = 0; ci < cpr; ++ci) {
+          const int chunk = src * cpr + ci;
+          const size_t prow0 = static_cast<size_t>(ci) * BM, srow0 = static_cast<size_t>(chunk) * BM;
+          for (size_t v0 = lo + (cw * 32 + lane); v0 < hi; v0 += COPY_WARPS * 32 * 4) {
+            uint4 tmp[4];
+            size_t idx[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              idx[u] = v0 + static_cast<size_t>(u) * COPY_WARPS * 32;
+              if (idx[u] < hi) {
+                const size_t r = idx[u] / vec_per_row, c = idx[u] - r * vec_per_row;
+                const uint4* src_p = peer + ((prow0 + r) * p.ag.lda) / 8 + c;
+                asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(tmp[u].x), "=r"(tmp[u].y), "=r"(tmp[u].z), "=r"(tmp[u].w) : "l"(src_p) : "memory");
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              if (idx[u] < hi) {
+                const size_t r = idx[u] / vec_per_row, c = idx[u] - r * vec_per_row;
+                *(static_cast<uint4*>(p.ag.a_stage) + ((srow0 + r) * p.ag.ld_stage) / 8 + c) = tmp[u];
+              }
+            }
+          }
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) {
+            const unsigned int prev = atomicAdd(p.ag.chunk_ctr + chunk, 1u);
+            if (prev + 1 == gridDim.x * COPY_WARPS) p_st_release_gpu(p.ag.chunk_flags + chunk, p.ag.epoch);
+          }
+        }
+      }
+    }
   } else {
     // -------------------------------- epilogue (both CTAs) --------------------------------
     const int q = warp & 3;
@@ -189,8 +316,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     SegIter iter(p.sched, pair_id, n_pairs, tiles_total, num_kb, 1, num_kb);
     Seg sg;
     for (; ok && iter.next(sg); ++it) {
-      const int n_idx = sg.tile / mt2;
-      const int m2 = sg.tile - n_idx * mt2;
+      int n_idx, m2;
+      tile_mn(sg.tile, m2, n_idx);
+      m2 = (m2 + m_rot) % mt2;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
@@ -316,6 +444,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   cluster_sync_all();
   tc_fence_after();
   if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  if (ag && threadIdx.x == 0) {
+    // last CTA: reset the counters; tell the peers this rank has stopped reading their shards and stay
+    // until they have stopped reading this rank's shard (the caller may then overwrite it)
+    __threadfence();
+    const unsigned int prev = atomicAdd(p.ag.cta_ctr, 1u);
+    if (prev == gridDim.x - 1) {
+      *p.ag.cta_ctr = 0;
+      const int chunks = p.ag.W * (p.ag.rows / BM);
+      for (int i = 0; i < chunks; ++i) p.ag.chunk_ctr[i] = 0;
+      if (*reinterpret_cast<volatile int*>(p.status) == 0) {
+        __threadfence_system();
+        for (int r = 0; r < p.ag.W; ++r) p_st_release_sys(p.ag.flags[r] + 1 * FLAG_STRIDE + p.ag.rank, p.ag.epoch);
+        for (int s = 0; s < p.ag.W; ++s)
+          if (!p_wait_flag<true>(p.ag.flags[p.ag.rank] + 1 * FLAG_STRIDE + s, p.ag.epoch, p.ag.wait_ns, p.status)) break;
+      }
+    }
+  }
 }
 
 // Number of CTA pairs the device keeps resident at once (the kernel runs one CTA per SM).
@@ -406,6 +551,7 @@ extern "C" int sb_gemm_pair_bf16(const void* A, const void* B, void* C, const vo
     workspace = nullptr;
   }
   p.gu = gu; p.ld_gu = ld_gu;
+  p.ag.W = 0;
   const int mt2 = (M + 2 * BM - 1) / (2 * BM), nt = ff ? (ff + BNH - 1) / BNH : (N + BN - 1) / BN;
   const int num_kb = (K + BK - 1) / BK;
   const int pairs_avail = max_pairs();
@@ -433,4 +579,45 @@ extern "C" int sb_gemm_pair_bf16(const void* A, const void* B, void* C, const vo
     if (cudaGetLastError() != cudaSuccess) return SB_ERR_LAUNCH;
   }
   return 0;
+}
+
+// All-gather -> GEMM on CTA pairs: C[M,N] = gather(A shards)[M,K] * op(B) (+ R). a_ptrs[s]: rank s's shard
+// [M/W, lda] (peer-mapped); a_stage: local landing buffer [M, ld_stage]; flag_ptrs[r]: this call site's flag
+// slot on rank r; chunk_flags / chunk_ctr: M/128 words each, cta_ctr one word (counters zero on entry, left
+// zero). (M / W) % 256 == 0, K % 8 == 0. B is local ([K,N] when b_mn, else [N,K]).
+extern "C" int sb_gemm_pair_ag_bf16(void* const* a_ptrs, const void* B, void* C, const void* R, int M, int N, int K,
+                                    int lda, int ldb, int ldc, int ldr, int b_mn, void* a_stage, int ld_stage,
+                                    void* const* flag_ptrs, uint32_t* chunk_flags, unsigned int* chunk_ctr,
+                                    unsigned int* cta_ctr, int rank, int W, uint32_t epoch, int wait_ms, int* status,
+                                    void* stream_) {
+  using namespace sb::pair;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0 || W < 2 || W > MAXW || rank < 0 || rank >= W) return SB_ERR_ARG;
+  if ((N & 7) || (K & 7) || (lda & 7) || (ld_stage & 7) || (ldc & 7) || (R && (ldr & 7)) || (M % (W * 2 * BM)))
+    return SB_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(a_stage) & 15)) return SB_ERR_ALIGN;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d_bf16(&ta, a_stage, K, M, ld_stage, BK, BM);
+  if (rc) return rc;
+  if (!b_mn) rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, BNH);
+  else rc = make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, BK);
+  if (rc) return rc;
+  Params p;
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.R = R; p.ldr = ldr; p.status = status;
+  p.ff = 0; p.act = nullptr; p.ld_act = 0; p.gu = nullptr; p.ld_gu = 0;
+  p.partials = nullptr;
+  p.sched.dp_tiles = p.sched.sk_tiles = p.sched.sk_workers = p.sched.sk_slots = 0;
+  p.ag.W = W; p.ag.rank = rank; p.ag.rows = M / W; p.ag.lda = lda;
+  p.ag.a_stage = a_stage; p.ag.ld_stage = ld_stage;
+  for (int r = 0; r < MAXW; ++r) {
+    p.ag.a_peer[r] = r < W ? a_ptrs[r] : nullptr;
+    p.ag.flags[r] = r < W ? static_cast<uint32_t*>(flag_ptrs[r]) : nullptr;
+  }
+  p.ag.chunk_flags = chunk_flags; p.ag.chunk_ctr = chunk_ctr; p.ag.cta_ctr = cta_ctr;
+  p.ag.epoch = epoch;
+  p.ag.wait_ns = wait_ms > 0 ? static_cast<uint64_t>(wait_ms) * 1000000ull : 10000000000ull;
+  // every CTA pair runs copier warps, so the whole device is launched whatever the tile count
+  const int grid = 2 * max_pairs();
+  if (!b_mn) return launch<false, false>(ta, tb, p, grid, stream);
+  return launch<false, true>(ta, tb, p, grid, stream);
 }

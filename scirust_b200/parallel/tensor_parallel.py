@@ -18,6 +18,7 @@ reduction contract (scirust-core/src/distributed.rs:96-167).
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 import torch.distributed as dist
@@ -32,6 +33,11 @@ _lib.register("sb_gemm_dist_bf16", [_lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.vp,
                                     _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32,
                                     _lib.i32, _lib.i32, _lib.i32, _lib.i32, C.c_uint32, _lib.vp, _lib.i32, _lib.i32,
                                     _lib.vp, _lib.i32, _lib.vp, _lib.vp, _lib.vp, _lib.vp])
+
+
+_lib.register("sb_gemm_pair_ag_bf16", [_lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.i32, _lib.i32,
+                                       _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.vp, _lib.i32, _lib.vp, _lib.vp,
+                                       _lib.vp, _lib.vp, _lib.i32, _lib.i32, C.c_uint32, _lib.i32, _lib.vp, _lib.vp])
 
 
 class TPContext:
@@ -49,6 +55,7 @@ class TPContext:
         self.dev = torch.device("cuda", torch.cuda.current_device())
         self.epoch = 0
         self.rs_calls = 0
+        self.pair = os.environ.get("SB_TP_PAIR", "1") != "0"   # CTA-pair kernel for all-gather -> GEMM
         self._named = {}
         if backend == "fused":
             stage_bytes = max_rows * max_cols * 2          # W * (rows/W) * cols bf16
@@ -84,6 +91,25 @@ class TPContext:
             return self.region.peer_ptrs(t)
         return (C.c_void_p * self.world)(*([t.data_ptr()] * self.world))
 
+    def _ag_pair(self, x_shard, w, out, M, N, K, b_mn):
+        """all-gather -> GEMM on the CTA-pair kernel (csrc/gemm_pair_tcgen05.cu): the shards land in a
+        local buffer chunk by chunk while 256 x 256 tiles are computed over two SMs."""
+        self.epoch += 1
+        if self._ag_stage is None or self._ag_stage.numel() < M * K:
+            self._ag_stage = torch.empty(M * K, dtype=BF, device=self.dev)
+        n = self._ag_flags.numel() // 2
+        _lib.call("sb_gemm_pair_ag_bf16", self.region.peer_ptrs(x_shard), w.data_ptr(), out.data_ptr(), None, M, N, K,
+                  x_shard.stride(0), w.stride(0), out.stride(0), 0, int(b_mn), self._ag_stage.data_ptr(), K,
+                  self.flag_ptrs, self._ag_flags.data_ptr(), self._ag_flags[n:].data_ptr(),
+                  self._ag_flags[2 * n - 1:].data_ptr(), self.rank, self.world, self.epoch, self.wait_ms,
+                  _lib.status_word(self.dev).data_ptr(), _lib.stream())
+        _g.launch_count += 1
+        return out
+
+    def _pair_ok(self, M, K):
+        return (self.pair and self.world > 1 and M % (self.world * 256) == 0 and K % 8 == 0
+                and M // 128 + 2 <= self._ag_flags.numel() // 2)
+
     def _call(self, a, b, out, residual, M, N, K, a_mn, b_mn, a_gather, b_gather, scatter, bn=0):
         self.epoch += 1
         stage = None
@@ -118,6 +144,8 @@ class TPContext:
             dist.all_gather_into_tensor(x, x_shard.contiguous(), group=self.group)
             return torch.matmul(x, w)
         out = torch.empty((T, N), dtype=BF, device=self.dev)
+        if self._pair_ok(T, K):
+            return self._ag_pair(x_shard, w, out, T, N, K, True)
         return self._call(x_shard, w, out, None, T, N, K, False, True, True, False, False)
 
     def ag_matmul_nt(self, x_shard, w):
@@ -129,6 +157,8 @@ class TPContext:
             dist.all_gather_into_tensor(x, x_shard.contiguous(), group=self.group)
             return torch.matmul(x, w.t())
         out = torch.empty((T, N), dtype=BF, device=self.dev)
+        if self._pair_ok(T, K):
+            return self._ag_pair(x_shard, w, out, T, N, K, False)
         return self._call(x_shard, w, out, None, T, N, K, False, False, True, False, False)
 
     def matmul_nn_rs(self, a, w, residual_shard=None):

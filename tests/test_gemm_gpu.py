@@ -170,6 +170,7 @@ def test_bias_epilogue(pair, monkeypatch):
 @pytest.mark.parametrize("M,K,ff", [(512, 256, 128), (4096, 1024, 2816), (1000, 512, 264)])
 def test_swiglu_epilogue_is_bitwise_the_unfused_path(M, K, ff, monkeypatch):
     from scirust_b200.ops import basic, gemm
+    monkeypatch.setattr(gemm, "FUSE_SWIGLU", True)
     x, wgu = _mk((M, K), 1), _mk((K, 2 * ff), 2)
     gu, act = ops.matmul_nn_swiglu(x, wgu)
     _lib.check_status()
@@ -185,6 +186,7 @@ def test_swiglu_epilogue_is_bitwise_the_unfused_path(M, K, ff, monkeypatch):
 @pytest.mark.parametrize("M,d,ff", [(512, 256, 128), (4096, 1024, 2816), (1000, 512, 264)])
 def test_swiglu_backward_epilogue_is_bitwise_the_unfused_path(M, d, ff, monkeypatch):
     from scirust_b200.ops import basic, gemm
+    monkeypatch.setattr(gemm, "FUSE_SWIGLU", True)
     dy, wd, gu = _mk((M, d), 1), _mk((ff, d), 2), _mk((M, 2 * ff), 3)
     dgu = ops.matmul_nt_swiglu_bwd(dy, wd, gu)
     _lib.check_status()
