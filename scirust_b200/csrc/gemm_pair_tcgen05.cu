@@ -72,7 +72,28 @@ struct Params {
     uint32_t* chunk_flags; unsigned int* chunk_ctr; unsigned int* cta_ctr;
     uint32_t epoch;
     uint64_t wait_ns;
+    int team;        // CTAs that share one chunk; teams work on different chunks at the same time
   } ag;
+  // GEMM -> reduce-scatter (rs.W > 1): C is this rank's PARTIAL product [M, ldc] in symmetric memory
+  // (p_peer[s] = rank s's copy). Rows [o*rows, (o+1)*rows) belong to rank o. The epilogue stores the
+  // partial as usual and counts finished tiles per 256-row block; the block's last warp raises
+  // "rank s's partial of this block is complete" on the block's owner (ready[o] + s * blocks + block).
+  // The copier warps of the owner then pull the W partials of a block (own copy locally, the others
+  // with plain peer loads), add them in rank order 0..W-1 (+ residual) and write out [rows, ld_out].
+  // Own rows are computed first, so the peers' partials of my rows arrive while I compute theirs.
+  struct {
+    int W, rank, rows;
+    const void* p_peer[MAXW];
+    uint32_t* ready[MAXW];          // per rank: [W sources][rows / 256 blocks] epochs
+    uint32_t* flags[MAXW];          // call-site slot: [1*16+s] "rank s has stopped reading my partial"
+    unsigned int* block_ctr;        // [M / 256], zero on entry, reset by the kernel
+    unsigned int* cta_ctr;
+    void* out; int ld_out;
+    const void* res; int ld_res;
+    uint32_t epoch;
+    uint64_t wait_ns;
+    int team;        // CTAs that share one row block; teams reduce different blocks at the same time
+  } rs;
 };
 
 __device__ __forceinline__ void p_st_release_sys(uint32_t* ptr, uint32_t v) {
@@ -106,7 +127,8 @@ __device__ bool p_wait_flag(const uint32_t* flag, uint32_t epoch, uint64_t limit
 
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Params p) {
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_a_own, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* tiles = smem;
@@ -142,7 +164,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     m2 = first + (within - n_idx * gm);
   };
   const bool ag = p.ag.W > 1;
-  const int m_rot = ag ? p.ag.rank * (mt2 / p.ag.W) : 0;   // walk the local shard's row tiles first
+  const bool rs = p.rs.W > 1;
+  const int m_rot = ag ? p.ag.rank * (mt2 / p.ag.W)        // walk the local shard's row tiles first
+                       : (rs ? p.rs.rank * (mt2 / p.rs.W) : 0);
 
   if (threadIdx.x == 0) {
     if (ag && blockIdx.x == 0) {
@@ -190,8 +214,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int row0 = (m2 * 2 + static_cast<int>(rank)) * BM;      // this CTA's rows of A
         const int col0 = p.ff ? n_idx * BNH + static_cast<int>(rank) * p.ff   // gate half | matching up half
                               : n_idx * BN + static_cast<int>(rank) * BNH;   // this CTA's columns of B
-        if (ag && row0 < p.M) {
-          // these 128 rows must have landed in the local buffer (copier warps of all CTAs)
+        const bool own_rows = ag && row0 / p.ag.rows == p.ag.rank;   // read straight from the local shard
+        const int row_own = row0 - (ag ? p.ag.rank * p.ag.rows : 0);
+        if (ag && !own_rows && row0 < p.M) {
+          // these 128 rows must have landed in the local buffer (copier warps of a team of CTAs)
           if (!p_wait_flag<false>(p.ag.chunk_flags + row0 / BM, p.ag.epoch, p.ag.wait_ns, p.status)) { ok = false; break; }
           asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy stores -> TMA reads
         }
@@ -202,7 +228,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
           const uint32_t bar = mapa_shared(smem_u32(&full_bar[stage]), 0);
           if constexpr (!A_MN) {
-            tma_load_2d_pair(sa, &tmap_a, bar, kb * BK, row0);
+            if (own_rows) tma_load_2d_pair(sa, &tmap_a_own, bar, kb * BK, row_own);
+            else tma_load_2d_pair(sa, &tmap_a, bar, kb * BK, row0);
           } else {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c)
@@ -261,47 +288,97 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int cpr = p.ag.rows / BM;                                        // chunks per rank
       const size_t vec_per_row = static_cast<size_t>(p.K) / 8;               // 16-byte words per row
       const size_t vec_per_chunk = vec_per_row * BM;
-      const size_t lo = vec_per_chunk * blockIdx.x / gridDim.x, hi = vec_per_chunk * (blockIdx.x + 1) / gridDim.x;
-      for (int s = 0; s < p.ag.W; ++s) {
-        const int src = (p.ag.rank + s) % p.ag.W;
-        if (s > 0) {
+      const int team = p.ag.team, n_teams = gridDim.x / team;
+      const int my_team = blockIdx.x / team, member = blockIdx.x - my_team * team;
+      const size_t lo = vec_per_chunk * member / team, hi = vec_per_chunk * (member + 1) / team;
+      const int n_remote = (p.ag.W - 1) * cpr;                               // chunks in the order they are needed
+      uint32_t ready_mask = 0;
+      for (int i = my_team; i < n_remote && my_team < n_teams; i += n_teams) {
+        const int src = (p.ag.rank + 1 + i / cpr) % p.ag.W;
+        const int ci = i % cpr;
+        if (!(ready_mask & (1u << src))) {
           int ready = 1;
           if (lane == 0)
             ready = p_wait_flag<true>(p.ag.flags[p.ag.rank] + 0 * FLAG_STRIDE + src, p.ag.epoch, p.ag.wait_ns, p.status) ? 1 : 0;
           ready = __shfl_sync(0xffffffffu, ready, 0);
           if (!ready) break;
+          ready_mask |= 1u << src;
         }
         const uint4* peer = static_cast<const uint4*>(p.ag.a_peer[src]);
-        for (int ci = 0; ci < cpr; ++ci) {
-          const int chunk = src * cpr + ci;
-          const size_t prow0 = static_cast<size_t>(ci) * BM, srow0 = static_cast<size_t>(chunk) * BM;
-          for (size_t v0 = lo + (cw * 32 + lane); v0 < hi; v0 += COPY_WARPS * 32 * 4) {
-            uint4 tmp[4];
-            size_t idx[4];
+        const int chunk = src * cpr + ci;
+        const size_t prow0 = static_cast<size_t>(ci) * BM, srow0 = static_cast<size_t>(chunk) * BM;
+        for (size_t v0 = lo + (cw * 32 + lane); v0 < hi; v0 += COPY_WARPS * 32 * 4) {
+          uint4 tmp[4];
+          size_t idx[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              idx[u] = v0 + static_cast<size_t>(u) * COPY_WARPS * 32;
-              if (idx[u] < hi) {
-                const size_t r = idx[u] / vec_per_row, c = idx[u] - r * vec_per_row;
-                const uint4* src_p = peer + ((prow0 + r) * p.ag.lda) / 8 + c;
-                asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                             : "=r"(tmp[u].x), "=r"(tmp[u].y), "=r"(tmp[u].z), "=r"(tmp[u].w) : "l"(src_p) : "memory");
-              }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              if (idx[u] < hi) {
-                const size_t r = idx[u] / vec_per_row, c = idx[u] - r * vec_per_row;
-                *(static_cast<uint4*>(p.ag.a_stage) + ((srow0 + r) * p.ag.ld_stage) / 8 + c) = tmp[u];
-              }
+          for (int u = 0; u < 4; ++u) {
+            idx[u] = v0 + static_cast<size_t>(u) * COPY_WARPS * 32;
+            if (idx[u] < hi) {
+              const size_t r = idx[u] / vec_per_row, c = idx[u] - r * vec_per_row;
+              const uint4* src_p = peer + ((prow0 + r) * p.ag.lda) / 8 + c;
+              asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(tmp[u].x), "=r"(tmp[u].y), "=r"(tmp[u].z), "=r"(tmp[u].w) : "l"(src_p) : "memory");
             }
           }
-          __threadfence();
-          __syncwarp();
-          if (lane == 0) {
-            const unsigned int prev = atomicAdd(p.ag.chunk_ctr + chunk, 1u);
-            if (prev + 1 == gridDim.x * COPY_WARPS) p_st_release_gpu(p.ag.chunk_flags + chunk, p.ag.epoch);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (idx[u] < hi) {
+              const size_t r = idx[u] / vec_per_row, c = idx[u] - r * vec_per_row;
+              *(static_cast<uint4*>(p.ag.a_stage) + ((srow0 + r) * p.ag.ld_stage) / 8 + c) = tmp[u];
+            }
           }
+        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          const unsigned int prev = atomicAdd(p.ag.chunk_ctr + chunk, 1u);
+          if (prev + 1 == static_cast<unsigned int>(team) * COPY_WARPS) p_st_release_gpu(p.ag.chunk_flags + chunk, p.ag.epoch);
+        }
+      }
+    }
+    if (rs) {
+      // ---- reduce-scatter: pull and add the partials of my row blocks as they complete ----
+      const int cw = warp - 10;
+      const int bpr = p.rs.rows / (2 * BM);                                   // my 256-row blocks
+      const size_t vec_per_row = static_cast<size_t>(p.N) / 8;
+      const size_t vec_per_block = vec_per_row * 2 * BM;
+      const int team = p.rs.team, n_teams = gridDim.x / team;
+      const int my_team = blockIdx.x / team, member = blockIdx.x - my_team * team;
+      const size_t lo = vec_per_block * member / team, hi = vec_per_block * (member + 1) / team;
+      const uint32_t* my_ready = p.rs.ready[p.rs.rank];
+      for (int bi = my_team; bi < bpr && my_team < n_teams; bi += n_teams) {
+        int okf = 1;
+        if (lane == 0) {
+          for (int sidx = 0; sidx < p.rs.W && okf; ++sidx)
+            okf = p_wait_flag<true>(my_ready + sidx * bpr + bi, p.rs.epoch, p.rs.wait_ns, p.status) ? 1 : 0;
+        }
+        okf = __shfl_sync(0xffffffffu, okf, 0);
+        if (!okf) break;
+        const size_t grow0 = (static_cast<size_t>(p.rs.rank) * bpr + bi) * 2 * BM;   // first global row of the block
+        const size_t lrow0 = static_cast<size_t>(bi) * 2 * BM;
+        for (size_t v = lo + (cw * 32 + lane); v < hi; v += COPY_WARPS * 32) {
+          const size_t r = v / vec_per_row, c = (v - r * vec_per_row) * 8;
+          float acc8[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc8[j] = 0.f;
+          for (int sidx = 0; sidx < p.rs.W; ++sidx) {      // fixed rank order
+            const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(p.rs.p_peer[sidx]) + (grow0 + r) * p.ldc + c;
+            uint4 x;
+            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(x.x), "=r"(x.y), "=r"(x.z), "=r"(x.w) : "l"(src) : "memory");
+            acc8[0] += bf16_lo(x.x); acc8[1] += bf16_hi(x.x); acc8[2] += bf16_lo(x.y); acc8[3] += bf16_hi(x.y);
+            acc8[4] += bf16_lo(x.z); acc8[5] += bf16_hi(x.z); acc8[6] += bf16_lo(x.w); acc8[7] += bf16_hi(x.w);
+          }
+          if (p.rs.res) {
+            const uint4 x = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.rs.res) +
+                                                            (lrow0 + r) * p.rs.ld_res + c);
+            acc8[0] += bf16_lo(x.x); acc8[1] += bf16_hi(x.x); acc8[2] += bf16_lo(x.y); acc8[3] += bf16_hi(x.y);
+            acc8[4] += bf16_lo(x.z); acc8[5] += bf16_hi(x.z); acc8[6] += bf16_lo(x.w); acc8[7] += bf16_hi(x.w);
+          }
+          uint4 o;
+          o.x = pack_bf16x2(acc8[0], acc8[1]); o.y = pack_bf16x2(acc8[2], acc8[3]);
+          o.z = pack_bf16x2(acc8[4], acc8[5]); o.w = pack_bf16x2(acc8[6], acc8[7]);
+          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.rs.out) + (lrow0 + r) * p.rs.ld_out + c) = o;
         }
       }
     }
@@ -434,6 +511,21 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
+      if (rs) {
+        // this warp's share of the tile is stored: publish it, count it; the warp that completes the
+        // 256-row block raises the block's flag on its owner
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const unsigned int prev = atomicAdd(p.rs.block_ctr + m2, 1u);
+          if (prev + 1 == static_cast<unsigned int>(nt) * 16u) {
+            const int bpr = p.rs.rows / (2 * BM);
+            const int owner = m2 / bpr;
+            __threadfence_system();
+            p_st_release_sys(p.rs.ready[owner] + p.rs.rank * bpr + (m2 - owner * bpr), p.rs.epoch);
+          }
+        }
+      }
     }
   }
 
@@ -444,6 +536,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   cluster_sync_all();
   tc_fence_after();
   if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  if (rs && threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int prev = atomicAdd(p.rs.cta_ctr, 1u);
+    if (prev == gridDim.x - 1) {
+      *p.rs.cta_ctr = 0;
+      for (int i = 0; i < mt2; ++i) p.rs.block_ctr[i] = 0;
+      if (*reinterpret_cast<volatile int*>(p.status) == 0) {
+        // every CTA of this rank has finished pulling: the peers may overwrite their partials; stay until
+        // the peers have finished pulling mine
+        __threadfence_system();
+        for (int r = 0; r < p.rs.W; ++r) p_st_release_sys(p.rs.flags[r] + 1 * FLAG_STRIDE + p.rs.rank, p.rs.epoch);
+        for (int sidx = 0; sidx < p.rs.W; ++sidx)
+          if (!p_wait_flag<true>(p.rs.flags[p.rs.rank] + 1 * FLAG_STRIDE + sidx, p.rs.epoch, p.rs.wait_ns, p.status)) break;
+      }
+    }
+  }
   if (ag && threadIdx.x == 0) {
     // last CTA: reset the counters; tell the peers this rank has stopped reading their shards and stay
     // until they have stopped reading this rank's shard (the caller may then overwrite it)
@@ -486,7 +594,8 @@ static int max_pairs() {
 }
 
 template <bool A_MN, bool B_MN>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int grid, cudaStream_t stream) {
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int grid, cudaStream_t stream,
+                  const CUtensorMap* ta_own = nullptr) {
   auto kern = gemm_pair_kernel<A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -506,7 +615,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p,
   at[0].val.clusterDim.z = 1;
   cfg.attrs = at;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, ta, tb, p) == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+  return cudaLaunchKernelEx(&cfg, kern, ta, tb, ta_own ? *ta_own : ta, p) == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
 
 }  // namespace pair
@@ -552,6 +661,7 @@ extern "C" int sb_gemm_pair_bf16(const void* A, const void* B, void* C, const vo
   }
   p.gu = gu; p.ld_gu = ld_gu;
   p.ag.W = 0;
+  p.rs.W = 0;
   const int mt2 = (M + 2 * BM - 1) / (2 * BM), nt = ff ? (ff + BNH - 1) / BNH : (N + BN - 1) / BN;
   const int num_kb = (K + BK - 1) / BK;
   const int pairs_avail = max_pairs();
@@ -607,6 +717,7 @@ extern "C" int sb_gemm_pair_ag_bf16(void* const* a_ptrs, const void* B, void* C,
   p.ff = 0; p.act = nullptr; p.ld_act = 0; p.gu = nullptr; p.ld_gu = 0;
   p.partials = nullptr;
   p.sched.dp_tiles = p.sched.sk_tiles = p.sched.sk_workers = p.sched.sk_slots = 0;
+  p.rs.W = 0;
   p.ag.W = W; p.ag.rank = rank; p.ag.rows = M / W; p.ag.lda = lda;
   p.ag.a_stage = a_stage; p.ag.ld_stage = ld_stage;
   for (int r = 0; r < MAXW; ++r) {
@@ -618,6 +729,62 @@ extern "C" int sb_gemm_pair_ag_bf16(void* const* a_ptrs, const void* B, void* C,
   p.ag.wait_ns = wait_ms > 0 ? static_cast<uint64_t>(wait_ms) * 1000000ull : 10000000000ull;
   // every CTA pair runs copier warps, so the whole device is launched whatever the tile count
   const int grid = 2 * max_pairs();
+  CUtensorMap ta_own;
+  rc = make_tmap_2d_bf16(&ta_own, a_ptrs[rank], K, M / W, lda, BK, BM);
+  if (rc) return rc;
+  // a team of CTAs shares one 128-row chunk so that every member moves about 32 KB of it
+  const long long chunk_bytes = static_cast<long long>(BM) * K * 2;
+  int team = static_cast<int>((chunk_bytes + 32767) / 32768);
+  if (team < 1) team = 1;
+  if (team > grid) team = grid;
+  p.ag.team = team;
+  if (!b_mn) return launch<false, false>(ta, tb, p, grid, stream, &ta_own);
+  return launch<false, true>(ta, tb, p, grid, stream, &ta_own);
+}
+
+// GEMM -> reduce-scatter on CTA pairs: out[M/W, N] = rows of this rank of sum over ranks (A_r * op(B_r)) (+ res).
+// part_ptrs[s]: rank s's partial buffer [M, ldp] (symmetric memory, peer-mapped; entry `rank` is the local
+// one this call writes); ready_ptrs[r]: rank r's [W][M/W/256] epoch words; flag_ptrs[r]: the call site's flag
+// slot on rank r; block_ctr: M/256 words, cta_ctr: one word (zero on entry, left zero). (M / W) % 256 == 0.
+extern "C" int sb_gemm_pair_rs_bf16(const void* A, const void* B, void* const* part_ptrs, int ldp, void* out, int ld_out,
+                                    const void* res, int ld_res, int M, int N, int K, int lda, int ldb, int b_mn,
+                                    void* const* ready_ptrs, void* const* flag_ptrs, unsigned int* block_ctr,
+                                    unsigned int* cta_ctr, int rank, int W, uint32_t epoch, int wait_ms, int* status,
+                                    void* stream_) {
+  using namespace sb::pair;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0 || W < 2 || W > MAXW || rank < 0 || rank >= W) return SB_ERR_ARG;
+  if ((N & 7) || (ldp & 7) || (ld_out & 7) || (res && (ld_res & 7)) || (M % (W * 2 * BM))) return SB_ERR_ARG;
+  void* C = part_ptrs[rank];
+  if ((reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return SB_ERR_ALIGN;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d_bf16(&ta, A, K, M, lda, BK, BM);
+  if (rc) return rc;
+  if (!b_mn) rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, BNH);
+  else rc = make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, BK);
+  if (rc) return rc;
+  Params p;
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldp; p.R = nullptr; p.ldr = 0; p.status = status;
+  p.ff = 0; p.act = nullptr; p.ld_act = 0; p.gu = nullptr; p.ld_gu = 0;
+  p.partials = nullptr;
+  p.sched.dp_tiles = p.sched.sk_tiles = p.sched.sk_workers = p.sched.sk_slots = 0;
+  p.ag.W = 0;
+  p.rs.W = W; p.rs.rank = rank; p.rs.rows = M / W;
+  for (int r = 0; r < MAXW; ++r) {
+    p.rs.p_peer[r] = r < W ? part_ptrs[r] : nullptr;
+    p.rs.ready[r] = r < W ? static_cast<uint32_t*>(ready_ptrs[r]) : nullptr;
+    p.rs.flags[r] = r < W ? static_cast<uint32_t*>(flag_ptrs[r]) : nullptr;
+  }
+  p.rs.block_ctr = block_ctr; p.rs.cta_ctr = cta_ctr;
+  p.rs.out = out; p.rs.ld_out = ld_out; p.rs.res = res; p.rs.ld_res = ld_res;
+  p.rs.epoch = epoch;
+  p.rs.wait_ns = wait_ms > 0 ? static_cast<uint64_t>(wait_ms) * 1000000ull : 10000000000ull;
+  const int grid = 2 * max_pairs();
+  const long long block_bytes = static_cast<long long>(2 * BM) * N * 2 * W;   // bytes read per 256-row block
+  int team = static_cast<int>((block_bytes + 65535) / 65536);
+  if (team < 1) team = 1;
+  if (team > grid) team = grid;
+  p.rs.team = team;
   if (!b_mn) return launch<false, false>(ta, tb, p, grid, stream);
   return launch<false, true>(ta, tb, p, grid, stream);
 }

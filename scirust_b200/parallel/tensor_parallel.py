@@ -40,6 +40,11 @@ _lib.register("sb_gemm_pair_ag_bf16", [_lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.
                                        _lib.vp, _lib.vp, _lib.i32, _lib.i32, C.c_uint32, _lib.i32, _lib.vp, _lib.vp])
 
 
+_lib.register("sb_gemm_pair_rs_bf16", [_lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.vp, _lib.i32, _lib.vp, _lib.i32, _lib.i32,
+                                       _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.vp, _lib.vp, _lib.vp,
+                                       _lib.vp, _lib.i32, _lib.i32, C.c_uint32, _lib.i32, _lib.vp, _lib.vp])
+
+
 class TPContext:
     """Process-group state for the fused tensor-parallel kernels: a symmetric region holding the
     peer-visible activation buffers, the double-buffered reduce-scatter staging area and the flag
@@ -71,6 +76,11 @@ class TPContext:
             # local landing buffer of the all-gather -> GEMM products (allocated on first use)
             self._ag_stage = None
             self._ag_flags = torch.zeros(2 * (max_rows // 128 + 2), dtype=torch.int32, device=self.dev)
+            # reduce-scatter on the pair kernel: "block complete" epochs pushed by the peers, local counters
+            self._rs_ready = self.region.tensor((8 * 512,), torch.int32)
+            self._rs_ready.zero_()
+            self._rs_ready_ptrs = self.region.peer_ptrs(self._rs_ready)
+            self._rs_ctr = torch.zeros(max_rows // 256 + 4, dtype=torch.int32, device=self.dev)
         else:
             self.region = None
 
@@ -105,6 +115,28 @@ class TPContext:
                   _lib.status_word(self.dev).data_ptr(), _lib.stream())
         _g.launch_count += 1
         return out
+
+    def _rs_pair(self, a, w, out, residual, M, N, K, b_mn):
+        """GEMM -> reduce-scatter on the CTA-pair kernel: the partial product stays in this rank's
+        symmetric buffer and the owners pull and add the partials of their rows block by block."""
+        self.epoch += 1
+        part = self.stage[self.rs_calls & 1]
+        ptrs = self.stage_ptrs[self.rs_calls & 1]
+        self.rs_calls += 1
+        if M * N > part.numel():
+            raise ValueError("reduce-scatter staging area too small for this product")
+        n = self._rs_ctr.numel()
+        _lib.call("sb_gemm_pair_rs_bf16", a.data_ptr(), w.data_ptr(), ptrs, N, out.data_ptr(), out.stride(0),
+                  _lib.ptr(residual), residual.stride(0) if residual is not None else 0, M, N, K, a.stride(0),
+                  w.stride(0), int(b_mn), self._rs_ready_ptrs, self.flag_ptrs, self._rs_ctr.data_ptr(),
+                  self._rs_ctr[n - 1:].data_ptr(), self.rank, self.world, self.epoch, self.wait_ms,
+                  _lib.status_word(self.dev).data_ptr(), _lib.stream())
+        _g.launch_count += 1
+        return out
+
+    def _rs_pair_ok(self, M, N):
+        return (self.pair and self.world > 1 and M % (self.world * 256) == 0 and N % 8 == 0
+                and self.world * (M // self.world // 256) <= 8 * 512 and M // 256 + 2 <= self._rs_ctr.numel())
 
     def _pair_ok(self, M, K):
         return (self.pair and self.world > 1 and M % (self.world * 256) == 0 and K % 8 == 0
@@ -172,6 +204,8 @@ class TPContext:
             dist.reduce_scatter_tensor(out, full, group=self.group)
             return out + residual_shard if residual_shard is not None else out
         out = torch.empty((Tl, N), dtype=BF, device=self.dev)
+        if self._rs_pair_ok(T, N):
+            return self._rs_pair(a, w, out, residual_shard, T, N, K, True)
         return self._call(a, w, out, residual_shard, T, N, K, False, True, False, False, True)
 
     def matmul_nt_rs(self, a, w, residual_shard=None):
@@ -185,6 +219,8 @@ class TPContext:
             dist.reduce_scatter_tensor(out, full, group=self.group)
             return out + residual_shard if residual_shard is not None else out
         out = torch.empty((Tl, N), dtype=BF, device=self.dev)
+        if self._rs_pair_ok(T, N):
+            return self._rs_pair(a, w, out, residual_shard, T, N, K, False)
         return self._call(a, w, out, residual_shard, T, N, K, False, False, False, False, True)
 
     def ag_matmul_tn(self, x_shard, dy, out=None, residual=None):
