@@ -1,7 +1,8 @@
 """Optimizers over N-D ``torch`` parameters (scirust-core/src/nn/nd_optim.rs:56-2428 and the raw-slice
 family of scirust-core/src/optim.rs:40-232): RMSprop, Lion, LAMB, Adafactor, Muon (momentum
 orthogonalised by Newton-Schulz iterations), Lookahead, SAM, Sophia-style clipped second-order,
-Adan, AdEMAMix, schedule-free SGD, Prodigy-style distance adaptation and GaLore low-rank projection.
+Adan, AdEMAMix, schedule-free SGD, Prodigy-style distance adaptation, GaLore low-rank projection,
+Shampoo and SOAP (Kronecker-factored preconditioners).
 Each follows the ``torch.optim.Optimizer`` protocol (``step()`` after ``backward()``)."""
 from __future__ import annotations
 
@@ -353,3 +354,113 @@ class Prodigy(Optimizer):
                 p.addcdiv_(m, v.sqrt() + self.d * g["eps"], value=-g["lr"] * self.d)
         if den > 0:
             self.d = max(self.d, self.num / den)
+
+
+def _sym_eigh(a: torch.Tensor):
+    """Eigen-decomposition of a symmetric matrix in fp64 with a sign convention (largest-magnitude
+    entry of every eigenvector positive), so that repeated runs give the same basis. The reference
+    uses cyclic Jacobi sweeps (nd_optim.rs:720-783); any orthonormal eigenbasis serves the optimizers."""
+    w, q = torch.linalg.eigh(a.double())
+    idx = q.abs().argmax(dim=0)
+    sign = torch.sign(q[idx, torch.arange(q.shape[1], device=q.device)])
+    sign[sign == 0] = 1.0
+    return w, q * sign
+
+
+def inverse_pth_root(a: torch.Tensor, p: float, eps: float) -> torch.Tensor:
+    """(A + eps I)^(-1/p) of a symmetric positive semi-definite matrix through its eigen-decomposition
+    (nd_optim.rs:1596-1624); eigenvalues are clamped at eps before the root."""
+    w, q = _sym_eigh(a)
+    d = (w.clamp_min(0.0) + eps).pow(-1.0 / p)
+    return ((q * d) @ q.t()).to(a.dtype)
+
+
+class Shampoo(Optimizer):
+    """Shampoo (nd_optim.rs:1629-1840): for a 2-D weight the Kronecker factors L = E[G G^T],
+    R = E[G^T G] (running averages with decay ``beta``) and the step W -= lr * L^(-1/4) G R^(-1/4);
+    the inverse roots are refreshed every ``precond_freq`` steps. Other shapes use diagonal Adagrad."""
+
+    def __init__(self, params, lr=0.1, beta=0.95, eps=1e-6, weight_decay=0.0, precond_freq=1):
+        super().__init__(params, dict(lr=lr, beta=beta, eps=eps, weight_decay=weight_decay, precond_freq=precond_freq))
+        self.t = 0
+
+    @torch.no_grad()
+    def step(self):
+        self.t += 1
+        for g in self.param_groups:
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                grad = p.grad.float()
+                st = self.state[p]
+                if p.dim() == 2 and min(p.shape) >= 2:
+                    m, n = p.shape
+                    if "l" not in st:
+                        st["l"] = torch.zeros(m, m, dtype=torch.float32, device=p.device)
+                        st["r"] = torch.zeros(n, n, dtype=torch.float32, device=p.device)
+                    st["l"].mul_(g["beta"]).add_(grad @ grad.t(), alpha=1 - g["beta"])
+                    st["r"].mul_(g["beta"]).add_(grad.t() @ grad, alpha=1 - g["beta"])
+                    if "il" not in st or self.t % g["precond_freq"] == 0:
+                        st["il"] = inverse_pth_root(st["l"], 4.0, g["eps"])
+                        st["ir"] = inverse_pth_root(st["r"], 4.0, g["eps"])
+                    u = st["il"] @ grad @ st["ir"]
+                    p.sub_((u + g["weight_decay"] * p.float()).to(p.dtype), alpha=g["lr"])
+                else:
+                    g2 = st.setdefault("g2", torch.zeros_like(grad))
+                    g2.addcmul_(grad, grad)
+                    u = grad / (g2.sqrt() + g["eps"])
+                    p.sub_((u + g["weight_decay"] * p.float()).to(p.dtype), alpha=g["lr"])
+
+
+class SOAP(Optimizer):
+    """SOAP (nd_optim.rs:790-1010): Adam run in the eigenbasis of Shampoo's factors. For a 2-D weight the
+    gradient is rotated (G^ = Q_L^T G Q_R), Adam's moments live in that basis, the update is rotated back;
+    the factors are running averages with decay ``shampoo_beta``; every ``precond_freq`` steps the bases are
+    recomputed and the moments rotated into them (the second moment kept non-negative). Other shapes use
+    plain Adam."""
+
+    def __init__(self, params, lr=3e-3, betas=(0.9, 0.999), shampoo_beta=0.95, eps=1e-8, weight_decay=0.0,
+                 precond_freq=10):
+        super().__init__(params, dict(lr=lr, betas=betas, shampoo_beta=shampoo_beta, eps=eps,
+                                      weight_decay=weight_decay, precond_freq=precond_freq))
+        self.t = 0
+
+    @torch.no_grad()
+    def step(self):
+        self.t += 1
+        for g in self.param_groups:
+            b1, b2 = g["betas"]
+            bc1, bc2 = 1 - b1 ** self.t, 1 - b2 ** self.t
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                grad = p.grad.float()
+                st = self.state[p]
+                if "m" not in st:
+                    st["m"] = torch.zeros_like(grad)
+                    st["v"] = torch.zeros_like(grad)
+                matrix = p.dim() == 2 and min(p.shape) >= 2
+                if matrix and "ql" not in st:      # first touch: factors and bases from this gradient
+                    st["l"] = grad @ grad.t()
+                    st["r"] = grad.t() @ grad
+                    st["ql"] = _sym_eigh(st["l"])[1].float()
+                    st["qr"] = _sym_eigh(st["r"])[1].float()
+                ghat = st["ql"].t() @ grad @ st["qr"] if matrix else grad
+                st["m"].mul_(b1).add_(ghat, alpha=1 - b1)
+                st["v"].mul_(b2).addcmul_(ghat, ghat, value=1 - b2)
+                upd = (st["m"] / bc1) / ((st["v"] / bc2).sqrt() + g["eps"])
+                if matrix:
+                    upd = st["ql"] @ upd @ st["qr"].t()
+                p.sub_((upd + g["weight_decay"] * p.float()).to(p.dtype), alpha=g["lr"])
+                if not matrix:
+                    continue
+                sb = g["shampoo_beta"]
+                st["l"].mul_(sb).add_(grad @ grad.t(), alpha=1 - sb)
+                st["r"].mul_(sb).add_(grad.t() @ grad, alpha=1 - sb)
+                if self.t % g["precond_freq"] == 0:
+                    ql_new = _sym_eigh(st["l"])[1].float()
+                    qr_new = _sym_eigh(st["r"])[1].float()
+                    rot_l, rot_r = ql_new.t() @ st["ql"], st["qr"].t() @ qr_new
+                    st["m"] = rot_l @ st["m"] @ rot_r
+                    st["v"] = (rot_l @ st["v"] @ rot_r).abs()
+                    st["ql"], st["qr"] = ql_new, qr_new

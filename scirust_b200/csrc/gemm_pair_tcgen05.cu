@@ -356,29 +356,65 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (!okf) break;
         const size_t grow0 = (static_cast<size_t>(p.rs.rank) * bpr + bi) * 2 * BM;   // first global row of the block
         const size_t lrow0 = static_cast<size_t>(bi) * 2 * BM;
-        for (size_t v = lo + (cw * 32 + lane); v < hi; v += COPY_WARPS * 32) {
-          const size_t r = v / vec_per_row, c = (v - r * vec_per_row) * 8;
-          float acc8[8];
+        for (size_t v0 = lo + (cw * 32 + lane); v0 < hi; v0 += COPY_WARPS * 32 * 4) {
+          // four 16-byte columns per thread and two sources at a time in flight; the sum runs in rank order
+          float acc8[4][8];
+          size_t off_p[4], off_l[4];
+          bool live[4];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) acc8[j] = 0.f;
-          for (int sidx = 0; sidx < p.rs.W; ++sidx) {      // fixed rank order
-            const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(p.rs.p_peer[sidx]) + (grow0 + r) * p.ldc + c;
-            uint4 x;
-            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(x.x), "=r"(x.y), "=r"(x.z), "=r"(x.w) : "l"(src) : "memory");
-            acc8[0] += bf16_lo(x.x); acc8[1] += bf16_hi(x.x); acc8[2] += bf16_lo(x.y); acc8[3] += bf16_hi(x.y);
-            acc8[4] += bf16_lo(x.z); acc8[5] += bf16_hi(x.z); acc8[6] += bf16_lo(x.w); acc8[7] += bf16_hi(x.w);
+          for (int u = 0; u < 4; ++u) {
+            const size_t v = v0 + static_cast<size_t>(u) * COPY_WARPS * 32;
+            live[u] = v < hi;
+            const size_t r = live[u] ? v / vec_per_row : 0, c = live[u] ? (v - r * vec_per_row) * 8 : 0;
+            off_p[u] = (grow0 + r) * p.ldc + c;
+            off_l[u] = (r << 20) | c;          // packed (row inside the block, column): N < 2^20
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc8[u][j] = 0.f;
           }
-          if (p.rs.res) {
-            const uint4 x = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.rs.res) +
-                                                            (lrow0 + r) * p.rs.ld_res + c);
-            acc8[0] += bf16_lo(x.x); acc8[1] += bf16_hi(x.x); acc8[2] += bf16_lo(x.y); acc8[3] += bf16_hi(x.y);
-            acc8[4] += bf16_lo(x.z); acc8[5] += bf16_hi(x.z); acc8[6] += bf16_lo(x.w); acc8[7] += bf16_hi(x.w);
+          for (int s0 = 0; s0 < p.rs.W; s0 += 2) {
+            uint4 x[2][4];
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+              if (s0 + t < p.rs.W) {
+                const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(p.rs.p_peer[s0 + t]);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                  if (live[u])
+                    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(x[t][u].x), "=r"(x[t][u].y), "=r"(x[t][u].z), "=r"(x[t][u].w)
+                                 : "l"(base + off_p[u]) : "memory");
+                }
+              }
+            }
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+              if (s0 + t < p.rs.W) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                  if (live[u]) {
+                    const uint4 y = x[t][u];
+                    acc8[u][0] += bf16_lo(y.x); acc8[u][1] += bf16_hi(y.x); acc8[u][2] += bf16_lo(y.y); acc8[u][3] += bf16_hi(y.y);
+                    acc8[u][4] += bf16_lo(y.z); acc8[u][5] += bf16_hi(y.z); acc8[u][6] += bf16_lo(y.w); acc8[u][7] += bf16_hi(y.w);
+                  }
+                }
+              }
+            }
           }
-          uint4 o;
-          o.x = pack_bf16x2(acc8[0], acc8[1]); o.y = pack_bf16x2(acc8[2], acc8[3]);
-          o.z = pack_bf16x2(acc8[4], acc8[5]); o.w = pack_bf16x2(acc8[6], acc8[7]);
-          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.rs.out) + (lrow0 + r) * p.rs.ld_out + c) = o;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (!live[u]) continue;
+            const size_t r = off_l[u] >> 20, c = off_l[u] & 0xfffff;
+            if (p.rs.res) {
+              const uint4 y = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.rs.res) +
+                                                              (lrow0 + r) * p.rs.ld_res + c);
+              acc8[u][0] += bf16_lo(y.x); acc8[u][1] += bf16_hi(y.x); acc8[u][2] += bf16_lo(y.y); acc8[u][3] += bf16_hi(y.y);
+              acc8[u][4] += bf16_lo(y.z); acc8[u][5] += bf16_hi(y.z); acc8[u][6] += bf16_lo(y.w); acc8[u][7] += bf16_hi(y.w);
+            }
+            uint4 o;
+            o.x = pack_bf16x2(acc8[u][0], acc8[u][1]); o.y = pack_bf16x2(acc8[u][2], acc8[u][3]);
+            o.z = pack_bf16x2(acc8[u][4], acc8[u][5]); o.w = pack_bf16x2(acc8[u][6], acc8[u][7]);
+            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.rs.out) + (lrow0 + r) * p.rs.ld_out + c) = o;
+          }
         }
       }
     }
@@ -737,6 +773,7 @@ extern "C" int sb_gemm_pair_ag_bf16(void* const* a_ptrs, const void* B, void* C,
   int team = static_cast<int>((chunk_bytes + 32767) / 32768);
   if (team < 1) team = 1;
   if (team > grid) team = grid;
+  team = grid / (grid / team);      // as few idle CTAs as the grid allows
   p.ag.team = team;
   if (!b_mn) return launch<false, false>(ta, tb, p, grid, stream, &ta_own);
   return launch<false, true>(ta, tb, p, grid, stream, &ta_own);
@@ -784,6 +821,7 @@ extern "C" int sb_gemm_pair_rs_bf16(const void* A, const void* B, void* const* p
   int team = static_cast<int>((block_bytes + 65535) / 65536);
   if (team < 1) team = 1;
   if (team > grid) team = grid;
+  team = grid / (grid / team);      // as few idle CTAs as the grid allows
   p.rs.team = team;
   if (!b_mn) return launch<false, false>(ta, tb, p, grid, stream);
   return launch<false, true>(ta, tb, p, grid, stream);

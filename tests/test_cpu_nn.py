@@ -99,7 +99,7 @@ def test_schedules():
 
 
 @pytest.mark.parametrize("name", ["RMSprop", "Lion", "LAMB", "Adafactor", "Muon", "Adan", "AdEMAMix", "Sophia",
-                                  "ScheduleFreeSGD", "GaLore", "Prodigy"])
+                                  "ScheduleFreeSGD", "GaLore", "Prodigy", "Shampoo", "SOAP"])
 def test_nd_optimizers_descend_a_quadratic(name):
     torch.manual_seed(0)
     target = torch.randn(8, 6)
@@ -108,7 +108,7 @@ def test_nd_optimizers_descend_a_quadratic(name):
     kw = {"Lion": dict(lr=3e-2), "ScheduleFreeSGD": dict(lr=0.5), "Muon": dict(lr=0.05, adam_lr=5e-2),
           "RMSprop": dict(lr=2e-2), "LAMB": dict(lr=5e-2), "Adafactor": dict(lr=5e-2), "Adan": dict(lr=5e-2),
           "AdEMAMix": dict(lr=5e-2), "Sophia": dict(lr=5e-2), "GaLore": dict(lr=5e-2, rank=4, update_gap=10),
-          "Prodigy": dict()}[name]
+          "Prodigy": dict(), "Shampoo": dict(lr=0.05), "SOAP": dict(lr=5e-2, precond_freq=5)}[name]
     opt = getattr(O, name)([w, b], **kw)
 
     def loss_fn():
@@ -119,6 +119,27 @@ def test_nd_optimizers_descend_a_quadratic(name):
         loss_fn().backward()
         opt.step()
     assert loss_fn().item() < 0.5 * first, (name, first, loss_fn().item())
+
+
+def test_inverse_root_and_soap_repeatability():
+    torch.manual_seed(1)
+    a = torch.randn(5, 5)
+    spd = a @ a.t() + 0.1 * torch.eye(5)
+    r = O.inverse_pth_root(spd, 4.0, 0.0)
+    back = torch.linalg.matrix_power(r, 4) @ spd          # (A^-1/4)^4 A = I
+    assert torch.allclose(back, torch.eye(5), atol=1e-3)
+
+    def run():
+        torch.manual_seed(2)
+        w = torch.nn.Parameter(torch.randn(6, 4))
+        opt = O.SOAP([w], lr=1e-2, precond_freq=3)
+        x = torch.randn(16, 6)
+        for _ in range(7):
+            opt.zero_grad()
+            ((x @ w) ** 2).mean().backward()
+            opt.step()
+        return w.detach().clone()
+    assert torch.equal(run(), run())                      # same bits on a second run
 
 
 def test_lookahead_sam_and_newton_schulz():
