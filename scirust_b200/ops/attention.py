@@ -16,9 +16,15 @@ from . import gemm as _g
 
 _lib.register("sb_attention_fwd", [_lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32,
                                    _lib.i32, _lib.i32, _lib.f32, _lib.i32, _lib.vp, _lib.vp])
+_lib.register("sb_attention_fwd_pp", [_lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32,
+                                      _lib.i32, _lib.i32, _lib.f32, _lib.i32, _lib.vp, _lib.vp])
 _lib.register("sb_attention_bwd", [_lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32,
                                    _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.f32,
                                    _lib.i32, _lib.vp, _lib.vp])
+
+# Head dimension 64 runs the kernel with two query tiles per CTA (output accumulator kept in tensor memory,
+# rescaled only when a row maximum grows by more than 2^8); SB_ATT_FWD=single selects the one-tile kernel.
+FWD_TWO_TILES = os.environ.get("SB_ATT_FWD", "pair") != "single"
 
 # The backward pass spills its dS tiles (bf16 [B*H, S, S]) to a scratch buffer so that dQ is a streamed
 # product instead of a second pass over scores and exponentials; above this size it recomputes instead.
@@ -63,7 +69,8 @@ def attention_fwd(qkv, B, S, H, Hkv, dh, causal=True, scale=None, want_lse=True)
         raise ValueError("qkv must be a 2-D bf16 matrix with unit inner stride")
     out = torch.empty((B * S, H * dh), dtype=torch.bfloat16, device=qkv.device)
     lse = torch.empty((B, H, S), dtype=torch.float32, device=qkv.device) if want_lse else None
-    _lib.call("sb_attention_fwd", qkv.data_ptr(), out.data_ptr(), _lib.ptr(lse), B, S, H, Hkv, dh, qkv.stride(0),
+    entry = "sb_attention_fwd_pp" if (FWD_TWO_TILES and dh == 64) else "sb_attention_fwd"
+    _lib.call(entry, qkv.data_ptr(), out.data_ptr(), _lib.ptr(lse), B, S, H, Hkv, dh, qkv.stride(0),
               out.stride(0), float(scale), int(causal), _lib.status_word(qkv.device).data_ptr(), _lib.stream())
     _g.launch_count += 1
     return out, lse
