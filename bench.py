@@ -143,12 +143,40 @@ def main():
                                                             gradient_as_bucket_view=True)
         trainer = TorchLibraryTrainer(model, ddp=ddp)
     else:
-        model = GQADecoder(cfg, device=dev, seed=1234)
-        reducer = None
-        if world > 1:
-            from scirust_b200.parallel.data_parallel import make_grad_reducer
-            reducer = make_grad_reducer(model, dist.group.WORLD, kind=args.comm)
-        trainer = Trainer(model, TrainerConfig(lr=3e-4, weight_decay=0.1, max_grad_norm=1.0), grad_reducer=reducer)
+        def build_trainer(comm):
+            m = GQADecoder(cfg, device=dev, seed=1234)
+            red = None
+            if world > 1:
+                from scirust_b200.parallel.data_parallel import make_grad_reducer
+                red = make_grad_reducer(m, dist.group.WORLD, kind=comm)
+            return Trainer(m, TrainerConfig(lr=3e-4, weight_decay=0.1, max_grad_norm=1.0), grad_reducer=red)
+
+        comm_used = args.comm
+        trainer = None
+        try:
+            trainer = build_trainer(args.comm)
+            ok = 1
+        except Exception as exc:  # symmetric-memory set-up refused (peer access, IPC): agree on the fallback below
+            print(f"[bench] rank {rank}: fused gradient reduce unavailable: {exc}", file=sys.stderr)
+            ok = 0
+        if world > 1 and args.comm == "fused":
+            # one probe step, then every rank learns whether all ranks came through it
+            if ok:
+                try:
+                    trainer.train_step(torch.zeros((B, S + 1), dtype=torch.int64, device=dev))
+                    _lib.check_status(dev)
+                except Exception as exc:
+                    print(f"[bench] rank {rank}: fused gradient reduce failed its probe step: {exc}", file=sys.stderr)
+                    ok = 0
+            flag = torch.tensor([ok], device=dev, dtype=torch.int32)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag.item()) == 0:
+                comm_used = "nccl"
+                trainer = None
+                torch.cuda.empty_cache()
+                trainer = build_trainer("nccl")
+        elif not ok:
+            raise SystemExit("trainer set-up failed")
 
     # synthetic data: a ring of pinned host batches, seeded per rank
     g = torch.Generator().manual_seed(1000 + rank)
@@ -227,7 +255,7 @@ def main():
                                 f"dh{cfg.head_dim} ff{cfg.d_ff} V{cfg.vocab_size}",
                        "global_batch": B * world, "seq_len": S, "parallelism": f"{args.parallelism}{world}",
                        "optimizer": "AdamW lr 3e-4 wd 0.1 clip 1.0, fp32 master weights",
-                       "grad_reduce": ("none" if world == 1 else "nccl-ddp" if args.impl == "baseline" else args.comm),
+                       "grad_reduce": ("none" if world == 1 else "nccl-ddp" if args.impl == "baseline" else comm_used),
                        "l2": "per-step working set (activations > 5 GB) exceeds the 126 MB L2; no flush needed"},
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "ms_per_step": max(ms_e2e, wall_ms) / args.steps},

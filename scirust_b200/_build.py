@@ -100,7 +100,10 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
         for src, obj, flags in stamps:
             _stamp(src, obj, headers, flags)
     if jobs or not CUDA_LIB.exists():
-        _run([nvcc, "-shared", "-o", str(CUDA_LIB), *map(str, objs), "-lcudart"])
+        # link beside the target and rename: a reader (or a copy of the tree) never sees a half-written library
+        tmp = CUDA_LIB.with_suffix(".so.tmp")
+        _run([nvcc, "-shared", "-o", str(tmp), *map(str, objs), "-lcudart"])
+        os.replace(tmp, CUDA_LIB)
     return CUDA_LIB
 
 
@@ -122,7 +125,9 @@ def build_rt(force: bool = False) -> Path:
         for src, obj in stamps:
             _stamp(src, obj, headers, CXX_FLAGS)
     if sources and (jobs or not RT_LIB.exists()):
-        _run([cxx, "-shared", "-pthread", "-o", str(RT_LIB), *map(str, objs)])
+        tmp = RT_LIB.with_suffix(".so.tmp")
+        _run([cxx, "-shared", "-pthread", "-o", str(tmp), *map(str, objs)])
+        os.replace(tmp, RT_LIB)
     return RT_LIB
 
 

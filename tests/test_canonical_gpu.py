@@ -1,0 +1,49 @@
+"""Canonical operators: the CUDA kernels agree with the CPU statement word for word."""
+import pytest
+import torch
+
+from scirust_b200.ops import canonical as K
+
+pytestmark = pytest.mark.gpu
+
+
+def _special(n, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(n, generator=g) * 3
+    x[:8] = torch.tensor([0.0, -0.0, float("inf"), float("-inf"), float("nan"), 1e-45, -1e-45, 3.4e38])
+    bits = x.view(torch.int32)
+    bits[4] = 0x7FC12345          # NaN with a payload
+    return x
+
+
+@pytest.mark.parametrize("op", ["relu", "scale", "add", "sub", "mul", "div", "copy"])
+def test_elementwise_bits(op):
+    a, b = _special(100003, 1), _special(100003, 2).flip(0)
+    kw = {"factor": 0.3} if op == "scale" else {}
+    ref = K.run(op, a, b if K.ARITY[op] == 2 else None, **kw)
+    out = K.run(op, a.cuda(), b.cuda() if K.ARITY[op] == 2 else None, **kw).cpu()
+    r, o = ref.view(torch.int32), out.view(torch.int32)
+    nan = torch.isnan(ref)
+    assert torch.equal(r[~nan], o[~nan])
+    assert torch.equal(torch.isnan(out), nan)
+    if op in ("relu", "copy"):
+        assert torch.equal(r, o)          # words move untouched, NaN payloads included
+
+
+@pytest.mark.parametrize("shape,perm", [((7, 5), (1, 0)), ((3, 4, 5), (2, 0, 1)), ((2, 3, 4, 5, 6), (4, 2, 0, 3, 1))])
+def test_permute_and_reshape_copy(shape, perm):
+    x = torch.randn(*shape)
+    out = K.run("permute", x.cuda(), perm=perm).cpu()
+    assert torch.equal(out, x.permute(perm).contiguous())
+    flat = K.run("copy", x.cuda(), shape=(x.numel(),)).cpu()
+    assert torch.equal(flat, x.reshape(-1))
+
+
+def test_refusals():
+    x = torch.ones(4)
+    with pytest.raises(K.Unsupported):
+        K.run("exp", x)
+    with pytest.raises(K.Unsupported):
+        K.run("log", x)
+    with pytest.raises(K.Unsupported):
+        K.run("tanh", x)

@@ -340,3 +340,17 @@ def test_interval_bounds_are_sound():
         x = x0 + (torch.rand(4) - 0.5) * 0.2
         y = torch.relu(x @ layers[0][0] + layers[0][1]) @ layers[1][0] + layers[1][1]
         assert (y >= lo - 1e-5).all() and (y <= hi + 1e-5).all()
+
+
+def test_canonical_operator_statements():
+    from scirust_b200.ops import canonical as K
+    x = torch.tensor([0.0, -0.0, float("nan"), 2.0, -1.0])
+    r = K.run("relu", x)
+    assert r[:2].view(torch.int32).tolist() == [0, 0] and torch.isnan(r[2]) and r[3:].tolist() == [2.0, 0.0]
+    assert K.run("scale", x, factor=0.5)[3:].tolist() == [1.0, -0.5]
+    q = K.run("div", torch.ones(2), torch.tensor([3.0, 0.0]))
+    assert q[0].item() == (torch.tensor(1.0) / torch.tensor(3.0)).item() and q[1].item() == float("inf")
+    assert K.run("permute", torch.arange(6.0).reshape(2, 3), perm=(1, 0)).tolist() == [[0, 3], [1, 4], [2, 5]]
+    for bad in ("exp", "log", "tanh"):
+        with pytest.raises(K.Unsupported):
+            K.run(bad, x)
