@@ -19,13 +19,15 @@
 //
 // A softmax thread holds its whole 128-column score row in registers (one pass over tensor memory),
 // scales it with packed fp32 pairs (fma.rn.f32x2, add.rn.f32x2: half the issue slots of scalar
-// code) and takes the row maximum with three-input max. Cycle stamps taken inside the kernel (issue
-// times of the products, arrival times of the softmax warps) fit a tensor pipe on which every
-// tcgen05.mma of a 128-row tile takes about the same time whatever its N: the 128x64 P V products
-// (8 instructions per kv block) then run at a quarter of the peak rate and the 128x128 score
-// products at half, about 1500 cycles per kv block of one tile, the same as the exponentials of its
-// softmax warps; issuing the scores of block j+1 early only delayed the P V of block j behind them. A polynomial 2^x on the FMA pipe (kept below, POLY_EVERY) therefore does not pay here: the
-// special-function unit is not the limiter, and the extra instructions slow the softmax warps down.
+// code) and takes the row maximum with three-input max. Cycle stamps taken inside the kernel put a kv
+// block of one tile at about 3500 cycles: 1500-1650 in the 128 exponentials with pack and store,
+// 400 in the row maximum, and about 1000 waiting for the tensor pipe (scores of the next block, P V
+// of the previous one), although the products themselves need only 256 + 436 cycles (a 128 x 128 x 16
+// tcgen05.mma takes 64 cycles, a 128 x 64 x 16 one 54.5: `bench_kernels umma`). Two variants that
+// looked right on paper measured slower and are not used: issuing the scores of block j+1 as soon
+// as block j sits in registers (the P V of block j then queued behind them), and taking every
+// fourth 2^x from a cubic polynomial on the FMA pipe (POLY_EVERY below; the softmax warps are short
+// of issue slots per warp, not of special-function throughput).
 //
 // Warps: 0 TMA producer, 1 MMA issuer, 2-5 softmax of tile 0, 6-9 softmax of tile 1.
 #include "sm100_ptx.cuh"
