@@ -67,18 +67,21 @@ __device__ __forceinline__ void bwd_chunk(uint32_t tm_S, uint32_t tm_dP, uint32_
   tmem_ld_32x32(tm_dP + lane_off + c * 32, dv);
   tmem_ld_wait();
   uint32_t pk[16], dk[16];
+  const float neg_lse2 = -lse2, neg_delta = -delta_s;
 #pragma unroll
   for (int i = 0; i < 32; i += 2) {
-    float p0 = fast_exp2(fmaf(__uint_as_float(sv[i]), sl2, -lse2));
-    float p1 = fast_exp2(fmaf(__uint_as_float(sv[i + 1]), sl2, -lse2));
+    // packed pairs: (s0, s1) * sl2 - lse2, (dP0, dP1) * scale - delta * scale, p * (...)
+    fma2(sv[i], sv[i + 1], sl2, neg_lse2);
+    fma2(dv[i], dv[i + 1], scale, neg_delta);
+    float p0 = fast_exp2(__uint_as_float(sv[i]));
+    float p1 = fast_exp2(__uint_as_float(sv[i + 1]));
     if (MASK) {
       if (c * 32 + i > lim) p0 = 0.f;
       if (c * 32 + i + 1 > lim) p1 = 0.f;
     }
-    const float d0 = p0 * fmaf(__uint_as_float(dv[i]), scale, -delta_s);
-    const float d1 = p1 * fmaf(__uint_as_float(dv[i + 1]), scale, -delta_s);
+    mul2(dv[i], dv[i + 1], p0, p1);
     if (WRITE_P) pk[i >> 1] = pack_bf16x2(p0, p1);
-    dk[i >> 1] = pack_bf16x2(d0, d1);
+    dk[i >> 1] = pack_bf16x2(__uint_as_float(dv[i]), __uint_as_float(dv[i + 1]));
   }
   if (WRITE_P) store_row32_sw128(p_buf, r, c, pk);
   store_row32_sw128(ds_buf, r, c, dk);

@@ -82,30 +82,6 @@ __device__ __forceinline__ float ex2_poly(float x) {
   pl = fmaf(pl, f, 0.9999280571937561f);
   return __int_as_float(__float_as_int(pl) + (__float_as_int(xr) << 23));
 }
-// Packed fp32 pairs (sm_100): one instruction, two lanes of fp32 math.
-__device__ __forceinline__ void fma2(uint32_t& x0, uint32_t& x1, float a, float b) {   // x = x * a + b, both lanes
-  asm("{\n"
-      ".reg .b64 vx, va, vb;\n"
-      "mov.b64 vx, {%0, %1};\n"
-      "mov.b64 va, {%2, %2};\n"
-      "mov.b64 vb, {%3, %3};\n"
-      "fma.rn.f32x2 vx, vx, va, vb;\n"
-      "mov.b64 {%0, %1}, vx;\n"
-      "}\n"
-      : "+r"(x0), "+r"(x1)
-      : "f"(a), "f"(b));
-}
-__device__ __forceinline__ void add2(float& s0, float& s1, uint32_t x0, uint32_t x1) {   // (s0, s1) += (x0, x1)
-  asm("{\n"
-      ".reg .b64 vs, vx;\n"
-      "mov.b64 vs, {%0, %1};\n"
-      "mov.b64 vx, {%2, %3};\n"
-      "add.rn.f32x2 vs, vs, vx;\n"
-      "mov.b64 {%0, %1}, vs;\n"
-      "}\n"
-      : "+f"(s0), "+f"(s1)
-      : "r"(x0), "r"(x1));
-}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));

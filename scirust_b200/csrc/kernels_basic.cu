@@ -377,6 +377,83 @@ ce_fwd_bwd_kernel(const __nv_bfloat16* __restrict__ logits, const int64_t* __res
 }
 
 // ---------------------------------------------------------------------------
+// Vocabulary-parallel softmax cross-entropy: every rank holds the logits of its vocabulary shard
+// [v0, v0 + cols). Phase 1 writes per-row (max, sum exp(x - max), target logit or 0) of the shard;
+// the ranks combine the three numbers; phase 2 turns the shard's logits into
+// (exp(x - lse) - onehot) * grad_scale with the global log-sum-exp. Rows with a negative target
+// contribute nothing.
+// ---------------------------------------------------------------------------
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
+ce_shard_stats_kernel(const __nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ targets,
+                      float* __restrict__ stats, int rows, int cols, int ld, int v0) {
+  __shared__ MaxSum red[THREADS / 32];
+  const int r = blockIdx.x;
+  if (r >= rows) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const __nv_bfloat16* lr = logits + static_cast<size_t>(r) * ld;
+  MaxSum acc;
+  acc.m = -3.0e38f;
+  acc.s = 0.f;
+  for (int c = tid * 8; c < cols; c += THREADS * 8) {
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(lr + c), f);
+    float mx = f[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) mx = fmaxf(mx, f[j]);
+    const float m = fmaxf(acc.m, mx);
+    float s = acc.s * __expf(acc.m - m);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += __expf(f[j] - m);
+    acc.m = m;
+    acc.s = s;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    MaxSum other;
+    other.m = __shfl_xor_sync(0xffffffffu, acc.m, o);
+    other.s = __shfl_xor_sync(0xffffffffu, acc.s, o);
+    acc = (lane & o) ? ms_combine(other, acc) : ms_combine(acc, other);
+  }
+  if (lane == 0) red[warp] = acc;
+  __syncthreads();
+  if (tid == 0) {
+    MaxSum tot = red[0];
+#pragma unroll
+    for (int w = 1; w < THREADS / 32; ++w) tot = ms_combine(tot, red[w]);
+    const int64_t tgt = targets[r] - v0;
+    stats[r * 3 + 0] = tot.m;
+    stats[r * 3 + 1] = tot.s;
+    stats[r * 3 + 2] = (tgt >= 0 && tgt < cols && targets[r] >= 0) ? __bfloat162float(lr[tgt]) : 0.f;
+  }
+}
+
+__global__ void __launch_bounds__(512)
+ce_shard_grad_kernel(const __nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ targets,
+                     const float* __restrict__ lse, __nv_bfloat16* __restrict__ dlogits, int rows, int cols, int ld,
+                     int v0, float grad_scale) {
+  const int r = blockIdx.x;
+  if (r >= rows) return;
+  const __nv_bfloat16* lr = logits + static_cast<size_t>(r) * ld;
+  __nv_bfloat16* dr = dlogits + static_cast<size_t>(r) * ld;
+  const bool ignore = targets[r] < 0;
+  const int64_t tgt = targets[r] - v0;
+  const float l = lse[r];
+  const float gs = ignore ? 0.f : grad_scale;
+  for (int c = threadIdx.x * 8; c < cols; c += 512 * 8) {
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(lr + c), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float p = __expf(f[j] - l);
+      if (c + j == tgt) p -= 1.f;
+      f[j] = p * gs;
+    }
+    *reinterpret_cast<uint4*>(dr + c) = pack8(f);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Deterministic sum of squares of a flat bf16 or fp32 buffer: one fp32 partial per
 // block (fixed tree), then a single block adds the partials in a fixed strided order.
 // ---------------------------------------------------------------------------
@@ -644,6 +721,23 @@ extern "C" int sb_ce_fwd_bwd(const void* logits, const int64_t* targets, float* 
   ce_fwd_bwd_kernel<512><<<rows, 512, 0, STREAM>>>(static_cast<const __nv_bfloat16*>(logits), targets, loss_rows,
                                                    static_cast<__nv_bfloat16*>(dlogits), rows, cols, ld,
                                                    grad_scale);
+  CHECK_LAUNCH();
+}
+
+// stats: fp32 [rows, 3] = (max, sum exp(x - max), target logit or 0) of the shard starting at vocabulary id v0.
+extern "C" int sb_ce_shard_stats(const void* logits, const int64_t* targets, float* stats, int rows, int cols, int ld,
+                                 int v0, void* stream) {
+  if (rows <= 0 || cols <= 0 || (cols & 7) || (ld & 7) || !al16(logits)) return SB_ERR_ARG;
+  ce_shard_stats_kernel<512><<<rows, 512, 0, STREAM>>>(static_cast<const __nv_bfloat16*>(logits), targets, stats, rows,
+                                                       cols, ld, v0);
+  CHECK_LAUNCH();
+}
+// dlogits (may alias logits) = (exp(x - lse[row]) - onehot) * grad_scale for the shard's columns.
+extern "C" int sb_ce_shard_grad(const void* logits, const int64_t* targets, const float* lse, void* dlogits, int rows,
+                                int cols, int ld, int v0, float grad_scale, void* stream) {
+  if (rows <= 0 || cols <= 0 || (cols & 7) || (ld & 7) || !al16(logits) || !al16(dlogits)) return SB_ERR_ARG;
+  ce_shard_grad_kernel<<<rows, 512, 0, STREAM>>>(static_cast<const __nv_bfloat16*>(logits), targets, lse,
+                                                 static_cast<__nv_bfloat16*>(dlogits), rows, cols, ld, v0, grad_scale);
   CHECK_LAUNCH();
 }
 

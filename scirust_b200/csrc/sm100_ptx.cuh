@@ -339,6 +339,42 @@ __device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t* r)
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// ---- packed fp32 pairs (sm_100): one instruction, two lanes of fp32 math ---------
+__device__ __forceinline__ void fma2(uint32_t& x0, uint32_t& x1, float a, float b) {   // x = x * a + b, both lanes
+  asm("{\n"
+      ".reg .b64 vx, va, vb;\n"
+      "mov.b64 vx, {%0, %1};\n"
+      "mov.b64 va, {%2, %2};\n"
+      "mov.b64 vb, {%3, %3};\n"
+      "fma.rn.f32x2 vx, vx, va, vb;\n"
+      "mov.b64 {%0, %1}, vx;\n"
+      "}\n"
+      : "+r"(x0), "+r"(x1)
+      : "f"(a), "f"(b));
+}
+__device__ __forceinline__ void add2(float& s0, float& s1, uint32_t x0, uint32_t x1) {   // (s0, s1) += (x0, x1)
+  asm("{\n"
+      ".reg .b64 vs, vx;\n"
+      "mov.b64 vs, {%0, %1};\n"
+      "mov.b64 vx, {%2, %3};\n"
+      "add.rn.f32x2 vs, vs, vx;\n"
+      "mov.b64 {%0, %1}, vs;\n"
+      "}\n"
+      : "+f"(s0), "+f"(s1)
+      : "r"(x0), "r"(x1));
+}
+__device__ __forceinline__ void mul2(uint32_t& x0, uint32_t& x1, float y0, float y1) {   // (x0, x1) *= (y0, y1)
+  asm("{\n"
+      ".reg .b64 vx, vy;\n"
+      "mov.b64 vx, {%0, %1};\n"
+      "mov.b64 vy, {%2, %3};\n"
+      "mul.rn.f32x2 vx, vx, vy;\n"
+      "mov.b64 {%0, %1}, vx;\n"
+      "}\n"
+      : "+r"(x0), "+r"(x1)
+      : "f"(y0), "f"(y1));
+}
+
 // ---- bf16 helpers --------------------------------------------------------------
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);

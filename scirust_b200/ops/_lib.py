@@ -39,6 +39,8 @@ _CUDA_SIGS = {
     "sb_embed_fwd": [vp, vp, vp, i32, i32, i32, vp],
     "sb_embed_bwd": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
     "sb_ce_fwd_bwd": [vp, vp, vp, vp, i32, i32, i32, f32, vp],
+    "sb_ce_shard_stats": [vp, vp, vp, i32, i32, i32, i32, vp],
+    "sb_ce_shard_grad": [vp, vp, vp, vp, i32, i32, i32, i32, f32, vp],
     "sb_sumsq": [vp, sz, i32, vp, vp, i32, vp],
     "sb_optim_step": [vp, vp, vp, vp, i32, vp, sz, sz, f32, f32, f32, f32, f32, f32, f32, vp, f32, f32, i32, vp],
     "sb_cast": [vp, vp, sz, i32, f32, vp],

@@ -216,6 +216,47 @@ def ce_fwd_bwd(logits, targets, grad_scale, dlogits=None, in_place=True):
     return loss, dlogits
 
 
+def ce_shard_stats(logits, targets, v0):
+    """Per-row (max, sum exp(x - max), target logit or 0) of the vocabulary shard [v0, v0 + cols): fp32 [rows, 3]."""
+    rows, cols = logits.shape
+    if not logits.is_cuda:
+        lf = logits.float()
+        m = lf.max(-1).values
+        s = torch.exp(lf - m[:, None]).sum(-1)
+        loc = targets.reshape(-1) - v0
+        own = (loc >= 0) & (loc < cols) & (targets.reshape(-1) >= 0)
+        t = torch.where(own, lf.gather(1, loc.clamp(0, cols - 1)[:, None])[:, 0], torch.zeros_like(m))
+        return torch.stack([m, s, t], 1)
+    stats = torch.empty((rows, 3), dtype=torch.float32, device=logits.device)
+    _lib.call("sb_ce_shard_stats", logits.data_ptr(), targets.data_ptr(), stats.data_ptr(), rows, cols,
+              logits.stride(0), int(v0), _lib.stream())
+    _count()
+    return stats
+
+
+def ce_shard_grad(logits, targets, v0, lse, grad_scale, in_place=True):
+    """(exp(x - lse) - onehot) * grad_scale over the shard's columns; rows with a negative target give zeros."""
+    rows, cols = logits.shape
+    if not logits.is_cuda:
+        p = torch.exp(logits.float() - lse[:, None])
+        loc = targets.reshape(-1) - v0
+        own = (loc >= 0) & (loc < cols)
+        rws = torch.arange(rows)[own]
+        p[rws, loc[own]] -= 1
+        p *= grad_scale
+        p[targets.reshape(-1) < 0] = 0
+        d = p.to(logits.dtype)
+        if in_place:
+            logits.copy_(d)
+            d = logits
+        return d
+    out = logits if in_place else torch.empty_like(logits)
+    _lib.call("sb_ce_shard_grad", logits.data_ptr(), targets.data_ptr(), lse.data_ptr(), out.data_ptr(), rows, cols,
+              logits.stride(0), int(v0), float(grad_scale), _lib.stream())
+    _count()
+    return out
+
+
 def ce_loss_only(logits, targets):
     rows, cols = logits.shape
     if not logits.is_cuda:

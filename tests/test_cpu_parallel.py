@@ -186,6 +186,15 @@ def test_tp_inference_engine_on_gloo_ranks(world, kv):
     assert r.returncode == 0 and "TP_INFER_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_vocab_parallel_embedding_ce_argmax_on_gloo_ranks(world):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29660 + world), os.path.join(ROOT, "tests", "mp", "mp_vocab_parallel.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600,
+                       env=dict(os.environ, PYTHONPATH=ROOT, SB_TEST_DEVICE="cpu"))
+    assert r.returncode == 0 and "VOCAB_PARALLEL_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
 def test_native_tcp_tree_allreduce_is_bitwise_the_python_engine_and_interoperates():
     """The C++ transport (csrc/rt_collectives.cpp) speaks the same frames and sums in the same order:
     all-native worlds, and worlds mixing native and Python ranks, give the in-process engine's bits."""

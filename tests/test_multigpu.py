@@ -56,6 +56,12 @@ def test_tp_decoder_trains_like_single_gpu():
     assert "TP_MODEL_OK" in out
 
 
+def test_vocab_parallel_embedding_ce_argmax():
+    _need(2)
+    out = _run("mp_vocab_parallel.py", 2, 29619)
+    assert "VOCAB_PARALLEL_OK" in out
+
+
 def test_dp_cnn_fused_allreduce_with_overlap():
     _need(2)
     out = _run("mp_dp_cnn.py", 2, 29615)
