@@ -159,8 +159,10 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __gri
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_t = (p.S + BT - 1) / BT;
-  const int kt = blockIdx.x;  // kv tile
-  const int kvh = blockIdx.y, b = blockIdx.z;
+  // The kv tile is the slowest grid index: CTAs are handed out in block-id order, so all the long tiles
+  // (causal: small kt, up to 4x16 query tiles) start first and the short ones fill the tail.
+  const int kt = blockIdx.z;  // kv tile
+  const int kvh = blockIdx.x, b = blockIdx.y;
   const int group = p.H / p.Hkv;
   const int kv0 = kt * BT;
   const int row_base = b * p.S;
@@ -401,8 +403,8 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_t = (p.S + BT - 1) / BT;
-  const int qt = n_t - 1 - blockIdx.x;
-  const int head = blockIdx.y, b = blockIdx.z;
+  const int qt = n_t - 1 - blockIdx.z;   // slowest grid index: longest rows of tiles first over the whole grid
+  const int head = blockIdx.x, b = blockIdx.y;
   const int kvh = head / (p.H / p.Hkv);
   const int q0 = qt * BT;
   const int row_base = b * p.S;
@@ -603,8 +605,8 @@ attention_bwd_dq_stream_kernel(const __grid_constant__ CUtensorMap tm_qkv, const
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_t = (p.S + BT - 1) / BT;
-  const int qt = n_t - 1 - blockIdx.x;   // longest rows of tiles first
-  const int head = blockIdx.y, b = blockIdx.z;
+  const int qt = n_t - 1 - blockIdx.z;   // slowest grid index: longest rows of tiles first over the whole grid
+  const int head = blockIdx.x, b = blockIdx.y;
   const int kvh = head / (p.H / p.Hkv);
   const int q0 = qt * BT;
   const int row_base = b * p.S;
@@ -713,10 +715,10 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& td, const CUtens
     attr_set = true;
   }
   const int n_t = (p.S + BT - 1) / BT;
-  k1<<<dim3(n_t, p.Hkv, p.B), BWD_THREADS, DkvCfg<DH>::SMEM_BYTES, stream>>>(tq, td, tds, p);
+  k1<<<dim3(p.Hkv, p.B, n_t), BWD_THREADS, DkvCfg<DH>::SMEM_BYTES, stream>>>(tq, td, tds, p);
   if (cudaGetLastError() != cudaSuccess) return SB_ERR_LAUNCH;
-  if (p.spill_ds) k3<<<dim3(n_t, p.H, p.B), BWD_THREADS, DqsCfg<DH>::SMEM_BYTES, stream>>>(tq, tds, p);
-  else k2<<<dim3(n_t, p.H, p.B), BWD_THREADS, DqCfg<DH>::SMEM_BYTES, stream>>>(tq, td, p);
+  if (p.spill_ds) k3<<<dim3(p.H, p.B, n_t), BWD_THREADS, DqsCfg<DH>::SMEM_BYTES, stream>>>(tq, tds, p);
+  else k2<<<dim3(p.H, p.B, n_t), BWD_THREADS, DqCfg<DH>::SMEM_BYTES, stream>>>(tq, td, p);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
 
@@ -737,6 +739,7 @@ extern "C" int sb_attention_bwd(const void* qkv, const void* O, const float* lse
                                 float* delta, void* ds_scratch, int B, int S, int H, int Hkv, int dh, int ld,
                                 int ld_o, int ld_do, float scale, int causal, int* status, void* stream_) {
   if (B <= 0 || S <= 0 || H <= 0 || Hkv <= 0 || (H % Hkv) || (dh != 64 && dh != 128)) return SB_ERR_ARG;
+  if (B > 65535 || (S + 127) / 128 > 65535) return SB_ERR_TOO_LARGE;   // grid y / z limits
   if ((ld & 7) || (reinterpret_cast<uintptr_t>(dqkv) & 15)) return SB_ERR_ALIGN;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   CUtensorMap tq, td;

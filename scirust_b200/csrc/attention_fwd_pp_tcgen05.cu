@@ -109,8 +109,8 @@ attention_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap, const Params p
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_pairs = (p.S + 2 * BM - 1) / (2 * BM);
-  const int pair = n_pairs - 1 - blockIdx.x;  // longest tiles first
-  const int head = blockIdx.y, b = blockIdx.z;
+  const int pair = n_pairs - 1 - blockIdx.z;  // slowest grid index: longest tiles first over the whole grid
+  const int head = blockIdx.x, b = blockIdx.y;
   const int kvh = head / (p.H / p.Hkv);
   const int q0 = pair * 2 * BM;
   const int row_base = b * p.S;
@@ -366,6 +366,7 @@ using namespace sb;
 extern "C" int sb_attention_fwd_pp(const void* qkv, void* O, float* lse, int B, int S, int H, int Hkv, int dh, int ld,
                                    int ld_o, float scale, int causal, int* status, void* stream_) {
   if (B <= 0 || S <= 0 || H <= 0 || Hkv <= 0 || (H % Hkv) || dh != attpp::DH) return SB_ERR_ARG;
+  if (B > 65535 || (S + 127) / 128 > 65535) return SB_ERR_TOO_LARGE;   // grid y / z limits
   if ((ld_o & 7) || (reinterpret_cast<uintptr_t>(O) & 15)) return SB_ERR_ALIGN;
   CUtensorMap tm;
   int rc = make_tmap_2d_bf16(&tm, qkv, static_cast<uint64_t>(ld), static_cast<uint64_t>(B) * S, ld, 64, 128);
@@ -385,7 +386,7 @@ extern "C" int sb_attention_fwd_pp(const void* qkv, void* O, float* lse, int B, 
       return SB_ERR_LAUNCH;
     attr_set = true;
   }
-  dim3 grid((S + 2 * attpp::BM - 1) / (2 * attpp::BM), H, B);
+  dim3 grid(H, B, (S + 2 * attpp::BM - 1) / (2 * attpp::BM));
   kern<<<grid, attpp::THREADS, attpp::SMEM_BYTES, static_cast<cudaStream_t>(stream_)>>>(tm, p);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }

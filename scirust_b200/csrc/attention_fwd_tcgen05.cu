@@ -130,8 +130,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap, const AttParams p
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qt = (p.S + ATT_BM - 1) / ATT_BM;
-  const int qt = n_qt - 1 - blockIdx.x;  // longest (most kv blocks) tiles first
-  const int head = blockIdx.y, b = blockIdx.z;
+  const int qt = n_qt - 1 - blockIdx.z;  // slowest grid index: longest (most kv blocks) tiles first over the whole grid
+  const int head = blockIdx.x, b = blockIdx.y;
   const int kvh = head / (p.H / p.Hkv);
   const int q0 = qt * ATT_BM;
   const int row_base = b * p.S;
@@ -296,7 +296,7 @@ static int launch_att_fwd(const CUtensorMap& tm, const AttParams& p, cudaStream_
       return SB_ERR_LAUNCH;
     attr_set = true;
   }
-  dim3 grid((p.S + ATT_BM - 1) / ATT_BM, p.H, p.B);
+  dim3 grid(p.H, p.B, (p.S + ATT_BM - 1) / ATT_BM);
   kern<<<grid, ATT_THREADS, Cfg::SMEM_BYTES, stream>>>(tm, p);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
@@ -309,6 +309,7 @@ using namespace sb;
 extern "C" int sb_attention_fwd(const void* qkv, void* O, float* lse, int B, int S, int H, int Hkv, int dh, int ld,
                                 int ld_o, float scale, int causal, int* status, void* stream_) {
   if (B <= 0 || S <= 0 || H <= 0 || Hkv <= 0 || (H % Hkv) || (dh != 64 && dh != 128)) return SB_ERR_ARG;
+  if (B > 65535 || (S + 127) / 128 > 65535) return SB_ERR_TOO_LARGE;   // grid y / z limits
   if ((ld_o & 7) || (reinterpret_cast<uintptr_t>(O) & 15)) return SB_ERR_ALIGN;
   CUtensorMap tm;
   int rc = make_tmap_2d_bf16(&tm, qkv, static_cast<uint64_t>(ld), static_cast<uint64_t>(B) * S, ld, 64, 128);
