@@ -264,6 +264,13 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __gri
       for (int t = 0; t < n_iter && ok; ++t) {
         if (!mbar_wait(p_full, t & 1, p.status, ST_TIMEOUT_MISC)) { ok = false; break; }
         tc_fence_after();
+        // scores of t+1 first (double-buffered P^T / dS^T): the softmax warps wait for nothing else, and the
+        // commit of these scores also covers the gradient MMAs of t-1, which is what lets the softmax warps
+        // reuse the P^T / dS^T buffer of parity (t+1)&1
+        // (the dS store of t-1 has long been read out of its buffer; the wait only makes that certain before the
+        // scores whose completion lets the softmax warps write that buffer again)
+        if (p.spill_ds) tma_store_wait_read<0>();
+        if (Cfg::PDB && t + 1 < n_iter) ok = issue_scores();
         if (p.spill_ds) {
           // the finished dS tile (bf16, [q rows][kv], scale included) also goes to global memory, where
           // the dQ kernel streams it back instead of recomputing scores; the bulk store reads shared
@@ -271,18 +278,12 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __gri
           const int head = kvh * group + t / n_qt;
           const int qt = qt_first + t % n_qt;
           const uint8_t* src = sdST + (Cfg::PDB ? (t & 1) : 0) * Cfg::PT_BYTES;
-          tma_store_wait_read<0>();
           tma_store_3d(&tm_ds, src, kv0, qt * BT, b * p.H + head);
           tma_store_3d(&tm_ds, src + BT * 128, kv0 + 64, qt * BT, b * p.H + head);
           tma_store_commit();
         }
-        if (Cfg::PDB) {
-          // scores of t+1 first: their commit also covers the gradient MMAs of t-1, which is what
-          // lets the softmax warps reuse the P^T/dS^T buffer of parity (t+1)&1.
-          if (t + 1 < n_iter) ok = issue_scores();
-          issue_grads(t);
-        } else {
-          issue_grads(t);
+        issue_grads(t);
+        if (!Cfg::PDB) {
           if (p.spill_ds) tma_store_wait_read<0>();   // single dS buffer: read out before it is rewritten
           if (t + 1 < n_iter) ok = issue_scores();
         }
