@@ -13,6 +13,7 @@
 #include <math.h>
 #include <stdint.h>
 #include "api.h"
+#include <cstdlib>
 #include "sm100_ptx.cuh"
 
 namespace sb {
@@ -282,6 +283,209 @@ gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
       for (int u = 0; u < 8; ++u) if (k + u < ns) sum += v[u];
     }
     if (p.scale) sum *= p.scale[gc];
+    if (p.R) sum += __bfloat162float(p.R[static_cast<size_t>(m) * p.ldr + gc]);
+    if (p.out) p.out[static_cast<size_t>(m) * p.ldo + gc] = __float2bfloat16_rn(sum);
+    if (p.out_f32) p.out_f32[static_cast<size_t>(m) * N + gc] = sum;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// bf16 GEMV on tensor cores. The FMA kernel above spends about five thread instructions per weight
+// (unpack, convert, multiply-add) and is bound by instruction issue at 0.55-0.7 of the memory
+// bandwidth; here a warp turns a 16 (k) x 16 (n) block of weights into one ldmatrix.x4.trans and one
+// mma.sync.m16n8k16: the weights are the A operand (W^T: n rows, k columns), the up to 8 activation
+// rows are the 8 columns of B (unused columns are zero), and the accumulator holds 16 outputs x 8
+// rows in fp32. Same grid, ring, producer warp, prologues and split-K finish as the FMA kernel; the
+// weight tile arrives as four 128-byte-swizzled [32 k x 64 n] boxes so that ldmatrix is free of
+// bank conflicts; warp w owns columns [32w, 32w+32) of the CTA's 256, so no cross-warp sum exists.
+// The staged activations are bf16 pairs laid out [k / 2][8 rows], one conflict-free 32-bit load per
+// B fragment register.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void gemv_ldsm_x4_t(uint32_t addr, uint32_t (&a)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(addr));
+}
+__device__ __forceinline__ void gemv_mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(GEMV_THREADS)
+gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ GemvParams p) {
+  constexpr int COLS = 256;
+  extern __shared__ __align__(1024) uint8_t smem_mma[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_mma) + 1023) & ~uintptr_t(1023));
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(tiles + GEMV_STAGES * GEMV_TILE_BYTES);  // [k/2][8][2]
+  __shared__ uint64_t full[GEMV_STAGES], empty[GEMV_STAGES];
+  __shared__ float s_inv[8];
+  __shared__ int s_last;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int M = p.M, N = p.N, K = p.K;
+  const int col0 = blockIdx.x * COLS;
+  const int k0 = blockIdx.y * p.k_per_split;            // a multiple of 32
+  const int k1 = min(K, k0 + p.k_per_split);
+  const int ntiles = (k1 - k0 + GEMV_KT - 1) / GEMV_KT;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap_w);
+    for (int s = 0; s < GEMV_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 8); }
+    fence_barrier_init();
+  }
+  __syncthreads();
+
+  float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+  const int g = lane >> 2, tq = lane & 3;   // mma fragment coordinates of this lane
+
+  if (warp == 8) {
+    // ------------------------------ producer ------------------------------
+    for (int t = 0; t < ntiles; ++t) {
+      const int s = t % GEMV_STAGES;
+      if (t >= GEMV_STAGES && !mbar_wait(&empty[s], ((t / GEMV_STAGES) - 1) & 1, p.status, ST_TIMEOUT_EMPTY)) break;
+      if (lane == 0) {
+        // rows past K and columns past N arrive as zeros and still count towards the byte total
+        mbar_arrive_expect_tx(&full[s], GEMV_TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          tma_load_2d(tiles + s * GEMV_TILE_BYTES + c * (GEMV_KT * 128), &tmap_w, &full[s], col0 + c * 64,
+                      k0 + t * GEMV_KT);
+      }
+      __syncwarp();
+    }
+    pdl_wait();
+  } else {
+    // ------------------------------ consumers -----------------------------
+    pdl_wait();   // X, the residual and the workspace belong to the previous kernel until here
+    if (p.prologue == PRO_RMSNORM) {
+      // row statistic with the association of rmsnorm_fwd_kernel (see the FMA kernel)
+      float* s_part = reinterpret_cast<float*>(xs);   // [M][8 warps][32 lanes], overwritten by the staging below
+      for (int m = 0; m < M; ++m) {
+        const __nv_bfloat16* xr = p.X + static_cast<size_t>(m) * p.ldx;
+        float a = 0.f;
+        for (int c = lane * 8 + warp * 256; c < K; c += 8 * 256) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
+          const float f[8] = {dbflo(raw.x), dbfhi(raw.x), dbflo(raw.y), dbfhi(raw.y),
+                              dbflo(raw.z), dbfhi(raw.z), dbflo(raw.w), dbfhi(raw.w)};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a += f[j] * f[j];
+        }
+        s_part[(m * 8 + warp) * 32 + lane] = a;
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (warp < M) {
+        float ss = s_part[(warp * 8) * 32 + lane];
+#pragma unroll
+        for (int a = 1; a < 8; ++a) ss += s_part[(warp * 8 + a) * 32 + lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) s_inv[warp] = rsqrtf(ss / static_cast<float>(K) + p.eps);
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+    }
+    // stage f(X) as bf16 pairs: (k, k + 1) of row m in the 32-bit word (k / 2) * 8 + m. Only the M live rows are
+    // written (lanes of the other rows feed zeros to the MMA below); k past the split's range is zero, since a
+    // weight row past K is zero too and 0 * x must not meet garbage
+    uint32_t* xs_w = reinterpret_cast<uint32_t*>(xs);
+    const int n_pairs = ntiles * GEMV_KT / 2;
+    for (int i = threadIdx.x; i < n_pairs * M; i += 256) {
+      const int kp = i / M, m = i - kp * M;
+      float xv[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int k = k0 + kp * 2 + e;
+        float v = 0.f;
+        if (k < k1) {
+          v = __bfloat162float(p.X[static_cast<size_t>(m) * p.ldx + k]);
+          if (p.prologue == PRO_RMSNORM) {
+            v = v * s_inv[m] * __bfloat162float(p.norm_w[k]);
+          } else if (p.prologue == PRO_SWIGLU) {
+            const float u = __bfloat162float(p.X[static_cast<size_t>(m) * p.ldx + K + k]);
+            v = v / (1.f + __expf(-v)) * u;
+          }
+        }
+        xv[e] = v;
+      }
+      xs_w[kp * 8 + m] = dpack(xv[0], xv[1]);
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+
+    const uint32_t* xs32 = reinterpret_cast<const uint32_t*>(xs);
+    // ldmatrix lane address: matrix mi = lane / 8 -> (k group = mi / 2, n half = mi % 2), row lane % 8
+    const int mi = lane >> 3, lr = lane & 7;
+    const int sub = warp >> 1;                          // which 64-column box holds this warp's columns
+    const uint32_t tiles_u32 = smem_u32(tiles) + sub * (GEMV_KT * 128);
+    for (int t = 0; t < ntiles; ++t) {
+      const int s = t % GEMV_STAGES;
+      if (!mbar_wait(&full[s], (t / GEMV_STAGES) & 1, p.status, ST_TIMEOUT_FULL)) break;
+      const uint32_t tbase = tiles_u32 + s * GEMV_TILE_BYTES;
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) {
+        const int kp = (t * GEMV_KT + ks * 16) >> 1;      // index of the first bf16 pair of this k-step
+        const uint32_t b0 = g < M ? xs32[(kp + tq) * 8 + g] : 0u;
+        const uint32_t b1 = g < M ? xs32[(kp + 4 + tq) * 8 + g] : 0u;
+        const int r = ks * 16 + (mi >> 1) * 8 + lr;       // k row inside the tile
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+          const int chunk = (warp & 1) * 4 + nb * 2 + (mi & 1);   // 16-byte chunk of the 128-byte row
+          uint32_t a[4];
+          gemv_ldsm_x4_t(tbase + r * 128 + ((chunk ^ (r & 7)) << 4), a);
+          gemv_mma_16816(acc[nb], a, b0, b1);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+    }
+  }
+  __syncthreads();
+  pdl_trigger();
+  const bool direct = gridDim.y == 1;
+  if (warp < 8) {
+    // accumulator (nb, j): column col0 + 32 warp + 16 nb + g + 8 (j / 2), row 2 tq + (j & 1)
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int gc = col0 + warp * 32 + nb * 16 + g + (j >> 1) * 8;
+        const int m = tq * 2 + (j & 1);
+        if (m < M && gc < N) {
+          float sum = acc[nb][j];
+          if (direct) {
+            if (p.R) sum += __bfloat162float(p.R[static_cast<size_t>(m) * p.ldr + gc]);
+            if (p.out) p.out[static_cast<size_t>(m) * p.ldo + gc] = __float2bfloat16_rn(sum);
+            if (p.out_f32) p.out_f32[static_cast<size_t>(m) * N + gc] = sum;
+          } else {
+            p.part[(static_cast<size_t>(blockIdx.y) * M + m) * N + gc] = sum;
+          }
+        }
+      }
+    }
+  }
+  if (direct) return;
+  // split-K finish by the last CTA of this column block
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(p.counters + blockIdx.x, 1u);
+    s_last = (prev == gridDim.y - 1) ? 1 : 0;
+    if (s_last) p.counters[blockIdx.x] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const int ncols = min(COLS, N - col0);
+  for (int i = threadIdx.x; i < M * ncols; i += GEMV_THREADS) {
+    const int m = i / ncols, gc = col0 + (i - m * ncols);
+    float sum = 0.f;
+    const float* pp = p.part + static_cast<size_t>(m) * N + gc;
+    const size_t pstride = static_cast<size_t>(M) * N;
+    const int ns = static_cast<int>(gridDim.y);
+    for (int k = 0; k < ns; k += 8) {   // eight loads in flight, added in split order
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = (k + u < ns) ? __ldcg(pp + (k + u) * pstride) : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) if (k + u < ns) sum += v[u];
+    }
     if (p.R) sum += __bfloat162float(p.R[static_cast<size_t>(m) * p.ldr + gc]);
     if (p.out) p.out[static_cast<size_t>(m) * p.ldo + gc] = __float2bfloat16_rn(sum);
     if (p.out_f32) p.out_f32[static_cast<size_t>(m) * N + gc] = sum;
@@ -790,6 +994,32 @@ static int launch_gemv(const GemvParams& p, int splits, cudaStream_t s) {
   }
 }
 
+namespace sb {
+int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_outer);   // gemm_tcgen05.cu (128-byte swizzle)
+}
+
+// bf16 weights: the tensor-core kernel. The staged slice of X takes 16 bytes per k (8 rows of bf16).
+static int launch_gemv_mma(const GemvParams& p, int splits, cudaStream_t s) {
+  dim3 grid((p.N + 255) / 256, splits);
+  const int kn_pad = (p.k_per_split + GEMV_KT - 1) / GEMV_KT * GEMV_KT;
+  const size_t xs_bytes = static_cast<size_t>(kn_pad) * 16;
+  if (xs_bytes > static_cast<size_t>(GEMV_MAX_XS_BYTES)) return SB_ERR_ARG;
+  // the RMSNorm prologue borrows the X staging area for 8 * 8 * 32 partial sums; 1 KB for the ring's alignment
+  const size_t smem = static_cast<size_t>(GEMV_STAGES) * GEMV_TILE_BYTES + (xs_bytes > 8192 ? xs_bytes : 8192) + 1024;
+  CUtensorMap tm;
+  const int rc = make_tmap_2d_bf16(&tm, p.W, static_cast<uint64_t>(p.N), p.K, static_cast<uint64_t>(p.ldw), 64, GEMV_KT);
+  if (rc) return rc;
+  auto kern = gemv_mma_kernel;
+  static size_t attr = 0;
+  if (smem > attr) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+      return SB_ERR_LAUNCH;
+    attr = smem;
+  }
+  return launch_dep(kern, grid, dim3(GEMV_THREADS), smem, s, tm, p) == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+}
+
 // Y[M,N] = f(X)[M,K] * W[K,N] (* scale[n]) (+ R). M <= 8 per call (callers loop over row groups).
 // W bf16 (is_int8 == 0) or int8 with fp32 column scales; the weight row pitch and base must be
 // multiples of 16 bytes. workspace: 4096 counter words (zero before the first call, left zero by
@@ -805,7 +1035,12 @@ extern "C" int sb_gemv(const void* X, int ldx, const void* W, int ldw, const flo
   const int esz = is_int8 ? 1 : 2;
   if ((reinterpret_cast<uintptr_t>(W) & 15) || ((static_cast<size_t>(ldw) * esz) & 15)) return SB_ERR_ALIGN;
   if (splits < 1) splits = 1;
-  int kps = ((K + splits - 1) / splits + 7) / 8 * 8;
+  // bf16 weights run on the tensor-core kernel (SB_GEMV_FMA=1 in the environment keeps them on the FMA kernel):
+  // its k ranges are whole 32-row tiles and its staged X takes 16 bytes per k, so at most 4096 k per split
+  static const bool bf16_fma = [] { const char* e = getenv("SB_GEMV_FMA"); return e && e[0] == '1'; }();
+  const bool mma = !is_int8 && !bf16_fma;
+  int kps = !mma ? ((K + splits - 1) / splits + 7) / 8 * 8 : ((K + splits - 1) / splits + 31) / 32 * 32;
+  if (mma && kps > 4096) kps = 4096;
   splits = (K + kps - 1) / kps;
   const int cols = is_int8 ? 512 : 256;
   if ((N + cols - 1) / cols > 4096) return SB_ERR_ARG;
@@ -817,7 +1052,7 @@ extern "C" int sb_gemv(const void* X, int ldx, const void* W, int ldw, const flo
   p.part = workspace + 4096;
   p.M = M; p.N = N; p.K = K; p.k_per_split = kps; p.prologue = prologue;
   p.norm_w = static_cast<const __nv_bfloat16*>(norm_w); p.eps = eps; p.status = status;
-  return is_int8 ? launch_gemv<true>(p, splits, STREAM) : launch_gemv<false>(p, splits, STREAM);
+  return is_int8 ? launch_gemv<true>(p, splits, STREAM) : mma ? launch_gemv_mma(p, splits, STREAM) : launch_gemv<false>(p, splits, STREAM);
 }
 
 extern "C" int sb_kv_append(const void* qkv, int ld, int H, int Hkv, int dh, void* pool, const int* block_table,

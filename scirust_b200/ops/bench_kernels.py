@@ -45,7 +45,10 @@ def _rand(shape, seed):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "gemm_model", "attention", "attention_bwd", "rmsnorm", "ce", "adamw", "umma"])
+    ap.add_argument("kernel", choices=["gemm", "gemm_model", "attention", "attention_bwd", "rmsnorm", "ce", "adamw", "umma", "gemv",
+                                      "decode_attn"])
+    ap.add_argument("--int8", action="store_true", help="gemv: per-channel int8 weights")
+    ap.add_argument("--ctx", type=int, default=4096, help="decode_attn: cached positions per sequence")
     ap.add_argument("--library", action="store_true", help="gemm_model: also time torch.matmul (cuBLAS)")
     ap.add_argument("--form", default="nt", choices=["nn", "nt", "tn"])
     ap.add_argument("--m", type=int, default=8192)
@@ -125,6 +128,27 @@ def main(argv=None):
                     rows.append({"m": M, "n": N, "k": 16, "b_major": "mn" if b_mn else "k",
                                  "cycles_per_mma": round(per, 1), "fma_per_cycle": round(M * N * 16 / per, 1)})
         out["rows"] = rows
+    elif a.kernel == "gemv":
+        # batch-1 decode product: W [K, N] streamed once (default 14336 x 4096 bf16 = 117 MB, larger than L2)
+        from . import decode
+        K, N, M = a.k, a.n, a.batch
+        w = _rand((K, N), 11)
+        x = _rand((M, K), 12)
+        wq = decode.quantize_per_channel(w) if a.int8 else w
+        ms = _time(lambda: decode.gemv(x, wq), a.iters, a.warmup, flush)
+        nbytes = K * N * (1 if a.int8 else 2)
+        out.update(m=M, k=K, n=N, int8=bool(a.int8), ms=ms, gbs=nbytes / ms / 1e6)
+    elif a.kernel == "decode_attn":
+        from . import decode
+        B, H, Hkv, dh, page, L = a.batch, a.heads, a.kv_heads, a.dh, 16, a.ctx
+        blocks = (L + page - 1) // page
+        pool = _rand((B * blocks, 2, Hkv, page, dh), 13)
+        table = torch.randperm(B * blocks, device="cuda").to(torch.int32).reshape(B, blocks)
+        lens = torch.full((B,), L, dtype=torch.int32, device="cuda")
+        q = _rand((B, H * dh), 14)
+        ms = _time(lambda: decode.decode_attention(q, pool, table, page, lens, H, Hkv, dh), a.iters, a.warmup, flush)
+        nbytes = B * L * 2 * Hkv * dh * 2
+        out.update(batch=B, heads=H, kv_heads=Hkv, dh=dh, ctx=L, ms=ms, gbs=nbytes / ms / 1e6)
     elif a.kernel in ("attention", "attention_bwd"):
         B, S, H, Hkv, dh = a.batch, a.seq, a.heads, a.kv_heads, a.dh
         qkv = _rand((B * S, (H + 2 * Hkv) * dh), 3)

@@ -113,13 +113,17 @@ def quantize_per_channel(w: torch.Tensor) -> QuantWeight:
     return QuantWeight(q, scale)
 
 
-def _auto_splits(N, K, cols, M=1):
-    """k-splits of the weight-streaming GEMV: about two CTAs per SM, and a staged slice of X
-    ((K / splits) rows x {1,2,4,8} floats) that fits the kernel's 64 KB."""
+def _auto_splits(N, K, cols, M=1, quant=False):
+    """k-splits of the weight-streaming GEMV: about two CTAs per SM, and a staged slice of X that fits the
+    kernel's 64 KB: (K / splits) rows x {1,2,4,8} floats for int8 weights, 16 bytes per k (8 rows of bf16)
+    for the tensor-core kernel that bf16 weights use."""
     ctas = (N + cols - 1) // cols
     s = max(1, min(148 * 2 // max(ctas, 1), K // 64))
-    mb = 1 if M <= 1 else 2 if M <= 2 else 4 if M <= 4 else 8
-    lim = 65536 // (4 * mb) // 8 * 8          # rows of X per split
+    if quant:
+        mb = 1 if M <= 1 else 2 if M <= 2 else 4 if M <= 4 else 8
+        lim = 65536 // (4 * mb) // 8 * 8      # rows of X per split
+    else:
+        lim = 4096
     return max(s, (K + lim - 1) // lim)
 
 
@@ -153,7 +157,9 @@ def gemv(x, w, residual=None, out=None, out_f32=None, splits=None, rms_weight=No
     if out is None and out_f32 is None:
         out = torch.empty((M, N), dtype=BF, device=x.device)
     if splits is None:
-        splits = _auto_splits(N, K, 512 if quant else 256, min(M, 8))
+        splits = _auto_splits(N, K, 512 if quant else 256, min(M, 8), quant)
+    if not quant:
+        splits = max(splits, (K + 4095) // 4096)
     ws = _gemv_workspace(4096 + splits * min(M, 8) * N, x.device)
     st = _lib.status_word(x.device)
     for m0 in range(0, M, 8):
