@@ -147,13 +147,13 @@ gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
         s_part[(m * 8 + warp) * 32 + lane] = a;
       }
       asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (warp < M) {
-        float ss = s_part[(warp * 8) * 32 + lane];
+      for (int m = warp; m < M; m += 8) {
+        float ss = s_part[(m * 8) * 32 + lane];
 #pragma unroll
-        for (int a = 1; a < 8; ++a) ss += s_part[(warp * 8 + a) * 32 + lane];
+        for (int a = 1; a < 8; ++a) ss += s_part[(m * 8 + a) * 32 + lane];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) s_inv[warp] = rsqrtf(ss / static_cast<float>(K) + p.eps);
+        if (lane == 0) s_inv[m] = rsqrtf(ss / static_cast<float>(K) + p.eps);
       }
       asm volatile("bar.sync 1, 256;" ::: "memory");
     }
@@ -311,14 +311,16 @@ __device__ __forceinline__ void gemv_mma_16816(float (&c)[4], const uint32_t (&a
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+template <int MBLK>   // blocks of 8 activation rows: 1, 2 or 4 (M <= 8 * MBLK)
 __global__ void __launch_bounds__(GEMV_THREADS)
 gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ GemvParams p) {
   constexpr int COLS = 256;
+  constexpr int XR = 8 * MBLK;   // 32-bit words per k pair in the staged activations
   extern __shared__ __align__(1024) uint8_t smem_mma[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_mma) + 1023) & ~uintptr_t(1023));
-  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(tiles + GEMV_STAGES * GEMV_TILE_BYTES);  // [k/2][8][2]
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(tiles + GEMV_STAGES * GEMV_TILE_BYTES);  // [k/2][XR][2]
   __shared__ uint64_t full[GEMV_STAGES], empty[GEMV_STAGES];
-  __shared__ float s_inv[8];
+  __shared__ float s_inv[32];
   __shared__ int s_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int M = p.M, N = p.N, K = p.K;
@@ -334,7 +336,13 @@ gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   }
   __syncthreads();
 
-  float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+  float acc[2][MBLK][4];
+#pragma unroll
+  for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+    for (int mb = 0; mb < MBLK; ++mb)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[nb][mb][j] = 0.f;
   const int g = lane >> 2, tq = lane & 3;   // mma fragment coordinates of this lane
 
   if (warp == 8) {
@@ -405,7 +413,7 @@ gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         }
         xv[e] = v;
       }
-      xs_w[kp * 8 + m] = dpack(xv[0], xv[1]);
+      xs_w[kp * XR + m] = dpack(xv[0], xv[1]);
     }
     asm volatile("bar.sync 1, 256;" ::: "memory");
 
@@ -421,15 +429,21 @@ gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 #pragma unroll
       for (int ks = 0; ks < 2; ++ks) {
         const int kp = (t * GEMV_KT + ks * 16) >> 1;      // index of the first bf16 pair of this k-step
-        const uint32_t b0 = g < M ? xs32[(kp + tq) * 8 + g] : 0u;
-        const uint32_t b1 = g < M ? xs32[(kp + 4 + tq) * 8 + g] : 0u;
+        uint32_t b0[MBLK], b1[MBLK];
+#pragma unroll
+        for (int mb = 0; mb < MBLK; ++mb) {
+          const bool live = mb * 8 + g < M;
+          b0[mb] = live ? xs32[(kp + tq) * XR + mb * 8 + g] : 0u;
+          b1[mb] = live ? xs32[(kp + 4 + tq) * XR + mb * 8 + g] : 0u;
+        }
         const int r = ks * 16 + (mi >> 1) * 8 + lr;       // k row inside the tile
 #pragma unroll
         for (int nb = 0; nb < 2; ++nb) {
           const int chunk = (warp & 1) * 4 + nb * 2 + (mi & 1);   // 16-byte chunk of the 128-byte row
           uint32_t a[4];
           gemv_ldsm_x4_t(tbase + r * 128 + ((chunk ^ (r & 7)) << 4), a);
-          gemv_mma_16816(acc[nb], a, b0, b1);
+#pragma unroll
+          for (int mb = 0; mb < MBLK; ++mb) gemv_mma_16816(acc[nb][mb], a, b0[mb], b1[mb]);
         }
       }
       __syncwarp();
@@ -440,21 +454,24 @@ gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   pdl_trigger();
   const bool direct = gridDim.y == 1;
   if (warp < 8) {
-    // accumulator (nb, j): column col0 + 32 warp + 16 nb + g + 8 (j / 2), row 2 tq + (j & 1)
+    // accumulator (nb, mb, j): column col0 + 32 warp + 16 nb + g + 8 (j / 2), row 8 mb + 2 tq + (j & 1)
 #pragma unroll
     for (int nb = 0; nb < 2; ++nb) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int gc = col0 + warp * 32 + nb * 16 + g + (j >> 1) * 8;
-        const int m = tq * 2 + (j & 1);
-        if (m < M && gc < N) {
-          float sum = acc[nb][j];
-          if (direct) {
-            if (p.R) sum += __bfloat162float(p.R[static_cast<size_t>(m) * p.ldr + gc]);
-            if (p.out) p.out[static_cast<size_t>(m) * p.ldo + gc] = __float2bfloat16_rn(sum);
-            if (p.out_f32) p.out_f32[static_cast<size_t>(m) * N + gc] = sum;
-          } else {
-            p.part[(static_cast<size_t>(blockIdx.y) * M + m) * N + gc] = sum;
+      for (int mb = 0; mb < MBLK; ++mb) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int gc = col0 + warp * 32 + nb * 16 + g + (j >> 1) * 8;
+          const int m = mb * 8 + tq * 2 + (j & 1);
+          if (m < M && gc < N) {
+            float sum = acc[nb][mb][j];
+            if (direct) {
+              if (p.R) sum += __bfloat162float(p.R[static_cast<size_t>(m) * p.ldr + gc]);
+              if (p.out) p.out[static_cast<size_t>(m) * p.ldo + gc] = __float2bfloat16_rn(sum);
+              if (p.out_f32) p.out_f32[static_cast<size_t>(m) * N + gc] = sum;
+            } else {
+              p.part[(static_cast<size_t>(blockIdx.y) * M + m) * N + gc] = sum;
+            }
           }
         }
       }
@@ -999,18 +1016,20 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64
                       uint32_t box_inner, uint32_t box_outer);   // gemm_tcgen05.cu (128-byte swizzle)
 }
 
-// bf16 weights: the tensor-core kernel. The staged slice of X takes 16 bytes per k (8 rows of bf16).
-static int launch_gemv_mma(const GemvParams& p, int splits, cudaStream_t s) {
+// bf16 weights: the tensor-core kernel. The staged slice of X takes 16 bytes per k for every 8 rows.
+template <int MBLK>
+static int launch_gemv_mma_mb(const GemvParams& p, int splits, cudaStream_t s) {
   dim3 grid((p.N + 255) / 256, splits);
   const int kn_pad = (p.k_per_split + GEMV_KT - 1) / GEMV_KT * GEMV_KT;
-  const size_t xs_bytes = static_cast<size_t>(kn_pad) * 16;
+  const size_t xs_bytes = static_cast<size_t>(kn_pad) * 16 * MBLK;
   if (xs_bytes > static_cast<size_t>(GEMV_MAX_XS_BYTES)) return SB_ERR_ARG;
-  // the RMSNorm prologue borrows the X staging area for 8 * 8 * 32 partial sums; 1 KB for the ring's alignment
-  const size_t smem = static_cast<size_t>(GEMV_STAGES) * GEMV_TILE_BYTES + (xs_bytes > 8192 ? xs_bytes : 8192) + 1024;
+  // the RMSNorm prologue borrows the X staging area for M * 8 * 32 partial sums; 1 KB for the ring's alignment
+  const size_t borrow = static_cast<size_t>(8 * MBLK) * 1024;
+  const size_t smem = static_cast<size_t>(GEMV_STAGES) * GEMV_TILE_BYTES + (xs_bytes > borrow ? xs_bytes : borrow) + 1024;
   CUtensorMap tm;
   const int rc = make_tmap_2d_bf16(&tm, p.W, static_cast<uint64_t>(p.N), p.K, static_cast<uint64_t>(p.ldw), 64, GEMV_KT);
   if (rc) return rc;
-  auto kern = gemv_mma_kernel;
+  auto kern = gemv_mma_kernel<MBLK>;
   static size_t attr = 0;
   if (smem > attr) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
@@ -1018,6 +1037,11 @@ static int launch_gemv_mma(const GemvParams& p, int splits, cudaStream_t s) {
     attr = smem;
   }
   return launch_dep(kern, grid, dim3(GEMV_THREADS), smem, s, tm, p) == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+}
+// Only one block of 8 rows is shipped: with two or four blocks the kernel is bound by the mma.sync rate, not by
+// memory (117 MB of weights: 33 us at 8 rows, 58 us at 16, 111 us at 32), and the tcgen05 GEMM is faster there.
+static int launch_gemv_mma(const GemvParams& p, int splits, cudaStream_t s) {
+  return launch_gemv_mma_mb<1>(p, splits, s);
 }
 
 // Y[M,N] = f(X)[M,K] * W[K,N] (* scale[n]) (+ R). M <= 8 per call (callers loop over row groups).

@@ -142,7 +142,7 @@ class InferenceEngine:
     def _proj_out(self, a, w, x, swiglu=False, site="attn"):
         """x + f(a) @ w: the attention-output and MLP-down products (row-parallel under tensor
         parallelism, where a subclass adds the all-reduce). ``swiglu``: a is a fused [gate | up]."""
-        if a.shape[0] <= 8:
+        if a.shape[0] <= D.gemv_max_rows(w):
             return D.gemv(a, w, residual=x, swiglu=swiglu)
         if swiglu:
             a = ops.swiglu_fwd(a)
@@ -150,7 +150,7 @@ class InferenceEngine:
 
     def _linear(self, x, w, residual=None):
         M = x.shape[0]
-        if M <= 8:
+        if M <= D.gemv_max_rows(w):
             return D.gemv(x, w, residual=residual)
         if isinstance(w, D.QuantWeight):
             # few rows: the product is bound by the weight bytes, so the int8 matrix is streamed and
@@ -202,7 +202,7 @@ class InferenceEngine:
 
     def _head_local(self, hn, logits, rms_weight=None):
         M = hn.shape[0]
-        if M <= 8:
+        if M <= D.gemv_max_rows(self.head_t):
             D.gemv(hn, self.head_t, out_f32=logits, rms_weight=rms_weight, eps=self.cfg.eps)
             return
         if rms_weight is not None:
@@ -219,7 +219,8 @@ class InferenceEngine:
         seq_of = self._seq_of[:B]
         pos = cache.seq_len[:B]
         x = ops.embed_fwd(self.embed, self.tokens[:B])
-        small = B <= 8      # weight-streaming path: norms and SwiGLU are fused into the GEMV loads
+        # weight-streaming path: norms and SwiGLU are fused into the GEMV loads
+        small = B <= D.gemv_max_rows(self.layers[0]["wqkv"])
         for li, l in enumerate(self.layers):
             if small:
                 qkv = D.gemv(x, l["wqkv"], rms_weight=l["rms1"], eps=cfg.eps)

@@ -106,7 +106,7 @@ class TPInferenceEngine(InferenceEngine):
         coll = self.coll
         if self.backend != "fused" or M * d * 2 * self.world <= SMALL_BYTES:
             full = coll.source(site, (self._small_rows, d), torch.float32, device=x.device)
-            if M <= 8:
+            if M <= D.gemv_max_rows(w):
                 src = full[:M]
                 D.gemv(a, w, out_f32=src, swiglu=swiglu)
             else:

@@ -113,6 +113,12 @@ def quantize_per_channel(w: torch.Tensor) -> QuantWeight:
     return QuantWeight(q, scale)
 
 
+def gemv_max_rows(w) -> int:
+    """Rows up to which the weight-streaming kernels beat the tcgen05 GEMM (one block of 8 MMA columns; with 16
+    or 32 rows the tensor-core GEMV is bound by the mma.sync rate: 58 and 111 us against 33 us for 117 MB)."""
+    return 8
+
+
 def _auto_splits(N, K, cols, M=1, quant=False):
     """k-splits of the weight-streaming GEMV: about two CTAs per SM, and a staged slice of X that fits the
     kernel's 64 KB: (K / splits) rows x {1,2,4,8} floats for int8 weights, 16 bytes per k (8 rows of bf16)
@@ -156,14 +162,15 @@ def gemv(x, w, residual=None, out=None, out_f32=None, splits=None, rms_weight=No
         return y.to(BF) if out_f32 is None else out_f32
     if out is None and out_f32 is None:
         out = torch.empty((M, N), dtype=BF, device=x.device)
+    grp = 8                                   # rows per call
     if splits is None:
-        splits = _auto_splits(N, K, 512 if quant else 256, min(M, 8), quant)
+        splits = _auto_splits(N, K, 512 if quant else 256, min(M, grp), quant)
     if not quant:
         splits = max(splits, (K + 4095) // 4096)
-    ws = _gemv_workspace(4096 + splits * min(M, 8) * N, x.device)
+    ws = _gemv_workspace(4096 + splits * min(M, grp) * N, x.device)
     st = _lib.status_word(x.device)
-    for m0 in range(0, M, 8):
-        mb = min(8, M - m0)
+    for m0 in range(0, M, grp):
+        mb = min(grp, M - m0)
         xs = x[m0:m0 + mb]
         _lib.call("sb_gemv", xs.data_ptr(), xs.stride(0), wm.data_ptr(), wm.stride(0),
                   w.scale.data_ptr() if quant else None,

@@ -16,7 +16,8 @@ def _r(shape, seed, scale=0.5):
 
 
 @pytest.mark.parametrize("M,K,N", [(1, 1024, 1536), (3, 4096, 512), (8, 2816, 1024), (13, 1024, 264),
-                                   (8, 14336, 520), (2, 40, 8), (1, 4096, 6144)])
+                                   (8, 14336, 520), (2, 40, 8), (1, 4096, 6144), (16, 4096, 1024), (27, 2816, 520),
+                                   (32, 14336, 256), (45, 1024, 512)])
 def test_gemv_bf16(M, K, N):
     x, w, r = _r((M, K), 1), _r((K, N), 2), _r((M, N), 3)
     y = D.gemv(x, w, residual=r)
