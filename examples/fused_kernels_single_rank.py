@@ -5,6 +5,7 @@ rank every "peer" pointer is the local buffer: the instruction stream, tile loop
 epilogues are the ones the multi-rank runs execute, only the NVLink hops are local.
 
     python examples/fused_kernels_single_rank.py --iters 3
+    SB_TP_PAIR_SINGLE=1 python examples/fused_kernels_single_rank.py --iters 3    # the CTA-pair kernels
 """
 import argparse
 import os
@@ -60,10 +61,13 @@ def main():
     for _ in range(a.iters):
         ar.reduce(0, n, 1.0, ar.next_epoch())
         coll.all_reduce(small, residual=res)
-        ctx.ag_matmul_nn(x, w1)
-        ctx.matmul_nn_rs(h, w2)
+        y1 = ctx.ag_matmul_nn(x, w1)
+        y2 = ctx.matmul_nn_rs(h, w2)
     torch.cuda.synchronize()
     _lib.check_status(dev)
+    for got, ref in ((y1, x.float() @ w1.float()), (y2, h.float() @ w2.float())):
+        err = (got.float() - ref).abs().max().item()
+        assert err <= 2e-2 * max(1.0, ref.abs().max().item()), err
     ctx.close()
     region.close()
     dist.destroy_process_group()

@@ -163,8 +163,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     n_idx = within / gm;
     m2 = first + (within - n_idx * gm);
   };
-  const bool ag = p.ag.W > 1;
-  const bool rs = p.rs.W > 1;
+  const bool ag = p.ag.W >= 1;   // a one-rank group runs the same protocol with itself as the only peer
+  const bool rs = p.rs.W >= 1;
   const int m_rot = ag ? p.ag.rank * (mt2 / p.ag.W)        // walk the local shard's row tiles first
                        : (rs ? p.rs.rank * (mt2 / p.rs.W) : 0);
 
@@ -738,7 +738,7 @@ extern "C" int sb_gemm_pair_ag_bf16(void* const* a_ptrs, const void* B, void* C,
                                     void* stream_) {
   using namespace sb::pair;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (M <= 0 || N <= 0 || K <= 0 || W < 2 || W > MAXW || rank < 0 || rank >= W) return SB_ERR_ARG;
+  if (M <= 0 || N <= 0 || K <= 0 || W < 1 || W > MAXW || rank < 0 || rank >= W) return SB_ERR_ARG;
   if ((N & 7) || (K & 7) || (lda & 7) || (ld_stage & 7) || (ldc & 7) || (R && (ldr & 7)) || (M % (W * 2 * BM)))
     return SB_ERR_ARG;
   if ((reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(a_stage) & 15)) return SB_ERR_ALIGN;
@@ -790,7 +790,7 @@ extern "C" int sb_gemm_pair_rs_bf16(const void* A, const void* B, void* const* p
                                     void* stream_) {
   using namespace sb::pair;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (M <= 0 || N <= 0 || K <= 0 || W < 2 || W > MAXW || rank < 0 || rank >= W) return SB_ERR_ARG;
+  if (M <= 0 || N <= 0 || K <= 0 || W < 1 || W > MAXW || rank < 0 || rank >= W) return SB_ERR_ARG;
   if ((N & 7) || (ldp & 7) || (ld_out & 7) || (res && (ld_res & 7)) || (M % (W * 2 * BM))) return SB_ERR_ARG;
   void* C = part_ptrs[rank];
   if ((reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return SB_ERR_ALIGN;

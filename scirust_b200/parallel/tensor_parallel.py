@@ -61,6 +61,9 @@ class TPContext:
         self.epoch = 0
         self.rs_calls = 0
         self.pair = os.environ.get("SB_TP_PAIR", "1") != "0"   # CTA-pair kernel for all-gather -> GEMM
+        # a one-rank group normally takes the plain GEMM; SB_TP_PAIR_SINGLE=1 sends it through the fused CTA-pair
+        # kernels (every "peer" is the local buffer) so that a profiler can capture them on one GPU
+        self._pair_min_world = 1 if os.environ.get("SB_TP_PAIR_SINGLE", "0") == "1" else 2
         self._named = {}
         if backend == "fused":
             stage_bytes = max_rows * max_cols * 2          # W * (rows/W) * cols bf16
@@ -135,11 +138,11 @@ class TPContext:
         return out
 
     def _rs_pair_ok(self, M, N):
-        return (self.pair and self.world > 1 and M % (self.world * 256) == 0 and N % 8 == 0
+        return (self.pair and self.world >= self._pair_min_world and M % (self.world * 256) == 0 and N % 8 == 0
                 and self.world * (M // self.world // 256) <= 8 * 512 and M // 256 + 2 <= self._rs_ctr.numel())
 
     def _pair_ok(self, M, K):
-        return (self.pair and self.world > 1 and M % (self.world * 256) == 0 and K % 8 == 0
+        return (self.pair and self.world >= self._pair_min_world and M % (self.world * 256) == 0 and K % 8 == 0
                 and M // 128 + 2 <= self._ag_flags.numel() // 2)
 
     def _call(self, a, b, out, residual, M, N, K, a_mn, b_mn, a_gather, b_gather, scatter, bn=0):
