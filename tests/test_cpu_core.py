@@ -19,7 +19,9 @@ from scirust_b200.numerics import lowprec as L
 from scirust_b200.numerics import portable as P
 from scirust_b200.numerics import reproducible as R
 
-REF = "/root/reference"
+# golden files of the reference implementation: a checkout beside this repository, or SCIRUST_REFERENCE_DIR
+REF = os.environ.get("SCIRUST_REFERENCE_DIR") or os.path.normpath(
+    os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "reference"))
 need_ref = pytest.mark.skipif(not os.path.isdir(REF), reason="reference tree not mounted")
 
 

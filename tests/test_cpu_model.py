@@ -11,7 +11,9 @@ from scirust_b200.models import GQADecoder, SciAgentConfig
 from scirust_b200.models.infer import InferenceEngine, reference_generate
 from scirust_b200.train import Trainer, TrainerConfig, WarmupCosineSchedule
 
-REF = "/root/reference"
+# golden files of the reference implementation: a checkout beside this repository, or SCIRUST_REFERENCE_DIR
+REF = os.environ.get("SCIRUST_REFERENCE_DIR") or os.path.normpath(
+    os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "reference"))
 CFG = SciAgentConfig(256, 64, 2, 4, 2, 128, 128, 10000.0)
 
 
