@@ -112,38 +112,70 @@ allreduce_bf16_kernel(const __grid_constant__ AllReduceParams p) {
     const size_t lo = min(p.n, per * p.rank);
     const size_t hi = min(p.n, lo + per);
     const size_t n8 = (hi - lo) / 8;
-    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-      const size_t e = lo + i * 8;
-      float acc[8];
+    // two 16-byte vectors per thread and iteration: 2 W peer loads are in flight before the first add, which is
+    // what hides the NVLink round trip with a few dozen CTAs; each vector is summed in rank order
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i0 = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < n8; i0 += 2 * stride) {
+      const size_t i1 = i0 + stride;
+      const bool two = i1 < n8;
+      const size_t e0 = lo + i0 * 8, e1 = lo + (two ? i1 : i0) * 8;
+      float accs[2][8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-      for (int r = 0; r < W; ++r) {  // fixed rank order
-        const uint4 v = ld_peer_v4(static_cast<const __nv_bfloat16*>(p.t.in[r]) + e);
-        acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x);
-        acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
-        acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z);
-        acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) accs[u][j] = 0.f;
+      for (int r0 = 0; r0 < W; r0 += 8) {     // ranks in groups of eight: loads first, then the adds in rank order
+        uint4 v0[8], v1[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          if (r0 + r < W) {
+            v0[r] = ld_peer_v4(static_cast<const __nv_bfloat16*>(p.t.in[r0 + r]) + e0);
+            if (two) v1[r] = ld_peer_v4(static_cast<const __nv_bfloat16*>(p.t.in[r0 + r]) + e1);
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          if (r0 + r < W) {
+            accs[0][0] += bf16_lo(v0[r].x); accs[0][1] += bf16_hi(v0[r].x);
+            accs[0][2] += bf16_lo(v0[r].y); accs[0][3] += bf16_hi(v0[r].y);
+            accs[0][4] += bf16_lo(v0[r].z); accs[0][5] += bf16_hi(v0[r].z);
+            accs[0][6] += bf16_lo(v0[r].w); accs[0][7] += bf16_hi(v0[r].w);
+            if (two) {
+              accs[1][0] += bf16_lo(v1[r].x); accs[1][1] += bf16_hi(v1[r].x);
+              accs[1][2] += bf16_lo(v1[r].y); accs[1][3] += bf16_hi(v1[r].y);
+              accs[1][4] += bf16_lo(v1[r].z); accs[1][5] += bf16_hi(v1[r].z);
+              accs[1][6] += bf16_lo(v1[r].w); accs[1][7] += bf16_hi(v1[r].w);
+            }
+          }
+        }
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] *= p.scale;
-      if (p.out_fp32) {
-        const uint4 a = make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]),
-                                   __float_as_uint(acc[3]));
-        const uint4 b = make_uint4(__float_as_uint(acc[4]), __float_as_uint(acc[5]), __float_as_uint(acc[6]),
-                                   __float_as_uint(acc[7]));
-        for (int r = 0; r < W; ++r) {
-          const int dst = (p.rank + r) % W;  // spread the pushes over the peers
-          float* o = static_cast<float*>(p.t.out[dst]) + e;
-          *reinterpret_cast<uint4*>(o) = a;
-          *reinterpret_cast<uint4*>(o + 4) = b;
-        }
-      } else {
-        const uint4 o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
-                                   pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
-        for (int r = 0; r < W; ++r) {
-          const int dst = (p.rank + r) % W;
-          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.t.out[dst]) + e) = o;
+      for (int u = 0; u < 2; ++u) {
+        if (u == 1 && !two) break;
+        const size_t e = u == 0 ? e0 : e1;
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = accs[u][j];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] *= p.scale;
+        if (p.out_fp32) {
+          const uint4 a = make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]),
+                                     __float_as_uint(acc[3]));
+          const uint4 b = make_uint4(__float_as_uint(acc[4]), __float_as_uint(acc[5]), __float_as_uint(acc[6]),
+                                     __float_as_uint(acc[7]));
+          for (int r = 0; r < W; ++r) {
+            const int dst = (p.rank + r) % W;  // spread the pushes over the peers
+            float* o = static_cast<float*>(p.t.out[dst]) + e;
+            *reinterpret_cast<uint4*>(o) = a;
+            *reinterpret_cast<uint4*>(o + 4) = b;
+          }
+        } else {
+          const uint4 o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                                     pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+          for (int r = 0; r < W; ++r) {
+            const int dst = (p.rank + r) % W;
+            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.t.out[dst]) + e) = o;
+          }
         }
       }
     }

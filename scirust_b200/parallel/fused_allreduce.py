@@ -9,6 +9,8 @@ receives identical bits.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -70,6 +72,8 @@ class FusedGradAllReduce:
     (embedding, norm gains) and joins the streams."""
 
     def __init__(self, model, group, overlap: bool = True, n_ctas: int = 24, out_dtype=torch.bfloat16):
+        n_ctas = int(os.environ.get("SB_AR_CTAS", n_ctas))       # CTAs of one bucket's all-reduce kernel
+        overlap = overlap and os.environ.get("SB_AR_OVERLAP", "1") != "0"
         self.model = model
         self.world = dist.get_world_size(group)
         n = model.flat_grad.numel()
