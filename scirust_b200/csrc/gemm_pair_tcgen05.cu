@@ -31,6 +31,7 @@ constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 448;        // warp 0 TMA, 1 MMA, 2-9 epilogue, 10-13 all-gather copiers (idle otherwise)
 constexpr int COPY_WARPS = 4;
+constexpr int CP_UNROLL = 8;   // 16-byte peer loads in flight per copier thread
 constexpr int GROUP_M = 8;           // row tiles (of 256 rows) per raster group
 constexpr int MAXW = 8;
 constexpr int FLAG_STRIDE = 16;     // flag words per phase in a call site's slot (as in gemm_dist_tcgen05.cu)
@@ -307,11 +308,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const uint4* peer = static_cast<const uint4*>(p.ag.a_peer[src]);
         const int chunk = src * cpr + ci;
         const size_t prow0 = static_cast<size_t>(ci) * BM, srow0 = static_cast<size_t>(chunk) * BM;
-        for (size_t v0 = lo + (cw * 32 + lane); v0 < hi; v0 += COPY_WARPS * 32 * 4) {
-          uint4 tmp[4];
-          size_t idx[4];
+        for (size_t v0 = lo + (cw * 32 + lane); v0 < hi; v0 += COPY_WARPS * 32 * CP_UNROLL) {
+          uint4 tmp[CP_UNROLL];
+          size_t idx[CP_UNROLL];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
+          for (int u = 0; u < CP_UNROLL; ++u) {
             idx[u] = v0 + static_cast<size_t>(u) * COPY_WARPS * 32;
             if (idx[u] < hi) {
               const size_t r = idx[u] / vec_per_row, c = idx[u] - r * vec_per_row;
@@ -321,7 +322,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
+          for (int u = 0; u < CP_UNROLL; ++u) {
             if (idx[u] < hi) {
               const size_t r = idx[u] / vec_per_row, c = idx[u] - r * vec_per_row;
               *(static_cast<uint4*>(p.ag.a_stage) + ((srow0 + r) * p.ag.ld_stage) / 8 + c) = tmp[u];
