@@ -46,7 +46,7 @@ def _rand(shape, seed):
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["gemm", "gemm_model", "attention", "attention_bwd", "rmsnorm", "ce", "adamw", "umma", "gemv",
-                                      "decode_attn"])
+                                      "decode_attn", "sampler"])
     ap.add_argument("--int8", action="store_true", help="gemv: per-channel int8 weights")
     ap.add_argument("--ctx", type=int, default=4096, help="decode_attn: cached positions per sequence")
     ap.add_argument("--library", action="store_true", help="gemm_model: also time torch.matmul (cuBLAS)")
@@ -138,6 +138,15 @@ def main(argv=None):
         ms = _time(lambda: decode.gemv(x, wq), a.iters, a.warmup, flush)
         nbytes = K * N * (1 if a.int8 else 2)
         out.update(m=M, k=K, n=N, int8=bool(a.int8), ms=ms, gbs=nbytes / ms / 1e6)
+    elif a.kernel == "sampler":
+        # top-k / top-p / temperature sampling of `batch` rows of `cols` fp32 logits (default: a 128256-word vocabulary)
+        from ..generate import SamplingParams
+        from .sampling import DeviceSampler
+        rows, V = a.batch, a.cols if a.cols > 4096 else 128256
+        logits = torch.randn((rows, V), device="cuda", generator=torch.Generator(device="cuda").manual_seed(15)) * 3
+        sp = DeviceSampler(SamplingParams(temperature=0.8, top_k=50, top_p=0.95), rows, V, list(range(1, rows + 1)), "cuda")
+        ms = _time(lambda: sp.sample(logits), a.iters, a.warmup, flush)
+        out.update(rows=rows, vocab=V, ms=ms, gbs=rows * V * 4 / ms / 1e6)
     elif a.kernel == "decode_attn":
         from . import decode
         B, H, Hkv, dh, page, L = a.batch, a.heads, a.kv_heads, a.dh, 16, a.ctx
