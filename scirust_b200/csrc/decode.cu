@@ -13,6 +13,7 @@
 #include <math.h>
 #include <stdint.h>
 #include "api.h"
+#include <cuda_fp16.h>
 #include <cstdlib>
 #include "sm100_ptx.cuh"
 
@@ -503,6 +504,235 @@ gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 #pragma unroll
       for (int u = 0; u < 8; ++u) if (k + u < ns) sum += v[u];
     }
+    if (p.R) sum += __bfloat162float(p.R[static_cast<size_t>(m) * p.ldr + gc]);
+    if (p.out) p.out[static_cast<size_t>(m) * p.ldo + gc] = __float2bfloat16_rn(sum);
+    if (p.out_f32) p.out_f32[static_cast<size_t>(m) * N + gc] = sum;
+  }
+}
+
+// int8 weights on the same tensor-core path: the tile is streamed as 16-bit words (two int8 columns per word) in
+// 128-byte-swizzled boxes, the transposed ldmatrix hands every thread 2 x 2 (k, column) bytes, a byte permute and one
+// packed fp16 subtract turn them into exact fp16 values, and the MMA runs in fp16 with fp32 accumulation; the
+// activations are the bf16-rounded values carried as fp16. The column scales are applied after the sum.
+__device__ __forceinline__ void gemv_mma_16816_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(GEMV_THREADS)
+gemv_mma_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ GemvParams p) {
+  constexpr int COLS = 512;      // int8 columns per CTA: 512 bytes of every weight row
+  constexpr int MBLK = 1;
+  constexpr int XR = 8;          // 32-bit words (fp16 pairs) per k pair in the staged activations
+  extern __shared__ __align__(1024) uint8_t smem_mma[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_mma) + 1023) & ~uintptr_t(1023));
+  __half* xs = reinterpret_cast<__half*>(tiles + GEMV_STAGES * GEMV_TILE_BYTES);  // [k/2][XR][2] fp16
+  __shared__ uint64_t full[GEMV_STAGES], empty[GEMV_STAGES];
+  __shared__ float s_inv[32];
+  __shared__ int s_last;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int M = p.M, N = p.N, K = p.K;
+  const int col0 = blockIdx.x * COLS;
+  const int k0 = blockIdx.y * p.k_per_split;            // a multiple of 32
+  const int k1 = min(K, k0 + p.k_per_split);
+  const int ntiles = (k1 - k0 + GEMV_KT - 1) / GEMV_KT;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap_w);
+    for (int s = 0; s < GEMV_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 8); }
+    fence_barrier_init();
+  }
+  __syncthreads();
+
+  float acc[4][MBLK][4];
+#pragma unroll
+  for (int nb = 0; nb < 4; ++nb)
+#pragma unroll
+    for (int mb = 0; mb < MBLK; ++mb)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[nb][mb][j] = 0.f;
+  const int g = lane >> 2, tq = lane & 3;   // mma fragment coordinates of this lane
+
+  if (warp == 8) {
+    // ------------------------------ producer ------------------------------
+    for (int t = 0; t < ntiles; ++t) {
+      const int s = t % GEMV_STAGES;
+      if (t >= GEMV_STAGES && !mbar_wait(&empty[s], ((t / GEMV_STAGES) - 1) & 1, p.status, ST_TIMEOUT_EMPTY)) break;
+      if (lane == 0) {
+        // rows past K and columns past N arrive as zeros and still count towards the byte total
+        mbar_arrive_expect_tx(&full[s], GEMV_TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          tma_load_2d(tiles + s * GEMV_TILE_BYTES + c * (GEMV_KT * 128), &tmap_w, &full[s], col0 / 2 + c * 64,
+                      k0 + t * GEMV_KT);   // the map is over 16-bit words: 64 words = 128 int8 columns
+      }
+      __syncwarp();
+    }
+    pdl_wait();
+  } else {
+    // ------------------------------ consumers -----------------------------
+    pdl_wait();   // X, the residual and the workspace belong to the previous kernel until here
+    if (p.prologue == PRO_RMSNORM) {
+      // row statistic with the association of rmsnorm_fwd_kernel (see the FMA kernel)
+      float* s_part = reinterpret_cast<float*>(xs);   // [M][8 warps][32 lanes], overwritten by the staging below
+      for (int m = 0; m < M; ++m) {
+        const __nv_bfloat16* xr = p.X + static_cast<size_t>(m) * p.ldx;
+        float a = 0.f;
+        for (int c = lane * 8 + warp * 256; c < K; c += 8 * 256) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
+          const float f[8] = {dbflo(raw.x), dbfhi(raw.x), dbflo(raw.y), dbfhi(raw.y),
+                              dbflo(raw.z), dbfhi(raw.z), dbflo(raw.w), dbfhi(raw.w)};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a += f[j] * f[j];
+        }
+        s_part[(m * 8 + warp) * 32 + lane] = a;
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (warp < M) {
+        float ss = s_part[(warp * 8) * 32 + lane];
+#pragma unroll
+        for (int a = 1; a < 8; ++a) ss += s_part[(warp * 8 + a) * 32 + lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) s_inv[warp] = rsqrtf(ss / static_cast<float>(K) + p.eps);
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+    }
+    // stage f(X) as fp16 pairs (of the bf16-rounded value, saturated to the fp16 range): (k, k + 1) of row m in the
+    // 32-bit word (k / 2) * 8 + m. Only the M live rows are
+    // written (lanes of the other rows feed zeros to the MMA below); k past the split's range is zero, since a
+    // weight row past K is zero too and 0 * x must not meet garbage
+    uint32_t* xs_w = reinterpret_cast<uint32_t*>(xs);
+    const int n_pairs = ntiles * GEMV_KT / 2;
+    for (int i = threadIdx.x; i < n_pairs * M; i += 256) {
+      const int kp = i / M, m = i - kp * M;
+      float xv[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int k = k0 + kp * 2 + e;
+        float v = 0.f;
+        if (k < k1) {
+          v = __bfloat162float(p.X[static_cast<size_t>(m) * p.ldx + k]);
+          if (p.prologue == PRO_RMSNORM) {
+            v = v * s_inv[m] * __bfloat162float(p.norm_w[k]);
+          } else if (p.prologue == PRO_SWIGLU) {
+            const float u = __bfloat162float(p.X[static_cast<size_t>(m) * p.ldx + K + k]);
+            v = v / (1.f + __expf(-v)) * u;
+          }
+        }
+        xv[e] = v;
+      }
+      {
+        const float c0 = fminf(fmaxf(__bfloat162float(__float2bfloat16_rn(xv[0])), -65504.f), 65504.f);
+        const float c1 = fminf(fmaxf(__bfloat162float(__float2bfloat16_rn(xv[1])), -65504.f), 65504.f);
+        const __half2 hp = __floats2half2_rn(c0, c1);
+        xs_w[kp * XR + m] = *reinterpret_cast<const uint32_t*>(&hp);
+      }
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+
+    const uint32_t* xs32 = reinterpret_cast<const uint32_t*>(xs);
+    // ldmatrix lane address: matrix mi = lane / 8 -> (n block of the pair = mi / 2, k group = mi % 2), row lane % 8.
+    // A 16-bit unit holds two int8 columns, so one transposed 8x8 matrix spans 16 columns x 8 k: the thread gets
+    // bytes {W[2tq][2g], W[2tq][2g+1], W[2tq+1][2g], W[2tq+1][2g+1]}; the even column feeds MMA row g, the odd one
+    // row g + 8 (the epilogue maps rows back to columns).
+    const int mi = lane >> 3, lr = lane & 7;
+    const int sub = warp >> 1;                          // which 128-column box holds this warp's 64 columns
+    const uint32_t tiles_u32 = smem_u32(tiles) + sub * (GEMV_KT * 128);
+    const __half2 bias = __floats2half2_rn(1152.f, 1152.f);   // 1024 (the magic exponent) + 128 (the sign flip)
+    for (int t = 0; t < ntiles; ++t) {
+      const int s = t % GEMV_STAGES;
+      if (!mbar_wait(&full[s], (t / GEMV_STAGES) & 1, p.status, ST_TIMEOUT_FULL)) break;
+      const uint32_t tbase = tiles_u32 + s * GEMV_TILE_BYTES;
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) {
+        const int kp = (t * GEMV_KT + ks * 16) >> 1;      // index of the first fp16 pair of this k-step
+        const bool live = g < M;
+        const uint32_t b0 = live ? xs32[(kp + tq) * XR + g] : 0u;
+        const uint32_t b1 = live ? xs32[(kp + 4 + tq) * XR + g] : 0u;
+        const int r = ks * 16 + (mi & 1) * 8 + lr;        // k row inside the tile
+#pragma unroll
+        for (int pr = 0; pr < 2; ++pr) {                  // two n blocks of 16 columns per ldmatrix.x4
+          const int chunk = (warp & 1) * 4 + pr * 2 + (mi >> 1);   // 16-byte chunk = 16 int8 columns
+          uint32_t raw[4];
+          gemv_ldsm_x4_t(tbase + r * 128 + ((chunk ^ (r & 7)) << 4), raw);
+#pragma unroll
+          for (int q2 = 0; q2 < 2; ++q2) {
+            // int8 -> fp16 without the conversion pipe: flip the sign bit (value + 128 as an unsigned byte), drop the
+            // byte into the mantissa of 1024.0 and subtract 1152
+            const uint32_t u_lo = raw[q2 * 2] ^ 0x80808080u, u_hi = raw[q2 * 2 + 1] ^ 0x80808080u;
+            uint32_t a[4];
+            a[0] = __byte_perm(u_lo, 0x64646464u, 0x4240);   // row g     (even column), k 0-7
+            a[1] = __byte_perm(u_lo, 0x64646464u, 0x4341);   // row g + 8 (odd column),  k 0-7
+            a[2] = __byte_perm(u_hi, 0x64646464u, 0x4240);   // k 8-15
+            a[3] = __byte_perm(u_hi, 0x64646464u, 0x4341);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __half2 h = *reinterpret_cast<__half2*>(&a[e]);
+              h = __hsub2(h, bias);
+              a[e] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            gemv_mma_16816_f16(acc[pr * 2 + q2][0], a, b0, b1);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+    }
+  }
+  __syncthreads();
+  pdl_trigger();
+  const bool direct = gridDim.y == 1;
+  if (warp < 8) {
+    // accumulator (nb, j): column col0 + 64 warp + 16 nb + 2 g + (j / 2), row 2 tq + (j & 1)
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int gc = col0 + warp * 64 + nb * 16 + 2 * g + (j >> 1);
+        const int m = tq * 2 + (j & 1);
+        if (m < M && gc < N) {
+          float sum = acc[nb][0][j];
+          if (direct) {
+            sum *= p.scale[gc];
+            if (p.R) sum += __bfloat162float(p.R[static_cast<size_t>(m) * p.ldr + gc]);
+            if (p.out) p.out[static_cast<size_t>(m) * p.ldo + gc] = __float2bfloat16_rn(sum);
+            if (p.out_f32) p.out_f32[static_cast<size_t>(m) * N + gc] = sum;
+          } else {
+            p.part[(static_cast<size_t>(blockIdx.y) * M + m) * N + gc] = sum;
+          }
+        }
+      }
+    }
+  }
+  if (direct) return;
+  // split-K finish by the last CTA of this column block
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(p.counters + blockIdx.x, 1u);
+    s_last = (prev == gridDim.y - 1) ? 1 : 0;
+    if (s_last) p.counters[blockIdx.x] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const int ncols = min(COLS, N - col0);
+  for (int i = threadIdx.x; i < M * ncols; i += GEMV_THREADS) {
+    const int m = i / ncols, gc = col0 + (i - m * ncols);
+    float sum = 0.f;
+    const float* pp = p.part + static_cast<size_t>(m) * N + gc;
+    const size_t pstride = static_cast<size_t>(M) * N;
+    const int ns = static_cast<int>(gridDim.y);
+    for (int k = 0; k < ns; k += 8) {   // eight loads in flight, added in split order
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = (k + u < ns) ? __ldcg(pp + (k + u) * pstride) : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) if (k + u < ns) sum += v[u];
+    }
+    sum *= p.scale[gc];
     if (p.R) sum += __bfloat162float(p.R[static_cast<size_t>(m) * p.ldr + gc]);
     if (p.out) p.out[static_cast<size_t>(m) * p.ldo + gc] = __float2bfloat16_rn(sum);
     if (p.out_f32) p.out_f32[static_cast<size_t>(m) * N + gc] = sum;
@@ -1038,6 +1268,27 @@ static int launch_gemv_mma_mb(const GemvParams& p, int splits, cudaStream_t s) {
   }
   return launch_dep(kern, grid, dim3(GEMV_THREADS), smem, s, tm, p) == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
+// int8 weights on the tensor-core kernel: the tensor map is over 16-bit words (two int8 columns each).
+static int launch_gemv_mma_i8(const GemvParams& p, int splits, cudaStream_t s) {
+  dim3 grid((p.N + 511) / 512, splits);
+  const int kn_pad = (p.k_per_split + GEMV_KT - 1) / GEMV_KT * GEMV_KT;
+  const size_t xs_bytes = static_cast<size_t>(kn_pad) * 16;
+  if (xs_bytes > static_cast<size_t>(GEMV_MAX_XS_BYTES)) return SB_ERR_ARG;
+  const size_t smem = static_cast<size_t>(GEMV_STAGES) * GEMV_TILE_BYTES + (xs_bytes > 8192 ? xs_bytes : 8192) + 1024;
+  if ((p.N & 1) || (p.ldw & 1)) return SB_ERR_ARG;
+  CUtensorMap tm;
+  const int rc = make_tmap_2d_bf16(&tm, p.W, static_cast<uint64_t>(p.N) / 2, p.K, static_cast<uint64_t>(p.ldw) / 2, 64, GEMV_KT);
+  if (rc) return rc;
+  auto kern = gemv_mma_i8_kernel;
+  static size_t attr = 0;
+  if (smem > attr) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+      return SB_ERR_LAUNCH;
+    attr = smem;
+  }
+  return launch_dep(kern, grid, dim3(GEMV_THREADS), smem, s, tm, p) == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+}
+
 // Only one block of 8 rows is shipped: with two or four blocks the kernel is bound by the mma.sync rate, not by
 // memory (117 MB of weights: 33 us at 8 rows, 58 us at 16, 111 us at 32), and the tcgen05 GEMM is faster there.
 static int launch_gemv_mma(const GemvParams& p, int splits, cudaStream_t s) {
@@ -1059,10 +1310,10 @@ extern "C" int sb_gemv(const void* X, int ldx, const void* W, int ldw, const flo
   const int esz = is_int8 ? 1 : 2;
   if ((reinterpret_cast<uintptr_t>(W) & 15) || ((static_cast<size_t>(ldw) * esz) & 15)) return SB_ERR_ALIGN;
   if (splits < 1) splits = 1;
-  // bf16 weights run on the tensor-core kernel (SB_GEMV_FMA=1 in the environment keeps them on the FMA kernel):
+  // the tensor-core kernels (SB_GEMV_FMA=1 in the environment selects the FMA kernels instead):
   // its k ranges are whole 32-row tiles and its staged X takes 16 bytes per k, so at most 4096 k per split
   static const bool bf16_fma = [] { const char* e = getenv("SB_GEMV_FMA"); return e && e[0] == '1'; }();
-  const bool mma = !is_int8 && !bf16_fma;
+  const bool mma = !bf16_fma;   // both weight types take the tensor-core kernels unless the FMA kernels are asked for
   int kps = !mma ? ((K + splits - 1) / splits + 7) / 8 * 8 : ((K + splits - 1) / splits + 31) / 32 * 32;
   if (mma && kps > 4096) kps = 4096;
   splits = (K + kps - 1) / kps;
@@ -1076,7 +1327,8 @@ extern "C" int sb_gemv(const void* X, int ldx, const void* W, int ldw, const flo
   p.part = workspace + 4096;
   p.M = M; p.N = N; p.K = K; p.k_per_split = kps; p.prologue = prologue;
   p.norm_w = static_cast<const __nv_bfloat16*>(norm_w); p.eps = eps; p.status = status;
-  return is_int8 ? launch_gemv<true>(p, splits, STREAM) : mma ? launch_gemv_mma(p, splits, STREAM) : launch_gemv<false>(p, splits, STREAM);
+  if (mma) return is_int8 ? launch_gemv_mma_i8(p, splits, STREAM) : launch_gemv_mma(p, splits, STREAM);
+  return is_int8 ? launch_gemv<true>(p, splits, STREAM) : launch_gemv<false>(p, splits, STREAM);
 }
 
 extern "C" int sb_kv_append(const void* qkv, int ld, int H, int Hkv, int dh, void* pool, const int* block_table,

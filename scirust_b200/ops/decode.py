@@ -121,19 +121,18 @@ def gemv_max_rows(w) -> int:
 
 def _auto_splits(N, K, cols, M=1, quant=False):
     """k-splits of the weight-streaming GEMV: about two CTAs per SM, and a staged slice of X that fits the
-    kernel's 64 KB: (K / splits) rows x {1,2,4,8} floats for int8 weights, 16 bytes per k (8 rows of bf16)
-    for the tensor-core kernel that bf16 weights use."""
+    kernel's 64 KB: 16 bytes per k (8 rows of 16-bit values) in the tensor-core kernels, (K / splits) rows x
+    {1,2,4,8} floats in the FMA kernels that SB_GEMV_FMA=1 selects."""
     ctas = (N + cols - 1) // cols
     s = max(1, min(148 * 2 // max(ctas, 1), K // 64))
     if ctas > 148 * 2 and not quant:
         # several waves of column blocks (an LM head): eight k-splits keep more CTAs streaming at once and shorten
         # the tail (4096 x 128256: 213 us with one split, 176 us with eight)
         s = max(1, min(8, K // 512))
-    if quant:
+    lim = 4096                                # 16 bytes of staged X per k in the tensor-core kernels
+    if os.environ.get("SB_GEMV_FMA") == "1":
         mb = 1 if M <= 1 else 2 if M <= 2 else 4 if M <= 4 else 8
-        lim = 65536 // (4 * mb) // 8 * 8      # rows of X per split
-    else:
-        lim = 4096
+        lim = min(lim, 65536 // (4 * mb) // 8 * 8)
     return max(s, (K + lim - 1) // lim)
 
 
@@ -169,8 +168,7 @@ def gemv(x, w, residual=None, out=None, out_f32=None, splits=None, rms_weight=No
     grp = 8                                   # rows per call
     if splits is None:
         splits = _auto_splits(N, K, 512 if quant else 256, min(M, grp), quant)
-    if not quant:
-        splits = max(splits, (K + 4095) // 4096)
+    splits = max(splits, (K + 4095) // 4096)
     ws = _gemv_workspace(4096 + splits * min(M, grp) * N, x.device)
     st = _lib.status_word(x.device)
     for m0 in range(0, M, grp):
