@@ -125,6 +125,54 @@ __global__ void rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, cons
   }
 }
 
+// The same for rows of NV * 256 columns (NV <= 8): dy and x of the row stay in registers, all loads are issued
+// before the first use, and the sums run in the order of the general kernel (same bits).
+template <int NV>
+__global__ void rmsnorm_bwd_dx_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                          const __nv_bfloat16* __restrict__ w, const float* __restrict__ inv_rms,
+                                          const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                                          int rows) {
+  constexpr int cols = NV * 256;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const size_t off = static_cast<size_t>(row) * cols;
+  uint4 va[NV], vb[NV], vg[NV], vd[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane * 8 + i * 256;
+    va[i] = *reinterpret_cast<const uint4*>(dy + off + c);
+    vb[i] = *reinterpret_cast<const uint4*>(x + off + c);
+    vg[i] = *reinterpret_cast<const uint4*>(w + c);
+    if (dres) vd[i] = *reinterpret_cast<const uint4*>(dres + off + c);
+  }
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    float a[8], b[8], g[8];
+    unpack8(va[i], a); unpack8(vb[i], b); unpack8(vg[i], g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dot += a[j] * g[j] * b[j];
+  }
+  dot = warp_sum(dot);
+  const float r = inv_rms[row];
+  const float k = r * r * dot / static_cast<float>(cols);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    float a[8], b[8], g[8], o[8];
+    unpack8(va[i], a); unpack8(vb[i], b); unpack8(vg[i], g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = r * (a[j] * g[j] - b[j] * k);
+    if (dres) {
+      float d[8];
+      unpack8(vd[i], d);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] += d[j];
+    }
+    *reinterpret_cast<uint4*>(dx + off + lane * 8 + i * 256) = pack8(o);
+  }
+}
+
 // RMSNorm gain gradient, stage 1: partial[ry][j] = sum over the rows of chunk ry of
 // dy*x*inv_rms, rows visited in ascending order by each warp, warps combined in warp
 // order. Stage 2 (colsum_finish_kernel) adds the chunks in chunk order.
@@ -139,13 +187,29 @@ __global__ void rmsnorm_bwd_dw_partial_kernel(const __nv_bfloat16* __restrict__ 
   const int r1 = min(rows, r0 + rows_per_chunk);
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (c < cols) {
-    for (int r = r0 + warp; r < r1; r += 8) {
-      float a[8], b[8];
-      unpack8(*reinterpret_cast<const uint4*>(dy + static_cast<size_t>(r) * cols + c), a);
-      unpack8(*reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * cols + c), b);
-      const float iv = inv_rms[r];
+    // four rows of this warp in flight; the adds keep the row order
+    for (int r = r0 + warp; r < r1; r += 32) {
+      uint4 va[4], vb[4];
+      float iv[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] += a[j] * b[j] * iv;
+      for (int u = 0; u < 4; ++u) {
+        const int rr = r + 8 * u;
+        if (rr < r1) {
+          va[u] = *reinterpret_cast<const uint4*>(dy + static_cast<size_t>(rr) * cols + c);
+          vb[u] = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(rr) * cols + c);
+          iv[u] = inv_rms[rr];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (r + 8 * u < r1) {
+          float a[8], b[8];
+          unpack8(va[u], a);
+          unpack8(vb[u], b);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += a[j] * b[j] * iv[u];
+        }
+      }
     }
   }
 #pragma unroll
@@ -645,10 +709,14 @@ extern "C" int sb_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
   if (rows <= 0 || cols <= 0 || (cols & 7)) return SB_ERR_ARG;
   if (!al16(dy) || !al16(x) || !al16(w) || !al16(dx) || (dres && !al16(dres))) return SB_ERR_ALIGN;
   const int wpb = 4;
-  rmsnorm_bwd_dx_kernel<<<(rows + wpb - 1) / wpb, wpb * 32, 0, STREAM>>>(
-      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
-      static_cast<const __nv_bfloat16*>(w), inv_rms, static_cast<const __nv_bfloat16*>(dres),
-      static_cast<__nv_bfloat16*>(dx), rows, cols);
+  const dim3 dgrid((rows + wpb - 1) / wpb);
+  const __nv_bfloat16 *pdy = static_cast<const __nv_bfloat16*>(dy), *px = static_cast<const __nv_bfloat16*>(x),
+                      *pw = static_cast<const __nv_bfloat16*>(w), *pres = static_cast<const __nv_bfloat16*>(dres);
+  __nv_bfloat16* pdx = static_cast<__nv_bfloat16*>(dx);
+  if (cols == 1024) rmsnorm_bwd_dx_reg_kernel<4><<<dgrid, wpb * 32, 0, STREAM>>>(pdy, px, pw, inv_rms, pres, pdx, rows);
+  else if (cols == 2048) rmsnorm_bwd_dx_reg_kernel<8><<<dgrid, wpb * 32, 0, STREAM>>>(pdy, px, pw, inv_rms, pres, pdx, rows);
+  else if (cols == 512) rmsnorm_bwd_dx_reg_kernel<2><<<dgrid, wpb * 32, 0, STREAM>>>(pdy, px, pw, inv_rms, pres, pdx, rows);
+  else rmsnorm_bwd_dx_kernel<<<dgrid, wpb * 32, 0, STREAM>>>(pdy, px, pw, inv_rms, pres, pdx, rows, cols);
   if (cudaGetLastError() != cudaSuccess) return SB_ERR_LAUNCH;
   if (dw_partial) {
     const int rpc = 256;
