@@ -151,6 +151,20 @@ def main():
                 red = make_grad_reducer(m, dist.group.WORLD, kind=comm)
             return Trainer(m, TrainerConfig(lr=3e-4, weight_decay=0.1, max_grad_norm=1.0), grad_reducer=red)
 
+        tp_mode = args.parallelism == "tp" and world > 1
+        if tp_mode:
+            # tensor parallel (sequence-sharded activations): every rank sees the same batch; the column- and
+            # row-parallel products run as all-gather -> GEMM and GEMM -> reduce-scatter kernels over peer memory
+            from scirust_b200.models.sciagent_tp import TPDecoder
+            from scirust_b200.parallel.tensor_parallel import TPContext
+
+            def build_trainer(comm):  # noqa: F811
+                # peer-visible buffers: two [tokens / W, d] activations per layer plus the gradient pair
+                sym = (2 * cfg.n_layers + 4) * (B * S // world) * cfg.d_model * 2 + (64 << 20)
+                tp = TPContext(dist.group.WORLD, B * S, cfg.d_model, sym_bytes=sym, backend=comm)
+                m = TPDecoder(cfg, tp, seed=1234)
+                return Trainer(m, TrainerConfig(lr=3e-4, weight_decay=0.1, max_grad_norm=1.0))
+
         comm_used = args.comm
         trainer = None
         try:
@@ -179,7 +193,8 @@ def main():
             raise SystemExit("trainer set-up failed")
 
     # synthetic data: a ring of pinned host batches, seeded per rank
-    g = torch.Generator().manual_seed(1000 + rank)
+    tp_mode = args.impl != "baseline" and args.parallelism == "tp" and world > 1
+    g = torch.Generator().manual_seed(1000 + (0 if tp_mode else rank))   # tensor-parallel ranks share the batch
     n_host = 4
     host = [torch.randint(0, cfg.vocab_size, (B, S + 1), generator=g, dtype=torch.int64).pin_memory()
             for _ in range(n_host)]
@@ -230,7 +245,7 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_dev, ms_e2e, wall_ms = (float(x) for x in t.tolist())
-    tokens_per_step = B * S * world
+    tokens_per_step = B * S * (1 if tp_mode else world)
     value = tokens_per_step * args.steps / (ms_dev / 1e3)
     e2e = tokens_per_step * args.steps / (max(ms_e2e, wall_ms) / 1e3)
 
@@ -244,7 +259,7 @@ def main():
             "warmup": args.warmup,
             "ms_per_step": ms_dev / args.steps,
             "higher_is_better": True,
-            "scaling": "weak",
+            "scaling": "strong" if tp_mode else "weak",
             "vs_baseline": value / REF_PUBLISHED_TOK_S,
             "vs_baseline_note": "published reference number is 3947.734 tok/s for its 24-layer 304M cousin "
                                 "(B8xT512) on Jetson AGX Thor; no B200 or multi-GPU number is published",
@@ -253,9 +268,11 @@ def main():
             "impl": args.impl,
             "config": {"model": f"{args.model}: {cfg.n_layers}L d{cfg.d_model} {cfg.n_heads}q/{cfg.n_kv_heads}kv "
                                 f"dh{cfg.head_dim} ff{cfg.d_ff} V{cfg.vocab_size}",
-                       "global_batch": B * world, "seq_len": S, "parallelism": f"{args.parallelism}{world}",
+                       "global_batch": B * (1 if tp_mode else world), "seq_len": S,
+                       "parallelism": f"{'tp' if tp_mode else 'dp'}{world}",
                        "optimizer": "AdamW lr 3e-4 wd 0.1 clip 1.0, fp32 master weights",
-                       "grad_reduce": ("none" if world == 1 else "nccl-ddp" if args.impl == "baseline" else comm_used),
+                       "grad_reduce": ("none" if world == 1 else "nccl-ddp" if args.impl == "baseline"
+                                       else f"tensor-parallel collectives: {comm_used}" if tp_mode else comm_used),
                        "l2": "per-step working set (activations > 5 GB) exceeds the 126 MB L2; no flush needed"},
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "ms_per_step": max(ms_e2e, wall_ms) / args.steps},

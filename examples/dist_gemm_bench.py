@@ -17,6 +17,8 @@ import sys
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
+os.environ.setdefault("SB_TP_RS_MIN_GFLOP", "0")   # time the fused kernels at every size
+
 import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 

@@ -64,6 +64,9 @@ class TPContext:
         # a one-rank group normally takes the plain GEMM; SB_TP_PAIR_SINGLE=1 sends it through the fused CTA-pair
         # kernels (every "peer" is the local buffer) so that a profiler can capture them on one GPU
         self._pair_min_world = 1 if os.environ.get("SB_TP_PAIR_SINGLE", "0") == "1" else 2
+        # weight gradients: SB_TP_DIRECT_WGRAD=1 keeps the kernel that reads the gathered operand from the peers tile
+        # by tile (every remote tile crosses NVLink once per output column tile: slower, kept for comparison)
+        self.direct_wgrad = os.environ.get("SB_TP_DIRECT_WGRAD", "0") == "1"
         self._named = {}
         if backend == "fused":
             stage_bytes = max_rows * max_cols * 2          # W * (rows/W) * cols bf16
@@ -137,6 +140,18 @@ class TPContext:
         _g.launch_count += 1
         return out
 
+    # Below this much work per rank the fused GEMM -> reduce-scatter is bound by its flag round trips (0.19 ms against
+    # 0.12 ms at 16384 x 1408 x 1024 on two GPUs); the product then runs on the plain GEMM and NCCL scatters it.
+    RS_FUSED_MIN_FLOP = float(os.environ.get("SB_TP_RS_MIN_GFLOP", "200")) * 1e9
+
+    def _rs_small(self, M, N, K):
+        return 2.0 * M * N * K < self.RS_FUSED_MIN_FLOP and self._pair_min_world == 2
+
+    def _rs_unfused(self, full, residual_shard, Tl, N):
+        out = torch.empty((Tl, N), dtype=BF, device=self.dev)
+        dist.reduce_scatter_tensor(out, full, group=self.group)
+        return out + residual_shard if residual_shard is not None else out
+
     def _rs_pair_ok(self, M, N):
         return (self.pair and self.world >= self._pair_min_world and M % (self.world * 256) == 0 and N % 8 == 0
                 and self.world * (M // self.world // 256) <= 8 * 512 and M // 256 + 2 <= self._rs_ctr.numel())
@@ -206,6 +221,8 @@ class TPContext:
             out = torch.empty((Tl, N), dtype=BF, device=self.dev)
             dist.reduce_scatter_tensor(out, full, group=self.group)
             return out + residual_shard if residual_shard is not None else out
+        if self._rs_small(T, N, K):
+            return self._rs_unfused(_g.matmul_nn(a, w), residual_shard, Tl, N)
         out = torch.empty((Tl, N), dtype=BF, device=self.dev)
         if self._rs_pair_ok(T, N):
             return self._rs_pair(a, w, out, residual_shard, T, N, K, True)
@@ -221,6 +238,8 @@ class TPContext:
             out = torch.empty((Tl, N), dtype=BF, device=self.dev)
             dist.reduce_scatter_tensor(out, full, group=self.group)
             return out + residual_shard if residual_shard is not None else out
+        if self._rs_small(T, N, K):
+            return self._rs_unfused(_g.matmul_nt(a, w), residual_shard, Tl, N)
         out = torch.empty((Tl, N), dtype=BF, device=self.dev)
         if self._rs_pair_ok(T, N):
             return self._rs_pair(a, w, out, residual_shard, T, N, K, False)
@@ -241,9 +260,15 @@ class TPContext:
                 out.copy_(r)
                 return out
             return r
-        if out is None:
-            out = torch.empty((M, N), dtype=BF, device=self.dev)
-        return self._call(x_shard, dy, out, residual, M, N, T, True, True, True, False, False)
+        if self.direct_wgrad:
+            if out is None:
+                out = torch.empty((M, N), dtype=BF, device=self.dev)
+            return self._call(x_shard, dy, out, residual, M, N, T, True, True, True, False, False)
+        # weight gradient: the gathered operand is needed whole by every output tile, so it is landed once in local
+        # memory (a plain all-gather) and the product runs on the CTA-pair GEMM
+        x = torch.empty((T, M), dtype=BF, device=self.dev)
+        dist.all_gather_into_tensor(x, x_shard.contiguous(), group=self.group)
+        return _g.matmul_tn(x, dy, residual=residual, out=out)
 
     def matmul_tn_ag(self, a, dy_shard, out=None, residual=None):
         """aᵀ @ all-gather(dy_shard) -> [K_a, N]: weight gradient of a row-parallel layer
@@ -260,9 +285,13 @@ class TPContext:
                 out.copy_(r)
                 return out
             return r
-        if out is None:
-            out = torch.empty((M, N), dtype=BF, device=self.dev)
-        return self._call(a, dy_shard, out, residual, M, N, T, True, True, False, True, False)
+        if self.direct_wgrad:
+            if out is None:
+                out = torch.empty((M, N), dtype=BF, device=self.dev)
+            return self._call(a, dy_shard, out, residual, M, N, T, True, True, False, True, False)
+        dy = torch.empty((T, N), dtype=BF, device=self.dev)
+        dist.all_gather_into_tensor(dy, dy_shard.contiguous(), group=self.group)
+        return _g.matmul_tn(a, dy, residual=residual, out=out)
 
     def close(self):
         if self.region is not None:

@@ -46,13 +46,14 @@ def test_dp_training_fused_equals_nccl_baseline():
 
 def test_tp_fused_layers_match_nccl_baseline():
     _need(2)
-    out = _run("mp_tp_layers.py", 2, 29613)
+    # SB_TP_RS_MIN_GFLOP=0: the tiny test shapes must still take the fused GEMM -> reduce-scatter kernel
+    out = _run("mp_tp_layers.py", 2, 29613, extra_env={"SB_TP_RS_MIN_GFLOP": "0"})
     assert "TP_OK" in out
 
 
 def test_tp_decoder_trains_like_single_gpu():
     _need(2)
-    out = _run("mp_tp_model.py", 2, 29614)
+    out = _run("mp_tp_model.py", 2, 29614, extra_env={"SB_TP_RS_MIN_GFLOP": "0"})
     assert "TP_MODEL_OK" in out
 
 
