@@ -26,7 +26,7 @@ from scirust_b200.ops import _lib  # noqa: E402
 from scirust_b200.parallel.tensor_parallel import TPContext  # noqa: E402
 
 BF = torch.bfloat16
-GEMM_TFLOPS = 1380.7     # measured sustained cuBLAS bf16 rate on this pool (TFLOP/s)
+GEMM_TFLOPS = 1380.7     # measured sustained cuBLAS bf16 rate of a B200 under its power cap (TFLOP/s)
 LINK_GBS = 770.0         # measured peer-copy rate per direction per GPU (GB/s)
 
 
