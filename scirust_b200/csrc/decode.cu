@@ -135,8 +135,8 @@ gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
       // row statistic with the association of rmsnorm_fwd_kernel: per lane, accumulator a takes the
       // 16-byte chunks lane*8 + 256*(a + 8*j); here warp a computes accumulator a of every row
       float* s_part = xs;   // [M][8 warps][32 lanes], overwritten by the staging below
-      for (int m = 0; m < M; ++m) {
-        const __nv_bfloat16* xr = p.X + static_cast<size_t>(m) * p.ldx;
+      if (M == 1) {
+        const __nv_bfloat16* xr = p.X;
         float a = 0.f;
         for (int c = lane * 8 + warp * 256; c < K; c += 8 * 256) {
           const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
@@ -145,7 +145,28 @@ gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 8; ++j) a += f[j] * f[j];
         }
-        s_part[(m * 8 + warp) * 32 + lane] = a;
+        s_part[warp * 32 + lane] = a;
+      } else {
+        // all rows of one column step are loaded before the first use; per row the adds keep their order
+        float a8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int c = lane * 8 + warp * 256; c < K; c += 8 * 256) {
+          uint4 raw[8];
+#pragma unroll
+          for (int m = 0; m < 8; ++m)
+            if (m < M) raw[m] = *reinterpret_cast<const uint4*>(p.X + static_cast<size_t>(m) * p.ldx + c);
+#pragma unroll
+          for (int m = 0; m < 8; ++m) {
+            if (m < M) {
+              const float f[8] = {dbflo(raw[m].x), dbfhi(raw[m].x), dbflo(raw[m].y), dbfhi(raw[m].y),
+                                  dbflo(raw[m].z), dbfhi(raw[m].z), dbflo(raw[m].w), dbfhi(raw[m].w)};
+#pragma unroll
+              for (int j = 0; j < 8; ++j) a8[m] += f[j] * f[j];
+            }
+          }
+        }
+#pragma unroll
+        for (int m = 0; m < 8; ++m)
+          if (m < M) s_part[(m * 8 + warp) * 32 + lane] = a8[m];
       }
       asm volatile("bar.sync 1, 256;" ::: "memory");
       for (int m = warp; m < M; m += 8) {
@@ -368,8 +389,8 @@ gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     if (p.prologue == PRO_RMSNORM) {
       // row statistic with the association of rmsnorm_fwd_kernel (see the FMA kernel)
       float* s_part = reinterpret_cast<float*>(xs);   // [M][8 warps][32 lanes], overwritten by the staging below
-      for (int m = 0; m < M; ++m) {
-        const __nv_bfloat16* xr = p.X + static_cast<size_t>(m) * p.ldx;
+      if (M == 1) {
+        const __nv_bfloat16* xr = p.X;
         float a = 0.f;
         for (int c = lane * 8 + warp * 256; c < K; c += 8 * 256) {
           const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
@@ -378,7 +399,28 @@ gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 #pragma unroll
           for (int j = 0; j < 8; ++j) a += f[j] * f[j];
         }
-        s_part[(m * 8 + warp) * 32 + lane] = a;
+        s_part[warp * 32 + lane] = a;
+      } else {
+        // all rows of one column step are loaded before the first use; per row the adds keep their order
+        float a8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int c = lane * 8 + warp * 256; c < K; c += 8 * 256) {
+          uint4 raw[8];
+#pragma unroll
+          for (int m = 0; m < 8; ++m)
+            if (m < M) raw[m] = *reinterpret_cast<const uint4*>(p.X + static_cast<size_t>(m) * p.ldx + c);
+#pragma unroll
+          for (int m = 0; m < 8; ++m) {
+            if (m < M) {
+              const float f[8] = {dbflo(raw[m].x), dbfhi(raw[m].x), dbflo(raw[m].y), dbfhi(raw[m].y),
+                                  dbflo(raw[m].z), dbfhi(raw[m].z), dbflo(raw[m].w), dbfhi(raw[m].w)};
+#pragma unroll
+              for (int j = 0; j < 8; ++j) a8[m] += f[j] * f[j];
+            }
+          }
+        }
+#pragma unroll
+        for (int m = 0; m < 8; ++m)
+          if (m < M) s_part[(m * 8 + warp) * 32 + lane] = a8[m];
       }
       asm volatile("bar.sync 1, 256;" ::: "memory");
       if (warp < M) {
@@ -396,25 +438,61 @@ gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     // weight row past K is zero too and 0 * x must not meet garbage
     uint32_t* xs_w = reinterpret_cast<uint32_t*>(xs);
     const int n_pairs = ntiles * GEMV_KT / 2;
-    for (int i = threadIdx.x; i < n_pairs * M; i += 256) {
-      const int kp = i / M, m = i - kp * M;
-      float xv[2];
+    const bool vec_ok = ((p.ldx & 7) == 0) && ((K & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.X) & 15) == 0) &&
+                        (p.prologue != PRO_RMSNORM || (reinterpret_cast<uintptr_t>(p.norm_w) & 15) == 0);
+    if (vec_ok && M > 1) {   // a single row is staged faster by the pair loop below (3.40 against 4.07 ms per decode step)
+      // eight consecutive k of one row per thread: one 16-byte load of X (and of the gain, or of the up half)
+      const int n_oct = n_pairs / 4;
+      for (int i = threadIdx.x; i < n_oct * M; i += 256) {
+        const int ko = i / M, m = i - ko * M;
+        const int k = k0 + ko * 8;
+        float v[8];
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int k = k0 + kp * 2 + e;
-        float v = 0.f;
-        if (k < k1) {
-          v = __bfloat162float(p.X[static_cast<size_t>(m) * p.ldx + k]);
+        for (int e = 0; e < 8; ++e) v[e] = 0.f;
+        if (k < k1) {      // k1 - k0 and K are multiples of 8: an octet is inside the range or outside it
+          const __nv_bfloat16* xr = p.X + static_cast<size_t>(m) * p.ldx + k;
+          const uint4 raw = *reinterpret_cast<const uint4*>(xr);
+          v[0] = dbflo(raw.x); v[1] = dbfhi(raw.x); v[2] = dbflo(raw.y); v[3] = dbfhi(raw.y);
+          v[4] = dbflo(raw.z); v[5] = dbfhi(raw.z); v[6] = dbflo(raw.w); v[7] = dbfhi(raw.w);
           if (p.prologue == PRO_RMSNORM) {
-            v = v * s_inv[m] * __bfloat162float(p.norm_w[k]);
+            const uint4 gw = *reinterpret_cast<const uint4*>(p.norm_w + k);
+            const float g[8] = {dbflo(gw.x), dbfhi(gw.x), dbflo(gw.y), dbfhi(gw.y),
+                                dbflo(gw.z), dbfhi(gw.z), dbflo(gw.w), dbfhi(gw.w)};
+            const float inv = s_inv[m];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = v[e] * inv * g[e];
           } else if (p.prologue == PRO_SWIGLU) {
-            const float u = __bfloat162float(p.X[static_cast<size_t>(m) * p.ldx + K + k]);
-            v = v / (1.f + __expf(-v)) * u;
+            const uint4 uw = *reinterpret_cast<const uint4*>(xr + K);
+            const float u[8] = {dbflo(uw.x), dbfhi(uw.x), dbflo(uw.y), dbfhi(uw.y),
+                                dbflo(uw.z), dbfhi(uw.z), dbflo(uw.w), dbfhi(uw.w)};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = v[e] / (1.f + __expf(-v[e])) * u[e];
           }
         }
-        xv[e] = v;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) xs_w[(ko * 4 + e) * XR + m] = dpack(v[2 * e], v[2 * e + 1]);
       }
-      xs_w[kp * XR + m] = dpack(xv[0], xv[1]);
+    } else {
+      for (int i = threadIdx.x; i < n_pairs * M; i += 256) {
+        const int kp = i / M, m = i - kp * M;
+        float xv[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int k = k0 + kp * 2 + e;
+          float v = 0.f;
+          if (k < k1) {
+            v = __bfloat162float(p.X[static_cast<size_t>(m) * p.ldx + k]);
+            if (p.prologue == PRO_RMSNORM) {
+              v = v * s_inv[m] * __bfloat162float(p.norm_w[k]);
+            } else if (p.prologue == PRO_SWIGLU) {
+              const float u = __bfloat162float(p.X[static_cast<size_t>(m) * p.ldx + K + k]);
+              v = v / (1.f + __expf(-v)) * u;
+            }
+          }
+          xv[e] = v;
+        }
+        xs_w[kp * XR + m] = dpack(xv[0], xv[1]);
+      }
     }
     asm volatile("bar.sync 1, 256;" ::: "memory");
 
@@ -510,6 +588,14 @@ gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   }
 }
 
+// fp16 pair of two values that are first rounded to bf16 (the activation format) and saturated to the fp16 range
+__device__ __forceinline__ uint32_t hpack_bf16_rounded(float a, float b) {
+  const float c0 = fminf(fmaxf(__bfloat162float(__float2bfloat16_rn(a)), -65504.f), 65504.f);
+  const float c1 = fminf(fmaxf(__bfloat162float(__float2bfloat16_rn(b)), -65504.f), 65504.f);
+  const __half2 hp = __floats2half2_rn(c0, c1);
+  return *reinterpret_cast<const uint32_t*>(&hp);
+}
+
 // int8 weights on the same tensor-core path: the tile is streamed as 16-bit words (two int8 columns per word) in
 // 128-byte-swizzled boxes, the transposed ldmatrix hands every thread 2 x 2 (k, column) bytes, a byte permute and one
 // packed fp16 subtract turn them into exact fp16 values, and the MMA runs in fp16 with fp32 accumulation; the
@@ -576,8 +662,8 @@ gemv_mma_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     if (p.prologue == PRO_RMSNORM) {
       // row statistic with the association of rmsnorm_fwd_kernel (see the FMA kernel)
       float* s_part = reinterpret_cast<float*>(xs);   // [M][8 warps][32 lanes], overwritten by the staging below
-      for (int m = 0; m < M; ++m) {
-        const __nv_bfloat16* xr = p.X + static_cast<size_t>(m) * p.ldx;
+      if (M == 1) {
+        const __nv_bfloat16* xr = p.X;
         float a = 0.f;
         for (int c = lane * 8 + warp * 256; c < K; c += 8 * 256) {
           const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
@@ -586,7 +672,28 @@ gemv_mma_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 #pragma unroll
           for (int j = 0; j < 8; ++j) a += f[j] * f[j];
         }
-        s_part[(m * 8 + warp) * 32 + lane] = a;
+        s_part[warp * 32 + lane] = a;
+      } else {
+        // all rows of one column step are loaded before the first use; per row the adds keep their order
+        float a8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int c = lane * 8 + warp * 256; c < K; c += 8 * 256) {
+          uint4 raw[8];
+#pragma unroll
+          for (int m = 0; m < 8; ++m)
+            if (m < M) raw[m] = *reinterpret_cast<const uint4*>(p.X + static_cast<size_t>(m) * p.ldx + c);
+#pragma unroll
+          for (int m = 0; m < 8; ++m) {
+            if (m < M) {
+              const float f[8] = {dbflo(raw[m].x), dbfhi(raw[m].x), dbflo(raw[m].y), dbfhi(raw[m].y),
+                                  dbflo(raw[m].z), dbfhi(raw[m].z), dbflo(raw[m].w), dbfhi(raw[m].w)};
+#pragma unroll
+              for (int j = 0; j < 8; ++j) a8[m] += f[j] * f[j];
+            }
+          }
+        }
+#pragma unroll
+        for (int m = 0; m < 8; ++m)
+          if (m < M) s_part[(m * 8 + warp) * 32 + lane] = a8[m];
       }
       asm volatile("bar.sync 1, 256;" ::: "memory");
       if (warp < M) {
@@ -605,29 +712,60 @@ gemv_mma_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     // weight row past K is zero too and 0 * x must not meet garbage
     uint32_t* xs_w = reinterpret_cast<uint32_t*>(xs);
     const int n_pairs = ntiles * GEMV_KT / 2;
-    for (int i = threadIdx.x; i < n_pairs * M; i += 256) {
-      const int kp = i / M, m = i - kp * M;
-      float xv[2];
+    const bool vec_ok = ((p.ldx & 7) == 0) && ((K & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.X) & 15) == 0) &&
+                        (p.prologue != PRO_RMSNORM || (reinterpret_cast<uintptr_t>(p.norm_w) & 15) == 0);
+    if (vec_ok && M > 1) {   // a single row is staged faster by the pair loop below (3.40 against 4.07 ms per decode step)
+      // eight consecutive k of one row per thread: one 16-byte load of X (and of the gain, or of the up half)
+      const int n_oct = n_pairs / 4;
+      for (int i = threadIdx.x; i < n_oct * M; i += 256) {
+        const int ko = i / M, m = i - ko * M;
+        const int k = k0 + ko * 8;
+        float v[8];
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int k = k0 + kp * 2 + e;
-        float v = 0.f;
-        if (k < k1) {
-          v = __bfloat162float(p.X[static_cast<size_t>(m) * p.ldx + k]);
+        for (int e = 0; e < 8; ++e) v[e] = 0.f;
+        if (k < k1) {      // k1 - k0 and K are multiples of 8: an octet is inside the range or outside it
+          const __nv_bfloat16* xr = p.X + static_cast<size_t>(m) * p.ldx + k;
+          const uint4 raw = *reinterpret_cast<const uint4*>(xr);
+          v[0] = dbflo(raw.x); v[1] = dbfhi(raw.x); v[2] = dbflo(raw.y); v[3] = dbfhi(raw.y);
+          v[4] = dbflo(raw.z); v[5] = dbfhi(raw.z); v[6] = dbflo(raw.w); v[7] = dbfhi(raw.w);
           if (p.prologue == PRO_RMSNORM) {
-            v = v * s_inv[m] * __bfloat162float(p.norm_w[k]);
+            const uint4 gw = *reinterpret_cast<const uint4*>(p.norm_w + k);
+            const float g[8] = {dbflo(gw.x), dbfhi(gw.x), dbflo(gw.y), dbfhi(gw.y),
+                                dbflo(gw.z), dbfhi(gw.z), dbflo(gw.w), dbfhi(gw.w)};
+            const float inv = s_inv[m];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = v[e] * inv * g[e];
           } else if (p.prologue == PRO_SWIGLU) {
-            const float u = __bfloat162float(p.X[static_cast<size_t>(m) * p.ldx + K + k]);
-            v = v / (1.f + __expf(-v)) * u;
+            const uint4 uw = *reinterpret_cast<const uint4*>(xr + K);
+            const float u[8] = {dbflo(uw.x), dbfhi(uw.x), dbflo(uw.y), dbfhi(uw.y),
+                                dbflo(uw.z), dbfhi(uw.z), dbflo(uw.w), dbfhi(uw.w)};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = v[e] / (1.f + __expf(-v[e])) * u[e];
           }
         }
-        xv[e] = v;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) xs_w[(ko * 4 + e) * XR + m] = hpack_bf16_rounded(v[2 * e], v[2 * e + 1]);
       }
-      {
-        const float c0 = fminf(fmaxf(__bfloat162float(__float2bfloat16_rn(xv[0])), -65504.f), 65504.f);
-        const float c1 = fminf(fmaxf(__bfloat162float(__float2bfloat16_rn(xv[1])), -65504.f), 65504.f);
-        const __half2 hp = __floats2half2_rn(c0, c1);
-        xs_w[kp * XR + m] = *reinterpret_cast<const uint32_t*>(&hp);
+    } else {
+      for (int i = threadIdx.x; i < n_pairs * M; i += 256) {
+        const int kp = i / M, m = i - kp * M;
+        float xv[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int k = k0 + kp * 2 + e;
+          float v = 0.f;
+          if (k < k1) {
+            v = __bfloat162float(p.X[static_cast<size_t>(m) * p.ldx + k]);
+            if (p.prologue == PRO_RMSNORM) {
+              v = v * s_inv[m] * __bfloat162float(p.norm_w[k]);
+            } else if (p.prologue == PRO_SWIGLU) {
+              const float u = __bfloat162float(p.X[static_cast<size_t>(m) * p.ldx + K + k]);
+              v = v / (1.f + __expf(-v)) * u;
+            }
+          }
+          xv[e] = v;
+        }
+        xs_w[kp * XR + m] = hpack_bf16_rounded(xv[0], xv[1]);
       }
     }
     asm volatile("bar.sync 1, 256;" ::: "memory");
