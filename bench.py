@@ -10,7 +10,15 @@ reduction + clip + optimizer update.
     python bench.py --gpus 1 --steps 20 --warmup 3
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 3
-    python bench.py --impl reference ...     # the reference arm (see below)
+    python bench.py --impl reference ...     # the reference arm (baseline/reference_replay.py)
+    python bench.py --mode infer --gpus 1    # only the inference half of the metric
+
+The metric has two halves: training tokens/s (``value``) and, for the Llama-3-8B-shaped serving
+configuration (32 layers, d 4096, 32 query / 8 KV heads, head_dim 128, SwiGLU 14336, vocab 128256,
+random-init bf16 weights; prompt 2048, greedy decode of 256 tokens, paged bf16 KV cache, batch 1 / 16 / 64,
+bf16 and int8 per-output-channel weights, tensor-parallel over ``--gpus``), decode tokens/s and p50
+time to first token (``decode_tok_s``, ``ttft_ms_p50`` = the batch-1 bf16 row; every row under
+``inference``).
 
 Rank 0 prints one JSON line. ``value`` is timed on the device with CUDA events (max over ranks)
 with the step's tokens already resident; ``e2e`` times the same steps through
@@ -43,6 +51,15 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"])
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--mode", default="all", choices=["all", "train", "infer"],
+                    help="train: training tokens/s only; infer: decode tokens/s and TTFT only; all: both")
+    ap.add_argument("--infer-model", default="llama3_8b")
+    ap.add_argument("--infer-batches", default="1,16,64")
+    ap.add_argument("--infer-quants", default="none,int8")
+    ap.add_argument("--prompt", type=int, default=2048)
+    ap.add_argument("--new", type=int, default=256)
+    ap.add_argument("--strict", action="store_true",
+                    help="exit non-zero when the fused path was abandoned for the library fallback")
     return ap.parse_args()
 
 
@@ -93,39 +110,29 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    """The reference is a pure-Rust Cargo workspace with no Python packaging; this image has no
-    cargo/rustc, so it cannot be built or installed (pip: 'not installable: neither setup.py nor
-    pyproject.toml')."""
-    print(json.dumps({"impl": "reference",
-                      "unavailable": "reference is a Rust Cargo workspace (no setup.py/pyproject.toml); "
-                                     "no cargo/rustc in this image, so baseline/_ref cannot be built"}))
-    return 0
+    """The reference is a pure-Rust Cargo workspace and this image has no cargo/rustc, so it cannot be built.
+    What can run is a replay of its CUDA route: its CUDA-C kernel sources (kept verbatim under
+    ``baseline/_ref``, outside this repository's history) compiled with NVRTC at the reference's options
+    and driven, with cuBLAS bf16 GEMMs, in the reference's own call order. None of this framework's
+    kernels, models or engine run on this arm."""
+    try:
+        from baseline import reference_replay
+    except Exception as exc:  # pragma: no cover - import guard
+        print(json.dumps({"impl": "reference", "unavailable": f"replay harness failed to import: {exc}"}))
+        return 0
+    return reference_replay.main(args, ClockSampler)
 
 
-def main():
-    args = parse()
-    if args.impl == "reference":
-        return reference_arm(args)
-
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            # re-launch under torchrun
-            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
-                   "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29511"),
-                   os.path.abspath(__file__)] + sys.argv[1:]
-            return subprocess.call(cmd)
-        raise SystemExit(f"WORLD_SIZE={world} does not match --gpus {args.gpus}")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-
+def _barrier(world):
     import torch.distributed as dist
     if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        dist.barrier()
+    torch.cuda.synchronize()
 
+
+def train_arm(args, rank, local_rank, world, dev):
+    """Training half: returns the fields of the JSON line (rank 0) after timing K steps."""
+    import torch.distributed as dist
     from scirust_b200.models import GQADecoder, SciAgentConfig
     from scirust_b200.ops import gemm as gemm_ops
     from scirust_b200.ops import _lib
@@ -133,6 +140,8 @@ def main():
 
     cfg = SciAgentConfig.preset(args.model)
     B, S = args.batch_per_gpu, args.seq_len
+    fallback = False
+    comm_used = args.comm
     if args.impl == "baseline":
         # library arm: stock PyTorch operators (cuBLAS, SDPA, fused AdamW) + NCCL DDP, none of our kernels
         from scirust_b200.models.baseline_torch import TorchLibraryDecoder, TorchLibraryTrainer
@@ -165,7 +174,6 @@ def main():
                 m = TPDecoder(cfg, tp, seed=1234)
                 return Trainer(m, TrainerConfig(lr=3e-4, weight_decay=0.1, max_grad_norm=1.0))
 
-        comm_used = args.comm
         trainer = None
         try:
             trainer = build_trainer(args.comm)
@@ -186,6 +194,7 @@ def main():
             dist.all_reduce(flag, op=dist.ReduceOp.MIN)
             if int(flag.item()) == 0:
                 comm_used = "nccl"
+                fallback = True
                 trainer = None
                 torch.cuda.empty_cache()
                 trainer = build_trainer("nccl")
@@ -200,33 +209,28 @@ def main():
             for _ in range(n_host)]
     resident = [h.to(dev) for h in host]
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
     # ---- device-timed region (inputs resident) --------------------------------------------
     for i in range(args.warmup):
         trainer.train_step(resident[i % n_host])
-    barrier()
+    _barrier(world)
     _lib.check_status(dev)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     launches0 = gemm_ops.launch_count
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
+    _barrier(world)
     e0.record()
     for i in range(args.steps):
         loss = trainer.train_step(resident[i % n_host])
     e1.record()
-    barrier()
+    _barrier(world)
     ms_dev = e0.elapsed_time(e1)
     launches = gemm_ops.launch_count - launches0
 
     # ---- end-to-end region: pinned host tokens in, loss out, every step ------------------
     h2d = host[0].numel() * host[0].element_size()
-    barrier()
+    _barrier(world)
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     e2.record()
@@ -235,7 +239,7 @@ def main():
         loss = trainer.train_step(host[i % n_host])
         last = float(loss.item())  # device -> host read of the step's loss (4 bytes)
     e3.record()
-    barrier()
+    _barrier(world)
     wall_ms = (time.perf_counter() - t0) * 1e3
     ms_e2e = max(e2.elapsed_time(e3), 0.0)
     clocks = sampler.stop() if rank == 0 else None
@@ -248,41 +252,184 @@ def main():
     tokens_per_step = B * S * (1 if tp_mode else world)
     value = tokens_per_step * args.steps / (ms_dev / 1e3)
     e2e = tokens_per_step * args.steps / (max(ms_e2e, wall_ms) / 1e3)
+    # the one published figure is for the reference's 24-layer 304M model at batch 8 x 512 on a Jetson AGX Thor;
+    # it is a like-for-like config only when that model and shape are benchmarked, on one GPU
+    like = args.model == "350m" and B == 8 and S == 512 and world == 1
+    out = {
+        "metric": "GQA decoder train tok/s & decode tok/s, p50 TTFT",
+        "value": value,
+        "unit": "tokens/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": ms_dev / args.steps,
+        "higher_is_better": True,
+        "scaling": "strong" if tp_mode else "weak",
+        "vs_baseline": (value / REF_PUBLISHED_TOK_S) if like else None,
+        "vs_baseline_note": "the only published training figure is 3947.734 tok/s for the reference's 24-layer 304M "
+                            "model (B8xT512) on a Jetson AGX Thor; no figure is published for this config or for a "
+                            "B200, so the ratio is given only for `--model 350m --seq-len 512` on one GPU",
+        "published_context": {"tok_s": REF_PUBLISHED_TOK_S, "ratio_other_config": value / REF_PUBLISHED_TOK_S},
+        "dtype": "bf16",
+        "data": "synthetic token ids ~U{0..V-1}, random-init N(0,0.02) weights",
+        "impl": args.impl,
+        "fallback": fallback,
+        "config": {"model": f"{args.model}: {cfg.n_layers}L d{cfg.d_model} {cfg.n_heads}q/{cfg.n_kv_heads}kv "
+                            f"dh{cfg.head_dim} ff{cfg.d_ff} V{cfg.vocab_size}",
+                   "global_batch": B * (1 if tp_mode else world), "seq_len": S,
+                   "parallelism": f"{'tp' if tp_mode else 'dp'}{world}",
+                   "optimizer": "AdamW lr 3e-4 wd 0.1 clip 1.0, fp32 master weights",
+                   "grad_reduce": ("none" if world == 1 else "nccl-ddp" if args.impl == "baseline"
+                                   else f"tensor-parallel collectives: {comm_used}" if tp_mode else comm_used),
+                   "l2": "per-step working set (activations > 5 GB) exceeds the 126 MB L2; no flush needed"},
+        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+                "ms_per_step": max(ms_e2e, wall_ms) / args.steps},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "final_loss": last,
+    }
+    del trainer
+    return out
 
+
+def infer_arm(args, rank, local_rank, world, dev):
+    """Inference half: Llama-3-8B-shaped decoder, prompt ``--prompt``, greedy decode of ``--new`` tokens with a
+    paged bf16 KV cache, for every batch in ``--infer-batches`` and weight format in ``--infer-quants``,
+    tensor-parallel over all ranks. Times are CUDA-event times, maximum over ranks. TTFT covers the prompt's
+    host->device copy from pinned memory, the prefill, the first arg-max and the token's device->host copy;
+    decode tokens/s covers the remaining ``new - 1`` steps (CUDA-graph replay, device-side token feedback);
+    the end-to-end figure is the whole request (prompt in from pinned memory, all tokens back on the host)."""
+    import statistics as st
+    import torch.distributed as dist
+    from scirust_b200.models import GQADecoder, SciAgentConfig
+    from scirust_b200.models.infer import InferenceEngine
+    from scirust_b200.ops import _lib
+    from scirust_b200.ops import gemm as gemm_ops
+
+    cfg = SciAgentConfig.preset(args.infer_model)
+    batches = [int(b) for b in args.infer_batches.split(",") if b]
+    quants = [q for q in args.infer_quants.split(",") if q]
+    P, NEW = args.prompt, args.new
+    model = GQADecoder(cfg, device=dev, seed=7)
+    rows = []
+    launches = 0
+    for quant in quants:
+        for B in batches:
+            row = {"batch": B, "weights": "bf16" if quant == "none" else quant, "tp": world}
+            eng = None
+            try:
+                q = None if quant == "none" else "int8"
+                if world > 1:
+                    from scirust_b200.models.infer_tp import TPInferenceEngine
+                    eng = TPInferenceEngine(model, quant=q, max_batch=B, max_seq=P + NEW + 1, page=64,
+                                            backend=args.comm)
+                else:
+                    eng = InferenceEngine(model, quant=q, max_batch=B, max_seq=P + NEW + 1, page=64)
+                g = torch.Generator().manual_seed(0)
+                prompts = torch.randint(0, cfg.vocab_size, (B, P), generator=g).pin_memory()
+                iters = 5 if B == 1 else 3 if B <= 16 else 2
+                ttft = []
+                for i in range(iters + 1):
+                    for b in range(B):
+                        if eng.cache.owned[b]:
+                            eng.cache.release(b)
+                    _barrier(world)
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    eng.prefill(prompts)
+                    first = eng.tokens[:B].cpu()          # noqa: F841  device -> host copy of the first tokens
+                    e1.record()
+                    torch.cuda.synchronize()
+                    if i >= 1:
+                        ttft.append(e0.elapsed_time(e1))
+                eng.generate(prompts, 4)                  # warm-up: workspaces, graph capture path
+                _barrier(world)
+                l0 = gemm_ops.launch_count
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0 = time.perf_counter()
+                e0.record()
+                out = eng.generate(prompts, NEW)
+                e1.record()
+                host_tokens = out.cpu()                    # device -> host read of every generated token
+                wall_ms = (time.perf_counter() - t0) * 1e3
+                torch.cuda.synchronize()
+                launches += gemm_ops.launch_count - l0
+                total_ms = e0.elapsed_time(e1)
+                decode_ms = eng.prefill_done.elapsed_time(e1)
+                p50 = st.median(ttft)
+                t = torch.tensor([p50, total_ms, decode_ms, wall_ms], dtype=torch.float64, device=dev)
+                if world > 1:
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                p50, total_ms, decode_ms, wall_ms = (float(x) for x in t.tolist())
+                _lib.check_status(dev)
+                row.update({"ttft_ms_p50": p50, "decode_tok_s": B * (NEW - 1) / (decode_ms / 1e3),
+                            "decode_ms_per_step": decode_ms / (NEW - 1),
+                            "e2e_request_tok_s": B * NEW / (max(total_ms, wall_ms) / 1e3),
+                            "h2d_bytes": prompts.numel() * 8, "d2h_bytes": host_tokens.numel() * 8,
+                            "first_tokens": host_tokens[:2, 0].tolist()})
+            except Exception as exc:      # keep the rows already measured; a failed row says why
+                row["error"] = f"{type(exc).__name__}: {exc}"[:300]
+            finally:
+                if eng is not None and hasattr(eng, "close"):
+                    try:
+                        eng.close()
+                    except Exception:
+                        pass
+                eng = None
+                torch.cuda.empty_cache()
+            rows.append(row)
+    head = next((r for r in rows if r["batch"] == 1 and r["weights"] == "bf16" and "error" not in r), None)
+    return {"decode_tok_s": head["decode_tok_s"] if head else None,
+            "ttft_ms_p50": head["ttft_ms_p50"] if head else None,
+            "inference": {"model": f"{args.infer_model}: {cfg.n_layers}L d{cfg.d_model} {cfg.n_heads}q/"
+                                   f"{cfg.n_kv_heads}kv dh{cfg.head_dim} ff{cfg.d_ff} V{cfg.vocab_size}, random-init",
+                          "prompt": P, "new_tokens": NEW, "kv_cache": "paged bf16, page 64",
+                          "parallelism": f"tp{world}", "timing": "CUDA events, max over ranks", "rows": rows,
+                          "gpu_launches": launches}}
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            # re-launch under torchrun
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+                   "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29511"),
+                   os.path.abspath(__file__)] + sys.argv[1:]
+            return subprocess.call(cmd)
+        raise SystemExit(f"WORLD_SIZE={world} does not match --gpus {args.gpus}")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+
+    import torch.distributed as dist
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    out = {}
+    if args.mode in ("all", "train"):
+        out = train_arm(args, rank, local_rank, world, dev)
+        torch.cuda.empty_cache()
+    if args.mode in ("all", "infer") and args.impl == "ours":
+        inf = infer_arm(args, rank, local_rank, world, dev)
+        if not out:
+            out = {"metric": "GQA decoder decode tok/s, p50 TTFT", "value": inf["decode_tok_s"], "unit": "tokens/s",
+                   "n_gpus": world, "higher_is_better": True, "dtype": "bf16", "impl": args.impl,
+                   "data": "synthetic token ids ~U{0..V-1}, random-init weights", "vs_baseline": None,
+                   "gpu_launches": inf["inference"]["gpu_launches"]}
+        out.update(inf)
     if rank == 0:
-        out = {
-            "metric": "GQA decoder train tok/s",
-            "value": value,
-            "unit": "tokens/s",
-            "n_gpus": world,
-            "steps": args.steps,
-            "warmup": args.warmup,
-            "ms_per_step": ms_dev / args.steps,
-            "higher_is_better": True,
-            "scaling": "strong" if tp_mode else "weak",
-            "vs_baseline": value / REF_PUBLISHED_TOK_S,
-            "vs_baseline_note": "published reference number is 3947.734 tok/s for its 24-layer 304M cousin "
-                                "(B8xT512) on Jetson AGX Thor; no B200 or multi-GPU number is published",
-            "dtype": "bf16",
-            "data": "synthetic token ids ~U{0..V-1}, random-init N(0,0.02) weights",
-            "impl": args.impl,
-            "config": {"model": f"{args.model}: {cfg.n_layers}L d{cfg.d_model} {cfg.n_heads}q/{cfg.n_kv_heads}kv "
-                                f"dh{cfg.head_dim} ff{cfg.d_ff} V{cfg.vocab_size}",
-                       "global_batch": B * (1 if tp_mode else world), "seq_len": S,
-                       "parallelism": f"{'tp' if tp_mode else 'dp'}{world}",
-                       "optimizer": "AdamW lr 3e-4 wd 0.1 clip 1.0, fp32 master weights",
-                       "grad_reduce": ("none" if world == 1 else "nccl-ddp" if args.impl == "baseline"
-                                       else f"tensor-parallel collectives: {comm_used}" if tp_mode else comm_used),
-                       "l2": "per-step working set (activations > 5 GB) exceeds the 126 MB L2; no flush needed"},
-            "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
-                    "ms_per_step": max(ms_e2e, wall_ms) / args.steps},
-            "gpu_launches": launches,
-            "clocks": clocks,
-            "final_loss": last,
-        }
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
+    if args.strict and out.get("fallback"):
+        return 3
     return 0
 
 

@@ -12,16 +12,19 @@
 //   (ld.acquire.sys).
 //
 // sb_allreduce_bf16 (the data-parallel gradient reduction; reference semantics: rank-ordered sum
-// then one multiply by 1/world, scirust-core/src/distributed.rs:96-167):
-//   phase 0  "my bucket is final"            -> wait for all peers
-//   reduce   rank r owns shard r of the bucket: pulls that shard from every rank's bucket with
-//            peer loads, adds in rank order 0..W-1 in fp32 (bf16 -> fp32 cast fused), scales by
-//            1/W (or any factor), rounds once, and pushes the result to every rank's output
-//            buffer (bf16 or fp32) with peer stores
-//   phase 1  "my pushes are done and I no longer read your bucket" -> last CTA waits for all
-//            peers before the kernel ends, so the next kernel in the stream may read the output
-//            and overwrite the bucket.
-// Because each element is reduced by exactly one rank and broadcast, all replicas receive
+// then one multiply by 1/world, scirust-core/src/distributed.rs:96-167). Reads only, no peer stores:
+//   phase 0   "my bucket is final"            -> every CTA waits for all peers (W lanes poll W flags)
+//   reduce    rank r owns shard r of the bucket: pulls that shard from every rank's bucket with
+//             peer loads, adds in rank order 0..W-1 in fp32 (bf16 -> fp32 cast fused), scales by
+//             1/W (or any factor), rounds once, and writes the result into shard r of its OWN output
+//   phase 1   the last CTA of the rank to finish its part announces "shard r of my output is reduced
+//             and I no longer read your bucket"; every CTA waits for all peers
+//   gather    pulls the W-1 other reduced shards from the peers' outputs into the local output
+//             (bf16 or fp32), eight 16-byte loads in flight per thread
+// No closing wait is needed: a peer overwrites its bucket only after its own kernel has passed
+// phase 1 (all ranks finished reading buckets), and it overwrites its output shard only in a later
+// call, after that call's phase 0, which every rank announces only once this kernel has ended on
+// its stream. Because each element is reduced by exactly one rank and copied, all replicas receive
 // identical bits, and the sum order is fixed: the result is bitwise repeatable at a fixed world.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -77,6 +80,28 @@ __device__ bool wait_flags(const uint32_t* flags, int W, uint32_t epoch, uint64_
   return true;
 }
 
+// Wait until flags[0..W-1] >= epoch with lanes 0..W-1 of the calling warp polling one flag each (W <= 16).
+// Every lane of the warp must call it; returns the same verdict on all lanes.
+__device__ bool wait_flags_warp(const uint32_t* flags, int W, uint32_t epoch, uint64_t limit_ns, int* status) {
+  const int lane = threadIdx.x & 31;
+  const uint64_t t0 = globaltimer_ns();
+  bool ok = true;
+  if (lane < W) {
+    uint32_t spins = 0;
+    while (static_cast<int32_t>(ld_acquire_sys(flags + lane) - epoch) < 0) {
+      if ((++spins & 0xff) == 0) {
+        if (globaltimer_ns() - t0 > limit_ns) {
+          atomicCAS(status, 0, ST_TIMEOUT_PEER);
+          ok = false;
+          break;
+        }
+        if (*reinterpret_cast<volatile int*>(status) != 0) { ok = false; break; }
+      }
+    }
+  }
+  return __all_sync(0xffffffffu, ok);
+}
+
 struct AllReduceParams {
   PeerTable t;
   int rank, W;
@@ -90,32 +115,39 @@ struct AllReduceParams {
   int* status;
 };
 
+__device__ __forceinline__ void accum8(float* acc, const uint4& v) {
+  acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x); acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
+  acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z); acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+}
+
 __global__ void __launch_bounds__(512)
 allreduce_bf16_kernel(const __grid_constant__ AllReduceParams p) {
   __shared__ int s_ok;
   const int W = p.W;
   uint32_t* my_flags = p.t.flags[p.rank] + static_cast<size_t>(p.slot) * SLOT_WORDS;
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < 32) {
     if (blockIdx.x == 0) {
       __threadfence_system();
-      for (int r = 0; r < W; ++r)
-        st_release_sys(p.t.flags[r] + static_cast<size_t>(p.slot) * SLOT_WORDS + p.rank, p.epoch);
+      if (threadIdx.x < W)
+        st_release_sys(p.t.flags[threadIdx.x] + static_cast<size_t>(p.slot) * SLOT_WORDS + p.rank, p.epoch);
     }
-    s_ok = wait_flags(my_flags, W, p.epoch, p.wait_ns, p.status) ? 1 : 0;
+    const bool w = wait_flags_warp(my_flags, W, p.epoch, p.wait_ns, p.status);
+    if (threadIdx.x == 0) s_ok = w ? 1 : 0;
   }
   __syncthreads();
-  const bool ok = s_ok != 0;
+  bool ok = s_ok != 0;
+  // shard r = [r*per, min(n, (r+1)*per)), per a multiple of 8 elements
+  const size_t per = ((p.n + W - 1) / W + 7) / 8 * 8;
+  const size_t gtid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
 
   if (ok) {
-    // shard r = [r*per, min(n, (r+1)*per)), per a multiple of 8 elements
-    const size_t per = ((p.n + W - 1) / W + 7) / 8 * 8;
     const size_t lo = min(p.n, per * p.rank);
     const size_t hi = min(p.n, lo + per);
     const size_t n8 = (hi - lo) / 8;
-    // two 16-byte vectors per thread and iteration: 2 W peer loads are in flight before the first add, which is
-    // what hides the NVLink round trip with a few dozen CTAs; each vector is summed in rank order
-    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-    for (size_t i0 = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < n8; i0 += 2 * stride) {
+    // two 16-byte vectors per thread and iteration: 2 W peer loads are in flight before the first add;
+    // each vector is summed in rank order
+    for (size_t i0 = gtid; i0 < n8; i0 += 2 * stride) {
       const size_t i1 = i0 + stride;
       const bool two = i1 < n8;
       const size_t e0 = lo + i0 * 8, e1 = lo + (two ? i1 : i0) * 8;
@@ -136,16 +168,8 @@ allreduce_bf16_kernel(const __grid_constant__ AllReduceParams p) {
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
           if (r0 + r < W) {
-            accs[0][0] += bf16_lo(v0[r].x); accs[0][1] += bf16_hi(v0[r].x);
-            accs[0][2] += bf16_lo(v0[r].y); accs[0][3] += bf16_hi(v0[r].y);
-            accs[0][4] += bf16_lo(v0[r].z); accs[0][5] += bf16_hi(v0[r].z);
-            accs[0][6] += bf16_lo(v0[r].w); accs[0][7] += bf16_hi(v0[r].w);
-            if (two) {
-              accs[1][0] += bf16_lo(v1[r].x); accs[1][1] += bf16_hi(v1[r].x);
-              accs[1][2] += bf16_lo(v1[r].y); accs[1][3] += bf16_hi(v1[r].y);
-              accs[1][4] += bf16_lo(v1[r].z); accs[1][5] += bf16_hi(v1[r].z);
-              accs[1][6] += bf16_lo(v1[r].w); accs[1][7] += bf16_hi(v1[r].w);
-            }
+            accum8(accs[0], v0[r]);
+            if (two) accum8(accs[1], v1[r]);
           }
         }
       }
@@ -155,44 +179,63 @@ allreduce_bf16_kernel(const __grid_constant__ AllReduceParams p) {
         const size_t e = u == 0 ? e0 : e1;
         float acc[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = accs[u][j];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] *= p.scale;
+        for (int j = 0; j < 8; ++j) acc[j] = accs[u][j] * p.scale;
         if (p.out_fp32) {
-          const uint4 a = make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]),
-                                     __float_as_uint(acc[3]));
-          const uint4 b = make_uint4(__float_as_uint(acc[4]), __float_as_uint(acc[5]), __float_as_uint(acc[6]),
-                                     __float_as_uint(acc[7]));
-          for (int r = 0; r < W; ++r) {
-            const int dst = (p.rank + r) % W;  // spread the pushes over the peers
-            float* o = static_cast<float*>(p.t.out[dst]) + e;
-            *reinterpret_cast<uint4*>(o) = a;
-            *reinterpret_cast<uint4*>(o + 4) = b;
-          }
+          float* o = static_cast<float*>(p.t.out[p.rank]) + e;
+          *reinterpret_cast<uint4*>(o) = make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]),
+                                                    __float_as_uint(acc[2]), __float_as_uint(acc[3]));
+          *reinterpret_cast<uint4*>(o + 4) = make_uint4(__float_as_uint(acc[4]), __float_as_uint(acc[5]),
+                                                        __float_as_uint(acc[6]), __float_as_uint(acc[7]));
         } else {
-          const uint4 o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
-                                     pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
-          for (int r = 0; r < W; ++r) {
-            const int dst = (p.rank + r) % W;
-            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.t.out[dst]) + e) = o;
-          }
+          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.t.out[p.rank]) + e) =
+              make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                         pack_bf16x2(acc[6], acc[7]));
         }
       }
     }
   }
-  // completion: the last CTA to finish announces phase 1 and waits for every peer's phase 1.
+  // the last CTA of this rank to finish its part of the shard tells every peer that the shard is reduced
   __threadfence_system();
   __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned int prev = atomicAdd(p.cta_counter, 1u);
+  if (threadIdx.x < 32) {
+    unsigned int prev = 0;
+    if (threadIdx.x == 0) prev = atomicAdd(p.cta_counter, 1u);
+    prev = __shfl_sync(0xffffffffu, prev, 0);
     if (prev == gridDim.x - 1) {
-      *p.cta_counter = 0;  // ready for the next call on this stream
+      if (threadIdx.x == 0) *p.cta_counter = 0;  // ready for the next call on this stream
       if (ok) {
         __threadfence_system();
-        for (int r = 0; r < W; ++r)
-          st_release_sys(p.t.flags[r] + static_cast<size_t>(p.slot) * SLOT_WORDS + MAX_WORLD + p.rank, p.epoch);
-        wait_flags(my_flags + MAX_WORLD, W, p.epoch, p.wait_ns, p.status);
+        if (threadIdx.x < W)
+          st_release_sys(p.t.flags[threadIdx.x] + static_cast<size_t>(p.slot) * SLOT_WORDS + MAX_WORLD + p.rank,
+                         p.epoch);
       }
+    }
+    if (ok) {
+      const bool w = wait_flags_warp(my_flags + MAX_WORLD, W, p.epoch, p.wait_ns, p.status);
+      if (threadIdx.x == 0) s_ok = w ? 1 : 0;
+    }
+  }
+  __syncthreads();
+  ok = ok && s_ok != 0;
+  if (!ok) return;
+
+  // gather: copy the other ranks' reduced shards, 16-byte words, eight loads in flight per thread
+  const size_t esz = p.out_fp32 ? 4 : 2;
+  uint4* mine = static_cast<uint4*>(p.t.out[p.rank]);
+  for (int q0 = 1; q0 < W; ++q0) {
+    const int q = (p.rank + q0) % W;          // start with the next rank so the peers' links are spread
+    const size_t lo = min(p.n, per * q), hi = min(p.n, lo + per);
+    const size_t w0 = lo * esz / 16, nw = (hi - lo) * esz / 16;
+    const uint4* src = static_cast<const uint4*>(p.t.out[q]) + w0;
+    uint4* dst = mine + w0;
+    for (size_t i = gtid; i < nw; i += 8 * stride) {
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (i + u * stride < nw) v[u] = ld_peer_v4(src + i + u * stride);
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (i + u * stride < nw) dst[i + u * stride] = v[u];
     }
   }
 }
@@ -338,6 +381,8 @@ extern "C" int sb_allreduce_bf16(void* const* in_ptrs, void* const* out_ptrs, vo
                                  int W, size_t n_elems, float scale, uint32_t epoch, int slot, int out_fp32,
                                  unsigned int* cta_counter, int n_ctas, int wait_ms, int* status, void* stream) {
   if (W < 1 || W > MAX_WORLD || rank < 0 || rank >= W || (n_elems & 7) || n_ctas < 1) return SB_ERR_ARG;
+  if (cta_counter == nullptr || status == nullptr || in_ptrs == nullptr || out_ptrs == nullptr || flag_ptrs == nullptr)
+    return SB_ERR_ARG;
   AllReduceParams p;
   for (int r = 0; r < W; ++r) {
     if ((reinterpret_cast<uintptr_t>(in_ptrs[r]) & 15) || (reinterpret_cast<uintptr_t>(out_ptrs[r]) & 15))
@@ -366,6 +411,7 @@ extern "C" int sb_small_collective(void* const* in_ptrs, void* const* flag_ptrs,
   if (W < 1 || W > MAX_WORLD || rank < 0 || rank >= W || n_ctas < 1 || mode < 0 || mode > 1) return SB_ERR_ARG;
   if (mode == 0 && (n & 7)) return SB_ERR_ARG;
   if (mode == 1 && rows < 1) return SB_ERR_ARG;
+  if (cta_counter == nullptr || status == nullptr || epoch_word == nullptr || out == nullptr) return SB_ERR_ARG;
   SmallCollParams p;
   for (int r = 0; r < W; ++r) {
     if (reinterpret_cast<uintptr_t>(in_ptrs[r]) & 15) return SB_ERR_ALIGN;

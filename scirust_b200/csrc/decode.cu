@@ -1228,13 +1228,19 @@ decode_attn_kernel(const __grid_constant__ DecodeAttnParams p) {
 }
 
 // ---------------------------------------------------------------------------
-// Arg-max over logits rows with the reference's tie rule (first maximum wins; a NaN never wins
-// against a number because `v > best` is false for NaN, decode.rs:107-114), two stages.
-// Stage 1: each CTA scans a slab of `cols_per_cta` columns of one row -> (value, index).
-// Stage 2: one CTA per row picks the best slab result, lower index on ties, and writes the token
-// to `out_tokens[row]` (int64, the device-side feedback buffer) and optionally appends it to
-// `generated[row, step]`.
+// Arg-max over logits rows with the rule of the reference's greedy loop (`best = row[0]; if v > best`,
+// scirust-cuda/src/decode.rs:107-114): a NaN in column 0 makes token 0 win outright; any other NaN is
+// skipped explicitly (`v != v`), never left to how a comparison with NaN folds; among equal maxima the
+// lowest index wins. Two stages.
+// Stage 1: each CTA scans a slab of `cols_per_cta` columns of one row -> (value, index), index
+// 0x7fffffff when the slab holds no number.
+// Stage 2: one thread per row picks the best slab result and writes the token to `out_tokens[row]`
+// (int64, the device-side feedback buffer) and optionally appends it to `generated[row, step]`.
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ bool argmax_better(float v, int i, float best, int bi) {
+  // both v and best are numbers here (NaN never enters); -inf with a real index beats the empty sentinel
+  return v > best || (v == best && i < bi);
+}
 __global__ void argmax_partial_kernel(const float* __restrict__ logits, int V, int cols_per_cta,
                                       float* __restrict__ pval, int* __restrict__ pidx) {
   __shared__ float sv[256];
@@ -1243,23 +1249,20 @@ __global__ void argmax_partial_kernel(const float* __restrict__ logits, int V, i
   const int c0 = slab * cols_per_cta, c1 = min(V, c0 + cols_per_cta);
   const float* lr = logits + static_cast<size_t>(row) * V;
   float best = -INFINITY;
-  int bi = c0;
-  bool have = false;
+  int bi = 0x7fffffff;
   for (int c = c0 + threadIdx.x; c < c1; c += 256) {
     const float v = lr[c];
-    if (!have) { best = v; bi = c; have = true; }
-    else if (v > best) { best = v; bi = c; }
+    if (v != v) continue;
+    if (argmax_better(v, c, best, bi)) { best = v; bi = c; }
   }
-  sv[threadIdx.x] = have ? best : -INFINITY;
-  si[threadIdx.x] = have ? bi : 0x7fffffff;
+  sv[threadIdx.x] = best;
+  si[threadIdx.x] = bi;
   __syncthreads();
   for (int s = 128; s > 0; s >>= 1) {
     if (threadIdx.x < s) {
-      const float a = sv[threadIdx.x], bb = sv[threadIdx.x + s];
-      const int ia = si[threadIdx.x], ib = si[threadIdx.x + s];
-      // keep the larger value; on equal values (or NaN on either side) keep the lower index
-      const bool take_b = (bb > a) || (!(a > bb) && !(bb > a) && ib < ia);
-      if (take_b) { sv[threadIdx.x] = bb; si[threadIdx.x] = ib; }
+      const float bb = sv[threadIdx.x + s];
+      const int ib = si[threadIdx.x + s];
+      if (argmax_better(bb, ib, sv[threadIdx.x], si[threadIdx.x])) { sv[threadIdx.x] = bb; si[threadIdx.x] = ib; }
     }
     __syncthreads();
   }
@@ -1268,19 +1271,20 @@ __global__ void argmax_partial_kernel(const float* __restrict__ logits, int V, i
     pidx[row * gridDim.x + slab] = si[0];
   }
 }
-__global__ void argmax_final_kernel(const float* __restrict__ pval, const int* __restrict__ pidx, int n_slabs,
-                                    int64_t* __restrict__ out_tokens, int64_t* __restrict__ generated,
-                                    int gen_stride, int step) {
+__global__ void argmax_final_kernel(const float* __restrict__ logits, int V, const float* __restrict__ pval,
+                                    const int* __restrict__ pidx, int n_slabs, int64_t* __restrict__ out_tokens,
+                                    int64_t* __restrict__ generated, int gen_stride, int step) {
   const int row = blockIdx.x;
   if (threadIdx.x != 0) return;
-  float best = pval[row * n_slabs];
-  int bi = pidx[row * n_slabs];
-  for (int s = 1; s < n_slabs; ++s) {
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int s = 0; s < n_slabs; ++s) {
     const float v = pval[row * n_slabs + s];
     const int i = pidx[row * n_slabs + s];
-    if (v > best || (!(best > v) && !(v > best) && i < bi)) { best = v; bi = i; }
+    if (argmax_better(v, i, best, bi)) { best = v; bi = i; }
   }
-  if (bi == 0x7fffffff) bi = 0;
+  const float first = logits[static_cast<size_t>(row) * V];
+  if (first != first || bi == 0x7fffffff) bi = 0;   // NaN in column 0, or no number in the row
   out_tokens[row] = bi;
   if (generated) generated[static_cast<size_t>(row) * gen_stride + step] = bi;
 }
@@ -1532,7 +1536,7 @@ extern "C" int sb_argmax(const float* logits, int rows, int V, float* pval, int*
   const int slabs = (V + cpc - 1) / cpc;
   argmax_partial_kernel<<<dim3(slabs, rows), 256, 0, STREAM>>>(logits, V, cpc, pval, pidx);
   if (cudaGetLastError() != cudaSuccess) return SB_ERR_LAUNCH;
-  argmax_final_kernel<<<rows, 32, 0, STREAM>>>(pval, pidx, slabs, out_tokens, generated, gen_stride, step);
+  argmax_final_kernel<<<rows, 32, 0, STREAM>>>(logits, V, pval, pidx, slabs, out_tokens, generated, gen_stride, step);
   CHECK_LAUNCH();
 }
 

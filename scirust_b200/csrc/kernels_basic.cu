@@ -530,13 +530,17 @@ __device__ __forceinline__ float ld_as_float<__nv_bfloat16>(const __nv_bfloat16*
 template <>
 __device__ __forceinline__ float ld_as_float<float>(const float* p, size_t i) { return p[i]; }
 
+// Elements summed by one block of sumsq_partial_kernel (= one partial): 256 threads x 16 strided reads.
+// sb_sumsq and sb_sumsq_no_alloc both size their launch from this one constant.
+constexpr size_t kSumsqElemsPerPartial = 4096;
+
 template <typename T>
 __global__ void sumsq_partial_kernel(const T* __restrict__ g, size_t n, float* __restrict__ partials) {
   __shared__ float red[8];
   float v = 0.f;
-  const size_t base = static_cast<size_t>(blockIdx.x) * 4096;
+  const size_t base = static_cast<size_t>(blockIdx.x) * kSumsqElemsPerPartial;
 #pragma unroll 4
-  for (int k = 0; k < 16; ++k) {
+  for (int k = 0; k < static_cast<int>(kSumsqElemsPerPartial / 256); ++k) {
     const size_t i = base + k * 256 + threadIdx.x;
     if (i < n) {
       const float x = ld_as_float<T>(g, i);
@@ -813,7 +817,7 @@ extern "C" int sb_ce_shard_grad(const void* logits, const int64_t* targets, cons
 extern "C" int sb_sumsq(const void* g, size_t n, int is_bf16, float* partials, float* out, int accumulate,
                         void* stream) {
   if (n == 0) return SB_ERR_ARG;
-  const size_t nb = (n + 4095) / 4096;
+  const size_t nb = (n + kSumsqElemsPerPartial - 1) / kSumsqElemsPerPartial;
   if (nb > 0x7fffffff) return SB_ERR_TOO_LARGE;
   if (is_bf16)
     sumsq_partial_kernel<__nv_bfloat16><<<static_cast<unsigned>(nb), 256, 0, STREAM>>>(
@@ -875,12 +879,57 @@ extern "C" int sb_cast(const void* in, void* out, size_t n, int to_bf16, float s
   CHECK_LAUNCH();
 }
 
+// Multi-tensor cast: up to MULTI_CAST_MAX fp32 tensors are rounded to bf16 into slices of one flat
+// buffer in a single launch (a data-parallel bucket's gradients). blockIdx.y selects the tensor.
+constexpr int MULTI_CAST_MAX = 96;
+struct MultiCastParams {
+  const float* src[MULTI_CAST_MAX];
+  unsigned long long dst_off[MULTI_CAST_MAX];   // element offset into dst
+  unsigned long long n[MULTI_CAST_MAX];
+};
+__global__ void multi_cast_f32_bf16_kernel(const __grid_constant__ MultiCastParams p, __nv_bfloat16* __restrict__ dst,
+                                           int accumulate) {
+  const int t = blockIdx.y;
+  const float* __restrict__ s = p.src[t];
+  __nv_bfloat16* __restrict__ d = dst + p.dst_off[t];
+  const size_t n = p.n[t];
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float v = s[i];
+    if (accumulate) v += __bfloat162float(d[i]);
+    d[i] = __float2bfloat16_rn(v);
+  }
+}
+
+// srcs / dst_offs / ns: host arrays of `count` entries (count <= 96). dst: bf16 flat buffer.
+extern "C" int sb_multi_cast_f32_bf16(const void* const* srcs, const unsigned long long* dst_offs,
+                                      const unsigned long long* ns, int count, void* dst, int accumulate,
+                                      void* stream) {
+  if (count < 1 || count > MULTI_CAST_MAX || dst == nullptr) return SB_ERR_ARG;
+  MultiCastParams p;
+  unsigned long long nmax = 0;
+  for (int i = 0; i < count; ++i) {
+    if (srcs[i] == nullptr) return SB_ERR_ARG;
+    p.src[i] = static_cast<const float*>(srcs[i]);
+    p.dst_off[i] = dst_offs[i];
+    p.n[i] = ns[i];
+    if (ns[i] > nmax) nmax = ns[i];
+  }
+  if (nmax == 0) return SB_ERR_ARG;
+  unsigned bx = static_cast<unsigned>((nmax + 255) / 256);
+  if (bx > 1024) bx = 1024;
+  multi_cast_f32_bf16_kernel<<<dim3(bx, count), 256, 0, STREAM>>>(p, static_cast<__nv_bfloat16*>(dst), accumulate);
+  CHECK_LAUNCH();
+}
+
 // ---------------------------------------------------------------------------
 // sb_sumsq_no_alloc: the sum of squares for callers that cannot allocate (see
 // sumsq_no_alloc.h). Same kernels and launch shape as sb_sumsq; the per-block partials go to
 // an array that is part of the library image instead of a caller-provided buffer.
 // ---------------------------------------------------------------------------
 #include "sumsq_no_alloc.h"
+static_assert(SB_SUMSQ_NO_ALLOC_ELEMS_PER_PARTIAL == kSumsqElemsPerPartial,
+              "the header's limit must describe the partial size the kernels use");
 
 static __device__ __align__(256) float g_sumsq_no_alloc_scratch[SB_SUMSQ_NO_ALLOC_MAX_PARTIALS];
 
@@ -901,7 +950,7 @@ extern "C" int sb_sumsq_no_alloc(const void* g, size_t n, int is_bf16, float* ou
     scratch = static_cast<float*>(p);
     g_sumsq_no_alloc_ptr[dev] = scratch;
   }
-  const size_t nb = (n + SB_SUMSQ_NO_ALLOC_ELEMS_PER_PARTIAL - 1) / SB_SUMSQ_NO_ALLOC_ELEMS_PER_PARTIAL;
+  const size_t nb = (n + kSumsqElemsPerPartial - 1) / kSumsqElemsPerPartial;
   if (is_bf16)
     sumsq_partial_kernel<__nv_bfloat16><<<static_cast<unsigned>(nb), 256, 0, STREAM>>>(
         static_cast<const __nv_bfloat16*>(g), n, scratch);

@@ -265,6 +265,10 @@ class InferenceEngine:
             if self.cache.owned[b]:
                 self.cache.release(b)
         logits = self.prefill(prompts)
+        if self.dev.type == "cuda":
+            # benchmarks time the decode steps from here (prefill and its arg-max are behind this event)
+            self.prefill_done = torch.cuda.Event(enable_timing=True)
+            self.prefill_done.record()
         for b in range(B):
             self.cache.reserve(b, P + max_new)
         self.cache.commit()

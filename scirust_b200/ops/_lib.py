@@ -51,6 +51,15 @@ class NativeError(RuntimeError):
     pass
 
 
+class CollectiveTimeout(NativeError):
+    """A bounded wait inside a kernel (peer flag, mbarrier) ran out; the data that kernel was to produce is
+    incomplete, so the step that contained it must not be trusted."""
+
+    def __init__(self, code: int):
+        super().__init__(f"device kernel reported: {STATUS.get(code, code)}")
+        self.code = code
+
+
 def _load(path: Path, builder) -> C.CDLL:
     if not path.exists():
         builder()
@@ -128,4 +137,37 @@ def check_status(device=None) -> None:
     code = int(w.item())
     if code != 0:
         w.zero_()
-        raise NativeError(f"device kernel reported: {STATUS.get(code, code)}")
+        raise CollectiveTimeout(code)
+
+
+class DeferredStatus:
+    """Reads the status word without stalling the stream: ``poll()`` queues a 4-byte copy into pinned host
+    memory behind the work already issued and examines the copy queued by the PREVIOUS ``poll()`` (which has
+    normally landed by then; otherwise its event is waited for). A non-zero code raises ``CollectiveTimeout``
+    one call late at most, before another optimizer step can build on a partial reduction."""
+
+    def __init__(self, device=None):
+        self.word = status_word(device)
+        self.host = [torch.zeros(1, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.events = [None, None]
+        self.turn = 0
+
+    def poll(self) -> None:
+        cur, prev = self.turn, self.turn ^ 1
+        if self.events[prev] is not None:
+            self.events[prev].synchronize()
+            code = int(self.host[prev][0])
+            if code != 0:
+                self.events = [None, None]
+                self.word.zero_()
+                raise CollectiveTimeout(code)
+        self.host[cur].copy_(self.word, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[cur] = ev
+        self.turn = prev
+
+    def flush(self) -> None:
+        """Synchronising check of everything issued so far."""
+        self.events = [None, None]
+        check_status(self.word.device)

@@ -331,3 +331,29 @@ def optim_step(p, m, v, grad, p_bf16, *, lr, beta1=0.9, beta2=0.999, eps=1e-8, w
               float(weight_decay), float(bc1), float(bc2), _lib.ptr(grad_sumsq), float(max_grad_norm),
               float(grad_scale), MODE[mode], _lib.stream())
     _count()
+
+
+_lib.register("sb_multi_cast_f32_bf16", [_lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.vp, _lib.i32, _lib.vp])
+
+
+def multi_cast_to_bf16(srcs, dst, offsets, accumulate: bool = False):
+    """Round fp32 tensors ``srcs[i]`` into ``dst[offsets[i] : offsets[i] + srcs[i].numel()]`` (flat bf16) with one
+    launch per 96 tensors; ``accumulate`` adds to what the slice holds (fp32 add, one rounding)."""
+    if not dst.is_cuda:
+        for s_, o in zip(srcs, offsets):
+            sl = dst[o:o + s_.numel()]
+            v = s_.reshape(-1).float()
+            sl.copy_((sl.float() + v) if accumulate else v)
+        return
+    import ctypes as C
+    for c0 in range(0, len(srcs), 96):
+        chunk = [t if t.is_contiguous() else t.contiguous() for t in srcs[c0:c0 + 96]]
+        for t in chunk:
+            if t.dtype != torch.float32:
+                raise TypeError("multi_cast_to_bf16 takes fp32 sources")
+        k = len(chunk)
+        ps = (C.c_void_p * k)(*[t.data_ptr() for t in chunk])
+        os_ = (C.c_ulonglong * k)(*[int(o) for o in offsets[c0:c0 + 96]])
+        ns = (C.c_ulonglong * k)(*[t.numel() for t in chunk])
+        _lib.call("sb_multi_cast_f32_bf16", ps, os_, ns, k, dst.data_ptr(), int(accumulate), _lib.stream())
+        _count()

@@ -4,7 +4,6 @@ iterations). Also the small fixed workloads that the committed profiler summarie
     python -m scirust_b200.ops.bench_kernels gemm --form nt --m 8192 --n 8192 --k 8192
     python -m scirust_b200.ops.bench_kernels attention --batch 8 --seq 2048 --heads 16 --kv-heads 4 --dh 64
     python -m scirust_b200.ops.bench_kernels attention_bwd --batch 1 --seq 2048
-    python -m scirust_b200.ops.bench_kernels umma        # cycles per tcgen05.mma for each (M, N)
 """
 from __future__ import annotations
 
@@ -45,7 +44,7 @@ def _rand(shape, seed):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "gemm_model", "attention", "attention_bwd", "rmsnorm", "ce", "adamw", "umma", "gemv",
+    ap.add_argument("kernel", choices=["gemm", "gemm_model", "attention", "attention_bwd", "rmsnorm", "ce", "adamw", "gemv",
                                       "decode_attn", "sampler"])
     ap.add_argument("--int8", action="store_true", help="gemv: per-channel int8 weights")
     ap.add_argument("--ctx", type=int, default=4096, help="decode_attn: cached positions per sequence")
@@ -106,27 +105,6 @@ def main(argv=None):
                     ml = _time(lib, a.iters, a.warmup, flush)
                     row.update(cublas_ms=round(ml, 4), cublas_tflops=round(fl / ml / 1e9, 1))
                 rows.append(row)
-        out["rows"] = rows
-    elif a.kernel == "umma":
-        # one CTA issues 4 * iters instructions of one shape into one accumulator; SM cycles per instruction
-        _lib.register("sb_umma_probe", [_lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.vp, _lib.vp, _lib.vp])
-        cyc = torch.zeros(2, dtype=torch.int64, device="cuda")
-        rows = []
-        n_inst = 4 * 2000
-        for b_mn in (0, 1):
-            for M in (128, 64):
-                for N in (64, 128, 256):
-                    best = None
-                    for _ in range(3):
-                        _lib.call("sb_umma_probe", M, N, b_mn, 2000, cyc.data_ptr(),
-                                  _lib.status_word(cyc.device).data_ptr(), _lib.stream())
-                        torch.cuda.synchronize()
-                        _lib.check_status()
-                        c = int(cyc[0].item())
-                        best = c if best is None else min(best, c)
-                    per = best / n_inst
-                    rows.append({"m": M, "n": N, "k": 16, "b_major": "mn" if b_mn else "k",
-                                 "cycles_per_mma": round(per, 1), "fma_per_cycle": round(M * N * 16 / per, 1)})
         out["rows"] = rows
     elif a.kernel == "gemv":
         # batch-1 decode product: W [K, N] streamed once (default 14336 x 4096 bf16 = 117 MB, larger than L2)

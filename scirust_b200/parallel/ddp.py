@@ -3,7 +3,7 @@
 ``FlatDataParallel`` flattens the module's fp32 parameters into one master buffer (parameters become
 views), mirrors the gradient as a flat bf16 buffer in symmetric (peer-mapped) memory, and registers
 post-accumulate hooks: as each parameter's gradient appears during backward it is cast into its
-slice of the bf16 buffer, and when the last gradient of a bucket has arrived the bucket's fused
+slice of the bf16 buffer (one multi-tensor launch per bucket), and when the last gradient of a bucket has arrived the bucket's fused
 all-reduce (rank-ordered fp32 sum x 1/world, fp32 output; csrc/comm.cu) is launched on a
 communication stream, overlapping the rest of backward. ``step()`` joins the streams and applies
 one fused optimizer launch (Adam / AdamW / SGD-momentum; csrc/kernels_basic.cu) over the flat
@@ -27,9 +27,21 @@ BF = torch.bfloat16
 
 
 class FlatDataParallel:
+    """Gradient bookkeeping, per step:
+
+    * a parameter whose hook did not fire (unused branch, frozen head) contributes a ZERO gradient: its
+      slice of the bf16 buffer is cleared in ``step()`` before the bucket is reduced;
+    * a second ``backward()`` before ``step()`` (gradient accumulation) ADDS to the slice (fp32 add, one
+      rounding); a bucket that had already been reduced is reduced again in ``step()``. Wrap all but the
+      last micro-batch in ``no_sync()`` to avoid the wasted early reductions;
+    * a bucket's gradients are cast into the flat buffer by one multi-tensor launch when the bucket is
+      complete, not by one copy per parameter.
+    """
+
     def __init__(self, module: torch.nn.Module, group=None, optimizer: str = "adam", lr: float = 1e-3,
                  momentum: float = 0.9, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0,
-                 comm: str = "fused", bucket_elems: int = 4 << 20, overlap: bool = True, n_ctas: int = 16):
+                 comm: str = "fused", bucket_elems: int = 4 << 20, overlap: bool = True, n_ctas: int = 32,
+                 max_buckets: int = 192):
         self.module, self.group = module, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.mode = {"adam": "adam", "adamw": "adamw", "sgd": "sgd"}[optimizer]
@@ -44,6 +56,8 @@ class FlatDataParallel:
             offs.append(off)
             off += (p.numel() + 7) // 8 * 8
         self.n = off
+        # every bucket takes a flag slot and a counter word of the fused reducer: grow the buckets of a large model
+        bucket_elems = max(bucket_elems, -(-off // max_buckets))
         self.master = torch.zeros(off, dtype=torch.float32, device=dev)
         for p, o in zip(params, offs):
             self.master[o:o + p.numel()].copy_(p.detach().reshape(-1))
@@ -77,11 +91,11 @@ class FlatDataParallel:
             lo = min(offs[i] for i in idxs)
             hi = max(offs[i] + (params[i].numel() + 7) // 8 * 8 for i in idxs)
             self.bucket_range.append((lo, hi - lo))
-        self.pending = [0] * len(self.buckets)
         self.overlap = overlap and self.world > 1
         self.comm_stream = torch.cuda.Stream(device=dev) if dev.type == "cuda" else None
-        self.epoch = 0
-        self._launched = set()
+        self._sync = True
+        # a peer-flag time-out inside the reducer leaves a partial sum: surface it one step late at most
+        self._status = _lib.DeferredStatus(dev) if (self.comm == "fused" and dev.type == "cuda") else None
         for i, p in enumerate(params):
             p.register_post_accumulate_grad_hook(self._make_hook(i))
         self._reset()
@@ -89,18 +103,61 @@ class FlatDataParallel:
     def _reset(self):
         self.pending = [len(b) for b in self.buckets]
         self._launched = set()
-        if self.comm == "fused":
-            self.epoch = self.ar.next_epoch()
+        self._fired = [False] * len(self.params)      # hook fired since the last step()
+        self._held = [[] for _ in self.buckets]       # (param index, fp32 gradient) waiting for the bucket's cast
+        self._dirty = [False] * len(self.buckets)     # slice holds gradients of an earlier backward of this step
+
+    class _NoSync:
+        def __init__(self, dp):
+            self.dp = dp
+
+        def __enter__(self):
+            self.prev, self.dp._sync = self.dp._sync, False
+
+        def __exit__(self, *exc):
+            self.dp._sync = self.prev
+
+    def no_sync(self):
+        """Context manager: backward passes inside it only accumulate; nothing is reduced until ``step()``
+        (or until a later backward outside the context completes a bucket)."""
+        return FlatDataParallel._NoSync(self)
+
+    def _cast_bucket(self, b):
+        held = self._held[b]
+        if not held:
+            return
+        if self._dirty[b] and b in self._launched and self.comm_stream is not None:
+            # an earlier reduction of this bucket may still be reading the slice
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+        fresh = [(i, g) for i, g, acc in held if not acc]
+        again = [(i, g) for i, g, acc in held if acc]
+        for items, acc in ((fresh, False), (again, True)):
+            if items:
+                ops.multi_cast_to_bf16([g.reshape(-1) for _, g in items], self.grad16,
+                                       [self.offs[i] for i, _ in items], accumulate=acc)
+        self._held[b] = []
 
     def _make_hook(self, i):
         def hook(p):
-            o = self.offs[i]
-            self.grad16[o:o + p.numel()].copy_(p.grad.reshape(-1))     # fp32 -> bf16 cast into the bucket
-            p.grad = None
             b = self.bucket_of[i]
+            g = p.grad
+            p.grad = None
+            if g.dtype != torch.float32:
+                g = g.float()
+            if self._fired[i]:
+                # a second backward before step(): add to the slice, and reduce the bucket (again) in step()
+                self._dirty[b] = True
+                self._held[b].append((i, g, True))
+                self._cast_bucket(b)
+                self._launched.discard(b)
+                return
+            self._fired[i] = True
+            self._held[b].append((i, g, False))
             self.pending[b] -= 1
-            if self.pending[b] == 0 and self.overlap:
-                self._reduce_bucket(b, async_=True)
+            if self.pending[b] == 0:
+                self._cast_bucket(b)
+                if self.overlap and self._sync:
+                    self._reduce_bucket(b, async_=True)
         return hook
 
     def _reduce_bucket(self, b, async_):
@@ -111,9 +168,9 @@ class FlatDataParallel:
                 ev = torch.cuda.Event()
                 ev.record()
                 self.comm_stream.wait_event(ev)
-                self.ar.reduce(lo, n, 1.0 / self.world, self.epoch, stream=self.comm_stream)
+                self.ar.reduce(lo, n, 1.0 / self.world, stream=self.comm_stream)
             else:
-                self.ar.reduce(lo, n, 1.0 / self.world, self.epoch)
+                self.ar.reduce(lo, n, 1.0 / self.world)
         elif self.comm == "nccl":
             t = self.grad16[lo:lo + n]
             dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
@@ -125,6 +182,13 @@ class FlatDataParallel:
 
     def step(self):
         """Finish the gradient reduction and apply the optimizer to every parameter."""
+        for b, idxs in enumerate(self.buckets):
+            if self.pending[b] > 0:
+                # some parameters of this bucket received no gradient in this step: theirs is zero
+                self._cast_bucket(b)
+                for i in idxs:
+                    if not self._fired[i]:
+                        self.grad16[self.offs[i]:self.offs[i] + self.params[i].numel()].zero_()
         if self.world > 1:
             for b in range(len(self.buckets)):
                 if b not in self._launched:
@@ -141,6 +205,8 @@ class FlatDataParallel:
         ops.optim_step(self.master, self.m, self.v, grad, None, lr=self.lr, beta1=b1, beta2=b2, eps=self.eps,
                        weight_decay=self.wd, step=self.step_count, mode=self.mode)
         self._reset()
+        if self._status is not None:
+            self._status.poll()
 
     def close(self):
         if self.region is not None:

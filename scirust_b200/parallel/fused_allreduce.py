@@ -3,8 +3,8 @@
 The model's flat bf16 gradient buffer is re-homed into symmetric memory, so weight-gradient
 GEMMs write straight into a buffer every peer can read. After backward (or per bucket, as the
 blocks finish, on a side stream) one kernel per bucket pulls the peers' shards over NVLink, sums
-them in rank order in fp32, scales by 1/world and pushes the rounded result to every rank's
-``reduced`` buffer, which the optimizer then consumes. Reduction order is fixed and every rank
+them in rank order in fp32, scales by 1/world, writes the rounded shard into its own ``reduced``
+buffer and then pulls the other ranks' reduced shards, so the optimizer finds the whole bucket there. Reduction order is fixed and every rank
 receives identical bits.
 """
 from __future__ import annotations
@@ -16,7 +16,7 @@ import torch.distributed as dist
 
 from ..ops import _lib
 from ..ops import gemm as _g
-from .symm import SymmetricRegion
+from .symm import FLAG_SLOTS, SymmetricRegion
 
 import ctypes as C
 
@@ -33,9 +33,11 @@ class FusedAllReduce:
         self.region, self.src, self.dst = region, src, dst
         self.n_ctas, self.wait_ms = n_ctas, wait_ms
         self.epoch = 0
-        self.counters = torch.zeros(64, dtype=torch.int32, device=src.device)
+        # one CTA-counter word per bucket; a bucket also takes one flag slot, so the two run out together
+        self.counters = torch.zeros(FLAG_SLOTS, dtype=torch.int32, device=src.device)
         self.flag_ptrs = region.flag_ptrs()
         self._buckets = {}
+        self._epochs = {}
 
     def bucket(self, start: int, n: int):
         key = (start, n)
@@ -43,6 +45,8 @@ class FusedAllReduce:
         if b is None:
             if start % 8 or n % 8:
                 raise ValueError("bucket bounds must be multiples of 8 elements")
+            if len(self._buckets) >= self.counters.numel():
+                raise RuntimeError(f"FusedAllReduce: more than {self.counters.numel()} buckets; use larger buckets")
             slot = self.region.new_slot()
             b = (self.region.peer_ptrs(self.src[start:start + n]), self.region.peer_ptrs(self.dst[start:start + n]),
                  slot, len(self._buckets))
@@ -53,13 +57,20 @@ class FusedAllReduce:
         self.epoch += 1
         return self.epoch
 
-    def reduce(self, start: int, n: int, scale: float, epoch: int, stream=None):
+    def reduce(self, start: int, n: int, scale: float, epoch: int | None = None, stream=None):
+        """Reduce ``src[start:start+n]`` into ``dst[start:start+n]`` on every rank. Each bucket owns a flag
+        slot, and its calls are numbered by a per-bucket counter that advances identically on every rank
+        (all ranks issue the same sequence of calls), so a bucket may be reduced any number of times per step.
+        ``epoch`` overrides the counter (it must grow from call to call of the bucket)."""
         in_p, out_p, slot, idx = self.bucket(start, n)
+        if epoch is None:
+            epoch = self._epochs.get(idx, 0) + 1
+        self._epochs[idx] = epoch
         r = self.region
         st = _lib.status_word(self.src.device)
         s = _lib.stream() if stream is None else stream.cuda_stream
         _lib.call("sb_allreduce_bf16", in_p, out_p, self.flag_ptrs, r.rank, r.world, n, float(scale), epoch, slot,
-                  int(self.dst.dtype == torch.float32), self.counters[idx:].data_ptr(), self.n_ctas, self.wait_ms,
+                  int(self.dst.dtype == torch.float32), self.counters.data_ptr() + 4 * idx, self.n_ctas, self.wait_ms,
                   st.data_ptr(), s)
         _g.launch_count += 1
 

@@ -31,6 +31,7 @@ class TrainerConfig:
     max_grad_norm: float = 1.0
     telemetry_interval: int = 0   # 0 = never read the loss back unless asked
     optimizer: str = "adamw"
+    status_interval: int = 1      # multi-GPU runs: look at the kernels' status word every N steps (0 = never)
 
 
 class Trainer:
@@ -53,6 +54,13 @@ class Trainer:
         self.grad_reducer = grad_reducer
         self.last_loss = None
         self._dev_tokens = None
+        # Kernels that wait on other ranks record a time-out in a device status word and skip their work. With
+        # a reducer or a tensor-parallel model attached the word is examined (without stalling the stream, one
+        # step late at most) so that a partial reduction surfaces as CollectiveTimeout instead of diverging replicas.
+        self._status = None
+        if flat.is_cuda and c.status_interval > 0 and (grad_reducer is not None or hasattr(model, "finish_grads")):
+            from ..ops import _lib
+            self._status = _lib.DeferredStatus(flat.device)
 
     # -- data ------------------------------------------------------------------------------
     def _to_device(self, tokens):
@@ -96,7 +104,14 @@ class Trainer:
                        grad_sumsq=self.grad_sumsq, max_grad_norm=c.max_grad_norm, grad_scale=grad_scale,
                        mode=c.optimizer)
         self.last_loss = loss.detach()
+        if self._status is not None and self.step % c.status_interval == 0:
+            self._status.poll()
         return self.last_loss
+
+    def check_status(self) -> None:
+        """Synchronising check of the device status word (checkpoint and telemetry points call it)."""
+        if self._status is not None:
+            self._status.flush()
 
     def grad_norm(self) -> float:
         return float(self.grad_sumsq.sqrt().item())

@@ -117,3 +117,24 @@ def test_sumsq_and_optimizer():
     before = pg.clone()
     ops.optim_step(pg, mg, vg, g.cuda(), pb, lr=1e-2, grad_sumsq=torch.tensor([float("nan")], device="cuda"))
     assert torch.equal(before, pg)
+
+
+def test_deferred_status_raises_collective_timeout_one_poll_late():
+    """A bounded wait that runs out leaves a code in the status word; the non-blocking reader used by the
+    trainers turns it into CollectiveTimeout on the following poll, and the word is cleared."""
+    import ctypes as C
+    from scirust_b200.ops import _lib
+    _lib.register("sb_wait_probe", [_lib.vp, _lib.i32, C.c_uint32, _lib.i32, _lib.vp, _lib.vp])
+    dev = torch.device("cuda", 0)
+    ds = _lib.DeferredStatus(dev)
+    ds.poll()
+    ds.poll()                                   # nothing recorded: no error
+    flags = torch.zeros(16, dtype=torch.int32, device=dev)
+    st = _lib.status_word(dev)
+    _lib.call("sb_wait_probe", flags.data_ptr(), 2, 7, 50, st.data_ptr(), _lib.stream())   # waits 50 ms for nothing
+    ds.poll()                                   # queues the copy behind the probe
+    with pytest.raises(_lib.CollectiveTimeout):
+        ds.poll()
+    assert int(st.item()) == 0
+    ds.poll()
+    ds.poll()

@@ -247,3 +247,88 @@ def test_native_tcp_failures_are_errors_not_hangs():
     t.join()
     s.close()
     assert "protocol" in res.get("err", "")
+
+
+def test_flat_data_parallel_unused_parameter_and_accumulation():
+    """A parameter without a gradient in a step contributes zero (not last step's gradient); a second backward
+    before step() adds to the first (world 1, CPU statements of the cast and optimizer kernels)."""
+    import torch.nn as nn
+    from scirust_b200.parallel.ddp import FlatDataParallel
+
+    class TwoHeads(nn.Module):
+        def __init__(self):
+            super().__init__()
+            torch.manual_seed(0)
+            self.trunk = nn.Linear(8, 8)
+            self.a = nn.Linear(8, 4)
+            self.b = nn.Linear(8, 4)
+
+        def forward(self, x, use_b):
+            h = torch.tanh(self.trunk(x))
+            return (self.b(h) if use_b else self.a(h)).pow(2).mean()
+
+    def run(dp_mode):
+        m = TwoHeads()
+        x = torch.randn(5, 8, generator=torch.Generator().manual_seed(1))
+        if dp_mode:
+            dp = FlatDataParallel(m, optimizer="sgd", lr=0.1, momentum=0.0)
+        else:
+            opt = torch.optim.SGD(m.parameters(), lr=0.1)
+        for step in range(4):
+            if dp_mode:
+                dp(x, use_b=bool(step % 2)).backward()
+                dp.step()
+            else:
+                opt.zero_grad(set_to_none=True)
+                m(x, use_b=bool(step % 2)).backward()
+                for p in m.parameters():          # bf16-rounded gradient, as the flat bf16 buffer holds it
+                    if p.grad is not None:
+                        p.grad = p.grad.to(torch.bfloat16).float()
+                opt.step()
+        return [p.detach().clone() for p in m.parameters()]
+
+    for got, want in zip(run(True), run(False)):
+        assert torch.allclose(got, want, atol=1e-6), (got - want).abs().max()
+
+    # accumulation: two backward passes before step() == one backward of the summed loss (up to bf16 rounding)
+    m = TwoHeads()
+    dp = FlatDataParallel(m, optimizer="sgd", lr=0.1, momentum=0.0)
+    x1 = torch.randn(5, 8, generator=torch.Generator().manual_seed(2))
+    x2 = torch.randn(5, 8, generator=torch.Generator().manual_seed(3))
+    with dp.no_sync():
+        dp(x1, use_b=False).backward()
+    dp(x2, use_b=False).backward()
+    g_acc = dp.grad16.float().clone()
+    dp.step()
+    m2 = TwoHeads()
+    (m2(x1, use_b=False) + m2(x2, use_b=False)).backward()
+    ref = torch.cat([(p.grad if p.grad is not None else torch.zeros_like(p)).reshape(-1) for p in m2.parameters()])
+    got = torch.cat([g_acc[o:o + p.numel()] for o, p in zip(dp.offs, dp.params)])
+    assert torch.allclose(got, ref, atol=2e-2 * ref.abs().max().item() + 1e-6)
+    assert got.abs().max() > 0
+
+
+def test_fused_allreduce_refuses_more_buckets_than_it_has_counters():
+    """The 257th bucket raises on the host; nothing is launched with an out-of-range counter pointer."""
+    from scirust_b200.parallel import fused_allreduce as far
+
+    class FakeRegion:
+        rank, world = 0, 2
+        slots = 0
+
+        def flag_ptrs(self):
+            return None
+
+        def new_slot(self):
+            FakeRegion.slots += 1
+            return FakeRegion.slots - 1
+
+        def peer_ptrs(self, t):
+            return None
+
+    src = torch.zeros(8 * 400, dtype=torch.bfloat16)
+    ar = far.FusedAllReduce(FakeRegion(), src, src.clone())
+    for i in range(far.FLAG_SLOTS):
+        ar.bucket(8 * i, 8)
+    with pytest.raises(RuntimeError, match="buckets"):
+        ar.bucket(8 * far.FLAG_SLOTS, 8)

@@ -68,16 +68,26 @@ def test_paged_decode_attention(dh, H, Hkv):
 
 def test_argmax_tie_and_nan_rules():
     V = 10000
-    lg = torch.randn(4, V, device="cuda")
+    lg = torch.randn(8, V, device="cuda")
     lg[0, 77] = 50.0
     lg[0, 9000] = 50.0          # tie -> lower id
-    lg[1, 5] = float("nan")     # NaN never beats a number
+    lg[1, 5] = float("nan")     # a NaN past column 0 is skipped
     lg[1, 4100] = 60.0
     lg[2] = -5.0
     lg[2, 8191] = -4.0
-    tok = D.argmax_rows(lg)
-    assert tok.tolist()[:3] == [77, 4100, 8191]
-    assert int(tok[3]) == int(torch.argmax(lg[3]))
+    lg[4, 0] = float("nan")     # NaN in column 0: the greedy loop starts from it and nothing compares greater
+    lg[4, 300] = 99.0
+    lg[5, 4096] = float("nan")  # first element of the second slab
+    lg[5, 4097] = 70.0
+    lg[6] = float("nan")        # no number at all
+    lg[7, 4096] = float("nan")  # the maximum sits in the first slab, the second slab starts with a NaN
+    lg[7, 17] = 80.0
+    tok = D.argmax_rows(lg).tolist()
+    assert tok[:3] == [77, 4100, 8191]
+    assert tok[3] == int(torch.argmax(lg[3]))
+    assert tok[4:] == [0, 4097, 0, 17]
+    # the host statement of the same rule agrees row by row
+    assert D.argmax_rows(lg.cpu()).tolist() == tok
 
 
 @pytest.mark.parametrize("quant", [None, "int8"])
