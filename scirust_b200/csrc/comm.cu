@@ -32,75 +32,9 @@
 #include <string.h>
 #include "api.h"
 #include "sm100_ptx.cuh"
+#include "peer_sync.cuh"
 
 namespace sb {
-
-constexpr int MAX_WORLD = 16;
-constexpr int SLOT_WORDS = 4 * MAX_WORLD;  // flag words per slot (phases 0..3 x MAX_WORLD ranks)
-constexpr uint64_t kPeerWaitNsDefault = 10000000000ull;  // 10 s: a peer may start its kernel late
-
-struct PeerTable {
-  void* in[MAX_WORLD];        // peers' input buffers (bucket base)
-  void* out[MAX_WORLD];       // peers' output buffers
-  uint32_t* flags[MAX_WORLD]; // peers' flag arrays
-};
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint4 ld_peer_v4(const void* p) {
-  uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
-
-// Wait until flags[0..W-1] >= epoch (epochs only grow). One thread calls this.
-__device__ bool wait_flags(const uint32_t* flags, int W, uint32_t epoch, uint64_t limit_ns, int* status) {
-  const uint64_t t0 = globaltimer_ns();
-  for (int r = 0; r < W; ++r) {
-    uint32_t spins = 0;
-    while (static_cast<int32_t>(ld_acquire_sys(flags + r) - epoch) < 0) {
-      if ((++spins & 0xff) == 0) {
-        if (globaltimer_ns() - t0 > limit_ns) {
-          atomicCAS(status, 0, ST_TIMEOUT_PEER);
-          return false;
-        }
-        if (*reinterpret_cast<volatile int*>(status) != 0) return false;
-      }
-    }
-  }
-  return true;
-}
-
-// Wait until flags[0..W-1] >= epoch with lanes 0..W-1 of the calling warp polling one flag each (W <= 16).
-// Every lane of the warp must call it; returns the same verdict on all lanes.
-__device__ bool wait_flags_warp(const uint32_t* flags, int W, uint32_t epoch, uint64_t limit_ns, int* status) {
-  const int lane = threadIdx.x & 31;
-  const uint64_t t0 = globaltimer_ns();
-  bool ok = true;
-  if (lane < W) {
-    uint32_t spins = 0;
-    while (static_cast<int32_t>(ld_acquire_sys(flags + lane) - epoch) < 0) {
-      if ((++spins & 0xff) == 0) {
-        if (globaltimer_ns() - t0 > limit_ns) {
-          atomicCAS(status, 0, ST_TIMEOUT_PEER);
-          ok = false;
-          break;
-        }
-        if (*reinterpret_cast<volatile int*>(status) != 0) { ok = false; break; }
-      }
-    }
-  }
-  return __all_sync(0xffffffffu, ok);
-}
 
 struct AllReduceParams {
   PeerTable t;
@@ -120,7 +54,10 @@ __device__ __forceinline__ void accum8(float* acc, const uint4& v) {
   acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z); acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
 }
 
-__global__ void __launch_bounds__(512)
+// U = 16-byte vectors per thread and iteration of the reduce phase; with W ranks U * W peer loads are in flight
+// before the first add (the host picks U = 8 / 4 / 2 for W <= 2 / <= 4 / larger, so about sixteen).
+template <int U, int THREADS>
+__global__ void __launch_bounds__(THREADS)
 allreduce_bf16_kernel(const __grid_constant__ AllReduceParams p) {
   __shared__ int s_ok;
   const int W = p.W;
@@ -145,38 +82,37 @@ allreduce_bf16_kernel(const __grid_constant__ AllReduceParams p) {
     const size_t lo = min(p.n, per * p.rank);
     const size_t hi = min(p.n, lo + per);
     const size_t n8 = (hi - lo) / 8;
-    // two 16-byte vectors per thread and iteration: 2 W peer loads are in flight before the first add;
-    // each vector is summed in rank order
-    for (size_t i0 = gtid; i0 < n8; i0 += 2 * stride) {
-      const size_t i1 = i0 + stride;
-      const bool two = i1 < n8;
-      const size_t e0 = lo + i0 * 8, e1 = lo + (two ? i1 : i0) * 8;
-      float accs[2][8];
+    constexpr int RG = 16 / U;       // ranks whose loads are issued together (U * RG = 16 vectors in registers)
+    for (size_t i0 = gtid; i0 < n8; i0 += U * stride) {
+      float accs[U][8];
 #pragma unroll
-      for (int u = 0; u < 2; ++u)
+      for (int u = 0; u < U; ++u)
 #pragma unroll
         for (int j = 0; j < 8; ++j) accs[u][j] = 0.f;
-      for (int r0 = 0; r0 < W; r0 += 8) {     // ranks in groups of eight: loads first, then the adds in rank order
-        uint4 v0[8], v1[8];
+      for (int r0 = 0; r0 < W; r0 += RG) {     // ranks in groups: loads first, then the adds in rank order
+        uint4 v[RG][U];
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
+        for (int r = 0; r < RG; ++r) {
           if (r0 + r < W) {
-            v0[r] = ld_peer_v4(static_cast<const __nv_bfloat16*>(p.t.in[r0 + r]) + e0);
-            if (two) v1[r] = ld_peer_v4(static_cast<const __nv_bfloat16*>(p.t.in[r0 + r]) + e1);
+            const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(p.t.in[r0 + r]) + lo;
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+              if (i0 + u * stride < n8) v[r][u] = ld_peer_v4(base + (i0 + u * stride) * 8);
           }
         }
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
+        for (int r = 0; r < RG; ++r) {
           if (r0 + r < W) {
-            accum8(accs[0], v0[r]);
-            if (two) accum8(accs[1], v1[r]);
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+              if (i0 + u * stride < n8) accum8(accs[u], v[r][u]);
           }
         }
       }
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        if (u == 1 && !two) break;
-        const size_t e = u == 0 ? e0 : e1;
+      for (int u = 0; u < U; ++u) {
+        if (i0 + u * stride >= n8) break;
+        const size_t e = lo + (i0 + u * stride) * 8;
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = accs[u][j] * p.scale;
@@ -396,7 +332,10 @@ extern "C" int sb_allreduce_bf16(void* const* in_ptrs, void* const* out_ptrs, vo
   p.wait_ns = wait_ms > 0 ? static_cast<uint64_t>(wait_ms) * 1000000ull : kPeerWaitNsDefault;
   p.cta_counter = cta_counter;
   p.status = status;
-  allreduce_bf16_kernel<<<n_ctas, 512, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  // eight vectors per thread need more than the 128 registers a 512-thread block leaves: half-size blocks, twice as many
+  if (W <= 2) allreduce_bf16_kernel<8, 256><<<2 * n_ctas, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  else if (W <= 4) allreduce_bf16_kernel<4, 512><<<n_ctas, 512, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  else allreduce_bf16_kernel<2, 512><<<n_ctas, 512, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
 

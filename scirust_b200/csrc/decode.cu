@@ -16,6 +16,7 @@
 #include <cuda_fp16.h>
 #include <cstdlib>
 #include "sm100_ptx.cuh"
+#include "peer_sync.cuh"
 
 namespace sb {
 
@@ -79,7 +80,73 @@ struct GemvParams {
   int M, N, K, k_per_split, prologue;
   const __nv_bfloat16* norm_w; float eps;
   int* status;
+  // Row-parallel product fused with its all-reduce (coll.W > 1; tensor-parallel decoding): the CTA that finishes a
+  // block of output columns does not write its rank's partial sums to local memory for a second kernel to combine;
+  // it stores them (fp32, before the residual) into slot [parity][rank] of EVERY rank's receive buffer with plain
+  // peer stores, raises the column block's flag on every rank, waits (bounded) for the W flags of its own column
+  // block and adds the W slots in rank order on top of the residual. Every rank adds the same values in the same
+  // order, so all ranks hold identical bits, the same bits as the GEMV followed by the stand-alone all-reduce.
+  //   recv[r]   rank r's receive buffer, fp32 [2][W][coll.rows][N]; a call uses half `epoch & 1`, so a rank that is
+  //             one call ahead never overwrites what a slower rank is still adding
+  //   flags[r]  rank r's epoch words [column block][MAX_WORLD]
+  //   epoch_word / done_ctr: local words; the call's epoch is *epoch_word + 1 and the last finishing CTA stores it
+  //             back, so a captured CUDA graph replays the call with the right epoch.
+  struct {
+    int W, rank, rows;
+    float* recv[MAX_WORLD];
+    uint32_t* flags[MAX_WORLD];
+    uint32_t* epoch_word;
+    unsigned int* done_ctr;
+    uint64_t wait_ns;
+  } coll;
 };
+
+// One finished partial sum (m, gc) of the fused all-reduce path: to slot [parity][rank] of every rank.
+__device__ __forceinline__ void gemv_coll_push(const GemvParams& p, uint32_t epoch, int m, int gc, float sum) {
+  const size_t off = ((static_cast<size_t>(epoch & 1u) * p.coll.W + p.coll.rank) * p.coll.rows + m) * p.N + gc;
+  for (int r = 0; r < p.coll.W; ++r) p.coll.recv[(p.coll.rank + r) % p.coll.W][off] = sum;
+}
+
+// Tail of the fused all-reduce path, called by all threads of the CTA that finished column block blockIdx.x.
+__device__ __forceinline__ void gemv_coll_finish(const GemvParams& p, uint32_t epoch, int col0, int ncols, int* s_flag) {
+  const int W = p.coll.W;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    if (static_cast<int>(threadIdx.x) < W)
+      st_release_sys(p.coll.flags[threadIdx.x] + blockIdx.x * MAX_WORLD + p.coll.rank, epoch);
+    const bool ok = wait_flags_warp(p.coll.flags[p.coll.rank] + blockIdx.x * MAX_WORLD, W, epoch, p.coll.wait_ns, p.status);
+    if (threadIdx.x == 0) *s_flag = ok ? 1 : 0;
+  }
+  __syncthreads();
+  if (*s_flag) {
+    const float* mine = p.coll.recv[p.coll.rank] + static_cast<size_t>(epoch & 1u) * W * p.coll.rows * p.N;
+    const size_t rstride = static_cast<size_t>(p.coll.rows) * p.N;
+    for (int i = threadIdx.x; i < p.M * ncols; i += blockDim.x) {
+      const int m = i / ncols, gc = col0 + (i - m * ncols);
+      float acc = p.R ? __bfloat162float(p.R[static_cast<size_t>(m) * p.ldr + gc]) : 0.f;
+      const float* src = mine + static_cast<size_t>(m) * p.N + gc;
+      for (int r0 = 0; r0 < W; r0 += 8) {      // eight loads in flight, added in rank order
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = (r0 + u < W) ? __ldcg(src + (r0 + u) * rstride) : 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) if (r0 + u < W) acc += v[u];
+      }
+      if (p.out) p.out[static_cast<size_t>(m) * p.ldo + gc] = __float2bfloat16_rn(acc);
+      if (p.out_f32) p.out_f32[static_cast<size_t>(m) * p.N + gc] = acc;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int prev = atomicAdd(p.coll.done_ctr, 1u);
+    if (prev == gridDim.x - 1) {
+      *p.coll.done_ctr = 0;
+      *reinterpret_cast<volatile uint32_t*>(p.coll.epoch_word) = epoch;
+    }
+  }
+}
 
 template <int MB, bool INT8>
 __global__ void __launch_bounds__(GEMV_THREADS)
@@ -532,6 +599,9 @@ gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   __syncthreads();
   pdl_trigger();
   const bool direct = gridDim.y == 1;
+  const bool coll = p.coll.W > 1;
+  // the epoch word is advanced only after every finishing CTA of this call has read it
+  const uint32_t epoch = coll ? *reinterpret_cast<volatile uint32_t*>(p.coll.epoch_word) + 1u : 0u;
   if (warp < 8) {
     // accumulator (nb, mb, j): column col0 + 32 warp + 16 nb + g + 8 (j / 2), row 8 mb + 2 tq + (j & 1)
 #pragma unroll
@@ -545,6 +615,7 @@ gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           if (m < M && gc < N) {
             float sum = acc[nb][mb][j];
             if (direct) {
+              if (coll) { gemv_coll_push(p, epoch, m, gc, sum); continue; }
               if (p.R) sum += __bfloat162float(p.R[static_cast<size_t>(m) * p.ldr + gc]);
               if (p.out) p.out[static_cast<size_t>(m) * p.ldo + gc] = __float2bfloat16_rn(sum);
               if (p.out_f32) p.out_f32[static_cast<size_t>(m) * N + gc] = sum;
@@ -556,7 +627,10 @@ gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       }
     }
   }
-  if (direct) return;
+  if (direct) {
+    if (coll) gemv_coll_finish(p, epoch, col0, min(COLS, N - col0), &s_last);
+    return;
+  }
   // split-K finish by the last CTA of this column block
   __threadfence();
   __syncthreads();
@@ -582,10 +656,12 @@ gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 #pragma unroll
       for (int u = 0; u < 8; ++u) if (k + u < ns) sum += v[u];
     }
+    if (coll) { gemv_coll_push(p, epoch, m, gc, sum); continue; }
     if (p.R) sum += __bfloat162float(p.R[static_cast<size_t>(m) * p.ldr + gc]);
     if (p.out) p.out[static_cast<size_t>(m) * p.ldo + gc] = __float2bfloat16_rn(sum);
     if (p.out_f32) p.out_f32[static_cast<size_t>(m) * N + gc] = sum;
   }
+  if (coll) gemv_coll_finish(p, epoch, col0, ncols, &s_last);
 }
 
 // fp16 pair of two values that are first rounded to bf16 (the activation format) and saturated to the fp16 range
@@ -822,6 +898,9 @@ gemv_mma_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   __syncthreads();
   pdl_trigger();
   const bool direct = gridDim.y == 1;
+  const bool coll = p.coll.W > 1;
+  // the epoch word is advanced only after every finishing CTA of this call has read it
+  const uint32_t epoch = coll ? *reinterpret_cast<volatile uint32_t*>(p.coll.epoch_word) + 1u : 0u;
   if (warp < 8) {
     // accumulator (nb, j): column col0 + 64 warp + 16 nb + 2 g + (j / 2), row 2 tq + (j & 1)
 #pragma unroll
@@ -834,6 +913,7 @@ gemv_mma_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           float sum = acc[nb][0][j];
           if (direct) {
             sum *= p.scale[gc];
+            if (coll) { gemv_coll_push(p, epoch, m, gc, sum); continue; }
             if (p.R) sum += __bfloat162float(p.R[static_cast<size_t>(m) * p.ldr + gc]);
             if (p.out) p.out[static_cast<size_t>(m) * p.ldo + gc] = __float2bfloat16_rn(sum);
             if (p.out_f32) p.out_f32[static_cast<size_t>(m) * N + gc] = sum;
@@ -844,7 +924,10 @@ gemv_mma_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       }
     }
   }
-  if (direct) return;
+  if (direct) {
+    if (coll) gemv_coll_finish(p, epoch, col0, min(COLS, N - col0), &s_last);
+    return;
+  }
   // split-K finish by the last CTA of this column block
   __threadfence();
   __syncthreads();
@@ -871,10 +954,12 @@ gemv_mma_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       for (int u = 0; u < 8; ++u) if (k + u < ns) sum += v[u];
     }
     sum *= p.scale[gc];
+    if (coll) { gemv_coll_push(p, epoch, m, gc, sum); continue; }
     if (p.R) sum += __bfloat162float(p.R[static_cast<size_t>(m) * p.ldr + gc]);
     if (p.out) p.out[static_cast<size_t>(m) * p.ldo + gc] = __float2bfloat16_rn(sum);
     if (p.out_f32) p.out_f32[static_cast<size_t>(m) * N + gc] = sum;
   }
+  if (coll) gemv_coll_finish(p, epoch, col0, ncols, &s_last);
 }
 
 // ---------------------------------------------------------------------------
@@ -1444,9 +1529,15 @@ static int launch_gemv_mma(const GemvParams& p, int splits, cudaStream_t s) {
 // must fit in 64 KB: callers raise `splits` accordingly.
 // prologue: 0 none, 1 RMSNorm of X with gain norm_w (K must be a multiple of 8), 2 SwiGLU over a
 // fused [gate | up] X of row width 2K.
-extern "C" int sb_gemv(const void* X, int ldx, const void* W, int ldw, const float* scale, const void* R, int ldr,
-                       void* out_bf16, int ldo, float* out_f32, int M, int N, int K, int is_int8, int splits,
-                       float* workspace, int prologue, const void* norm_w, float eps, int* status, void* stream) {
+struct GemvCollArgs {
+  void* const* recv_ptrs; void* const* flag_ptrs; uint32_t* epoch_word; unsigned int* done_ctr;
+  int rank, W, rows, wait_ms;
+};
+
+static int gemv_impl(const void* X, int ldx, const void* W, int ldw, const float* scale, const void* R, int ldr,
+                     void* out_bf16, int ldo, float* out_f32, int M, int N, int K, int is_int8, int splits,
+                     float* workspace, int prologue, const void* norm_w, float eps, int* status, void* stream,
+                     const GemvCollArgs* ca) {
   if (M <= 0 || M > 8 || N <= 0 || K <= 0 || (N & 7) || (is_int8 && (N & 15))) return SB_ERR_ARG;
   if (prologue < 0 || prologue > 2 || (prologue == 1 && (!norm_w || (K & 7) || (ldx & 7)))) return SB_ERR_ARG;
   const int esz = is_int8 ? 1 : 2;
@@ -1469,8 +1560,46 @@ extern "C" int sb_gemv(const void* X, int ldx, const void* W, int ldw, const flo
   p.part = workspace + 4096;
   p.M = M; p.N = N; p.K = K; p.k_per_split = kps; p.prologue = prologue;
   p.norm_w = static_cast<const __nv_bfloat16*>(norm_w); p.eps = eps; p.status = status;
+  p.coll.W = 0; p.coll.rank = 0; p.coll.rows = 0; p.coll.epoch_word = nullptr; p.coll.done_ctr = nullptr;
+  p.coll.wait_ns = 0;
+  if (ca) {
+    if (!mma || ca->W < 2 || ca->W > MAX_WORLD || ca->rank < 0 || ca->rank >= ca->W || ca->rows < M ||
+        !ca->epoch_word || !ca->done_ctr || !status)
+      return SB_ERR_ARG;
+    p.coll.W = ca->W; p.coll.rank = ca->rank; p.coll.rows = ca->rows;
+    for (int r = 0; r < ca->W; ++r) {
+      if (!ca->recv_ptrs[r] || !ca->flag_ptrs[r]) return SB_ERR_ARG;
+      p.coll.recv[r] = static_cast<float*>(ca->recv_ptrs[r]);
+      p.coll.flags[r] = static_cast<uint32_t*>(ca->flag_ptrs[r]);
+    }
+    p.coll.epoch_word = ca->epoch_word; p.coll.done_ctr = ca->done_ctr;
+    p.coll.wait_ns = ca->wait_ms > 0 ? static_cast<uint64_t>(ca->wait_ms) * 1000000ull : kPeerWaitNsDefault;
+  }
   if (mma) return is_int8 ? launch_gemv_mma_i8(p, splits, STREAM) : launch_gemv_mma(p, splits, STREAM);
   return is_int8 ? launch_gemv<true>(p, splits, STREAM) : launch_gemv<false>(p, splits, STREAM);
+}
+
+extern "C" int sb_gemv(const void* X, int ldx, const void* W, int ldw, const float* scale, const void* R, int ldr,
+                       void* out_bf16, int ldo, float* out_f32, int M, int N, int K, int is_int8, int splits,
+                       float* workspace, int prologue, const void* norm_w, float eps, int* status, void* stream) {
+  return gemv_impl(X, ldx, W, ldw, scale, R, ldr, out_bf16, ldo, out_f32, M, N, K, is_int8, splits, workspace,
+                   prologue, norm_w, eps, status, stream, nullptr);
+}
+
+// The row-parallel GEMV of tensor-parallel decoding fused with its all-reduce: out = R + sum over ranks of
+// f(X_r) W_r, one launch. recv_ptrs[r]: rank r's receive buffer (peer-mapped, fp32 [2][world][rows][N], rows >= M);
+// flag_ptrs[r]: rank r's epoch words [ceil(N / 256 or 512)][16], zero when the channel is created; epoch_word and
+// done_ctr: local device words, zero when the channel is created. Every rank must issue the same sequence of
+// calls on a channel. Tensor-core kernels only (not with SB_GEMV_FMA=1).
+extern "C" int sb_gemv_allreduce(const void* X, int ldx, const void* W, int ldw, const float* scale, const void* R,
+                                 int ldr, void* out_bf16, int ldo, int M, int N, int K, int is_int8, int splits,
+                                 float* workspace, int prologue, const void* norm_w, float eps,
+                                 void* const* recv_ptrs, void* const* flag_ptrs, uint32_t* epoch_word,
+                                 unsigned int* done_ctr, int rank, int world, int rows, int wait_ms, int* status,
+                                 void* stream) {
+  GemvCollArgs ca{recv_ptrs, flag_ptrs, epoch_word, done_ctr, rank, world, rows, wait_ms};
+  return gemv_impl(X, ldx, W, ldw, scale, R, ldr, out_bf16, ldo, nullptr, M, N, K, is_int8, splits, workspace,
+                   prologue, norm_w, eps, status, stream, &ca);
 }
 
 extern "C" int sb_kv_append(const void* qkv, int ld, int H, int Hkv, int dh, void* pool, const int* block_table,

@@ -308,6 +308,31 @@ class InferenceEngine:
         return out
 
 
+def teacher_forced_logits(engine: "InferenceEngine", prompts: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
+    """Logits ``[B, n, V]`` (fp32) of ``engine`` when it is FED ``tokens [B, n]`` after ``prompts`` instead of its own
+    arg-max: step i sees the prompt and tokens[:, :i+1]. Two engines given the same tokens can then be compared
+    step by step, which greedy generation does not allow once one near-tie flips a token (eager steps, no graph)."""
+    B, P = prompts.shape
+    n = tokens.shape[1]
+    for b in range(B):
+        if engine.cache.owned[b]:
+            engine.cache.release(b)
+    engine.prefill(prompts)
+    for b in range(B):
+        engine.cache.reserve(b, P + n + 1)
+    engine.cache.commit()
+    engine._seq_of = torch.arange(engine.max_batch, dtype=torch.int32, device=engine.dev)
+    engine._len_plus1 = torch.zeros(engine.max_batch, dtype=torch.int32, device=engine.dev)
+    engine._generated = None
+    out = []
+    tok = tokens.to(engine.dev)
+    for i in range(n):
+        engine.tokens[:B] = tok[:, i]
+        engine._step_eager(B, P + n + 1)
+        out.append(engine.logits[:B].float().clone())
+    return torch.stack(out, 1)
+
+
 def reference_generate(model: GQADecoder, prompts: torch.Tensor, max_new: int) -> torch.Tensor:
     """Full-recompute greedy decoding through the training forward (the naive path the cached
     decoder must agree with token for token: scirust-sciagent/tests/cuda_parity.rs:184)."""

@@ -16,6 +16,8 @@ cuda_decode.rs:17-470); this engine keeps its greedy/tie rules and KV-cache sema
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -61,13 +63,19 @@ class TPInferenceEngine(InferenceEngine):
             big_rows = max_batch * max_seq
             self._big_elems = big_rows * d if big_rows * d * 2 * W > SMALL_BYTES else 0
             nbytes = (2 * self._big_elems * 2 + 2 * self._small_rows * d * 4
-                      + max_batch * (cfg.vocab_size // W) * 4 + (1 << 16))
+                      + max_batch * (cfg.vocab_size // W) * 4 + 2 * W * 8 * d * 4 + (1 << 17))
             self.region = SymmetricRegion(self.group, nbytes, device=dev)
             if self._big_elems:
                 self.big_src = self.region.tensor((self._big_elems,), BF)
                 self.big_dst = self.region.tensor((self._big_elems,), BF)
                 self.big = FusedAllReduce(self.region, self.big_src, self.big_dst, n_ctas=64)
         self.coll = SmallCollectives(self.group, self.region, backend=self.backend)
+        # decode steps of up to 8 rows: the row-parallel GEMV performs its own all-reduce (one launch instead of two);
+        # SB_TP_FUSED_GEMV=0 keeps the GEMV + stand-alone collective pair
+        self.gemv_chan = None
+        if self.backend == "fused" and os.environ.get("SB_TP_FUSED_GEMV", "1") != "0":
+            from ..parallel.small_collectives import GemvAllReduceChannel
+            self.gemv_chan = GemvAllReduceChannel(self.region, rows=8, n_max=cfg.d_model)
         super().__init__(model, quant=quant, max_batch=max_batch, max_seq=max_seq, page=page,
                          use_graph=use_graph and self.backend == "fused")
         self.vocab_local = cfg.vocab_size // W
@@ -105,6 +113,8 @@ class TPInferenceEngine(InferenceEngine):
         M, d = x.shape
         coll = self.coll
         if self.backend != "fused" or M * d * 2 * self.world <= SMALL_BYTES:
+            if self.gemv_chan is not None and M <= D.gemv_max_rows(w) and os.environ.get("SB_GEMV_FMA") != "1":
+                return D.gemv_allreduce(a, w, self.gemv_chan, residual=x, swiglu=swiglu)
             full = coll.source(site, (self._small_rows, d), torch.float32, device=x.device)
             if M <= D.gemv_max_rows(w):
                 src = full[:M]

@@ -186,6 +186,38 @@ def gemv(x, w, residual=None, out=None, out_f32=None, splits=None, rms_weight=No
     return out if out is not None else out_f32
 
 
+_lib.register("sb_gemv_allreduce", [vp, i32, vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, vp, i32, vp, f32,
+                                    vp, vp, vp, vp, i32, i32, i32, i32, vp, vp])
+
+
+def gemv_allreduce(x, w, chan, residual=None, out=None, splits=None, swiglu=False):
+    """out[M,N] = residual + sum over the ranks of ``chan`` of f(x_r)[M,K_r] @ W_r, M <= 8, in ONE launch per rank:
+    the row-parallel product of tensor-parallel decoding with its all-reduce done by the CTAs that finish each block
+    of output columns (csrc/decode.cu: ``sb_gemv_allreduce``). ``chan`` is a ``GemvAllReduceChannel``
+    (parallel/small_collectives.py) that owns the peer-mapped receive buffers, flags and the epoch word."""
+    quant = isinstance(w, QuantWeight)
+    wm = w.q if quant else w
+    K, N = wm.shape
+    M = x.shape[0]
+    if M > chan.rows or N > chan.n_max:
+        raise ValueError("gemv_allreduce: product larger than the channel was sized for")
+    if out is None:
+        out = torch.empty((M, N), dtype=BF, device=x.device)
+    if splits is None:
+        splits = _auto_splits(N, K, 512 if quant else 256, M, quant)
+    splits = max(splits, (K + 4095) // 4096)
+    ws = _gemv_workspace(4096 + splits * M * N, x.device)
+    st = _lib.status_word(x.device)
+    _lib.call("sb_gemv_allreduce", x.data_ptr(), x.stride(0), wm.data_ptr(), wm.stride(0),
+              w.scale.data_ptr() if quant else None, _lib.ptr(residual),
+              residual.stride(0) if residual is not None else 0, out.data_ptr(), out.stride(0), M, N, K, int(quant),
+              splits, ws.data_ptr(), 2 if swiglu else 0, None, 1e-5, chan.recv_ptrs(N), chan.flag_ptrs,
+              chan.state.data_ptr(), chan.state.data_ptr() + 128, chan.rank, chan.world, chan.rows, chan.wait_ms,
+              st.data_ptr(), _lib.stream())
+    _g.launch_count += 1
+    return out
+
+
 def matmul_w8(x, w: QuantWeight, residual=None, out=None, splits=None):
     """y[M,N] = (x[M,K] @ int8 W) * scale (+ residual) on the dequant-fused tcgen05 GEMM
     (csrc/gemm_w8_tcgen05.cu): the int8 codes are widened to bf16 in shared memory, so the weights

@@ -40,7 +40,7 @@ class FlatDataParallel:
 
     def __init__(self, module: torch.nn.Module, group=None, optimizer: str = "adam", lr: float = 1e-3,
                  momentum: float = 0.9, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0,
-                 comm: str = "fused", bucket_elems: int = 4 << 20, overlap: bool = True, n_ctas: int = 32,
+                 comm: str = "fused", bucket_elems: int = 4 << 20, overlap: bool = True, n_ctas: int = 48,
                  max_buckets: int = 192):
         self.module, self.group = module, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1

@@ -69,8 +69,10 @@ class FusedAllReduce:
         r = self.region
         st = _lib.status_word(self.src.device)
         s = _lib.stream() if stream is None else stream.cuda_stream
+        # buckets of tens of MB (an embedding table) are bound by bytes in flight: more CTAs
+        n_ctas = self.n_ctas if n < (24 << 20) else max(self.n_ctas, 64)
         _lib.call("sb_allreduce_bf16", in_p, out_p, self.flag_ptrs, r.rank, r.world, n, float(scale), epoch, slot,
-                  int(self.dst.dtype == torch.float32), self.counters.data_ptr() + 4 * idx, self.n_ctas, self.wait_ms,
+                  int(self.dst.dtype == torch.float32), self.counters.data_ptr() + 4 * idx, n_ctas, self.wait_ms,
                   st.data_ptr(), s)
         _g.launch_count += 1
 
@@ -82,7 +84,7 @@ class FusedGradAllReduce:
     as that layer's backward has produced it; the call at the end of backward reduces what is left
     (embedding, norm gains) and joins the streams."""
 
-    def __init__(self, model, group, overlap: bool = True, n_ctas: int = 24, out_dtype=torch.bfloat16):
+    def __init__(self, model, group, overlap: bool = True, n_ctas: int = 48, out_dtype=torch.bfloat16):
         n_ctas = int(os.environ.get("SB_AR_CTAS", n_ctas))       # CTAs of one bucket's all-reduce kernel
         overlap = overlap and os.environ.get("SB_AR_OVERLAP", "1") != "0"
         self.model = model

@@ -108,3 +108,31 @@ class SmallCollectives:
         dist.all_gather(parts, src.contiguous(), group=self.group)
         out.view(rows, self.world, n).copy_(torch.stack(parts, 1))
         return out
+
+
+class GemvAllReduceChannel:
+    """Peer-mapped state of the fused row-parallel GEMV + all-reduce (``ops.decode.gemv_allreduce``): per rank a
+    receive buffer ``fp32 [2][world][rows][n_max]`` (every peer stores its partial sums of a call into slot
+    ``[call parity][its rank]``), one epoch word per (block of output columns, source rank), and a local epoch
+    word / CTA counter that the kernel maintains, so a captured CUDA graph replays the calls correctly. All ranks
+    must issue the same sequence of calls on a channel; consecutive calls alternate the buffer halves, which is what
+    lets a rank run one call ahead of its slowest peer.
+
+    The receive buffer is addressed as ``[2][world][rows][N]`` with the N of the call, so calls of different widths
+    may share a channel as long as every rank uses the same width for the same call."""
+
+    def __init__(self, region, rows: int = 8, n_max: int = 8192, wait_ms: int = 0):
+        self.region, self.rows, self.n_max, self.wait_ms = region, rows, n_max, wait_ms
+        self.rank, self.world = region.rank, region.world
+        self.recv = region.tensor((2 * self.world * rows * n_max,), torch.float32)
+        self.recv.zero_()
+        self.flags = region.tensor((((n_max + 255) // 256) * 16,), torch.int32)
+        self.flags.zero_()
+        self._recv_ptrs = region.peer_ptrs(self.recv)
+        self.flag_ptrs = region.peer_ptrs(self.flags)
+        self.state = torch.zeros(64, dtype=torch.int32, device=region.device)   # [0] epoch word, [32] CTA counter
+        torch.cuda.synchronize(region.device)
+        dist.barrier(group=region.group)      # nobody pushes into a buffer that is still being cleared
+
+    def recv_ptrs(self, n: int):
+        return self._recv_ptrs
