@@ -110,11 +110,12 @@ __device__ __forceinline__ void gemv_coll_push(const GemvParams& p, uint32_t epo
 // Tail of the fused all-reduce path, called by all threads of the CTA that finished column block blockIdx.x.
 __device__ __forceinline__ void gemv_coll_finish(const GemvParams& p, uint32_t epoch, int col0, int ncols, int* s_flag) {
   const int W = p.coll.W;
-  __threadfence_system();
-  __syncthreads();
+  __syncthreads();      // every thread's pushes are ordered before the fence of the announcing lanes (cumulative release)
   if (threadIdx.x < 32) {
-    if (static_cast<int>(threadIdx.x) < W)
+    if (static_cast<int>(threadIdx.x) < W) {
+      __threadfence_system();
       st_release_sys(p.coll.flags[threadIdx.x] + blockIdx.x * MAX_WORLD + p.coll.rank, epoch);
+    }
     const bool ok = wait_flags_warp(p.coll.flags[p.coll.rank] + blockIdx.x * MAX_WORLD, W, epoch, p.coll.wait_ns, p.status);
     if (threadIdx.x == 0) *s_flag = ok ? 1 : 0;
   }

@@ -9,9 +9,13 @@
 //
 //   warp 0   TMA producer (both CTAs; bytes of both are counted on the leader's "full" barrier)
 //   warp 1   MMA issuer (leader CTA only); the same warp allocates TMEM in both CTAs
-//   warp 2-9 epilogue (both CTAs; "accumulator drained" arrives on the leader's barrier)
+//   warp 2-9 epilogue (both CTAs; "accumulator drained" arrives on the leader's barrier). The plain epilogue
+//            (no SwiGLU, no split parts) does not store from registers: a warp converts 32 rows x 64 columns, lays
+//            them out as 128-byte swizzled rows in its own 4 KB of shared memory and hands them to a TMA tensor
+//            store, so the output leaves the SM as full 128-byte lines and edge tiles are clipped by the hardware
 // Stage release and "accumulator ready" are tcgen05.commit arrivals delivered to both CTAs.
 // No TMA multicast is used.
+#include <cstdlib>
 #include "sm100_ptx.cuh"
 #include "api.h"
 #include "gemm_sched.cuh"
@@ -40,13 +44,20 @@ constexpr int B_BYTES = BNH * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // 32 KB per CTA
 constexpr int STAGES = 6;
 constexpr int TMEM_COLS = 2 * BN;                // two accumulators
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int EPI_WARPS = 8;
+constexpr int EPI_STAGE_BYTES = 32 * 128;        // one warp's 32 rows x 64 bf16 columns, 128-byte swizzled rows
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_WARPS * EPI_STAGE_BYTES + 1024 + 256;
+
+struct TmapSet {
+  CUtensorMap m[MAXW];   // reduce-scatter: the slot of this rank in every owner's receive buffer
+};
 
 struct Params {
   int M, N, K;
   void* C; int ldc;
   const void* R; int ldr;
   int* status;
+  int use_tma_store;     // plain tiles leave through shared memory + TMA tensor store (tmap_c is valid)
   BalancedSched sched;   // workers are CTA pairs; see gemm_sched.cuh
   float* partials;       // dense fp32 [256, 256] blocks, one per scratch slot
   // SwiGLU epilogue (ff > 0): B is a fused [gate | up] weight of 2*ff columns and N == 2*ff. A tile then
@@ -75,13 +86,15 @@ struct Params {
     uint64_t wait_ns;
     int team;        // CTAs that share one chunk; teams work on different chunks at the same time
   } ag;
-  // GEMM -> reduce-scatter (rs.W > 1): C is this rank's PARTIAL product [M, ldc] in symmetric memory
-  // (p_peer[s] = rank s's copy). Rows [o*rows, (o+1)*rows) belong to rank o. The epilogue stores the
-  // partial as usual and counts finished tiles per 256-row block; the block's last warp raises
-  // "rank s's partial of this block is complete" on the block's owner (ready[o] + s * blocks + block).
-  // The copier warps of the owner then pull the W partials of a block (own copy locally, the others
-  // with plain peer loads), add them in rank order 0..W-1 (+ residual) and write out [rows, ld_out].
-  // Own rows are computed first, so the peers' partials of my rows arrive while I compute theirs.
+  // GEMM -> reduce-scatter (rs.W >= 1): every rank computes the partial product of ALL rows; rows
+  // [o*rows, (o+1)*rows) belong to rank o. The epilogue PUSHES each finished tile straight into the owner's
+  // receive buffer (p_peer[o] = rank o's buffer, bf16 [W sources][rows][ldc]; slot [my rank]) with a TMA tensor
+  // store through the owner's tensor map, so the transfer over NVLink runs under the main loop of the following
+  // tiles and nothing is left to pull at the end. Finished tiles are counted per 256-row block; when a block is
+  // complete (its stores have been waited for) the rank raises "rank s's partial of this block has landed" on
+  // the owner (ready[o] + s * blocks + block). The copier warps of the owner add the W slots of a block in rank
+  // order 0..W-1 (+ residual) from LOCAL memory and write out [rows, ld_out]. Blocks of other owners are computed
+  // first, own rows last, so the peers' pushes of my rows arrive while I compute theirs.
   struct {
     int W, rank, rows;
     const void* p_peer[MAXW];
@@ -129,11 +142,13 @@ __device__ bool p_wait_flag(const uint32_t* flag, uint32_t epoch, uint64_t limit
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_a_own, const Params p) {
+                 const __grid_constant__ CUtensorMap tmap_a_own, const __grid_constant__ CUtensorMap tmap_c,
+                 const __grid_constant__ TmapSet tmap_rs, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* tiles = smem;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* epi_stage = smem + STAGES * STAGE_BYTES;      // EPI_WARPS x 4 KB, 1024-byte aligned
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_stage + EPI_WARPS * EPI_STAGE_BYTES);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tmem_full = empty_bar + STAGES;
   uint64_t* tmem_empty = tmem_full + 2;
@@ -167,7 +182,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const bool ag = p.ag.W >= 1;   // a one-rank group runs the same protocol with itself as the only peer
   const bool rs = p.rs.W >= 1;
   const int m_rot = ag ? p.ag.rank * (mt2 / p.ag.W)        // walk the local shard's row tiles first
-                       : (rs ? p.rs.rank * (mt2 / p.rs.W) : 0);
+                       : (rs ? ((p.rs.rank + 1) % p.rs.W) * (mt2 / p.rs.W) : 0);   // the next rank's rows first, own rows last
 
   if (threadIdx.x == 0) {
     if (ag && blockIdx.x == 0) {
@@ -355,8 +370,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         okf = __shfl_sync(0xffffffffu, okf, 0);
         if (!okf) break;
-        const size_t grow0 = (static_cast<size_t>(p.rs.rank) * bpr + bi) * 2 * BM;   // first global row of the block
-        const size_t lrow0 = static_cast<size_t>(bi) * 2 * BM;
+        const size_t lrow0 = static_cast<size_t>(bi) * 2 * BM;                      // first row of the block in my shard
         for (size_t v0 = lo + (cw * 32 + lane); v0 < hi; v0 += COPY_WARPS * 32 * 4) {
           // four 16-byte columns per thread and two sources at a time in flight; the sum runs in rank order
           float acc8[4][8];
@@ -367,7 +381,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const size_t v = v0 + static_cast<size_t>(u) * COPY_WARPS * 32;
             live[u] = v < hi;
             const size_t r = live[u] ? v / vec_per_row : 0, c = live[u] ? (v - r * vec_per_row) * 8 : 0;
-            off_p[u] = (grow0 + r) * p.ldc + c;
+            off_p[u] = (lrow0 + r) * p.ldc + c;      // inside one source's slot of my receive buffer
             off_l[u] = (r << 20) | c;          // packed (row inside the block, column): N < 2^20
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc8[u][j] = 0.f;
@@ -377,7 +391,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
             for (int t = 0; t < 2; ++t) {
               if (s0 + t < p.rs.W) {
-                const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(p.rs.p_peer[s0 + t]);
+                const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(p.rs.p_peer[p.rs.rank]) +
+                                            static_cast<size_t>(s0 + t) * p.rs.rows * p.ldc;
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                   if (live[u])
@@ -427,6 +442,21 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t leader_empty1 = mapa_shared(smem_u32(&tmem_empty[1]), 0);
     bool ok = true;
     int it = 0;
+    // reduce-scatter: the row block whose stores (TMA, to the owner's memory) this warp has issued but not yet
+    // announced. A warp's share of a tile counts once those stores are complete; the warp that completes a
+    // 256-row block raises the block's flag on its owner.
+    int pend_m2 = -1;
+    auto rs_announce = [&](int mb) {
+      asm volatile("fence.proxy.async;" ::: "memory");     // the stores went through the async proxy
+      __threadfence_system();
+      const unsigned int prev = atomicAdd(p.rs.block_ctr + mb, 1u);
+      if (prev + 1 == static_cast<unsigned int>(nt) * 16u) {
+        const int bpr = p.rs.rows / (2 * BM);
+        const int owner = mb / bpr;
+        __threadfence_system();
+        p_st_release_sys(p.rs.ready[owner] + p.rs.rank * bpr + (mb - owner * bpr), p.rs.epoch);
+      }
+    };
     SegIter iter(p.sched, pair_id, n_pairs, tiles_total, num_kb, 1, num_kb);
     Seg sg;
     for (; ok && iter.next(sg); ++it) {
@@ -470,6 +500,65 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 *reinterpret_cast<uint4*>(arow + gcol + v * 8) = oa;
               }
             }
+          }
+        }
+      } else if (!p.gu && sg.slot < 0 && p.use_tma_store) {
+        // plain tile through shared memory and a TMA tensor store: two slabs of 64 columns per warp
+        uint8_t* stg = epi_stage + (warp - 2) * EPI_STAGE_BYTES;
+        const int row0w = (m2 * 2 + static_cast<int>(rank)) * BM + q * 32;      // first row of this warp
+#pragma unroll 1
+        for (int sl = 0; sl < 2; ++sl) {
+          const int colw = n_idx * BN + half * (BN / 2) + sl * 64;
+          if (lane == 0) tma_store_wait_read<0>();      // the previous slab has left the staging buffer
+          __syncwarp();
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr_row + (half * (BN / 64) + sl * 2 + cc) * 32, r);
+            tmem_ld_wait();
+            const int col0 = colw + cc * 32;
+            const __nv_bfloat16* rrow = (p.R && row < p.M && col0 < p.N)
+                ? reinterpret_cast<const __nv_bfloat16*>(p.R) + static_cast<size_t>(row) * p.ldr + col0 : nullptr;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              float f[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+              if (rrow && col0 + v * 8 < p.N) {
+                const uint4 rv = *reinterpret_cast<const uint4*>(rrow + v * 8);
+                f[0] += bf16_lo(rv.x); f[1] += bf16_hi(rv.x);
+                f[2] += bf16_lo(rv.y); f[3] += bf16_hi(rv.y);
+                f[4] += bf16_lo(rv.z); f[5] += bf16_hi(rv.z);
+                f[6] += bf16_lo(rv.w); f[7] += bf16_hi(rv.w);
+              }
+              uint4 o;
+              o.x = pack_bf16x2(f[0], f[1]);
+              o.y = pack_bf16x2(f[2], f[3]);
+              o.z = pack_bf16x2(f[4], f[5]);
+              o.w = pack_bf16x2(f[6], f[7]);
+              const int chunk = cc * 4 + v;              // 16-byte chunk of the 128-byte row
+              *reinterpret_cast<uint4*>(stg + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = o;
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          const bool issued = row0w < p.M && colw < p.N;    // a slab wholly past the edge stores nothing
+          if (lane == 0 && issued) {
+            if (rs) {
+              const int owner = m2 / (p.rs.rows / (2 * BM));
+              tma_store_2d(&tmap_rs.m[owner], stg, colw, row0w - owner * p.rs.rows);
+            } else {
+              tma_store_2d(&tmap_c, stg, colw, row0w);
+            }
+            tma_store_commit();
+          }
+          if (rs && sl == 0 && pend_m2 >= 0) {
+            // all but the group just committed are complete: the previous tile has landed on its owner
+            if (lane == 0) {
+              if (issued) tma_store_wait<1>(); else tma_store_wait<0>();
+              rs_announce(pend_m2);
+            }
+            pend_m2 = -1;
           }
         }
       } else {
@@ -548,24 +637,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
-      if (rs) {
-        // this warp's share of the tile is stored: publish it, count it; the warp that completes the
-        // 256-row block raises the block's flag on its owner
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0) {
-          const unsigned int prev = atomicAdd(p.rs.block_ctr + m2, 1u);
-          if (prev + 1 == static_cast<unsigned int>(nt) * 16u) {
-            const int bpr = p.rs.rows / (2 * BM);
-            const int owner = m2 / bpr;
-            __threadfence_system();
-            p_st_release_sys(p.rs.ready[owner] + p.rs.rank * bpr + (m2 - owner * bpr), p.rs.epoch);
-          }
-        }
-      }
+      if (rs) pend_m2 = m2;     // announced once its stores have completed (during the next tile, or below)
+    }
+    if (rs && pend_m2 >= 0) {
+      if (lane == 0) { tma_store_wait<0>(); rs_announce(pend_m2); }
+      __syncwarp();
     }
   }
 
+  if (warp >= 2 && warp < 2 + EPI_WARPS && lane == 0) tma_store_wait<0>();   // staged output has left shared memory
   // Teardown: every role loop is bounded, so all threads of both CTAs arrive here. Neither CTA may
   // leave while the other can still read its shared memory or signal its barriers.
   tc_fence_before();
@@ -632,7 +712,7 @@ static int max_pairs() {
 
 template <bool A_MN, bool B_MN>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int grid, cudaStream_t stream,
-                  const CUtensorMap* ta_own = nullptr) {
+                  const CUtensorMap* ta_own = nullptr, const CUtensorMap* tc = nullptr, const TmapSet* trs = nullptr) {
   auto kern = gemm_pair_kernel<A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -652,7 +732,11 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p,
   at[0].val.clusterDim.z = 1;
   cfg.attrs = at;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, ta, tb, ta_own ? *ta_own : ta, p) == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+  static const TmapSet none = {};
+  return cudaLaunchKernelEx(&cfg, kern, ta, tb, ta_own ? *ta_own : ta, tc ? *tc : ta, trs ? *trs : none, p) ==
+                 cudaSuccess
+             ? 0
+             : SB_ERR_LAUNCH;
 }
 
 }  // namespace pair
@@ -699,6 +783,15 @@ extern "C" int sb_gemm_pair_bf16(const void* A, const void* B, void* C, const vo
   p.gu = gu; p.ld_gu = ld_gu;
   p.ag.W = 0;
   p.rs.W = 0;
+  // output through shared memory + TMA tensor store (SB_GEMM_TMA_STORE=0 keeps the register stores)
+  static const bool tma_store = [] { const char* e = getenv("SB_GEMM_TMA_STORE"); return !(e && e[0] == '0'); }();
+  CUtensorMap tc;
+  p.use_tma_store = 0;
+  if (tma_store && !ff && !gu) {
+    rc = make_tmap_2d_bf16(&tc, C, N, M, ldc, 64, 32);
+    if (rc) return rc;
+    p.use_tma_store = 1;
+  }
   const int mt2 = (M + 2 * BM - 1) / (2 * BM), nt = ff ? (ff + BNH - 1) / BNH : (N + BN - 1) / BN;
   const int num_kb = (K + BK - 1) / BK;
   const int pairs_avail = max_pairs();
@@ -713,10 +806,11 @@ extern "C" int sb_gemm_pair_bf16(const void* A, const void* B, void* C, const vo
     p.sched.dp_tiles = p.sched.sk_tiles = p.sched.sk_workers = p.sched.sk_slots = 0;
   }
   const int grid = 2 * pairs;
-  if (!a_mn && !b_mn) rc = launch<false, false>(ta, tb, p, grid, stream);
-  else if (!a_mn && b_mn) rc = launch<false, true>(ta, tb, p, grid, stream);
-  else if (a_mn && !b_mn) rc = launch<true, false>(ta, tb, p, grid, stream);
-  else rc = launch<true, true>(ta, tb, p, grid, stream);
+  const CUtensorMap* tcp = p.use_tma_store ? &tc : nullptr;
+  if (!a_mn && !b_mn) rc = launch<false, false>(ta, tb, p, grid, stream, nullptr, tcp);
+  else if (!a_mn && b_mn) rc = launch<false, true>(ta, tb, p, grid, stream, nullptr, tcp);
+  else if (a_mn && !b_mn) rc = launch<true, false>(ta, tb, p, grid, stream, nullptr, tcp);
+  else rc = launch<true, true>(ta, tb, p, grid, stream, nullptr, tcp);
   if (rc) return rc;
   if (fixup) {
     dim3 fg(p.sched.sk_tiles, 2 * BM * BN / (256 * 4));
@@ -753,6 +847,7 @@ extern "C" int sb_gemm_pair_ag_bf16(void* const* a_ptrs, const void* B, void* C,
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.R = R; p.ldr = ldr; p.status = status;
   p.ff = 0; p.act = nullptr; p.ld_act = 0; p.gu = nullptr; p.ld_gu = 0;
   p.partials = nullptr;
+  p.use_tma_store = 0;
   p.sched.dp_tiles = p.sched.sk_tiles = p.sched.sk_workers = p.sched.sk_slots = 0;
   p.rs.W = 0;
   p.ag.W = W; p.ag.rank = rank; p.ag.rows = M / W; p.ag.lda = lda;
@@ -776,8 +871,12 @@ extern "C" int sb_gemm_pair_ag_bf16(void* const* a_ptrs, const void* B, void* C,
   if (team > grid) team = grid;
   team = grid / (grid / team);      // as few idle CTAs as the grid allows
   p.ag.team = team;
-  if (!b_mn) return launch<false, false>(ta, tb, p, grid, stream, &ta_own);
-  return launch<false, true>(ta, tb, p, grid, stream, &ta_own);
+  CUtensorMap tc;
+  rc = make_tmap_2d_bf16(&tc, C, N, M, ldc, 64, 32);
+  if (rc) return rc;
+  p.use_tma_store = 1;
+  if (!b_mn) return launch<false, false>(ta, tb, p, grid, stream, &ta_own, &tc);
+  return launch<false, true>(ta, tb, p, grid, stream, &ta_own, &tc);
 }
 
 // GEMM -> reduce-scatter on CTA pairs: out[M/W, N] = rows of this rank of sum over ranks (A_r * op(B_r)) (+ res).
@@ -793,7 +892,7 @@ extern "C" int sb_gemm_pair_rs_bf16(const void* A, const void* B, void* const* p
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0 || K <= 0 || W < 1 || W > MAXW || rank < 0 || rank >= W) return SB_ERR_ARG;
   if ((N & 7) || (ldp & 7) || (ld_out & 7) || (res && (ld_res & 7)) || (M % (W * 2 * BM))) return SB_ERR_ARG;
-  void* C = part_ptrs[rank];
+  void* C = part_ptrs[rank];     // this rank's receive buffer [W][M / W][ldp]: the reducer reads it locally
   if ((reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return SB_ERR_ALIGN;
   CUtensorMap ta, tb;
   int rc = make_tmap_2d_bf16(&ta, A, K, M, lda, BK, BM);
@@ -801,10 +900,18 @@ extern "C" int sb_gemm_pair_rs_bf16(const void* A, const void* B, void* const* p
   if (!b_mn) rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, BNH);
   else rc = make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, BK);
   if (rc) return rc;
+  // slot [rank] of every owner's receive buffer: [M / W rows][N columns], row pitch ldp
+  TmapSet trs = {};
+  for (int o = 0; o < W; ++o) {
+    const __nv_bfloat16* slot = static_cast<const __nv_bfloat16*>(part_ptrs[o]) + static_cast<size_t>(rank) * (M / W) * ldp;
+    rc = make_tmap_2d_bf16(&trs.m[o], slot, N, M / W, ldp, 64, 32);
+    if (rc) return rc;
+  }
   Params p;
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldp; p.R = nullptr; p.ldr = 0; p.status = status;
   p.ff = 0; p.act = nullptr; p.ld_act = 0; p.gu = nullptr; p.ld_gu = 0;
   p.partials = nullptr;
+  p.use_tma_store = 1;           // reduce-scatter tiles always leave by TMA store, into the owners' memory
   p.sched.dp_tiles = p.sched.sk_tiles = p.sched.sk_workers = p.sched.sk_slots = 0;
   p.ag.W = 0;
   p.rs.W = W; p.rs.rank = rank; p.rs.rows = M / W;
@@ -824,6 +931,6 @@ extern "C" int sb_gemm_pair_rs_bf16(const void* A, const void* B, void* const* p
   if (team > grid) team = grid;
   team = grid / (grid / team);      // as few idle CTAs as the grid allows
   p.rs.team = team;
-  if (!b_mn) return launch<false, false>(ta, tb, p, grid, stream);
-  return launch<false, true>(ta, tb, p, grid, stream);
+  if (!b_mn) return launch<false, false>(ta, tb, p, grid, stream, nullptr, nullptr, &trs);
+  return launch<false, true>(ta, tb, p, grid, stream, nullptr, nullptr, &trs);
 }

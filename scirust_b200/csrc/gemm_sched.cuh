@@ -112,14 +112,26 @@ __global__ void balanced_fixup_kernel(BalancedSched s, const float* __restrict__
   const int tr = e / TN, tc = e - tr * TN;
   const int row = m_idx * TM + tr, col = n_idx * TN + tc;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (; c < s.sk_workers; ++c) {
-    const long long u0 = U * c / s.sk_workers, u1 = U * (c + 1) / s.sk_workers;
-    if (u0 >= hi) break;
-    if (u1 <= lo || u1 == u0) continue;
-    const int ordinal = r - static_cast<int>(u0 / num_kb);
-    const size_t slot = static_cast<size_t>(c) * s.sk_slots + ordinal;
-    const float4 v = *reinterpret_cast<const float4*>(partials + (slot * TM + tr) * TN + tc);
-    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  // the parts of this tile, in ascending k (= ascending worker); eight loads are in flight before the first add and
+  // the adds keep the part order, so the sum is the same whatever the grouping
+  while (c < s.sk_workers) {
+    const float* src[8];
+    int n = 0;
+    for (; c < s.sk_workers && n < 8; ++c) {
+      const long long u0 = U * c / s.sk_workers, u1 = U * (c + 1) / s.sk_workers;
+      if (u0 >= hi) { c = s.sk_workers; break; }
+      if (u1 <= lo || u1 == u0) continue;
+      const int ordinal = r - static_cast<int>(u0 / num_kb);
+      const size_t slot = static_cast<size_t>(c) * s.sk_slots + ordinal;
+      src[n++] = partials + (slot * TM + tr) * TN + tc;
+    }
+    float4 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (i < n) v[i] = __ldcs(reinterpret_cast<const float4*>(src[i]));
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (i < n) { acc.x += v[i].x; acc.y += v[i].y; acc.z += v[i].z; acc.w += v[i].w; }
   }
   if (row >= M || col >= N) return;
   if (R) {

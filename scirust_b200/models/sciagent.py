@@ -291,7 +291,7 @@ class GQADecoder(nn.Module):
     ``forward(tokens)`` returns logits of the last position of every sequence."""
 
     def __init__(self, cfg: SciAgentConfig, device="cpu", seed: int = 0, init_std: float = 0.02,
-                 head_chunk: int = 4096):
+                 head_chunk: int = 16384):
         super().__init__()
         cfg.validate()
         self.cfg = cfg

@@ -19,8 +19,18 @@ import torch
 
 from . import _lib
 
-_NUM_SMS = 148
+_sm_count: dict[int, int] = {}
 _workspaces: dict[int, torch.Tensor] = {}
+
+
+def num_sms(device=None) -> int:
+    """Streaming multiprocessors of the device (148 on a B200), asked of the driver once per device."""
+    idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+    n = _sm_count.get(idx)
+    if n is None:
+        n = torch.cuda.get_device_properties(idx).multi_processor_count
+        _sm_count[idx] = n
+    return n
 
 # Count of native kernel launches, for benchmark reporting.
 launch_count = 0
@@ -38,9 +48,11 @@ def _workspace(nfloats: int, device) -> torch.Tensor:
 def _pick_splits(M: int, N: int, K: int, bn: int) -> int:
     tiles = ((M + 127) // 128) * ((N + bn - 1) // bn)
     num_kb = (K + 63) // 64
-    if tiles >= _NUM_SMS // 2 or num_kb < 16:
+    sms = num_sms()
+    if tiles >= sms // 2 or num_kb < 16:
         return 1
-    s = min((_NUM_SMS + tiles - 1) // tiles, num_kb // 8, 16)
+    # as many k-splits as keep tiles * splits within ONE wave of CTAs (a second, nearly empty wave doubles the time)
+    s = min(max(1, sms // tiles), num_kb // 8, 16)
     return max(1, s)
 
 
@@ -65,7 +77,11 @@ FUSE_SWIGLU = os.environ.get("SB_FUSE_SWIGLU", "0") == "1"
 # pairs). It wins when tiles are long (weight-gradient products, K = tokens) AND there is at least one
 # whole wave besides the partial one; with less than one wave of tiles, or short K, whole tiles stay.
 _BALANCED_MIN_K = 4096
-_PAIRS = _NUM_SMS // 2
+
+
+# Long-K products with few output tiles (weight gradients: K = tokens) also run on CTA pairs: the balanced schedule
+# deals their k-blocks evenly over all pairs (every SM busy whatever the tile count) and the fix-up pass adds the parts.
+_PAIR_LONGK = os.environ.get("SB_GEMM_PAIR_LONGK", "1") != "0"
 
 
 def _use_pair(M, N, K, splits, bn) -> bool:
@@ -74,11 +90,15 @@ def _use_pair(M, N, K, splits, bn) -> bool:
     if PAIR_MODE == "1":
         return True
     pair_tiles = ((M + 255) // 256) * ((N + 255) // 256)
-    return pair_tiles >= 40 and K >= 256
+    if pair_tiles >= 40 and K >= 256:
+        return True
+    return _PAIR_LONGK and BALANCED and pair_tiles >= 4 and K >= 8192 and M >= 256 and N >= 256
 
 
 def _use_balanced(tiles: int, workers: int, K: int) -> bool:
-    return BALANCED and K >= _BALANCED_MIN_K and (tiles >= workers or _BALANCED_MIN_K == 0)
+    if not BALANCED or K < _BALANCED_MIN_K:
+        return False
+    return tiles >= workers or _BALANCED_MIN_K == 0 or (_PAIR_LONGK and K >= 8192)
 
 
 class _Bias:
@@ -119,7 +139,8 @@ def _gemm(a, b, M, N, K, a_mn, b_mn, out, residual, splits, bn, bias=None):
     if _use_pair(M, N, K, splits, bn):
         st = _lib.status_word(a.device)
         pair_tiles = ((M + 255) // 256) * ((N + 255) // 256)
-        ws = _workspace(_PAIRS * 3 * 256 * 256, a.device) if _use_balanced(pair_tiles, _PAIRS, K) else None
+        pairs = num_sms(a.device) // 2
+        ws = _workspace(pairs * 3 * 256 * 256, a.device) if _use_balanced(pair_tiles, pairs, K) else None
         _lib.call("sb_gemm_pair_bf16", a.data_ptr(), b.data_ptr(), out.data_ptr(), residual.data_ptr() if residual is not None else None, M, N, K,
                   a.stride(0), b.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
                   int(a_mn), int(b_mn), _lib.ptr(ws), None, 0, 0, None, 0, st.data_ptr(), _lib.stream())
@@ -131,9 +152,9 @@ def _gemm(a, b, M, N, K, a_mn, b_mn, out, residual, splits, bn, bias=None):
         # balanced schedule: whole waves one tile per CTA, the last partial wave's k-blocks dealt out
         # evenly over all SMs and finished by a fix-up pass (fixed k order)
         tiles = ((M + 127) // 128) * ((N + bn - 1) // bn)
-        splits = 0 if _use_balanced(tiles, _NUM_SMS, K) else _pick_splits(M, N, K, bn)
+        splits = 0 if _use_balanced(tiles, num_sms(a.device), K) else _pick_splits(M, N, K, bn)
     if splits == 0:
-        ws = _workspace(_NUM_SMS * 3 * 128 * 256, a.device)
+        ws = _workspace(num_sms(a.device) * 3 * 128 * 256, a.device)
     else:
         ws = _workspace(splits * M * N, a.device) if splits > 1 else None
     st = _lib.status_word(a.device)

@@ -57,7 +57,19 @@ def main():
     tp_steps = teacher_forced_logits(tp, prompts, ref_tokens).cpu()
     step_err = (tp_steps - ref_steps).abs().amax(dim=(0, 2))
     step_scale = ref_steps.abs().amax(dim=(0, 2)).clamp(min=1.0)
-    assert bool((step_err <= 3e-2 * step_scale).all()), f"rank {rank}: per-step logits differ: {step_err.tolist()}"
+    # int8: a rank quantises its own shard, so the row-parallel matrices get other per-column scales than the
+    # unsharded matrix and the two engines differ by quantisation noise, not by rounding order
+    tol = 1e-1 if quant else 3e-2
+    assert bool((step_err <= tol * step_scale).all()), f"rank {rank}: per-step logits differ: {step_err.tolist()}"
+    if use_cuda and backend == "fused" and tp.gemv_chan is not None:
+        # the GEMV that performs its own all-reduce must give the bits of the GEMV + stand-alone all-reduce pair
+        os.environ["SB_TP_FUSED_GEMV"] = "0"
+        tp2 = TPInferenceEngine(model, quant=quant, max_batch=B, max_seq=P + NEW + 1, page=16, backend=backend)
+        os.environ.pop("SB_TP_FUSED_GEMV")
+        assert tp2.gemv_chan is None
+        pair_steps = teacher_forced_logits(tp2, prompts, ref_tokens).cpu()
+        assert torch.equal(pair_steps, tp_steps), "fused GEMV + all-reduce differs from the two-kernel path"
+        tp2.close()
     match = (tokens == ref_tokens).float().mean().item()       # reported, not asserted
     if use_cuda:
         from scirust_b200.ops import _lib
