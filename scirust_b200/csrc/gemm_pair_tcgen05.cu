@@ -69,19 +69,25 @@ struct Params {
   // of storing it, the epilogue reads the saved [gate | up] row of the forward pass and writes
   // dgu = [dh * up * silu'(gate) | dh * silu(gate)] into C [M, 2N].
   const void* gu; int ld_gu;
-  // All-gather -> GEMM (ag.W > 1): A's rows are sharded over the ranks (rank s holds rows
-  // [s*rows, (s+1)*rows) in its own buffer a_peer[s], row pitch lda). The copier warps of every CTA
-  // pull ALL shards (the local one too) into the local landing buffer that tmap_a describes,
-  // 128-row chunk by chunk, own rows first, then rank+1's, ...; a chunk's counter raises its flag and
-  // the TMA producer waits (bounded) for the flag of the chunk it is about to read. Tiles are walked in
-  // the same rotated order. flags[r]: this call site's slot on rank r ([0*16+s] "rank s's shard is
-  // final", [1*16+s] "rank s has stopped reading my shard").
+  // All-gather -> GEMM (ag.W >= 1): A's rows are sharded over the ranks (rank s holds rows
+  // [s*rows, (s+1)*rows) in its own buffer a_peer[s], row pitch lda). Every rank PUSHES its shard into the
+  // landing buffers of all peers (stage_peer[r], peer-mapped, [M, ld_stage]; plain 16-byte stores, which, unlike
+  // loads, need no round trip over NVLink): the copier warps of the CTAs work in teams on one 128-row chunk for
+  // one destination at a time, first for the peer that needs this shard first (rank-1), then rank-2, ...; the
+  // team member that completes a chunk raises chunk_flags[chunk] on the destination. The own shard is read in
+  // place (tmap_a_own). The TMA producer waits (bounded) for the flag of the chunk it is about to read and walks
+  // the row tiles in the matching rotated order (own rows, then rank+1's, ...). flags[r]: this call site's slot on
+  // rank r; [1*16+s] "rank s has consumed its landing buffer": nobody leaves the kernel before every rank has,
+  // so the next call's pushes cannot overwrite rows that a slower rank is still reading.
   struct {
     int W, rank, rows;
-    const void* a_peer[MAXW]; int lda;
-    void* a_stage; int ld_stage;
+    const void* a_peer[MAXW]; int lda;     // only a_peer[rank] (the local shard) is read
+    void* a_stage; int ld_stage;           // the local landing buffer (= stage_peer[rank])
+    void* stage_peer[MAXW];
     uint32_t* flags[MAXW];
-    uint32_t* chunk_flags; unsigned int* chunk_ctr; unsigned int* cta_ctr;
+    uint32_t* chunk_flags;                 // local: chunk_flags[chunk], raised by the rank that pushed the chunk
+    uint32_t* chunk_flags_peer[MAXW];
+    unsigned int* chunk_ctr; unsigned int* cta_ctr;
     uint32_t epoch;
     uint64_t wait_ns;
     int team;        // CTAs that share one chunk; teams work on different chunks at the same time
@@ -185,11 +191,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                        : (rs ? ((p.rs.rank + 1) % p.rs.W) * (mt2 / p.rs.W) : 0);   // the next rank's rows first, own rows last
 
   if (threadIdx.x == 0) {
-    if (ag && blockIdx.x == 0) {
-      // my shard is final (stream order): tell every peer
-      __threadfence_system();
-      for (int r = 0; r < p.ag.W; ++r) p_st_release_sys(p.ag.flags[r] + 0 * FLAG_STRIDE + p.ag.rank, p.ag.epoch);
-    }
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);     // leader's producer arms it; both CTAs' copies complete on it
       mbar_init(&empty_bar[s], 1);    // one commit arrival (delivered to both CTAs)
@@ -234,7 +235,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int row_own = row0 - (ag ? p.ag.rank * p.ag.rows : 0);
         if (ag && !own_rows && row0 < p.M) {
           // these 128 rows must have landed in the local buffer (copier warps of a team of CTAs)
-          if (!p_wait_flag<false>(p.ag.chunk_flags + row0 / BM, p.ag.epoch, p.ag.wait_ns, p.status)) { ok = false; break; }
+          if (!p_wait_flag<true>(p.ag.chunk_flags + row0 / BM, p.ag.epoch, p.ag.wait_ns, p.status)) { ok = false; break; }
           asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy stores -> TMA reads
         }
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
@@ -299,7 +300,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else if (warp >= 10) {
     // -------------------------------- copiers (both CTAs) ---------------------------------
-    if (ag && !A_MN) {
+    if (ag && !A_MN && p.ag.W > 1) {
       const int cw = warp - 10;
       const int cpr = p.ag.rows / BM;                                        // chunks per rank
       const size_t vec_per_row = static_cast<size_t>(p.K) / 8;               // 16-byte words per row
@@ -307,21 +308,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int team = p.ag.team, n_teams = gridDim.x / team;
       const int my_team = blockIdx.x / team, member = blockIdx.x - my_team * team;
       const size_t lo = vec_per_chunk * member / team, hi = vec_per_chunk * (member + 1) / team;
-      const int n_remote = (p.ag.W - 1) * cpr;                               // chunks in the order they are needed
-      uint32_t ready_mask = 0;
-      for (int i = my_team; i < n_remote && my_team < n_teams; i += n_teams) {
-        const int src = (p.ag.rank + 1 + i / cpr) % p.ag.W;
+      const int n_items = (p.ag.W - 1) * cpr;                                // (destination, chunk) pairs, in the order
+      const uint4* mine = static_cast<const uint4*>(p.ag.a_peer[p.ag.rank]);  // the destinations need them
+      for (int i = my_team; i < n_items && my_team < n_teams; i += n_teams) {
+        const int dst = (p.ag.rank + p.ag.W - 1 - i / cpr) % p.ag.W;          // rank-1 first: it reads my shard first
         const int ci = i % cpr;
-        if (!(ready_mask & (1u << src))) {
-          int ready = 1;
-          if (lane == 0)
-            ready = p_wait_flag<true>(p.ag.flags[p.ag.rank] + 0 * FLAG_STRIDE + src, p.ag.epoch, p.ag.wait_ns, p.status) ? 1 : 0;
-          ready = __shfl_sync(0xffffffffu, ready, 0);
-          if (!ready) break;
-          ready_mask |= 1u << src;
-        }
-        const uint4* peer = static_cast<const uint4*>(p.ag.a_peer[src]);
-        const int chunk = src * cpr + ci;
+        const int chunk = p.ag.rank * cpr + ci;                               // row chunk of the gathered matrix
+        uint4* land = static_cast<uint4*>(p.ag.stage_peer[dst]);
         const size_t prow0 = static_cast<size_t>(ci) * BM, srow0 = static_cast<size_t>(chunk) * BM;
         for (size_t v0 = lo + (cw * 32 + lane); v0 < hi; v0 += COPY_WARPS * 32 * CP_UNROLL) {
           uint4 tmp[CP_UNROLL];
@@ -331,24 +324,25 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             idx[u] = v0 + static_cast<size_t>(u) * COPY_WARPS * 32;
             if (idx[u] < hi) {
               const size_t r = idx[u] / vec_per_row, c = idx[u] - r * vec_per_row;
-              const uint4* src_p = peer + ((prow0 + r) * p.ag.lda) / 8 + c;
-              asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                           : "=r"(tmp[u].x), "=r"(tmp[u].y), "=r"(tmp[u].z), "=r"(tmp[u].w) : "l"(src_p) : "memory");
+              tmp[u] = __ldg(mine + ((prow0 + r) * p.ag.lda) / 8 + c);
             }
           }
 #pragma unroll
           for (int u = 0; u < CP_UNROLL; ++u) {
             if (idx[u] < hi) {
               const size_t r = idx[u] / vec_per_row, c = idx[u] - r * vec_per_row;
-              *(static_cast<uint4*>(p.ag.a_stage) + ((srow0 + r) * p.ag.ld_stage) / 8 + c) = tmp[u];
+              *(land + ((srow0 + r) * p.ag.ld_stage) / 8 + c) = tmp[u];
             }
           }
         }
-        __threadfence();
+        __threadfence_system();        // this warp's stores have reached the destination
         __syncwarp();
         if (lane == 0) {
-          const unsigned int prev = atomicAdd(p.ag.chunk_ctr + chunk, 1u);
-          if (prev + 1 == static_cast<unsigned int>(team) * COPY_WARPS) p_st_release_gpu(p.ag.chunk_flags + chunk, p.ag.epoch);
+          const unsigned int prev = atomicAdd(p.ag.chunk_ctr + i, 1u);
+          if (prev + 1 == static_cast<unsigned int>(team) * COPY_WARPS) {
+            __threadfence_system();
+            p_st_release_sys(p.ag.chunk_flags_peer[dst] + chunk, p.ag.epoch);
+          }
         }
       }
     }
@@ -670,14 +664,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   }
   if (ag && threadIdx.x == 0) {
-    // last CTA: reset the counters; tell the peers this rank has stopped reading their shards and stay
-    // until they have stopped reading this rank's shard (the caller may then overwrite it)
+    // last CTA: reset the counters; tell the peers this rank has consumed its landing buffer and stay until every
+    // peer has consumed its own (all pushes of this call have then been read, and the next call may push again)
     __threadfence();
     const unsigned int prev = atomicAdd(p.ag.cta_ctr, 1u);
     if (prev == gridDim.x - 1) {
       *p.ag.cta_ctr = 0;
       const int chunks = p.ag.W * (p.ag.rows / BM);
-      for (int i = 0; i < chunks; ++i) p.ag.chunk_ctr[i] = 0;
+      for (int i = 0; i < chunks; ++i) p.ag.chunk_ctr[i] = 0;      // (W - 1) * chunks-per-rank of them were used
       if (*reinterpret_cast<volatile int*>(p.status) == 0) {
         __threadfence_system();
         for (int r = 0; r < p.ag.W; ++r) p_st_release_sys(p.ag.flags[r] + 1 * FLAG_STRIDE + p.ag.rank, p.ag.epoch);
@@ -823,12 +817,14 @@ extern "C" int sb_gemm_pair_bf16(const void* A, const void* B, void* C, const vo
 }
 
 // All-gather -> GEMM on CTA pairs: C[M,N] = gather(A shards)[M,K] * op(B) (+ R). a_ptrs[s]: rank s's shard
-// [M/W, lda] (peer-mapped); a_stage: local landing buffer [M, ld_stage]; flag_ptrs[r]: this call site's flag
-// slot on rank r; chunk_flags / chunk_ctr: M/128 words each, cta_ctr one word (counters zero on entry, left
-// zero). (M / W) % 256 == 0, K % 8 == 0. B is local ([K,N] when b_mn, else [N,K]).
+// [M/W, lda] (only entry `rank`, the local one, is read); stage_ptrs[r]: rank r's landing buffer [M, ld_stage]
+// (peer-mapped: every rank pushes its shard into every peer's); flag_ptrs[r]: this call site's flag slot on rank r;
+// chunk_flag_ptrs[r]: rank r's M/128 chunk epochs (peer-mapped, zero when created); chunk_ctr: M/128 local words,
+// cta_ctr one local word (zero on entry, left zero). (M / W) % 256 == 0, K % 8 == 0. B is local ([K,N] when b_mn,
+// else [N,K]).
 extern "C" int sb_gemm_pair_ag_bf16(void* const* a_ptrs, const void* B, void* C, const void* R, int M, int N, int K,
-                                    int lda, int ldb, int ldc, int ldr, int b_mn, void* a_stage, int ld_stage,
-                                    void* const* flag_ptrs, uint32_t* chunk_flags, unsigned int* chunk_ctr,
+                                    int lda, int ldb, int ldc, int ldr, int b_mn, void* const* stage_ptrs, int ld_stage,
+                                    void* const* flag_ptrs, void* const* chunk_flag_ptrs, unsigned int* chunk_ctr,
                                     unsigned int* cta_ctr, int rank, int W, uint32_t epoch, int wait_ms, int* status,
                                     void* stream_) {
   using namespace sb::pair;
@@ -836,6 +832,7 @@ extern "C" int sb_gemm_pair_ag_bf16(void* const* a_ptrs, const void* B, void* C,
   if (M <= 0 || N <= 0 || K <= 0 || W < 1 || W > MAXW || rank < 0 || rank >= W) return SB_ERR_ARG;
   if ((N & 7) || (K & 7) || (lda & 7) || (ld_stage & 7) || (ldc & 7) || (R && (ldr & 7)) || (M % (W * 2 * BM)))
     return SB_ERR_ARG;
+  void* a_stage = stage_ptrs[rank];
   if ((reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(a_stage) & 15)) return SB_ERR_ALIGN;
   CUtensorMap ta, tb;
   int rc = make_tmap_2d_bf16(&ta, a_stage, K, M, ld_stage, BK, BM);
@@ -855,8 +852,10 @@ extern "C" int sb_gemm_pair_ag_bf16(void* const* a_ptrs, const void* B, void* C,
   for (int r = 0; r < MAXW; ++r) {
     p.ag.a_peer[r] = r < W ? a_ptrs[r] : nullptr;
     p.ag.flags[r] = r < W ? static_cast<uint32_t*>(flag_ptrs[r]) : nullptr;
+    p.ag.stage_peer[r] = r < W ? stage_ptrs[r] : nullptr;
+    p.ag.chunk_flags_peer[r] = r < W ? static_cast<uint32_t*>(chunk_flag_ptrs[r]) : nullptr;
   }
-  p.ag.chunk_flags = chunk_flags; p.ag.chunk_ctr = chunk_ctr; p.ag.cta_ctr = cta_ctr;
+  p.ag.chunk_flags = static_cast<uint32_t*>(chunk_flag_ptrs[rank]); p.ag.chunk_ctr = chunk_ctr; p.ag.cta_ctr = cta_ctr;
   p.ag.epoch = epoch;
   p.ag.wait_ns = wait_ms > 0 ? static_cast<uint64_t>(wait_ms) * 1000000ull : 10000000000ull;
   // every CTA pair runs copier warps, so the whole device is launched whatever the tile count

@@ -2,13 +2,18 @@
 
 Activations between blocks are sharded over the token dimension (rank r holds rows
 ``[r*T/W, (r+1)*T/W)``); inside a block the QKV and gate/up projections are column-parallel and the
-o_proj / down projections row-parallel. Each boundary is one fused kernel
-(csrc/gemm_dist_tcgen05.cu):
+o_proj / down projections row-parallel. Each boundary is one fused kernel on CTA pairs
+(csrc/gemm_pair_tcgen05.cu; csrc/gemm_dist_tcgen05.cu for shapes whose rows per rank are not a
+multiple of 256):
 
-* ``ag_matmul``   all-gather -> GEMM: the sharded operand is read tile by tile from the owning
-  rank's memory by TMA while the tensor cores run; nothing is gathered into a buffer.
-* ``matmul_rs``   GEMM -> reduce-scatter: partial tiles go straight from the epilogue to the owning
-  rank, which adds the W partials in rank order (+ residual).
+* ``ag_matmul``   all-gather -> GEMM: every rank pushes its shard, 128-row chunk by chunk, into the
+  peers' landing buffers with plain peer stores while the tensor cores already work on the rows that
+  have arrived (own rows first); a remote row crosses NVLink once and is then read from local memory
+  by TMA for every output column tile.
+* ``matmul_rs``   GEMM -> reduce-scatter: the epilogue sends every finished tile straight to the
+  rank that owns its rows (TMA tensor store into that rank's receive buffer, slot = source rank),
+  under the main loop of the following tiles; the owner adds the W slots of a row block in rank order
+  (+ residual) from local memory as soon as the block is complete.
 
 ``backend="nccl"`` runs the same math as NCCL all-gather / reduce-scatter around library GEMMs
 (`torch.matmul`): the baseline configuration the fused path is measured against. The reference has
@@ -70,7 +75,7 @@ class TPContext:
         self._named = {}
         if backend == "fused":
             stage_bytes = max_rows * max_cols * 2          # W * (rows/W) * cols bf16
-            total = 2 * stage_bytes + sym_bytes + (1 << 20)
+            total = 3 * stage_bytes + sym_bytes + (1 << 20)
             self.region = SymmetricRegion(group, total, device=self.dev)
             self.stage = [self.region.tensor((max_rows * max_cols,), BF) for _ in range(2)]
             self.stage_ptrs = [self.region.peer_ptrs(s) for s in self.stage]
@@ -79,9 +84,15 @@ class TPContext:
             self.flag_ptrs = (C.c_void_p * self.world)(
                 *[b + self.region.data_bytes + self.slot * wps * 4 for b in self.region.peer_base])
             self.counters = torch.zeros(32, dtype=torch.int32, device=self.dev)
-            # local landing buffer of the all-gather -> GEMM products (allocated on first use)
-            self._ag_stage = None
+            # landing buffer of the all-gather -> GEMM products: peer-mapped, every rank pushes its shard into it
+            self._ag_stage = self.region.tensor((max_rows * max_cols,), BF)
+            self._ag_stage_ptrs = self.region.peer_ptrs(self._ag_stage)
+            self._ag_chunk_flags = self.region.tensor((max_rows // 128 + 2,), torch.int32)
+            self._ag_chunk_flags.zero_()
+            self._ag_chunk_flag_ptrs = self.region.peer_ptrs(self._ag_chunk_flags)
             self._ag_flags = torch.zeros(2 * (max_rows // 128 + 2), dtype=torch.int32, device=self.dev)
+            # single-CTA distributed kernel (shapes the pair kernel refuses): its own local landing buffer
+            self._local_stage, self._local_stage_elems = None, max_rows * max_cols
             # reduce-scatter on the pair kernel: "block complete" epochs pushed by the peers, local counters
             self._rs_ready = self.region.tensor((8 * 512,), torch.int32)
             self._rs_ready.zero_()
@@ -111,20 +122,20 @@ class TPContext:
         """all-gather -> GEMM on the CTA-pair kernel (csrc/gemm_pair_tcgen05.cu): the shards land in a
         local buffer chunk by chunk while 256 x 256 tiles are computed over two SMs."""
         self.epoch += 1
-        if self._ag_stage is None or self._ag_stage.numel() < M * K:
-            self._ag_stage = torch.empty(M * K, dtype=BF, device=self.dev)
+        if M * K > self._ag_stage.numel():
+            raise ValueError("all-gather landing buffer too small for this product")
         n = self._ag_flags.numel() // 2
         _lib.call("sb_gemm_pair_ag_bf16", self.region.peer_ptrs(x_shard), w.data_ptr(), out.data_ptr(), None, M, N, K,
-                  x_shard.stride(0), w.stride(0), out.stride(0), 0, int(b_mn), self._ag_stage.data_ptr(), K,
-                  self.flag_ptrs, self._ag_flags.data_ptr(), self._ag_flags[n:].data_ptr(),
+                  x_shard.stride(0), w.stride(0), out.stride(0), 0, int(b_mn), self._ag_stage_ptrs, K,
+                  self.flag_ptrs, self._ag_chunk_flag_ptrs, self._ag_flags[n:].data_ptr(),
                   self._ag_flags[2 * n - 1:].data_ptr(), self.rank, self.world, self.epoch, self.wait_ms,
                   _lib.status_word(self.dev).data_ptr(), _lib.stream())
         _g.launch_count += 1
         return out
 
     def _rs_pair(self, a, w, out, residual, M, N, K, b_mn):
-        """GEMM -> reduce-scatter on the CTA-pair kernel: the partial product stays in this rank's
-        symmetric buffer and the owners pull and add the partials of their rows block by block."""
+        """GEMM -> reduce-scatter on the CTA-pair kernel: tiles are pushed into the owners' receive buffers
+        (``stage``: [W sources][rows / W][N] per rank) and the owners add the W slots block by block."""
         self.epoch += 1
         part = self.stage[self.rs_calls & 1]
         ptrs = self.stage_ptrs[self.rs_calls & 1]
@@ -140,9 +151,9 @@ class TPContext:
         _g.launch_count += 1
         return out
 
-    # Below this much work per rank the fused GEMM -> reduce-scatter is bound by its flag round trips (0.19 ms against
-    # 0.12 ms at 16384 x 1408 x 1024 on two GPUs); the product then runs on the plain GEMM and NCCL scatters it.
-    RS_FUSED_MIN_FLOP = float(os.environ.get("SB_TP_RS_MIN_GFLOP", "200")) * 1e9
+    # SB_TP_RS_MIN_GFLOP: products below this much work per rank run as plain GEMM + NCCL reduce-scatter instead of
+    # the fused kernel (0 = the fused kernel always; kept as a switch for comparisons).
+    RS_FUSED_MIN_FLOP = float(os.environ.get("SB_TP_RS_MIN_GFLOP", "0")) * 1e9
 
     def _rs_small(self, M, N, K):
         return 2.0 * M * N * K < self.RS_FUSED_MIN_FLOP and self._pair_min_world == 2
@@ -158,7 +169,7 @@ class TPContext:
 
     def _pair_ok(self, M, K):
         return (self.pair and self.world >= self._pair_min_world and M % (self.world * 256) == 0 and K % 8 == 0
-                and M // 128 + 2 <= self._ag_flags.numel() // 2)
+                and M // 128 + 2 <= self._ag_flags.numel() // 2 and M * K <= self._ag_stage.numel())
 
     def _call(self, a, b, out, residual, M, N, K, a_mn, b_mn, a_gather, b_gather, scatter, bn=0):
         self.epoch += 1
@@ -169,10 +180,11 @@ class TPContext:
             if M * N > self.stage[0].numel():
                 raise ValueError("reduce-scatter staging area too small for this product")
         ag_stage, ld_stage, cflags, cctr = None, 0, None, None
-        if a_gather and not a_mn and self.world > 1 and M // 128 + 2 <= self._ag_flags.numel() // 2:
-            if self._ag_stage is None or self._ag_stage.numel() < M * K:
-                self._ag_stage = torch.empty(M * K, dtype=BF, device=self.dev)
-            ag_stage, ld_stage = self._ag_stage.data_ptr(), K
+        if (a_gather and not a_mn and self.world > 1 and M // 128 + 2 <= self._ag_flags.numel() // 2
+                and M * K <= self._local_stage_elems):
+            if self._local_stage is None:
+                self._local_stage = torch.empty(self._local_stage_elems, dtype=BF, device=self.dev)
+            ag_stage, ld_stage = self._local_stage.data_ptr(), K
             half = self._ag_flags.numel() // 2
             cflags, cctr = self._ag_flags.data_ptr(), self._ag_flags[half:].data_ptr()
         _lib.call("sb_gemm_dist_bf16", self._ptrs(a, a_gather), self._ptrs(b, b_gather), out.data_ptr(),

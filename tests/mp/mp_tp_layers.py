@@ -14,8 +14,12 @@ from scirust_b200.ops import _lib  # noqa: E402
 from scirust_b200.parallel.tensor_parallel import TPContext  # noqa: E402
 
 BF = torch.bfloat16
-T, d, Nr, Kr = 256 * world * 2, 512, 384, 256   # tokens, model dim, column shard, row shard
+# tokens, model dim, column shard, row shard; rows per rank from the environment (a multiple of 256 runs on the
+# CTA-pair kernels, anything else on the single-CTA distributed kernel)
+ROWS = int(os.environ.get("SB_TP_ROWS_PER_RANK", "512"))
+T, d, Nr, Kr = ROWS * world, 512, 384, 256
 Tl = T // world
+N_ODD = 320      # an output width that ends inside a 64-column store slab and a 256-column tile
 
 
 def rnd(shape, seed):
@@ -36,6 +40,10 @@ dy_loc = rnd((T, Nr), 40 + rank)         # local gradient with all tokens (colum
 dy_full = rnd((T, d), 2)
 dy_shard = fused.buffer("dy", (Tl, d)); dy_shard.copy_(dy_full[rank * Tl:(rank + 1) * Tl])
 res = rnd((Tl, d), 50 + rank)
+w_row_odd = rnd((Kr, N_ODD), 60 + rank)  # row-parallel weight with a ragged output width
+x_odd_full = rnd((T, N_ODD), 3)          # gathered operand with a ragged contraction width
+x_odd = fused.buffer("x_odd", (Tl, N_ODD)); x_odd.copy_(x_odd_full[rank * Tl:(rank + 1) * Tl])
+w_col_odd = rnd((N_ODD, Nr), 70 + rank)
 
 
 def close(a, b, what):
@@ -69,19 +77,43 @@ for rep in range(2):
     y4 = fused.matmul_nt_rs(dy_loc, w_col); sync()
     close(y4, ref, "matmul_nt_rs")
 
+    # ragged widths: output columns / contraction length that are not multiples of the tile sizes
+    parts_o = [torch.empty((T, N_ODD), dtype=torch.float32, device=dev) for _ in range(world)]
+    dist.all_gather(parts_o, (a_loc.float() @ w_row_odd.float()))
+    ref = sum(p[rank * Tl:(rank + 1) * Tl] for p in parts_o)
+    y5 = fused.matmul_nn_rs(a_loc, w_row_odd); sync()
+    close(y5, ref, "matmul_nn_rs ragged N")
+    y6 = fused.ag_matmul_nn(x_odd, w_col_odd); sync()
+    close(y6, x_odd_full.float() @ w_col_odd.float(), "ag_matmul_nn ragged K")
+
     # weight gradients with one operand gathered along the contraction (token) dimension
     g1 = fused.ag_matmul_tn(x_shard, dy_loc); sync()
     close(g1, x_full.float().t() @ dy_loc.float(), "ag_matmul_tn")
     g2 = fused.matmul_tn_ag(a_loc, dy_shard); sync()
     close(g2, a_loc.float().t() @ dy_full.float(), "matmul_tn_ag")
     if rep == 0:
-        first = [t.clone() for t in (y1, y2, y3, y4, g1, g2)]
+        first = [t.clone() for t in (y1, y2, y3, y4, y5, y6, g1, g2)]
     else:
-        for a, b in zip(first, (y1, y2, y3, y4, g1, g2)):
+        for a, b in zip(first, (y1, y2, y3, y4, y5, y6, g1, g2)):
             assert torch.equal(a, b), "fused tensor-parallel products are not bitwise repeatable"
+
+# two fused products in flight on two streams (each with its own context: flag slots, staging and landing buffers
+# are per context), interleaved with each other on the GPU
+other = TPContext(dist.group.WORLD, T, d, sym_bytes=8 << 20, backend="fused")
+x_b = other.buffer("x", (Tl, d)); x_b.copy_(x_shard)
+side = torch.cuda.Stream()
+side.wait_stream(torch.cuda.current_stream())
+for _ in range(3):
+    ya = fused.matmul_nn_rs(a_loc, w_row, residual_shard=res)
+    with torch.cuda.stream(side):
+        yb = other.ag_matmul_nn(x_b, w_col)
+torch.cuda.current_stream().wait_stream(side)
+sync()
+assert torch.equal(ya, first[2]) and torch.equal(yb, first[0]), "concurrent fused products disturbed one another"
+other.close()
 
 dist.barrier()
 if rank == 0:
-    print("TP_OK")
+    print(f"TP_OK world={world} rows_per_rank={ROWS}")
 fused.close()
 dist.destroy_process_group()

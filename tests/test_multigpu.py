@@ -51,6 +51,23 @@ def test_tp_fused_layers_match_nccl_baseline():
     assert "TP_OK" in out
 
 
+@pytest.mark.parametrize("world,rows", [(2, 256), (2, 768), (2, 200), (4, 256), (4, 768), (8, 256), (8, 768)])
+def test_tp_fused_layers_world_and_rows(world, rows):
+    """Rows per rank of one and three 256-row blocks (CTA-pair kernels) and off the 256 grid (single-CTA
+    distributed kernel), at every world size the box offers."""
+    _need(world)
+    out = _run("mp_tp_layers.py", world, 29620 + world, extra_env={"SB_TP_ROWS_PER_RANK": str(rows)},
+               tag=f"_w{world}_r{rows}")
+    assert f"TP_OK world={world} rows_per_rank={rows}" in out
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_fused_allreduce_larger_worlds(world):
+    _need(world)
+    out = _run("mp_allreduce.py", world, 29630 + world, tag=f"_w{world}")
+    assert "ALLREDUCE_OK" in out
+
+
 def test_tp_decoder_trains_like_single_gpu():
     _need(2)
     out = _run("mp_tp_model.py", 2, 29614, extra_env={"SB_TP_RS_MIN_GFLOP": "0"})
