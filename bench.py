@@ -168,8 +168,10 @@ def train_arm(args, rank, local_rank, world, dev):
             from scirust_b200.parallel.tensor_parallel import TPContext
 
             def build_trainer(comm):  # noqa: F811
-                # peer-visible buffers: two [tokens / W, d] activations per layer plus the gradient pair
-                sym = (2 * cfg.n_layers + 4) * (B * S // world) * cfg.d_model * 2 + (64 << 20)
+                # peer-visible buffers: two [tokens / W, d] activation shards and their two gathered [tokens, d]
+                # copies per layer, plus the gradient pair and its gathered copies
+                sym = ((2 * cfg.n_layers + 4) * (B * S // world) + (2 * cfg.n_layers + 2) * B * S) * cfg.d_model * 2
+                sym += 64 << 20
                 tp = TPContext(dist.group.WORLD, B * S, cfg.d_model, sym_bytes=sym, backend=comm)
                 m = TPDecoder(cfg, tp, seed=1234)
                 return Trainer(m, TrainerConfig(lr=3e-4, weight_decay=0.1, max_grad_norm=1.0))
@@ -288,6 +290,11 @@ def train_arm(args, rank, local_rank, world, dev):
         "clocks": clocks,
         "final_loss": last,
     }
+    tpc = getattr(getattr(trainer, "model", None), "tp", None)
+    if tpc is not None and getattr(tpc, "_prof", None) is not None and rank == 0:
+        for key, (n, ms) in sorted(tpc.profile_report().items(), key=lambda kv: -kv[1][1]):
+            print(f"[tp-profile] {key[0]:<14} {str(key[1]):<16} {str(key[2]):<16} calls {n:5d}  "
+                  f"{ms / max(n, 1) * 1e3:8.1f} us/call  {ms:9.2f} ms total", file=sys.stderr)
     del trainer
     return out
 

@@ -50,6 +50,7 @@ def main():
         for _ in range(a.iters):
             scratch.zero_()
             dist.barrier()
+            torch.cuda._sleep(400_000)      # the GPU spins ~0.2 ms while the host queues the call
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             fn()

@@ -6,7 +6,8 @@
 
 Per rank, W ranks, T tokens: the column-parallel product all-gather(x [T/W, d]) @ W1 [d, ff/W] and the
 row-parallel product reduce-scatter(h [T, ff/W] @ W2 [ff/W, d]). Times are CUDA events on the launching
-stream after warm-up, maximum over ranks; every iteration's inputs are larger than L2 together with a
+stream after warm-up (the call is queued behind a short spin kernel, so the host's launch latency is not in the
+interval), maximum over ranks; every iteration's inputs are larger than L2 together with a
 256 MiB scratch rewrite between iterations. The roofline time of a fused kernel is the slower of its FLOPs at
 the measured bf16 GEMM rate and the bytes it must move over NVLink at the measured peer-copy rate.
 """
@@ -40,6 +41,7 @@ def timed(fn, iters, warmup, scratch):
         scratch.zero_()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         dist.barrier()
+        torch.cuda._sleep(400_000)      # the GPU spins ~0.2 ms while the host queues the call: no launch latency in the time
         e0.record()
         fn()
         e1.record()

@@ -197,10 +197,15 @@ def cmd_sciagent(a):
     if a.action == "attest":
         from pathlib import Path
         mb = (Path(a.checkpoint) / "model.safetensors").read_bytes()
-        rec = {"model_sha256": hashlib.sha256(mb).hexdigest(), "model_bytes": len(mb),
-               "kernel_semantics_version": CK.MODEL_SEMANTICS_VERSION}
+        from .io import execution_attestation as EA
+        tok_sha = EA.file_sha256(a.tokenizer) if a.tokenizer else EA.sha256_hex(b"")
+        model_sha = hashlib.sha256(mb).hexdigest()
+        rec = {"model_sha256": model_sha, "model_bytes": len(mb),
+               "model_semantics_version": CK.MODEL_SEMANTICS_VERSION,
+               "training_route": json.loads(EA.build_training_route_attestation(model_sha, tok_sha).to_json()),
+               "decode_route": json.loads(EA.build_decode_route_attestation(model_sha, tok_sha).to_json())}
         if a.tokenizer:
-            rec["tokenizer_sha256"] = hashlib.sha256(Path(a.tokenizer).read_bytes()).hexdigest()
+            rec["tokenizer_sha256"] = tok_sha
         print(json.dumps(rec, indent=2, sort_keys=True))
         return EXIT_OK
     return EXIT_USAGE
@@ -342,6 +347,204 @@ def cmd_calibrate(a):
     return EXIT_OK
 
 
+
+def cmd_lm(a):
+    """Next-token training of a one-block decoder on a token sequence with a chosen optimizer of the zoo
+    (scirust-cli/src/nlp.rs:214-330)."""
+    import torch
+    from .autodiff import nd_optim as NO
+    from .nn.zoo import NdDecoderLM
+    try:
+        toks = [int(t) for t in a.tokens.split(",") if t.strip()]
+    except ValueError:
+        sys.stderr.write("error: tokens must be non-negative integers\n")
+        return EXIT_USAGE
+    if len(toks) < 2 or min(toks) < 0:
+        sys.stderr.write("error: need at least 2 non-negative tokens for next-token training\n")
+        return EXIT_USAGE
+    torch.manual_seed(a.seed)
+    vocab = max(toks) + 1
+    model = NdDecoderLM(vocab, d_model=16, n_layers=1, n_heads=2, n_kv_heads=1, d_ff=32)
+    table = {"adam": lambda p: torch.optim.Adam(p, lr=a.lr), "adamw": lambda p: torch.optim.AdamW(p, lr=a.lr),
+             "lion": lambda p: NO.Lion(p, lr=a.lr * 0.3), "lamb": lambda p: NO.LAMB(p, lr=a.lr),
+             "adan": lambda p: NO.Adan(p, lr=a.lr), "adafactor": lambda p: NO.Adafactor(p, lr=a.lr),
+             "ademamix": lambda p: NO.AdEMAMix(p, lr=a.lr), "soap": lambda p: NO.SOAP(p, lr=a.lr),
+             "shampoo": lambda p: NO.Shampoo(p, lr=a.lr), "prodigy": lambda p: NO.Prodigy(p),
+             "galore": lambda p: NO.GaLore(p, lr=a.lr), "schedule-free": lambda p: NO.ScheduleFreeSGD(p, lr=a.lr * 10),
+             "muon": lambda p: NO.Muon(p, lr=a.lr), "sophia": lambda p: NO.Sophia(p, lr=a.lr),
+             "lookahead": lambda p: NO.Lookahead(torch.optim.Adam(p, lr=a.lr))}
+    if a.opt not in table:
+        sys.stderr.write(f"error: unknown optimizer {a.opt!r}; known: {sorted(table)}\n")
+        return EXIT_USAGE
+    opt = table[a.opt](list(model.parameters()))
+    x = torch.tensor([toks[:-1]])
+    y = torch.tensor(toks[1:])
+    first = last = None
+    for step in range(a.steps):
+        logits = model(x)[0]
+        loss = torch.nn.functional.cross_entropy(logits, y)
+        if step == 0:
+            first = float(loss.detach())
+        if hasattr(opt, "zero_grad"):
+            opt.zero_grad()
+        loss.backward()
+        opt.step()
+        last = float(loss.detach())
+    pred = model(x)[0].argmax(-1).tolist()
+    acc = sum(int(p_ == t) for p_, t in zip(pred, toks[1:])) / len(pred)
+    print(f"lm: {len(toks)} tokens, vocab {vocab}, optimizer {a.opt}, seed {a.seed}")
+    print(f"  loss {first:.4f} -> {last:.4f} after {a.steps} steps; next-token accuracy {acc:.2f}")
+    print(f"  predicted continuation: {pred}")
+    return EXIT_OK if last == last else EXIT_NUMERICAL
+
+
+def cmd_certify(a):
+    """IBP and CROWN output bounds of a seeded 4->8->3 ReLU MLP over an L-infinity box
+    (scirust-cli/src/learning.rs:46-120)."""
+    import torch
+    from .certify import IbpLinear, IbpMlp, Interval, certified_robust, crown_bounds
+    if not (a.eps > 0 and a.eps == a.eps and a.eps != float("inf")):
+        sys.stderr.write("usage: scirust certify [--seed N] [--eps E]\nerror: --eps must be a positive number\n")
+        return EXIT_USAGE
+    g = torch.Generator().manual_seed(a.seed)
+    l1 = IbpLinear(torch.randn(4, 8, generator=g) * 0.5, torch.zeros(8))
+    l2 = IbpLinear(torch.randn(8, 3, generator=g) * 0.5, torch.zeros(3))
+    centre = [0.2, -0.5, 0.7, -0.1]
+    box = Interval.around(centre, a.eps)
+    mlp = IbpMlp([l1, l2])
+    pred = mlp.forward(centre)
+    cls = int(pred.argmax())
+    ibp, crown = mlp.certify(box), crown_bounds(l1, l2, box)
+    print(f"Certified bounds (seed {a.seed}): MLP 4->8->3 (ReLU), input {centre} -> class {cls}, eps = {a.eps}")
+    for name, out in (("IBP  ", ibp), ("CROWN", crown)):
+        verdict = (f"CERTIFIED: class {cls} cannot change in the box" if certified_robust(out, cls)
+                   else "not certified at this eps")
+        print(f"  {name} avg width {float(out.width().mean()):.4f}  {verdict}")
+        for c in range(3):
+            print(f"      y[{c}] in [{float(out.lo[c]):+.4f}, {float(out.hi[c]):+.4f}]")
+    return EXIT_OK
+
+
+def cmd_guard(a):
+    """Calibrate the statistical guard on synthetic 3-class probabilities and report coverage and verdicts
+    (scirust-cli/src/synergy.rs:90-160)."""
+    import torch
+    from .certify import StatisticalGuard
+    if not (0.0 < a.alpha < 1.0):
+        sys.stderr.write("usage: scirust guard [--seed N] [--alpha A]\nerror: --alpha must be in (0, 1)\n")
+        return EXIT_USAGE
+    g = torch.Generator().manual_seed(a.seed)
+
+    def sample(n):
+        y = torch.randint(0, 3, (n,), generator=g)
+        lg = torch.rand(n, 3, generator=g) * 2 - 1
+        lg[torch.arange(n), y] += 1.5
+        return torch.softmax(lg, -1), y
+    cp, cy = sample(2000)
+    guard = StatisticalGuard.calibrate(cp, cy, a.alpha)
+    tp, ty = sample(5000)
+    covered = sum(guard.covers(p_, int(t)) for p_, t in zip(tp, ty))
+    print(f"Statistical guard (seed {a.seed}): target coverage >= {1 - a.alpha:.2f}, "
+          f"empirical {covered / 5000:.4f} on 5000 fresh samples")
+    for name, p_ in (("confident", [0.92, 0.05, 0.03]), ("ambiguous", [0.48, 0.46, 0.06]),
+                     ("flat", [0.34, 0.33, 0.33])):
+        verdict, cls = guard.decide(p_)
+        text = {"accept": f"ACCEPT class {cls}", "abstain": "ABSTAIN (ambiguous: flag for review)",
+                "reject": "REJECT (out of distribution)"}[verdict]
+        print(f"  {name:<10} {p_} -> {text}")
+    return EXIT_OK
+
+
+def cmd_attest(a):
+    """Verified inferences chained into an attestation log; a forged output is refused and an altered event changes
+    the chain head (scirust-cli/src/synergy.rs:163-230)."""
+    import random
+    from .io.attest import AttestationLog, P, VModel, attest_and_record
+    rng = random.Random(a.seed)
+    out, inn, batch = 4, 6, 3
+    model = VModel([rng.randrange(P) for _ in range(out * inn)], out, inn)
+    log = AttestationLog()
+    for _ in range(4):
+        x = [rng.randrange(P) for _ in range(inn * batch)]
+        attest_and_record(log, model, x, batch, model.infer(x, batch), 2)
+    x = [rng.randrange(P) for _ in range(inn * batch)]
+    forged = model.infer(x, batch)
+    forged[0] = (forged[0] + 1) % P
+    rejected = attest_and_record(log, model, x, batch, forged, 2) is None
+    heads = []
+    for tamper in (False, True):
+        alt = AttestationLog()
+        for i in range(4):
+            xx = [(i * 7 + j) % P for j in range(inn * batch)]
+            yy = model.infer(xx, batch)
+            if tamper and i == 1:
+                yy[0] = (yy[0] + 1) % P
+            alt.record(model.commit(), xx, yy)
+        heads.append(alt.head.hex())
+    print(f"Attestation log (seed {a.seed}): model commitment {model.commit().hex()[:16]}..")
+    print(f"  {len(log)} verified inferences chained, head {log.head.hex()[:16]}.., chain valid: {log.verify_chain()}")
+    print(f"  forged output refused: {rejected}")
+    print(f"  altered event changes the head: {heads[0] != heads[1]}")
+    return EXIT_OK if rejected and log.verify_chain() and heads[0] != heads[1] else EXIT_VALIDATION
+
+
+def _sciagent_reply(a, prompt_text, max_new):
+    import torch
+    from .generate import SamplingParams
+    from .io import checkpoint as CK
+    from .models.infer import InferenceEngine
+    dev = _device(a.device)
+    model, _ = CK.load_sciagent_checkpoint(a.checkpoint, device=dev)
+    tok = _load_tokenizer(a.tokenizer) if a.tokenizer else None
+    ids = tok.encode(prompt_text) if tok else [b for b in prompt_text.encode()][:model.cfg.max_seq_len]
+    ids = [min(i, model.cfg.vocab_size - 1) for i in ids][-(model.cfg.max_seq_len - max_new - 1):]
+    if not ids:
+        raise ValueError("empty prompt")
+    eng = InferenceEngine(model, quant=a.quant, max_batch=1, max_seq=len(ids) + max_new + 1)
+    params = SamplingParams(a.temperature, a.top_k, a.top_p, a.repetition_penalty)
+    out = eng.generate(torch.tensor([ids]), max_new, params, seed=a.seed)[0].tolist()
+    if 0 in out:
+        out = out[:out.index(0)]
+    return tok.decode(out) if tok else bytes(t % 256 for t in out).decode("utf-8", "replace")
+
+
+def cmd_sciagent_text(a):
+    """`sciagent ask <prompt>`, `chat` (one reply per input line until end of input) and `explain <path>`
+    (scirust-cli/src/sciagent.rs:137-260). Without a tokenizer file, text is fed as bytes."""
+    if a.action == "ask":
+        if not a.prompt:
+            sys.stderr.write("usage: scirust sciagent ask --prompt TEXT --checkpoint PATH\n")
+            return EXIT_USAGE
+        print(_sciagent_reply(a, a.prompt, a.max_new))
+        return EXIT_OK
+    if a.action == "explain":
+        from pathlib import Path
+        if not a.path:
+            sys.stderr.write("usage: scirust sciagent explain --path FILE [--lines N-M] --checkpoint PATH\n")
+            return EXIT_USAGE
+        content = Path(a.path).read_text(errors="replace")
+        if a.lines:
+            lo, _, hi = a.lines.partition("-")
+            start = int(lo or 1)
+            end = int(hi) if hi else start + 30
+            excerpt = "\n".join(content.splitlines()[max(start - 1, 0):end])
+        else:
+            excerpt = content[:2000]
+        print(_sciagent_reply(a, "Explain the following code:\n" + excerpt + "\nExplanation:", a.max_new))
+        return EXIT_OK
+    history = ""
+    print("SCIAGENT chat (end of input to exit)")
+    for line in sys.stdin:
+        line = line.strip()
+        if not line:
+            continue
+        history += line + "\n"
+        reply = _sciagent_reply(a, history, a.max_new)
+        history += reply + "\n"
+        print(reply)
+    return EXIT_OK
+
+
 def build_parser():
     p = _Parser(prog="scirust", description="scirust_b200 command line")
     sub = p.add_subparsers(dest="cmd")
@@ -399,11 +602,31 @@ def build_parser():
     gen_args(i)
     i.set_defaults(fn=cmd_infer)
     s = sub.add_parser("sciagent")
-    s.add_argument("action", choices=["info", "generate", "quantize", "attest"])
+    s.add_argument("action", choices=["info", "generate", "quantize", "attest", "ask", "chat", "explain"])
     gen_args(s)
     s.add_argument("--out", default="model.int4.bin")
     s.add_argument("--group", type=int, default=32)
-    s.set_defaults(fn=cmd_sciagent)
+    s.add_argument("--path", default="")
+    s.add_argument("--lines", default="")
+    s.set_defaults(fn=lambda a: cmd_sciagent_text(a) if a.action in ("ask", "chat", "explain") else cmd_sciagent(a))
+    lm = sub.add_parser("lm")
+    lm.add_argument("tokens", nargs="?", default="1,2,3,4,2,5")
+    lm.add_argument("--seed", type=int, default=123)
+    lm.add_argument("--steps", type=int, default=200)
+    lm.add_argument("--lr", type=float, default=0.05)
+    lm.add_argument("--opt", default="adam")
+    lm.set_defaults(fn=cmd_lm)
+    ce = sub.add_parser("certify")
+    ce.add_argument("--seed", type=int, default=1)
+    ce.add_argument("--eps", type=float, default=0.05)
+    ce.set_defaults(fn=cmd_certify)
+    gd = sub.add_parser("guard")
+    gd.add_argument("--seed", type=int, default=1)
+    gd.add_argument("--alpha", type=float, default=0.1)
+    gd.set_defaults(fn=cmd_guard)
+    at = sub.add_parser("attest")
+    at.add_argument("--seed", type=int, default=1)
+    at.set_defaults(fn=cmd_attest)
     for name in ("gptq", "awq", "bitnet", "int4"):
         qz = sub.add_parser(name)
         qz.add_argument("--weights", default="")

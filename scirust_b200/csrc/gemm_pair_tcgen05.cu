@@ -84,6 +84,8 @@ struct Params {
     const void* a_peer[MAXW]; int lda;     // only a_peer[rank] (the local shard) is read
     void* a_stage; int ld_stage;           // the local landing buffer (= stage_peer[rank])
     void* stage_peer[MAXW];
+    int copy_own;                          // also place the own shard in the local landing buffer (nobody waits for
+                                           // it: the caller wants the whole gathered matrix afterwards)
     uint32_t* flags[MAXW];
     uint32_t* chunk_flags;                 // local: chunk_flags[chunk], raised by the rank that pushed the chunk
     uint32_t* chunk_flags_peer[MAXW];
@@ -300,7 +302,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else if (warp >= 10) {
     // -------------------------------- copiers (both CTAs) ---------------------------------
-    if (ag && !A_MN && p.ag.W > 1) {
+    if (ag && !A_MN && (p.ag.W > 1 || p.ag.copy_own)) {
       const int cw = warp - 10;
       const int cpr = p.ag.rows / BM;                                        // chunks per rank
       const size_t vec_per_row = static_cast<size_t>(p.K) / 8;               // 16-byte words per row
@@ -308,7 +310,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int team = p.ag.team, n_teams = gridDim.x / team;
       const int my_team = blockIdx.x / team, member = blockIdx.x - my_team * team;
       const size_t lo = vec_per_chunk * member / team, hi = vec_per_chunk * (member + 1) / team;
-      const int n_items = (p.ag.W - 1) * cpr;                                // (destination, chunk) pairs, in the order
+      const int n_items = (p.ag.W - 1 + (p.ag.copy_own ? 1 : 0)) * cpr;     // (destination, chunk) pairs, in the order
       const uint4* mine = static_cast<const uint4*>(p.ag.a_peer[p.ag.rank]);  // the destinations need them
       for (int i = my_team; i < n_items && my_team < n_teams; i += n_teams) {
         const int dst = (p.ag.rank + p.ag.W - 1 - i / cpr) % p.ag.W;          // rank-1 first: it reads my shard first
@@ -335,6 +337,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
         }
+        if (dst == p.ag.rank) continue;   // own rows (last items): a local copy that no flag announces
         __threadfence_system();        // this warp's stores have reached the destination
         __syncwarp();
         if (lane == 0) {
@@ -821,12 +824,13 @@ extern "C" int sb_gemm_pair_bf16(const void* A, const void* B, void* C, const vo
 // (peer-mapped: every rank pushes its shard into every peer's); flag_ptrs[r]: this call site's flag slot on rank r;
 // chunk_flag_ptrs[r]: rank r's M/128 chunk epochs (peer-mapped, zero when created); chunk_ctr: M/128 local words,
 // cta_ctr one local word (zero on entry, left zero). (M / W) % 256 == 0, K % 8 == 0. B is local ([K,N] when b_mn,
-// else [N,K]).
+// else [N,K]). copy_own != 0: the own shard is copied into the local landing buffer too, which then holds the whole
+// gathered matrix when the kernel has finished (weight-gradient products reuse it instead of gathering again).
 extern "C" int sb_gemm_pair_ag_bf16(void* const* a_ptrs, const void* B, void* C, const void* R, int M, int N, int K,
                                     int lda, int ldb, int ldc, int ldr, int b_mn, void* const* stage_ptrs, int ld_stage,
                                     void* const* flag_ptrs, void* const* chunk_flag_ptrs, unsigned int* chunk_ctr,
-                                    unsigned int* cta_ctr, int rank, int W, uint32_t epoch, int wait_ms, int* status,
-                                    void* stream_) {
+                                    unsigned int* cta_ctr, int rank, int W, uint32_t epoch, int wait_ms, int copy_own,
+                                    int* status, void* stream_) {
   using namespace sb::pair;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0 || K <= 0 || W < 1 || W > MAXW || rank < 0 || rank >= W) return SB_ERR_ARG;
@@ -856,6 +860,7 @@ extern "C" int sb_gemm_pair_ag_bf16(void* const* a_ptrs, const void* B, void* C,
     p.ag.chunk_flags_peer[r] = r < W ? static_cast<uint32_t*>(chunk_flag_ptrs[r]) : nullptr;
   }
   p.ag.chunk_flags = static_cast<uint32_t*>(chunk_flag_ptrs[rank]); p.ag.chunk_ctr = chunk_ctr; p.ag.cta_ctr = cta_ctr;
+  p.ag.copy_own = copy_own;
   p.ag.epoch = epoch;
   p.ag.wait_ns = wait_ms > 0 ? static_cast<uint64_t>(wait_ms) * 1000000ull : 10000000000ull;
   // every CTA pair runs copier warps, so the whole device is launched whatever the tile count

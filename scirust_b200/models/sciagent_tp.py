@@ -39,13 +39,13 @@ class _TPBlockFn(torch.autograd.Function):
         Tl, d = x.shape
         h1 = tp.buffer(f"h1.{i}", (Tl, d))
         _, inv1 = ops.rmsnorm_fwd(x, rms1, cfg.eps, out=h1)
-        qkv = tp.ag_matmul_nn(h1, wqkv)
+        qkv = tp.ag_matmul_nn(h1, wqkv, keep=f"h1.{i}")
         ops.rope_(qkv, Hq + Hkv, dh, S, blk.cos, blk.sin)
         a, lse = att.attention_fwd(qkv, B, S, Hq, Hkv, dh, causal=True)
         x2 = tp.matmul_nn_rs(a, wo, residual_shard=x)
         h2 = tp.buffer(f"h2.{i}", (Tl, d))
         _, inv2 = ops.rmsnorm_fwd(x2, rms2, cfg.eps, out=h2)
-        gu = tp.ag_matmul_nn(h2, wgu)
+        gu = tp.ag_matmul_nn(h2, wgu, keep=f"h2.{i}")
         hm = ops.swiglu_fwd(gu)
         x3 = tp.matmul_nn_rs(hm, wd, residual_shard=x2)
         ctx.save_for_backward(x, inv1, h1, qkv, a, lse, x2, inv2, h2, gu, hm)
@@ -64,11 +64,13 @@ class _TPBlockFn(torch.autograd.Function):
         # the incoming gradient shard must be peer-visible: the next two products gather it
         g3 = tp.buffer("dy.a", (Tl, d))
         g3.copy_(dx3)
-        dhm = tp.ag_matmul_nt(g3, wd)
-        _acc_into(wd, lambda out, res: tp.matmul_tn_ag(hm, g3, out=out, residual=res))
+        i = blk.index
+        dhm = tp.ag_matmul_nt(g3, wd, keep="dy.a")
+        # the gathered gradient is already in local memory: the weight gradient needs no second gather
+        _acc_into(wd, lambda out, res: tp.matmul_tn_ag(hm, g3, out=out, residual=res, keep="dy.a"))
         dgu = ops.swiglu_bwd(gu, dhm)
         dh2 = tp.matmul_nt_rs(dgu, wgu)
-        _acc_into(wgu, lambda out, res: tp.ag_matmul_tn(h2, dgu, out=out, residual=res))
+        _acc_into(wgu, lambda out, res: tp.ag_matmul_tn(h2, dgu, out=out, residual=res, keep=f"h2.{i}"))
         res = {}
 
         def _n2(out):
@@ -78,12 +80,12 @@ class _TPBlockFn(torch.autograd.Function):
         g_rms2 = _vgrad(rms2, _n2)
         g2 = tp.buffer("dy.b", (Tl, d))
         g2.copy_(res["dx2"])
-        da = tp.ag_matmul_nt(g2, wo)
-        _acc_into(wo, lambda out, r: tp.matmul_tn_ag(a, g2, out=out, residual=r))
+        da = tp.ag_matmul_nt(g2, wo, keep="dy.b")
+        _acc_into(wo, lambda out, r: tp.matmul_tn_ag(a, g2, out=out, residual=r, keep="dy.b"))
         dqkv = att.attention_bwd(qkv, a, lse, da, B, S, Hq, Hkv, dh, causal=True)
         ops.rope_(dqkv, Hq + Hkv, dh, S, blk.cos, blk.sin, backward=True)
         dh1 = tp.matmul_nt_rs(dqkv, wqkv)
-        _acc_into(wqkv, lambda out, r: tp.ag_matmul_tn(h1, dqkv, out=out, residual=r))
+        _acc_into(wqkv, lambda out, r: tp.ag_matmul_tn(h1, dqkv, out=out, residual=r, keep=f"h1.{i}"))
 
         def _n1(out):
             dx, dw = ops.rmsnorm_bwd(dh1, x, rms1, inv1, dres=g2, dw_out=out)

@@ -42,7 +42,8 @@ _lib.register("sb_gemm_dist_bf16", [_lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.vp,
 
 _lib.register("sb_gemm_pair_ag_bf16", [_lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.i32, _lib.i32,
                                        _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.vp, _lib.i32, _lib.vp, _lib.vp,
-                                       _lib.vp, _lib.vp, _lib.i32, _lib.i32, C.c_uint32, _lib.i32, _lib.vp, _lib.vp])
+                                       _lib.vp, _lib.vp, _lib.i32, _lib.i32, C.c_uint32, _lib.i32, _lib.i32, _lib.vp,
+                                       _lib.vp])
 
 
 _lib.register("sb_gemm_pair_rs_bf16", [_lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.vp, _lib.i32, _lib.vp, _lib.i32, _lib.i32,
@@ -72,7 +73,14 @@ class TPContext:
         # weight gradients: SB_TP_DIRECT_WGRAD=1 keeps the kernel that reads the gathered operand from the peers tile
         # by tile (every remote tile crosses NVLink once per output column tile: slower, kept for comparison)
         self.direct_wgrad = os.environ.get("SB_TP_DIRECT_WGRAD", "0") == "1"
+        # SB_TP_PROFILE=1: CUDA-event time of every product, by method and shape (``profile_report()``)
+        self._prof = {} if os.environ.get("SB_TP_PROFILE", "0") == "1" else None
+        if self._prof is not None:
+            for name in ("ag_matmul_nn", "ag_matmul_nt", "matmul_nn_rs", "matmul_nt_rs", "ag_matmul_tn", "matmul_tn_ag"):
+                setattr(self, name, self._profiled(name, getattr(self, name)))
         self._named = {}
+        self._gathered = {}          # keep-name -> gathered operand of the last all-gather -> GEMM with that name
+        self._peer_ptr_cache = {}
         if backend == "fused":
             stage_bytes = max_rows * max_cols * 2          # W * (rows/W) * cols bf16
             total = 3 * stage_bytes + sym_bytes + (1 << 20)
@@ -101,6 +109,26 @@ class TPContext:
         else:
             self.region = None
 
+    def _profiled(self, name, fn):
+        def wrapped(*a, **kw):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = fn(*a, **kw)
+            e1.record()
+            key = (name, tuple(a[0].shape), tuple(a[1].shape))
+            self._prof.setdefault(key, []).append((e0, e1))
+            return r
+        return wrapped
+
+    def profile_report(self, skip: int = 0):
+        """{(method, shape a, shape b): (calls, total ms)} of the products recorded under SB_TP_PROFILE=1."""
+        torch.cuda.synchronize()
+        out = {}
+        for key, evs in (self._prof or {}).items():
+            evs = evs[skip:]
+            out[key] = (len(evs), sum(a.elapsed_time(b) for a, b in evs))
+        return out
+
     # peer-visible persistent buffers, keyed by name (activations that another rank's kernel reads)
     def buffer(self, name: str, shape, dtype=BF) -> torch.Tensor:
         key = (name, tuple(shape), dtype)
@@ -118,20 +146,34 @@ class TPContext:
             return self.region.peer_ptrs(t)
         return (C.c_void_p * self.world)(*([t.data_ptr()] * self.world))
 
-    def _ag_pair(self, x_shard, w, out, M, N, K, b_mn):
-        """all-gather -> GEMM on the CTA-pair kernel (csrc/gemm_pair_tcgen05.cu): the shards land in a
-        local buffer chunk by chunk while 256 x 256 tiles are computed over two SMs."""
+    def _ag_pair(self, x_shard, w, out, M, N, K, b_mn, keep=None):
+        """all-gather -> GEMM on the CTA-pair kernel (csrc/gemm_pair_tcgen05.cu): every rank pushes its shard
+        into the peers' landing buffers chunk by chunk while 256 x 256 tiles are computed over two SMs. With
+        ``keep`` the landing buffer is a named one that also receives the own shard, so that it holds the whole
+        gathered matrix afterwards (``gathered(keep)``)."""
         self.epoch += 1
-        if M * K > self._ag_stage.numel():
-            raise ValueError("all-gather landing buffer too small for this product")
+        if keep is None:
+            if M * K > self._ag_stage.numel():
+                raise ValueError("all-gather landing buffer too small for this product")
+            stage_ptrs = self._ag_stage_ptrs
+        else:
+            full = self.buffer("gathered." + keep, (M, K))
+            stage_ptrs = self._peer_ptr_cache.get(full.data_ptr())
+            if stage_ptrs is None:
+                stage_ptrs = self._peer_ptr_cache[full.data_ptr()] = self.region.peer_ptrs(full)
+            self._gathered[keep] = full
         n = self._ag_flags.numel() // 2
         _lib.call("sb_gemm_pair_ag_bf16", self.region.peer_ptrs(x_shard), w.data_ptr(), out.data_ptr(), None, M, N, K,
-                  x_shard.stride(0), w.stride(0), out.stride(0), 0, int(b_mn), self._ag_stage_ptrs, K,
+                  x_shard.stride(0), w.stride(0), out.stride(0), 0, int(b_mn), stage_ptrs, K,
                   self.flag_ptrs, self._ag_chunk_flag_ptrs, self._ag_flags[n:].data_ptr(),
                   self._ag_flags[2 * n - 1:].data_ptr(), self.rank, self.world, self.epoch, self.wait_ms,
-                  _lib.status_word(self.dev).data_ptr(), _lib.stream())
+                  int(keep is not None), _lib.status_word(self.dev).data_ptr(), _lib.stream())
         _g.launch_count += 1
         return out
+
+    def gathered(self, keep: str):
+        """The whole gathered operand of the last ``ag_matmul_*(..., keep=keep)`` call, or None."""
+        return self._gathered.get(keep)
 
     def _rs_pair(self, a, w, out, residual, M, N, K, b_mn):
         """GEMM -> reduce-scatter on the CTA-pair kernel: tiles are pushed into the owners' receive buffers
@@ -197,30 +239,39 @@ class TPContext:
         return out
 
     # ---------------------------------------------------------------- fused products
-    def ag_matmul_nn(self, x_shard, w):
-        """all-gather(x_shard over rows) @ w   -> [T, N]; x_shard must come from ``buffer()``."""
+    def _gather_nccl(self, x_shard, keep):
+        Tl, K = x_shard.shape
+        x = (self.buffer("gathered." + keep, (Tl * self.world, K)) if keep is not None
+             else torch.empty((Tl * self.world, K), dtype=BF, device=self.dev))
+        dist.all_gather_into_tensor(x, x_shard.contiguous(), group=self.group)
+        if keep is not None:
+            self._gathered[keep] = x
+        return x
+
+    def ag_matmul_nn(self, x_shard, w, keep=None):
+        """all-gather(x_shard over rows) @ w   -> [T, N]; x_shard must come from ``buffer()``. ``keep`` names a
+        buffer in which the gathered operand stays available (``gathered(keep)``) until the next call with that name:
+        the weight-gradient product of the same layer reuses it instead of gathering again."""
         Tl, K = x_shard.shape
         T, N = Tl * self.world, w.shape[1]
         if self.backend != "fused":
-            x = torch.empty((T, K), dtype=BF, device=self.dev)
-            dist.all_gather_into_tensor(x, x_shard.contiguous(), group=self.group)
-            return torch.matmul(x, w)
+            return torch.matmul(self._gather_nccl(x_shard, keep), w)
         out = torch.empty((T, N), dtype=BF, device=self.dev)
         if self._pair_ok(T, K):
-            return self._ag_pair(x_shard, w, out, T, N, K, True)
+            return self._ag_pair(x_shard, w, out, T, N, K, True, keep)
+        self._gathered.pop(keep, None)
         return self._call(x_shard, w, out, None, T, N, K, False, True, True, False, False)
 
-    def ag_matmul_nt(self, x_shard, w):
-        """all-gather(x_shard) @ wᵀ  (w [N, K]) -> [T, N]."""
+    def ag_matmul_nt(self, x_shard, w, keep=None):
+        """all-gather(x_shard) @ wᵀ  (w [N, K]) -> [T, N]; ``keep`` as in ``ag_matmul_nn``."""
         Tl, K = x_shard.shape
         T, N = Tl * self.world, w.shape[0]
         if self.backend != "fused":
-            x = torch.empty((T, K), dtype=BF, device=self.dev)
-            dist.all_gather_into_tensor(x, x_shard.contiguous(), group=self.group)
-            return torch.matmul(x, w.t())
+            return torch.matmul(self._gather_nccl(x_shard, keep), w.t())
         out = torch.empty((T, N), dtype=BF, device=self.dev)
         if self._pair_ok(T, K):
-            return self._ag_pair(x_shard, w, out, T, N, K, False)
+            return self._ag_pair(x_shard, w, out, T, N, K, False, keep)
+        self._gathered.pop(keep, None)
         return self._call(x_shard, w, out, None, T, N, K, False, False, True, False, False)
 
     def matmul_nn_rs(self, a, w, residual_shard=None):
@@ -257,11 +308,23 @@ class TPContext:
             return self._rs_pair(a, w, out, residual_shard, T, N, K, False)
         return self._call(a, w, out, residual_shard, T, N, K, False, False, False, False, True)
 
-    def ag_matmul_tn(self, x_shard, dy, out=None, residual=None):
+    def ag_matmul_tn(self, x_shard, dy, out=None, residual=None, keep=None):
         """all-gather(x_shard)ᵀ @ dy -> [K_x, N]: weight gradient of a column-parallel layer
-        (x sharded over tokens, dy local with all tokens)."""
+        (x sharded over tokens, dy local with all tokens). ``keep``: name under which an earlier
+        ``ag_matmul_*`` left the gathered ``x``; it is then used as it is, without any communication."""
         Tl, M = x_shard.shape
         T, N = dy.shape
+        full = self._gathered.get(keep) if keep is not None else None
+        if full is not None and tuple(full.shape) == (T, M):
+            if self.backend != "fused":
+                r = torch.matmul(full.t(), dy)
+                if residual is not None:
+                    r = r + residual
+                if out is not None:
+                    out.copy_(r)
+                    return out
+                return r
+            return _g.matmul_tn(full, dy, residual=residual, out=out)
         if self.backend != "fused":
             x = torch.empty((T, M), dtype=BF, device=self.dev)
             dist.all_gather_into_tensor(x, x_shard.contiguous(), group=self.group)
@@ -282,11 +345,22 @@ class TPContext:
         dist.all_gather_into_tensor(x, x_shard.contiguous(), group=self.group)
         return _g.matmul_tn(x, dy, residual=residual, out=out)
 
-    def matmul_tn_ag(self, a, dy_shard, out=None, residual=None):
+    def matmul_tn_ag(self, a, dy_shard, out=None, residual=None, keep=None):
         """aᵀ @ all-gather(dy_shard) -> [K_a, N]: weight gradient of a row-parallel layer
-        (a local with all tokens, dy sharded over tokens)."""
+        (a local with all tokens, dy sharded over tokens); ``keep`` as in ``ag_matmul_tn``."""
         T, M = a.shape
         Tl, N = dy_shard.shape
+        full = self._gathered.get(keep) if keep is not None else None
+        if full is not None and tuple(full.shape) == (T, N):
+            if self.backend != "fused":
+                r = torch.matmul(a.t(), full)
+                if residual is not None:
+                    r = r + residual
+                if out is not None:
+                    out.copy_(r)
+                    return out
+                return r
+            return _g.matmul_tn(a, full, residual=residual, out=out)
         if self.backend != "fused":
             dy = torch.empty((T, N), dtype=BF, device=self.dev)
             dist.all_gather_into_tensor(dy, dy_shard.contiguous(), group=self.group)

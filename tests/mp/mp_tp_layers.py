@@ -57,6 +57,26 @@ def sync():
     _lib.check_status(dev)
 
 
+if ROWS % 128:
+    # rows per rank off the kernels' 128-row grid: every fused product must refuse on the host (a typed error, the
+    # same on all ranks) instead of computing something
+    refused = 0
+    for call in (lambda: fused.ag_matmul_nn(x_shard, w_col), lambda: fused.matmul_nn_rs(a_loc, w_row),
+                 lambda: fused.matmul_nt_rs(dy_loc, w_col)):
+        try:
+            call()
+        except (_lib.NativeError, ValueError):
+            refused += 1
+    sync()
+    assert refused == 3, f"only {refused} of 3 off-grid products were refused"
+    dist.barrier()
+    if rank == 0:
+        print(f"TP_OK world={world} rows_per_rank={ROWS} (refused)")
+    fused.close()
+    dist.destroy_process_group()
+    raise SystemExit(0)
+
+
 for rep in range(2):
     # all-gather -> GEMM (forward of column-parallel, and input-gradient of row-parallel)
     y1 = fused.ag_matmul_nn(x_shard, w_col); sync()

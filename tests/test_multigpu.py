@@ -53,8 +53,8 @@ def test_tp_fused_layers_match_nccl_baseline():
 
 @pytest.mark.parametrize("world,rows", [(2, 256), (2, 768), (2, 200), (4, 256), (4, 768), (8, 256), (8, 768)])
 def test_tp_fused_layers_world_and_rows(world, rows):
-    """Rows per rank of one and three 256-row blocks (CTA-pair kernels) and off the 256 grid (single-CTA
-    distributed kernel), at every world size the box offers."""
+    """Rows per rank of one and three 256-row blocks (CTA-pair kernels), and off the kernels' row grid, where every
+    fused product must refuse cleanly; at every world size the box offers."""
     _need(world)
     out = _run("mp_tp_layers.py", world, 29620 + world, extra_env={"SB_TP_ROWS_PER_RANK": str(rows)},
                tag=f"_w{world}_r{rows}")
