@@ -143,3 +143,64 @@ class AdamW(Adam):
                  weight_decay: float = 0.01):
         super().__init__(lr, beta1, beta2, epsilon)
         self.weight_decay = weight_decay
+
+
+class MuonOptimizer(Optimizer):
+    """Muon on the tape family: momentum ``m = mu m + (1 - mu) g``; a matrix parameter (both sides >= 2) steps along
+    the Newton-Schulz orthogonalisation of ``m`` scaled by ``sqrt(max(1, rows / cols))``, any other parameter along
+    ``m`` itself; decoupled weight decay on both (scirust-sciagent/src/train/optimizer.rs:11-103)."""
+
+    def __init__(self, lr: float, momentum: float = 0.95, ns_steps: int = 5, weight_decay: float = 0.0):
+        self.lr, self.momentum, self.ns_steps, self.weight_decay = lr, momentum, ns_steps, weight_decay
+        self.mu = {}
+
+    def step(self, params, tape) -> None:
+        from .nd_optim import newton_schulz_orthogonalize
+        for idx in params:
+            value, grad = tape.value(idx).t.clone(), tape.grad(idx).t
+            if value.shape != grad.shape:
+                raise ValueError(f"Muon.step: parameter / gradient shape mismatch (idx={idx})")
+            mk = self.mu.get(idx)
+            if mk is None:
+                mk = self.mu[idx] = torch.zeros_like(value)
+            mk.mul_(self.momentum).add_(grad, alpha=1.0 - self.momentum)
+            rows, cols = value.shape
+            if rows >= 2 and cols >= 2:
+                upd = newton_schulz_orthogonalize(mk, self.ns_steps) * (max(rows / cols, 1.0) ** 0.5)
+            else:
+                upd = mk
+            value.sub_(self.lr * (upd + self.weight_decay * value))
+            tape.set_value(idx, value)
+
+
+class TrainOptimizer:
+    """The SciAgent trainer's optimizer choice (Adam or Muon) behind one interface, with ``apply_schedule``
+    (scirust-sciagent/src/train/optimizer.rs:105-170)."""
+
+    def __init__(self, inner):
+        self.inner = inner
+
+    @staticmethod
+    def new_adam(lr: float) -> "TrainOptimizer":
+        return TrainOptimizer(Adam(lr))
+
+    @staticmethod
+    def new_muon(lr: float) -> "TrainOptimizer":
+        return TrainOptimizer(MuonOptimizer(lr))
+
+    def with_weight_decay(self, wd: float) -> "TrainOptimizer":
+        self.inner.weight_decay = wd
+        return self
+
+    def step(self, params, tape) -> None:
+        self.inner.step(params, tape)
+
+    @property
+    def lr(self) -> float:
+        return self.inner.lr
+
+    def set_lr(self, lr: float) -> None:
+        self.inner.set_lr(lr)
+
+    def apply_schedule(self, scheduler, step: int) -> None:
+        self.set_lr(scheduler.lr_at(step))

@@ -313,3 +313,103 @@ def test_cli_exit_codes(tmp_path, capsys):
     out1 = capsys.readouterr().out
     assert cli.run(["infer", "--checkpoint", str(tmp_path / "ck" / "step_2"), "--prompt", "5 6 7", "--max-new", "4"]) == 0
     assert capsys.readouterr().out.splitlines()[-1] == out1.splitlines()[-1]
+
+
+def test_nd_tape_surface_gradients_and_errors():
+    """N-D tape: finite-difference check through gather / rope / bmm / softmax / rmsnorm / layernorm / causal_conv /
+    cross_entropy, lag-ordered convolution equals the direct loop bit for bit, tapes do not mix."""
+    from scirust_b200.autodiff import NdTape, NdTapeError
+    torch.manual_seed(0)
+    E0, W0, H0 = torch.randn(10, 8) * 0.3, torch.randn(8, 10) * 0.3, torch.randn(4, 8) * 0.1
+
+    def loss_of(Ev):
+        t = NdTape()
+        E = t.input(Ev)
+        x = E.gather([1, 2, 3, 4])
+        q = x.reshape([1, 4, 8]).rope(10000.0)
+        a = q.bmm(q.transpose_last2()).softmax().bmm(x.reshape([1, 4, 8])).reshape([4, 8]).rmsnorm(1e-5)
+        y = a.causal_conv(t.input(H0)).add(x.layernorm(1e-5)).relu().add(x.sigmoid().mul(0.1))
+        loss = y.matmul(t.input(W0)).cross_entropy([2, 3, 4, 5])
+        return t, E, loss
+
+    t, E, loss = loss_of(E0)
+    g = t.backward(loss)[E.idx]
+    assert g.shape == E0.shape and float(g[0].abs().sum()) == 0.0      # row 0 was not gathered
+    for (r, c) in ((1, 0), (3, 5), (4, 7)):
+        d = torch.zeros_like(E0)
+        d[r, c] = 1e-3
+        fp = float(loss_of(E0 + d)[0].value(loss_of(E0 + d)[2]))
+        fm = float(loss_of(E0 - d)[0].value(loss_of(E0 - d)[2]))
+        assert abs((fp - fm) / 2e-3 - float(g[r, c])) < 5e-3
+    u, h = torch.randn(6, 3), torch.randn(6, 3)
+    t2 = NdTape()
+    y = t2.value(t2.input(u).causal_conv(t2.input(h)))
+    ref = torch.zeros(6, 3)
+    for tt in range(6):
+        for c in range(3):
+            acc = torch.tensor(0.0)
+            for tau in range(tt + 1):
+                acc = acc + h[tau, c] * u[tt - tau, c]
+            ref[tt, c] = acc
+    assert torch.equal(y, ref)
+    with pytest.raises(NdTapeError):
+        NdTape().input(u).add(t2.input(h))
+    with pytest.raises(NdTapeError):
+        t2.input(torch.randn(3, 4)).cross_entropy([0, 1, 9])
+    s = t2.input(torch.ones(2, 3)).sum()
+    assert t2.value(s).tolist() == [6.0] and s.shape() == [1]
+    parts = t2.input(torch.ones(1, 3)).cat0([t2.input(torch.zeros(2, 3))])
+    assert parts.shape() == [3, 3]
+
+
+def test_attestation_log_certified_bounds_and_guard():
+    from scirust_b200.certify import (IbpLinear, IbpMlp, Interval, StatisticalGuard, certified_robust, crown_bounds)
+    from scirust_b200.io.attest import AttestationLog, P, VModel, attest_and_record, verify_inference
+    from scirust_b200.io.execution_attestation import (ExecutionAttestation, build_decode_route_attestation,
+                                                       build_training_route_attestation, sha256_hex)
+    m = VModel(list(range(1, 25)), 4, 6)
+    x = list(range(18))
+    y = m.infer(x, 3)
+    assert verify_inference(m, x, 3, y)
+    log = AttestationLog()
+    assert attest_and_record(log, m, x, 3, y) is not None and log.verify_chain()
+    bad = list(y)
+    bad[5] = (bad[5] + 1) % P
+    assert attest_and_record(log, m, x, 3, bad) is None and len(log) == 1
+    log.record(m.commit(), x, y)
+    head = log.head
+    log.events[0].output_hash = bytes(32)
+    assert not log.verify_chain() and log.head == head
+
+    torch.manual_seed(0)
+    l1 = IbpLinear(torch.randn(4, 8) * 0.5, torch.randn(8) * 0.1)
+    l2 = IbpLinear(torch.randn(8, 3) * 0.5, torch.randn(3) * 0.1)
+    box = Interval.around([0.2, -0.5, 0.7, -0.1], 0.05)
+    mlp = IbpMlp([l1, l2])
+    ibp, cr = mlp.certify(box), crown_bounds(l1, l2, box)
+    assert float(cr.width().mean()) <= float(ibp.width().mean()) + 1e-6
+    for _ in range(200):
+        pt = box.lo + (box.hi - box.lo) * torch.rand(4)
+        out = mlp.forward(pt)
+        assert bool((out >= cr.lo - 1e-5).all() and (out <= cr.hi + 1e-5).all())
+        assert bool((out >= ibp.lo - 1e-5).all() and (out <= ibp.hi + 1e-5).all())
+    tight = mlp.certify(Interval.around([0.2, -0.5, 0.7, -0.1], 1e-6))
+    assert certified_robust(tight, int(mlp.forward([0.2, -0.5, 0.7, -0.1]).argmax()))
+
+    g = torch.Generator().manual_seed(1)
+    yv = torch.randint(0, 3, (3000,), generator=g)
+    lg = torch.rand(3000, 3, generator=g) * 2 - 1
+    lg[torch.arange(3000), yv] += 1.5
+    pr = torch.softmax(lg, -1)
+    guard = StatisticalGuard.calibrate(pr[:1500], yv[:1500], 0.1)
+    cover = sum(guard.covers(p_, int(t_)) for p_, t_ in zip(pr[1500:], yv[1500:])) / 1500
+    assert cover >= 0.87
+    assert guard.decide([0.97, 0.02, 0.01])[0] == "accept" and guard.decide([0.34, 0.33, 0.33])[0] == "reject"
+
+    a1 = build_training_route_attestation(sha256_hex(b"m"), sha256_hex(b"t"))
+    a2 = build_decode_route_attestation(sha256_hex(b"m"), sha256_hex(b"t"), weights="int8")
+    assert a1.verify() and a2.verify() and a1.attestation_sha256 != a2.attestation_sha256
+    back = ExecutionAttestation.from_json(a2.to_json())
+    assert back.verify() and back.profile.numeric_mode.startswith("int8")
+    back.profile.model_sha256 = sha256_hex(b"other")
+    assert not back.verify()

@@ -150,3 +150,76 @@ def test_library_baseline_model_computes_the_same_loss():
     l_ours = ours(toks[:, :-1], toks[:, 1:]).float().item()
     l_lib = lib(toks[:, :-1], toks[:, 1:]).float().item()
     assert abs(l_ours - l_lib) < 3e-2, (l_ours, l_lib)
+
+
+def test_corpus_filter_dedup_split_and_muon_train_optimizer(tmp_path):
+    import numpy as np
+    from scirust_b200.autodiff import Tape, TrainOptimizer
+    from scirust_b200.data import corpus as CP
+    from scirust_b200.train.schedule import WarmupCosineSchedule
+
+    assert CP.parse_extensions(".rs, PY,,md") == ["rs", "py", "md"]
+    assert CP.skip_source_dir("node_modules") and not CP.skip_source_dir("src")
+    assert CP.content_hash("") == 0xCBF29CE484222325 and CP.content_hash("a") == 0xAF63DC4C8601EC8C
+    assert CP.source_quality("x.rs", "   \n") == "empty"
+    assert CP.source_quality("Cargo.lock", "[[package]]") is not None
+    assert CP.source_quality("a.rs", "// @generated by tool\nfn main() {}\n") == "declared generated"
+    assert CP.source_quality("a.js", "x" * 12000) == "minified (giant line)"
+    assert CP.source_quality("t.csv", ("1234567890," * 30 + "\n") * 3) is not None
+    good = "//! module\nuse std::collections::HashMap;\nfn add(a: i32, b: i32) -> i32 { a + b }\n" * 5
+    assert CP.source_quality("lib.rs", good) is None
+
+    tr, va = CP.distributed_window_split(100_001, 100, 0.1)
+    assert len(tr) + len(va) == 1000 and not set(tr) & set(va) and 60 <= len(va) <= 140
+    assert (tr, va) == CP.distributed_window_split(100_001, 100, 0.1)
+    assert CP.distributed_window_split(50, 100, 0.1) == ([], [])
+    t2, v2 = CP.distributed_window_split(201, 100, 0.1)
+    assert len(t2) == 1 and len(v2) == 1
+
+    src = tmp_path / "src"
+    (src / "node_modules").mkdir(parents=True)
+    (src / "a.rs").write_text(good)
+    (src / "b.rs").write_text(good)                    # exact duplicate
+    (src / "c.rs").write_text("// do not edit\n" + good)
+    (src / "node_modules" / "d.rs").write_text(good + "// other\n")
+    (src / "e.txt").write_text(good)
+
+    class ByteTok:
+        def encode(self, text):
+            return list(text.encode())
+    rep = CP.collect_corpus(src, ["rs"], ByteTok(), tmp_path / "shard.bin")
+    assert rep["files_kept"] == 1 and rep["duplicates"] == 1 and rep["dropped"] == {"declared generated": 1}
+    ld = CP.ShardLoader()
+    ld.load_dir(tmp_path)
+    assert ld.total_tokens() == rep["tokens"] == len(good.encode()) + 1
+    assert CP.token_stream_hash(ld.tokens()) == rep["token_stream_hash"]
+    ds = CP.PretrainDataset(np.array([0, 1, 2, 200, 4, 5, 6, 7, 8]), 4, 10)
+    x, y = ds.next_batch(1)
+    assert x == [0, 1, 2, 3] and y == [1, 2, 3, 4]      # 200 is out of vocabulary -> <unk> = 3
+    a, b = CP.PretrainDataset(np.arange(60), 5, 100), CP.PretrainDataset(np.arange(60), 5, 100)
+    a.shuffle(42)
+    b.shuffle(42)
+    assert a.next_batch(2) == b.next_batch(2) and a.starts != sorted(a.starts)
+
+    # Muon / Adam behind TrainOptimizer drive a tape regression downhill; the schedule sets the rate
+    torch.manual_seed(0)
+    X, Wt = torch.randn(32, 6), torch.randn(6, 3)
+    Y = X @ Wt
+    for make in (TrainOptimizer.new_muon, TrainOptimizer.new_adam):
+        W0 = torch.zeros(6, 3)
+        opt = make(0.05).with_weight_decay(0.0)
+        sched = WarmupCosineSchedule(0.05, 0.005, 5, 120)
+        first = last = None
+        for step in range(120):
+            tape = Tape()
+            w = tape.input(W0)
+            diff = tape.constant(X).matmul(w).sub(tape.constant(Y))
+            loss = diff.mul(diff).sum()
+            tape.backward(loss)
+            opt.apply_schedule(sched, step)
+            opt.step([w.idx], tape)
+            W0 = tape.value(w.idx).t.clone()
+            first = first if first is not None else loss.item()
+            last = loss.item()
+        assert last < 0.2 * first, (make.__name__, first, last)
+        assert abs(opt.lr - sched.lr_at(119)) < 1e-9
