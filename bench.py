@@ -222,10 +222,12 @@ def train_arm(args, rank, local_rank, world, dev):
     launches0 = gemm_ops.launch_count
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     _barrier(world)
+    t_issue = time.perf_counter()
     e0.record()
     for i in range(args.steps):
         loss = trainer.train_step(resident[i % n_host])
     e1.record()
+    host_issue_ms = (time.perf_counter() - t_issue) * 1e3 / args.steps    # time the host needs to queue a step
     _barrier(world)
     ms_dev = e0.elapsed_time(e1)
     launches = gemm_ops.launch_count - launches0
@@ -287,6 +289,7 @@ def train_arm(args, rank, local_rank, world, dev):
         "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                 "ms_per_step": max(ms_e2e, wall_ms) / args.steps},
         "gpu_launches": launches,
+        "host_issue_ms_per_step": host_issue_ms,
         "clocks": clocks,
         "final_loss": last,
     }

@@ -72,9 +72,9 @@ struct Params {
   // All-gather -> GEMM (ag.W >= 1): A's rows are sharded over the ranks (rank s holds rows
   // [s*rows, (s+1)*rows) in its own buffer a_peer[s], row pitch lda). Every rank PUSHES its shard into the
   // landing buffers of all peers (stage_peer[r], peer-mapped, [M, ld_stage]; plain 16-byte stores, which, unlike
-  // loads, need no round trip over NVLink): the copier warps of the CTAs work in teams on one 128-row chunk for
-  // one destination at a time, first for the peer that needs this shard first (rank-1), then rank-2, ...; the
-  // team member that completes a chunk raises chunk_flags[chunk] on the destination. The own shard is read in
+  // loads, need no round trip over NVLink): the copier warps of all CTAs share the copy for one destination at
+  // a time, first the peer that needs this shard first (rank-1), then rank-2, ...; the warp that completes a
+  // destination raises chunk_flags[source rank] there (one flag per source). The own shard is read in
   // place (tmap_a_own). The TMA producer waits (bounded) for the flag of the chunk it is about to read and walks
   // the row tiles in the matching rotated order (own rows, then rank+1's, ...). flags[r]: this call site's slot on
   // rank r; [1*16+s] "rank s has consumed its landing buffer": nobody leaves the kernel before every rank has,
@@ -87,7 +87,7 @@ struct Params {
     int copy_own;                          // also place the own shard in the local landing buffer (nobody waits for
                                            // it: the caller wants the whole gathered matrix afterwards)
     uint32_t* flags[MAXW];
-    uint32_t* chunk_flags;                 // local: chunk_flags[chunk], raised by the rank that pushed the chunk
+    uint32_t* chunk_flags;                 // local: chunk_flags[source rank], raised by the rank that pushed its shard
     uint32_t* chunk_flags_peer[MAXW];
     unsigned int* chunk_ctr; unsigned int* cta_ctr;
     uint32_t epoch;
@@ -236,8 +236,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const bool own_rows = ag && row0 / p.ag.rows == p.ag.rank;   // read straight from the local shard
         const int row_own = row0 - (ag ? p.ag.rank * p.ag.rows : 0);
         if (ag && !own_rows && row0 < p.M) {
-          // these 128 rows must have landed in the local buffer (copier warps of a team of CTAs)
-          if (!p_wait_flag<true>(p.ag.chunk_flags + row0 / BM, p.ag.epoch, p.ag.wait_ns, p.status)) { ok = false; break; }
+          // the shard of the rank that owns these rows must have landed in the local buffer
+          if (!p_wait_flag<true>(p.ag.chunk_flags + row0 / p.ag.rows, p.ag.epoch, p.ag.wait_ns, p.status)) { ok = false; break; }
           asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy stores -> TMA reads
         }
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
@@ -303,21 +303,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else if (warp >= 10) {
     // -------------------------------- copiers (both CTAs) ---------------------------------
     if (ag && !A_MN && (p.ag.W > 1 || p.ag.copy_own)) {
+      // Push my shard to every peer, one destination after the other (rank-1 first: it needs my rows first), all
+      // CTAs sharing each destination's copy. One system fence per warp and destination; the warp that completes a
+      // destination raises "rank's shard has landed" (chunk_flags[my rank]) there. Last, without any flag, the own
+      // shard goes to the local landing buffer if the caller wants the whole gathered matrix.
       const int cw = warp - 10;
-      const int cpr = p.ag.rows / BM;                                        // chunks per rank
       const size_t vec_per_row = static_cast<size_t>(p.K) / 8;               // 16-byte words per row
-      const size_t vec_per_chunk = vec_per_row * BM;
-      const int team = p.ag.team, n_teams = gridDim.x / team;
-      const int my_team = blockIdx.x / team, member = blockIdx.x - my_team * team;
-      const size_t lo = vec_per_chunk * member / team, hi = vec_per_chunk * (member + 1) / team;
-      const int n_items = (p.ag.W - 1 + (p.ag.copy_own ? 1 : 0)) * cpr;     // (destination, chunk) pairs, in the order
-      const uint4* mine = static_cast<const uint4*>(p.ag.a_peer[p.ag.rank]);  // the destinations need them
-      for (int i = my_team; i < n_items && my_team < n_teams; i += n_teams) {
-        const int dst = (p.ag.rank + p.ag.W - 1 - i / cpr) % p.ag.W;          // rank-1 first: it reads my shard first
-        const int ci = i % cpr;
-        const int chunk = p.ag.rank * cpr + ci;                               // row chunk of the gathered matrix
+      const size_t vecs = vec_per_row * p.ag.rows;                            // words of one shard
+      const size_t lo = vecs * blockIdx.x / gridDim.x, hi = vecs * (blockIdx.x + 1) / gridDim.x;
+      const uint4* mine = static_cast<const uint4*>(p.ag.a_peer[p.ag.rank]);
+      const size_t srow0 = static_cast<size_t>(p.ag.rank) * p.ag.rows;       // my rows in the gathered matrix
+      const int n_dst = p.ag.W - 1 + (p.ag.copy_own ? 1 : 0);
+      for (int q = 1; q <= n_dst; ++q) {
+        const int dst = (p.ag.rank + p.ag.W - q) % p.ag.W;                    // q == W: myself
         uint4* land = static_cast<uint4*>(p.ag.stage_peer[dst]);
-        const size_t prow0 = static_cast<size_t>(ci) * BM, srow0 = static_cast<size_t>(chunk) * BM;
         for (size_t v0 = lo + (cw * 32 + lane); v0 < hi; v0 += COPY_WARPS * 32 * CP_UNROLL) {
           uint4 tmp[CP_UNROLL];
           size_t idx[CP_UNROLL];
@@ -326,7 +325,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             idx[u] = v0 + static_cast<size_t>(u) * COPY_WARPS * 32;
             if (idx[u] < hi) {
               const size_t r = idx[u] / vec_per_row, c = idx[u] - r * vec_per_row;
-              tmp[u] = __ldg(mine + ((prow0 + r) * p.ag.lda) / 8 + c);
+              tmp[u] = __ldg(mine + (r * p.ag.lda) / 8 + c);
             }
           }
 #pragma unroll
@@ -337,14 +336,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
         }
-        if (dst == p.ag.rank) continue;   // own rows (last items): a local copy that no flag announces
+        if (dst == p.ag.rank) continue;
         __threadfence_system();        // this warp's stores have reached the destination
         __syncwarp();
         if (lane == 0) {
-          const unsigned int prev = atomicAdd(p.ag.chunk_ctr + i, 1u);
-          if (prev + 1 == static_cast<unsigned int>(team) * COPY_WARPS) {
+          const unsigned int prev = atomicAdd(p.ag.chunk_ctr + dst, 1u);
+          if (prev + 1 == gridDim.x * COPY_WARPS) {
             __threadfence_system();
-            p_st_release_sys(p.ag.chunk_flags_peer[dst] + chunk, p.ag.epoch);
+            p_st_release_sys(p.ag.chunk_flags_peer[dst] + p.ag.rank, p.ag.epoch);
           }
         }
       }
@@ -439,15 +438,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t leader_empty1 = mapa_shared(smem_u32(&tmem_empty[1]), 0);
     bool ok = true;
     int it = 0;
-    // reduce-scatter: the row block whose stores (TMA, to the owner's memory) this warp has issued but not yet
-    // announced. A warp's share of a tile counts once those stores are complete; the warp that completes a
-    // 256-row block raises the block's flag on its owner.
+    // reduce-scatter: the row block whose stores (TMA, to the owner's memory) this CTA has issued but not yet
+    // announced. A CTA's share of a tile counts once the stores of its eight epilogue warps are complete (each warp
+    // waits for its own, then the warps meet at a named barrier and ONE thread pays for the system fence); the CTA
+    // that completes a 256-row block raises the block's flag on its owner.
     int pend_m2 = -1;
     auto rs_announce = [&](int mb) {
       asm volatile("fence.proxy.async;" ::: "memory");     // the stores went through the async proxy
       __threadfence_system();
       const unsigned int prev = atomicAdd(p.rs.block_ctr + mb, 1u);
-      if (prev + 1 == static_cast<unsigned int>(nt) * 16u) {
+      if (prev + 1 == static_cast<unsigned int>(nt) * 2u) {
         const int bpr = p.rs.rows / (2 * BM);
         const int owner = mb / bpr;
         __threadfence_system();
@@ -553,8 +553,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             // all but the group just committed are complete: the previous tile has landed on its owner
             if (lane == 0) {
               if (issued) tma_store_wait<1>(); else tma_store_wait<0>();
-              rs_announce(pend_m2);
+              asm volatile("fence.proxy.async;" ::: "memory");
             }
+            __syncwarp();
+            asm volatile("bar.sync 2, 256;" ::: "memory");      // the eight epilogue warps of this CTA
+            if (warp == 2 && lane == 0) rs_announce(pend_m2);
             pend_m2 = -1;
           }
         }
@@ -637,8 +640,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if (rs) pend_m2 = m2;     // announced once its stores have completed (during the next tile, or below)
     }
     if (rs && pend_m2 >= 0) {
-      if (lane == 0) { tma_store_wait<0>(); rs_announce(pend_m2); }
+      if (lane == 0) {
+        tma_store_wait<0>();
+        asm volatile("fence.proxy.async;" ::: "memory");
+      }
       __syncwarp();
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      if (warp == 2 && lane == 0) rs_announce(pend_m2);
     }
   }
 
@@ -673,8 +681,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const unsigned int prev = atomicAdd(p.ag.cta_ctr, 1u);
     if (prev == gridDim.x - 1) {
       *p.ag.cta_ctr = 0;
-      const int chunks = p.ag.W * (p.ag.rows / BM);
-      for (int i = 0; i < chunks; ++i) p.ag.chunk_ctr[i] = 0;      // (W - 1) * chunks-per-rank of them were used
+      for (int i = 0; i < p.ag.W; ++i) p.ag.chunk_ctr[i] = 0;      // one counter per destination
       if (*reinterpret_cast<volatile int*>(p.status) == 0) {
         __threadfence_system();
         for (int r = 0; r < p.ag.W; ++r) p_st_release_sys(p.ag.flags[r] + 1 * FLAG_STRIDE + p.ag.rank, p.ag.epoch);
@@ -822,7 +829,7 @@ extern "C" int sb_gemm_pair_bf16(const void* A, const void* B, void* C, const vo
 // All-gather -> GEMM on CTA pairs: C[M,N] = gather(A shards)[M,K] * op(B) (+ R). a_ptrs[s]: rank s's shard
 // [M/W, lda] (only entry `rank`, the local one, is read); stage_ptrs[r]: rank r's landing buffer [M, ld_stage]
 // (peer-mapped: every rank pushes its shard into every peer's); flag_ptrs[r]: this call site's flag slot on rank r;
-// chunk_flag_ptrs[r]: rank r's M/128 chunk epochs (peer-mapped, zero when created); chunk_ctr: M/128 local words,
+// chunk_flag_ptrs[r]: rank r's per-source epochs (peer-mapped, >= W words, zero when created); chunk_ctr: >= W local words,
 // cta_ctr one local word (zero on entry, left zero). (M / W) % 256 == 0, K % 8 == 0. B is local ([K,N] when b_mn,
 // else [N,K]). copy_own != 0: the own shard is copied into the local landing buffer too, which then holds the whole
 // gathered matrix when the kernel has finished (weight-gradient products reuse it instead of gathering again).

@@ -81,6 +81,7 @@ class TPContext:
         self._named = {}
         self._gathered = {}          # keep-name -> gathered operand of the last all-gather -> GEMM with that name
         self._peer_ptr_cache = {}
+        self._status_ptr = _lib.status_word(self.dev).data_ptr() if backend == "fused" else None
         if backend == "fused":
             stage_bytes = max_rows * max_cols * 2          # W * (rows/W) * cols bf16
             total = 3 * stage_bytes + sym_bytes + (1 << 20)
@@ -141,6 +142,14 @@ class TPContext:
             self._named[key] = t
         return t
 
+    def _peer_ptrs(self, t: torch.Tensor):
+        """Per-rank addresses of a symmetric tensor, built once per buffer (the call sites reuse their buffers)."""
+        key = t.data_ptr()
+        p = self._peer_ptr_cache.get(key)
+        if p is None:
+            p = self._peer_ptr_cache[key] = self.region.peer_ptrs(t)
+        return p
+
     def _ptrs(self, t: torch.Tensor, gathered: bool):
         if gathered:
             return self.region.peer_ptrs(t)
@@ -158,16 +167,14 @@ class TPContext:
             stage_ptrs = self._ag_stage_ptrs
         else:
             full = self.buffer("gathered." + keep, (M, K))
-            stage_ptrs = self._peer_ptr_cache.get(full.data_ptr())
-            if stage_ptrs is None:
-                stage_ptrs = self._peer_ptr_cache[full.data_ptr()] = self.region.peer_ptrs(full)
+            stage_ptrs = self._peer_ptrs(full)
             self._gathered[keep] = full
         n = self._ag_flags.numel() // 2
-        _lib.call("sb_gemm_pair_ag_bf16", self.region.peer_ptrs(x_shard), w.data_ptr(), out.data_ptr(), None, M, N, K,
+        _lib.call("sb_gemm_pair_ag_bf16", self._peer_ptrs(x_shard), w.data_ptr(), out.data_ptr(), None, M, N, K,
                   x_shard.stride(0), w.stride(0), out.stride(0), 0, int(b_mn), stage_ptrs, K,
                   self.flag_ptrs, self._ag_chunk_flag_ptrs, self._ag_flags[n:].data_ptr(),
                   self._ag_flags[2 * n - 1:].data_ptr(), self.rank, self.world, self.epoch, self.wait_ms,
-                  int(keep is not None), _lib.status_word(self.dev).data_ptr(), _lib.stream())
+                  int(keep is not None), self._status_ptr, _lib.stream())
         _g.launch_count += 1
         return out
 
