@@ -169,6 +169,8 @@ def _optimizer_views(model, flat: torch.Tensor) -> dict:
         o, n = model.segments[name]
         return flat[o:o + n].view(shape)
     out = {"embedding": seg("embed", (cfg.vocab_size, cfg.d_model)), "final_norm": seg("rms_final", (1, cfg.d_model))}
+    if "lm_head" in model.segments:          # untied head: its moments and master weights are state too
+        out["lm_head"] = seg("lm_head", (cfg.vocab_size, cfg.d_model))
     for i in range(cfg.n_layers):
         wqkv = seg(f"layers.{i}.wqkv", (cfg.d_model, cfg.qkv_dim))
         wgu = seg(f"layers.{i}.wgu", (cfg.d_model, 2 * ff))

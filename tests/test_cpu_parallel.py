@@ -332,3 +332,79 @@ def test_fused_allreduce_refuses_more_buckets_than_it_has_counters():
         ar.bucket(8 * i, 8)
     with pytest.raises(RuntimeError, match="buckets"):
         ar.bucket(8 * far.FLAG_SLOTS, 8)
+
+
+def test_multihost_proof_program_and_reduction_overhead_bench():
+    """One process per rank over real TCP on the loopback; rank 0 recomputes the reference and must print PASS,
+    for the fp32 fixed-order sum (Python and native transports) and the exact accumulator."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=root)
+    for k, (combine, native) in enumerate((("fixed", 0), ("exact", 0), ("fixed", 1))):
+        port0, port1 = 29490 + 4 * k, 29491 + 4 * k
+        base = [sys.executable, "-m", "scirust_b200.parallel.proof_tcp_multihost", "--n", "4", "--dim", "3001",
+                "--seed", "7", "--combine", combine, "--native", str(native)]
+        procs = [subprocess.Popen(base + ["--rank", "0", "--my-addr", f"127.0.0.1:{port0}"], env=env,
+                                  stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True),
+                 subprocess.Popen(base + ["--rank", "1", "--my-addr", f"127.0.0.1:{port1}", "--parent-addr",
+                                          f"127.0.0.1:{port0}"], env=env, stdout=subprocess.PIPE,
+                                  stderr=subprocess.PIPE, text=True),
+                 subprocess.Popen(base + ["--rank", "2", "--parent-addr", f"127.0.0.1:{port0}"], env=env,
+                                  stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True),
+                 subprocess.Popen(base + ["--rank", "3", "--parent-addr", f"127.0.0.1:{port1}"], env=env,
+                                  stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)]
+        outs = [p.communicate(timeout=120) for p in procs]
+        assert all(p.returncode == 0 for p in procs), outs
+        assert "verdict=PASS" in outs[0][0], outs[0]
+        fps = {o[0].split("fingerprint=")[1].split()[0] for o in outs}
+        assert len(fps) == 1
+    # a root without a listener address is a usage error, not a hang
+    r = subprocess.run([sys.executable, "-m", "scirust_b200.parallel.proof_tcp_multihost", "--rank", "0", "--n", "2"],
+                       env=env, capture_output=True, text=True, timeout=60)
+    assert r.returncode == 2
+    from scirust_b200.parallel.bench_reduction_overhead import bench
+    rows = bench(4096, [1, 3], 5)
+    assert all(row["pinned_distinct_results"] == 1 for row in rows)
+
+
+def test_rank_leaves_job_restarts_from_checkpoint_and_matches_uninterrupted_run(tmp_path):
+    """Recovery: rank 1 leaves between steps, rank 0 gets PeerLost from the heartbeat, the supervisor restarts the job
+    from the latest checkpoint, and the final loss and weights equal the uninterrupted run's bit for bit."""
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "mp"))
+    from elastic_worker import worker
+    from scirust_b200.train.elastic import EXIT_PEER_LOST, run_elastic
+
+    a, b = tmp_path / "interrupted", tmp_path / "straight"
+    a.mkdir()
+    b.mkdir()
+    hist = run_elastic(worker, 2, args=(str(a), 29540, 6, 1, 3), max_restarts=2, grace_s=30.0)
+    assert len(hist) == 2 and hist[0][1] == 17 and hist[0][0] == EXIT_PEER_LOST and hist[1] == [0, 0]
+    hist2 = run_elastic(worker, 2, args=(str(b), 29550, 6, -1, -1), max_restarts=0)
+    assert hist2 == [[0, 0]]
+    for r in range(2):
+        assert (a / f"final_rank{r}.txt").read_text() == (b / f"final_rank{r}.txt").read_text()
+
+
+def test_status_watchdog_reports_timeout_and_hang_without_a_gpu():
+    import time
+    from scirust_b200.ops._lib import CollectiveTimeout
+    from scirust_b200.train.elastic import StatusWatchdog, StepHung
+    code = {"v": 0}
+    told = []
+    wd = StatusWatchdog(lambda: code["v"], lambda: True, interval_s=0.02, hang_s=5.0, on_error=told.append).start()
+    time.sleep(0.1)
+    wd.check()
+    code["v"] = 5                                  # a kernel recorded "peer flag never arrived"
+    time.sleep(0.2)
+    with pytest.raises(CollectiveTimeout):
+        wd.check()
+    assert len(told) == 1 and told[0].code == 5
+    wd.stop()
+    wd2 = StatusWatchdog(lambda: 0, lambda: False, interval_s=0.02, hang_s=0.1).start()
+    wd2.arm()
+    time.sleep(0.4)
+    with pytest.raises(StepHung):
+        wd2.check()
+    wd2.stop()
