@@ -16,9 +16,12 @@ from scirust_b200.ops import _lib  # noqa: E402
 from scirust_b200.parallel.tensor_parallel import TPContext  # noqa: E402
 from scirust_b200.train import Trainer, TrainerConfig  # noqa: E402
 
-cfg = SciAgentConfig(vocab_size=1024, d_model=256, n_layers=2, n_heads=4, n_kv_heads=2, d_ff=512, max_seq_len=256,
-                     rope_theta=10000.0)
-B, S = 2, 256
+# heads / KV heads / batch from the environment: a KV-head count below the world size replicates KV heads over
+# groups of ranks (their gradients are then summed inside each group)
+H = int(os.environ.get("SB_TP_HEADS", "4"))
+cfg = SciAgentConfig(vocab_size=1024, d_model=64 * H, n_layers=2, n_heads=H, n_kv_heads=int(os.environ.get("SB_TP_KV", "2")),
+                     d_ff=512, max_seq_len=256, rope_theta=10000.0)
+B, S = int(os.environ.get("SB_TP_BATCH", "2")), 256
 g = torch.Generator().manual_seed(7)
 batches = [torch.randint(0, cfg.vocab_size, (B, S + 1), generator=g) for _ in range(3)]
 
@@ -53,5 +56,5 @@ rel = (wf.float() - wn.float()).norm() / wn.float().norm()
 assert rel < 5e-2, rel
 dist.barrier()
 if rank == 0:
-    print("TP_MODEL_OK", lf, ln, l1, float(rel))
+    print(f"TP_MODEL_OK world={world} kv={cfg.n_kv_heads}", lf, ln, l1, float(rel))
 dist.destroy_process_group()

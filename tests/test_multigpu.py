@@ -74,6 +74,15 @@ def test_tp_decoder_trains_like_single_gpu():
     assert "TP_MODEL_OK" in out
 
 
+@pytest.mark.parametrize("world,heads,kv,batch", [(2, 4, 1, 2), (4, 4, 2, 4), (8, 8, 2, 8)])
+def test_tp_decoder_replicated_kv_heads_and_larger_worlds(world, heads, kv, batch):
+    _need(world)
+    out = _run("mp_tp_model.py", world, 29640 + world, extra_env={"SB_TP_HEADS": str(heads), "SB_TP_KV": str(kv),
+                                                                    "SB_TP_BATCH": str(batch)},
+               tag=f"_w{world}_kv{kv}")
+    assert f"TP_MODEL_OK world={world} kv={kv}" in out
+
+
 def test_vocab_parallel_embedding_ce_argmax():
     _need(2)
     out = _run("mp_vocab_parallel.py", 2, 29619)
