@@ -131,11 +131,61 @@ def build_rt(force: bool = False) -> Path:
     return RT_LIB
 
 
+_DECL_RE = None
+
+
+def cuda_entry_points() -> list[tuple[str, str]]:
+    """``(file name, declaration)`` of every ``extern "C"`` entry point defined in ``csrc/*.cu``: the C ABI of
+    ``libscirust_b200_cuda.so``. Declarations are the definitions' signatures with the body cut off."""
+    import re
+    global _DECL_RE
+    if _DECL_RE is None:
+        _DECL_RE = re.compile(r'^extern "C" ([^;{]*?\))\s*\{', re.S | re.M)
+    out = []
+    for src in sorted(CSRC.glob("*.cu")):
+        for m in _DECL_RE.finditer(src.read_text()):
+            out.append((src.name, " ".join(m.group(1).split())))
+    return out
+
+
+API_BEGIN = "// ---- entry points (generated from the definitions by scirust_b200._build.write_api_header) ----"
+API_END = "// ---- end of entry points ----"
+
+
+def api_header_text() -> str:
+    """api.h: the fixed preamble (error codes) plus one declaration per entry point, grouped by source file."""
+    path = CSRC / "api.h"
+    text = path.read_text()
+    head = text.split("#ifdef __cplusplus")[0]
+    lines = [head.rstrip(), "", "#ifdef __cplusplus", 'extern "C" {', "#endif", "", API_BEGIN]
+    cur = None
+    for fname, decl in cuda_entry_points():
+        if fname != cur:
+            lines += ["", f"// {fname}"]
+            cur = fname
+        lines.append(decl + ";")
+    lines += ["", API_END, "", "#ifdef __cplusplus", "}", "#endif", ""]
+    return "\n".join(lines)
+
+
+def write_api_header() -> bool:
+    """Regenerate ``csrc/api.h``; returns True when the file changed."""
+    path = CSRC / "api.h"
+    new = api_header_text()
+    if path.read_text() == new:
+        return False
+    path.write_text(new)
+    return True
+
+
 def build_all(force: bool = False, verbose: bool = False) -> None:
     build_cuda(force=force, verbose=verbose)
     build_rt(force=force)
 
 
 if __name__ == "__main__":
+    if "--api-header" in sys.argv:
+        print("api.h", "rewritten" if write_api_header() else "up to date")
+        sys.exit(0)
     build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print("built:", CUDA_LIB, RT_LIB)

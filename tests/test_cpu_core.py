@@ -413,3 +413,30 @@ def test_attestation_log_certified_bounds_and_guard():
     assert back.verify() and back.profile.numeric_mode.startswith("int8")
     back.profile.model_sha256 = sha256_hex(b"other")
     assert not back.verify()
+
+
+def test_api_header_lists_every_entry_point_and_matches_the_ctypes_tables():
+    """csrc/api.h is generated from the extern "C" definitions: it must be current, and every ctypes signature
+    registered by the ops modules must have the arity of its declaration."""
+    import importlib
+    import re
+    from scirust_b200 import _build
+    from scirust_b200.ops import _lib
+    assert (_build.CSRC / "api.h").read_text() == _build.api_header_text(), \
+        "api.h is stale: run python -m scirust_b200._build --api-header"
+    decls = {}
+    for _f, d in _build.cuda_entry_points():
+        m = re.match(r".*?\b(sb_\w+)\((.*)\)$", d)
+        args = [a for a in m.group(2).split(",") if a.strip() and a.strip() != "void"]
+        decls[m.group(1)] = len(args)
+    assert len(decls) >= 60
+    for mod in ("basic", "gemm", "attention", "decode", "conv", "sampling", "canonical"):
+        importlib.import_module(f"scirust_b200.ops.{mod}")
+    for mod in ("symm", "fused_allreduce", "small_collectives", "tensor_parallel", "vocab_parallel"):
+        importlib.import_module(f"scirust_b200.parallel.{mod}")
+    checked = 0
+    for name, sig in _lib._CUDA_SIGS.items():
+        assert name in decls, f"{name} has a ctypes signature but no entry point"
+        assert len(sig) == decls[name], f"{name}: ctypes table has {len(sig)} parameters, the definition {decls[name]}"
+        checked += 1
+    assert checked >= 40
