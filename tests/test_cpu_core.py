@@ -440,3 +440,40 @@ def test_api_header_lists_every_entry_point_and_matches_the_ctypes_tables():
         assert len(sig) == decls[name], f"{name}: ctypes table has {len(sig)} parameters, the definition {decls[name]}"
         checked += 1
     assert checked >= 40
+
+
+def test_raw_runtime_validation_and_strict_compile_without_a_gpu():
+    from scirust_b200.runtime import (RawAccess, RawBinding, RawBuffer, RawError, RawLaunchConfig, compile_cuda_c,
+                                      validate_alias_groups, validate_launch_geometry)
+    from scirust_b200.runtime.raw import validate_bindings
+    ok = RawLaunchConfig((4, 1, 1), (256, 1, 1), 1024)
+    validate_launch_geometry(ok)
+    for bad, frag in ((RawLaunchConfig((0, 1, 1), (256, 1, 1)), "grid dimensions must be non-zero"),
+                      (RawLaunchConfig((1, 1, 1), (0, 1, 1)), "block dimensions must be non-zero"),
+                      (RawLaunchConfig((1, 70000, 1), (32, 1, 1)), "grid dimension 1"),
+                      (RawLaunchConfig((1, 1, 1), (32, 32, 2)), "2048 threads"),
+                      (RawLaunchConfig((1, 1, 1), (32, 1, 1), 300 * 1024), "shared-memory")):
+        with pytest.raises(RawError, match=frag):
+            validate_launch_geometry(bad)
+    a, b = RawBuffer(1024), RawBuffer(1024)
+    R, W = RawAccess.READ, RawAccess.WRITE
+    validate_alias_groups([RawBinding(a, R), RawBinding(a, R), RawBinding(b, W)])             # two readers share
+    validate_alias_groups([RawBinding(a, R, 0, 512), RawBinding(a, W, 512, 512)])             # disjoint halves
+    with pytest.raises(RawError, match="alias"):
+        validate_alias_groups([RawBinding(a, R), RawBinding(b, R), RawBinding(a, W, 100, 8)])
+    with pytest.raises(RawError, match="alias"):
+        validate_alias_groups([RawBinding(a, RawAccess.READ_WRITE), RawBinding(a, RawAccess.READ_WRITE)])
+    with pytest.raises(RawError, match="exceeds buffer bounds"):
+        validate_bindings([RawBinding(a, R, 1000, 100)])
+    with pytest.raises(RawError, match="non-zero"):
+        validate_bindings([RawBinding(a, R, 10, 0)])
+    src = 'extern "C" __global__ void axpy(float* y, const float* x, float a, int n) {' \
+          ' int i = blockIdx.x * blockDim.x + threadIdx.x; if (i < n) y[i] = a * x[i] + y[i]; }'
+    ptx = compile_cuda_c(src).decode(errors="replace")
+    assert "axpy" in ptx and "sm_100a" in ptx
+    assert "fma.rn.f32" not in ptx and "mul.rn.f32" in ptx and "add.rn.f32" in ptx        # --fmad=false: no contraction
+    assert "fma.rn.f32" in compile_cuda_c(src, strict_ieee=False).decode(errors="replace")
+    with pytest.raises(RawError, match="pinned"):
+        compile_cuda_c(src, extra_options=["--use_fast_math"])
+    with pytest.raises(RawError, match="compilation failed"):
+        compile_cuda_c("this is not CUDA")
