@@ -477,3 +477,63 @@ def test_raw_runtime_validation_and_strict_compile_without_a_gpu():
         compile_cuda_c(src, extra_options=["--use_fast_math"])
     with pytest.raises(RawError, match="compilation failed"):
         compile_cuda_c("this is not CUDA")
+
+
+def test_squeezellm_spqr_omniquant_aqlm_quip_and_fake_quant():
+    from scirust_b200 import quantization_methods as QM
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(64, 32, generator=g) * 0.1
+    w[3, 5], w[40, 7] = 2.5, -3.0                                    # heavy tails
+    qmax = 7.0
+
+    def rtn(x):
+        s = x.abs().amax(0) / qmax
+        return torch.clamp(torch.round(x / s), -qmax, qmax) * s
+    e_rtn = (w - rtn(w)).pow(2).sum()
+
+    # SqueezeLLM: lower sensitivity-weighted error than the uniform grid of the same size; deterministic
+    sens = torch.ones(w.numel())
+    cb = QM.SqueezeLlmCodebook.fit(w.reshape(-1), sens, 4, 25)
+    rec = cb.dequantize(cb.quantize(w))
+    s_all = w.abs().max() / qmax
+    uni = torch.clamp(torch.round(w / s_all), -qmax - 1, qmax) * s_all
+    assert (w - rec).pow(2).sum() < 0.5 * (w - uni).pow(2).sum()
+    assert torch.equal(cb.levels, QM.SqueezeLlmCodebook.fit(w.reshape(-1), sens, 4, 25).levels)
+    assert cb.levels.numel() == 16 and torch.equal(cb.levels, torch.sort(cb.levels).values)
+    # SpQR: 1 % outliers remove most of the dense error, and are exactly the largest errors
+    sp = QM.SpqrOutliers.extract(w, uni, 0.01)
+    fixed = sp.apply(uni)
+    assert sp.indices.numel() == round(w.numel() * 0.01)
+    assert (w - fixed).pow(2).sum() < (w - uni).pow(2).sum()
+    assert float((w - fixed).abs().max()) <= float((w - uni).abs().reshape(-1).sort().values[-sp.indices.numel() - 1]) + 1e-7
+    assert QM.SpqrOutliers.extract(w, uni, 0.0).indices.numel() == 0
+    # OmniQuant: never worse than RTN per channel, strictly better where a channel has an outlier
+    oq = QM.omniquant_quantize(w, 4)
+    e_oq = (w - oq.dequantize()).pow(2).sum(0)
+    e_r = (w - rtn(w)).pow(2).sum(0)
+    assert bool((e_oq <= e_r + 1e-9).all()) and e_oq[5] < e_r[5] and float(oq.gammas[5]) < 1.0 and e_oq.sum() < e_r.sum()
+    assert oq.codes.dtype == torch.int8 and int(oq.codes.abs().max()) <= 7
+    # AQLM: two additive codebooks beat one at the same group size; reported bit budget
+    a1 = QM.quantize_aqlm(w, 8, 1, 16, 6)
+    a2 = QM.quantize_aqlm(w, 8, 2, 16, 6)
+    assert (w - a2.dequantize()).pow(2).sum() < (w - a1.dequantize()).pow(2).sum()
+    assert a2.bits_per_weight() == 1.0 and a2.dequantize().shape == w.shape
+    # QuIP#: the transform is orthonormal and self-inverse, E8 points are lattice points, error shrinks with bits
+    v = torch.randn(37, generator=g)
+    t = QM.random_hadamard_transform(v, 9)
+    assert torch.allclose(QM.inverse_random_hadamard_transform(t, 9, 37), v, atol=1e-6)
+    assert abs(float(t.pow(2).sum()) - float(v.pow(2).sum())) < 1e-4
+    pts = QM.nearest_e8(torch.randn(200, 8, generator=g) * 2)
+    twice = pts * 2
+    assert torch.equal(twice, twice.round())                                     # integers or half-integers
+    assert bool(((twice.long() % 2 == 0).all(1) | (twice.long() % 2 != 0).all(1)).all())   # never mixed
+    assert bool((pts.sum(1).round().long() % 2 == 0).all())                      # even coordinate sum
+    q2, q4 = QM.quantize_quip(w, 2, 3), QM.quantize_quip(w, 4, 3)
+    assert (w - q4.dequantize()).pow(2).sum() < (w - q2.dequantize()).pow(2).sum()
+    assert torch.equal(q4.dequantize(), QM.quantize_quip(w, 4, 3).dequantize())
+    # fake quantisation: values on the grid, straight-through gradient with zero outside the clip range
+    x = torch.tensor([0.11, -0.52, 3.0, -4.0], requires_grad=True)
+    y = QM.fake_quantize(x, 4, scale=0.1)
+    assert torch.allclose(y, torch.tensor([0.1, -0.5, 0.7, -0.7]))
+    y.sum().backward()
+    assert x.grad.tolist() == [1.0, 1.0, 0.0, 0.0]
