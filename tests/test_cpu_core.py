@@ -537,3 +537,73 @@ def test_squeezellm_spqr_omniquant_aqlm_quip_and_fake_quant():
     assert torch.allclose(y, torch.tensor([0.1, -0.5, 0.7, -0.7]))
     y.sum().backward()
     assert x.grad.tolist() == [1.0, 1.0, 0.0, 0.0]
+
+
+def test_residual_latent_adaptive_and_tiered_kv_caches():
+    from scirust_b200.nn.kv_cache import PlainKvCache
+    from scirust_b200.nn.kv_cache_latent import (AdaptiveKvPlanner, ResidualLatentCacheError,
+                                                 ResidualQuantizedLatentKvCache, SparseResidualConfig,
+                                                 TieredResidualLatentBackend, estimate_channel_bytes, fit_basis)
+    g = torch.Generator().manual_seed(0)
+    dim, n = 32, 40
+    low = torch.randn(n, 6, generator=g) @ torch.randn(6, dim, generator=g)       # rows near a rank-6 subspace
+    K = low + 0.02 * torch.randn(n, dim, generator=g)
+    V = torch.randn(n, 6, generator=g) @ torch.randn(6, dim, generator=g) + 0.02 * torch.randn(n, dim, generator=g)
+    K[7, 3] += 4.0                                                               # an off-subspace spike
+    kb, vb = fit_basis(K), fit_basis(V)
+    plain = PlainKvCache(dim)
+    full = ResidualQuantizedLatentKvCache(dim, n, dim, dim, "fp32", "fp32", key_basis=kb, value_basis=vb)
+    lat = ResidualQuantizedLatentKvCache(dim, n, 8, 8, "int8", "int8", key_basis=kb, value_basis=vb)
+    res = ResidualQuantizedLatentKvCache(dim, n, 8, 8, "int8", "int8", SparseResidualConfig(2, "int8"),
+                                         SparseResidualConfig(2, "int8"), kb, vb)
+    for t in range(n):
+        for c in (plain, full, lat, res):
+            c.append(K[t], V[t])
+    q = torch.randn(dim, generator=g)
+    want = plain.decode_step(q)
+    assert torch.allclose(full.attention(q), want, atol=1e-4)                   # full rank, fp32: the exact attention
+    e_lat, e_res = (lat.attention(q) - want).norm(), (res.attention(q) - want).norm()
+    assert e_lat < 0.2 * want.norm() and e_res <= e_lat + 1e-6
+    k7, _ = res.reconstruct_token(7)
+    k7_lat, _ = lat.reconstruct_token(7)
+    assert (k7 - K[7]).norm() < (k7_lat - K[7]).norm()          # the residual slots pick up what the subspace lost
+    assert len(res.key_residual_indices_for(7)) == 2 and lat.key_residual_indices_for(7) is None
+    assert res.bytes_per_token() == 2 * estimate_channel_bytes(8, "int8", SparseResidualConfig(2, "int8"))
+    assert res.allocated_bytes() == n * res.bytes_per_token() and res.used_bytes() == res.allocated_bytes()
+    with pytest.raises(ResidualLatentCacheError, match="full"):
+        res.append(K[0], V[0])
+    res.remove_oldest()
+    assert len(res) == n - 1 and torch.allclose(res.reconstruct_token(6)[0], k7)
+    with pytest.raises(ResidualLatentCacheError):
+        ResidualQuantizedLatentKvCache(dim, 4, 8, 8).append(torch.full((dim,), float("nan")), V[0])
+
+    # planner: a larger budget never gives a worse plan, every plan respects its budget, planning is deterministic
+    pl = AdaptiveKvPlanner(dim, ranks=(4, 8, 16), slot_choices=(0, 2), formats=("int8", "int4"))
+    for t in range(24):
+        pl.observe(K[t], V[t])
+    small, _, _ = pl.plan(20)
+    big, _, _ = pl.plan(64)
+    assert small.bytes_per_token <= 20 and big.bytes_per_token <= 64 and big.error <= small.error + 1e-9
+    assert pl.plan(20)[0] == small
+    with pytest.raises(ResidualLatentCacheError, match="budget"):
+        pl.plan(3)
+    cache = pl.build(64, 16)
+    cache.append(K[0], V[0])
+    assert cache.bytes_per_token() == big.bytes_per_token
+
+    # tiers: rows age hot -> warm -> cold, the cold tier evicts, attention spans all tiers
+    hot = dict(capacity=4, key_rank=dim, value_rank=dim, key_fmt="fp32", value_fmt="fp32")
+    warm = dict(capacity=8, key_rank=12, value_rank=12, key_fmt="int8", value_fmt="int8",
+                key_residual=SparseResidualConfig(2, "int8"), value_residual=SparseResidualConfig(2, "int8"))
+    cold = dict(capacity=8, key_rank=8, value_rank=8, key_fmt="int4", value_fmt="int4")
+    tb = TieredResidualLatentBackend(dim, hot, warm, cold, kb, vb)
+    for t in range(26):
+        tb.append(K[t], V[t])
+    tel = tb.telemetry()
+    assert (tel.hot_tokens, tel.warm_tokens, tel.cold_tokens, tel.evictions) == (4, 8, 8, 6) and len(tb) == 20
+    ref = PlainKvCache(dim)
+    for t in range(6, 26):
+        ref.append(K[t], V[t])
+    got, wantt = tb.attention(q), ref.decode_step(q)
+    assert (got - wantt).norm() < 0.35 * wantt.norm()
+    assert tel.planned_persistent_bytes <= tel.allocated_bytes
