@@ -77,3 +77,18 @@ def test_raw_runtime_compiles_and_launches_with_validated_bindings():
         rt.launch(k, RawLaunchConfig((1, 1, 1), (2048, 1, 1)), [RawBinding(by, RawAccess.READ_WRITE),
                                                                  RawBinding(bx, RawAccess.READ)],
                   scalars=[C.c_float(1.0), C.c_int(n)])
+
+
+def test_canonical_facade_conformance_device_equals_cpu_bit_for_bit():
+    """Every conformance graph (element-wise with NaN / -0 / inf operands, matmul + permute + reshape, broadcast +
+    ordered reduce, batched matmul) gives the CPU adapter's bits on the device adapter; exp / log are refused there."""
+    from scirust_b200.canonical import Graph, ReferenceJitSession, run_conformance
+    cpu, dev = run_conformance("cpu"), run_conformance("cuda")
+    for name in cpu:
+        for a, b in zip(cpu[name], dev[name]):
+            assert torch.equal(a.view(torch.int32), b.view(torch.int32)), name
+    g = Graph()
+    g.set_outputs(g.exp(g.input("x", (4,))))
+    with pytest.raises(K.Unsupported):
+        ReferenceJitSession("cuda").run(g, {"x": torch.zeros(4)})
+    assert torch.allclose(ReferenceJitSession("cpu").run(g, {"x": torch.zeros(4)})[0], torch.ones(4))
