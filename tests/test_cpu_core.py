@@ -607,3 +607,70 @@ def test_residual_latent_adaptive_and_tiered_kv_caches():
     got, wantt = tb.attention(q), ref.decode_step(q)
     assert (got - wantt).norm() < 0.35 * wantt.norm()
     assert tel.planned_persistent_bytes <= tel.allocated_bytes
+
+
+def test_native_cpu_flash_attention_w8a8_block_and_kv_cache():
+    import math
+    from scirust_b200 import cpu_kernels as CK
+    g = torch.Generator().manual_seed(0)
+    B, S, H, Hkv, dh = 2, 70, 4, 2, 16
+    q, k, v = (torch.randn(B, S, h, dh, generator=g) for h in (H, Hkv, Hkv))
+    kr, vr = k.repeat_interleave(H // Hkv, 2), v.repeat_interleave(H // Hkv, 2)
+    for causal in (True, False):
+        sc = torch.einsum("bqhd,bkhd->bhqk", q, kr) / math.sqrt(dh)
+        if causal:
+            sc = sc.masked_fill(torch.triu(torch.ones(S, S, dtype=torch.bool), 1), float("-inf"))
+        ref = torch.einsum("bhqk,bkhd->bqhd", sc.softmax(-1), vr)
+        out1 = CK.flash_attention(q, k, v, causal, block=16, threads=1)
+        out4 = CK.flash_attention(q, k, v, causal, block=16, threads=4)
+        assert torch.allclose(out1, ref, atol=2e-5) and torch.equal(out1, out4)       # thread-count independent
+    # W8A8: equals the reference arithmetic written out in torch (int32 accumulation, one rescale)
+    x, w = torch.randn(9, 40, generator=g), torch.randn(40, 24, generator=g) * 0.2
+    wq, ws = CK.quantize_weight(w)
+    sx = x.abs().amax(1) / 127.0
+    xv = x / sx[:, None]
+    xq = torch.where(xv >= 0, torch.floor(xv + 0.5), torch.ceil(xv - 0.5)).clamp(-128, 127)
+    want = (xq.to(torch.int64) @ wq.to(torch.int64)).float() * (sx[:, None] * ws[None, :])
+    got = CK.w8a8_linear(x, wq, ws)
+    assert torch.equal(got, want)
+    assert (got - x @ w).abs().max() < 0.05 * (x @ w).abs().max()
+    # int8 decoder block close to its fp32 statement
+    S2, d, ff, Hh, Hk = 24, 32, 48, 4, 2
+    ws_ = {n: torch.randn(a, b, generator=g) * (1.0 / math.sqrt(a)) for n, (a, b) in
+           dict(wq=(d, d), wk=(d, d // 2), wv=(d, d // 2), wo=(d, d), wg=(d, ff), wu=(d, ff), wd=(ff, d)).items()}
+    g1, g2 = torch.ones(d), torch.ones(d)
+    blk = CK.Int8DecoderBlock(Hh, Hk, 10000.0, 1e-5, g1, g2, **ws_)
+    xs = torch.randn(S2, d, generator=g)
+    y = blk.forward(xs)
+
+    def rms(t):
+        return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + 1e-5)
+
+    def rope(t, nh):
+        dh2 = d // Hh
+        t = t.view(S2, nh, dh2 // 2, 2)
+        ang = torch.arange(S2).float()[:, None] * (10000.0 ** (-2 * torch.arange(dh2 // 2).float() / dh2))[None]
+        c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        return torch.stack([t[..., 0] * c - t[..., 1] * s, t[..., 0] * s + t[..., 1] * c], -1).reshape(S2, nh, dh2)
+    h = rms(xs)
+    qf, kf, vf = rope(h @ ws_["wq"], Hh), rope(h @ ws_["wk"], Hk), (h @ ws_["wv"]).view(S2, Hk, d // Hh)
+    ctx = CK.flash_attention(qf[None], kf[None], vf[None], True)[0].reshape(S2, d)
+    x2 = xs + ctx @ ws_["wo"]
+    h2 = rms(x2)
+    ref = x2 + (torch.nn.functional.silu(h2 @ ws_["wg"]) * (h2 @ ws_["wu"])) @ ws_["wd"]
+    assert (y - ref).norm() < 0.06 * ref.norm()
+    assert torch.equal(y, blk.forward(xs, threads=3))
+    # KV cache: fp32 rows give the plain attention, int8 rows stay close at a quarter of the bytes
+    dim = 32
+    cf, cq = CK.NativeKvCache(dim, 50), CK.NativeKvCache(dim, 50, quantized=True)
+    K, V = torch.randn(50, dim, generator=g), torch.randn(50, dim, generator=g)
+    for t in range(50):
+        cf.append(K[t], V[t])
+        cq.append(K[t], V[t])
+    qq = torch.randn(dim, generator=g)
+    want = torch.softmax((K @ qq) / math.sqrt(dim), 0) @ V
+    assert torch.allclose(cf.attend(qq, block=8), want, atol=1e-5)
+    assert (cq.attend(qq) - want).norm() < 0.05 * want.norm()
+    assert cq.nbytes() < 0.3 * cf.nbytes() and len(cf) == 50
+    with pytest.raises(MemoryError):
+        cf.append(K[0], V[0])
