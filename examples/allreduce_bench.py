@@ -50,7 +50,7 @@ def main():
         for _ in range(a.iters):
             scratch.zero_()
             dist.barrier()
-            torch.cuda._sleep(400_000)      # the GPU spins ~0.2 ms while the host queues the call
+            torch.cuda._sleep(3_000_000)    # the GPU spins ~1.5 ms while the host queues the call
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             fn()
@@ -77,6 +77,12 @@ def main():
             _lib.check_status(dev)
             bus = 2 * (world - 1) / world * n * 2 / (ms * 1e6)
             rows.append({"elems": n, "impl": f"fused/{ctas} CTAs", "ms": round(ms, 4), "busbw_gbs": round(bus, 1)})
+        ar = FusedAllReduce(region, src, dst)
+        ms = timed(lambda: ar.reduce(0, n, 1.0 / world, lean=True))
+        _lib.check_status(dev)
+        bus = 2 * (world - 1) / world * n * 2 / (ms * 1e6)
+        rows.append({"elems": n, "impl": f"fused lean/{ar.lean_ctas} CTAs x 128 threads", "ms": round(ms, 4),
+                     "busbw_gbs": round(bus, 1)})
     if rank == 0:
         print(json.dumps({"world": world, "rows": rows}))
     region.close()

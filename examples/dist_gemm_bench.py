@@ -41,7 +41,7 @@ def timed(fn, iters, warmup, scratch):
         scratch.zero_()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         dist.barrier()
-        torch.cuda._sleep(400_000)      # the GPU spins ~0.2 ms while the host queues the call: no launch latency in the time
+        torch.cuda._sleep(3_000_000)    # the GPU spins ~1.5 ms while the host queues the call: no launch latency in the time
         e0.record()
         fn()
         e1.record()

@@ -46,6 +46,7 @@ int sb_ipc_close(void* p);
 int sb_ipc_handle_size();
 int sb_flag_words_per_slot();
 int sb_allreduce_bf16(void* const* in_ptrs, void* const* out_ptrs, void* const* flag_ptrs, int rank, int W, size_t n_elems, float scale, uint32_t epoch, int slot, int out_fp32, unsigned int* cta_counter, int n_ctas, int wait_ms, int* status, void* stream);
+int sb_allreduce_bf16_lean(void* const* in_ptrs, void* const* out_ptrs, void* const* flag_ptrs, int rank, int W, size_t n_elems, float scale, uint32_t epoch, int slot, int out_fp32, unsigned int* cta_counter, int n_ctas, int wait_ms, int* status, void* stream);
 int sb_small_collective(void* const* in_ptrs, void* const* flag_ptrs, int rank, int W, int mode, int in_fp32, size_t n, int rows, const void* residual, void* out, uint32_t* epoch_word, int slot, unsigned int* cta_counter, int n_ctas, int wait_ms, int* status, void* stream);
 int sb_wait_probe(const void* flags, int W, uint32_t epoch, int wait_ms, int* status, void* stream);
 
@@ -64,6 +65,7 @@ int sb_bias_act(const void* x, const float* bias, void* y, size_t total, int C, 
 int sb_set_pdl(int on);
 int sb_gemv(const void* X, int ldx, const void* W, int ldw, const float* scale, const void* R, int ldr, void* out_bf16, int ldo, float* out_f32, int M, int N, int K, int is_int8, int splits, float* workspace, int prologue, const void* norm_w, float eps, int* status, void* stream);
 int sb_gemv_allreduce(const void* X, int ldx, const void* W, int ldw, const float* scale, const void* R, int ldr, void* out_bf16, int ldo, int M, int N, int K, int is_int8, int splits, float* workspace, int prologue, const void* norm_w, float eps, void* const* recv_ptrs, void* const* flag_ptrs, uint32_t* epoch_word, unsigned int* done_ctr, int rank, int world, int rows, int wait_ms, int* status, void* stream);
+int sb_gemv_argmax(const void* X, int ldx, const void* W, int ldw, const float* scale, float* logits_f32, int M, int N, int K, int is_int8, int splits, float* workspace, int prologue, const void* norm_w, float eps, int32_t* amax_ws, int64_t* out_tokens, int64_t* generated, int gen_stride, int step, int col_offset, void* const* cand_ptrs, void* const* flag_ptrs, uint32_t* epoch_word, int rank, int world, int wait_ms, int* status, void* stream);
 int sb_kv_append(const void* qkv, int ld, int H, int Hkv, int dh, void* pool, const int* block_table, int max_blocks, int page, const int* seq_of, const int* pos, int n_tok, void* stream);
 int sb_rope_kv_append(void* qkv, int ld, int H, int Hkv, int dh, const float* cos_t, const float* sin_t, void* pool, const int* block_table, int max_blocks, int page, const int* seq_of, const int* pos, int n_tok, void* stream);
 int sb_decode_attention(const void* q, int ldq, const void* pool, const int* block_table, int max_blocks, int page, const int* seq_len, int B, int H, int Hkv, int dh, int n_splits, float scale, float* part_o, float* part_ml, unsigned int* counters, void* out, int ldo, void* stream);

@@ -56,8 +56,8 @@ __device__ __forceinline__ void accum8(float* acc, const uint4& v) {
 
 // U = 16-byte vectors per thread and iteration of the reduce phase; with W ranks U * W peer loads are in flight
 // before the first add (the host picks U = 8 / 4 / 2 for W <= 2 / <= 4 / larger, so about sixteen).
-template <int U, int THREADS>
-__global__ void __launch_bounds__(THREADS)
+template <int U, int RG, int THREADS, int MIN_BLOCKS>
+__global__ void __launch_bounds__(THREADS, MIN_BLOCKS)
 allreduce_bf16_kernel(const __grid_constant__ AllReduceParams p) {
   __shared__ int s_ok;
   const int W = p.W;
@@ -82,7 +82,6 @@ allreduce_bf16_kernel(const __grid_constant__ AllReduceParams p) {
     const size_t lo = min(p.n, per * p.rank);
     const size_t hi = min(p.n, lo + per);
     const size_t n8 = (hi - lo) / 8;
-    constexpr int RG = 16 / U;       // ranks whose loads are issued together (U * RG = 16 vectors in registers)
     for (size_t i0 = gtid; i0 < n8; i0 += U * stride) {
       float accs[U][8];
 #pragma unroll
@@ -313,9 +312,9 @@ extern "C" int sb_flag_words_per_slot() { return SLOT_WORDS; }
 
 // in_ptrs/out_ptrs/flag_ptrs: host arrays of W device pointers (peer-mapped; entry `rank` is local).
 // n_elems must be a multiple of 8; buffers 16-byte aligned. wait_ms <= 0 selects the default.
-extern "C" int sb_allreduce_bf16(void* const* in_ptrs, void* const* out_ptrs, void* const* flag_ptrs, int rank,
-                                 int W, size_t n_elems, float scale, uint32_t epoch, int slot, int out_fp32,
-                                 unsigned int* cta_counter, int n_ctas, int wait_ms, int* status, void* stream) {
+static int allreduce_bf16_impl(void* const* in_ptrs, void* const* out_ptrs, void* const* flag_ptrs, int rank,
+                               int W, size_t n_elems, float scale, uint32_t epoch, int slot, int out_fp32,
+                               unsigned int* cta_counter, int n_ctas, int wait_ms, int* status, void* stream, bool lean) {
   if (W < 1 || W > MAX_WORLD || rank < 0 || rank >= W || (n_elems & 7) || n_ctas < 1) return SB_ERR_ARG;
   if (cta_counter == nullptr || status == nullptr || in_ptrs == nullptr || out_ptrs == nullptr || flag_ptrs == nullptr)
     return SB_ERR_ARG;
@@ -332,13 +331,37 @@ extern "C" int sb_allreduce_bf16(void* const* in_ptrs, void* const* out_ptrs, vo
   p.wait_ns = wait_ms > 0 ? static_cast<uint64_t>(wait_ms) * 1000000ull : kPeerWaitNsDefault;
   p.cta_counter = cta_counter;
   p.status = status;
-  // eight vectors per thread need more than the 128 registers a 512-thread block leaves: half-size blocks, twice as many
-  if (W <= 2) allreduce_bf16_kernel<8, 256><<<2 * n_ctas, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  else if (W <= 4) allreduce_bf16_kernel<4, 512><<<n_ctas, 512, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  else allreduce_bf16_kernel<2, 512><<<n_ctas, 512, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  const cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (lean) {
+    // 128 threads x 64 registers: a CTA of this shape fits on an SM beside a resident GEMM CTA (448 threads x 128
+    // registers), so a bucket reduced on a side stream during backward neither waits for whole SMs to drain nor
+    // keeps GEMM CTAs off the SMs it sits on while it waits for its peers
+    if (W <= 2) allreduce_bf16_kernel<4, 2, 128, 8><<<n_ctas, 128, 0, st>>>(p);
+    else if (W <= 4) allreduce_bf16_kernel<2, 4, 128, 8><<<n_ctas, 128, 0, st>>>(p);
+    else allreduce_bf16_kernel<1, 8, 128, 8><<<n_ctas, 128, 0, st>>>(p);
+  } else {
+    // sixteen vectors per thread; eight per rank need more than the 128 registers a 512-thread block leaves:
+    // half-size blocks, twice as many
+    if (W <= 2) allreduce_bf16_kernel<8, 2, 256, 1><<<2 * n_ctas, 256, 0, st>>>(p);
+    else if (W <= 4) allreduce_bf16_kernel<4, 4, 512, 1><<<n_ctas, 512, 0, st>>>(p);
+    else allreduce_bf16_kernel<2, 8, 512, 1><<<n_ctas, 512, 0, st>>>(p);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
 
+extern "C" int sb_allreduce_bf16(void* const* in_ptrs, void* const* out_ptrs, void* const* flag_ptrs, int rank,
+                                 int W, size_t n_elems, float scale, uint32_t epoch, int slot, int out_fp32,
+                                 unsigned int* cta_counter, int n_ctas, int wait_ms, int* status, void* stream) {
+  return allreduce_bf16_impl(in_ptrs, out_ptrs, flag_ptrs, rank, W, n_elems, scale, epoch, slot, out_fp32, cta_counter,
+                             n_ctas, wait_ms, status, stream, false);
+}
+// Same collective, same bits, in CTAs of 128 threads x 64 registers for calls that overlap other kernels.
+extern "C" int sb_allreduce_bf16_lean(void* const* in_ptrs, void* const* out_ptrs, void* const* flag_ptrs, int rank,
+                                      int W, size_t n_elems, float scale, uint32_t epoch, int slot, int out_fp32,
+                                      unsigned int* cta_counter, int n_ctas, int wait_ms, int* status, void* stream) {
+  return allreduce_bf16_impl(in_ptrs, out_ptrs, flag_ptrs, rank, W, n_elems, scale, epoch, slot, out_fp32, cta_counter,
+                             n_ctas, wait_ms, status, stream, true);
+}
 
 // mode 0: all-reduce sum (+ residual) of n elements -> bf16 `out` (local memory);
 // mode 1: all-gather of `rows` rows of n 16-byte words per rank -> out[row][rank][n].

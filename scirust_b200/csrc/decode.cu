@@ -99,7 +99,130 @@ struct GemvParams {
     unsigned int* done_ctr;
     uint64_t wait_ns;
   } coll;
+  // LM head fused with the greedy arg-max (amax.out_tokens != nullptr; scirust-cuda/src/bf16_lm_head_argmax.rs:46-176):
+  // the CTA that finishes a block of columns keeps its final values in shared memory, reduces them to one
+  // (value, column) per row and the last CTA of the grid reduces those and writes the token to the device-side
+  // feedback buffer: no logits round trip, no second and third launch. With amax.W > 1 the head is sharded over
+  // the vocabulary (col_offset = first global column of this rank): the last CTA stores the rank's candidates into
+  // slot [parity][rank] of every rank's `cand`, raises its flag on every rank, waits (bounded) for the W flags and
+  // reduces the W candidates, so every rank writes the same token.
+  struct {
+    float* pval; int* pidx;            // [M][gridDim.x]
+    unsigned int* ctr;                 // zero between calls
+    int64_t* out_tokens; int64_t* generated; int gen_stride, step;
+    int col_offset, W, rank;
+    unsigned long long* cand[MAX_WORLD];   // rank r's candidates: [2][W][8] of (value bits << 32 | column)
+    uint32_t* flags[MAX_WORLD];            // rank r's epoch words [MAX_WORLD]
+    uint32_t* epoch_word;
+    uint64_t wait_ns;
+  } amax;
 };
+
+// Arg-max order of the greedy loop (`best = row[0]; if v > best`, scirust-cuda/src/decode.rs:107-114): the larger
+// value wins, among equal values the lower column. Both operands are numbers (NaN never enters); -inf at a real
+// column beats the empty sentinel (-inf, 0x7fffffff).
+__device__ __forceinline__ bool argmax_better(float v, int i, float best, int bi) {
+  return v > best || (v == best && i < bi);
+}
+__device__ __forceinline__ void warp_argmax(float& best, int& bi) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (argmax_better(ov, oi, best, bi)) { best = ov; bi = oi; }
+  }
+}
+
+// Tail of the fused LM head: `vals[m * cols_per_cta + c]` holds the final values of this CTA's `ncols` columns.
+__device__ __noinline__ void gemv_argmax_tail(const GemvParams& p, float* vals, int cols_per_cta, int col0, int ncols,
+                                              int* s_flag) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int nblk = gridDim.x;
+  constexpr int NONE = 0x7fffffff;
+  __syncthreads();
+  for (int m = warp; m < p.M; m += nw) {
+    float best = -INFINITY;
+    int bi = NONE;
+    for (int c = lane; c < ncols; c += 32) {
+      const float v = vals[m * cols_per_cta + c];
+      if (v != v) continue;                        // a NaN is skipped explicitly ...
+      const int gi = p.amax.col_offset + col0 + c;
+      if (argmax_better(v, gi, best, bi)) { best = v; bi = gi; }
+    }
+    warp_argmax(best, bi);
+    if (lane == 0) {
+      if (col0 == 0 && p.amax.col_offset == 0) {   // ... except in column 0, where it makes token 0 win outright
+        const float f = vals[m * cols_per_cta];
+        if (f != f) { best = INFINITY; bi = 0; }
+      }
+      p.amax.pval[m * nblk + blockIdx.x] = best;
+      p.amax.pidx[m * nblk + blockIdx.x] = bi;
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(p.amax.ctr, 1u);
+    *s_flag = (prev == static_cast<unsigned int>(nblk) - 1u) ? 1 : 0;
+    if (*s_flag) *p.amax.ctr = 0;
+  }
+  __syncthreads();
+  if (!*s_flag) return;
+  __threadfence();
+  const int W = p.amax.W;
+  const uint32_t epoch = W > 1 ? *reinterpret_cast<volatile uint32_t*>(p.amax.epoch_word) + 1u : 0u;
+  for (int m = warp; m < p.M; m += nw) {
+    float best = -INFINITY;
+    int bi = NONE;
+    for (int s = lane; s < nblk; s += 32) {
+      const float v = __ldcg(p.amax.pval + m * nblk + s);
+      const int i = __ldcg(p.amax.pidx + m * nblk + s);
+      if (argmax_better(v, i, best, bi)) { best = v; bi = i; }
+    }
+    warp_argmax(best, bi);
+    if (W <= 1) {
+      if (lane == 0) {
+        if (bi == NONE) bi = 0;                    // no number in the row
+        p.amax.out_tokens[m] = bi;
+        if (p.amax.generated) p.amax.generated[static_cast<size_t>(m) * p.amax.gen_stride + p.amax.step] = bi;
+      }
+    } else if (lane < W) {
+      const unsigned long long pk = (static_cast<unsigned long long>(__float_as_uint(best)) << 32) |
+                                    static_cast<uint32_t>(bi);
+      p.amax.cand[lane][(static_cast<size_t>(epoch & 1u) * W + p.amax.rank) * 8 + m] = pk;
+    }
+  }
+  if (W <= 1) return;
+  __syncthreads();          // every candidate store is ordered before the fence of the announcing lanes
+  if (threadIdx.x < 32) {
+    if (static_cast<int>(threadIdx.x) < W) {
+      __threadfence_system();
+      st_release_sys(p.amax.flags[threadIdx.x] + p.amax.rank, epoch);
+    }
+    const bool ok = wait_flags_warp(p.amax.flags[p.amax.rank], W, epoch, p.amax.wait_ns, p.status);
+    if (threadIdx.x == 0) *s_flag = ok ? 1 : 0;
+  }
+  __syncthreads();
+  if (*s_flag) {
+    for (int m = warp; m < p.M; m += nw) {
+      float best = -INFINITY;
+      int bi = NONE;
+      if (lane < W) {
+        const unsigned long long pk = __ldcg(p.amax.cand[p.amax.rank] + (static_cast<size_t>(epoch & 1u) * W + lane) * 8 + m);
+        best = __uint_as_float(static_cast<uint32_t>(pk >> 32));
+        bi = static_cast<int>(static_cast<uint32_t>(pk));
+      }
+      warp_argmax(best, bi);
+      if (lane == 0) {
+        if (bi == NONE) bi = 0;
+        p.amax.out_tokens[m] = bi;
+        if (p.amax.generated) p.amax.generated[static_cast<size_t>(m) * p.amax.gen_stride + p.amax.step] = bi;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *reinterpret_cast<volatile uint32_t*>(p.amax.epoch_word) = epoch;
+}
 
 // One finished partial sum (m, gc) of the fused all-reduce path: to slot [parity][rank] of every rank.
 __device__ __forceinline__ void gemv_coll_push(const GemvParams& p, uint32_t epoch, int m, int gc, float sum) {
@@ -601,6 +724,8 @@ gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   pdl_trigger();
   const bool direct = gridDim.y == 1;
   const bool coll = p.coll.W > 1;
+  const bool amax = p.amax.out_tokens != nullptr;
+  float* vals = reinterpret_cast<float*>(tiles);   // [M][COLS]: the ring is idle from here on
   // the epoch word is advanced only after every finishing CTA of this call has read it
   const uint32_t epoch = coll ? *reinterpret_cast<volatile uint32_t*>(p.coll.epoch_word) + 1u : 0u;
   if (warp < 8) {
@@ -620,6 +745,7 @@ gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
               if (p.R) sum += __bfloat162float(p.R[static_cast<size_t>(m) * p.ldr + gc]);
               if (p.out) p.out[static_cast<size_t>(m) * p.ldo + gc] = __float2bfloat16_rn(sum);
               if (p.out_f32) p.out_f32[static_cast<size_t>(m) * N + gc] = sum;
+              if (amax) vals[m * COLS + (gc - col0)] = sum;
             } else {
               p.part[(static_cast<size_t>(blockIdx.y) * M + m) * N + gc] = sum;
             }
@@ -630,6 +756,7 @@ gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   }
   if (direct) {
     if (coll) gemv_coll_finish(p, epoch, col0, min(COLS, N - col0), &s_last);
+    else if (amax) gemv_argmax_tail(p, vals, COLS, col0, min(COLS, N - col0), &s_last);
     return;
   }
   // split-K finish by the last CTA of this column block
@@ -661,8 +788,10 @@ gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     if (p.R) sum += __bfloat162float(p.R[static_cast<size_t>(m) * p.ldr + gc]);
     if (p.out) p.out[static_cast<size_t>(m) * p.ldo + gc] = __float2bfloat16_rn(sum);
     if (p.out_f32) p.out_f32[static_cast<size_t>(m) * N + gc] = sum;
+    if (amax) vals[m * COLS + (gc - col0)] = sum;
   }
   if (coll) gemv_coll_finish(p, epoch, col0, ncols, &s_last);
+  else if (amax) gemv_argmax_tail(p, vals, COLS, col0, ncols, &s_last);
 }
 
 // fp16 pair of two values that are first rounded to bf16 (the activation format) and saturated to the fp16 range
@@ -900,6 +1029,8 @@ gemv_mma_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   pdl_trigger();
   const bool direct = gridDim.y == 1;
   const bool coll = p.coll.W > 1;
+  const bool amax = p.amax.out_tokens != nullptr;
+  float* vals = reinterpret_cast<float*>(tiles);   // [M][COLS]: the ring is idle from here on
   // the epoch word is advanced only after every finishing CTA of this call has read it
   const uint32_t epoch = coll ? *reinterpret_cast<volatile uint32_t*>(p.coll.epoch_word) + 1u : 0u;
   if (warp < 8) {
@@ -918,6 +1049,7 @@ gemv_mma_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             if (p.R) sum += __bfloat162float(p.R[static_cast<size_t>(m) * p.ldr + gc]);
             if (p.out) p.out[static_cast<size_t>(m) * p.ldo + gc] = __float2bfloat16_rn(sum);
             if (p.out_f32) p.out_f32[static_cast<size_t>(m) * N + gc] = sum;
+            if (amax) vals[m * COLS + (gc - col0)] = sum;
           } else {
             p.part[(static_cast<size_t>(blockIdx.y) * M + m) * N + gc] = sum;
           }
@@ -927,6 +1059,7 @@ gemv_mma_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   }
   if (direct) {
     if (coll) gemv_coll_finish(p, epoch, col0, min(COLS, N - col0), &s_last);
+    else if (amax) gemv_argmax_tail(p, vals, COLS, col0, min(COLS, N - col0), &s_last);
     return;
   }
   // split-K finish by the last CTA of this column block
@@ -959,8 +1092,10 @@ gemv_mma_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     if (p.R) sum += __bfloat162float(p.R[static_cast<size_t>(m) * p.ldr + gc]);
     if (p.out) p.out[static_cast<size_t>(m) * p.ldo + gc] = __float2bfloat16_rn(sum);
     if (p.out_f32) p.out_f32[static_cast<size_t>(m) * N + gc] = sum;
+    if (amax) vals[m * COLS + (gc - col0)] = sum;
   }
   if (coll) gemv_coll_finish(p, epoch, col0, ncols, &s_last);
+  else if (amax) gemv_argmax_tail(p, vals, COLS, col0, ncols, &s_last);
 }
 
 // ---------------------------------------------------------------------------
@@ -1323,10 +1458,6 @@ decode_attn_kernel(const __grid_constant__ DecodeAttnParams p) {
 // Stage 2: one thread per row picks the best slab result and writes the token to `out_tokens[row]`
 // (int64, the device-side feedback buffer) and optionally appends it to `generated[row, step]`.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ bool argmax_better(float v, int i, float best, int bi) {
-  // both v and best are numbers here (NaN never enters); -inf with a real index beats the empty sentinel
-  return v > best || (v == best && i < bi);
-}
 __global__ void argmax_partial_kernel(const float* __restrict__ logits, int V, int cols_per_cta,
                                       float* __restrict__ pval, int* __restrict__ pidx) {
   __shared__ float sv[256];
@@ -1535,10 +1666,16 @@ struct GemvCollArgs {
   int rank, W, rows, wait_ms;
 };
 
+struct GemvAmaxArgs {
+  int32_t* ws;                 // word 0: CTA counter (zero between calls); 16...: pval [8][4096]; then pidx [8][4096]
+  int64_t* out_tokens; int64_t* generated; int gen_stride, step, col_offset;
+  void* const* cand_ptrs; void* const* flag_ptrs; uint32_t* epoch_word; int rank, W, wait_ms;
+};
+
 static int gemv_impl(const void* X, int ldx, const void* W, int ldw, const float* scale, const void* R, int ldr,
                      void* out_bf16, int ldo, float* out_f32, int M, int N, int K, int is_int8, int splits,
                      float* workspace, int prologue, const void* norm_w, float eps, int* status, void* stream,
-                     const GemvCollArgs* ca) {
+                     const GemvCollArgs* ca, const GemvAmaxArgs* aa = nullptr) {
   if (M <= 0 || M > 8 || N <= 0 || K <= 0 || (N & 7) || (is_int8 && (N & 15))) return SB_ERR_ARG;
   if (prologue < 0 || prologue > 2 || (prologue == 1 && (!norm_w || (K & 7) || (ldx & 7)))) return SB_ERR_ARG;
   const int esz = is_int8 ? 1 : 2;
@@ -1576,6 +1713,27 @@ static int gemv_impl(const void* X, int ldx, const void* W, int ldw, const float
     p.coll.epoch_word = ca->epoch_word; p.coll.done_ctr = ca->done_ctr;
     p.coll.wait_ns = ca->wait_ms > 0 ? static_cast<uint64_t>(ca->wait_ms) * 1000000ull : kPeerWaitNsDefault;
   }
+  p.amax.out_tokens = nullptr; p.amax.W = 0;
+  if (aa) {
+    if (!mma || ca || !aa->ws || !aa->out_tokens || aa->col_offset < 0) return SB_ERR_ARG;
+    p.amax.ctr = reinterpret_cast<unsigned int*>(aa->ws);
+    p.amax.pval = reinterpret_cast<float*>(aa->ws + 16);
+    p.amax.pidx = aa->ws + 16 + 8 * 4096;
+    p.amax.out_tokens = aa->out_tokens; p.amax.generated = aa->generated; p.amax.gen_stride = aa->gen_stride;
+    p.amax.step = aa->step; p.amax.col_offset = aa->col_offset; p.amax.W = aa->W > 1 ? aa->W : 0;
+    p.amax.rank = aa->rank; p.amax.epoch_word = aa->epoch_word;
+    p.amax.wait_ns = aa->wait_ms > 0 ? static_cast<uint64_t>(aa->wait_ms) * 1000000ull : kPeerWaitNsDefault;
+    if (aa->W > 1) {
+      if (aa->W > MAX_WORLD || aa->rank < 0 || aa->rank >= aa->W || !aa->cand_ptrs || !aa->flag_ptrs ||
+          !aa->epoch_word || !status)
+        return SB_ERR_ARG;
+      for (int r = 0; r < aa->W; ++r) {
+        if (!aa->cand_ptrs[r] || !aa->flag_ptrs[r]) return SB_ERR_ARG;
+        p.amax.cand[r] = static_cast<unsigned long long*>(aa->cand_ptrs[r]);
+        p.amax.flags[r] = static_cast<uint32_t*>(aa->flag_ptrs[r]);
+      }
+    }
+  }
   if (mma) return is_int8 ? launch_gemv_mma_i8(p, splits, STREAM) : launch_gemv_mma(p, splits, STREAM);
   return is_int8 ? launch_gemv<true>(p, splits, STREAM) : launch_gemv<false>(p, splits, STREAM);
 }
@@ -1601,6 +1759,23 @@ extern "C" int sb_gemv_allreduce(const void* X, int ldx, const void* W, int ldw,
   GemvCollArgs ca{recv_ptrs, flag_ptrs, epoch_word, done_ctr, rank, world, rows, wait_ms};
   return gemv_impl(X, ldx, W, ldw, scale, R, ldr, out_bf16, ldo, nullptr, M, N, K, is_int8, splits, workspace,
                    prologue, norm_w, eps, status, stream, &ca);
+}
+
+// LM head and greedy arg-max in one launch: out_tokens[m] = argmax over n of (f(X) W)[m, n] + col_offset (NaN in
+// global column 0 -> token 0; other NaNs skipped; ties -> lower column). logits_f32 [M, N] is optional. amax_ws:
+// 16 + 2 * 8 * 4096 32-bit words, the first one zero before the first call. world > 1: the head is sharded over the
+// vocabulary; cand_ptrs[r] / flag_ptrs[r] are rank r's peer-mapped candidate slots (2 * world * 8 64-bit words, zero at
+// creation) and epoch words (16), epoch_word a local device word (zero at creation); every rank issues the same calls.
+extern "C" int sb_gemv_argmax(const void* X, int ldx, const void* W, int ldw, const float* scale, float* logits_f32,
+                              int M, int N, int K, int is_int8, int splits, float* workspace, int prologue,
+                              const void* norm_w, float eps, int32_t* amax_ws, int64_t* out_tokens,
+                              int64_t* generated, int gen_stride, int step, int col_offset, void* const* cand_ptrs,
+                              void* const* flag_ptrs, uint32_t* epoch_word, int rank, int world, int wait_ms,
+                              int* status, void* stream) {
+  GemvAmaxArgs aa{amax_ws, out_tokens, generated, gen_stride, step, col_offset, cand_ptrs, flag_ptrs, epoch_word,
+                  rank, world, wait_ms};
+  return gemv_impl(X, ldx, W, ldw, scale, nullptr, 0, nullptr, 0, logits_f32, M, N, K, is_int8, splits, workspace,
+                   prologue, norm_w, eps, status, stream, nullptr, &aa);
 }
 
 extern "C" int sb_kv_append(const void* qkv, int ld, int H, int Hkv, int dh, void* pool, const int* block_table,

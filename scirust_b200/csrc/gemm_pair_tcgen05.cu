@@ -314,6 +314,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const uint4* mine = static_cast<const uint4*>(p.ag.a_peer[p.ag.rank]);
       const size_t srow0 = static_cast<size_t>(p.ag.rank) * p.ag.rows;       // my rows in the gathered matrix
       const int n_dst = p.ag.W - 1 + (p.ag.copy_own ? 1 : 0);
+      // A shard of a few MB is pushed to all destinations before the one fence (the fence waits for the stores to be
+      // acknowledged over NVLink, several microseconds each time, more than such a shard's GEMM gains by starting early);
+      // larger shards fence and announce destination by destination, so the consumer starts on the first while the
+      // others are still in flight.
+      const bool announce_each = vecs * 16 > (static_cast<size_t>(8) << 20);
       for (int q = 1; q <= n_dst; ++q) {
         const int dst = (p.ag.rank + p.ag.W - q) % p.ag.W;                    // q == W: myself
         uint4* land = static_cast<uint4*>(p.ag.stage_peer[dst]);
@@ -336,7 +341,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
         }
-        if (dst == p.ag.rank) continue;
+        if (dst == p.ag.rank || !announce_each) continue;
         __threadfence_system();        // this warp's stores have reached the destination
         __syncwarp();
         if (lane == 0) {
@@ -344,6 +349,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (prev + 1 == gridDim.x * COPY_WARPS) {
             __threadfence_system();
             p_st_release_sys(p.ag.chunk_flags_peer[dst] + p.ag.rank, p.ag.epoch);
+          }
+        }
+      }
+      if (!announce_each && p.ag.W > 1) {
+        __threadfence_system();        // this warp's stores have reached every destination
+        __syncwarp();
+        if (lane == 0) {
+          const unsigned int prev = atomicAdd(p.ag.chunk_ctr, 1u);
+          if (prev + 1 == gridDim.x * COPY_WARPS) {
+            __threadfence_system();
+            for (int q = 1; q < p.ag.W; ++q)
+              p_st_release_sys(p.ag.chunk_flags_peer[(p.ag.rank + p.ag.W - q) % p.ag.W] + p.ag.rank, p.ag.epoch);
           }
         }
       }

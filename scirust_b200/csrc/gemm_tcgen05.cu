@@ -15,7 +15,7 @@
 //     dY*W^T                 = A K-major,  B K-major
 //     X^T*dY   (weight grad) = A MN-major, B MN-major
 //
-// Kernel shape: persistent, one CTA per SM, 6 warps:
+// Kernel shape: persistent, one CTA per SM, 10 warps:
 //   warp 0   TMA producer (one elected lane)
 //   warp 1   MMA issuer (one elected lane); owns the TMEM allocation
 //   warp 2-9 epilogue: a warp may touch the 32 TMEM lanes of quarter (warp_id % 4); the two

@@ -14,6 +14,8 @@ logits row copied to the host.
 """
 from __future__ import annotations
 
+import os
+
 import ctypes as C
 import math
 
@@ -122,6 +124,9 @@ class InferenceEngine:
         self.logits = torch.zeros((max_batch, cfg.vocab_size), dtype=torch.float32, device=dev)
         self._graph = None
         self._graph_batch = None
+        self._generated = None
+        # greedy decoding of up to 8 rows: the LM-head GEMV does its own arg-max (SB_FUSED_ARGMAX=0: three launches)
+        self.fused_argmax = os.environ.get("SB_FUSED_ARGMAX", "1") != "0"
 
     def _prep(self, w):
         w = w.detach()
@@ -213,7 +218,7 @@ class InferenceEngine:
             logits.copy_(ops.matmul_nn(hn, self.head_t).float())
 
     # ------------------------------------------------------------------ decode
-    def _decode_body(self, B: int, max_len: int):
+    def _decode_body(self, B: int, max_len: int, greedy: bool = False):
         cfg, cache = self.cfg, self.cache
         H, Hkv, dh = self.H, self.Hkv, cfg.head_dim
         seq_of = self._seq_of[:B]
@@ -238,13 +243,27 @@ class InferenceEngine:
                 h, _ = ops.rmsnorm_fwd(x, l["rms2"], cfg.eps, want_inv=False)
                 gu = self._linear(h, l["wgu"])
             x = self._proj_out(gu, l["wd"], x, swiglu=True, site="mlp")
+        if greedy and self._fused_argmax_ok(B):
+            self._head_argmax(x, B)          # LM head and arg-max in one launch; the logits are not written
+            return True
         self._head(x, self.logits[:B], rms_weight=self.rms_final)
+        return False
 
-    def _step_eager(self, B, max_len, sampler=None):
+    def _fused_argmax_ok(self, B: int) -> bool:
+        return (self.dev.type == "cuda" and self.fused_argmax and B <= min(8, D.gemv_max_rows(self.head_t))
+                and os.environ.get("SB_GEMV_FMA") != "1")
+
+    def _head_argmax(self, x, B: int, logits=None):
+        D.gemv_argmax(x, self.head_t, out_tokens=self.tokens[:B], rms_weight=self.rms_final, eps=self.cfg.eps,
+                      logits=logits, generated=self._generated, step=0)
+
+    def _step_eager(self, B, max_len, sampler=None, want_logits=False):
         torch.add(self.cache.seq_len[:B], 1, out=self._len_plus1[:B])
         with D.dependent_launch(self.dev.type == "cuda"):
-            self._decode_body(B, max_len)
-        if sampler is None:
+            done = self._decode_body(B, max_len, greedy=sampler is None and not want_logits)
+        if done:
+            pass
+        elif sampler is None:
             D.argmax_rows(self.logits[:B], out_tokens=self.tokens[:B], generated=self._generated, step=0)
         else:
             sampler.sample(self.logits[:B], out_tokens=self.tokens[:B])
@@ -286,13 +305,14 @@ class InferenceEngine:
         out[:, 0] = self.tokens[:B]
         max_len = P + max_new
         if self.use_graph and max_new > 2:
-            # one eager step warms every workspace, then the step is captured once and replayed
-            self._step_eager(B, max_len, sampler)
-            out[:, 1] = self.tokens[:B]
+            # one eager step on the capture stream warms every workspace (they are kept per stream, and nothing may be
+            # allocated or cleared inside the capture), then the step is captured once and replayed
             g = torch.cuda.CUDAGraph()
             s = torch.cuda.Stream(device=self.dev)
             s.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(s):
+                self._step_eager(B, max_len, sampler)
+                out[:, 1] = self.tokens[:B]
                 with torch.cuda.graph(g, stream=s):
                     self._step_eager(B, max_len, sampler)
             torch.cuda.current_stream().wait_stream(s)
@@ -328,7 +348,7 @@ def teacher_forced_logits(engine: "InferenceEngine", prompts: torch.Tensor, toke
     tok = tokens.to(engine.dev)
     for i in range(n):
         engine.tokens[:B] = tok[:, i]
-        engine._step_eager(B, P + n + 1)
+        engine._step_eager(B, P + n + 1, want_logits=True)
         out.append(engine.logits[:B].float().clone())
     return torch.stack(out, 1)
 

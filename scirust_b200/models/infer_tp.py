@@ -76,6 +76,10 @@ class TPInferenceEngine(InferenceEngine):
         if self.backend == "fused" and os.environ.get("SB_TP_FUSED_GEMV", "1") != "0":
             from ..parallel.small_collectives import GemvAllReduceChannel
             self.gemv_chan = GemvAllReduceChannel(self.region, rows=8, n_max=cfg.d_model)
+        self.amax_chan = None
+        if self.backend == "fused" and self.region is not None and W > 1:
+            from ..parallel.small_collectives import ArgmaxChannel
+            self.amax_chan = ArgmaxChannel(self.region)
         super().__init__(model, quant=quant, max_batch=max_batch, max_seq=max_seq, page=page,
                          use_graph=use_graph and self.backend == "fused")
         self.vocab_local = cfg.vocab_size // W
@@ -151,6 +155,14 @@ class TPInferenceEngine(InferenceEngine):
         local = self.logits_local[:M]
         self._head_local(hn, local, rms_weight)
         self.coll.gather_rows(local, logits)
+
+    def _fused_argmax_ok(self, B: int) -> bool:
+        return self.amax_chan is not None and super()._fused_argmax_ok(B)
+
+    def _head_argmax(self, x, B: int, logits=None):
+        D.gemv_argmax(x, self.head_t, out_tokens=self.tokens[:B], rms_weight=self.rms_final, eps=self.cfg.eps,
+                      logits=logits, chan=self.amax_chan, col_offset=self.rank * self.vocab_local,
+                      generated=self._generated, step=0)
 
     def close(self):
         """Collective: unmaps the peers' symmetric memory."""

@@ -130,7 +130,7 @@ class _BlockFn(torch.autograd.Function):
     """One decoder block, forward and hand-scheduled backward."""
 
     @staticmethod
-    def forward(ctx, x, rms1, wqkv, wo, rms2, wgu, wd, blk):
+    def _run(x, rms1, wqkv, wo, rms2, wgu, wd, blk):
         cfg, B, S = blk.cfg, blk.B, blk.S
         H, Hkv, dh = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
         h1, inv1 = ops.rmsnorm_fwd(x, rms1, cfg.eps)
@@ -140,17 +140,32 @@ class _BlockFn(torch.autograd.Function):
         x2 = ops.matmul_nn(a, wo, residual=x)
         h2, inv2 = ops.rmsnorm_fwd(x2, rms2, cfg.eps)
         gu, hm = ops.matmul_nn_swiglu(h2, wgu)      # SwiGLU in the GEMM epilogue on CUDA
-        x3 = ops.matmul_nn(hm, wd, residual=x2)
-        ctx.save_for_backward(x, inv1, h1, qkv, a, lse, x2, inv2, h2, gu, hm)
+        return (x, inv1, h1, qkv, a, lse, x2, inv2, h2, gu, hm)
+
+    @staticmethod
+    def forward(ctx, x, rms1, wqkv, wo, rms2, wgu, wd, blk):
+        saved = _BlockFn._run(x, rms1, wqkv, wo, rms2, wgu, wd, blk)
+        x3 = ops.matmul_nn(saved[10], wd, residual=saved[6])
+        if blk.recompute:
+            # activation recompute: keep only the block input; backward re-runs the forward kernels (fixed
+            # reduction orders, so the recomputed activations are the bits of the first pass)
+            ctx.save_for_backward(x)
+        else:
+            ctx.save_for_backward(*saved)
         ctx.blk = blk
         ctx.params = (rms1, wqkv, wo, rms2, wgu, wd)
         return x3
 
     @staticmethod
     def backward(ctx, dx3):
-        x, inv1, h1, qkv, a, lse, x2, inv2, h2, gu, hm = ctx.saved_tensors
         rms1, wqkv, wo, rms2, wgu, wd = ctx.params
         blk = ctx.blk
+        if blk.recompute:
+            with torch.no_grad():
+                saved = _BlockFn._run(ctx.saved_tensors[0], rms1, wqkv, wo, rms2, wgu, wd, blk)
+        else:
+            saved = ctx.saved_tensors
+        x, inv1, h1, qkv, a, lse, x2, inv2, h2, gu, hm = saved
         cfg, B, S = blk.cfg, blk.B, blk.S
         H, Hkv, dh = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
         dx3 = dx3.contiguous()
@@ -170,6 +185,8 @@ class _BlockFn(torch.autograd.Function):
         # attention
         da = ops.matmul_nt(dx2, wo)
         g_wo = _wgrad(wo, a, dx2)
+        if blk.on_attention_bwd is not None:
+            blk.on_attention_bwd(blk.index)
         dqkv = att.attention_bwd(qkv, a, lse, da, B, S, H, Hkv, dh, causal=True)
         ops.rope_(dqkv, H + Hkv, dh, S, blk.cos, blk.sin, backward=True)
         dh1 = ops.matmul_nt(dqkv, wqkv)
@@ -262,10 +279,12 @@ class _HeadLossFn(torch.autograd.Function):
 class _BlockState:
     """Per-call constants shared by the blocks of one forward pass."""
 
-    def __init__(self, cfg, B, S, cos, sin, index, on_grads_ready):
+    def __init__(self, cfg, B, S, cos, sin, index, on_grads_ready, on_attention_bwd=None, recompute=False):
         self.cfg, self.B, self.S, self.cos, self.sin = cfg, B, S, cos, sin
         self.index = index
         self.on_grads_ready = on_grads_ready
+        self.on_attention_bwd = on_attention_bwd
+        self.recompute = recompute
 
 
 class DecoderLayer(nn.Module):
@@ -301,6 +320,12 @@ class GQADecoder(nn.Module):
         self.rms_final = nn.Parameter(torch.empty(cfg.d_model, dtype=BF))
         self.lm_head = None if cfg.tie_embeddings else nn.Parameter(torch.empty(cfg.vocab_size, cfg.d_model, dtype=BF))
         self.on_grads_ready = None  # callback(layer_index) used by data-parallel overlap
+        # callback(layer_index) just before a layer's attention backward is launched: the stretch of backward whose
+        # kernels are many short CTAs, not persistent GEMMs, so a collective started here takes SMs without stalling
+        self.on_attention_bwd = None
+        # long contexts: keep one activation (the block input) per layer and re-run the block's forward kernels in
+        # backward, 1/15 of the saved bytes for about a third more compute
+        self.activation_recompute = False
         self.to(device)
         self._flatten()
         self.reset_parameters(seed, init_std)
@@ -386,7 +411,8 @@ class GQADecoder(nn.Module):
         cos, sin = ops.rope_table(max(cfg.max_seq_len, S), cfg.head_dim, cfg.rope_theta, self.flat.device)
         x = _EmbedFn.apply(self.embed, tokens.reshape(-1))
         for i, l in enumerate(self.layers):
-            blk = _BlockState(cfg, B, S, cos, sin, i, self.on_grads_ready)
+            blk = _BlockState(cfg, B, S, cos, sin, i, self.on_grads_ready, self.on_attention_bwd,
+                              self.activation_recompute and torch.is_grad_enabled())
             x = _BlockFn.apply(x, l.rms_attn, l.wqkv, l.wo, l.rms_ffn, l.wgu, l.wd, blk)
         return x
 

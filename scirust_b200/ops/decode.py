@@ -28,7 +28,7 @@ _ws: dict = {}
 
 
 def _workspace(n, device):
-    key = str(device)
+    key = (str(device), _lib.stream())        # per stream: concurrent calls on two streams must not share scratch
     w = _ws.get(key)
     if w is None or w.numel() < n:
         w = torch.empty(max(n, 1 << 22), dtype=torch.float32, device=device)
@@ -65,8 +65,9 @@ _gemv_ws: dict = {}
 
 
 def _gemv_workspace(n, device):
-    """Workspace of the GEMV: 4096 counter words (kept zero by the kernel) + split partials."""
-    key = str(device)
+    """Workspace of the GEMV: 4096 counter words (kept zero by the kernel) + split partials; one per (device,
+    stream), so that GEMVs issued on two streams share neither counters nor partial sums."""
+    key = (str(device), _lib.stream())
     w = _gemv_ws.get(key)
     if w is None or w.numel() < n:
         w = torch.zeros(max(n, 1 << 22), dtype=torch.float32, device=device)
@@ -216,6 +217,54 @@ def gemv_allreduce(x, w, chan, residual=None, out=None, splits=None, swiglu=Fals
               st.data_ptr(), _lib.stream())
     _g.launch_count += 1
     return out
+
+
+_lib.register("sb_gemv_argmax", [vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, vp, i32, vp, f32, vp, vp, vp, i32,
+                                 i32, i32, vp, vp, vp, i32, i32, i32, vp, vp])
+_amax_ws: dict = {}
+
+
+def gemv_argmax(x, w, out_tokens=None, rms_weight=None, eps=1e-5, logits=None, chan=None, col_offset=0,
+                generated=None, step=0, splits=None):
+    """Greedy token of every row of ``f(x)[M,K] @ W`` (M <= 8) in ONE launch: the LM-head GEMV reduces its own
+    outputs to one (value, column) per row and the last CTA writes the int64 token to ``out_tokens`` (the
+    device-side feedback buffer), so the logits never make a round trip through memory unless ``logits`` (fp32
+    [M, N]) is given (csrc/decode.cu: ``sb_gemv_argmax``; rule of scirust-cuda/src/bf16_lm_head_argmax.rs:46-176).
+    ``chan`` (an ``ArgmaxChannel``) and ``col_offset`` make it the vocabulary-parallel head: every rank reduces its
+    shard and the ranks exchange W candidates inside the same launch."""
+    quant = isinstance(w, QuantWeight)
+    wm = w.q if quant else w
+    K, N = wm.shape
+    M = x.shape[0]
+    if M > 8:
+        raise ValueError("gemv_argmax: at most 8 rows")
+    if not x.is_cuda:
+        lg = logits if logits is not None else torch.empty((M, N), dtype=torch.float32)
+        gemv(x, w, out_f32=lg, rms_weight=rms_weight, eps=eps)
+        if chan is not None:
+            raise ValueError("gemv_argmax: the vocabulary-parallel form needs CUDA tensors")
+        return argmax_rows(lg, out_tokens=out_tokens, generated=generated, step=step)
+    if out_tokens is None:
+        out_tokens = torch.empty(M, dtype=torch.int64, device=x.device)
+    if splits is None:
+        splits = _auto_splits(N, K, 512 if quant else 256, M, quant)
+    splits = max(splits, (K + 4095) // 4096)
+    ws = _gemv_workspace(4096 + splits * M * N, x.device)
+    key = (str(x.device), _lib.stream())
+    aws = _amax_ws.get(key)
+    if aws is None:
+        aws = _amax_ws[key] = torch.zeros(16 + 2 * 8 * 4096, dtype=torch.int32, device=x.device)
+    st = _lib.status_word(x.device)
+    _lib.call("sb_gemv_argmax", x.data_ptr(), x.stride(0), wm.data_ptr(), wm.stride(0),
+              w.scale.data_ptr() if quant else None, _lib.ptr(logits), M, N, K, int(quant), splits, ws.data_ptr(),
+              1 if rms_weight is not None else 0, _lib.ptr(rms_weight), float(eps), aws.data_ptr(),
+              out_tokens.data_ptr(), _lib.ptr(generated), generated.stride(0) if generated is not None else 0, step,
+              col_offset, chan.cand_ptrs if chan is not None else None, chan.flag_ptrs if chan is not None else None,
+              chan.state.data_ptr() if chan is not None else None, chan.rank if chan is not None else 0,
+              chan.world if chan is not None else 1, chan.wait_ms if chan is not None else 0, st.data_ptr(),
+              _lib.stream())
+    _g.launch_count += 1
+    return out_tokens
 
 
 def matmul_w8(x, w: QuantWeight, residual=None, out=None, splits=None):

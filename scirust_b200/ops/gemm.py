@@ -20,7 +20,7 @@ import torch
 from . import _lib
 
 _sm_count: dict[int, int] = {}
-_workspaces: dict[int, torch.Tensor] = {}
+_workspaces: dict = {}
 
 
 def num_sms(device=None) -> int:
@@ -37,7 +37,10 @@ launch_count = 0
 
 
 def _workspace(nfloats: int, device) -> torch.Tensor:
-    key = device.index if device.index is not None else torch.cuda.current_device()
+    """Split-K / balanced-schedule scratch, one buffer per (device, stream): two products issued on two streams
+    (backward on one, a collective's GEMM on another) must not share partial sums. The buffer is allocated while
+    its stream is current, so the caching allocator orders its reuse on that stream."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _lib.stream())
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nfloats:
         ws = torch.empty(max(nfloats, 1 << 22), dtype=torch.float32, device=device)

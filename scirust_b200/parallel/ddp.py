@@ -192,7 +192,9 @@ class FlatDataParallel:
         if self.world > 1:
             for b in range(len(self.buckets)):
                 if b not in self._launched:
-                    self._reduce_bucket(b, async_=False)
+                    # late buckets take the communication stream too: kernels whose CTAs wait for other GPUs run in
+                    # one order on one stream per GPU (two of them side by side can close a cycle of waits)
+                    self._reduce_bucket(b, async_=self.overlap and self.comm_stream is not None)
             if self.overlap and self.comm == "fused":
                 ev = torch.cuda.Event()
                 ev.record(self.comm_stream)

@@ -1,0 +1,179 @@
+"""Pipeline parallelism for the GQA decoder: contiguous groups of layers on consecutive ranks, micro-batches in a
+one-forward-one-backward (1F1B) schedule, activations and their gradients exchanged with point-to-point
+``torch.distributed`` transfers (NCCL between GPUs, gloo between CPU ranks).
+
+Stage ``s`` of ``P`` owns layers ``[lo, hi)``; stage 0 also owns the embedding, stage ``P - 1`` the final norm, the
+LM head and the loss. Every stage keeps its parameters, gradients and optimizer state in the same flat buffers as
+the single-device model (``models/sciagent.py``), so ``train.Trainer`` drives a ``PipelineModel`` unchanged: one call
+of the model runs the whole schedule (forward and backward of every micro-batch), ``loss.backward()`` is then a
+no-op, and the gradient norm is the sum over the stages.
+
+Semantics kept from the reference's data-parallel trainer (scirust-core/src/distributed.rs:96-167): the loss is the
+mean over the micro-batches, gradients accumulate in micro-batch order, so a run equals the single-process run that
+accumulates the same micro-batches, bit for bit while gradient clipping is inactive (asserted on CPU ranks; the
+squared gradient norm is added stage by stage, so an active clip factor may differ in its last bit). With tied embeddings the first and last
+stage both hold the table; their gradients are summed between the two before the optimizer, and counted once in
+the gradient norm.
+
+Sends are asynchronous and receives blocking, which is what makes the schedule free of send/send deadlocks on both
+backends; on CUDA every transfer is issued on the stage's current stream (NCCL orders them with the kernels).
+"""
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..models.sciagent import BF, GQADecoder, SciAgentConfig, _BlockFn, _BlockState, _EmbedFn, _HeadLossFn
+
+
+def split_layers(n_layers: int, stages: int) -> list[tuple[int, int]]:
+    """Contiguous ``[lo, hi)`` per stage; the first ``n_layers % stages`` stages take one layer more."""
+    if stages < 1 or n_layers < stages:
+        raise ValueError("need at least one layer per pipeline stage")
+    base, extra = divmod(n_layers, stages)
+    out, lo = [], 0
+    for s in range(stages):
+        hi = lo + base + (1 if s < extra else 0)
+        out.append((lo, hi))
+        lo = hi
+    return out
+
+
+class PipelineModel:
+    """One pipeline stage behind the interface ``train.Trainer`` expects from a model."""
+
+    def __init__(self, cfg: SciAgentConfig, group=None, device=None, micro_batches: int = 4, seed: int = 0):
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.cfg_full = cfg
+        self.lo, self.hi = split_layers(cfg.n_layers, self.world)[self.rank]
+        self.first, self.last = self.rank == 0, self.rank == self.world - 1
+        self.micro_batches = micro_batches
+        local = dataclasses.replace(cfg, n_layers=self.hi - self.lo)
+        self.stage = GQADecoder(local, device=device, seed=seed + 1000 * self.rank)
+        self.device = self.stage.flat.device
+        self.flat, self.flat_grad, self.decay_end = self.stage.flat, self.stage.flat_grad, self.stage.decay_end
+        self.tied = cfg.tie_embeddings and self.world > 1
+        # created by every rank (a collective), used by the two end stages only
+        self.tie_group = dist.new_group([self._global(0), self._global(self.world - 1)]) if self.tied else None
+        self._sends = []
+        self.last_losses = None
+
+    def _global(self, r):
+        return dist.get_global_rank(self.group, r) if self.group is not dist.group.WORLD else r
+
+    # ------------------------------------------------------------------ weights
+    def load_from_full(self, full: GQADecoder) -> None:
+        """Copy this stage's parameters out of a complete model (tests, conversion of a single-device checkpoint)."""
+        with torch.no_grad():
+            for i in range(self.lo, self.hi):
+                src, dst = full.layers[i], self.stage.layers[i - self.lo]
+                for name in ("rms_attn", "wqkv", "wo", "rms_ffn", "wgu", "wd"):
+                    getattr(dst, name).copy_(getattr(src, name))
+            self.stage.embed.copy_(full.embed)
+            self.stage.rms_final.copy_(full.rms_final)
+            if full.lm_head is not None:
+                self.stage.lm_head.copy_(full.lm_head)
+
+    def zero_grad_flags(self):
+        self.stage.zero_grad_flags()
+
+    def parameters(self):
+        return self.stage.parameters()
+
+    # ------------------------------------------------------------------ transfers
+    def _send(self, t, dst):
+        self._sends.append((dist.isend(t.contiguous(), self._global(dst), group=self.group), t))
+
+    def _recv(self, shape, src, dtype=BF):
+        t = torch.empty(shape, dtype=dtype, device=self.device)
+        dist.recv(t, self._global(src), group=self.group)
+        return t
+
+    def _drain(self):
+        for w, _ in self._sends:
+            w.wait()
+        self._sends = []
+
+    # ------------------------------------------------------------------ one micro-batch
+    def _forward(self, inp, tgt, scale):
+        st, cfg = self.stage, self.stage.cfg
+        B, S = inp.shape
+        cos, sin = ops.rope_table(max(cfg.max_seq_len, S), cfg.head_dim, cfg.rope_theta, self.device)
+        if self.first:
+            x_in = None
+            x = _EmbedFn.apply(st.embed, inp.reshape(-1))
+        else:
+            x_in = self._recv((B * S, cfg.d_model), self.rank - 1).requires_grad_()
+            x = x_in
+        for i, l in enumerate(st.layers):
+            blk = _BlockState(cfg, B, S, cos, sin, i, None, None, st.activation_recompute)
+            x = _BlockFn.apply(x, l.rms_attn, l.wqkv, l.wo, l.rms_ffn, l.wgu, l.wd, blk)
+        if self.last:
+            loss = _HeadLossFn.apply(x, st.rms_final, st.head_weight(), tgt, cfg.eps, st.head_chunk)
+            return x_in, loss * scale, loss.detach()
+        self._send(x.detach(), self.rank + 1)
+        return x_in, x, None
+
+    def _backward(self, x_in, out):
+        if self.last:
+            out.backward()
+        else:
+            out.backward(self._recv(tuple(out.shape), self.rank + 1))
+        if not self.first:
+            self._send(x_in.grad, self.rank - 1)
+
+    # ------------------------------------------------------------------ the schedule
+    def __call__(self, inp, tgt):
+        M = self.micro_batches
+        B = inp.shape[0]
+        if B % M:
+            raise ValueError("batch size must be a multiple of the number of micro-batches")
+        mb = B // M
+        warm = min(self.world - self.rank - 1, M)
+        live, losses = [], []
+        nf = nb = 0
+
+        def fwd():
+            nonlocal nf
+            sl = slice(nf * mb, (nf + 1) * mb)
+            x_in, out, lv = self._forward(inp[sl], tgt[sl] if self.last else None, 1.0 / M)
+            live.append((x_in, out))
+            if lv is not None:
+                losses.append(lv)
+            nf += 1
+
+        def bwd():
+            nonlocal nb
+            self._backward(*live.pop(0))
+            nb += 1
+        for _ in range(warm):
+            fwd()
+        for _ in range(M - warm):
+            fwd()
+            bwd()
+        for _ in range(warm):
+            bwd()
+        self._drain()
+        if self.tied and (self.first or self.last):
+            g = self.stage.embed.main_grad if hasattr(self.stage.embed, "main_grad") else self.stage.embed.grad
+            dist.all_reduce(g, group=self.tie_group)
+        # the mean loss is known on the last stage; every stage reports it
+        total = torch.zeros(1, dtype=torch.float32, device=self.device)
+        if self.last:
+            total += torch.stack(losses).float().sum() / M
+        dist.broadcast(total, self._global(self.world - 1), group=self.group)
+        self.last_losses = losses
+        return total[0].detach().requires_grad_()      # Trainer calls .backward() on it: nothing is left to do
+
+    # ------------------------------------------------------------------ hooks used by Trainer
+    def global_grad_sumsq(self, out: torch.Tensor, scale: float = 1.0) -> None:
+        ops.sumsq(self.flat_grad, out=out)
+        if self.tied and self.last:
+            # the tied table's gradient is also held (and counted) by stage 0
+            g = self.stage.embed.main_grad
+            out -= g.float().pow(2).sum()
+        dist.all_reduce(out, group=self.group)     # the optimizer applies `scale` to the gradient and its norm

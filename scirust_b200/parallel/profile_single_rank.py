@@ -4,14 +4,14 @@ profiler can capture it on a single GPU (a profiler must not wrap a multi-rank c
 rank every "peer" pointer is the local buffer: the instruction stream, tile loop, flag protocol and
 epilogues are the ones the multi-rank runs execute, only the NVLink hops are local.
 
-    python examples/fused_kernels_single_rank.py --iters 3
-    SB_TP_PAIR_SINGLE=1 python examples/fused_kernels_single_rank.py --iters 3    # the CTA-pair kernels
+    python -m scirust_b200.parallel.profile_single_rank --iters 3
+    SB_TP_PAIR_SINGLE=1 python -m scirust_b200.parallel.profile_single_rank --iters 3    # the CTA-pair kernels
 """
 import argparse
 import os
 import sys
 
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 
 import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402

@@ -136,3 +136,23 @@ class GemvAllReduceChannel:
 
     def recv_ptrs(self, n: int):
         return self._recv_ptrs
+
+
+class ArgmaxChannel:
+    """Peer-mapped state of the vocabulary-parallel fused LM head (``ops.decode.gemv_argmax``): per rank
+    ``2 x world x 8`` candidate words (value bits and global column of a rank's best entry per row; a call uses the
+    half of its parity), ``world`` epoch words, and a local epoch word that the kernel advances, so a captured CUDA
+    graph replays the calls correctly. Every rank must issue the same sequence of calls."""
+
+    def __init__(self, region, wait_ms: int = 0):
+        self.region, self.wait_ms = region, wait_ms
+        self.rank, self.world = region.rank, region.world
+        self.cand = region.tensor((2 * self.world * 8,), torch.int64)
+        self.cand.zero_()
+        self.flags = region.tensor((16,), torch.int32)
+        self.flags.zero_()
+        self.cand_ptrs = region.peer_ptrs(self.cand)
+        self.flag_ptrs = region.peer_ptrs(self.flags)
+        self.state = torch.zeros(16, dtype=torch.int32, device=region.device)   # [0] epoch word
+        torch.cuda.synchronize(region.device)
+        dist.barrier(group=region.group)

@@ -32,6 +32,7 @@ class TrainerConfig:
     telemetry_interval: int = 0   # 0 = never read the loss back unless asked
     optimizer: str = "adamw"
     status_interval: int = 1      # multi-GPU runs: look at the kernels' status word every N steps (0 = never)
+    activation_recompute: bool = False   # keep one activation per layer, re-run each block's forward in backward
 
 
 class Trainer:
@@ -52,6 +53,10 @@ class Trainer:
         self.grad_sumsq = torch.zeros(1, dtype=torch.float32, device=flat.device)
         self.step = 0
         self.grad_reducer = grad_reducer
+        if c.activation_recompute:
+            if not hasattr(model, "activation_recompute"):
+                raise ValueError("this model has no activation-recompute path")
+            model.activation_recompute = True
         self.last_loss = None
         self._dev_tokens = None
         # Kernels that wait on other ranks record a time-out in a device status word and skip their work. With

@@ -24,7 +24,7 @@ results = []
 for it in range(3):
     g = torch.Generator(device=dev).manual_seed(100 * it + rank)
     src.copy_(torch.randn(n, generator=g, device=dev).to(torch.bfloat16))
-    ar.reduce(0, n, 1.0 / world, ar.next_epoch())
+    ar.reduce(0, n, 1.0 / world, ar.next_epoch(), lean=(it == 1))      # the small CTA shape gives the same bits
     torch.cuda.synchronize()
     _lib.check_status(dev)
     # oracle: gather every rank's input, add in rank order in fp32, scale, round once

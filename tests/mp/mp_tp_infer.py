@@ -70,6 +70,14 @@ def main():
         pair_steps = teacher_forced_logits(tp2, prompts, ref_tokens).cpu()
         assert torch.equal(pair_steps, tp_steps), "fused GEMV + all-reduce differs from the two-kernel path"
         tp2.close()
+    if use_cuda and getattr(tp, "amax_chan", None) is not None and B <= 8:
+        # the vocabulary-parallel head that exchanges (value, column) candidates inside the GEMV launch must emit the
+        # tokens of the path that gathers the logit shards and runs the stand-alone arg-max
+        assert tp._fused_argmax_ok(B)
+        tp.fused_argmax = False
+        unfused = tp.generate(prompts, NEW).cpu()
+        tp.fused_argmax = True
+        assert torch.equal(unfused, tokens), "fused LM head + arg-max differs from gather + arg-max"
     match = (tokens == ref_tokens).float().mean().item()       # reported, not asserted
     if use_cuda:
         from scirust_b200.ops import _lib

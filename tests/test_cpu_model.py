@@ -223,3 +223,22 @@ def test_corpus_filter_dedup_split_and_muon_train_optimizer(tmp_path):
             last = loss.item()
         assert last < 0.2 * first, (make.__name__, first, last)
         assert abs(opt.lr - sched.lr_at(119)) < 1e-9
+
+
+def test_activation_recompute_gives_identical_gradients_and_losses():
+    """Backward that re-runs each block's forward from the saved block input produces the bits of the backward that
+    kept every activation (same kernels, same reduction orders), step after step."""
+    from scirust_b200.models.sciagent import GQADecoder, SciAgentConfig
+    from scirust_b200.train.trainer import Trainer, TrainerConfig
+    cfg = SciAgentConfig(vocab_size=96, d_model=32, n_layers=3, n_heads=4, n_kv_heads=2, d_ff=64, max_seq_len=32)
+    g = torch.Generator().manual_seed(0)
+    toks = torch.randint(0, cfg.vocab_size, (4, 3, 17), generator=g)
+    losses, flats = [], []
+    for rec in (False, True):
+        m = GQADecoder(cfg, device=torch.device("cpu"), seed=5)
+        tr = Trainer(m, TrainerConfig(lr=1e-2, activation_recompute=rec))
+        assert m.activation_recompute == rec
+        losses.append([float(tr.train_step(t)) for t in toks])
+        flats.append(m.flat.clone())
+    assert losses[0] == losses[1]
+    assert torch.equal(flats[0], flats[1])

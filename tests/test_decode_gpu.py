@@ -90,6 +90,38 @@ def test_argmax_tie_and_nan_rules():
     assert D.argmax_rows(lg.cpu()).tolist() == tok
 
 
+@pytest.mark.parametrize("quant", [False, True])
+@pytest.mark.parametrize("M,K,N,splits", [(1, 1024, 50272, 1), (5, 2048, 4112, 4), (8, 512, 1024, None)])
+def test_lm_head_fused_with_argmax_equals_gemv_then_argmax(quant, M, K, N, splits):
+    """One launch (GEMV + in-kernel arg-max) gives the tokens and the logits of the three-launch path, including the
+    NaN rules: weights with NaN columns make NaN logits in column 0 (row wins token 0), column 7 (skipped)."""
+    g = torch.Generator(device="cuda").manual_seed(M * 31 + K)
+    x = (torch.randn(M, K, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(K, N, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    gain = (1 + 0.1 * torch.randn(K, generator=g, device="cuda")).to(torch.bfloat16)
+    w[:, N - 3] = w[:, 40]                          # a tie between two columns when x.w is the row maximum
+    cases = [w]
+    if not quant:
+        wn = w.clone(); wn[0, 7] = float("nan"); cases.append(wn)           # NaN logits in column 7: skipped
+        w0 = w.clone(); w0[0, 0] = float("nan"); cases.append(w0)           # NaN logits in column 0: token 0
+    for wc in cases:
+        wt = D.quantize_per_channel(wc) if quant else wc
+        lg = torch.empty(M, N, dtype=torch.float32, device="cuda")
+        D.gemv(x, wt, out_f32=lg, rms_weight=gain, splits=splits)
+        want = D.argmax_rows(lg)
+        lg2 = torch.zeros_like(lg)
+        got = D.gemv_argmax(x, wt, rms_weight=gain, logits=lg2, splits=splits)
+        nolog = D.gemv_argmax(x, wt, rms_weight=gain, splits=splits)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want) and torch.equal(nolog, want)
+        nan = torch.isnan(lg)
+        assert torch.equal(torch.isnan(lg2), nan) and torch.equal(lg2[~nan], lg[~nan])
+    if not quant:
+        assert got.tolist() == [0] * M
+    from scirust_b200.ops import _lib
+    _lib.check_status(torch.device("cuda"))
+
+
 @pytest.mark.parametrize("quant", [None, "int8"])
 def test_engine_cached_equals_naive_and_graph(quant):
     cfg = SciAgentConfig(vocab_size=1024, d_model=256, n_layers=2, n_heads=4, n_kv_heads=2, d_ff=512,
