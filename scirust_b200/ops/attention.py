@@ -84,11 +84,41 @@ def attention_bwd_ref(qkv, do, B, S, H, Hkv, dh, causal=True, scale=None):
     return g
 
 
+def attention_bwd_flash_ref(qkv, o, lse, do, B, S, H, Hkv, dh, causal=True, scale=None):
+    """fp32 statement of the flash backward, written on the SAVED normaliser and output like the kernels:
+    P = exp(S - lse), delta = rowsum(dO * O), dS = P * (dP - delta). With the block's own (o, lse) it equals
+    ``attention_bwd_ref``; with the merged (o, lse) of a ring of KV blocks it is that block's share of the gradient,
+    which is what context parallelism needs."""
+    scale = 1.0 / math.sqrt(dh) if scale is None else scale
+    rep = H // Hkv
+    x = qkv.float().reshape(B, S, H + 2 * Hkv, dh)
+    q = x[:, :, :H].permute(0, 2, 1, 3)
+    k = x[:, :, H:H + Hkv].permute(0, 2, 1, 3).repeat_interleave(rep, 1)
+    v = x[:, :, H + Hkv:].permute(0, 2, 1, 3).repeat_interleave(rep, 1)
+    dof = do.float().reshape(B, S, H, dh).permute(0, 2, 1, 3)
+    of = o.float().reshape(B, S, H, dh).permute(0, 2, 1, 3)
+    s = torch.matmul(q, k.transpose(-1, -2)) * scale
+    p = torch.exp(s - lse.float()[..., None])
+    if causal:
+        p = p.masked_fill(torch.triu(torch.ones(S, S, dtype=torch.bool, device=qkv.device), 1), 0.0)
+    p = torch.nan_to_num(p, nan=0.0)                       # rows with lse = -inf (no visible key) contribute nothing
+    dv = torch.matmul(p.transpose(-1, -2), dof)
+    dp = torch.matmul(dof, v.transpose(-1, -2))
+    delta = (dof * of).sum(-1, keepdim=True)
+    ds = p * (dp - delta)
+    dq = torch.matmul(ds, k) * scale
+    dk = torch.matmul(ds.transpose(-1, -2), q) * scale
+    dk = dk.reshape(B, Hkv, rep, S, dh).sum(2)
+    dv = dv.reshape(B, Hkv, rep, S, dh).sum(2)
+    g = torch.cat([dq.permute(0, 2, 1, 3), dk.permute(0, 2, 1, 3), dv.permute(0, 2, 1, 3)], 2)
+    return g.reshape(B * S, (H + 2 * Hkv) * dh)
+
+
 def attention_bwd(qkv, o, lse, do, B, S, H, Hkv, dh, causal=True, scale=None):
     """Gradient w.r.t. the fused qkv matrix (same layout), deterministic (no atomics)."""
     scale = 1.0 / math.sqrt(dh) if scale is None else scale
     if not qkv.is_cuda:
-        return attention_bwd_ref(qkv, do, B, S, H, Hkv, dh, causal, scale).to(qkv.dtype)
+        return attention_bwd_flash_ref(qkv, o, lse, do, B, S, H, Hkv, dh, causal, scale).to(qkv.dtype)
     dqkv = torch.empty_like(qkv)
     delta = torch.empty((B, H, S, 2), dtype=torch.float32, device=qkv.device)
     ds = _scratch(B, S, H, qkv.device)

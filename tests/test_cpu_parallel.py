@@ -206,6 +206,16 @@ def test_pipeline_parallel_1f1b_equals_single_process_accumulation_on_gloo_ranks
     assert r.returncode == 0 and "PIPELINE_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
 
+@pytest.mark.parametrize("world", [2, 3])
+def test_ring_attention_equals_dense_attention_on_gloo_ranks(world):
+    """Context parallelism: K/V shards travel around the ring, blocks are merged by log-sum-exp; forward output and
+    the qkv gradient of every rank's slice equal dense attention over the whole sequence (causal and full)."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29690 + world), os.path.join(ROOT, "tests", "mp", "mp_ring_attention.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, PYTHONPATH=ROOT))
+    assert r.returncode == 0 and "RING_ATTENTION_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
 def test_native_tcp_tree_allreduce_is_bitwise_the_python_engine_and_interoperates():
     """The C++ transport (csrc/rt_collectives.cpp) speaks the same frames and sums in the same order:
     all-native worlds, and worlds mixing native and Python ranks, give the in-process engine's bits."""

@@ -108,3 +108,22 @@ def test_tp_inference_batch16_and_replicated_kv_heads():
     out = _run("mp_tp_infer.py", 2, 29617, extra_env={"SB_TEST_DEVICE": "cuda", "SB_TP_BATCH": "16", "SB_TP_KV": "1"},
                tag="_b16")
     assert "TP_INFER_OK" in out
+
+
+@pytest.mark.parametrize("stages,tied", [(2, 0), (4, 1)])
+def test_pipeline_parallel_training_over_nccl(stages, tied):
+    """1F1B pipeline over NCCL point-to-point transfers: the stages end on the weights of the single-GPU run that
+    accumulates the same micro-batches (tests/mp/mp_pipeline.py)."""
+    _need(stages)
+    out = _run("mp_pipeline.py", stages, 29680 + stages, tag=f"_p{stages}",
+               extra_env={"SB_PP_CUDA": "1", "SB_PP_TIED": str(tied), "SB_PP_MICRO": "4"})
+    assert "PIPELINE_OK" in out
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_ring_attention_over_nccl(world):
+    """Context parallelism on the flash kernels: every hop is one attention_fwd / attention_bwd launch on the
+    visiting K/V shard, merged by log-sum-exp; equals dense attention over the whole sequence."""
+    _need(world)
+    out = _run("mp_ring_attention.py", world, 29690 + world, tag=f"_w{world}", extra_env={"SB_CP_CUDA": "1"})
+    assert "RING_ATTENTION_OK" in out
