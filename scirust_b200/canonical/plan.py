@@ -109,10 +109,19 @@ def plan_memory(ep: ExecutionPlan) -> MemoryPlan:
     top = 0
     offsets: dict = {}
     release_at: dict = {}
+    # inputs and constants are written before the first kernel runs, whatever their position in the graph: they get
+    # their storage up front (and give it back after their last use like every other value)
+    feeds = [v for v in ep.order if g.nodes[v].op in ("Input", "Constant")]
+    for v in feeds:
+        offsets[v] = top
+        top += size[v]
+        release_at.setdefault(last[v], []).append(v)
     for i, v in enumerate(ep.order):
         r = _root(g, v)
         if r != v:
             offsets[v] = offsets[r]
+        elif v in offsets:
+            pass                     # a feed, placed above
         else:
             need = size[v]
             for k, (off, nb) in enumerate(free):

@@ -27,6 +27,7 @@ from .plan import LoweredPlan, lower
 class ReferencePlanRuntime:
     def __init__(self, device="cpu"):
         self.device = torch.device(device)
+        self._fused = None          # compiled fused element-wise kernels of this device
 
     def _view(self, arena, plan: LoweredPlan, vid: int):
         shape = plan.exec_plan.graph.nodes[vid].shape
@@ -51,6 +52,13 @@ class ReferencePlanRuntime:
         for k in plan.kernels:
             if k.kind == "alias":
                 continue
+            if k.kind == "fused_elementwise" and self.device.type == "cuda":
+                from .fusion import FusedKernelCache
+                if self._fused is None:
+                    self._fused = FusedKernelCache(self.device)
+                self._fused.launch(k.attrs["program"], arena, plan.memory.offsets[k.out],
+                                   [plan.memory.offsets[i] for i in k.inputs], _numel(k.attrs["shape"]))
+                continue
             ins = [self._view(arena, plan, i) for i in k.inputs]
             out = self._view(arena, plan, k.out)
             out.copy_(self._kernel(k, ins))
@@ -59,6 +67,9 @@ class ReferencePlanRuntime:
     def _kernel(self, k, ins):
         dev = self.device.type == "cuda"
         op = k.op
+        if k.kind == "fused_elementwise":
+            from .fusion import run_program_cpu
+            return run_program_cpu(k.attrs["program"], ins)
         if k.kind == "elementwise":
             if op in ("Add", "Sub", "Mul", "Div"):
                 return K.run(op.lower(), ins[0].contiguous(), ins[1].contiguous())
@@ -117,16 +128,22 @@ def _reduce_sum_to(x, shape):
 
 
 class ReferenceJitSession:
-    def __init__(self, device="cpu"):
+    def __init__(self, device="cpu", fuse: bool = False):
         self.runtime = ReferencePlanRuntime(device)
         self.cache: dict = {}
         self.compilations = 0
+        self.fuse = fuse            # run the element-wise fusion pass (canonical/fusion.py) when lowering
 
     def run(self, g: Graph, feeds: dict) -> list:
         key = g.signature()
         plan = self.cache.get(key)
         if plan is None:
-            plan = self.cache[key] = lower(g)
+            if self.fuse:
+                from .fusion import lower_fused
+                plan = lower_fused(g)
+            else:
+                plan = lower(g)
+            self.cache[key] = plan
             self.compilations += 1
         return self.runtime.run(plan, feeds)
 
@@ -201,7 +218,7 @@ def conformance_cases():
     return cases
 
 
-def run_conformance(device="cpu") -> dict:
+def run_conformance(device="cpu", fuse: bool = False) -> dict:
     """name -> list of output tensors (on the host) for every conformance case on ``device``."""
-    sess = ReferenceJitSession(device)
+    sess = ReferenceJitSession(device, fuse=fuse)
     return {name: [o.cpu() for o in sess.run(g, feeds)] for name, g, feeds in conformance_cases()}

@@ -94,3 +94,32 @@ def test_canonical_facade_conformance_device_equals_cpu_bit_for_bit():
     with pytest.raises(K.Unsupported):
         ReferenceJitSession("cuda").run(g, {"x": torch.zeros(4)})
     assert torch.allclose(ReferenceJitSession("cpu").run(g, {"x": torch.zeros(4)})[0], torch.ones(4))
+
+
+def test_fused_elementwise_groups_run_as_one_generated_kernel_with_the_unfused_bits():
+    """The fusion pass on the device adapter: each element-wise tree is ONE NVRTC-compiled kernel launched on views of
+    the plan's arena; outputs equal the CPU adapter (fused or not) word for word, NaN positions included."""
+    from scirust_b200.canonical import Graph, ReferenceJitSession, run_conformance
+    g = Graph()
+    a, b = g.input("x", (300, 77)), g.input("y", (300, 77))
+    t = g.div(g.mul(g.add(a, b), g.sub(a, b)), g.scale(b, 0.3))
+    r = g.relu(t)
+    w = g.input("w", (77, 9))
+    tail = g.scale(g.relu(g.matmul(r, w)), 2.0)
+    g.set_outputs(tail, g.relu_grad(a, b), r)
+    gen = torch.Generator().manual_seed(0)
+    feeds = {"x": torch.randn(300, 77, generator=gen), "y": torch.randn(300, 77, generator=gen),
+             "w": torch.randn(77, 9, generator=gen)}
+    feeds["x"][0, 0], feeds["x"][0, 1], feeds["y"][0, 2] = float("nan"), -0.0, float("inf")
+    cpu = ReferenceJitSession("cpu").run(g, feeds)
+    sess = ReferenceJitSession("cuda", fuse=True)
+    dev = [o.cpu() for o in sess.run(g, feeds)]
+    assert sess.runtime._fused is not None and sess.runtime._fused.compiled == 2
+    for p, q in zip(cpu, dev):
+        nan = torch.isnan(p)
+        assert torch.equal(torch.isnan(q), nan) and torch.equal(p.view(torch.int32)[~nan], q.view(torch.int32)[~nan])
+    c0, c1 = run_conformance("cpu"), run_conformance("cuda", fuse=True)
+    for name in c0:
+        for p, q in zip(c0[name], c1[name]):
+            nan = torch.isnan(p)
+            assert torch.equal(torch.isnan(q), nan) and torch.equal(p.view(torch.int32)[~nan], q.view(torch.int32)[~nan])

@@ -148,3 +148,53 @@ def test_conformance_cases_run_on_cpu_and_are_repeatable():
     for k in a:
         for x, y in zip(a[k], b[k]):
             assert torch.equal(x.view(torch.int32), y.view(torch.int32))
+
+
+def test_fusion_pass_groups_elementwise_trees_keeps_bits_and_shrinks_the_arena():
+    from scirust_b200.canonical import (Graph, ReferenceJitSession, cuda_source, find_groups, lower, lower_fused,
+                                        plan_execution, run_conformance)
+    g = Graph()
+    a, b = g.input("x", (64, 33)), g.input("y", (64, 33))
+    t = g.div(g.mul(g.add(a, b), g.sub(a, b)), g.scale(b, 0.3))
+    r = g.relu(t)
+    w = g.input("w", (33, 5))
+    mm = g.matmul(r, w)                      # r feeds a matmul: the tree above ends at r
+    tail = g.scale(g.relu(mm), 2.0)
+    g.set_outputs(tail, g.relu_grad(a, b))
+    groups = find_groups(plan_execution(g))
+    sizes = sorted(len(m) for m in groups.values())
+    assert sizes == [2, 6]                   # {relu(mm), scale} and {add, sub, mul, scale, div, relu}
+    plain, fused = lower(g), lower_fused(g)
+    n_plain = sum(k.kind != "alias" for k in plain.kernels)
+    n_fused = sum(k.kind != "alias" for k in fused.kernels)
+    assert n_fused == n_plain - 6 and fused.memory.arena_bytes < plain.memory.arena_bytes
+    gen = torch.Generator().manual_seed(0)
+    feeds = {"x": torch.randn(64, 33, generator=gen), "y": torch.randn(64, 33, generator=gen),
+             "w": torch.randn(33, 5, generator=gen)}
+    feeds["x"][0, 0], feeds["x"][0, 1], feeds["y"][0, 2] = float("nan"), -0.0, float("inf")
+    o1 = ReferenceJitSession("cpu").run(g, feeds)
+    o2 = ReferenceJitSession("cpu", fuse=True).run(g, feeds)
+    # "w" is declared after values that are dead by the time it is used: a feed must still own its storage from the
+    # start, since every input is written before the first kernel runs
+    xs, ys = torch.nan_to_num(feeds["x"][1:]), feeds["y"][1:]
+    want = torch.relu(torch.relu((xs + ys) * (xs - ys) / (ys * 0.3)) @ feeds["w"]) * 2.0
+    assert torch.allclose(o1[0][1:], want, rtol=1e-4, atol=1e-4)
+    for p, q in zip(o1, o2):
+        nan = torch.isnan(p)
+        assert torch.equal(torch.isnan(q), nan) and torch.equal(p.view(torch.int32)[~nan], q.view(torch.int32)[~nan])
+    # a value with two consumers, or a graph output, is never swallowed
+    g2 = Graph()
+    x = g2.input("x", (8,))
+    s = g2.scale(x, 2.0)
+    g2.set_outputs(g2.add(s, x), g2.relu(s))
+    assert find_groups(plan_execution(g2)) == {}
+    # the conformance suite gives the same words with the pass switched on
+    c0, c1 = run_conformance("cpu"), run_conformance("cpu", fuse=True)
+    for name in c0:
+        for p, q in zip(c0[name], c1[name]):
+            nan = torch.isnan(p)
+            assert torch.equal(p.view(torch.int32)[~nan], q.view(torch.int32)[~nan]), name
+    # generated device source: individually rounded intrinsics, never a bare * or +
+    k = [k for k in fused.kernels if k.kind == "fused_elementwise" and len(k.attrs["program"]) == 6][0]
+    src = cuda_source(k.attrs["program"], len(k.inputs))
+    assert "__fdiv_rn" in src and "__fmul_rn" in src and "__fadd_rn" in src and " * " not in src.split("{", 1)[1].replace("blockIdx.x * (long long)blockDim.x", "")
