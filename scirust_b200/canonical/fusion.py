@@ -191,9 +191,8 @@ class FusedKernelCache:
             k = self.kernels[key] = self.rt.compile(cuda_source(steps, len(in_offs)), "fused_elementwise")
             self.compiled += 1
         buf = RawBuffer(arena.numel() * 4, arena.view(torch.uint8))
+        # bindings: the output span (write) and one read span per program input; the validator refuses the launch if
+        # the memory plan ever let the output overlap an input
         binds = [RawBinding(buf, RawAccess.WRITE, out_off, n * 4)]
-        binds += [RawBinding(buf, RawAccess.READ, off, n * 4) for off in dict.fromkeys(in_offs)]
-        # one pointer per DISTINCT span is validated; the kernel still takes one pointer per program input
-        self.rt.launch(k, RawLaunchConfig(((n + 255) // 256, 1, 1), (256, 1, 1)),
-                       [binds[0]] + [RawBinding(buf, RawAccess.READ, off, n * 4) for off in in_offs],
-                       scalars=[C.c_longlong(n)])
+        binds += [RawBinding(buf, RawAccess.READ, off, n * 4) for off in in_offs]
+        self.rt.launch(k, RawLaunchConfig(((n + 255) // 256, 1, 1), (256, 1, 1)), binds, scalars=[C.c_longlong(n)])

@@ -9,6 +9,7 @@ to another implementation silently.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 import torch
@@ -103,6 +104,63 @@ def ptr(t) -> int | None:
     return t.data_ptr()
 
 
+# --------------------------------------------------------------------------------------------------
+# Debug build of the op layer (SB_DEBUG_POISON=1): every buffer an op allocates for a kernel to fill is
+#   * poisoned: all payload bytes 0xFF (bf16 / fp32 NaN, integer -1), so anything a kernel was supposed to write and
+#     did not shows up in the first comparison instead of reading as a plausible stale value;
+#   * fenced: 256 canary bytes (0xA5) on both sides, checked at every `check_status()` and by `check_canaries()`,
+#     so a kernel that writes a tile past the end of its output is caught at the next synchronisation point.
+# The stand-in for a memory-checking tool on hosts where none may be run; off by default (one branch per allocation).
+# --------------------------------------------------------------------------------------------------
+DEBUG_POISON = os.environ.get("SB_DEBUG_POISON") == "1"
+_GUARD = 256
+_fenced: list = []          # (weak reference to the backing byte buffer, payload bytes, tag)
+
+
+def empty(shape, dtype, device, tag: str = "") -> torch.Tensor:
+    """``torch.empty`` for op outputs and workspaces; poisoned and fenced in the debug build."""
+    if not DEBUG_POISON or torch.device(device).type != "cuda":
+        return torch.empty(shape, dtype=dtype, device=device)
+    return fenced_empty(shape, dtype, device, tag)
+
+
+def fenced_empty(shape, dtype, device, tag: str = "") -> torch.Tensor:
+    import weakref
+    n = 1
+    for d in (shape if isinstance(shape, (tuple, list, torch.Size)) else (shape,)):
+        n *= int(d)
+    nbytes = n * torch.empty((), dtype=dtype).element_size()
+    pad = (-nbytes) % 16
+    raw = torch.empty(nbytes + pad + 2 * _GUARD, dtype=torch.uint8, device=device)
+    raw[:_GUARD].fill_(0xA5)
+    raw[_GUARD + nbytes:].fill_(0xA5)
+    raw[_GUARD:_GUARD + nbytes].fill_(0xFF)
+    out = raw[_GUARD:_GUARD + nbytes].view(dtype).view(shape)
+    out._sb_fence = raw          # the fences are watched for as long as the tensor handed out is alive
+    _fenced.append((weakref.ref(raw), nbytes, tag or f"{tuple(out.shape)} {dtype}"))
+    if len(_fenced) > 4096:
+        _fenced[:] = [e for e in _fenced if e[0]() is not None]
+    return out
+
+
+def check_canaries() -> None:
+    """Debug build: raise if any live fenced buffer has a damaged canary (synchronises)."""
+    if not _fenced:
+        return
+    live = []
+    for ref, nbytes, tag in _fenced:
+        raw = ref()
+        if raw is None:
+            continue
+        live.append((ref, nbytes, tag))
+        lo_ok = bool((raw[:_GUARD] == 0xA5).all())
+        hi_ok = bool((raw[_GUARD + nbytes:] == 0xA5).all())
+        if not (lo_ok and hi_ok):
+            side = "before" if not lo_ok else "past the end of"
+            raise NativeError(f"a kernel wrote {side} a buffer it was given: {tag}")
+    _fenced[:] = live
+
+
 def stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -138,6 +196,8 @@ def check_status(device=None) -> None:
     if code != 0:
         w.zero_()
         raise CollectiveTimeout(code)
+    if DEBUG_POISON:
+        check_canaries()
 
 
 class DeferredStatus:

@@ -39,7 +39,7 @@ def _scratch(B, S, H, device):
     key = str(device)
     t = _ds_scratch.get(key)
     if t is None or t.numel() < n:
-        t = torch.empty(n, dtype=torch.bfloat16, device=device)
+        t = _lib.empty(n, torch.bfloat16, device)
         _ds_scratch[key] = t
     return t
 
@@ -67,8 +67,8 @@ def attention_fwd(qkv, B, S, H, Hkv, dh, causal=True, scale=None, want_lse=True)
         return o.to(qkv.dtype), lse
     if qkv.dim() != 2 or qkv.stride(1) != 1 or qkv.dtype != torch.bfloat16:
         raise ValueError("qkv must be a 2-D bf16 matrix with unit inner stride")
-    out = torch.empty((B * S, H * dh), dtype=torch.bfloat16, device=qkv.device)
-    lse = torch.empty((B, H, S), dtype=torch.float32, device=qkv.device) if want_lse else None
+    out = _lib.empty((B * S, H * dh), torch.bfloat16, qkv.device)
+    lse = _lib.empty((B, H, S), torch.float32, qkv.device) if want_lse else None
     entry = "sb_attention_fwd_pp" if (FWD_TWO_TILES and dh == 64) else "sb_attention_fwd"
     _lib.call(entry, qkv.data_ptr(), out.data_ptr(), _lib.ptr(lse), B, S, H, Hkv, dh, qkv.stride(0),
               out.stride(0), float(scale), int(causal), _lib.status_word(qkv.device).data_ptr(), _lib.stream())
@@ -120,7 +120,7 @@ def attention_bwd(qkv, o, lse, do, B, S, H, Hkv, dh, causal=True, scale=None):
     if not qkv.is_cuda:
         return attention_bwd_flash_ref(qkv, o, lse, do, B, S, H, Hkv, dh, causal, scale).to(qkv.dtype)
     dqkv = torch.empty_like(qkv)
-    delta = torch.empty((B, H, S, 2), dtype=torch.float32, device=qkv.device)
+    delta = _lib.empty((B, H, S, 2), torch.float32, qkv.device)
     ds = _scratch(B, S, H, qkv.device)
     _lib.call("sb_attention_bwd", qkv.data_ptr(), o.data_ptr(), lse.data_ptr(), do.data_ptr(), dqkv.data_ptr(),
               delta.data_ptr(), _lib.ptr(ds), B, S, H, Hkv, dh, qkv.stride(0), o.stride(0), do.stride(0), float(scale),

@@ -33,8 +33,8 @@ def rmsnorm_fwd(x, w, eps=1e-5, out=None, want_inv=True):
         y = (xf * inv[:, None] * w.float()).to(x.dtype)
         return y, (inv if want_inv else None)
     if out is None:
-        out = torch.empty((rows, cols), dtype=BF, device=x.device)
-    inv = torch.empty(rows, dtype=torch.float32, device=x.device) if want_inv else None
+        out = _lib.empty((rows, cols), BF, x.device)
+    inv = _lib.empty(rows, torch.float32, x.device) if want_inv else None
     _lib.call("sb_rmsnorm_fwd", x.data_ptr(), w.data_ptr(), out.data_ptr(), _lib.ptr(inv), rows, cols,
               x.stride(0), out.stride(0), float(eps), _lib.stream())
     _count()
@@ -61,9 +61,9 @@ def rmsnorm_bwd(dy, x, w, inv, dres=None, dw_out=None, want_dw=True):
     part = dwf = dwb = None
     if want_dw:
         chunks = (rows + 255) // 256
-        part = torch.empty(chunks * cols, dtype=torch.float32, device=x.device)
+        part = _lib.empty(chunks * cols, torch.float32, x.device)
         if dw_out is None:
-            dw_out = torch.empty(cols, dtype=torch.float32, device=x.device)
+            dw_out = _lib.empty(cols, torch.float32, x.device)
         if dw_out.dtype == torch.float32:
             dwf = dw_out
         else:
@@ -121,7 +121,7 @@ def swiglu_fwd(gu, out=None):
         g, u = gu[:, :ff].float(), gu[:, ff:].float()
         return (g * torch.sigmoid(g) * u).to(gu.dtype)
     if out is None:
-        out = torch.empty((rows, ff), dtype=BF, device=gu.device)
+        out = _lib.empty((rows, ff), BF, gu.device)
     _lib.call("sb_swiglu_fwd", gu.data_ptr(), out.data_ptr(), rows, ff, _lib.stream())
     _count()
     return out
@@ -157,7 +157,7 @@ def embed_fwd(table, tokens):
     vocab, d = table.shape
     if not table.is_cuda:
         return table[tokens.reshape(-1).clamp(0, vocab - 1)]
-    out = torch.empty((n, d), dtype=table.dtype, device=table.device)
+    out = _lib.empty((n, d), table.dtype, table.device)
     _lib.call("sb_embed_fwd", table.data_ptr(), tokens.data_ptr(), out.data_ptr(), n, d, vocab, _lib.stream())
     _count()
     return out
@@ -207,7 +207,7 @@ def ce_fwd_bwd(logits, targets, grad_scale, dlogits=None, in_place=True):
             logits.copy_(d)
             d = logits
         return loss, d
-    loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    loss = _lib.empty(rows, torch.float32, logits.device)
     if dlogits is None:
         dlogits = logits if in_place else torch.empty_like(logits)
     _lib.call("sb_ce_fwd_bwd", logits.data_ptr(), targets.data_ptr(), loss.data_ptr(), dlogits.data_ptr(), rows,
@@ -227,7 +227,7 @@ def ce_shard_stats(logits, targets, v0):
         own = (loc >= 0) & (loc < cols) & (targets.reshape(-1) >= 0)
         t = torch.where(own, lf.gather(1, loc.clamp(0, cols - 1)[:, None])[:, 0], torch.zeros_like(m))
         return torch.stack([m, s, t], 1)
-    stats = torch.empty((rows, 3), dtype=torch.float32, device=logits.device)
+    stats = _lib.empty((rows, 3), torch.float32, logits.device)
     _lib.call("sb_ce_shard_stats", logits.data_ptr(), targets.data_ptr(), stats.data_ptr(), rows, cols,
               logits.stride(0), int(v0), _lib.stream())
     _count()
@@ -261,7 +261,7 @@ def ce_loss_only(logits, targets):
     rows, cols = logits.shape
     if not logits.is_cuda:
         return ce_fwd_bwd(logits.clone(), targets, 0.0)[0]
-    loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    loss = _lib.empty(rows, torch.float32, logits.device)
     _lib.call("sb_ce_fwd_bwd", logits.data_ptr(), targets.data_ptr(), loss.data_ptr(), None, rows, cols,
               logits.stride(0), 0.0, _lib.stream())
     _count()
@@ -280,7 +280,7 @@ def sumsq(g, out=None, accumulate=False):
         return s
     if out is None:
         out = torch.zeros(1, dtype=torch.float32, device=g.device)
-    part = torch.empty((n + 4095) // 4096, dtype=torch.float32, device=g.device)
+    part = _lib.empty((n + 4095) // 4096, torch.float32, g.device)
     _lib.call("sb_sumsq", g.data_ptr(), n, int(g.dtype == BF), part.data_ptr(), out.data_ptr(), int(accumulate),
               _lib.stream())
     _count(2)

@@ -67,13 +67,13 @@ def run(op: str, a: torch.Tensor, b: torch.Tensor | None = None, *, factor: floa
         return _cpu(op, a, b, factor, perm, shape)
     a = a.contiguous()
     if op == "permute":
-        out = torch.empty([a.shape[p] for p in perm], dtype=torch.float32, device=a.device)
+        out = _lib.empty([a.shape[p] for p in perm], torch.float32, a.device)
         shp = (C.c_longlong * a.dim())(*a.shape)
         prm = (C.c_int * a.dim())(*perm)
         _lib.call("sb_canon_permute", a.data_ptr(), out.data_ptr(), a.dim(), C.addressof(shp), C.addressof(prm),
                   _lib.stream())
     else:
-        out = torch.empty(shape if (op == "copy" and shape is not None) else a.shape, dtype=torch.float32, device=a.device)
+        out = _lib.empty(shape if (op == "copy" and shape is not None) else a.shape, torch.float32, a.device)
         if out.numel() != a.numel():
             raise ValueError("copy keeps the number of elements")
         bb = b.contiguous() if b is not None else None

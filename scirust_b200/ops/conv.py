@@ -72,7 +72,7 @@ class _Conv(torch.autograd.Function):
         B, H, W, C = geom.B, geom.H, geom.W, geom.C
         OH, OW = (H + 2 * pad - k) // stride + 1, (W + 2 * pad - k) // stride + 1
         Kp = wp.shape[1]
-        col = torch.empty((B * OH * OW, Kp), dtype=BF, device=x.device)
+        col = _lib.empty((B * OH * OW, Kp), BF, x.device)
         _lib.call("sb_im2col_nhwc", x.data_ptr(), col.data_ptr(), B, H, W, C, k, k, stride, pad, OH, OW, Kp,
                   _lib.stream())
         G.launch_count += 1
@@ -91,7 +91,7 @@ class _Conv(torch.autograd.Function):
             dw = G.matmul_tn(dy, col)                         # [oc, Kp] = dy^T col
         if ctx.needs_input_grad[0]:
             dcol = G.matmul_nn(dy, wp)                        # [M, Kp]
-            dx = torch.empty((geom.rows, geom.C), dtype=BF, device=dy.device)
+            dx = _lib.empty((geom.rows, geom.C), BF, dy.device)
             _lib.call("sb_col2im_nhwc", dcol.data_ptr(), dx.data_ptr(), geom.B, geom.H, geom.W, geom.C, k, k, stride,
                       pad, OH, OW, wp.shape[1], _lib.stream())
             G.launch_count += 1
@@ -114,8 +114,8 @@ class _MaxPool(torch.autograd.Function):
     def forward(ctx, x, geom, k, stride):
         B, H, W, C = geom.B, geom.H, geom.W, geom.C
         OH, OW = (H - k) // stride + 1, (W - k) // stride + 1
-        y = torch.empty((B * OH * OW, C), dtype=BF, device=x.device)
-        arg = torch.empty((B * OH * OW, C), dtype=torch.uint8, device=x.device)
+        y = _lib.empty((B * OH * OW, C), BF, x.device)
+        arg = _lib.empty((B * OH * OW, C), torch.uint8, x.device)
         _lib.call("sb_maxpool_fwd", x.data_ptr(), y.data_ptr(), arg.data_ptr(), B, H, W, C, k, stride, OH, OW,
                   _lib.stream())
         G.launch_count += 1
@@ -127,7 +127,7 @@ class _MaxPool(torch.autograd.Function):
     def backward(ctx, dy):
         (arg,) = ctx.saved_tensors
         geom, k, stride, OH, OW = ctx.meta
-        dx = torch.empty((geom.rows, geom.C), dtype=BF, device=dy.device)
+        dx = _lib.empty((geom.rows, geom.C), BF, dy.device)
         _lib.call("sb_maxpool_bwd", dy.contiguous().data_ptr(), arg.data_ptr(), dx.data_ptr(), geom.B, geom.H, geom.W,
                   geom.C, k, stride, OH, OW, _lib.stream())
         G.launch_count += 1
@@ -145,8 +145,8 @@ def maxpool2d(x, geom: ConvGeom, k: int, stride: int):
 def _colstats(a, b):
     rows, C = a.shape
     part = torch.empty(2 * ((rows + 255) // 256) * C, dtype=torch.float32, device=a.device)
-    s1 = torch.empty(C, dtype=torch.float32, device=a.device)
-    s2 = torch.empty(C, dtype=torch.float32, device=a.device)
+    s1 = _lib.empty(C, torch.float32, a.device)
+    s2 = _lib.empty(C, torch.float32, a.device)
     _lib.call("sb_colstats", a.data_ptr(), b.data_ptr(), part.data_ptr(), s1.data_ptr(), s2.data_ptr(), rows, C,
               _lib.stream())
     G.launch_count += 2
@@ -157,8 +157,8 @@ class _BatchNorm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, gamma, beta, run_mean, run_var, eps, momentum, relu, training):
         rows, C = x.shape
-        mean = torch.empty(C, dtype=torch.float32, device=x.device)
-        inv = torch.empty(C, dtype=torch.float32, device=x.device)
+        mean = _lib.empty(C, torch.float32, x.device)
+        inv = _lib.empty(C, torch.float32, x.device)
         if training:
             s1, s2 = _colstats(x, x)
         else:
@@ -185,8 +185,8 @@ class _BatchNorm(torch.autograd.Function):
             g = torch.empty_like(dy)
             _lib.call("sb_relu_mask", dy.data_ptr(), y.data_ptr(), g.data_ptr(), dy.numel(), _lib.stream())
         sg, sgx = _colstats(g, x)
-        dgamma = torch.empty(C, dtype=torch.float32, device=x.device)
-        dbeta = torch.empty(C, dtype=torch.float32, device=x.device)
+        dgamma = _lib.empty(C, torch.float32, x.device)
+        dbeta = _lib.empty(C, torch.float32, x.device)
         dx = torch.empty_like(x)
         _lib.call("sb_bn_bwd", g.data_ptr(), x.data_ptr(), sg.data_ptr(), sgx.data_ptr(), mean.data_ptr(),
                   inv.data_ptr(), gamma.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), dx.data_ptr(), rows, C,

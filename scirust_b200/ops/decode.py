@@ -31,7 +31,7 @@ def _workspace(n, device):
     key = (str(device), _lib.stream())        # per stream: concurrent calls on two streams must not share scratch
     w = _ws.get(key)
     if w is None or w.numel() < n:
-        w = torch.empty(max(n, 1 << 22), dtype=torch.float32, device=device)
+        w = _lib.empty(max(n, 1 << 22), torch.float32, device)
         _ws[key] = w
     return w
 
@@ -90,7 +90,7 @@ class QuantWeight:
         if not self.q.is_cuda:
             return (self.q.float() * self.scale[None, :]).to(BF)
         K, N = self.q.shape
-        w = torch.empty((K, N), dtype=BF, device=self.q.device)
+        w = _lib.empty((K, N), BF, self.q.device)
         _lib.call("sb_dequantize", self.q.data_ptr(), self.scale.data_ptr(), K, N, w.data_ptr(), _lib.stream())
         _g.launch_count += 1
         return w
@@ -106,8 +106,8 @@ def quantize_per_channel(w: torch.Tensor) -> QuantWeight:
         q = torch.where(v >= 0, torch.floor(v + 0.5), torch.ceil(v - 0.5)).clamp(-128, 127).to(torch.int8)
         return QuantWeight(q, scale)
     w = w.contiguous()
-    scale = torch.empty(N, dtype=torch.float32, device=w.device)
-    q = torch.empty((K, N), dtype=torch.int8, device=w.device)
+    scale = _lib.empty(N, torch.float32, w.device)
+    q = _lib.empty((K, N), torch.int8, w.device)
     _lib.call("sb_quantize_per_channel", w.data_ptr(), K, N, w.stride(0), scale.data_ptr(), q.data_ptr(),
               _lib.stream())
     _g.launch_count += 2
@@ -165,7 +165,7 @@ def gemv(x, w, residual=None, out=None, out_f32=None, splits=None, rms_weight=No
             return out
         return y.to(BF) if out_f32 is None else out_f32
     if out is None and out_f32 is None:
-        out = torch.empty((M, N), dtype=BF, device=x.device)
+        out = _lib.empty((M, N), BF, x.device)
     grp = 8                                   # rows per call
     if splits is None:
         splits = _auto_splits(N, K, 512 if quant else 256, min(M, grp), quant)
@@ -203,7 +203,7 @@ def gemv_allreduce(x, w, chan, residual=None, out=None, splits=None, swiglu=Fals
     if M > chan.rows or N > chan.n_max:
         raise ValueError("gemv_allreduce: product larger than the channel was sized for")
     if out is None:
-        out = torch.empty((M, N), dtype=BF, device=x.device)
+        out = _lib.empty((M, N), BF, x.device)
     if splits is None:
         splits = _auto_splits(N, K, 512 if quant else 256, M, quant)
     splits = max(splits, (K + 4095) // 4096)
@@ -245,7 +245,7 @@ def gemv_argmax(x, w, out_tokens=None, rms_weight=None, eps=1e-5, logits=None, c
             raise ValueError("gemv_argmax: the vocabulary-parallel form needs CUDA tensors")
         return argmax_rows(lg, out_tokens=out_tokens, generated=generated, step=step)
     if out_tokens is None:
-        out_tokens = torch.empty(M, dtype=torch.int64, device=x.device)
+        out_tokens = _lib.empty(M, torch.int64, x.device)
     if splits is None:
         splits = _auto_splits(N, K, 512 if quant else 256, M, quant)
     splits = max(splits, (K + 4095) // 4096)
@@ -279,7 +279,7 @@ def matmul_w8(x, w: QuantWeight, residual=None, out=None, splits=None):
             y = y + residual.float()
         return y.to(BF)
     if out is None:
-        out = torch.empty((M, N), dtype=BF, device=x.device)
+        out = _lib.empty((M, N), BF, x.device)
     if splits is None:
         tiles = ((M + 127) // 128) * ((N + 255) // 256)
         nkb = (K + 63) // 64
@@ -354,7 +354,7 @@ def decode_attention(q, pool, block_table, page, seq_len, H, Hkv, dh, scale=None
         raise ValueError("decode_attention: batch * kv_heads above 2048 is not supported")
     part_o = ws[:B * H * n_splits * dh]
     part_ml = ws[B * H * n_splits * dh:B * H * n_splits * (dh + 2)]
-    out = torch.empty((B, H * dh), dtype=BF, device=q.device)
+    out = _lib.empty((B, H * dh), BF, q.device)
     _lib.call("sb_decode_attention", q.data_ptr(), q.stride(0), pool.data_ptr(), block_table.data_ptr(),
               block_table.shape[1], page, seq_len.data_ptr(), B, H, Hkv, dh, n_splits, float(scale),
               part_o.data_ptr(), part_ml.data_ptr(), ctr[2048:].data_ptr(), out.data_ptr(), out.stride(0),
@@ -376,10 +376,10 @@ def argmax_rows(logits_f32, out_tokens=None, generated=None, step=0):
             generated[:, step] = tok
         return tok
     slabs = (V + 4095) // 4096
-    pval = torch.empty(rows * slabs, dtype=torch.float32, device=logits_f32.device)
-    pidx = torch.empty(rows * slabs, dtype=torch.int32, device=logits_f32.device)
+    pval = _lib.empty(rows * slabs, torch.float32, logits_f32.device)
+    pidx = _lib.empty(rows * slabs, torch.int32, logits_f32.device)
     if out_tokens is None:
-        out_tokens = torch.empty(rows, dtype=torch.int64, device=logits_f32.device)
+        out_tokens = _lib.empty(rows, torch.int64, logits_f32.device)
     _lib.call("sb_argmax", logits_f32.data_ptr(), rows, V, pval.data_ptr(), pidx.data_ptr(), out_tokens.data_ptr(),
               _lib.ptr(generated), generated.stride(0) if generated is not None else 0, step, _lib.stream())
     _g.launch_count += 2

@@ -43,7 +43,7 @@ def _workspace(nfloats: int, device) -> torch.Tensor:
     key = (device.index if device.index is not None else torch.cuda.current_device(), _lib.stream())
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nfloats:
-        ws = torch.empty(max(nfloats, 1 << 22), dtype=torch.float32, device=device)
+        ws = _lib.empty(max(nfloats, 1 << 22), torch.float32, device)
         _workspaces[key] = ws
     return ws
 
@@ -130,7 +130,7 @@ def _gemm(a, b, M, N, K, a_mn, b_mn, out, residual, splits, bn, bias=None):
     _check2d(a, "a")
     _check2d(b, "b")
     if out is None:
-        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+        out = _lib.empty((M, N), torch.bfloat16, a.device)
     else:
         _check2d(out, "out")
         if tuple(out.shape) != (M, N):
@@ -210,9 +210,9 @@ def matmul_nn_swiglu(x, wgu, out=None, act=None):
     _check2d(x, "x")
     _check2d(wgu, "wgu")
     if out is None:
-        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        out = _lib.empty((M, N), torch.bfloat16, x.device)
     if act is None:
-        act = torch.empty((M, ff), dtype=torch.bfloat16, device=x.device)
+        act = _lib.empty((M, ff), torch.bfloat16, x.device)
     st = _lib.status_word(x.device)
     _lib.call("sb_gemm_pair_bf16", x.data_ptr(), wgu.data_ptr(), out.data_ptr(), None, M, N, K, x.stride(0),
               wgu.stride(0), out.stride(0), 0, 0, 1, None, act.data_ptr(), act.stride(0), ff, None, 0, st.data_ptr(),
@@ -238,7 +238,7 @@ def matmul_nt_swiglu_bwd(dy, wd, gu, out=None):
     _check2d(wd, "wd")
     _check2d(gu, "gu")
     if out is None:
-        out = torch.empty((M, 2 * ff), dtype=torch.bfloat16, device=dy.device)
+        out = _lib.empty((M, 2 * ff), torch.bfloat16, dy.device)
     st = _lib.status_word(dy.device)
     _lib.call("sb_gemm_pair_bf16", dy.data_ptr(), wd.data_ptr(), out.data_ptr(), None, M, ff, K, dy.stride(0),
               wd.stride(0), out.stride(0), 0, 0, 0, None, None, 0, 0, gu.data_ptr(), gu.stride(0), st.data_ptr(),

@@ -37,7 +37,7 @@ class DeviceSampler:
         self.state = torch.tensor([_i64(seed_to_state(s)) for s in seeds], dtype=torch.int64, device=self.device)
         self.history = torch.zeros((rows, max(history_len, 1)), dtype=torch.int64, device=self.device)
         self.n_hist = torch.zeros(rows, dtype=torch.int32, device=self.device)
-        self.work = (torch.empty((rows, vocab), dtype=torch.int32, device=self.device)
+        self.work = (_lib.empty((rows, vocab), torch.int32, self.device)
                      if self.device.type == "cuda" else None)
         self.tokens = torch.zeros(rows, dtype=torch.int64, device=self.device)
 

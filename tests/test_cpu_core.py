@@ -674,3 +674,21 @@ def test_native_cpu_flash_attention_w8a8_block_and_kv_cache():
     assert cq.nbytes() < 0.3 * cf.nbytes() and len(cf) == 50
     with pytest.raises(MemoryError):
         cf.append(K[0], V[0])
+
+
+def test_debug_allocator_poisons_payload_and_catches_a_write_past_the_end():
+    from scirust_b200.ops import _lib
+    t = _lib.fenced_empty((5, 3), torch.float32, "cpu", tag="probe")
+    assert torch.isnan(t).all() and t.is_contiguous() and t.data_ptr() % 16 == 0
+    b = _lib.fenced_empty((7,), torch.bfloat16, "cpu")
+    assert torch.isnan(b.float()).all()
+    _lib.check_canaries()
+    t.fill_(1.0)                                           # a well-behaved writer leaves the fences alone
+    _lib.check_canaries()
+    # what a kernel that runs one element past its output does, made on the host: the byte after the payload
+    past = torch.empty(0, dtype=torch.uint8).set_(t.untyped_storage())   # the backing buffer: fence | payload | fence
+    past[256 + 5 * 3 * 4] = 0
+    with pytest.raises(_lib.NativeError, match="past the end.*probe"):
+        _lib.check_canaries()
+    del t, b, past
+    _lib._fenced.clear()
