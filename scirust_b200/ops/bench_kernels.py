@@ -45,7 +45,7 @@ def _rand(shape, seed):
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["gemm", "gemm_model", "attention", "attention_bwd", "rmsnorm", "ce", "adamw", "gemv",
-                                      "decode_attn", "sampler"])
+                                      "decode_attn", "sampler", "gemm_w8", "conv"])
     ap.add_argument("--int8", action="store_true", help="gemv: per-channel int8 weights")
     ap.add_argument("--ctx", type=int, default=4096, help="decode_attn: cached positions per sequence")
     ap.add_argument("--library", action="store_true", help="gemm_model: also time torch.matmul (cuBLAS)")
@@ -116,6 +116,27 @@ def main(argv=None):
         ms = _time(lambda: decode.gemv(x, wq), a.iters, a.warmup, flush)
         nbytes = K * N * (1 if a.int8 else 2)
         out.update(m=M, k=K, n=N, int8=bool(a.int8), ms=ms, gbs=nbytes / ms / 1e6)
+    elif a.kernel == "gemm_w8":
+        # batched decode product on the dequant-fused tcgen05 GEMM: x [batch, K] bf16, W [K, N] int8 + column scales
+        from . import decode
+        K, N, M = a.k, a.n, a.batch
+        w = _rand((K, N), 11)
+        x = _rand((M, K), 12)
+        wq = decode.quantize_per_channel(w)
+        ms = _time(lambda: decode.matmul_w8(x, wq), a.iters, a.warmup, flush)
+        mb = _time(lambda: gemm.matmul_nn(x, w), a.iters, a.warmup, flush)
+        out.update(m=M, k=K, n=N, ms=ms, gbs=K * N / ms / 1e6, tflops=2.0 * M * K * N / ms / 1e9, bf16_ms=mb,
+                   bf16_gbs=2 * K * N / mb / 1e6)
+    elif a.kernel == "conv":
+        # 3x3 stride-1 convolution, NHWC rows: batch x seq x seq image of `heads` channels -> `cols` channels
+        from . import conv
+        B, Hs, Cin, Cout = a.batch, a.seq, a.heads, a.cols
+        geom = conv.ConvGeom(B, Hs, Hs, Cin)
+        x = _rand((geom.rows, Cin), 21)
+        wp = conv.pack_conv_weight(_rand((Cout, Cin, 3, 3), 22).float(), Cin, 3).to(torch.bfloat16).cuda()
+        ms = _time(lambda: conv.conv2d(x, wp, geom, 3, 1, 1), a.iters, a.warmup, flush)
+        fl = 2.0 * geom.rows * Cout * 9 * Cin
+        out.update(batch=B, hw=Hs, cin=Cin, cout=Cout, ms=ms, tflops=fl / ms / 1e9)
     elif a.kernel == "sampler":
         # top-k / top-p / temperature sampling of `batch` rows of `cols` fp32 logits (default: a 128256-word vocabulary)
         from ..generate import SamplingParams

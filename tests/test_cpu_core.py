@@ -692,3 +692,75 @@ def test_debug_allocator_poisons_payload_and_catches_a_write_past_the_end():
         _lib.check_canaries()
     del t, b, past
     _lib._fenced.clear()
+
+
+def test_certified_transform_pairs_round_trip_within_their_certificates():
+    import math
+    import random
+    from scirust_b200.numerics import certified as CN
+    rng = random.Random(0)
+
+    def ulp(x):
+        return math.ulp(abs(x)) if x != 0 else math.ulp(0.0)
+    cases = [(CN.Log(), 1e-6, 1e6), (CN.Log1p(), -0.9, 1e6), (CN.SignedLog(), -1e6, 1e6), (CN.Power(0.25), 1e-8, 1e8),
+             (CN.MuLaw(255.0), -1.0, 1.0), (CN.Logit(), 1e-6, 0.999), (CN.Anscombe(), 0.5, 1e6)]
+    for pair, lo, hi in cases:
+        iv = CN.Interval(lo, hi)
+        bound = pair.roundtrip_bound(iv).ulps
+        for _ in range(400):
+            x = rng.uniform(lo, hi) if lo < 0 else math.exp(rng.uniform(math.log(lo), math.log(hi)))
+            if x == 0.0:
+                continue
+            back = pair.decode(pair.encode(x))
+            assert abs(back - x) <= bound * ulp(x), (type(pair).__name__, x, back, bound)
+            assert pair.kappa_rt(x) <= pair.kappa_rt_sup(iv) * (1 + 1e-12)
+    assert CN.Log().encode(-1.0) is None and CN.Anscombe().invalid_at(1e-17) and not CN.Anscombe().invalid_at(1.0)
+    assert CN.Power(0.5).roundtrip_bound(CN.Interval(1e-12, 1.0)).ulps > CN.Power(0.5).roundtrip_bound(CN.Interval(0.5, 1.0)).ulps
+
+
+def test_certificate_driven_summation_picks_the_cheapest_sound_method():
+    import math
+    import random
+    from scirust_b200.numerics import certified as CN
+    rng = random.Random(1)
+    easy = [rng.uniform(0.5, 1.5) for _ in range(1000)]
+    sel = CN.select_sum(easy, 1e-9)
+    assert sel.method == "naive" and abs(sel.value - math.fsum(easy)) <= sel.cert_rel_bound * abs(math.fsum(easy))
+    big = [rng.uniform(0.5, 1.5) for _ in range(200000)]
+    assert CN.select_sum(big, 1e-13).method in ("pairwise", "neumaier")
+    hard = [1e16, 1.0, -1e16, 1e-3] * 50                  # catastrophic cancellation: condition ~ 1e18
+    sel = CN.select_sum(hard, 1e-9)
+    assert sel.method == "expansion" and sel.value == math.fsum(hard) and sel.condition > 1e15
+    assert CN.sum_klein(hard) == math.fsum(hard)           # second-order compensation survives what first-order cannot
+    assert CN.sum_expansion(hard) == math.fsum(hard) and CN.sum_condition([1.0, -1.0]) == math.inf
+    xs = [rng.gauss(0, 1) for _ in range(5000)]
+    for f in (CN.sum_neumaier, CN.sum_klein, CN.sum_pairwise, CN.sum_expansion):
+        assert abs(f(xs) - math.fsum(xs)) <= 1e-12
+
+
+def test_a_priori_rational_proofs_hold_and_the_kernels_meet_them():
+    import math
+    from fractions import Fraction
+    from scirust_b200.numerics import formal as FP
+    assert Fraction(math.log(2)) < FP.ln2_upper() < Fraction(math.log(2)) + Fraction(1, 2 ** 50)
+    assert Fraction(math.pi) < FP.pi_upper() < Fraction(math.pi) + Fraction(1, 2 ** 40)
+    for proof in (FP.prove_exp(), FP.prove_cos(), FP.prove_sin()):
+        assert proof.holds(), proof.name
+        assert proof.relative_bound > 0 and isinstance(proof.relative_bound, Fraction)
+    # a degree-5 polynomial fails the exp proof: the threshold is not vacuous
+    FP.EXP_DEGREE, keep = 5, FP.EXP_DEGREE
+    try:
+        assert not FP.prove_exp().holds()
+    finally:
+        FP.EXP_DEGREE = keep
+    # the float64 kernels stay inside the proven relative bound on their ranges (measured against the host libm)
+    lim = float(FP.THRESHOLD)
+    for i in range(-200, 201):
+        r = i / 200 * (math.log(2) / 2)
+        assert abs(FP.exp_kernel(r) - math.exp(r)) <= lim * math.exp(r)
+        q = i / 200 * (math.pi / 4)
+        assert abs(FP.cos_kernel(q) - math.cos(q)) <= lim * math.cos(q)
+        assert abs(FP.sin_kernel(q) - math.sin(q)) <= lim * abs(math.sin(q)) + 1e-300
+    for x in (-50.0, -3.3, -1e-9, 0.0, 0.7, 12.5, 88.0):
+        assert abs(FP.exp_portable(x) - math.exp(x)) <= 4e-16 * math.exp(x)
+    assert FP.exp_portable(1000.0) == math.inf and FP.exp_portable(-1000.0) == 0.0
