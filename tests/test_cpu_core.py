@@ -764,3 +764,52 @@ def test_a_priori_rational_proofs_hold_and_the_kernels_meet_them():
     for x in (-50.0, -3.3, -1e-9, 0.0, 0.7, 12.5, 88.0):
         assert abs(FP.exp_portable(x) - math.exp(x)) <= 4e-16 * math.exp(x)
     assert FP.exp_portable(1000.0) == math.inf and FP.exp_portable(-1000.0) == 0.0
+
+
+def test_elastic_bpe_kernels_match_the_rank_priority_oracle_and_autotune_keeps_semantics():
+    import random
+    from scirust_b200 import tokenizer_elastic as ET
+    A, B, C, AB, BC, AA = 10, 11, 12, 21, 20, 30
+    o = ET.CanonicalBpeOracle([(B, C, BC), (A, B, AB)])
+    assert o.encode_ids([A, B, C]) == [A, BC]                  # rank beats left-to-right order
+    assert ET.CanonicalBpeOracle([(A, A, AA)]).encode_ids([A, A, A]) == [AA, A]      # left-most occurrence on ties
+    with pytest.raises(ET.DuplicateMergeRule):
+        ET.CanonicalBpeOracle([(1, 2, 3), (1, 2, 4)])
+    th = ET.ElasticThresholds(16, 64, 256, 1024, 4096)
+    assert [th.classify(n) for n in (0, 16, 17, 65, 257, 1025, 4097)] == ["S", "S", "M", "L", "XL", "XXL", "XXXL"]
+    with pytest.raises(ValueError):
+        ET.ElasticThresholds(16, 16, 256, 1024, 4096)
+    # a random merge table over bytes: every kernel reproduces the oracle on pieces of every class
+    rng = random.Random(3)
+    merges, next_id, seen = [], 256, set()
+    pool = list(range(97, 105))
+    while len(merges) < 300:
+        l, r = rng.choice(pool), rng.choice(pool)
+        if (l, r) in seen:
+            continue
+        seen.add((l, r))
+        merges.append((l, r, next_id))
+        pool.append(next_id)
+        next_id += 1
+    oracle = ET.CanonicalBpeOracle(merges)
+    cases = {cls: [[rng.randrange(97, 105) for _ in range(n)] for _ in range(6)]
+             for cls, n in zip(ET.CLASSES, (9, 40, 150, 600, 1500, 4200))}
+    for cls, pieces in cases.items():
+        for p in pieces[:2 if cls in ("XXL", "XXXL") else 6]:
+            want = oracle.encode_ids(p)
+            for name in ("tiny_scan", "indexed", "heap"):
+                assert oracle.kernel(name)(p) == want, (cls, name)
+    assert oracle.encode_heap([]) == [] and oracle.encode_indexed([97]) == [97]
+    # the auto-tuner: picks per class, never a kernel that disagrees with the oracle
+    small = {c: cases[c][:3] for c in ("S", "M", "L")}
+    rep = ET.autotune(oracle, small, th, repeats=3)
+    assert rep.profile.kernels[3:] == ("reference",) * 3 and all(k in ET.KERNELS for k in rep.profile.kernels)
+    broken = ET.CanonicalBpeOracle(merges)
+    broken.encode_heap = lambda ids: list(ids)                 # a fast kernel that is wrong
+    rep2 = ET.autotune(broken, small, th, repeats=2)
+    assert all("heap" in rep2.rejected[c] for c in small) and "heap" not in rep2.profile.kernels
+    # two different profiles, identical ids
+    t1 = ET.ElasticTokenizer(merges, ET.ElasticProfile.reference_only(th))
+    t2 = ET.ElasticTokenizer(merges, rep.profile)
+    data = bytes(rng.randrange(97, 105) for _ in range(500))
+    assert t1.encode_bytes(data) == t2.encode_bytes(data) == ET.ElasticTokenizer(merges).encode_bytes(data)
