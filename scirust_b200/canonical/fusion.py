@@ -185,7 +185,7 @@ class FusedKernelCache:
 
     def launch(self, steps, arena: torch.Tensor, out_off: int, in_offs: list, n: int) -> None:
         from ..runtime import RawAccess, RawBinding, RawBuffer, RawLaunchConfig
-        key = (steps, len(in_offs))
+        key = (repr(steps), len(in_offs))
         k = self.kernels.get(key)
         if k is None:
             k = self.kernels[key] = self.rt.compile(cuda_source(steps, len(in_offs)), "fused_elementwise")

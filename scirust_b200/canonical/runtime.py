@@ -79,9 +79,7 @@ class ReferencePlanRuntime:
                 return K.run("relu", ins[0].contiguous())
             if op == "ReluGrad":
                 # cotangent where the primal is strictly positive, +0 elsewhere (NaN primal: +0)
-                mask = (ins[0] > 0).to(torch.float32)
-                return K.run("mul", ins[1].contiguous(), mask.contiguous()) if not dev else \
-                    torch.where(ins[0] > 0, ins[1], torch.zeros_like(ins[1]))
+                return torch.where(ins[0] > 0, ins[1], torch.zeros_like(ins[1]))      # a select, never inf * 0
             if op == "ZerosLike":
                 return torch.zeros_like(ins[0])
             return torch.ones_like(ins[0])

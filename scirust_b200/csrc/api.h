@@ -76,6 +76,10 @@ int sb_dequantize(const void* Q, const float* scale, int K, int N, void* W, void
 // gemm_dist_tcgen05.cu
 int sb_gemm_dist_bf16(void* const* a_ptrs, void* const* b_ptrs, void* C, const void* R, void* const* stage_ptrs, void* const* flag_ptrs, int M, int N, int K, int lda, int ldb, int ldc, int ldr, int a_mn, int b_mn, int a_gather, int b_gather, int scatter, int rank, int W, uint32_t epoch, unsigned int* counters, int bn, int wait_ms, void* a_stage, int ld_stage, uint32_t* chunk_flags, unsigned int* chunk_ctr, int* status, void* stream_);
 
+// gemm_i8_tcgen05.cu
+int sb_quantize_rows(const void* x, int ldx, void* xq, int ldq, float* sx, int M, int K, void* stream);
+int sb_gemm_i8(const void* xq, int ldq, const float* sx, const void* wq_t, int ldw, const float* sw, void* C, int ldc, const void* R, int ldr, int M, int N, int K, int splits, void* workspace, int* status, void* stream);
+
 // gemm_pair_tcgen05.cu
 size_t sb_gemm_pair_workspace_floats();
 int sb_gemm_pair_bf16(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb, int ldc, int ldr, int a_mn, int b_mn, void* workspace, void* act, int ld_act, int ff, const void* gu, int ld_gu, int* status, void* stream_);

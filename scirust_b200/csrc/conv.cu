@@ -42,6 +42,66 @@ __global__ void im2col_nhwc_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfl
   col[idx] = v;
 }
 
+// The same gather, eight channels (16 bytes) per thread, for C a multiple of 8 (every layer but an RGB stem): one
+// index decomposition per 16-byte word instead of per element, and 16-byte loads and stores.
+__global__ void im2col_nhwc_vec8_kernel(const uint4* __restrict__ x, uint4* __restrict__ col, int B, int H, int W,
+                                        int C8, int KH, int KW, int stride, int pad, int OH, int OW, int Kp8) {
+  const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const size_t total = static_cast<size_t>(B) * OH * OW * Kp8;
+  if (idx >= total) return;
+  const int k8 = static_cast<int>(idx % Kp8);
+  const size_t row = idx / Kp8;
+  const int ow = static_cast<int>(row % OW);
+  const int oh = static_cast<int>((row / OW) % OH);
+  const int b = static_cast<int>(row / (static_cast<size_t>(OW) * OH));
+  uint4 v = make_uint4(0u, 0u, 0u, 0u);
+  if (k8 < KH * KW * C8) {
+    const int c8 = k8 % C8;
+    const int kw = (k8 / C8) % KW;
+    const int kh = k8 / (C8 * KW);
+    const int ih = oh * stride - pad + kh, iw = ow * stride - pad + kw;
+    if (ih >= 0 && ih < H && iw >= 0 && iw < W) v = __ldg(x + ((static_cast<size_t>(b) * H + ih) * W + iw) * C8 + c8);
+  }
+  col[idx] = v;
+}
+
+__device__ __forceinline__ float conv_bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float conv_bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ uint32_t conv_pack(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// col2im, eight channels per thread; the taps are added in the same ascending (kh, kw) order as the scalar kernel
+__global__ void col2im_nhwc_vec8_kernel(const uint4* __restrict__ dcol, uint4* __restrict__ dx, int B, int H, int W,
+                                        int C8, int KH, int KW, int stride, int pad, int OH, int OW, int Kp8) {
+  const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const size_t total = static_cast<size_t>(B) * H * W * C8;
+  if (idx >= total) return;
+  const int c8 = static_cast<int>(idx % C8);
+  const int iw = static_cast<int>((idx / C8) % W);
+  const int ih = static_cast<int>((idx / (static_cast<size_t>(C8) * W)) % H);
+  const int b = static_cast<int>(idx / (static_cast<size_t>(C8) * W * H));
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int kh = 0; kh < KH; ++kh) {
+    const int th = ih + pad - kh;
+    if (th < 0 || th % stride) continue;
+    const int oh = th / stride;
+    if (oh >= OH) continue;
+    for (int kw = 0; kw < KW; ++kw) {
+      const int tw = iw + pad - kw;
+      if (tw < 0 || tw % stride) continue;
+      const int ow = tw / stride;
+      if (ow >= OW) continue;
+      const uint4 v = __ldg(dcol + ((static_cast<size_t>(b) * OH + oh) * OW + ow) * Kp8 + (kh * KW + kw) * C8 + c8);
+      acc[0] += conv_bf_lo(v.x); acc[1] += conv_bf_hi(v.x); acc[2] += conv_bf_lo(v.y); acc[3] += conv_bf_hi(v.y);
+      acc[4] += conv_bf_lo(v.z); acc[5] += conv_bf_hi(v.z); acc[6] += conv_bf_lo(v.w); acc[7] += conv_bf_hi(v.w);
+    }
+  }
+  dx[idx] = make_uint4(conv_pack(acc[0], acc[1]), conv_pack(acc[2], acc[3]), conv_pack(acc[4], acc[5]),
+                       conv_pack(acc[6], acc[7]));
+}
+
 // dx[b,ih,iw,c] = sum over (kh,kw) in ascending order of dcol[(b,oh,ow),(kh,kw,c)] where the output
 // position maps onto this input pixel. Gather form: one thread per input element.
 __global__ void col2im_nhwc_kernel(const __nv_bfloat16* __restrict__ dcol, __nv_bfloat16* __restrict__ dx, int B,
@@ -236,6 +296,11 @@ extern "C" int sb_im2col_nhwc(const void* x, void* col, int B, int H, int W, int
                               int pad, int OH, int OW, int Kp, void* stream) {
   if (B <= 0 || Kp < KH * KW * C || (Kp & 7)) return SB_ERR_ARG;
   const size_t total = static_cast<size_t>(B) * OH * OW * Kp;
+  if ((C & 7) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(col)) & 15) == 0) {
+    im2col_nhwc_vec8_kernel<<<nblk(total / 8), 256, 0, STREAM>>>(static_cast<const uint4*>(x), static_cast<uint4*>(col),
+                                                                 B, H, W, C / 8, KH, KW, stride, pad, OH, OW, Kp / 8);
+    CHECK_LAUNCH();
+  }
   im2col_nhwc_kernel<<<nblk(total), 256, 0, STREAM>>>(static_cast<const __nv_bfloat16*>(x),
                                                       static_cast<__nv_bfloat16*>(col), B, H, W, C, KH, KW, stride,
                                                       pad, OH, OW, Kp);
@@ -245,6 +310,12 @@ extern "C" int sb_col2im_nhwc(const void* dcol, void* dx, int B, int H, int W, i
                               int pad, int OH, int OW, int Kp, void* stream) {
   if (B <= 0 || Kp < KH * KW * C) return SB_ERR_ARG;
   const size_t total = static_cast<size_t>(B) * H * W * C;
+  if ((C & 7) == 0 && (Kp & 7) == 0 && ((reinterpret_cast<uintptr_t>(dcol) | reinterpret_cast<uintptr_t>(dx)) & 15) == 0) {
+    col2im_nhwc_vec8_kernel<<<nblk(total / 8), 256, 0, STREAM>>>(static_cast<const uint4*>(dcol),
+                                                                 static_cast<uint4*>(dx), B, H, W, C / 8, KH, KW,
+                                                                 stride, pad, OH, OW, Kp / 8);
+    CHECK_LAUNCH();
+  }
   col2im_nhwc_kernel<<<nblk(total), 256, 0, STREAM>>>(static_cast<const __nv_bfloat16*>(dcol),
                                                       static_cast<__nv_bfloat16*>(dx), B, H, W, C, KH, KW, stride,
                                                       pad, OH, OW, Kp);

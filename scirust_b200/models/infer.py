@@ -163,7 +163,7 @@ class InferenceEngine:
             # layer's weights are expanded to bf16 once (a few percent of the GEMM's time) and the
             # plain bf16 kernel runs at full rate
             if M < 1024 and w.q.shape[1] % 16 == 0:
-                return D.matmul_w8(x, w, residual=residual)
+                return D.matmul_int8(x, w, residual=residual)
             w = w.dequantize()
         return ops.matmul_nn(x, w, residual=residual)
 
@@ -213,7 +213,7 @@ class InferenceEngine:
         if rms_weight is not None:
             hn, _ = ops.rmsnorm_fwd(hn, rms_weight, self.cfg.eps, want_inv=False)
         if isinstance(self.head_t, D.QuantWeight):
-            logits.copy_(D.matmul_w8(hn, self.head_t).float())
+            logits.copy_(D.matmul_int8(hn, self.head_t).float())
         else:
             logits.copy_(ops.matmul_nn(hn, self.head_t).float())
 

@@ -145,7 +145,7 @@ class TPInferenceEngine(InferenceEngine):
             return out
         if isinstance(w, D.QuantWeight):
             if a.shape[0] < 1024 and w.q.shape[1] % 16 == 0:
-                return D.matmul_w8(a, w, out=out)
+                return D.matmul_int8(a, w, out=out)
             w = w.dequantize()
         return ops.matmul_nn(a, w, out=out)
 

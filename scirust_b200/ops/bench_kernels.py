@@ -124,9 +124,13 @@ def main(argv=None):
         x = _rand((M, K), 12)
         wq = decode.quantize_per_channel(w)
         ms = _time(lambda: decode.matmul_w8(x, wq), a.iters, a.warmup, flush)
+        wq.transposed()
+        m8 = _time(lambda: decode.matmul_w8a8(x, wq), a.iters, a.warmup, flush)
+        xq, sx = decode.quantize_rows(x)
+        mq = _time(lambda: decode.quantize_rows(x), a.iters, a.warmup, flush)
         mb = _time(lambda: gemm.matmul_nn(x, w), a.iters, a.warmup, flush)
-        out.update(m=M, k=K, n=N, ms=ms, gbs=K * N / ms / 1e6, tflops=2.0 * M * K * N / ms / 1e9, bf16_ms=mb,
-                   bf16_gbs=2 * K * N / mb / 1e6)
+        out.update(m=M, k=K, n=N, w8a16_ms=ms, w8a16_gbs=K * N / ms / 1e6, w8a8_ms=m8, w8a8_gbs=K * N / m8 / 1e6,
+                   quantize_rows_ms=mq, bf16_ms=mb, bf16_gbs=2 * K * N / mb / 1e6)
     elif a.kernel == "conv":
         # 3x3 stride-1 convolution, NHWC rows: batch x seq x seq image of `heads` channels -> `cols` channels
         from . import conv

@@ -81,6 +81,17 @@ class QuantWeight:
 
     def __init__(self, q: torch.Tensor, scale: torch.Tensor):
         self.q, self.scale = q, scale
+        self._qt = None
+
+    def transposed(self) -> torch.Tensor:
+        """The codes as ``[N, K]`` (K contiguous, rows padded to 16 bytes): the operand layout of the W8A8 GEMM."""
+        if self._qt is None:
+            K, N = self.q.shape
+            Kp = (K + 15) // 16 * 16
+            t = torch.zeros((N, Kp), dtype=torch.int8, device=self.q.device)
+            t[:, :K] = self.q.t()
+            self._qt = t
+        return self._qt
 
     @property
     def shape(self):
@@ -267,6 +278,16 @@ def gemv_argmax(x, w, out_tokens=None, rms_weight=None, eps=1e-5, logits=None, c
     return out_tokens
 
 
+def matmul_int8(x, w: QuantWeight, residual=None, out=None):
+    """The int8-weight product for batched decoding (more rows than the GEMV takes, fewer than prefill): the W8A8
+    integer-tensor-core kernel (``matmul_w8a8``, the reference's dynamic-activation arithmetic) unless ``SB_W8A8=0``
+    or the shape does not fit it, else the W8A16 dequant-fused kernel (``matmul_w8``)."""
+    K, N = w.q.shape
+    if x.is_cuda and os.environ.get("SB_W8A8", "1") != "0" and K % 16 == 0 and N % 8 == 0:
+        return matmul_w8a8(x, w, residual=residual, out=out)
+    return matmul_w8(x, w, residual=residual, out=out)
+
+
 def matmul_w8(x, w: QuantWeight, residual=None, out=None, splits=None):
     """y[M,N] = (x[M,K] @ int8 W) * scale (+ residual) on the dequant-fused tcgen05 GEMM
     (csrc/gemm_w8_tcgen05.cu): the int8 codes are widened to bf16 in shared memory, so the weights
@@ -288,6 +309,64 @@ def matmul_w8(x, w: QuantWeight, residual=None, out=None, splits=None):
     _lib.call("sb_gemm_w8", x.data_ptr(), w.q.data_ptr(), w.scale.data_ptr(), out.data_ptr(), _lib.ptr(residual), M, N,
               K, x.stride(0), w.q.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0, splits,
               _lib.ptr(ws), _lib.status_word(x.device).data_ptr(), _lib.stream())
+    _g.launch_count += 2 if splits > 1 else 1
+    return out
+
+
+_lib.register("sb_quantize_rows", [vp, i32, vp, i32, vp, i32, i32, vp])
+_lib.register("sb_gemm_i8", [vp, i32, vp, vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, i32, vp, vp, vp])
+
+
+def quantize_rows(x):
+    """Dynamic per-row activation quantisation: ``(q int8 [M, K], scale fp32 [M])`` with ``scale = max|x| / 127`` (1 for
+    a zero row) and round half away from zero (scirust-core/src/quantization.rs:150-170)."""
+    M, K = x.shape
+    if not x.is_cuda:
+        xf = x.float()
+        mx = xf.abs().amax(1)
+        s = torch.where(mx == 0, torch.ones_like(mx), mx / 127.0)
+        v = xf / s[:, None]
+        q = torch.where(v >= 0, torch.floor(v + 0.5), torch.ceil(v - 0.5)).clamp(-128, 127).to(torch.int8)
+        return q, s
+    Kp = (K + 15) // 16 * 16
+    q = _lib.empty((M, Kp), torch.int8, x.device)
+    s = _lib.empty((M,), torch.float32, x.device)
+    if Kp != K:
+        q.zero_()
+    _lib.call("sb_quantize_rows", x.data_ptr(), x.stride(0), q.data_ptr(), Kp, s.data_ptr(), M, K, _lib.stream())
+    _g.launch_count += 1
+    return q[:, :K], s
+
+
+def matmul_w8a8(x, w: QuantWeight, residual=None, out=None, splits=None):
+    """y[M,N] = (quant_rows(x) . int8 W) * sx[m] * sw[n] (+ residual): the reference's quantised linear layer
+    (dynamic per-row activation scales, int32 accumulation, one rescale; quantization.rs:150-190) on the integer
+    tensor cores (csrc/gemm_i8_tcgen05.cu, tcgen05.mma.kind::i8). The int8 weights stream from HBM once and go from TMA
+    straight into the MMA; integer accumulation makes the result independent of tiling and split-K. ``w`` keeps a
+    K-major transposed copy of its codes for this kernel (made on first use)."""
+    M, K = x.shape
+    N = w.q.shape[1]
+    xq, sx = quantize_rows(x)
+    if not x.is_cuda:
+        y = (xq.to(torch.int64) @ w.q.to(torch.int64)).float() * (sx[:, None] * w.scale[None, :])
+        if residual is not None:
+            y = y + residual.float()
+        return y.to(BF)
+    if K % 16 or N % 8:
+        raise ValueError("matmul_w8a8: K must be a multiple of 16 and N of 8")
+    qt = w.transposed()
+    if out is None:
+        out = _lib.empty((M, N), BF, x.device)
+    if splits is None:
+        tiles = ((M + 127) // 128) * ((N + 255) // 256)
+        nkb = (K + 127) // 128
+        splits = 1 if tiles >= 100 else max(1, min((148 * 2) // max(tiles, 1), nkb // 4, 16))
+    ws = _workspace(splits * M * N, x.device) if splits > 1 else None
+    xq_full = xq if xq.stride(0) % 16 == 0 else xq.contiguous()
+    _lib.call("sb_gemm_i8", xq_full.data_ptr(), xq_full.stride(0), sx.data_ptr(), qt.data_ptr(), qt.stride(0),
+              w.scale.data_ptr(), out.data_ptr(), out.stride(0), _lib.ptr(residual),
+              residual.stride(0) if residual is not None else 0, M, N, K, splits, _lib.ptr(ws),
+              _lib.status_word(x.device).data_ptr(), _lib.stream())
     _g.launch_count += 2 if splits > 1 else 1
     return out
 

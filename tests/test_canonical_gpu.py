@@ -74,7 +74,7 @@ def test_raw_runtime_compiles_and_launches_with_validated_bindings():
         rt.launch(k, cfg, [RawBinding(by, RawAccess.READ_WRITE), RawBinding(by, RawAccess.READ)],
                   scalars=[C.c_float(1.0), C.c_int(n)])
     with pytest.raises(RawError, match="threads"):
-        rt.launch(k, RawLaunchConfig((1, 1, 1), (2048, 1, 1)), [RawBinding(by, RawAccess.READ_WRITE),
+        rt.launch(k, RawLaunchConfig((1, 1, 1), (32, 64, 1)), [RawBinding(by, RawAccess.READ_WRITE),
                                                                  RawBinding(bx, RawAccess.READ)],
                   scalars=[C.c_float(1.0), C.c_int(n)])
 

@@ -151,3 +151,29 @@ def test_dequant_fused_gemm(M, K, N):
     _lib.check_status()
     assert (y2.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
     assert torch.equal(y2, D.matmul_w8(x, qw, residual=r, splits=4))
+
+
+@pytest.mark.parametrize("M,K,N,splits", [(16, 4096, 1024, None), (64, 512, 768, 1), (200, 1040, 264, 3), (9, 128, 8, None)])
+def test_w8a8_gemm_on_integer_tensor_cores_is_exact(M, K, N, splits):
+    """tcgen05.mma.kind::i8: int8 x int8 -> int32 is exact, so the kernel must reproduce the host statement of the
+    reference's quantised linear layer (dynamic row scales, int64 accumulation, one rescale) to the last bf16 bit,
+    whatever the split-K factor; and it stays close to the unquantised product."""
+    g = torch.Generator(device="cuda").manual_seed(M + K)
+    x = (torch.randn(M, K, generator=g, device="cuda") * 0.7).to(torch.bfloat16)
+    w = (torch.randn(K, N, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    r = (torch.randn(M, N, generator=g, device="cuda") * 0.3).to(torch.bfloat16)
+    wq = D.quantize_per_channel(w)
+    xq, sx = D.quantize_rows(x)
+    xq_ref, sx_ref = D.quantize_rows(x.cpu())
+    assert torch.equal(xq.cpu(), xq_ref) and torch.equal(sx.cpu(), sx_ref)
+    acc = xq.cpu().to(torch.int64) @ wq.q.cpu().to(torch.int64)
+    want = (acc.float() * (sx_ref[:, None] * wq.scale.cpu()[None, :]) + r.cpu().float()).to(torch.bfloat16)
+    got = D.matmul_w8a8(x, wq, residual=r, splits=splits)
+    torch.cuda.synchronize()
+    assert torch.equal(got.cpu(), want)
+    again = D.matmul_w8a8(x, wq, residual=r, splits=2 if K >= 256 else 1)
+    assert torch.equal(again, got)                        # split-K adds integers: same bits
+    full = x.float() @ w.float() + r.float()
+    assert (got.float() - full).abs().max().item() <= 0.04 * full.abs().max().item()
+    from scirust_b200.ops import _lib
+    _lib.check_status(torch.device("cuda"))
