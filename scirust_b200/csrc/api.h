@@ -86,6 +86,9 @@ int sb_gemm_pair_bf16(const void* A, const void* B, void* C, const void* R, int 
 int sb_gemm_pair_ag_bf16(void* const* a_ptrs, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb, int ldc, int ldr, int b_mn, void* const* stage_ptrs, int ld_stage, void* const* flag_ptrs, void* const* chunk_flag_ptrs, unsigned int* chunk_ctr, unsigned int* cta_ctr, int rank, int W, uint32_t epoch, int wait_ms, int copy_own, int* status, void* stream_);
 int sb_gemm_pair_rs_bf16(const void* A, const void* B, void* const* part_ptrs, int ldp, void* out, int ld_out, const void* res, int ld_res, int M, int N, int K, int lda, int ldb, int b_mn, void* const* ready_ptrs, void* const* flag_ptrs, unsigned int* block_ctr, unsigned int* cta_ctr, int rank, int W, uint32_t epoch, int wait_ms, int* status, void* stream_);
 
+// gemm_skinny_tcgen05.cu
+int sb_gemm_skinny(const void* X, int ldx, const void* W, int ldw, void* C, int ldc, const void* R, int ldr, int rows, int N, int K, int is_i8, const float* sx, const float* sw, int splits, void* workspace, int* status, void* stream_);
+
 // gemm_tcgen05.cu
 size_t sb_gemm_balanced_workspace_floats();
 int sb_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda, int ldb, int ldc, int ldr, int a_mn, int b_mn, int splits, void* workspace, int bn, int* status, void* stream_);

@@ -157,6 +157,9 @@ class InferenceEngine:
         M = x.shape[0]
         if M <= D.gemv_max_rows(w):
             return D.gemv(x, w, residual=residual)
+        if D.skinny_ok(x, w):
+            # 9..64 rows (batched decoding): still bound by the weight bytes; the weight-streaming tcgen05 kernel
+            return D.matmul_skinny(x, w, residual=residual)
         if isinstance(w, D.QuantWeight):
             # few rows: the product is bound by the weight bytes, so the int8 matrix is streamed and
             # dequantised inside the GEMM; many rows (prefill): it is bound by the tensor cores, so the
@@ -212,6 +215,9 @@ class InferenceEngine:
             return
         if rms_weight is not None:
             hn, _ = ops.rmsnorm_fwd(hn, rms_weight, self.cfg.eps, want_inv=False)
+        if D.skinny_ok(hn, self.head_t):
+            logits.copy_(D.matmul_skinny(hn, self.head_t).float())
+            return
         if isinstance(self.head_t, D.QuantWeight):
             logits.copy_(D.matmul_int8(hn, self.head_t).float())
         else:

@@ -143,6 +143,8 @@ class TPInferenceEngine(InferenceEngine):
         if not a.is_cuda:
             out.copy_(self._linear(a, w))
             return out
+        if D.skinny_ok(a, w):
+            return D.matmul_skinny(a, w, out=out)
         if isinstance(w, D.QuantWeight):
             if a.shape[0] < 1024 and w.q.shape[1] % 16 == 0:
                 return D.matmul_int8(a, w, out=out)

@@ -129,6 +129,10 @@ def main(argv=None):
         xq, sx = decode.quantize_rows(x)
         mq = _time(lambda: decode.quantize_rows(x), a.iters, a.warmup, flush)
         mb = _time(lambda: gemm.matmul_nn(x, w), a.iters, a.warmup, flush)
+        if M <= decode.SKINNY_MAX_ROWS:
+            out.update(skinny_bf16_ms=_time(lambda: decode.matmul_skinny(x, w), a.iters, a.warmup, flush),
+                       skinny_w8a8_ms=_time(lambda: decode.matmul_skinny(x, wq), a.iters, a.warmup, flush))
+            out.update(skinny_bf16_gbs=2 * K * N / out["skinny_bf16_ms"] / 1e6, skinny_w8a8_gbs=K * N / out["skinny_w8a8_ms"] / 1e6)
         out.update(m=M, k=K, n=N, w8a16_ms=ms, w8a16_gbs=K * N / ms / 1e6, w8a8_ms=m8, w8a8_gbs=K * N / m8 / 1e6,
                    quantize_rows_ms=mq, bf16_ms=mb, bf16_gbs=2 * K * N / mb / 1e6)
     elif a.kernel == "conv":

@@ -278,6 +278,55 @@ def gemv_argmax(x, w, out_tokens=None, rms_weight=None, eps=1e-5, logits=None, c
     return out_tokens
 
 
+_lib.register("sb_gemm_skinny", [vp, i32, vp, i32, vp, i32, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, vp, vp])
+SKINNY_MAX_ROWS = 64
+
+
+def skinny_ok(x, w) -> bool:
+    """Whether ``matmul_skinny`` takes this product: CUDA, 9..64 rows, and a weight layout its TMA maps accept."""
+    if not x.is_cuda or os.environ.get("SB_SKINNY", "1") == "0":
+        return False
+    M = x.shape[0]
+    if M <= 8 or M > SKINNY_MAX_ROWS:
+        return False
+    if isinstance(w, QuantWeight):
+        K, N = w.q.shape
+        return os.environ.get("SB_W8A8", "1") != "0" and K % 16 == 0 and N % 8 == 0
+    K, N = w.shape
+    return N % 8 == 0 and w.stride(1) == 1 and w.stride(0) % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+
+
+def matmul_skinny(x, w, residual=None, out=None, splits=0):
+    """y[M,N] = x[M,K] @ W (+ residual) for 9..64 rows on the weight-streaming tcgen05 kernel
+    (csrc/gemm_skinny_tcgen05.cu): the weight tile is the 128-row MMA operand and the activations the narrow one, so
+    nearly all shared memory holds weight bytes in flight. ``w`` bf16 ``[K, N]``, or a ``QuantWeight`` (W8A8: the
+    activations are quantised per row, the product is exact in int32 and rescaled once)."""
+    quant = isinstance(w, QuantWeight)
+    M, K = x.shape
+    N = (w.q if quant else w).shape[1]
+    if out is None:
+        out = _lib.empty((M, N), BF, x.device)
+    if quant:
+        xq, sx = quantize_rows(x)
+        xq = xq if xq.stride(0) % 16 == 0 else xq.contiguous()
+        wt = w.transposed()
+        args = (xq.data_ptr(), xq.stride(0), wt.data_ptr(), wt.stride(0))
+        scales = (sx.data_ptr(), w.scale.data_ptr())
+    else:
+        args = (x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0))
+        scales = (None, None)
+    nt = (N + 127) // 128
+    bke = 128 if quant else 64
+    nkb = (K + bke - 1) // bke
+    est = splits if splits > 0 else max(1, min(148 // max(nt, 1), max(nkb // 4, 1)))
+    ws = _workspace(est * M * N, x.device) if est > 1 else None
+    _lib.call("sb_gemm_skinny", *args, out.data_ptr(), out.stride(0), _lib.ptr(residual),
+              residual.stride(0) if residual is not None else 0, M, N, K, int(quant), *scales,
+              est, _lib.ptr(ws), _lib.status_word(x.device).data_ptr(), _lib.stream())
+    _g.launch_count += 2 if est > 1 else 1
+    return out
+
+
 def matmul_int8(x, w: QuantWeight, residual=None, out=None):
     """The int8-weight product for batched decoding (more rows than the GEMV takes, fewer than prefill): the W8A8
     integer-tensor-core kernel (``matmul_w8a8``, the reference's dynamic-activation arithmetic) unless ``SB_W8A8=0``

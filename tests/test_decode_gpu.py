@@ -177,3 +177,39 @@ def test_w8a8_gemm_on_integer_tensor_cores_is_exact(M, K, N, splits):
     assert (got.float() - full).abs().max().item() <= 0.04 * full.abs().max().item()
     from scirust_b200.ops import _lib
     _lib.check_status(torch.device("cuda"))
+
+
+@pytest.mark.parametrize("quant", [False, True])
+@pytest.mark.parametrize("M,K,N,splits", [(16, 4096, 1024, 0), (9, 320, 264, 1), (33, 1040, 4104, 3), (64, 512, 128, 0),
+                                          (12, 128, 19200, 0)])
+def test_skinny_weight_streaming_gemm_matches_reference(quant, M, K, N, splits):
+    """9..64 rows on the swapped-operand tcgen05 kernel (weights as the 128-row operand, C^T in tensor memory):
+    bf16 against the fp32 product, int8 (W8A8) bit for bit against the integer statement; ragged N and K, one and
+    several work items per CTA, explicit and automatic split-K; two runs agree bit for bit."""
+    if quant and K % 16:
+        K = (K + 15) // 16 * 16
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + K)
+    x = (torch.randn(M, K, generator=g, device="cuda") * 0.7).to(torch.bfloat16)
+    w = (torch.randn(K, N, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    r = (torch.randn(M, N, generator=g, device="cuda") * 0.3).to(torch.bfloat16)
+    if quant:
+        wq = D.quantize_per_channel(w)
+        xq, sx = D.quantize_rows(x.cpu())
+        acc = xq.to(torch.int64) @ wq.q.cpu().to(torch.int64)
+        want = (acc.float() * (sx[:, None] * wq.scale.cpu()[None, :]) + r.cpu().float()).to(torch.bfloat16)
+        got = D.matmul_skinny(x, wq, residual=r, splits=splits)
+        torch.cuda.synchronize()
+        assert torch.equal(got.cpu(), want)
+        assert torch.equal(D.matmul_skinny(x, wq, residual=r, splits=splits), got)
+    else:
+        ref = x.float() @ w.float() + r.float()
+        got = D.matmul_skinny(x, w, residual=r, splits=splits)
+        torch.cuda.synchronize()
+        err = (got.float() - ref).abs()
+        tol = ref.abs() * 2.0 ** -7 + 2.0 ** -14 * 0.035 * 0.8 * K + 1e-3
+        assert bool((err <= tol).all()), float((err - tol).max())
+        assert torch.equal(D.matmul_skinny(x, w, residual=r, splits=splits), got)
+        plain = D.matmul_skinny(x, w, splits=1)
+        assert (plain.float() - x.float() @ w.float()).abs().max().item() <= 0.02 * max(1.0, (x.float() @ w.float()).abs().max().item())
+    from scirust_b200.ops import _lib
+    _lib.check_status(torch.device("cuda"))
