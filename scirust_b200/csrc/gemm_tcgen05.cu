@@ -23,6 +23,7 @@
 // Two fp32 accumulators (2 x BN columns of TMEM) let the epilogue of tile i overlap the
 // main loop of tile i+1. K is walked in a fixed order, so results are bitwise
 // repeatable; split-K writes fp32 partials that a second kernel adds in split order.
+#include <stdio.h>
 #include "sm100_ptx.cuh"
 #include "api.h"
 #include "gemm_sched.cuh"
@@ -290,13 +291,23 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 static EncodeTiledFn get_encode_fn() {
+  // cuTensorMapEncodeTiled is a driver call and wants a context current on the calling thread. A thread that has
+  // only ever used device 0 through a framework that skips cudaSetDevice when "the device is already 0" (an autograd
+  // worker whose first native call is a tensor-map encode) has none: bind the primary context once per thread.
+  thread_local bool context_bound = false;
+  if (!context_bound) {
+    cudaFree(nullptr);
+    context_bound = true;
+  }
   static EncodeTiledFn fn = nullptr;
   if (!fn) {
     void* ptr = nullptr;
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
-        qres != cudaDriverEntryPointSuccess)
+        qres != cudaDriverEntryPointSuccess) {
+      fprintf(stderr, "scirust_b200: cuTensorMapEncodeTiled could not be resolved\n");
       return nullptr;
+    }
     fn = reinterpret_cast<EncodeTiledFn>(ptr);
   }
   return fn;
@@ -316,6 +327,10 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr, "scirust_b200: tensor map refused (driver code %d): base %p, dims %llu x %llu, pitch %llu B, box %u x %u\n",
+            static_cast<int>(r), base, static_cast<unsigned long long>(inner), static_cast<unsigned long long>(outer),
+            static_cast<unsigned long long>(ld * 2), box_inner, box_outer);
   return r == CUDA_SUCCESS ? 0 : SB_ERR_DRIVER;
 }
 

@@ -253,6 +253,11 @@ typedef CUresult (*EncodeTiledFn8)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 
 static int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld_bytes,
                            uint32_t box_inner, uint32_t box_outer) {
+  thread_local bool context_bound = false;      // the driver call below wants a context current on this thread
+  if (!context_bound) {
+    cudaFree(nullptr);
+    context_bound = true;
+  }
   static EncodeTiledFn8 fn = nullptr;
   if (!fn) {
     void* ptr = nullptr;

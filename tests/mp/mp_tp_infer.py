@@ -40,7 +40,9 @@ def main():
     logits = tp.prefill(prompts).float().cpu().clone()
     err = (logits - ref_logits).abs().max().item()
     scale = ref_logits.abs().max().item()
-    assert err <= 3e-2 * max(1.0, scale), f"rank {rank}: prefill logits differ by {err} (scale {scale})"
+    # int8: a rank quantises its own weight shard and (W8A8) its own share of the activations, so the two engines
+    # differ by quantisation noise, not by rounding order
+    assert err <= (1e-1 if quant else 3e-2) * max(1.0, scale), f"rank {rank}: prefill logits differ by {err} (scale {scale})"
     tokens = tp.generate(prompts, NEW).cpu()
     again = tp.generate(prompts, NEW).cpu()
     assert torch.equal(tokens, again), "tensor-parallel decode is not repeatable"
