@@ -354,3 +354,61 @@ def test_canonical_operator_statements():
     for bad in ("exp", "log", "tanh"):
         with pytest.raises(K.Unsupported):
             K.run(bad, x)
+
+
+def test_sequence_scans_recurrent_and_parallel_forms_agree():
+    import math
+    from scirust_b200.nn import sequence_scans as S
+    g = torch.Generator().manual_seed(0)
+    T, dk, dv = 37, 8, 6
+    q, k, v = (torch.randn(T, d, generator=g, dtype=torch.float64) * 0.5 for d in (dk, dk, dv))
+    close = lambda a, b, tol=1e-9: torch.allclose(a, b, atol=tol, rtol=1e-8)     # noqa: E731
+    assert close(S.retention(q, k, v, 0.9), S.retention_recurrent(q, k, v, 0.9))
+    alpha = torch.sigmoid(torch.randn(T, dk, generator=g, dtype=torch.float64)) * 0.5 + 0.5
+    assert close(S.gated_linear_attention(q, k, v, alpha), S.gla_recurrent(q, k, v, alpha), 1e-7)
+    beta = torch.sigmoid(torch.randn(T, generator=g, dtype=torch.float64))
+    kn = k / k.norm(dim=1, keepdim=True)
+    assert close(S.delta_rule(q, kn, v, beta), S.delta_rule_recurrent(q, kn, v, beta))
+    d, n = 5, 4
+    x = torch.randn(T, d, generator=g, dtype=torch.float64)
+    dt = torch.nn.functional.softplus(torch.randn(T, d, generator=g, dtype=torch.float64))
+    A = -torch.rand(d, n, generator=g, dtype=torch.float64) - 0.1
+    B, C = torch.randn(T, n, generator=g, dtype=torch.float64), torch.randn(T, n, generator=g, dtype=torch.float64)
+    assert close(S.selective_scan(x, dt, A, B, C), S.selective_scan_recurrent(x, dt, A, B, C))
+    a = torch.sigmoid(torch.randn(T, generator=g, dtype=torch.float64)) * 0.5 + 0.5
+    assert close(S.ssd_dual(x, a, B, C), S.ssd_dual_recurrent(x, a, B, C))
+    lam = torch.complex(-torch.rand(n, generator=g, dtype=torch.float64) * 0.5, torch.randn(n, generator=g, dtype=torch.float64))
+    lam = torch.exp(lam)
+    Bc = torch.randn(n, 3, generator=g, dtype=torch.float64).to(torch.complex128)
+    Cc = torch.randn(2, n, generator=g, dtype=torch.float64).to(torch.complex128)
+    u = torch.randn(T, 3, generator=g, dtype=torch.float64)
+    assert close(S.s5_parallel_scan(u, lam, Bc, Cc), S.s5_scan(u, lam, Bc, Cc))
+    As = -torch.rand(n, generator=g, dtype=torch.float64) - 0.2
+    y = S.s4_scan(u[:, 0], As, torch.ones(n, dtype=torch.float64), torch.ones(n, dtype=torch.float64), 0.1)
+    h = torch.zeros(n, dtype=torch.float64)
+    want = []
+    for t in range(T):
+        h = torch.exp(0.1 * As) * h + (torch.exp(0.1 * As) - 1) / As * u[t, 0]
+        want.append(h.sum())
+    assert close(y, torch.stack(want))
+    f, c = torch.sigmoid(torch.randn(T, d, generator=g, dtype=torch.float64)), torch.randn(T, d, generator=g, dtype=torch.float64)
+    assert close(S.hgrn(f, c), S.hgrn_recurrent(f, c))
+    w, uu = torch.rand(d, generator=g, dtype=torch.float64) + 0.1, torch.randn(d, generator=g, dtype=torch.float64)
+    kk, vv = torch.randn(12, d, generator=g, dtype=torch.float64), torch.randn(12, d, generator=g, dtype=torch.float64)
+    assert close(S.rwkv_wkv(w, uu, kk, vv), S.rwkv_wkv_direct(w, uu, kk, vv))
+    big = S.rwkv_wkv(w, uu, kk * 0 + 500.0, vv)                  # the stabiliser keeps e^{500} out of the arithmetic
+    assert torch.isfinite(big).all()
+    ip, fp = torch.randn(T, generator=g, dtype=torch.float64), torch.randn(T, generator=g, dtype=torch.float64) + 2
+    assert close(S.mlstm_parallel(q, k / math.sqrt(dk), v, ip, fp), S.mlstm_scan(q, k / math.sqrt(dk), v, ip, fp).to(torch.float64), 1e-5)
+    hs = S.slstm_scan(torch.randn(T, d, generator=g) * 3, torch.randn(T, d, generator=g), torch.tanh(torch.randn(T, d, generator=g)),
+                      torch.sigmoid(torch.randn(T, d, generator=g)))
+    assert torch.isfinite(hs).all() and hs.abs().max() <= 1.0 + 1e-5
+    filt = torch.randn(T, d, generator=g, dtype=torch.float64) * 0.2
+    assert close(S.hyena_long_conv(x, filt), S.hyena_long_conv_direct(x, filt), 1e-9)
+    # ALiBi: slopes for 8 heads are 2^-1 .. 2^-8; a non-power-of-two count keeps the first power's slopes
+    s8 = S.alibi_slopes(8)
+    assert torch.allclose(s8, torch.tensor([2.0 ** -(i + 1) for i in range(8)]))
+    s12 = S.alibi_slopes(12)
+    assert torch.allclose(s12[:8], s8) and s12.numel() == 12
+    bias = S.alibi_bias(s8, 5)
+    assert bias.shape == (8, 5, 5) and bias[0, 3, 1] == -1.0 and bias[0, 1, 3] == float("-inf") and bias[3, 2, 2] == 0
