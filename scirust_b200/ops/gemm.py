@@ -76,15 +76,19 @@ BALANCED = os.environ.get("SB_GEMM_BALANCED", "1") != "0"
 FUSE_SWIGLU = os.environ.get("SB_FUSE_SWIGLU", "0") == "1"
 
 
-# The balanced schedule pays a fix-up pass and fp32 scratch traffic (measured: about 20 us on 74 CTA
-# pairs). It wins when tiles are long (weight-gradient products, K = tokens) AND there is at least one
-# whole wave besides the partial one; with less than one wave of tiles, or short K, whole tiles stay.
+# The balanced schedule pays a fix-up pass and fp32 scratch traffic (measured: about 20 us on 74 CTA pairs). Measured
+# per shape on the training step's products (TFLOP/s, plain tiles against balanced):
+#   3.46 waves (gate_up dgrad)  1248 / 1108     0.86 waves (LM-head dgrad)  1570 / 1129     0.59 waves (down wgrad) 1069 / 905
+#   1.19 waves (gate_up wgrad)  1108 / 1367     6.76 waves (LM-head wgrad)  1245 / 1093
+# so it is used when K is long AND the tiles make at least one whole wave AND the last, partial wave would leave more
+# than 15 % of the machine idle; with less than one wave whole tiles (or explicit split-K) stay.
 _BALANCED_MIN_K = 4096
 
 
-# Long-K products with few output tiles (weight gradients: K = tokens) also run on CTA pairs: the balanced schedule
-# deals their k-blocks evenly over all pairs (every SM busy whatever the tile count) and the fix-up pass adds the parts.
-_PAIR_LONGK = os.environ.get("SB_GEMM_PAIR_LONGK", "1") != "0"
+# Long-K products with few output tiles (weight gradients: K = tokens) on CTA pairs with the balanced schedule:
+# measured slower than explicit split-K on the single-CTA kernel (qkv wgrad 690 against 745 TFLOP/s, wo wgrad 531
+# against 570), so off unless asked for.
+_PAIR_LONGK = os.environ.get("SB_GEMM_PAIR_LONGK", "0") != "0"
 
 
 def _use_pair(M, N, K, splits, bn) -> bool:
@@ -101,7 +105,13 @@ def _use_pair(M, N, K, splits, bn) -> bool:
 def _use_balanced(tiles: int, workers: int, K: int) -> bool:
     if not BALANCED or K < _BALANCED_MIN_K:
         return False
-    return tiles >= workers or _BALANCED_MIN_K == 0 or (_PAIR_LONGK and K >= 8192)
+    if _BALANCED_MIN_K == 0:
+        return True                       # tests force the schedule on every shape
+    if tiles < workers:
+        return _PAIR_LONGK and K >= 8192 and 2 * tiles < workers
+    waves = tiles / workers
+    whole = -(-tiles // workers)
+    return tiles % workers != 0 and waves / whole < 0.85
 
 
 class _Bias:

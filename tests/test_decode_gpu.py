@@ -213,3 +213,10 @@ def test_skinny_weight_streaming_gemm_matches_reference(quant, M, K, N, splits):
         assert (plain.float() - x.float() @ w.float()).abs().max().item() <= 0.02 * max(1.0, (x.float() @ w.float()).abs().max().item())
     from scirust_b200.ops import _lib
     _lib.check_status(torch.device("cuda"))
+
+
+def test_driver_smoke_entry_runs_training_decode_and_batched_decode():
+    """The entry point the round-end driver calls: a few training steps, a cached decode, and 12-sequence decodes with
+    bf16 and int8 weights (the weight-streaming GEMM and its W8A8 form)."""
+    import __graft_entry__ as entry
+    entry.smoke()
