@@ -9,6 +9,9 @@ sequence. Backward: the same ring; every block is differentiated with the flash 
 normaliser and output (``P = exp(S - lse)``, ``delta = rowsum(dO * O)``), which yields that block's share of dQ and
 the dK/dV of the visiting shard; dK/dV travel on with their shard and arrive home after W hops.
 
+With ``layout="zigzag"`` a rank holds chunks r and 2W - 1 - r of 2W instead of one contiguous slice, which gives
+every rank the same causal work (the contiguous layout gives the last rank W times the first rank's).
+
 The blocks are visited in the same order on every run and merged in hop order, so results are repeatable bit for
 bit at a fixed world size. Transfers are ``torch.distributed`` point-to-point operations (NCCL between GPUs, gloo
 between CPU ranks), issued before the block's kernels so that the copy of hop t + 1 runs under the math of hop t.
@@ -46,67 +49,119 @@ def _merge(o, lse, o_b, lse_b):
     return out.view(B * S, H * dh), new
 
 
+def _chunk_ids(rank: int, world: int, layout: str):
+    """Global indices of the sequence chunks a rank holds: one chunk (``contiguous``), or chunks ``r`` and
+    ``2W - 1 - r`` of ``2W`` (``zigzag``): with a causal mask every rank then has the same number of visible
+    (query chunk, key chunk) pairs, where the contiguous layout gives rank W - 1 W times the work of rank 0."""
+    if layout == "contiguous":
+        return [rank]
+    if layout == "zigzag":
+        return [rank, 2 * world - 1 - rank]
+    raise ValueError("layout must be 'contiguous' or 'zigzag'")
+
+
+def _rows(x, B, S, n_chunks, c):
+    """Rows of chunk ``c`` of a local ``[B * S, C]`` matrix whose sequences hold ``n_chunks`` equal chunks."""
+    sc = S // n_chunks
+    return x.view(B, n_chunks, sc, -1)[:, c].reshape(B * sc, -1)
+
+
 class _RingAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, qkv, B, S, H, Hkv, dh, group, causal):
+    def forward(ctx, qkv, B, S, H, Hkv, dh, group, causal, layout):
         rank, W = dist.get_rank(group), dist.get_world_size(group)
         qd = H * dh
+        mine = _chunk_ids(rank, W, layout)
+        nc, sc = len(mine), S // len(mine)
         kv = qkv[:, qd:].contiguous()                       # the shard that travels
-        o = torch.zeros((B * S, qd), dtype=torch.float32, device=qkv.device)
-        lse = torch.full((B, H, S), float("-inf"), dtype=torch.float32, device=qkv.device)
-        blk = qkv.clone()
+        o = [torch.zeros((B * sc, qd), dtype=torch.float32, device=qkv.device) for _ in mine]
+        lse = [torch.full((B, H, sc), float("-inf"), dtype=torch.float32, device=qkv.device) for _ in mine]
+        qs = [_rows(qkv, B, S, nc, i)[:, :qd] for i in range(nc)]
         for t in range(W):
             src = (rank - t) % W
+            theirs = _chunk_ids(src, W, layout)
             nxt = _ring_exchange(kv, group, rank, W) if t + 1 < W else None     # hop t + 1 is in flight during hop t
-            if not causal or src <= rank:
-                blk[:, qd:] = kv
-                o_b, lse_b = att.attention_fwd(blk, B, S, H, Hkv, dh, causal=causal and src == rank)
-                o, lse = _merge(o, lse, o_b, lse_b)
+            for i, a in enumerate(mine):
+                for j, b in enumerate(theirs):
+                    if causal and b > a:
+                        continue                              # every key of that chunk lies in the future
+                    blk = torch.cat([qs[i], _rows(kv, B, S, nc, j)], 1)
+                    o_b, lse_b = att.attention_fwd(blk, B, sc, H, Hkv, dh, causal=causal and a == b)
+                    o[i], lse[i] = _merge(o[i], lse[i], o_b, lse_b)
             kv = nxt
-        out = o.to(qkv.dtype)
-        ctx.save_for_backward(qkv, out, lse)
-        ctx.meta = (B, S, H, Hkv, dh, group, causal)
+        out = torch.stack([x.view(B, sc, qd) for x in o], 1).reshape(B * S, qd).to(qkv.dtype)
+        ctx.save_for_backward(qkv, out, torch.stack(lse, 0))
+        ctx.meta = (B, S, H, Hkv, dh, group, causal, layout)
         return out
 
     @staticmethod
     def backward(ctx, do):
         qkv, out, lse = ctx.saved_tensors
-        B, S, H, Hkv, dh, group, causal = ctx.meta
+        B, S, H, Hkv, dh, group, causal, layout = ctx.meta
         rank, W = dist.get_rank(group), dist.get_world_size(group)
         qd = H * dh
+        mine = _chunk_ids(rank, W, layout)
+        nc, sc = len(mine), S // len(mine)
         do = do.contiguous()
         kv = qkv[:, qd:].contiguous()
-        dkv = torch.zeros_like(kv, dtype=torch.float32)     # gradient of the visiting shard, travels with it
-        dq = torch.zeros((B * S, qd), dtype=torch.float32, device=qkv.device)
-        blk = qkv.clone()
+        kvd = kv.shape[1]
+        dkv = torch.zeros((B, nc, sc, kvd), dtype=torch.float32, device=qkv.device)    # travels with its shard
+        dq = torch.zeros((B, nc, sc, qd), dtype=torch.float32, device=qkv.device)
+        qs = [_rows(qkv, B, S, nc, i)[:, :qd] for i in range(nc)]
+        outs = [_rows(out, B, S, nc, i).contiguous() for i in range(nc)]
+        dos = [_rows(do, B, S, nc, i).contiguous() for i in range(nc)]
         for t in range(W):
             src = (rank - t) % W
-            if not causal or src <= rank:
-                blk[:, qd:] = kv
-                g = att.attention_bwd(blk, out, lse, do, B, S, H, Hkv, dh, causal=causal and src == rank).float()
-                dq += g[:, :qd]
-                dkv += g[:, qd:]
+            theirs = _chunk_ids(src, W, layout)
+            for i, a in enumerate(mine):
+                for j, b in enumerate(theirs):
+                    if causal and b > a:
+                        continue
+                    blk = torch.cat([qs[i], _rows(kv, B, S, nc, j)], 1)
+                    g = att.attention_bwd(blk, outs[i], lse[i], dos[i], B, sc, H, Hkv, dh,
+                                          causal=causal and a == b).float()
+                    dq[:, i] += g[:, :qd].view(B, sc, qd)
+                    dkv[:, j] += g[:, qd:].view(B, sc, kvd)
             # shard and its gradient move on together; after the last hop the gradient is home
             if t + 1 < W:
                 kv = _ring_exchange(kv, group, rank, W)
-            dkv = _ring_exchange(dkv, group, rank, W)
-        dqkv = torch.cat([dq, dkv], 1).to(qkv.dtype)
-        return dqkv, None, None, None, None, None, None, None
+            dkv = _ring_exchange(dkv.reshape(B * S, kvd), group, rank, W).view(B, nc, sc, kvd)
+        dqkv = torch.cat([dq.reshape(B * S, qd), dkv.reshape(B * S, kvd)], 1).to(qkv.dtype)
+        return dqkv, None, None, None, None, None, None, None, None
 
 
 def ring_attention(qkv: torch.Tensor, B: int, S_local: int, H: int, Hkv: int, dh: int, group=None,
-                   causal: bool = True) -> torch.Tensor:
+                   causal: bool = True, layout: str = "contiguous") -> torch.Tensor:
     """Attention output ``[B * S_local, H * dh]`` of this rank's queries over the WHOLE sequence (``world * S_local``
-    tokens per sequence, sharded contiguously by rank). Differentiable w.r.t. ``qkv``."""
+    tokens per sequence, sharded by ``shard_sequence`` with the same ``layout``). Differentiable w.r.t. ``qkv``."""
     group = group if group is not None else dist.group.WORLD
-    return _RingAttention.apply(qkv, B, S_local, H, Hkv, dh, group, causal)
+    if layout == "zigzag" and S_local % 2:
+        raise ValueError("the zigzag layout needs an even number of local tokens")
+    return _RingAttention.apply(qkv, B, S_local, H, Hkv, dh, group, causal, layout)
 
 
-def shard_sequence(x: torch.Tensor, B: int, S: int, group=None) -> torch.Tensor:
-    """Rows of ``x [B * S, C]`` that belong to this rank's contiguous slice of every sequence."""
+def shard_sequence(x: torch.Tensor, B: int, S: int, group=None, layout: str = "contiguous") -> torch.Tensor:
+    """Rows of ``x [B * S, C]`` that belong to this rank: its contiguous slice of every sequence, or (``zigzag``) chunks
+    ``r`` and ``2W - 1 - r`` of ``2W``, concatenated in that order."""
     group = group if group is not None else dist.group.WORLD
     rank, W = dist.get_rank(group), dist.get_world_size(group)
-    if S % W:
-        raise ValueError("sequence length must be a multiple of the context-parallel size")
-    sl = S // W
-    return x.view(B, S, -1)[:, rank * sl:(rank + 1) * sl].reshape(B * sl, -1).contiguous()
+    ids = _chunk_ids(rank, W, layout)
+    n = W * len(ids)
+    if S % n:
+        raise ValueError("sequence length must be a multiple of the number of chunks")
+    sc = S // n
+    xv = x.view(B, n, sc, -1)
+    return torch.cat([xv[:, c] for c in ids], 1).reshape(B * sc * len(ids), -1).contiguous()
+
+
+def visible_pairs(world: int, layout: str) -> list:
+    """(query chunk, key chunk) pairs with at least one visible key under a causal mask, per rank: the work measure."""
+    out = []
+    for r in range(world):
+        n = 0
+        for src in range(world):
+            for a in _chunk_ids(r, world, layout):
+                for b in _chunk_ids(src, world, layout):
+                    n += b <= a
+        out.append(n)
+    return out

@@ -28,21 +28,24 @@ def main():
     g = torch.Generator().manual_seed(5)
     qkv = (torch.randn(B * S, (H + 2 * Hkv) * dh, generator=g) * 0.5).to(dt).to(dev)
     do = (torch.randn(B * S, H * dh, generator=g) * 0.5).to(dt).to(dev)
-    for causal in (True, False):
-        ref_o, _ = att.attention_ref(qkv, B, S, H, Hkv, dh, causal)
-        ref_g = att.attention_bwd_ref(qkv, do, B, S, H, Hkv, dh, causal)
-        local = shard_sequence(qkv, B, S).requires_grad_()
-        out = ring_attention(local, B, S // W, H, Hkv, dh, causal=causal)
-        out.backward(shard_sequence(do, B, S))
-        tol = 3e-2 if use_cuda else 2e-5
-        eo = (out.float() - shard_sequence(ref_o, B, S)).abs().max().item()
-        eg = (local.grad.float() - shard_sequence(ref_g, B, S)).abs().max().item()
-        assert eo <= tol and eg <= tol * 4, (rank, causal, eo, eg)
-        # repeatable bit for bit
-        local2 = shard_sequence(qkv, B, S).requires_grad_()
-        out2 = ring_attention(local2, B, S // W, H, Hkv, dh, causal=causal)
-        out2.backward(shard_sequence(do, B, S))
-        assert torch.equal(out, out2) and torch.equal(local.grad, local2.grad)
+    from scirust_b200.parallel.context_parallel import visible_pairs
+    assert len(set(visible_pairs(W, "zigzag"))) == 1 and visible_pairs(W, "contiguous")[-1] == W * visible_pairs(W, "contiguous")[0]
+    for layout in ("contiguous", "zigzag"):
+        for causal in (True, False):
+            ref_o, _ = att.attention_ref(qkv, B, S, H, Hkv, dh, causal)
+            ref_g = att.attention_bwd_ref(qkv, do, B, S, H, Hkv, dh, causal)
+            local = shard_sequence(qkv, B, S, layout=layout).requires_grad_()
+            out = ring_attention(local, B, S // W, H, Hkv, dh, causal=causal, layout=layout)
+            out.backward(shard_sequence(do, B, S, layout=layout))
+            tol = 3e-2 if use_cuda else 2e-5
+            eo = (out.float() - shard_sequence(ref_o, B, S, layout=layout)).abs().max().item()
+            eg = (local.grad.float() - shard_sequence(ref_g, B, S, layout=layout)).abs().max().item()
+            assert eo <= tol and eg <= tol * 4, (rank, layout, causal, eo, eg)
+            # repeatable bit for bit
+            local2 = shard_sequence(qkv, B, S, layout=layout).requires_grad_()
+            out2 = ring_attention(local2, B, S // W, H, Hkv, dh, causal=causal, layout=layout)
+            out2.backward(shard_sequence(do, B, S, layout=layout))
+            assert torch.equal(out, out2) and torch.equal(local.grad, local2.grad)
     dist.barrier()
     if rank == 0:
         print(f"RING_ATTENTION_OK world={W} S={S}")
