@@ -315,6 +315,12 @@ class RetNet(_Recurrent):
         S = self.gamma * S + k[:, :, None] * v[:, None, :]
         return torch.einsum("bd,bde->be", q, S), S
 
+    def forward_parallel(self, x):
+        """Training form: (Q K^T * decay mask) V per sequence, no loop over time (``sequence_scans.retention``)."""
+        from .sequence_scans import retention
+        q, k, v = self.q(x), self.k(x) / math.sqrt(x.shape[-1]), self.v(x)
+        return torch.stack([retention(q[b], k[b], v[b], self.gamma) for b in range(x.shape[0])])
+
 
 class GLA(_Recurrent):
     """Gated linear attention: data-dependent per-key decay alpha_t in (0, 1)."""
@@ -332,6 +338,12 @@ class GLA(_Recurrent):
         alpha = torch.sigmoid(self.a(xt))
         S = alpha[:, :, None] * S + k[:, :, None] * v[:, None, :]
         return torch.einsum("bd,bde->be", q, S), S
+
+    def forward_parallel(self, x):
+        from .sequence_scans import gated_linear_attention
+        q, k, v = self.q(x), self.k(x) / math.sqrt(x.shape[-1]), self.v(x)
+        alpha = torch.sigmoid(self.a(x))
+        return torch.stack([gated_linear_attention(q[b], k[b], v[b], alpha[b]) for b in range(x.shape[0])])
 
 
 class DeltaNet(_Recurrent):
@@ -354,6 +366,14 @@ class DeltaNet(_Recurrent):
         S = S + beta[:, :, None] * k[:, :, None] * (v - pred)[:, None, :]
         return torch.einsum("bd,bde->be", q, S), S
 
+    def forward_parallel(self, x):
+        """Training form: the written values come from one unit-triangular solve per sequence."""
+        from .sequence_scans import delta_rule
+        q, v = self.q(x), self.v(x)
+        k = F.normalize(self.k(x), dim=-1)
+        beta = torch.sigmoid(self.beta(x))[..., 0]
+        return torch.stack([delta_rule(q[b], k[b], v[b], beta[b]) for b in range(x.shape[0])])
+
 
 class HGRN(_Recurrent):
     """Hierarchically gated recurrence: h_t = f_t h_{t-1} + (1 - f_t) c_t, y_t = o_t * h_t, with a
@@ -371,6 +391,88 @@ class HGRN(_Recurrent):
         f = self.lb + (1 - self.lb) * torch.sigmoid(self.f(xt))
         h = f * h + (1 - f) * F.silu(self.c(xt))
         return torch.sigmoid(self.o(xt)) * h, h
+
+    def forward_parallel(self, x):
+        from .sequence_scans import hgrn
+        f = self.lb + (1 - self.lb) * torch.sigmoid(self.f(x))
+        h = hgrn(f.transpose(0, 1), F.silu(self.c(x)).transpose(0, 1)).transpose(0, 1)      # the scan runs along dim 0
+        return torch.sigmoid(self.o(x)) * h
+
+
+class Mamba2(nn.Module):
+    """Mamba-2 mixer: heads of width ``head_dim`` share ONE scalar decay per step (a_t = exp(-softplus(dt_t) e^{A_log})),
+    with input-dependent B_t, C_t of size ``d_state`` shared by all heads. ``forward`` is the quadratic dual form
+    (``sequence_scans.ssd_dual``: masked (C B^T * L) X, matrix products only); ``step`` is the recurrence a decoder runs."""
+
+    def __init__(self, d_model, d_state=16, head_dim=16, expand=2):
+        super().__init__()
+        d_in = expand * d_model
+        if d_in % head_dim:
+            raise ValueError("expand * d_model must be a multiple of head_dim")
+        self.d_in, self.n_heads, self.hd, self.ds = d_in, d_in // head_dim, head_dim, d_state
+        self.in_proj = nn.Linear(d_model, 2 * d_in + 2 * d_state + self.n_heads, bias=False)
+        self.A_log = nn.Parameter(torch.zeros(self.n_heads))
+        self.dt_bias = nn.Parameter(torch.full((self.n_heads,), -1.0))
+        self.D = nn.Parameter(torch.ones(self.n_heads))
+        self.out_proj = nn.Linear(d_in, d_model, bias=False)
+
+    def _split(self, x):
+        z, u, Bm, Cm, dt = torch.split(self.in_proj(x), [self.d_in, self.d_in, self.ds, self.ds, self.n_heads], -1)
+        dt = F.softplus(dt + self.dt_bias)
+        a = torch.exp(-dt * torch.exp(self.A_log))                 # per head and step, in (0, 1)
+        return z, u, Bm, Cm, dt, a
+
+    def forward(self, x):
+        from .sequence_scans import ssd_dual
+        Bsz, T, _ = x.shape
+        z, u, Bm, Cm, dt, a = self._split(x)
+        uh = u.view(Bsz, T, self.n_heads, self.hd)
+        ys = []
+        for b in range(Bsz):
+            heads = [ssd_dual(uh[b, :, h] * dt[b, :, h, None], a[b, :, h], Bm[b], Cm[b]) + self.D[h] * uh[b, :, h]
+                     for h in range(self.n_heads)]
+            ys.append(torch.cat(heads, -1))
+        return self.out_proj(torch.stack(ys) * F.silu(z))
+
+    def init_state(self, x):
+        return x.new_zeros(x.shape[0], self.n_heads, self.ds, self.hd)
+
+    def step(self, xt, state):
+        z, u, Bm, Cm, dt, a = self._split(xt[:, None])
+        z, u, Bm, Cm, dt, a = (t[:, 0] for t in (z, u, Bm, Cm, dt, a))
+        uh = u.view(-1, self.n_heads, self.hd)
+        state = a[:, :, None, None] * state + Bm[:, None, :, None] * (uh * dt[:, :, None])[:, :, None, :]
+        y = torch.einsum("bn,bhnp->bhp", Cm, state) + self.D[None, :, None] * uh
+        return self.out_proj(y.reshape(-1, self.d_in) * F.silu(z)), state
+
+
+class S5(nn.Module):
+    """S5 layer: ONE multi-input multi-output diagonal state space per layer (complex eigenvalues, |lambda| < 1),
+    evaluated by the parallel prefix scan in ``forward`` and by its recurrence in ``step``."""
+
+    def __init__(self, d_model, d_state=32):
+        super().__init__()
+        self.log_mag = nn.Parameter(torch.log(torch.linspace(0.05, 0.6, d_state)))     # -log|lambda|
+        self.phase = nn.Parameter(torch.linspace(0.0, math.pi, d_state))
+        self.B = nn.Parameter(torch.randn(d_state, d_model, 2) / math.sqrt(d_model))
+        self.C = nn.Parameter(torch.randn(d_model, d_state, 2) / math.sqrt(d_state))
+        self.D = nn.Parameter(torch.ones(d_model))
+
+    def _lam(self):
+        return torch.exp(torch.complex(-torch.exp(self.log_mag), self.phase))
+
+    def forward(self, x):
+        from .sequence_scans import s5_parallel_scan
+        lam, Bc, Cc = self._lam(), torch.view_as_complex(self.B), torch.view_as_complex(self.C)
+        return torch.stack([s5_parallel_scan(x[b].float(), lam, Bc, Cc) for b in range(x.shape[0])]).to(x.dtype) + self.D * x
+
+    def init_state(self, x):
+        return torch.zeros(x.shape[0], self.log_mag.shape[0], dtype=torch.complex64, device=x.device)
+
+    def step(self, xt, s):
+        lam, Bc, Cc = self._lam(), torch.view_as_complex(self.B), torch.view_as_complex(self.C)
+        s = lam * s + xt.float().to(torch.complex64) @ Bc.t()
+        return (s @ Cc.t()).real.to(xt.dtype) + self.D * xt, s
 
 
 class S4D(_Recurrent):

@@ -412,3 +412,22 @@ def test_sequence_scans_recurrent_and_parallel_forms_agree():
     assert torch.allclose(s12[:8], s8) and s12.numel() == 12
     bias = S.alibi_bias(s8, 5)
     assert bias.shape == (8, 5, 5) and bias[0, 3, 1] == -1.0 and bias[0, 1, 3] == float("-inf") and bias[3, 2, 2] == 0
+
+
+def test_zoo_layers_parallel_training_form_equals_the_decoding_recurrence():
+    from scirust_b200.nn import zoo
+    torch.manual_seed(0)
+    x = torch.randn(2, 19, 16)
+    for cls in (zoo.RetNet, zoo.GLA, zoo.DeltaNet, zoo.HGRN):
+        layer = cls(16)
+        assert torch.allclose(layer.forward_parallel(x), layer(x), atol=2e-5), cls.__name__
+    for layer in (zoo.Mamba2(16, d_state=8, head_dim=8), zoo.S5(16, d_state=12)):
+        par = layer(x)
+        st = layer.init_state(x)
+        seq = []
+        for t in range(x.shape[1]):
+            y, st = layer.step(x[:, t], st)
+            seq.append(y)
+        assert torch.allclose(par, torch.stack(seq, 1), atol=3e-5), type(layer).__name__
+        par.sum().backward()
+        assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in layer.parameters())
