@@ -169,6 +169,50 @@ class PipelineModel:
         self.last_losses = losses
         return total[0].detach().requires_grad_()      # Trainer calls .backward() on it: nothing is left to do
 
+    # ------------------------------------------------------------------ checkpoints
+    def save_checkpoint(self, directory, step: int, loss: float, lr: float, trainer=None):
+        """Every stage writes ``directory/step_N/stage_K`` (its layers, under their LOCAL indices, with the optimizer
+        state and fp32 masters when a trainer is given; atomic per stage); rank 0 writes ``pipeline.json`` with the
+        layer split once all stages are done, which is what marks the checkpoint complete."""
+        import json
+        from pathlib import Path
+        from ..io.checkpoint import save_sciagent_checkpoint
+        root = Path(directory) / f"step_{int(step)}"
+        root.mkdir(parents=True, exist_ok=True)
+        save_sciagent_checkpoint(self.stage, root / f"stage_{self.rank}", step, loss, lr, trainer=trainer,
+                                 extra_opt={"pipeline_stage": self.rank, "layers": [self.lo, self.hi]})
+        dist.barrier(group=self.group)
+        if self.rank == 0:
+            info = {"stages": self.world, "n_layers": self.cfg_full.n_layers, "micro_batches": self.micro_batches,
+                    "split": split_layers(self.cfg_full.n_layers, self.world), "step": int(step)}
+            (root / "pipeline.json").write_text(json.dumps(info, indent=2, sort_keys=True))
+        dist.barrier(group=self.group)
+        return root
+
+    def load_checkpoint(self, root, trainer=None) -> dict:
+        """Resume this stage from ``root`` (a ``step_N`` directory written by the same layer split)."""
+        import json
+        from pathlib import Path
+        from ..io.checkpoint import load_optimizer_state, load_sciagent_checkpoint
+        root = Path(root)
+        info = json.loads((root / "pipeline.json").read_text())
+        if info["stages"] != self.world or info["n_layers"] != self.cfg_full.n_layers:
+            raise ValueError(f"checkpoint was written by {info['stages']} stages over {info['n_layers']} layers")
+        _, meta = load_sciagent_checkpoint(root / f"stage_{self.rank}", model=self.stage)
+        if trainer is not None:
+            load_optimizer_state(self.stage, trainer, root / f"stage_{self.rank}")
+        return meta
+
+    @staticmethod
+    def latest(directory):
+        """Newest ``step_N`` directory that holds a complete pipeline checkpoint, or None."""
+        from pathlib import Path
+        d = Path(directory)
+        if not d.exists():
+            return None
+        done = [p for p in d.iterdir() if p.name.startswith("step_") and p.name[5:].isdigit() and (p / "pipeline.json").exists()]
+        return max(done, key=lambda p: int(p.name[5:])) if done else None
+
     # ------------------------------------------------------------------ hooks used by Trainer
     def global_grad_sumsq(self, out: torch.Tensor, scale: float = 1.0) -> None:
         ops.sumsq(self.flat_grad, out=out)

@@ -88,6 +88,23 @@ def main():
     if rank == P - 1:
         assert close(pm.stage.rms_final, full.rms_final)
         assert close(pm.stage.head_weight(), full.head_weight())
+    # checkpoint / resume: two steps, save, a fresh stage + trainer resumes and takes the third step; its weights are
+    # the bits of the run that took three steps without stopping (pm above)
+    ckpt = os.environ.get("SB_PP_CKPT")
+    if ckpt:
+        full2 = GQADecoder(cfg, device=dev, seed=11)
+        a = PipelineModel(cfg, device=dev, micro_batches=M)
+        a.load_from_full(full2)
+        ta = Trainer(a, tcfg)
+        for t in data[:2]:
+            last = ta.train_step(t)
+        root = a.save_checkpoint(ckpt, 2, float(last), tcfg.lr, trainer=ta)
+        assert PipelineModel.latest(ckpt) == root
+        b = PipelineModel(cfg, device=dev, micro_batches=M, seed=99)      # other initial weights: everything must come from disk
+        tb = Trainer(b, tcfg)
+        assert b.load_checkpoint(root, trainer=tb)["step"] == 2 and tb.step == 2
+        tb.train_step(data[2])
+        assert torch.equal(b.stage.flat, pm.stage.flat), "resumed pipeline stage differs from the uninterrupted run"
     dist.barrier()
     if rank == 0:
         print(f"PIPELINE_OK stages={P} micro={M} tied={tied} loss={pp_losses[-1]:.4f}")

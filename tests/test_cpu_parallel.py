@@ -196,13 +196,15 @@ def test_vocab_parallel_embedding_ce_argmax_on_gloo_ranks(world):
 
 
 @pytest.mark.parametrize("stages,tied,micro", [(2, 0, 4), (3, 1, 2)])
-def test_pipeline_parallel_1f1b_equals_single_process_accumulation_on_gloo_ranks(stages, tied, micro):
+def test_pipeline_parallel_1f1b_equals_single_process_accumulation_on_gloo_ranks(stages, tied, micro, tmp_path):
     """Layers split over 2 / 3 stages, 1F1B over the micro-batches, per-stage optimizer with a global gradient norm:
-    three steps end on the weights of the single-process run that accumulates the same micro-batches."""
+    three steps end on the weights of the single-process run that accumulates the same micro-batches; a run that is
+    checkpointed after two steps and resumed by fresh stages ends on the same bits."""
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={stages}", "--master-addr",
            "127.0.0.1", "--master-port", str(29670 + stages), os.path.join(ROOT, "tests", "mp", "mp_pipeline.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600,
-                       env=dict(os.environ, PYTHONPATH=ROOT, SB_PP_TIED=str(tied), SB_PP_MICRO=str(micro)))
+                       env=dict(os.environ, PYTHONPATH=ROOT, SB_PP_TIED=str(tied), SB_PP_MICRO=str(micro),
+                                SB_PP_CKPT=str(tmp_path / "pp")))
     assert r.returncode == 0 and "PIPELINE_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
 
