@@ -398,6 +398,109 @@ def cmd_lm(a):
     return EXIT_OK if last == last else EXIT_NUMERICAL
 
 
+_SEQ_LAYERS = {"deltanet": ("DeltaNet", "delta-rule linear attention (fast-weight recurrence)"),
+               "retnet": ("RetNet", "retention with decay 0.9 (recurrent form = parallel form)"),
+               "gla": ("GLA", "gated linear attention (data-dependent per-key decay)"),
+               "hgrn": ("HGRN", "hierarchically gated recurrence"),
+               "mamba": ("Mamba", "selective state space (input-dependent dt, B, C)"),
+               "mamba2": ("Mamba2", "Mamba-2: scalar decay per head, quadratic dual form"),
+               "rwkv": ("RWKVTimeMix", "RWKV time mixing (stabilised wkv recurrence)"),
+               "s5": ("S5", "S5: one MIMO diagonal state space, parallel prefix scan")}
+
+
+def cmd_seq_layer(a):
+    """``deltanet | retnet | gla | hgrn | mamba | mamba2 | rwkv | s5 [--seed N] [--steps S]``: train one sequence-mixing
+    layer to fit a fixed target sequence (x = sin(0.3 i - 1), target = cos(0.2 i), Adam lr 0.05) and report the MSE
+    reduction; where the layer has both forms, also the gap between the recurrence and the parallel form
+    (scirust-cli/src/nlp.rs: run_deltanet / run_retnet / run_gla / run_hgrn / run_mamba / run_rwkv)."""
+    import torch
+    from .nn import zoo
+    cls_name, what = _SEQ_LAYERS[a.cmd]
+    torch.manual_seed(a.seed)
+    T, d = 6, 8
+    kw = {"gamma": 0.9} if a.cmd == "retnet" else {"d_state": 4, "head_dim": 4} if a.cmd == "mamba2" else \
+        {"d_state": 8} if a.cmd in ("s5",) else {"d_state": 4} if a.cmd == "mamba" else {}
+    layer = getattr(zoo, cls_name)(d, **kw)
+    i = torch.arange(T * d, dtype=torch.float32)
+    x, target = torch.sin(i * 0.3 - 1.0).view(1, T, d), torch.cos(i * 0.2).view(1, T, d)
+    opt = torch.optim.Adam(layer.parameters(), lr=0.05)
+    fwd = layer.forward_parallel if hasattr(layer, "forward_parallel") else layer
+    first = last = float("nan")
+    for step in range(a.steps):
+        loss = ((fwd(x) - target) ** 2).sum()
+        if step == 0:
+            first = float(loss)
+        last = float(loss)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+    print(f"{cls_name} layer - deterministic (seed {a.seed})")
+    print(f"  {what}; d_model {d}, sequence length {T}; {a.steps} Adam steps")
+    print(f"  MSE to target: {first:.4f} -> {last:.4f}  ({100.0 * last / first:.1f}% of initial)")
+    if hasattr(layer, "forward_parallel"):
+        with torch.no_grad():
+            gap = float((layer.forward_parallel(x) - layer(x)).abs().max())
+        print(f"  recurrent form vs parallel form: max difference {gap:.2e}")
+    return 0
+
+
+def cmd_tt(a):
+    """``tt``: a tensor-train linear layer against the dense layer it replaces: parameter count and fit error."""
+    import torch
+    from .nn import zoo
+    torch.manual_seed(a.seed)
+    layer = zoo.TTLinear([4, 4, 4], [4, 4, 4], rank=a.rank)
+    dense = torch.nn.Linear(64, 64)
+    x = torch.randn(256, 64)
+    y = dense(x).detach()
+    opt = torch.optim.Adam(layer.parameters(), lr=0.02)
+    first = last = 0.0
+    for step in range(a.steps):
+        loss = ((layer(x) - y) ** 2).mean()
+        first = float(loss) if step == 0 else first
+        last = float(loss)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+    n_tt, n_dense = sum(p.numel() for p in layer.parameters()), sum(p.numel() for p in dense.parameters())
+    print(f"tensor-train linear 64 -> 64, modes 4x4x4, rank {a.rank}: {n_tt} parameters against {n_dense} dense "
+          f"({n_dense / n_tt:.1f}x fewer)")
+    print(f"  fit of a random dense layer: MSE {first:.4f} -> {last:.4f} in {a.steps} Adam steps")
+    return 0
+
+
+def cmd_search(a):
+    """``evo`` / ``cmaes``: minimise a test function (sphere, rosenbrock, rastrigin) without gradients."""
+    from . import search
+    f = search.OBJECTIVES[a.objective]
+    if a.cmd == "cmaes":
+        x, fx, hist = search.cma_es(f, a.dim, generations=a.generations, seed=a.seed)
+        name = "CMA-ES"
+    else:
+        x, fx, hist = search.evolution_strategy(f, a.dim, generations=a.generations, seed=a.seed)
+        name = "(mu + lambda) evolution strategy"
+    print(f"{name} on {a.objective} ({a.dim} dimensions, seed {a.seed}): best {hist[0]:.4g} -> {fx:.4g} "
+          f"after {len(hist)} generations")
+    print("  x* =", " ".join(f"{v:.4f}" for v in x[:8]), "..." if a.dim > 8 else "")
+    return 0
+
+
+def cmd_som(a):
+    """``som``: fit a self-organising map to three Gaussian clusters; quantisation and topographic error."""
+    import numpy as np
+    from . import search
+    rng = np.random.default_rng(a.seed)
+    centres = np.array([[0.2, 0.2], [0.8, 0.3], [0.5, 0.8]])
+    data = np.concatenate([c + 0.05 * rng.standard_normal((60, 2)) for c in centres])
+    som = search.SelfOrganizingMap(a.rows, a.cols, 2, seed=a.seed)
+    q0 = som.quantization_error(data)
+    som.fit(data, epochs=a.epochs, seed=a.seed)
+    print(f"self-organising map {a.rows} x {a.cols} on 180 points from 3 clusters (seed {a.seed})")
+    print(f"  quantisation error {q0:.4f} -> {som.quantization_error(data):.4f}; topographic error "
+          f"{som.topographic_error(data):.3f}")
+    return 0
+
+
 def cmd_certify(a):
     """IBP and CROWN output bounds of a seeded 4->8->3 ReLU MLP over an L-infinity box
     (scirust-cli/src/learning.rs:46-120)."""
@@ -616,6 +719,29 @@ def build_parser():
     lm.add_argument("--lr", type=float, default=0.05)
     lm.add_argument("--opt", default="adam")
     lm.set_defaults(fn=cmd_lm)
+    for name in _SEQ_LAYERS:
+        sq = sub.add_parser(name)
+        sq.add_argument("--seed", type=int, default=7)
+        sq.add_argument("--steps", type=int, default=150)
+        sq.set_defaults(fn=cmd_seq_layer)
+    tt = sub.add_parser("tt")
+    tt.add_argument("--seed", type=int, default=0)
+    tt.add_argument("--rank", type=int, default=4)
+    tt.add_argument("--steps", type=int, default=200)
+    tt.set_defaults(fn=cmd_tt)
+    for name in ("evo", "cmaes"):
+        sr = sub.add_parser(name)
+        sr.add_argument("--objective", default="rosenbrock", choices=["sphere", "rosenbrock", "rastrigin"])
+        sr.add_argument("--dim", type=int, default=5)
+        sr.add_argument("--generations", type=int, default=300)
+        sr.add_argument("--seed", type=int, default=0)
+        sr.set_defaults(fn=cmd_search)
+    so = sub.add_parser("som")
+    so.add_argument("--rows", type=int, default=6)
+    so.add_argument("--cols", type=int, default=6)
+    so.add_argument("--epochs", type=int, default=20)
+    so.add_argument("--seed", type=int, default=0)
+    so.set_defaults(fn=cmd_som)
     ce = sub.add_parser("certify")
     ce.add_argument("--seed", type=int, default=1)
     ce.add_argument("--eps", type=float, default=0.05)

@@ -431,3 +431,32 @@ def test_zoo_layers_parallel_training_form_equals_the_decoding_recurrence():
         assert torch.allclose(par, torch.stack(seq, 1), atol=3e-5), type(layer).__name__
         par.sum().backward()
         assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in layer.parameters())
+
+
+def test_cli_sequence_layer_search_and_som_commands(capsys):
+    from scirust_b200 import cli, search
+    import numpy as np
+    for cmd in ("retnet", "deltanet", "gla", "hgrn", "mamba", "mamba2", "rwkv", "s5"):
+        assert cli.run([cmd, "--steps", "25", "--seed", "3"]) == 0
+        out = capsys.readouterr().out
+        first, last = (float(v) for v in out.split("MSE to target:")[1].split("(")[0].replace("->", " ").split())
+        assert last < first, cmd
+        if "recurrent form vs parallel form" in out:
+            assert float(out.rsplit("max difference", 1)[1]) < 1e-4
+    assert cli.run(["tt", "--steps", "30"]) == 0 and "fewer" in capsys.readouterr().out
+    assert cli.run(["cmaes", "--objective", "rosenbrock", "--dim", "4", "--generations", "250"]) == 0
+    assert cli.run(["evo", "--objective", "sphere", "--generations", "60"]) == 0
+    assert cli.run(["som", "--epochs", "8"]) == 0
+    capsys.readouterr()
+    x, fx, hist = search.cma_es(search.rosenbrock, 4, generations=300, seed=1)
+    assert fx < 1e-8 and np.allclose(x, 1.0, atol=1e-3) and hist[-1] <= hist[0]
+    x2, fx2, _ = search.cma_es(search.rosenbrock, 4, generations=300, seed=1)
+    assert fx2 == fx and np.array_equal(x, x2)                     # deterministic in the seed
+    _, fe, he = search.evolution_strategy(search.sphere, 6, generations=120, seed=2)
+    assert fe < 1e-6 and all(b <= a for a, b in zip(he, he[1:]))    # elitist: never worse
+    rng = np.random.default_rng(0)
+    data = np.concatenate([c + 0.04 * rng.standard_normal((40, 2)) for c in ([0.2, 0.2], [0.8, 0.7])])
+    som = search.SelfOrganizingMap(5, 5, 2, seed=0)
+    q0 = som.quantization_error(data)
+    som.fit(data, epochs=10)
+    assert som.quantization_error(data) < 0.5 * q0 and som.topographic_error(data) < 0.3
