@@ -485,6 +485,43 @@ def cmd_search(a):
     return 0
 
 
+def cmd_pinn(a):
+    """``pinn``: a physics-informed network for u'' + pi^2 u = 0 on [0, 1] with u(0) = 0, u'(0) = pi (solution
+    sin(pi x)): data loss on the two boundary conditions plus the mean squared residual at collocation points
+    (``nn.loss.PINNLoss``); derivatives of the network by automatic differentiation."""
+    import math
+    import torch
+    from .nn.loss import PINNLoss
+    torch.manual_seed(a.seed)
+    net = torch.nn.Sequential(torch.nn.Linear(1, 24), torch.nn.Tanh(), torch.nn.Linear(24, 24), torch.nn.Tanh(),
+                              torch.nn.Linear(24, 1))
+    opt = torch.optim.Adam(net.parameters(), lr=5e-3)
+    lossf = PINNLoss(residual_weight=a.weight)
+    xs = torch.linspace(0, 1, 64).reshape(-1, 1).requires_grad_()
+    x0 = torch.zeros(1, 1, requires_grad=True)
+    first = last = 0.0
+    for step in range(a.steps):
+        u = net(xs)
+        du = torch.autograd.grad(u.sum(), xs, create_graph=True)[0]
+        d2u = torch.autograd.grad(du.sum(), xs, create_graph=True)[0]
+        u0 = net(x0)
+        du0 = torch.autograd.grad(u0.sum(), x0, create_graph=True)[0]
+        pred = torch.cat([u0, du0], 1)
+        loss = lossf(pred, torch.tensor([[0.0, math.pi]]), d2u + math.pi ** 2 * u)
+        loss = (loss if isinstance(loss, torch.Tensor) else loss.t).reshape(())
+        first = float(loss) if step == 0 else first
+        last = float(loss)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+    with torch.no_grad():
+        grid = torch.linspace(0, 1, 101).reshape(-1, 1)
+        err = float((net(grid) - torch.sin(math.pi * grid)).abs().max())
+    print(f"physics-informed network for u'' + pi^2 u = 0, u(0) = 0, u'(0) = pi (seed {a.seed})")
+    print(f"  loss {first:.4f} -> {last:.6f} in {a.steps} Adam steps; max |u - sin(pi x)| on [0, 1] = {err:.4f}")
+    return 0
+
+
 def cmd_som(a):
     """``som``: fit a self-organising map to three Gaussian clusters; quantisation and topographic error."""
     import numpy as np
@@ -736,6 +773,11 @@ def build_parser():
         sr.add_argument("--generations", type=int, default=300)
         sr.add_argument("--seed", type=int, default=0)
         sr.set_defaults(fn=cmd_search)
+    pn = sub.add_parser("pinn")
+    pn.add_argument("--seed", type=int, default=0)
+    pn.add_argument("--steps", type=int, default=1500)
+    pn.add_argument("--weight", type=float, default=0.1)
+    pn.set_defaults(fn=cmd_pinn)
     so = sub.add_parser("som")
     so.add_argument("--rows", type=int, default=6)
     so.add_argument("--cols", type=int, default=6)

@@ -448,6 +448,9 @@ def test_cli_sequence_layer_search_and_som_commands(capsys):
     assert cli.run(["evo", "--objective", "sphere", "--generations", "60"]) == 0
     assert cli.run(["som", "--epochs", "8"]) == 0
     capsys.readouterr()
+    assert cli.run(["pinn", "--steps", "400"]) == 0
+    out = capsys.readouterr().out
+    assert float(out.rsplit("=", 1)[1]) < 0.5 and "loss" in out
     x, fx, hist = search.cma_es(search.rosenbrock, 4, generations=300, seed=1)
     assert fx < 1e-8 and np.allclose(x, 1.0, atol=1e-3) and hist[-1] <= hist[0]
     x2, fx2, _ = search.cma_es(search.rosenbrock, 4, generations=300, seed=1)
