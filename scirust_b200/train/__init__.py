@@ -1,2 +1,2 @@
 from .trainer import Trainer, TrainerConfig  # noqa: F401
-from .schedule import WarmupCosineSchedule  # noqa: F401
+from .schedule import ConstantSchedule, WarmupCosineSchedule  # noqa: F401
