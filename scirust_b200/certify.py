@@ -14,9 +14,9 @@ Counterparts in the reference: scirust-core/src/nn/ibp.rs (``Interval``, ``IbpLi
 """
 from __future__ import annotations
 
-import math
-
 import torch
+
+from .conformal import ConformalClassifier  # noqa: F401  (the guard's calibrated threshold rule)
 
 
 class Interval:
@@ -121,30 +121,6 @@ def crown_bounds(l1: IbpLinear, l2: IbpLinear, box: Interval) -> Interval:
             else:
                 lo[o] = centre - rad
     return Interval(torch.minimum(lo, hi), torch.maximum(lo, hi))
-
-
-class ConformalClassifier:
-    """Split conformal classification with the score ``1 - p[true class]``."""
-
-    def __init__(self, qhat: float):
-        self.qhat = qhat
-
-    @staticmethod
-    def calibrate(cal_probs, cal_labels, alpha: float) -> "ConformalClassifier":
-        probs = torch.as_tensor(cal_probs, dtype=torch.float32)
-        labels = torch.as_tensor(cal_labels, dtype=torch.int64)
-        n = probs.shape[0]
-        scores = 1.0 - probs.gather(1, labels[:, None]).squeeze(1)
-        k = min(n, max(1, math.ceil((n + 1) * (1.0 - alpha))))
-        qhat = float(torch.sort(scores).values[k - 1])
-        return ConformalClassifier(qhat)
-
-    def predict_set(self, probs):
-        p = torch.as_tensor(probs, dtype=torch.float32)
-        return [int(i) for i in torch.nonzero(p >= 1.0 - self.qhat).reshape(-1)]
-
-    def covers(self, probs, y_true: int) -> bool:
-        return y_true in self.predict_set(probs)
 
 
 class StatisticalGuard:
