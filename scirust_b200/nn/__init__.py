@@ -9,3 +9,7 @@ from .transformer import (MultiHeadAttention, TransformerBlock, TransformerEncod
 from .vision import ResidualBlock, ResNet, resnet18, resnet34, MnistCNN, CifarCNN, ViT  # noqa: F401
 from .kv_cache import (AttentionBackend, PlainKvCache, PagedKvCache, QuantKvCache, ElasticKvCache, LatentKvCache,  # noqa: F401
                        TieredKvCache)
+from .audio import AudioEncoder, ctc_loss  # noqa: F401
+from .contracts import CertifiedModule, ValueBoundedContract  # noqa: F401
+from .ensemble import DeepEnsemble  # noqa: F401
+from .sampling import SamplingConfig, sample_token  # noqa: F401
