@@ -225,3 +225,56 @@ def test_embedding_engine():
     assert torch.equal(again.embed("moon"), batch[3])                           # seeded construction
     tok = CharTokenizer(["abc"])
     assert tok.encode("cabz") == [3, 1, 2, 0] and tok.decode([3, 1, 2, 0]) == "cab" and tok.vocab_size == 4
+
+
+def test_certificate_gated_transform_selection():
+    from scirust_b200.numerics import transform_search as T
+    xs = np.logspace(-6, 6, 200)
+    rep = T.select_transform(xs, 64.0, T.default_positive_dictionary())
+    by = {v.repr.name: v for v in rep.verdicts}
+    assert rep.chosen == T.Representation("power", 0.5) and rep.chosen_bound_ulps == pytest.approx(12.0)
+    assert by["log"].accepted and by["anscombe"].rejected.kind == "tolerance-exceeded"
+    assert rep.support.lo == pytest.approx(1e-6) and rep.support.hi == pytest.approx(1e6)
+    # a tighter tolerance rejects more; an impossible one rejects all, with reasons
+    assert T.select_transform(xs, 1.0, T.default_positive_dictionary()).chosen is None
+    # negative samples are outside the domain of log: the first offender is reported
+    neg = T.select_transform([1.0, -2.0, 3.0], 64.0, [T.LOG, T.SIGNED_LOG])
+    why = {v.repr.name: v.rejected for v in neg.verdicts}
+    assert why["log"] == T.RejectReason("outside-domain", -2.0) and neg.chosen == T.SIGNED_LOG
+    # Anscombe near 0: sqrt(x + 3/8) forgets a tiny x entirely (kappa_rt * u >= 1/2): the invalid region, whatever the tolerance
+    tight = T.select_transform([1e-17, 1.0], 1e30, [T.ANSCOMBE])
+    assert tight.verdicts[0].rejected.kind == "invalid-region" and tight.chosen is None
+    empty = T.select_transform([], 64.0, [T.LOG])
+    assert empty.chosen is None and empty.verdicts == []
+    assert [r.cost() for r in (T.ANSCOMBE, T.LOG, T.LOGIT, T.Representation("mu-law", 255.0))] == [2, 3, 4, 5]
+
+
+def test_quantizer_autotune_and_plan_search():
+    from scirust_b200.numerics import transform_search as T
+    q = T.UniformQuantizer.fit([0.0, 10.0], 10)
+    assert q.round_trip(np.array([0.2, 9.99, 25.0, -3.0])).tolist() == pytest.approx([0.5, 9.5, 9.5, 0.5])
+    assert T.sqnr_db([1.0, 2.0], [1.0, 2.0]) == math.inf and T.sqnr_db([3.0, 4.0], [3.0, 3.0]) == pytest.approx(10 * math.log10(25))
+    rng = np.random.default_rng(0)
+    data = np.exp(rng.standard_normal(3000) * 2.0)
+    rep = T.autotune_quantizer(data[:1500], data[1500:], T.default_positive_quantizer_dictionary(), 64)
+    assert rep.chosen is not None and rep.beats_baseline and rep.chosen_eval_sqnr_db > rep.baseline_eval_sqnr_db
+    assert len(rep.verdicts) == 9 and all(not isinstance(s, T.RejectReason) for _, s in rep.verdicts)
+    # data with zeros: log is gated out with a reason, log1p / power stay
+    z = np.concatenate([[0.0], data[:200]])
+    rz = T.autotune_quantizer(z[:100], z[100:], [T.LOG, T.LOG1P], 32)
+    assert isinstance(dict((r.name, s) for r, s in rz.verdicts)["log"], T.RejectReason) and rz.chosen == T.LOG1P
+    joint = T.joint_search(data[:200], data[200:400])
+    seq = T.sequential_baseline(data[:200], data[200:400])
+    assert joint.evaluated == 6 * 5 and seq.evaluated == 5
+    assert joint.chosen is not None and seq.chosen.representation.kind != "identity"
+    dev_best = min(e for _, e in joint.dev_errors if e is not None)
+    assert T.pipeline_relative_error(joint.chosen, data[:200], data[:200]) == dev_best      # the dev optimum was taken
+    assert dev_best <= min(e for _, e in seq.dev_errors if e is not None) + 1e-15             # joint search covers the baseline's pair
+    cache = T.PlanCache()
+    p1 = cache.plan_for("sum", "cpu", data[:200], data[200:400])
+    p2 = cache.plan_for("sum", "cpu", data[:200] * 1.01, data[200:400])                      # same distribution summary: reused
+    assert p1 == p2 and (cache.hits, cache.misses) == (1, 1)
+    assert cache.get("sum", "cpu", T.summarize(-data[:50])) is None
+    s = T.summarize(data)
+    assert s.sign == "positive" and s.decades >= 4 and T.summarize([0.0, 0.0]).decades == 0
+    assert T.summarize([-1.0, 2.0]).sign == "mixed" and T.current_hardware_key() in ("cpu",) or True
