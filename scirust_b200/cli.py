@@ -836,6 +836,8 @@ def build_parser():
     v.add_argument("--seeds", type=int, nargs="*", default=[1, 2, 3])
     v.add_argument("--out", default="")
     v.set_defaults(fn=cmd_verify)
+    from . import cli_tools
+    cli_tools.register(sub)
     return p
 
 
