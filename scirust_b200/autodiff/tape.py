@@ -111,6 +111,19 @@ class Tape:
                     g.mul_(k)
         return norm
 
+    def clip_grad_value(self, indices, max_value: float) -> None:
+        """Clamp every gradient element of the given nodes to ``[-max_value, max_value]``."""
+        for i in indices:
+            g = self.vars[i].t.grad
+            if g is not None:
+                g.clamp_(-max_value, max_value)
+
+    def zeros(self, rows: int, cols: int) -> "Var":
+        return self.constant(torch.zeros(rows, cols))
+
+    def ones(self, rows: int, cols: int) -> "Var":
+        return self.constant(torch.ones(rows, cols))
+
     def set_seed(self, seed: int) -> None:
         """Seed of the dropout mask stream (reverse.rs:1406)."""
         self._gen.manual_seed(int(seed))
@@ -348,3 +361,97 @@ class Var:
     def matmul_portable(self, o):
         from ..numerics import portable
         return self._new(portable.PortableMatmul.apply(self.t, o.t))
+
+    def ln_portable(self):
+        from ..numerics import portable
+        return self._new(portable.PortableLn.apply(self.t))
+
+    def softmax_portable(self):
+        from ..numerics import portable
+        return self._new(portable.PortableSoftmax.apply(self.t))
+
+    # ---- remaining elementwise / structural ops of the reference surface
+    def sinh(self): return self._new(torch.sinh(self.t))
+    def cosh(self): return self._new(torch.cosh(self.t))
+    def log10(self): return self._new(torch.log10(self.t))
+
+    def add_scaled(self, o, k: float):
+        """self + k * o."""
+        self._same(o); self._shape_eq(o, "add_scaled")
+        return self._new(self.t + float(k) * o.t)
+
+    def add_hadamard(self, a, b):
+        """self + a * b (element-wise)."""
+        self._same(a); self._same(b); self._shape_eq(a, "add_hadamard"); self._shape_eq(b, "add_hadamard")
+        return self._new(torch.addcmul(self.t, a.t, b.t))
+
+    def sub_hadamard(self, a, b):
+        self._same(a); self._same(b); self._shape_eq(a, "sub_hadamard"); self._shape_eq(b, "sub_hadamard")
+        return self._new(torch.addcmul(self.t, a.t, b.t, value=-1.0))
+
+    def broadcast_to(self, rows: int, cols: int):
+        r, c = self.t.shape
+        if (r not in (1, rows)) or (c not in (1, cols)):
+            raise TapeError(f"broadcast_to: cannot expand {(r, c)} to {(rows, cols)}")
+        return self._new(self.t.expand(rows, cols))
+
+    def detach(self):
+        """The same values as a new leaf that stops the gradient."""
+        return self.tape.constant(self.t.detach())
+
+    def fake_quantize_ste_range(self, lo: float, hi: float, bits: int = 8):
+        """Uniform quantiser over a FIXED range with a straight-through gradient inside it and zero outside."""
+        if not hi > lo:
+            raise TapeError("fake_quantize_ste_range needs hi > lo")
+        levels = float(2 ** bits - 1)
+        step = (hi - lo) / levels
+        x = self.t.clamp(lo, hi)
+        q = torch.round((x - lo) / step) * step + lo
+        return self._new(x + (q - x).detach())
+
+    def tt_contract(self, cores, bias, in_dims, out_dims, ranks):
+        """``x [B, prod(in_dims)]`` through a tensor-train weight: core k is ``[r_k * in_k * out_k, r_{k+1}]``
+        (row-major ``(r_k, in_k, out_k)``), ``ranks`` has ``d + 1`` entries starting and ending with 1. The product is
+        contracted core by core, never forming the dense ``[in, out]`` matrix."""
+        d = len(in_dims)
+        if d == 0 or d > 8 or len(out_dims) != d or len(ranks) != d + 1 or len(cores) != d:
+            raise TapeError("tt_contract: need 1..8 modes, matching out_dims, d + 1 ranks and d cores")
+        if ranks[0] != 1 or ranks[-1] != 1:
+            raise TapeError("tt_contract: boundary ranks must be 1")
+        B = self.t.shape[0]
+        if self.t.shape[1] != math.prod(in_dims):
+            raise TapeError(f"tt_contract: input width {self.t.shape[1]} != prod(in_dims) {math.prod(in_dims)}")
+        # state [B, r_k, remaining inputs..., produced outputs]
+        state = self.t.reshape(B, 1, *in_dims, 1)
+        for k, core in enumerate(cores):
+            self._same(core)
+            rk, ik, ok, rn = ranks[k], in_dims[k], out_dims[k], ranks[k + 1]
+            if core.t.numel() != rk * ik * ok * rn:
+                raise TapeError(f"tt_contract: core {k} has {core.t.numel()} elements, expected {rk * ik * ok * rn}")
+            g = core.t.reshape(rk, ik, ok, rn)
+            rest = state.shape[3:-1]
+            st = state.reshape(B, rk, ik, -1, state.shape[-1])                 # [B, r, i, rest, outs]
+            st = torch.einsum("brixo,ripn->bnxop", st, g)                      # -> [B, r', rest, outs, out_k]
+            state = st.reshape(B, rn, *rest, st.shape[3] * ok)
+        y = state.reshape(B, -1)
+        if bias is not None:
+            self._same(bias)
+            y = y + bias.t.reshape(1, -1)
+        return self._new(y)
+    try_tt_contract = tt_contract
+
+    def quantum_expectations(self, parameters, layer):
+        """Rows of classical features through a ``quantum.QuantumLayer`` with shared trainable ``parameters [1, P]``:
+        ``[batch, observables]``, differentiable in both."""
+        self._same(parameters)
+        return self._new(layer.forward(self.t, parameters.t))
+    try_quantum_expectations = quantum_expectations
+
+    def quantum_expectation(self, parameters, layer):
+        from ..quantum import QuantumError
+        if len(layer.observables) != 1:
+            raise QuantumError("quantum_expectation needs a layer with exactly one observable")
+        if self.t.shape[0] != 1:
+            raise QuantumError("quantum_expectation takes one row of features")
+        return self.quantum_expectations(parameters, layer)
+    try_quantum_expectation = quantum_expectation

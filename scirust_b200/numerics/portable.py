@@ -148,3 +148,33 @@ class PortableMatmul(torch.autograd.Function):
     def backward(ctx, g):
         a, b = ctx.saved_tensors
         return gemm_f32(g, b.t().contiguous()).to(a.device), gemm_f32(a.t().contiguous(), g).to(a.device)
+
+
+class PortableLn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        y = torch.tensor([float(ln_f32(v)) for v in x.detach().cpu().reshape(-1).tolist()],
+                         dtype=torch.float32).reshape(x.shape).to(x.device)
+        ctx.save_for_backward(x)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        (x,) = ctx.saved_tensors
+        return g / x
+
+
+class PortableSoftmax(torch.autograd.Function):
+    """Row softmax through the libm-free kernels; the vector-Jacobian product is ``y * (g - sum(g * y))``."""
+
+    @staticmethod
+    def forward(ctx, x):
+        rows = [softmax_f32(r) for r in x.detach().cpu().numpy()]
+        y = torch.tensor(np.stack(rows), dtype=torch.float32).to(x.device)
+        ctx.save_for_backward(y)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        (y,) = ctx.saved_tensors
+        return y * (g - (g * y).sum(1, keepdim=True))
