@@ -249,3 +249,67 @@ class TensorND:
 
     def to(self, device): return TensorND(self.t.to(device))
     def __repr__(self): return f"TensorND{self.shape}"
+
+
+class Tensor3D:
+    """A ``(batch, seq_len, d_model)`` view over a 2-D ``(batch * seq_len, d_model)`` tensor: the shape convention of
+    the sequence layers (scirust-core/src/tensor/tensor3d.rs:7-80)."""
+
+    def __init__(self, inner: Tensor, batch: int, seq_len: int, d_model: int):
+        if inner.rows != batch * seq_len or inner.cols != d_model:
+            raise ValueError(f"Tensor3D: a {inner.shape} matrix is not ({batch} * {seq_len}, {d_model})")
+        self.inner, self.batch, self.seq_len, self.d_model = inner, batch, seq_len, d_model
+
+    @staticmethod
+    def zeros(batch: int, seq_len: int, d_model: int) -> "Tensor3D":
+        return Tensor3D(Tensor.zeros(batch * seq_len, d_model), batch, seq_len, d_model)
+
+    @property
+    def shape(self):
+        return self.batch, self.seq_len, self.d_model
+
+    def as_nd(self) -> "TensorND":
+        return TensorND(self.inner.t.reshape(self.batch, self.seq_len, self.d_model))
+
+
+class Var3D:
+    """The tape counterpart of ``Tensor3D``: a ``Var`` plus its 3-D interpretation."""
+
+    def __init__(self, var, batch: int, seq_len: int, d_model: int):
+        if tuple(var.t.shape) != (batch * seq_len, d_model):
+            raise ValueError(f"Var3D: a {tuple(var.t.shape)} variable is not ({batch} * {seq_len}, {d_model})")
+        self.var, self.batch, self.seq_len, self.d_model = var, batch, seq_len, d_model
+
+    @staticmethod
+    def input_3d(tape, t3d: Tensor3D) -> "Var3D":
+        return Var3D(tape.input(t3d.inner), t3d.batch, t3d.seq_len, t3d.d_model)
+
+    from_var = classmethod(lambda cls, var, b, s, d: cls(var, b, s, d))
+
+    @property
+    def shape(self):
+        return self.batch, self.seq_len, self.d_model
+
+    def as_var(self):
+        return self.var
+
+
+def broadcast_get(data, shape, idx) -> float:
+    """Element of a row-major array read with broadcasting: axes of extent 1 ignore their index
+    (scirust-core/src/tensor/broadcast.rs:23)."""
+    off, stride = 0, 1
+    for extent, i in zip(reversed(list(shape)), reversed(list(idx))):
+        off += (0 if extent == 1 else i) * stride
+        stride *= extent
+    return float(data[off])
+
+
+def unbroadcast(grad: "torch.Tensor", shape) -> "torch.Tensor":
+    """Sum a gradient back to the shape it was broadcast from (leading axes and axes of extent 1)."""
+    g = grad
+    while g.dim() > len(shape):
+        g = g.sum(0)
+    for ax, extent in enumerate(shape):
+        if extent == 1 and g.shape[ax] != 1:
+            g = g.sum(ax, keepdim=True)
+    return g

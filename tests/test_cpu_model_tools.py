@@ -278,3 +278,46 @@ def test_quantizer_autotune_and_plan_search():
     s = T.summarize(data)
     assert s.sign == "positive" and s.decades >= 4 and T.summarize([0.0, 0.0]).decades == 0
     assert T.summarize([-1.0, 2.0]).sign == "mixed" and T.current_hardware_key() in ("cpu",) or True
+
+
+def test_pinned_pool_uploader_and_tensor3d():
+    from scirust_b200.autodiff import Tape
+    from scirust_b200.tensor import Tensor, Tensor3D, Var3D, broadcast_get, unbroadcast
+    from scirust_b200.utils import pinned as PN
+    buf = PN.PinnedBuffer(4)
+    assert buf.as_tensor().tolist() == [0.0] * 4 and buf.is_aligned() and buf.len_bytes() == 16 and len(buf) == 4
+    assert buf.layout() in (PN.MemoryLayout.CPU, PN.MemoryLayout.PINNED) and PN.PinnedBuffer(0).is_empty()
+    with pytest.raises(PN.PinError, match="too large"):
+        PN.PinnedBuffer(1 << 60, torch.int64)
+    pool = PN.PinnedPool(2, 8)
+    first, second = pool.borrow(), pool.borrow()
+    assert pool.available() == 0 and pool.capacity() == 2 and {first.index, second.index} == {0, 1}
+    with pytest.raises(PN.PinError, match="allocation failed"):
+        pool.borrow()
+    first.as_tensor()[0] = 7.0
+    pool.release(first)
+    assert pool.available() == 1 and float(pool.borrow().as_tensor()[0]) == 7.0       # storage is reused, not reallocated
+    with pytest.raises(PN.PinError, match="does not belong"):
+        pool.release(first)                                                            # double release
+    with pytest.raises(PN.PinError, match="does not belong"):
+        PN.PinnedPool(1, 8).release(second)                                            # another pool's buffer
+    with pytest.raises(PN.PinError, match="released"):
+        first.as_tensor()
+    up = PN.DoubleBufferedUploader(16, torch.float32, "cpu")
+    a, b = up.submit(torch.arange(6.0).reshape(2, 3)), up.submit(torch.ones(4))
+    with pytest.raises(PN.PinError):
+        up.submit(torch.zeros(2))                                                      # both slots in flight
+    assert up.take(a).tolist() == [[0, 1, 2], [3, 4, 5]] and up.take(b).tolist() == [1.0] * 4
+    assert up.take is not None and up.pool.available() == 2
+    with pytest.raises(PN.PinError):
+        up.take(a)
+    with pytest.raises(PN.PinError):
+        PN.stage_to_device(torch.zeros(32), up.pool.borrow(), "cpu")
+    t3 = Tensor3D.zeros(2, 3, 4)
+    assert t3.shape == (2, 3, 4) and t3.as_nd().shape == (2, 3, 4)
+    with pytest.raises(ValueError):
+        Tensor3D(Tensor.zeros(5, 4), 2, 3, 4)
+    v3 = Var3D.input_3d(Tape(), t3)
+    assert v3.shape == (2, 3, 4) and tuple(v3.as_var().t.shape) == (6, 4)
+    assert broadcast_get([1, 2, 3], [1, 3], [5, 2]) == 3.0 and broadcast_get([1, 2, 3, 4], [2, 2], [1, 0]) == 3.0
+    assert unbroadcast(torch.ones(4, 2, 3), (1, 3)).tolist() == [[8.0, 8.0, 8.0]] and unbroadcast(torch.ones(2, 3), (2, 3)).shape == (2, 3)
