@@ -51,6 +51,8 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"])
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--tp-vocab-parallel", action="store_true",
+                    help="tensor parallel only: shard the embedding table, LM head and cross-entropy over the vocabulary too")
     ap.add_argument("--mode", default="all", choices=["all", "train", "infer"],
                     help="train: training tokens/s only; infer: decode tokens/s and TTFT only; all: both")
     ap.add_argument("--infer-model", default="llama3_8b")
@@ -164,7 +166,7 @@ def train_arm(args, rank, local_rank, world, dev):
         if tp_mode:
             # tensor parallel (sequence-sharded activations): every rank sees the same batch; the column- and
             # row-parallel products run as all-gather -> GEMM and GEMM -> reduce-scatter kernels over peer memory
-            from scirust_b200.models.sciagent_tp import TPDecoder
+            from scirust_b200.models.sciagent_tp import TPDecoder, TPDecoderVocabParallel
             from scirust_b200.parallel.tensor_parallel import TPContext
 
             def build_trainer(comm):  # noqa: F811
@@ -173,7 +175,7 @@ def train_arm(args, rank, local_rank, world, dev):
                 sym = ((2 * cfg.n_layers + 4) * (B * S // world) + (2 * cfg.n_layers + 2) * B * S) * cfg.d_model * 2
                 sym += 64 << 20
                 tp = TPContext(dist.group.WORLD, B * S, cfg.d_model, sym_bytes=sym, backend=comm)
-                m = TPDecoder(cfg, tp, seed=1234)
+                m = (TPDecoderVocabParallel if args.tp_vocab_parallel else TPDecoder)(cfg, tp, seed=1234)
                 return Trainer(m, TrainerConfig(lr=3e-4, weight_decay=0.1, max_grad_norm=1.0))
 
         trainer = None

@@ -273,3 +273,149 @@ class TPDecoder(nn.Module):
         dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.tp.group)
         out += ops.sumsq(self.flat_grad[rs:])
         return out
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# Vocabulary-parallel variant: the embedding table and the LM head are sharded over the vocabulary axis as well, so no
+# rank holds the whole table, a [tokens, V] logit matrix or a full-vocabulary gradient.
+# ------------------------------------------------------------------------------------------------------------------
+class _VPEmbedFn(torch.autograd.Function):
+    """Sequence-parallel embedding from a vocabulary shard: every rank looks ALL tokens up in its own slice (zero rows
+    for ids it does not own) and a reduce-scatter over rows leaves each rank with its token shard: exactly one rank
+    contributes a non-zero row, so the bf16 sum is exact. Backward gathers the row shards and scatters into the local
+    slice only."""
+
+    @staticmethod
+    def forward(ctx, table, tokens, v0, group, world):
+        per = table.shape[0]
+        loc = tokens.reshape(-1) - v0
+        own = (loc >= 0) & (loc < per)
+        loc = loc.clamp(0, per - 1)
+        full = ops.embed_fwd(table, loc) * own[:, None].to(table.dtype)
+        T, d = full.shape
+        out = torch.empty((T // world, d), dtype=table.dtype, device=table.device)
+        dist.reduce_scatter_tensor(out, full.contiguous(), group=group)
+        ctx.table, ctx.loc, ctx.own, ctx.group, ctx.T = table, loc, own, group, T
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        table = ctx.table
+        full = torch.empty((ctx.T, dy.shape[1]), dtype=dy.dtype, device=dy.device)
+        dist.all_gather_into_tensor(full, dy.contiguous(), group=ctx.group)
+        full = full * ctx.own[:, None].to(full.dtype)
+        ops.embed_bwd(full, ctx.loc, table.main_grad, accumulate=getattr(table, "grad_started", False))
+        table.grad_started = True
+        return None, None, None, None, None
+
+
+class _VPHeadLossFn(torch.autograd.Function):
+    """Final RMSNorm (on the token shard) -> all-gather of the normalised rows -> logits of THIS rank's vocabulary
+    slice, chunk of rows by chunk -> vocabulary-parallel cross-entropy (three numbers per row exchanged, combined in
+    rank order) -> partial d(hidden) = dlogits_local @ head_slice, summed over ranks by a reduce-scatter over rows.
+    The head-slice gradient is complete locally (all tokens, own vocabulary rows). Gradients are produced in the forward
+    pass, as in the single-device head, scaled by 1 / (tokens per rank) like every other shard of this model."""
+
+    @staticmethod
+    def forward(ctx, x, rmsf, head_w, targets, eps, chunk, v0, group, world):
+        from ..parallel import vocab_parallel as VP
+        Tl, d = x.shape
+        T = Tl * world
+        hn_l, inv = ops.rmsnorm_fwd(x, rmsf, eps)
+        hn = torch.empty((T, d), dtype=hn_l.dtype, device=x.device)
+        dist.all_gather_into_tensor(hn, hn_l.contiguous(), group=group)
+        tgt = targets.reshape(-1)
+        need_grad = any(ctx.needs_input_grad[:3])
+        loss_rows = torch.empty(T, dtype=torch.float32, device=x.device)
+        dhn = torch.empty_like(hn) if need_grad else None
+        mg = head_w.main_grad
+        for r0 in range(0, T, chunk):
+            r1 = min(T, r0 + chunk)
+            logits = ops.matmul_nt(hn[r0:r1], head_w)
+            lr, dl = VP.vocab_parallel_ce(logits, tgt[r0:r1], v0, 1.0 / Tl, group=group)
+            loss_rows[r0:r1] = lr
+            if need_grad:
+                ops.matmul_nn(dl, head_w, out=dhn[r0:r1])
+                started = (r0 > 0) or getattr(head_w, "grad_started", False)
+                ops.matmul_tn(dl, hn[r0:r1], out=mg, residual=mg if started else None)
+        dhn_l = None
+        if need_grad:
+            head_w.grad_started = True
+            dhn_l = torch.empty((Tl, d), dtype=dhn.dtype, device=x.device)
+            dist.reduce_scatter_tensor(dhn_l, dhn, group=group)
+        ctx.save_for_backward(x, inv, dhn_l if dhn_l is not None else x)
+        ctx.rmsf = rmsf
+        return loss_rows.sum() / T
+
+    @staticmethod
+    def backward(ctx, dloss):
+        x, inv, dhn_l = ctx.saved_tensors
+        rmsf = ctx.rmsf
+        res = {}
+
+        def _nf(out):
+            dx, dw = ops.rmsnorm_bwd(dhn_l, x, rmsf, inv, dw_out=out)
+            res["dx"] = dx
+            return dw
+        g = _vgrad(rmsf, _nf)
+        return res["dx"], g, None, None, None, None, None, None, None
+
+
+class TPDecoderVocabParallel(TPDecoder):
+    """``TPDecoder`` whose embedding table and LM head hold only the vocabulary ids ``[r V / W, (r + 1) V / W)``.
+    The replicated segment shrinks to the norm gains; per-rank memory for the table, its two optimizer moments and the
+    logits falls by ``W``. The returned loss is the mean over ALL ``B * S`` positions and is identical on every rank."""
+
+    def __init__(self, cfg: SciAgentConfig, tp, seed: int = 0, head_chunk: int = 4096):
+        if cfg.vocab_size % (tp.world * 8):
+            raise ValueError("vocab_size / 8 must divide by the tensor-parallel size")
+        self.vper = cfg.vocab_size // tp.world
+        self.v0 = tp.rank * self.vper
+        super().__init__(cfg, tp, seed=seed, head_chunk=head_chunk)
+
+    def _vocab_shard(self, full_table):
+        return full_table[self.v0:self.v0 + self.vper]
+
+    def ordered_params(self):
+        out = []
+        for i, l in enumerate(self.layers):
+            out += [(f"layers.{i}.{n}", getattr(l, n), True, False) for n in ("wqkv", "wo", "wgu", "wd")]
+        out.append(("embed", self.embed, True, False))                 # sharded over the vocabulary: not replicated
+        if self.lm_head is not None:
+            out.append(("lm_head", self.lm_head, True, False))
+        for i, l in enumerate(self.layers):
+            out += [(f"layers.{i}.{n}", getattr(l, n), False, True) for n in ("rms_attn", "rms_ffn")]
+        out.append(("rms_final", self.rms_final, False, True))
+        return out
+
+    def _flatten(self):
+        # the parent allocated full tables; keep only this rank's slice before the flat storage is laid out
+        dev = self.embed.device
+        self.embed = nn.Parameter(torch.empty(self.vper, self.cfg.d_model, dtype=BF, device=dev))
+        if self.lm_head is not None:
+            self.lm_head = nn.Parameter(torch.empty(self.vper, self.cfg.d_model, dtype=BF, device=dev))
+        super()._flatten()
+
+    def load_from_full(self, full: GQADecoder) -> None:
+        class _View:                                                   # the parent copies whole tables: hand it slices
+            pass
+        view = _View()
+        view.embed = self._vocab_shard(full.embed)
+        view.lm_head = None if full.lm_head is None else self._vocab_shard(full.lm_head)
+        view.rms_final, view.layers = full.rms_final, full.layers
+        super().load_from_full(view)
+
+    def forward(self, tokens, targets):
+        cfg, tp = self.cfg, self.tp
+        B, S = tokens.shape
+        T = B * S
+        W = tp.world
+        if T % (W * 128):
+            raise ValueError("B*S must be a multiple of 128 * tensor-parallel size")
+        cos, sin = ops.rope_table(max(cfg.max_seq_len, S), cfg.head_dim, cfg.rope_theta, self.flat.device)
+        x = _VPEmbedFn.apply(self.embed, tokens.reshape(-1).contiguous(), self.v0, tp.group, W)
+        for i, l in enumerate(self.layers):
+            blk = _TPBlockState(cfg, tp, B, S, cos, sin, i, self.hq, self.hkv)
+            x = _TPBlockFn.apply(x, l.rms_attn, l.wqkv, l.wo, l.rms_ffn, l.wgu, l.wd, blk)
+        return _VPHeadLossFn.apply(x, self.rms_final, self.head_weight(), targets.reshape(-1).contiguous(), cfg.eps,
+                                   self.head_chunk, self.v0, tp.group, W)

@@ -31,6 +31,9 @@ def rmsnorm_fwd(x, w, eps=1e-5, out=None, want_inv=True):
         xf = x.float()
         inv = torch.rsqrt(xf.pow(2).mean(-1) + eps)
         y = (xf * inv[:, None] * w.float()).to(x.dtype)
+        if out is not None:
+            out.copy_(y)
+            y = out
         return y, (inv if want_inv else None)
     if out is None:
         out = _lib.empty((rows, cols), BF, x.device)

@@ -63,7 +63,9 @@ class TPContext:
         self.world = dist.get_world_size(group)
         self.backend = backend
         self.wait_ms = wait_ms
-        self.dev = torch.device("cuda", torch.cuda.current_device())
+        # backend "host": the NCCL arm's collectives-around-library-products on CPU tensors over a gloo group (the
+        # sharding logic of the models can then be checked on machines without a GPU)
+        self.dev = torch.device("cpu") if backend == "host" else torch.device("cuda", torch.cuda.current_device())
         self.epoch = 0
         self.rs_calls = 0
         self.pair = os.environ.get("SB_TP_PAIR", "1") != "0"   # CTA-pair kernel for all-gather -> GEMM

@@ -431,3 +431,15 @@ def test_status_watchdog_reports_timeout_and_hang_without_a_gpu():
     with pytest.raises(StepHung):
         wd2.check()
     wd2.stop()
+
+
+@pytest.mark.parametrize("world,kv,vp", [(2, 2, 0), (2, 2, 1), (4, 2, 1)])
+def test_tensor_parallel_training_on_the_host_backend_follows_the_single_device_model(world, kv, vp):
+    """The tensor-parallel decoder (and its vocabulary-parallel variant: sharded embedding, LM head and cross-entropy)
+    on gloo ranks with CPU tensors: losses and trained shards follow the single-device model, replicated parameters
+    stay identical on every rank. With 4 ranks and 2 KV heads each KV head is replicated over a group of 2 ranks."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29700 + 3 * world + vp), os.path.join(ROOT, "tests", "mp", "mp_tp_model_host.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900,
+                       env=dict(os.environ, PYTHONPATH=ROOT, SB_TP_KV=str(kv), SB_TP_VOCAB_PARALLEL=str(vp)))
+    assert r.returncode == 0 and f"TP_HOST_OK world={world} kv={kv} vp={vp}" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
