@@ -147,11 +147,17 @@ class TPDecoder(nn.Module):
         self._flatten()
         self._kv_group = None
         if self.kv_rep > 1:
+            glob = dist.get_process_group_ranks(tp.group)
+            whole_job = len(glob) == dist.get_world_size()
             for g in range(cfg.n_kv_heads):
                 ranks = list(range(g * self.kv_rep, (g + 1) * self.kv_rep))
-                grp = dist.new_group(ranks)
-                if r in ranks:
-                    self._kv_group = grp
+                if whole_job:
+                    grp = dist.new_group(ranks)
+                    if r in ranks:
+                        self._kv_group = grp
+                elif r in ranks:
+                    # the tensor-parallel group is one of several (a mesh axis): only its own members can take part
+                    self._kv_group = dist.new_group([glob[i] for i in ranks], use_local_synchronization=True)
         self.load_from_full(GQADecoder(cfg, device=dev, seed=seed))
 
     # ---------------------------------------------------------------- flat storage

@@ -53,6 +53,28 @@ class DeviceMesh:
         me = self.coords(rank)
         return [r for r in self.ranks() if all(v == me[k] for k, v in self.coords(r).items() if k != axis)]
 
+    def process_groups(self, rank: int | None = None) -> dict:
+        """``torch.distributed`` groups of the calling rank, one per mesh axis (``{"dp": group, "tp": group}``). Every
+        rank of the job must call this, in the same order: all groups of all axes are created collectively, each rank
+        keeps the ones it belongs to. The last axis varies fastest, so with ``("dp", "tp")`` a tensor-parallel group is
+        a run of consecutive ranks: the GPUs that share an NVSwitch domain on one node."""
+        import torch.distributed as dist
+        if dist.get_world_size() != self.size:
+            raise ShardingError(f"mesh of {self.size} ranks on a job of {dist.get_world_size()}")
+        rank = dist.get_rank() if rank is None else rank
+        mine = {}
+        for axis in self.axis_names:
+            seen = set()
+            for r in self.ranks():
+                members = tuple(self.group_ranks(axis, r))
+                if members in seen:
+                    continue
+                seen.add(members)
+                g = dist.new_group(list(members))
+                if rank in members:
+                    mine[axis] = g
+        return mine
+
 
 @dataclass(frozen=True)
 class PartitionSpec:

@@ -443,3 +443,15 @@ def test_tensor_parallel_training_on_the_host_backend_follows_the_single_device_
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=900,
                        env=dict(os.environ, PYTHONPATH=ROOT, SB_TP_KV=str(kv), SB_TP_VOCAB_PARALLEL=str(vp)))
     assert r.returncode == 0 and f"TP_HOST_OK world={world} kv={kv} vp={vp}" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.parametrize("dp,tp,vp", [(2, 2, 0), (2, 4, 1)])
+def test_data_parallel_times_tensor_parallel_on_a_mesh_of_gloo_ranks(dp, tp, vp):
+    """A ("dp", "tp") mesh: tensor-parallel groups are runs of consecutive ranks, replicas differ in their batch, the
+    gradient is summed over the data-parallel axis. With tp = 4 and 2 KV heads the replicated KV projections are reduced
+    inside sub-groups of each tensor-parallel group. Result: the single-device model trained on the whole batch."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={dp * tp}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29720 + dp * tp + vp), os.path.join(ROOT, "tests", "mp", "mp_dp_tp_host.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=1200,
+                       env=dict(os.environ, PYTHONPATH=ROOT, SB_DP=str(dp), SB_TP=str(tp), SB_TP_VOCAB_PARALLEL=str(vp)))
+    assert r.returncode == 0 and f"DP_TP_HOST_OK dp={dp} tp={tp} vp={vp}" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
