@@ -57,6 +57,9 @@ def cmd_info(a):
         print(f"device {p.name} sm_{p.major}{p.minor} {p.total_memory // (1 << 20)} MiB x{torch.cuda.device_count()}")
     print(f"native_cuda_lib {'present' if CUDA_LIB.exists() else 'missing'}")
     print(f"native_rt_lib {'present' if RT_LIB.exists() else 'missing'}")
+    from .utils import capability_registry as CR
+    CR.register_default_capabilities(probe=False)
+    print(f"compute_paths {CR.capability_summary()}")
     return EXIT_OK
 
 

@@ -204,7 +204,33 @@ def cmd_fuse(a):
     return EXIT_OK
 
 
+def cmd_pretrain(a):
+    """The SCIAGENT_* environment harness (flags override the environment)."""
+    import os
+    from .train.pretrain import run_from_env
+    env = dict(os.environ)
+    for flag, key in (("config", "SCIAGENT_CONFIG"), ("text", "SCIAGENT_TEXT"), ("shards", "SCIAGENT_SHARDS"), ("ckpt", "SCIAGENT_CKPT"),
+                      ("steps", "SCIAGENT_STEPS"), ("seq", "SCIAGENT_SEQ"), ("batch", "SCIAGENT_BATCH"), ("lr", "SCIAGENT_LR"),
+                      ("save", "SCIAGENT_SAVE"), ("val_frac", "SCIAGENT_VAL_FRAC"), ("telemetry", "SCIAGENT_TELEMETRY")):
+        v = getattr(a, flag)
+        if v not in (None, ""):
+            env[key] = str(v)
+    if a.preflight_only:
+        env["SCIAGENT_PREFLIGHT_ONLY"] = "1"
+    if a.require_fresh:
+        env["SCIAGENT_REQUIRE_FRESH"] = "1"
+    from . import cli
+    return run_from_env(env, device=cli._device(a.device))
+
+
 def register(sub):
+    p = sub.add_parser("pretrain")
+    for flag in ("config", "text", "shards", "ckpt", "steps", "seq", "batch", "lr", "save", "val-frac", "telemetry"):
+        p.add_argument(f"--{flag}", default=None)
+    p.add_argument("--preflight-only", action="store_true")
+    p.add_argument("--require-fresh", action="store_true")
+    p.add_argument("--device", default="auto")
+    p.set_defaults(fn=cmd_pretrain)
     p = sub.add_parser("byte-shard")
     p.add_argument("--input", "-i", nargs="+", required=True)
     p.add_argument("--output", "-o", default="./shards")

@@ -81,6 +81,21 @@ class SciAgentConfig:
     def debug():
         return SciAgentConfig(256, 64, 2, 4, 2, 128, 128, 10000.0, tie_embeddings=False)
 
+    # pretraining harness presets (scirust-sciagent/examples/cuda_pretrain.rs:64-120)
+    @staticmethod
+    def byte():
+        """Tied, vocabulary 256: raw bytes, no tokenizer."""
+        return SciAgentConfig(256, 256, 6, 8, 2, 512, 512, 10000.0)
+
+    @staticmethod
+    def demo():
+        return SciAgentConfig(512, 256, 6, 8, 2, 512, 256, 10000.0)
+
+    @staticmethod
+    def code350m():
+        """The 350M trunk on raw bytes (about 270M parameters)."""
+        return SciAgentConfig(256, 1024, 24, 16, 4, 2816, 2048, 1_000_000.0)
+
     # benchmark shapes
     @staticmethod
     def gqa_12l():
@@ -95,7 +110,9 @@ class SciAgentConfig:
     def preset(name: str) -> "SciAgentConfig":
         table = {"7b": SciAgentConfig.sciagent_7b, "350m": SciAgentConfig.sciagent_350m,
                  "small": SciAgentConfig.small, "debug": SciAgentConfig.debug,
-                 "gqa_12l": SciAgentConfig.gqa_12l, "llama3_8b": SciAgentConfig.llama3_8b}
+                 "gqa_12l": SciAgentConfig.gqa_12l, "llama3_8b": SciAgentConfig.llama3_8b, "byte": SciAgentConfig.byte,
+                 "demo": SciAgentConfig.demo, "code350m": SciAgentConfig.code350m, "large": SciAgentConfig.code350m,
+                 "byte-large": SciAgentConfig.code350m}
         if name not in table:
             raise KeyError(f"unknown model preset {name!r}; known: {sorted(table)}")
         return table[name]()

@@ -113,6 +113,35 @@ class Trainer:
             self._status.poll()
         return self.last_loss
 
+    def train_step_accumulated(self, micro_batches):
+        """One optimizer step over several micro-batches (gradient accumulation): every micro-batch runs forward and
+        backward into the SAME flat gradient (the first write overwrites, the rest accumulate), the sum is scaled by
+        ``1 / n`` inside the optimizer kernel, so activations are only ever held for one micro-batch. Returns the mean of
+        the micro-batch losses (device scalar). Equals one step on the concatenated batch up to summation order."""
+        model, c = self.model, self.cfg
+        micro_batches = list(micro_batches)
+        if not micro_batches:
+            raise ValueError("train_step_accumulated needs at least one micro-batch")
+        if hasattr(model, "finish_grads") or self.grad_reducer is not None:
+            raise ValueError("gradient accumulation is implemented for the single-process trainer")
+        model.zero_grad_flags()
+        total = None
+        for tokens in micro_batches:
+            tok = self._to_device(tokens)
+            loss = model(tok[:, :-1].contiguous(), tok[:, 1:].contiguous())
+            loss.backward()
+            total = loss.detach() if total is None else total + loss.detach()
+        scale = 1.0 / len(micro_batches)
+        grad = model.flat_grad
+        ops.sumsq(grad, out=self.grad_sumsq)                             # of the SUM; the optimizer applies scale^2 itself
+        self.step += 1
+        ops.optim_step(self.master, self.m, self.v, grad, model.flat, lr=self.schedule.lr_at(self.step - 1), beta1=c.beta1,
+                       beta2=c.beta2, eps=c.eps, weight_decay=c.weight_decay, step=self.step, decay_end=model.decay_end,
+                       grad_sumsq=self.grad_sumsq, max_grad_norm=c.max_grad_norm, grad_scale=scale, mode=c.optimizer)
+        self.grad_sumsq.mul_(scale * scale)                              # what grad_norm() reports: the averaged gradient
+        self.last_loss = total * scale
+        return self.last_loss
+
     def check_status(self) -> None:
         """Synchronising check of the device status word (checkpoint and telemetry points call it)."""
         if self._status is not None:
