@@ -33,6 +33,7 @@ def _rt():
         lib.sbrt_kv_bytes.restype = i64
         lib.sbrt_kv_append.argtypes = [vp, vp, vp]
         lib.sbrt_kv_attend.argtypes = [vp, vp, vp, i32]
+        lib.sbrt_sos_filter_f64.argtypes = [vp, i32, vp, vp, vp, i64, i64, i32]
         _cfg = True
     return lib
 
@@ -140,3 +141,14 @@ class NativeKvCache:
                 self._h = None
         except Exception:
             pass
+
+
+def sos_filter_native(sos, x, state, threads: int = 0) -> torch.Tensor:
+    """Cascade of second-order sections (direct form I) over the rows of ``x [rows, n]`` (float64); ``sos [sections, 5]``
+    = (b0, b1, b2, a1, a2); ``state [rows, sections, 4]`` is read and updated in place (it must be contiguous)."""
+    assert x.dtype == torch.float64 and sos.dtype == torch.float64 and state.dtype == torch.float64
+    assert x.is_contiguous() and sos.is_contiguous() and state.is_contiguous()
+    y = torch.empty_like(x)
+    _rt().sbrt_sos_filter_f64(sos.data_ptr(), sos.shape[0], x.data_ptr(), y.data_ptr(), state.data_ptr(), x.shape[0],
+                              x.shape[1], _threads(threads))
+    return y
