@@ -841,6 +841,8 @@ def build_parser():
     v.set_defaults(fn=cmd_verify)
     from . import cli_tools
     cli_tools.register(sub)
+    from . import cli_math
+    cli_math.register(sub)
     return p
 
 
