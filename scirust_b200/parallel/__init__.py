@@ -13,6 +13,9 @@ def __getattr__(name):
     if name == "PipelineModel":
         from .pipeline import PipelineModel
         return PipelineModel
+    if name == "InterleavedPipelineModel":
+        from .pipeline import InterleavedPipelineModel
+        return InterleavedPipelineModel
     if name == "ring_attention":
         from .context_parallel import ring_attention
         return ring_attention

@@ -221,3 +221,229 @@ class PipelineModel:
             g = self.stage.embed.main_grad
             out -= g.float().pow(2).sum()
         dist.all_reduce(out, group=self.group)     # the optimizer applies `scale` to the gradient and its norm
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# Interleaved (virtual-stage) schedule
+# ----------------------------------------------------------------------------------------------------------------------
+def interleaved_schedule(stages: int, virtual: int, micro_batches: int, rank: int) -> list[tuple[str, int, int]]:
+    """Order of work on one rank as ``(kind, chunk, micro_batch)`` with kind ``"F"`` or ``"B"``.
+
+    Every rank owns ``virtual`` chunks of layers; chunk ``v`` of rank ``r`` is global stage ``v * stages + r``, so a
+    micro-batch crosses every rank ``virtual`` times and the pipeline bubble shrinks by that factor. Forward step ``k``
+    works on chunk ``(k mod (stages * virtual)) // stages`` and micro-batch ``(k // (stages * virtual)) * stages + k mod
+    stages``; backward steps walk the chunks in the opposite order. A rank runs ``2 (stages - rank - 1) + (virtual - 1)
+    stages`` forward steps ahead, then alternates one forward with one backward, then drains. For each chunk the
+    micro-batches appear in increasing order in both directions, so gradients accumulate in the order of the
+    single-process run."""
+    P, V, M = stages, virtual, micro_batches
+    if M % P:
+        raise ValueError("the interleaved schedule needs a number of micro-batches that is a multiple of the stages")
+    if not 0 <= rank < P or V < 1:
+        raise ValueError("bad rank or virtual-stage count")
+    total = M * V
+
+    def item(k, forward):
+        in_group = k % (P * V)
+        chunk = in_group // P
+        return ("F" if forward else "B", chunk if forward else V - 1 - chunk, (k // (P * V)) * P + in_group % P)
+    warm = min(total, 2 * (P - rank - 1) + (V - 1) * P)
+    out = [item(k, True) for k in range(warm)]
+    for i in range(total - warm):
+        out.append(item(warm + i, True))
+        out.append(item(i, False))
+    out += [item(k, False) for k in range(total - warm, total)]
+    return out
+
+
+def check_schedule(stages: int, virtual: int, micro_batches: int) -> int:
+    """Replay the schedules of all ranks with asynchronous sends, blocking receives and first-in-first-out matching
+    per (sender, receiver, direction): raises on a deadlock or on a message that would be received out of order;
+    returns the number of scheduling rounds (a rank advances at most one item per round), a proxy for the makespan."""
+    P, V = stages, virtual
+    plans = [interleaved_schedule(P, V, micro_batches, r) for r in range(P)]
+    pos = [0] * P
+    queues: dict = {}
+    rounds = 0
+    while any(pos[r] < len(plans[r]) for r in range(P)):
+        progressed = False
+        sends = []
+        for r in range(P):
+            if pos[r] >= len(plans[r]):
+                continue
+            kind, v, m = plans[r][pos[r]]
+            g = v * P + r
+            first, last = g == 0, g == P * V - 1
+            if kind == "F" and not first:
+                q = queues.get(((r - 1) % P, r, "F"), [])
+                want = (v if r > 0 else v - 1, m)
+                if not q:
+                    continue
+                if q[0] != want:
+                    raise AssertionError(f"rank {r} expects activation {want}, the channel delivers {q[0]} first")
+                q.pop(0)
+            if kind == "B" and not last:
+                q = queues.get(((r + 1) % P, r, "B"), [])
+                want = (v if r < P - 1 else v + 1, m)
+                if not q:
+                    continue
+                if q[0] != want:
+                    raise AssertionError(f"rank {r} expects gradient {want}, the channel delivers {q[0]} first")
+                q.pop(0)
+            if kind == "F" and not last:
+                sends.append(((r, (r + 1) % P, "F"), (v, m)))
+            if kind == "B" and not first:
+                sends.append(((r, (r - 1) % P, "B"), (v, m)))
+            pos[r] += 1
+            progressed = True
+        for key, msg in sends:                                               # visible from the next round on
+            queues.setdefault(key, []).append(msg)
+        rounds += 1
+        if not progressed:
+            raise AssertionError(f"deadlock at positions {pos}")
+    return rounds
+
+
+class InterleavedPipelineModel(PipelineModel):
+    """``PipelineModel`` with ``virtual_stages`` chunks of layers per rank (global stage ``v * P + rank``), run in the
+    interleaved one-forward-one-backward order of ``interleaved_schedule``. The chunks of a rank sit one after the other
+    in ONE flat parameter / gradient buffer, so the trainer and the optimizer see a single stage. Activations and
+    gradients travel in two separate process groups (one per direction): each keeps its own per-pair ordering, which
+    the schedule respects (``check_schedule``), also when ``P = 2`` makes the next and the previous rank the same."""
+
+    def __init__(self, cfg: SciAgentConfig, group=None, device=None, micro_batches: int = 4, virtual_stages: int = 2, seed: int = 0):
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.virtual = virtual_stages
+        self.cfg_full = cfg
+        self.micro_batches = micro_batches
+        self.split = split_layers(cfg.n_layers, self.world * virtual_stages)
+        self.chunks, off = [], 0
+        for v in range(virtual_stages):
+            lo, hi = self.split[v * self.world + self.rank]
+            self.chunks.append((lo, hi, off))                                 # global [lo, hi) sits at local offset off
+            off += hi - lo
+        self.lo, self.hi = self.chunks[0][0], self.chunks[-1][1]
+        self.first, self.last = self.rank == 0, self.rank == self.world - 1
+        self.stage = GQADecoder(dataclasses.replace(cfg, n_layers=off), device=device, seed=seed + 1000 * self.rank)
+        self.device = self.stage.flat.device
+        self.flat, self.flat_grad, self.decay_end = self.stage.flat, self.stage.flat_grad, self.stage.decay_end
+        self.tied = cfg.tie_embeddings and self.world > 1
+        self.tie_group = dist.new_group([self._global(0), self._global(self.world - 1)]) if self.tied else None
+        members = [self._global(r) for r in range(self.world)]
+        self.fwd_group, self.bwd_group = dist.new_group(members), dist.new_group(members)
+        self._sends = []
+        self.last_losses = None
+        interleaved_schedule(self.world, virtual_stages, micro_batches, self.rank)      # validates M against P early
+
+    def load_from_full(self, full: GQADecoder) -> None:
+        with torch.no_grad():
+            for lo, hi, off in self.chunks:
+                for i in range(lo, hi):
+                    src, dst = full.layers[i], self.stage.layers[off + i - lo]
+                    for name in ("rms_attn", "wqkv", "wo", "rms_ffn", "wgu", "wd"):
+                        getattr(dst, name).copy_(getattr(src, name))
+            self.stage.embed.copy_(full.embed)
+            self.stage.rms_final.copy_(full.rms_final)
+            if full.lm_head is not None:
+                self.stage.lm_head.copy_(full.lm_head)
+
+    def local_layer(self, global_index: int):
+        for lo, hi, off in self.chunks:
+            if lo <= global_index < hi:
+                return self.stage.layers[off + global_index - lo]
+        raise IndexError(f"layer {global_index} is not on this rank")
+
+    def _isend(self, t, dst, group):
+        self._sends.append((dist.isend(t.contiguous(), self._global(dst), group=group), t))
+
+    def _recv_from(self, shape, src, group, dtype=BF):
+        t = torch.empty(shape, dtype=dtype, device=self.device)
+        dist.recv(t, self._global(src), group=group)
+        return t
+
+    def _forward_chunk(self, v, inp, tgt, scale):
+        st, cfg = self.stage, self.stage.cfg
+        B, S = inp.shape
+        P = self.world
+        g_first, g_last = self.first and v == 0, self.last and v == self.virtual - 1
+        cos, sin = ops.rope_table(max(cfg.max_seq_len, S), cfg.head_dim, cfg.rope_theta, self.device)
+        if g_first:
+            x_in = None
+            x = _EmbedFn.apply(st.embed, inp.reshape(-1))
+        else:
+            x_in = self._recv_from((B * S, cfg.d_model), (self.rank - 1) % P, self.fwd_group).requires_grad_()
+            x = x_in
+        lo, hi, off = self.chunks[v]
+        for i in range(off, off + hi - lo):
+            l = st.layers[i]
+            blk = _BlockState(cfg, B, S, cos, sin, i, None, None, st.activation_recompute)
+            x = _BlockFn.apply(x, l.rms_attn, l.wqkv, l.wo, l.rms_ffn, l.wgu, l.wd, blk)
+        if g_last:
+            loss = _HeadLossFn.apply(x, st.rms_final, st.head_weight(), tgt, cfg.eps, st.head_chunk)
+            return x_in, loss * scale, loss.detach()
+        self._isend(x.detach(), (self.rank + 1) % P, self.fwd_group)
+        return x_in, x, None
+
+    def _backward_chunk(self, v, x_in, out):
+        P = self.world
+        g_first, g_last = self.first and v == 0, self.last and v == self.virtual - 1
+        if g_last:
+            out.backward()
+        else:
+            out.backward(self._recv_from(tuple(out.shape), (self.rank + 1) % P, self.bwd_group))
+        if not g_first:
+            self._isend(x_in.grad, (self.rank - 1) % P, self.bwd_group)
+
+    def __call__(self, inp, tgt):
+        M = self.micro_batches
+        B = inp.shape[0]
+        if B % M:
+            raise ValueError("batch size must be a multiple of the number of micro-batches")
+        mb = B // M
+        live, losses = {}, []
+        for kind, v, m in interleaved_schedule(self.world, self.virtual, M, self.rank):
+            if kind == "F":
+                sl = slice(m * mb, (m + 1) * mb)
+                needs_tgt = self.last and v == self.virtual - 1
+                x_in, out, lv = self._forward_chunk(v, inp[sl], tgt[sl] if needs_tgt else None, 1.0 / M)
+                live[(v, m)] = (x_in, out)
+                if lv is not None:
+                    losses.append(lv)
+            else:
+                self._backward_chunk(v, *live.pop((v, m)))
+        self._drain()
+        if self.tied and (self.first or self.last):
+            g = self.stage.embed.main_grad if hasattr(self.stage.embed, "main_grad") else self.stage.embed.grad
+            dist.all_reduce(g, group=self.tie_group)
+        total = torch.zeros(1, dtype=torch.float32, device=self.device)
+        if self.last:
+            total += torch.stack(losses).float().sum() / M
+        dist.broadcast(total, self._global(self.world - 1), group=self.group)
+        self.last_losses = losses
+        return total[0].detach().requires_grad_()
+
+    def save_checkpoint(self, directory, step: int, loss: float, lr: float, trainer=None):
+        import json
+        from pathlib import Path
+        from ..io.checkpoint import save_sciagent_checkpoint
+        root = Path(directory) / f"step_{int(step)}"
+        root.mkdir(parents=True, exist_ok=True)
+        save_sciagent_checkpoint(self.stage, root / f"stage_{self.rank}", step, loss, lr, trainer=trainer,
+                                 extra_opt={"pipeline_stage": self.rank, "chunks": [[lo, hi] for lo, hi, _ in self.chunks]})
+        dist.barrier(group=self.group)
+        if self.rank == 0:
+            info = {"stages": self.world, "virtual_stages": self.virtual, "n_layers": self.cfg_full.n_layers,
+                    "micro_batches": self.micro_batches, "split": self.split, "step": int(step)}
+            (root / "pipeline.json").write_text(json.dumps(info, indent=2, sort_keys=True))
+        dist.barrier(group=self.group)
+        return root
+
+    def load_checkpoint(self, root, trainer=None) -> dict:
+        import json
+        from pathlib import Path
+        root = Path(root)
+        info = json.loads((root / "pipeline.json").read_text())
+        if info.get("virtual_stages", 1) != self.virtual:
+            raise ValueError(f"checkpoint was written with {info.get('virtual_stages', 1)} virtual stages per rank")
+        return super().load_checkpoint(root, trainer=trainer)
