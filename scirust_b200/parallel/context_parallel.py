@@ -14,7 +14,9 @@ every rank the same causal work (the contiguous layout gives the last rank W tim
 
 The blocks are visited in the same order on every run and merged in hop order, so results are repeatable bit for
 bit at a fixed world size. Transfers are ``torch.distributed`` point-to-point operations (NCCL between GPUs, gloo
-between CPU ranks), issued before the block's kernels so that the copy of hop t + 1 runs under the math of hop t.
+between CPU ranks). The K/V transfer of hop t + 1 is posted before the block's kernels of hop t are launched and
+waited for after them, so it runs under that math (forward and backward); the dK/dV transfer depends on the hop's
+result and is a blocking hop.
 Long-context surface of the reference: its blockwise attention oracle and planner
 (scirust-sciagent/src/flash_attention.rs:1-321); the reference itself is single-device.
 """
@@ -26,15 +28,27 @@ import torch.distributed as dist
 from ..ops import attention as att
 
 
+class _Hop:
+    """One hop of the ring in flight: ``send`` goes to rank + 1 while the same shape arrives from rank - 1. The
+    transfer is posted by the constructor; ``wait`` returns the received tensor. Between the two the caller may launch
+    kernels that READ ``send`` (it must not be written before ``wait``)."""
+
+    def __init__(self, send: torch.Tensor, group, rank: int, world: int):
+        self.send, self.recv = send, torch.empty_like(send)
+        g = (lambda r: dist.get_global_rank(group, r)) if group is not dist.group.WORLD else (lambda r: r)
+        ops_ = [dist.P2POp(dist.isend, send, g((rank + 1) % world), group),
+                dist.P2POp(dist.irecv, self.recv, g((rank - 1) % world), group)]
+        self.work = dist.batch_isend_irecv(ops_)
+
+    def wait(self) -> torch.Tensor:
+        for w in self.work:
+            w.wait()
+        return self.recv
+
+
 def _ring_exchange(send: torch.Tensor, group, rank: int, world: int) -> torch.Tensor:
-    """Send ``send`` to rank + 1, receive the same shape from rank - 1 (one hop of the ring)."""
-    recv = torch.empty_like(send)
-    g = (lambda r: dist.get_global_rank(group, r)) if group is not dist.group.WORLD else (lambda r: r)
-    ops_ = [dist.P2POp(dist.isend, send, g((rank + 1) % world), group),
-            dist.P2POp(dist.irecv, recv, g((rank - 1) % world), group)]
-    for w in dist.batch_isend_irecv(ops_):
-        w.wait()
-    return recv
+    """Blocking form: one hop, finished on return."""
+    return _Hop(send, group, rank, world).wait()
 
 
 def _merge(o, lse, o_b, lse_b):
@@ -80,7 +94,7 @@ class _RingAttention(torch.autograd.Function):
         for t in range(W):
             src = (rank - t) % W
             theirs = _chunk_ids(src, W, layout)
-            nxt = _ring_exchange(kv, group, rank, W) if t + 1 < W else None     # hop t + 1 is in flight during hop t
+            hop = _Hop(kv, group, rank, W) if t + 1 < W else None               # hop t + 1 is in flight during hop t
             for i, a in enumerate(mine):
                 for j, b in enumerate(theirs):
                     if causal and b > a:
@@ -88,7 +102,7 @@ class _RingAttention(torch.autograd.Function):
                     blk = torch.cat([qs[i], _rows(kv, B, S, nc, j)], 1)
                     o_b, lse_b = att.attention_fwd(blk, B, sc, H, Hkv, dh, causal=causal and a == b)
                     o[i], lse[i] = _merge(o[i], lse[i], o_b, lse_b)
-            kv = nxt
+            kv = hop.wait() if hop is not None else None
         out = torch.stack([x.view(B, sc, qd) for x in o], 1).reshape(B * S, qd).to(qkv.dtype)
         ctx.save_for_backward(qkv, out, torch.stack(lse, 0))
         ctx.meta = (B, S, H, Hkv, dh, group, causal, layout)
@@ -113,6 +127,7 @@ class _RingAttention(torch.autograd.Function):
         for t in range(W):
             src = (rank - t) % W
             theirs = _chunk_ids(src, W, layout)
+            hop = _Hop(kv, group, rank, W) if t + 1 < W else None               # the shard moves on under this hop's math
             for i, a in enumerate(mine):
                 for j, b in enumerate(theirs):
                     if causal and b > a:
@@ -122,9 +137,9 @@ class _RingAttention(torch.autograd.Function):
                                           causal=causal and a == b).float()
                     dq[:, i] += g[:, :qd].view(B, sc, qd)
                     dkv[:, j] += g[:, qd:].view(B, sc, kvd)
-            # shard and its gradient move on together; after the last hop the gradient is home
-            if t + 1 < W:
-                kv = _ring_exchange(kv, group, rank, W)
+            # the gradient follows its shard once this hop's share is added; after the last hop it is home
+            if hop is not None:
+                kv = hop.wait()
             dkv = _ring_exchange(dkv.reshape(B * S, kvd), group, rank, W).view(B, nc, sc, kvd)
         dqkv = torch.cat([dq.reshape(B * S, qd), dkv.reshape(B * S, kvd)], 1).to(qkv.dtype)
         return dqkv, None, None, None, None, None, None, None, None
