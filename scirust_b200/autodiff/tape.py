@@ -208,6 +208,7 @@ class Var:
     def sigmoid(self): return self._new(torch.sigmoid(self.t))
     def tanh(self): return self._new(torch.tanh(self.t))
     def gelu(self): return self._new(F.gelu(self.t))
+    def gelu_tanh(self): return self._new(F.gelu(self.t, approximate="tanh"))   # the form of tensor/parity.rs:136 and of the fused kernels
     def silu(self): return self._new(F.silu(self.t))
     __add__, __sub__, __mul__, __truediv__, __neg__ = add, sub, mul, div, neg
 
