@@ -209,6 +209,29 @@ class Var:
     def tanh(self): return self._new(torch.tanh(self.t))
     def gelu(self): return self._new(F.gelu(self.t))
     def gelu_tanh(self): return self._new(F.gelu(self.t, approximate="tanh"))   # the form of tensor/parity.rs:136 and of the fused kernels
+
+    def lgamma(self): return self._new(torch.lgamma(self.t))
+    def digamma(self): return self._new(torch.digamma(self.t))
+
+    def gather(self, axis: int, indices):
+        """``out[i][j] = x[indices[i][j]][j]`` (axis 0) or ``x[i][indices[i][j]]`` (axis 1); gradients scatter-add back."""
+        idx = torch.as_tensor(indices, dtype=torch.long, device=self.t.device).reshape(self.t.shape)
+        return self._new(torch.gather(self.t, axis, idx))
+
+    def unfold(self, axis: int, size: int, step: int):
+        """Sliding windows along ``axis``, flattened to 2-D: rows = (kept axis, window index), columns = window."""
+        u = self.t.unfold(axis, size, step)                                   # [.., windows, size] with the window axis last
+        return self._new(u.reshape(-1, size))
+
+    def conv1d(self, w, b, in_c: int, length: int, k: int, stride: int = 1):
+        """Input ``(B, C * L)`` flattened like the 2-D convolution, weight ``(out_c, in_c * K)``, bias ``(1, out_c)``."""
+        x = self.t.reshape(-1, in_c, length)
+        y = F.conv1d(x, w.t.reshape(w.t.shape[0], in_c, k), b.t.reshape(-1) if b is not None else None, stride=stride)
+        return self._new(y.reshape(y.shape[0], -1))
+
+    def cholesky(self):
+        """Lower-triangular factor of a symmetric positive-definite matrix."""
+        return self._new(torch.linalg.cholesky(self.t))
     def silu(self): return self._new(F.silu(self.t))
     __add__, __sub__, __mul__, __truediv__, __neg__ = add, sub, mul, div, neg
 

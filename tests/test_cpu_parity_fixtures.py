@@ -251,3 +251,35 @@ def test_rope_fake_quantisation_einsum_bf16_and_sparse():
         a = SP.CsrTensor(c["values"], c["colidx"], c["rowptr"], c["n"], c["m"])   # the vectors are f64, the CSR type is f32
         _close(SP.spmm_dense(a, torch.tensor(c["x"]).reshape(c["m"], 1)), c["yv"], 1e-6)
         _close(SP.spmm_dense(a, torch.tensor(c["b"]).reshape(c["m"], -1)), c["ym"], 1e-6)
+
+
+def test_special_functions_gather_unfold_conv1d_cholesky_and_sparse_solve():
+    for op in ("lgamma", "digamma"):
+        for c in _cases(f"special/{op}.json"):
+            y, g = _run(lambda t, v: getattr(v["x"], op)(), {"x": _t(c["x"], c["shape"])}, c["gout"])
+            _close(y, c["y"], 5e-5)
+            _close(g["x"], c["gx"], 1e-4)
+    for c in _cases("shape/gather.json"):
+        y, g = _run(lambda t, v: v["x"].gather(c["axis"], c["indices"]), {"x": _t(c["x"], c["shape"])}, c["gout"])
+        _close(y, c["y"])
+        _close(g["x"], c["gx"])
+    for c in _cases("shape/unfold.json"):
+        y, g = _run(lambda t, v: v["x"].unfold(c["axis"], c["size"], c["step"]), {"x": _t(c["x"], c["shape"])}, c["gout"])
+        _close(y, c["y"])
+        _close(g["x"], c["gx"])                                               # overlapping windows add their gradients
+    for c in _cases("convolution/conv1d.json"):
+        n, ic, length = c["shape"]
+        oc = c["out_shape"][1]
+        y, g = _run(lambda t, v: v["x"].conv1d(v["w"], v["b"], ic, length, c["kernel"]),
+                    {"x": _t(c["x"], [n, -1]), "w": _t(c["w"], [oc, -1]), "b": _t(c["b"], [1, -1])}, c["gout"])
+        _close(y, c["y"])
+        for k_, want in (("x", "gx"), ("w", "gw"), ("b", "gb")):
+            _close(g[k_], c[want], 5e-5)
+    for c in _cases("linalg/cholesky.json"):
+        y, _ = _run(lambda t, v: v["a"].cholesky(), {"a": _t(c["a"], c["shape"])}, None)
+        _close(y, c["y"], 5e-6)
+    for c in _cases("sparse/solve.json"):
+        n = c["n"]
+        a = SP.CsrTensor.from_dense(torch.tensor(c["a"], dtype=torch.float64).reshape(n, n).float())
+        _close(SP.solve(a, torch.tensor(c["b1"], dtype=torch.float64)), c["y1"], 1e-6)          # the CSR values are fp32
+        _close(SP.solve(a, torch.tensor(c["b2"], dtype=torch.float64).reshape(n, -1)), c["y2"], 1e-6)
