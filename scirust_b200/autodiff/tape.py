@@ -225,13 +225,20 @@ class Var:
 
     def conv1d(self, w, b, in_c: int, length: int, k: int, stride: int = 1):
         """Input ``(B, C * L)`` flattened like the 2-D convolution, weight ``(out_c, in_c * K)``, bias ``(1, out_c)``."""
+        if k > length:
+            raise TapeError(f"conv1d: kernel {k} is larger than the input length {length}")
         x = self.t.reshape(-1, in_c, length)
         y = F.conv1d(x, w.t.reshape(w.t.shape[0], in_c, k), b.t.reshape(-1) if b is not None else None, stride=stride)
         return self._new(y.reshape(y.shape[0], -1))
 
     def cholesky(self):
         """Lower-triangular factor of a symmetric positive-definite matrix."""
-        return self._new(torch.linalg.cholesky(self.t))
+        if self.t.dim() != 2 or self.t.shape[0] != self.t.shape[1]:
+            raise TapeError(f"cholesky: the matrix must be square, got {tuple(self.t.shape)}")
+        l, info = torch.linalg.cholesky_ex(self.t)
+        if int(info):
+            raise TapeError(f"cholesky: the matrix is not positive-definite (leading minor {int(info)})")
+        return self._new(l)
     def silu(self): return self._new(F.silu(self.t))
     __add__, __sub__, __mul__, __truediv__, __neg__ = add, sub, mul, div, neg
 
@@ -281,10 +288,14 @@ class Var:
     # ---- structure
     @staticmethod
     def concat_rows(vs):
+        if len({v.t.shape[1] for v in vs}) != 1:
+            raise TapeError(f"concat_rows: column counts differ: {[v.t.shape[1] for v in vs]}")
         return vs[0]._new(torch.cat([v.t for v in vs], 0))
 
     @staticmethod
     def concat_cols(vs):
+        if len({v.t.shape[0] for v in vs}) != 1:
+            raise TapeError(f"concat_cols: row counts differ: {[v.t.shape[0] for v in vs]}")
         return vs[0]._new(torch.cat([v.t for v in vs], 1))
 
     def slice_rows(self, a: int, b: int): return self._new(self.t[a:b])
@@ -332,6 +343,8 @@ class Var:
 
     # ---- convolution family: NCHW flattened to (B, C*H*W); weight (out_c, in_c*K*K)
     def conv2d(self, w, b, in_c: int, h: int, wd: int, k: int, stride: int = 1, same: bool = False):
+        if not same and (k > h or k > wd):
+            raise TapeError(f"conv2d: kernel {k} is larger than the {h} x {wd} input")
         self._same(w)
         B = self.t.shape[0]
         out_c = w.t.shape[0]

@@ -78,6 +78,8 @@ def solve(a: CsrTensor, b: torch.Tensor, tol: float = 1e-12, max_iter: int | Non
         raise ValueError("solve: the matrix must be square")
     csr = torch.sparse_csr_tensor(a.row_offsets, a.column_indices, a.values.double(), (a.rows, a.cols), check_invariants=False)
     rhs = torch.as_tensor(b, dtype=torch.float64)
+    if rhs.dim() not in (1, 2) or rhs.shape[0] != a.rows:
+        raise ValueError(f"solve: the right-hand side must have {a.rows} rows, got {tuple(rhs.shape)}")
     cols = rhs.reshape(a.rows, -1)
     out = torch.zeros_like(cols)
     for j in range(cols.shape[1]):

@@ -17,7 +17,7 @@ from scirust_b200.numerics import lowprec
 REF = os.environ.get("SCIRUST_REFERENCE_DIR") or os.path.normpath(
     os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "reference"))
 FIX = os.path.join(REF, "tests", "parity", "fixtures")
-pytestmark = pytest.mark.skipif(not os.path.isdir(FIX), reason="reference parity fixtures not mounted")
+need_fixtures = pytest.mark.skipif(not os.path.isdir(FIX), reason="reference parity fixtures not mounted")
 
 TOL = 2e-5
 
@@ -58,6 +58,7 @@ UNARY = ["acos", "asin", "atan", "cos", "cosh", "exp", "gelu", "log", "log10", "
          "sin", "sinh", "sqrt", "tan", "tanh"]
 
 
+@need_fixtures
 @pytest.mark.parametrize("op", UNARY)
 def test_elementwise_unary(op):
     for c in _cases(f"elementwise/{op}.json"):
@@ -68,6 +69,7 @@ def test_elementwise_unary(op):
         _close(g["x"], c["gx"], 5e-5)
 
 
+@need_fixtures
 @pytest.mark.parametrize("op", ["add", "sub", "mul", "div", "atan2"])
 def test_elementwise_binary_and_broadcast(op):
     for c in _cases(f"elementwise/{op}.json"):
@@ -84,6 +86,7 @@ def test_elementwise_binary_and_broadcast(op):
         _close(g["b"], c["gb"])
 
 
+@need_fixtures
 def test_pow_and_reductions():
     for c in _cases("elementwise/pow.json"):
         y, g = _run(lambda t, v: v["x"].pow(c["scalar"]), {"x": _t(c["x"], c["shape"])}, c["gout"])
@@ -98,6 +101,7 @@ def test_pow_and_reductions():
             _close(g["x"], c["gx"])
 
 
+@need_fixtures
 def test_normalisation_family():
     for op in ("softmax", "log_softmax"):
         for c in _cases(f"normalization/{op}.json"):
@@ -133,6 +137,7 @@ def test_normalisation_family():
         _close(g["x"], c["gx"], 5e-5)
 
 
+@need_fixtures
 def test_linear_family_and_losses():
     for c in _cases("linear/matmul.json"):
         k = c["shape"][1]
@@ -174,6 +179,7 @@ def test_linear_family_and_losses():
         _close(g["x"], c["gx"])
 
 
+@need_fixtures
 def test_convolution_pooling_attention_embedding():
     for c in _cases("convolution/conv2d.json"):
         n, ic, h, w = c["shape"]
@@ -203,6 +209,7 @@ def test_convolution_pooling_attention_embedding():
         _close(g["w"], c["gw"])                                               # repeated indices accumulate
 
 
+@need_fixtures
 def test_shape_operations():
     def check(c, build, inputs=None):
         y, g = _run(build, inputs or {"x": _t(c["x"], c["shape"])}, c["gout"])
@@ -228,6 +235,7 @@ def test_shape_operations():
         _close(g["b"], c["gb"])
 
 
+@need_fixtures
 def test_rope_fake_quantisation_einsum_bf16_and_sparse():
     for c in _cases("positional/rope.json"):
         tape = NdTape()
@@ -253,6 +261,7 @@ def test_rope_fake_quantisation_einsum_bf16_and_sparse():
         _close(SP.spmm_dense(a, torch.tensor(c["b"]).reshape(c["m"], -1)), c["ym"], 1e-6)
 
 
+@need_fixtures
 def test_special_functions_gather_unfold_conv1d_cholesky_and_sparse_solve():
     for op in ("lgamma", "digamma"):
         for c in _cases(f"special/{op}.json"):
@@ -283,3 +292,32 @@ def test_special_functions_gather_unfold_conv1d_cholesky_and_sparse_solve():
         a = SP.CsrTensor.from_dense(torch.tensor(c["a"], dtype=torch.float64).reshape(n, n).float())
         _close(SP.solve(a, torch.tensor(c["b1"], dtype=torch.float64)), c["y1"], 1e-6)          # the CSR values are fp32
         _close(SP.solve(a, torch.tensor(c["b2"], dtype=torch.float64).reshape(n, -1)), c["y2"], 1e-6)
+
+
+def test_error_paths_are_structured():
+    """Malformed requests raise the framework's own error types with the offending sizes, not a backend exception."""
+    from scirust_b200.autodiff.tape import TapeError
+    t = Tape()
+    x1, w1, b1 = t.input(torch.randn(1, 6)), t.input(torch.randn(2, 10)), t.input(torch.zeros(1, 2))
+    with pytest.raises(TapeError, match="kernel 5 is larger"):
+        x1.conv1d(w1, b1, 2, 3, 5)
+    with pytest.raises(TapeError, match="kernel 3 is larger"):
+        t.input(torch.randn(1, 4)).conv2d(t.input(torch.randn(1, 9)), None, 1, 2, 2, 3, 1, False)
+    with pytest.raises(TapeError, match="not positive-definite"):
+        t.input(torch.tensor([[-1.0]])).cholesky()
+    with pytest.raises(TapeError, match="must be square"):
+        t.input(torch.randn(2, 3)).cholesky()
+    V = type(x1)
+    assert V.concat_rows([t.input(torch.zeros(2, 3)), t.input(torch.zeros(1, 3))]).t.shape == (3, 3)     # unequal along the joined axis is fine
+    with pytest.raises(TapeError, match="column counts differ"):
+        V.concat_rows([t.input(torch.zeros(2, 3)), t.input(torch.zeros(1, 4))])
+    with pytest.raises(ValueError, match="rows\\+1"):
+        SP.CsrTensor([], [], [], 0, 0)
+    with pytest.raises(ValueError, match="must have 3 rows"):
+        SP.solve(SP.CsrTensor.from_dense(torch.eye(3)), torch.zeros(4))
+    with pytest.raises(ValueError, match="dense operand"):
+        SP.spmm_dense(SP.CsrTensor.from_dense(torch.eye(3)), torch.zeros(2, 1))
+    with pytest.raises(ValueError, match="values.len"):
+        SP.CsrTensor([1.0, 2.0], [0], [0, 2], 1, 2)
+    assert ES.einsum("ij,ij->", torch.ones(2, 2), torch.ones(2, 2)).dim() == 0                               # a scalar result has rank zero
+    assert t.input(torch.randn(1, 25)).avg_pool2d(1, 5, 5, 2, 2).t.shape == (1, 4)                           # the odd border is dropped
