@@ -109,3 +109,50 @@ def test_training_session_minimises_an_energy_and_rejects_non_finite_loss():
     with pytest.raises(Q.QuantumError):
         sess.train_step(vc, lambda e, _t: e.sum() * float("nan"), x, None)
     assert torch.equal(before, vc.theta.detach())
+
+
+def _hybrid(seed=0):
+    b = V.VariationalCircuitBuilder(1)
+    b.angle_encoding("y", [0])
+    b.variational_ansatz(1, ["y", "z"], "none")
+    b.measure_z([0])
+    torch.manual_seed(seed)
+    return torch.nn.Sequential(torch.nn.Linear(2, 1), b.build(seed=seed), torch.nn.Linear(1, 1))
+
+
+def test_quantum_module_composes_with_classical_layers_state_round_trips_and_trains_from_a_loader():
+    model = _hybrid()
+    x = torch.randn(6, 2, generator=torch.Generator().manual_seed(1))
+    out = model(x)
+    assert out.shape == (6, 1)
+    out.sum().backward()
+    assert all(p.grad is not None and bool(torch.isfinite(p.grad).all()) for p in model.parameters())   # gradients cross the circuit
+    state = model.state_dict()
+    assert "1.theta" in state and state["1.theta"].shape == (1, 2)                                       # the circuit's angles are ordinary state
+    other = _hybrid(seed=9)
+    assert not torch.allclose(other(x), model(x))
+    other.load_state_dict(state)
+    assert torch.equal(other(x), model(x))
+    bad = dict(state)
+    bad["1.theta"] = torch.zeros(1, 3)
+    with pytest.raises(RuntimeError):
+        other.load_state_dict(bad)
+    with pytest.raises(Q.QuantumError):
+        model[1](torch.zeros(4, 3))                                                                      # wrong feature count: the circuit's own error
+    target = torch.sin(x[:, :1] + 0.5 * x[:, 1:])
+    data = torch.utils.data.DataLoader(torch.utils.data.TensorDataset(x, target), batch_size=3, shuffle=False)
+    opt = torch.optim.Adam(model.parameters(), lr=0.05)
+    sess = V.TrainingSession(opt)
+    first = sess.train_epoch(model, torch.nn.functional.mse_loss, data, epoch=0)
+    for ep in range(1, 40):
+        last = sess.train_epoch(model, torch.nn.functional.mse_loss, data, epoch=ep)
+    assert first.batches == 2 and last.mean_loss < 0.5 * first.mean_loss and sess.steps == 80
+    import copy
+    opt_state = copy.deepcopy(opt.state_dict())                                                          # as a checkpoint on disk would hold it
+    resumed, ropt = _hybrid(seed=3), None
+    resumed.load_state_dict(model.state_dict())
+    ropt = torch.optim.Adam(resumed.parameters(), lr=0.05)
+    ropt.load_state_dict(opt_state)
+    a = V.TrainingSession(opt).train_epoch(model, torch.nn.functional.mse_loss, data)
+    b2 = V.TrainingSession(ropt).train_epoch(resumed, torch.nn.functional.mse_loss, data)
+    assert a.mean_loss == b2.mean_loss and torch.equal(model[1].theta, resumed[1].theta)                  # exact resume
